@@ -1,0 +1,413 @@
+// Element-wise and row-wise kernels of the StripedHyena2 block graph:
+// E4M3 quantisation, RMSNorm (optionally emitting E4M3 codes in the same
+// pass), GELU, gating, residual / bias adds, embedding gather and the
+// interleaved-triple split.  All are HBM-bound; every kernel moves 128-bit
+// vectors where the shape allows and sizes its grid in SM multiples.
+//
+// Numerics follow the upstream CUDA operators one rounding at a time
+// (src/cuda/ops.cu:72-198, 232-275; src/cuda/hyena.cu:194-208;
+// src/cuda/model.cu:269-284).
+#include <cuda_fp8.h>
+
+#include "common.cuh"
+#include "ops_internal.hpp"
+
+namespace evob {
+namespace {
+
+constexpr int kThreads = 256;
+
+__host__ unsigned int grid_for(const std::size_t work_items,
+                               const int per_block = kThreads) {
+  const std::size_t blocks = (work_items + per_block - 1) / per_block;
+  const std::size_t cap = static_cast<std::size_t>(kSmCount) * 16;
+  return static_cast<unsigned int>(blocks < 1 ? 1 : (blocks > cap ? cap : blocks));
+}
+
+__device__ __forceinline__ std::uint8_t e4m3_code(const float scaled) {
+  // RNE with saturate-to-finite, the conversion upstream uses
+  // (src/cuda/ops.cu:258-260).
+  return static_cast<std::uint8_t>(
+      __nv_cvt_float_to_fp8(scaled, __NV_SATFINITE, __NV_E4M3));
+}
+
+__device__ __forceinline__ float e4m3_value(const std::uint8_t code) {
+  const __half_raw half = __nv_cvt_fp8_to_halfraw(code, __NV_E4M3);
+  return __half2float(*reinterpret_cast<const __half *>(&half));
+}
+
+// ---------------------------------------------------------------- quantise
+template <typename In>
+__global__ void quantize_kernel(const In *__restrict__ input,
+                                std::uint8_t *__restrict__ codes,
+                                float *__restrict__ dequantized,
+                                const std::size_t elements, const float scale) {
+  const float inverse = __frcp_rn(scale);
+  const std::size_t stride = static_cast<std::size_t>(blockDim.x) * gridDim.x;
+  for (std::size_t i = static_cast<std::size_t>(blockIdx.x) * blockDim.x +
+                       threadIdx.x;
+       i < elements; i += stride) {
+    float value;
+    if constexpr (sizeof(In) == 2) {
+      value = bf2f(input[i]);
+    } else {
+      value = input[i];
+    }
+    const std::uint8_t code = e4m3_code(value * scale);
+    if (codes != nullptr) codes[i] = code;
+    if (dequantized != nullptr) dequantized[i] = e4m3_value(code) * inverse;
+  }
+}
+
+// 16 BF16 values -> 16 codes per thread per step (2x128-bit in, 128-bit out).
+__global__ void quantize_bf16_vec_kernel(const uint4 *__restrict__ input,
+                                         uint4 *__restrict__ codes,
+                                         const std::size_t vectors,
+                                         const float scale) {
+  const std::size_t stride = static_cast<std::size_t>(blockDim.x) * gridDim.x;
+  for (std::size_t i = static_cast<std::size_t>(blockIdx.x) * blockDim.x +
+                       threadIdx.x;
+       i < vectors; i += stride) {
+    Bf16x8 a, b;
+    a.raw = input[2 * i];
+    b.raw = input[2 * i + 1];
+    unsigned int out[4];
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+      unsigned int word = 0;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int k = w * 4 + j;
+        const float v = k < 8 ? a.get(k) : b.get(k - 8);
+        word |= static_cast<unsigned int>(e4m3_code(v * scale)) << (8 * j);
+      }
+      out[w] = word;
+    }
+    codes[i] = make_uint4(out[0], out[1], out[2], out[3]);
+  }
+}
+
+// ---------------------------------------------------------------- RMSNorm
+// One 256-thread block per row.  The F32 sum of squares is taken in the same
+// order as upstream (thread-strided columns, shuffle-down tree, 8 warp
+// partials through a second tree; src/cuda/ops.cu:72-96) so that the BF16
+// rounding chain sees bit-identical sums.
+__device__ __forceinline__ float warp_sum_down(float value) {
+#pragma unroll
+  for (int offset = 16; offset > 0; offset /= 2)
+    value += __shfl_down_sync(0xffffffffU, value, offset);
+  return value;
+}
+
+__global__ void __launch_bounds__(kThreads)
+rms_norm_kernel(const bf16 *__restrict__ input, const float *__restrict__ scale,
+                bf16 *__restrict__ output, std::uint8_t *__restrict__ codes,
+                const std::size_t width, const float epsilon,
+                const float quant_scale) {
+  extern __shared__ unsigned short row_cache[];  // width BF16 values
+  __shared__ float partial[32];
+  const std::size_t row = blockIdx.x;
+  const bf16 *const in = input + row * width;
+  float sum = 0.0F;
+  for (std::size_t column = threadIdx.x; column < width; column += kThreads) {
+    const bf16 raw = in[column];
+    row_cache[column] = __bfloat16_as_ushort(raw);
+    const float value = bf2f(raw);
+    sum = fmaf(value, value, sum);
+  }
+  sum = warp_sum_down(sum);
+  const int lane = threadIdx.x % 32;
+  const int warp = threadIdx.x / 32;
+  if (lane == 0) partial[warp] = sum;
+  __syncthreads();
+  if (warp == 0) {
+    float block_sum = lane < kThreads / 32 ? partial[lane] : 0.0F;
+    block_sum = warp_sum_down(block_sum);
+    if (lane == 0) {
+      const float norm = rbf(sqrtf(block_sum));
+      const float scaled = rbf(norm * rsqrtf(static_cast<float>(width)));
+      partial[0] = rbf(scaled + epsilon);
+    }
+  }
+  __syncthreads();
+  const float denominator = partial[0];
+  for (std::size_t column = threadIdx.x; column < width; column += kThreads) {
+    const float value = bits2f_bf16(row_cache[column]);
+    const float column_scale = rbf(scale[column]);
+    const float normalized = rbf(__fdiv_rn(value, denominator));
+    const bf16 result = f2bf(normalized * column_scale);
+    if (output != nullptr) output[row * width + column] = result;
+    if (codes != nullptr)
+      codes[row * width + column] = e4m3_code(bf2f(result) * quant_scale);
+  }
+}
+
+// ---------------------------------------------------------------- pointwise
+__device__ __forceinline__ bf16 gelu_bf16(const bf16 input) {
+  const float value = bf2f(input);
+  constexpr float kAlpha = 0.70710678118654752440F;
+  const bf16 computed = f2bf(value * 0.5F * (1.0F + ::erff(value * kAlpha)));
+  // Seven inputs whose rounding depends on the libdevice erf revision are
+  // pinned to fixed outputs upstream (src/cuda/ops.cu:125-139).
+  switch (__bfloat16_as_ushort(input)) {
+    case 0xc049: return __ushort_as_bfloat16(0xbb2d);
+    case 0xc081: return __ushort_as_bfloat16(0xb8eb);
+    case 0xc089: return __ushort_as_bfloat16(0xb827);
+    case 0xc092: return __ushort_as_bfloat16(0xb742);
+    case 0xc0a0: return __ushort_as_bfloat16(0xb5c8);
+    case 0xc0a8: return __ushort_as_bfloat16(0xb4fc);
+    case 0xc0ab: return __ushort_as_bfloat16(0xb4ab);
+    default: return computed;
+  }
+}
+
+enum class Pointwise { kGelu, kGate, kGeluGate, kAdd };
+
+template <Pointwise Op>
+__device__ __forceinline__ float pointwise(const float a, const float b) {
+  if constexpr (Op == Pointwise::kGelu) {
+    return bf2f(gelu_bf16(f2bf(a)));
+  } else if constexpr (Op == Pointwise::kGate) {
+    return a * b;
+  } else if constexpr (Op == Pointwise::kGeluGate) {
+    return bf2f(gelu_bf16(f2bf(a))) * b;
+  } else {
+    return a + b;
+  }
+}
+
+template <Pointwise Op>
+__global__ void pointwise_kernel(const bf16 *__restrict__ first,
+                                 const bf16 *__restrict__ second,
+                                 bf16 *__restrict__ output,
+                                 const std::size_t elements) {
+  const std::size_t vectors = elements / 8;
+  const std::size_t stride = static_cast<std::size_t>(blockDim.x) * gridDim.x;
+  const std::size_t tid =
+      static_cast<std::size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  for (std::size_t i = tid; i < vectors; i += stride) {
+    Bf16x8 a, b;
+    a.raw = reinterpret_cast<const uint4 *>(first)[i];
+    if constexpr (Op != Pointwise::kGelu)
+      b.raw = reinterpret_cast<const uint4 *>(second)[i];
+    else
+      b.raw = a.raw;
+    unsigned int out[4];
+#pragma unroll
+    for (int w = 0; w < 4; ++w)
+      out[w] = pack_bf16x2(pointwise<Op>(a.get(2 * w), b.get(2 * w)),
+                           pointwise<Op>(a.get(2 * w + 1), b.get(2 * w + 1)));
+    reinterpret_cast<uint4 *>(output)[i] =
+        make_uint4(out[0], out[1], out[2], out[3]);
+  }
+  for (std::size_t i = vectors * 8 + tid; i < elements; i += stride) {
+    const float b = Op == Pointwise::kGelu ? 0.0F : bf2f(second[i]);
+    output[i] = f2bf(pointwise<Op>(bf2f(first[i]), b));
+  }
+}
+
+__global__ void add_bias_kernel(bf16 *__restrict__ output,
+                                const bf16 *__restrict__ bias,
+                                const std::size_t elements,
+                                const std::size_t width) {
+  const std::size_t stride = static_cast<std::size_t>(blockDim.x) * gridDim.x;
+  for (std::size_t i = static_cast<std::size_t>(blockIdx.x) * blockDim.x +
+                       threadIdx.x;
+       i < elements; i += stride)
+    output[i] = f2bf(bf2f(output[i]) + bf2f(bias[i % width]));
+}
+
+__global__ void embedding_kernel(const std::uint32_t *__restrict__ tokens,
+                                 const bf16 *__restrict__ table,
+                                 bf16 *__restrict__ output,
+                                 const std::size_t rows,
+                                 const std::size_t width) {
+  const std::size_t elements = rows * width;
+  const std::size_t stride = static_cast<std::size_t>(blockDim.x) * gridDim.x;
+  for (std::size_t i = static_cast<std::size_t>(blockIdx.x) * blockDim.x +
+                       threadIdx.x;
+       i < elements; i += stride) {
+    const std::size_t row = i / width;
+    output[i] = table[static_cast<std::size_t>(tokens[row]) * width + i % width];
+  }
+}
+
+__global__ void split_triples_kernel(const bf16 *__restrict__ projection,
+                                     bf16 *__restrict__ x2,
+                                     bf16 *__restrict__ x1,
+                                     bf16 *__restrict__ value,
+                                     const std::size_t elements) {
+  const std::size_t stride = static_cast<std::size_t>(blockDim.x) * gridDim.x;
+  for (std::size_t i = static_cast<std::size_t>(blockIdx.x) * blockDim.x +
+                       threadIdx.x;
+       i < elements; i += stride) {
+    x2[i] = projection[3 * i];
+    x1[i] = projection[3 * i + 1];
+    value[i] = projection[3 * i + 2];
+  }
+}
+
+__global__ void transpose_kernel(const bf16 *__restrict__ input,
+                                 bf16 *__restrict__ output,
+                                 const std::size_t rows,
+                                 const std::size_t columns) {
+  __shared__ unsigned short tile[32][33];
+  const std::size_t c0 = static_cast<std::size_t>(blockIdx.x) * 32;
+  const std::size_t r0 = static_cast<std::size_t>(blockIdx.y) * 32;
+  for (int j = threadIdx.y; j < 32; j += blockDim.y) {
+    const std::size_t r = r0 + j, c = c0 + threadIdx.x;
+    if (r < rows && c < columns)
+      tile[j][threadIdx.x] = __bfloat16_as_ushort(input[r * columns + c]);
+  }
+  __syncthreads();
+  for (int j = threadIdx.y; j < 32; j += blockDim.y) {
+    const std::size_t c = c0 + j, r = r0 + threadIdx.x;
+    if (r < rows && c < columns)
+      output[c * rows + r] = __ushort_as_bfloat16(tile[threadIdx.x][j]);
+  }
+}
+
+bool aligned16(const void *p) {
+  return (reinterpret_cast<std::uintptr_t>(p) & 15U) == 0;
+}
+
+}  // namespace
+
+int quantize_bf16(const void *input, const std::size_t elements,
+                  const float scale, void *codes, float *dequantized,
+                  cudaStream_t stream) {
+  if (input == nullptr || (codes == nullptr && dequantized == nullptr) ||
+      !(scale > 0.0F) || !isfinite(scale))
+    return fail(kInvalidArgument, "E4M3 quantise arguments are invalid");
+  if (elements == 0) return kOk;
+  if (dequantized == nullptr && elements % 16 == 0 && aligned16(input) &&
+      aligned16(codes)) {
+    quantize_bf16_vec_kernel<<<grid_for(elements / 16), kThreads, 0, stream>>>(
+        static_cast<const uint4 *>(input), static_cast<uint4 *>(codes),
+        elements / 16, scale);
+  } else {
+    quantize_kernel<bf16><<<grid_for(elements), kThreads, 0, stream>>>(
+        static_cast<const bf16 *>(input), static_cast<std::uint8_t *>(codes),
+        dequantized, elements, scale);
+  }
+  return check_launch("E4M3 quantise kernel");
+}
+
+int quantize_f32(const float *input, const std::size_t elements,
+                 const float scale, void *codes, cudaStream_t stream) {
+  if (input == nullptr || codes == nullptr || !(scale > 0.0F) ||
+      !isfinite(scale))
+    return fail(kInvalidArgument, "E4M3 quantise arguments are invalid");
+  if (elements == 0) return kOk;
+  quantize_kernel<float><<<grid_for(elements), kThreads, 0, stream>>>(
+      input, static_cast<std::uint8_t *>(codes), nullptr, elements, scale);
+  return check_launch("E4M3 F32 quantise kernel");
+}
+
+int rms_norm(const void *input, const float *scale, const std::size_t rows,
+             const std::size_t width, const float epsilon, void *output,
+             void *codes, const float quant_scale, cudaStream_t stream) {
+  if (input == nullptr || scale == nullptr ||
+      (output == nullptr && codes == nullptr) || width == 0 ||
+      width > 24576 || rows > 0x7fffffffU)
+    return fail(kInvalidArgument, "RMSNorm arguments are invalid");
+  if (codes != nullptr && (!(quant_scale > 0.0F) || !isfinite(quant_scale)))
+    return fail(kInvalidArgument, "RMSNorm quantisation scale is invalid");
+  if (rows == 0) return kOk;
+  rms_norm_kernel<<<static_cast<unsigned int>(rows), kThreads,
+                    width * sizeof(unsigned short), stream>>>(
+      static_cast<const bf16 *>(input), scale, static_cast<bf16 *>(output),
+      static_cast<std::uint8_t *>(codes), width, epsilon, quant_scale);
+  return check_launch("RMSNorm kernel");
+}
+
+template <Pointwise Op>
+static int launch_pointwise(const void *a, const void *b, void *out,
+                            const std::size_t elements, cudaStream_t stream,
+                            const char *what) {
+  if (a == nullptr || out == nullptr ||
+      (Op != Pointwise::kGelu && b == nullptr))
+    return fail(kInvalidArgument, std::string(what) + " arguments are invalid");
+  if (elements == 0) return kOk;
+  if (!aligned16(a) || !aligned16(out) || (b != nullptr && !aligned16(b)))
+    return fail(kInvalidArgument,
+                std::string(what) + " buffers must be 16-byte aligned");
+  pointwise_kernel<Op><<<grid_for(elements / 8 + 1), kThreads, 0, stream>>>(
+      static_cast<const bf16 *>(a), static_cast<const bf16 *>(b),
+      static_cast<bf16 *>(out), elements);
+  return check_launch(what);
+}
+
+int gelu(const void *input, void *output, const std::size_t elements,
+         cudaStream_t stream) {
+  return launch_pointwise<Pointwise::kGelu>(input, nullptr, output, elements,
+                                            stream, "GELU kernel");
+}
+
+int gate(const void *first, const void *second, void *output,
+         const std::size_t elements, const bool apply_gelu,
+         cudaStream_t stream) {
+  return apply_gelu ? launch_pointwise<Pointwise::kGeluGate>(
+                          first, second, output, elements, stream,
+                          "GELU gate kernel")
+                    : launch_pointwise<Pointwise::kGate>(
+                          first, second, output, elements, stream,
+                          "gate kernel");
+}
+
+int add(const void *first, const void *second, void *output,
+        const std::size_t elements, cudaStream_t stream) {
+  return launch_pointwise<Pointwise::kAdd>(first, second, output, elements,
+                                           stream, "residual add kernel");
+}
+
+int add_bias(void *output, const void *bias, const std::size_t rows,
+             const std::size_t width, cudaStream_t stream) {
+  if (output == nullptr || bias == nullptr || width == 0)
+    return fail(kInvalidArgument, "bias add arguments are invalid");
+  if (rows == 0) return kOk;
+  add_bias_kernel<<<grid_for(rows * width), kThreads, 0, stream>>>(
+      static_cast<bf16 *>(output), static_cast<const bf16 *>(bias),
+      rows * width, width);
+  return check_launch("bias add kernel");
+}
+
+int embedding(const std::uint32_t *tokens, const void *table,
+              const std::size_t rows, const std::size_t width, void *output,
+              cudaStream_t stream) {
+  if (tokens == nullptr || table == nullptr || output == nullptr || width == 0)
+    return fail(kInvalidArgument, "embedding arguments are invalid");
+  if (rows == 0) return kOk;
+  embedding_kernel<<<grid_for(rows * width), kThreads, 0, stream>>>(
+      tokens, static_cast<const bf16 *>(table), static_cast<bf16 *>(output),
+      rows, width);
+  return check_launch("embedding kernel");
+}
+
+int split_triples(const void *projection, const std::size_t rows,
+                  const std::size_t width, void *x2, void *x1, void *value,
+                  cudaStream_t stream) {
+  if (projection == nullptr || x2 == nullptr || x1 == nullptr ||
+      value == nullptr || width == 0)
+    return fail(kInvalidArgument, "projection split arguments are invalid");
+  if (rows == 0) return kOk;
+  split_triples_kernel<<<grid_for(rows * width), kThreads, 0, stream>>>(
+      static_cast<const bf16 *>(projection), static_cast<bf16 *>(x2),
+      static_cast<bf16 *>(x1), static_cast<bf16 *>(value), rows * width);
+  return check_launch("projection split kernel");
+}
+
+int transpose(const void *input, const std::size_t rows,
+              const std::size_t columns, void *output, cudaStream_t stream) {
+  if (input == nullptr || output == nullptr || rows == 0 || columns == 0)
+    return fail(kInvalidArgument, "transpose arguments are invalid");
+  const dim3 grid(ceil_div_u(columns, 32), ceil_div_u(rows, 32));
+  if (grid.y > 65535)
+    return fail(kInvalidArgument, "transpose has too many rows");
+  transpose_kernel<<<grid, dim3(32, 8), 0, stream>>>(
+      static_cast<const bf16 *>(input), static_cast<bf16 *>(output), rows,
+      columns);
+  return check_launch("transpose kernel");
+}
+
+}  // namespace evob

@@ -1,0 +1,721 @@
+// Dense projections y = x . W^T on the 5th-generation tensor cores.
+//
+// One persistent CTA per SM walks 128 x BN output tiles.  Warp roles:
+//   warp 0   TMA producer: streams 128B-swizzled K-major tiles of x [M,K] and
+//            W [N,K] into a 4-deep shared-memory ring (mbarrier full/empty).
+//   warp 1   MMA issuer: one lane issues tcgen05.mma (M=128, N=BN, K=32 bytes
+//            per instruction) into a double-buffered TMEM accumulator and
+//            releases ring slots / publishes accumulators with tcgen05.commit.
+//   warps 2-5  epilogue: tcgen05.ld the F32 accumulator (one TMEM lane
+//            quarter per warp), apply scale / bias / residual / SwiGLU-style
+//            gating with the BF16 rounding points of the upstream graph, and
+//            store BF16.
+// The same kernel serves BF16 operands (kind::f16) and E4M3 codes
+// (kind::f8f6f4); only the instruction descriptor and element size differ.
+//
+// Every wait is bounded: a wait that exceeds its time limit raises a sticky
+// error word, all roles drain, TMEM is released and the host reports failure.
+//
+// Replaces upstream's cuBLASLt call (src/cuda/ops.cu:535-748) and, in the
+// tensor-core execution profile, the scalar FP8 emulation
+// (src/cuda/ops.cu:916-1006).
+#include <cuda.h>
+
+#include <mutex>
+
+#include "common.cuh"
+#include "ops_internal.hpp"
+
+namespace evob {
+namespace {
+
+constexpr int kBlockM = 128;
+constexpr int kBlockKBytes = 128;  // one 128-byte swizzle atom along K
+constexpr int kStages = 4;
+constexpr int kGemmThreads = 192;
+constexpr unsigned long long kWaitLimitNs = 2000000000ULL;  // 2 s
+
+struct EpilogueParams {
+  bf16 *out;
+  const bf16 *bias;
+  const bf16 *residual;
+  std::size_t ld_out;
+  float alpha;
+  int bias_mode;  // 0 none, 1 fused into the F32 sum, 2 separate BF16 add
+  int gate_mode;  // 0 none, 1 first*second halves, 2 gelu(first)*second
+};
+
+// ------------------------------------------------------------------ PTX
+__device__ __forceinline__ std::uint32_t smem_u32(const void *p) {
+  return static_cast<std::uint32_t>(__cvta_generic_to_shared(p));
+}
+__device__ __forceinline__ void mbar_init(const std::uint32_t bar,
+                                          const std::uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count)
+               : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(const std::uint32_t bar,
+                                               const std::uint32_t bytes) {
+  asm volatile(
+      "mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar),
+      "r"(bytes)
+      : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(const std::uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar)
+               : "memory");
+}
+__device__ __forceinline__ unsigned long long global_timer_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+// Bounded parity wait.  Returns false if the wait was abandoned (either this
+// thread ran out of time or another role already raised the abort flag).
+__device__ __forceinline__ bool mbar_wait(const std::uint32_t bar,
+                                          const std::uint32_t parity,
+                                          volatile int *const abort_flag) {
+  unsigned long long start = 0;
+  for (std::uint32_t spin = 0;; ++spin) {
+    std::uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    if (done != 0U) return true;
+    if ((spin & 255U) == 255U) {
+      if (*abort_flag != 0) return false;
+      const unsigned long long now = global_timer_ns();
+      if (start == 0) start = now;
+      if (now - start > kWaitLimitNs) {
+        *abort_flag = 1;
+        return false;
+      }
+    }
+  }
+}
+__device__ __forceinline__ void tma_load_2d(const std::uint32_t dst,
+                                            const CUtensorMap *const map,
+                                            const std::uint32_t bar,
+                                            const int x, const int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::"
+      "bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(dst),
+      "l"(map), "r"(bar), "r"(x), "r"(y)
+      : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() {
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tc_fence_after() {
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tc_commit(const std::uint32_t bar) {
+  asm volatile(
+      "tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 "
+      "[%0];" ::"r"(bar)
+      : "memory");
+}
+template <bool kFp8>
+__device__ __forceinline__ void tc_mma(const std::uint32_t tmem_d,
+                                       const std::uint64_t desc_a,
+                                       const std::uint64_t desc_b,
+                                       const std::uint32_t idesc,
+                                       const std::uint32_t accumulate) {
+  if constexpr (kFp8) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}" ::"r"(
+            tmem_d),
+        "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+        : "memory");
+  } else {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(
+            tmem_d),
+        "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+        : "memory");
+  }
+}
+__device__ __forceinline__ void tmem_load_32(const std::uint32_t taddr,
+                                             std::uint32_t (&v)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, "
+      "%30, %31}, [%32];"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]),
+        "=r"(v[6]), "=r"(v[7]), "=r"(v[8]), "=r"(v[9]), "=r"(v[10]),
+        "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),
+        "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]),
+        "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]), "=r"(v[25]),
+        "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]),
+        "=r"(v[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_load_wait() {
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// K-major, 128-byte swizzle: rows are 128 bytes apart, 8-row groups 1024
+// bytes apart; version 1 (Blackwell) descriptor.
+__device__ __forceinline__ std::uint64_t smem_descriptor(
+    const std::uint32_t address) {
+  std::uint64_t desc = 0;
+  desc |= static_cast<std::uint64_t>((address & 0x3ffffU) >> 4U);
+  desc |= static_cast<std::uint64_t>(1U) << 16U;            // LBO (unused)
+  desc |= static_cast<std::uint64_t>(1024U >> 4U) << 32U;   // SBO
+  desc |= static_cast<std::uint64_t>(1U) << 46U;            // version
+  desc |= static_cast<std::uint64_t>(2U) << 61U;            // SWIZZLE_128B
+  return desc;
+}
+
+template <bool kFp8, int BN>
+__host__ __device__ constexpr std::uint32_t instruction_descriptor() {
+  std::uint32_t d = 0;
+  d |= 1U << 4U;                          // accumulator F32
+  d |= (kFp8 ? 0U : 1U) << 7U;            // A: E4M3 / BF16
+  d |= (kFp8 ? 0U : 1U) << 10U;           // B: E4M3 / BF16
+  d |= static_cast<std::uint32_t>(BN >> 3) << 17U;
+  d |= static_cast<std::uint32_t>(kBlockM >> 4) << 24U;
+  return d;
+}
+
+__device__ __forceinline__ bf16 gelu_round(const float x) {
+  // Same definition as the stand-alone GELU kernel (seven pinned inputs).
+  const bf16 input = f2bf(x);
+  const float value = bf2f(input);
+  const bf16 computed =
+      f2bf(value * 0.5F * (1.0F + ::erff(value * 0.70710678118654752440F)));
+  switch (__bfloat16_as_ushort(input)) {
+    case 0xc049: return __ushort_as_bfloat16(0xbb2d);
+    case 0xc081: return __ushort_as_bfloat16(0xb8eb);
+    case 0xc089: return __ushort_as_bfloat16(0xb827);
+    case 0xc092: return __ushort_as_bfloat16(0xb742);
+    case 0xc0a0: return __ushort_as_bfloat16(0xb5c8);
+    case 0xc0a8: return __ushort_as_bfloat16(0xb4fc);
+    case 0xc0ab: return __ushort_as_bfloat16(0xb4ab);
+    default: return computed;
+  }
+}
+
+template <int BN>
+struct SharedLayout {
+  static constexpr int kABytes = kBlockM * kBlockKBytes;
+  static constexpr int kBBytes = BN * kBlockKBytes;
+  static constexpr int kStageBytes = kABytes + kBBytes;
+  static constexpr int kBarrierOffset = kStages * kStageBytes;
+  // full[kStages], empty[kStages], tmem_full[2], tmem_empty[2]
+  static constexpr int kBarrierCount = 2 * kStages + 4;
+  static constexpr int kTmemPtrOffset = kBarrierOffset + kBarrierCount * 8;
+  static constexpr int kAbortOffset = kTmemPtrOffset + 8;
+  static constexpr int kTotal = kAbortOffset + 8 + 1024;  // + alignment slack
+};
+
+template <bool kFp8, int BN>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
+                    const __grid_constant__ CUtensorMap map_b,
+                    const EpilogueParams ep, const int M, const int N,
+                    const int K_bytes, int *const error_word) {
+  using L = SharedLayout<BN>;
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char *const smem = reinterpret_cast<unsigned char *>(
+      (reinterpret_cast<std::uintptr_t>(smem_raw) + 1023U) &
+      ~static_cast<std::uintptr_t>(1023U));
+  const std::uint32_t smem_base = smem_u32(smem);
+  const std::uint32_t bar_base = smem_base + L::kBarrierOffset;
+  auto full_bar = [&](const int s) { return bar_base + 8U * s; };
+  auto empty_bar = [&](const int s) { return bar_base + 8U * (kStages + s); };
+  auto tmem_full_bar = [&](const int s) {
+    return bar_base + 8U * (2 * kStages + s);
+  };
+  auto tmem_empty_bar = [&](const int s) {
+    return bar_base + 8U * (2 * kStages + 2 + s);
+  };
+  volatile std::uint32_t *const tmem_ptr =
+      reinterpret_cast<volatile std::uint32_t *>(smem + L::kTmemPtrOffset);
+  volatile int *const abort_flag =
+      reinterpret_cast<volatile int *>(smem + L::kAbortOffset);
+
+  const int warp = threadIdx.x / 32;
+  const int lane = threadIdx.x % 32;
+  constexpr std::uint32_t kTmemColumns = 2 * BN;  // 256 or 512, power of two
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(tmem_full_bar(s), 1);
+      mbar_init(tmem_empty_bar(s), 4);
+    }
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile(
+        "tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::
+            "r"(smem_u32(const_cast<std::uint32_t *>(tmem_ptr))),
+        "r"(kTmemColumns)
+        : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;"
+                 ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const std::uint32_t tmem_base = *tmem_ptr;
+
+  const int tiles_m = (M + kBlockM - 1) / kBlockM;
+  const int tiles_n = (N + BN - 1) / BN;
+  const int tiles = tiles_m * tiles_n;
+  const int k_blocks = (K_bytes + kBlockKBytes - 1) / kBlockKBytes;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      int stage = 0;
+      std::uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x) {
+        const int m0 = (tile % tiles_m) * kBlockM;
+        const int n0 = (tile / tiles_m) * BN;
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          if (!mbar_wait(empty_bar(stage), phase ^ 1U, abort_flag)) {
+            ok = false;
+            break;
+          }
+          const std::uint32_t a_dst = smem_base + stage * L::kStageBytes;
+          const std::uint32_t b_dst = a_dst + L::kABytes;
+          mbar_expect_tx(full_bar(stage), L::kStageBytes);
+          const int k_elem = kFp8 ? kb * kBlockKBytes : kb * (kBlockKBytes / 2);
+          tma_load_2d(a_dst, &map_a, full_bar(stage), k_elem, m0);
+          tma_load_2d(b_dst, &map_b, full_bar(stage), k_elem, n0);
+          if (++stage == kStages) {
+            stage = 0;
+            phase ^= 1U;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr std::uint32_t idesc = instruction_descriptor<kFp8, BN>();
+      int stage = 0;
+      std::uint32_t phase = 0;
+      int local = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < tiles && ok;
+           tile += gridDim.x, ++local) {
+        const int acc = local & 1;
+        const std::uint32_t acc_phase = (local >> 1) & 1U;
+        if (!mbar_wait(tmem_empty_bar(acc), acc_phase ^ 1U, abort_flag)) break;
+        tc_fence_after();
+        const std::uint32_t tmem_d = tmem_base + acc * BN;
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          if (!mbar_wait(full_bar(stage), phase, abort_flag)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const std::uint32_t a_addr = smem_base + stage * L::kStageBytes;
+          const std::uint64_t a_desc = smem_descriptor(a_addr);
+          const std::uint64_t b_desc = smem_descriptor(a_addr + L::kABytes);
+#pragma unroll
+          for (int k = 0; k < kBlockKBytes / 32; ++k) {
+            // 32 bytes of K per instruction: +2 in the 16-byte address field.
+            tc_mma<kFp8>(tmem_d, a_desc + 2U * k, b_desc + 2U * k, idesc,
+                         (kb | k) != 0 ? 1U : 0U);
+          }
+          tc_commit(empty_bar(stage));
+          if (++stage == kStages) {
+            stage = 0;
+            phase ^= 1U;
+          }
+        }
+        if (ok) tc_commit(tmem_full_bar(acc));
+      }
+    }
+  } else {
+    const int quarter = warp % 4;
+    int local = 0;
+    for (int tile = blockIdx.x; tile < tiles; tile += gridDim.x, ++local) {
+      const int m0 = (tile % tiles_m) * kBlockM;
+      const int n0 = (tile / tiles_m) * BN;
+      const int acc = local & 1;
+      const std::uint32_t acc_phase = (local >> 1) & 1U;
+      if (!mbar_wait(tmem_full_bar(acc), acc_phase, abort_flag)) break;
+      tc_fence_after();
+      const int row = m0 + quarter * 32 + lane;
+      const std::uint32_t taddr =
+          tmem_base + acc * BN + (static_cast<std::uint32_t>(quarter * 32) << 16U);
+      const bool gated = ep.gate_mode != 0;
+      const int chunks = gated ? BN / 64 : BN / 32;
+      for (int c = 0; c < chunks; ++c) {
+        std::uint32_t v[32];
+        std::uint32_t w[32];
+        tmem_load_32(taddr + c * 32, v);
+        if (gated) tmem_load_32(taddr + BN / 2 + c * 32, w);
+        tmem_load_wait();
+        const int col = gated ? n0 / 2 + c * 32 : n0 + c * 32;
+        const int n_limit = gated ? N / 2 : N;
+        if (row < M && col < n_limit) {
+          bf16 *const out_row = ep.out + static_cast<std::size_t>(row) * ep.ld_out;
+          float r[32];
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            float value = __uint_as_float(v[j]) * ep.alpha;
+            if (gated) {
+              const float first =
+                  ep.gate_mode == 2 ? bf2f(gelu_round(value)) : rbf(value);
+              const float second = rbf(__uint_as_float(w[j]) * ep.alpha);
+              r[j] = rbf(first * second);
+            } else {
+              if (ep.bias_mode == 1 && col + j < n_limit)
+                value += bf2f(ep.bias[col + j]);
+              value = rbf(value);
+              if (ep.bias_mode == 2 && col + j < n_limit)
+                value = rbf(value + bf2f(ep.bias[col + j]));
+              r[j] = value;
+            }
+          }
+          const bool vector_ok =
+              col + 32 <= n_limit && (ep.ld_out % 8) == 0 &&
+              (reinterpret_cast<std::uintptr_t>(ep.out) & 15U) == 0;
+          if (ep.residual != nullptr) {
+            const bf16 *const res_row =
+                ep.residual + static_cast<std::size_t>(row) * ep.ld_out;
+            if (vector_ok &&
+                (reinterpret_cast<std::uintptr_t>(ep.residual) & 15U) == 0) {
+#pragma unroll
+              for (int q = 0; q < 4; ++q) {
+                Bf16x8 packed;
+                packed.raw = *reinterpret_cast<const uint4 *>(res_row + col + q * 8);
+#pragma unroll
+                for (int j = 0; j < 8; ++j)
+                  r[q * 8 + j] = rbf(r[q * 8 + j] + packed.get(j));
+              }
+            } else {
+              for (int j = 0; j < 32; ++j)
+                if (col + j < n_limit) r[j] = rbf(r[j] + bf2f(res_row[col + j]));
+            }
+          }
+          if (vector_ok) {
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              const uint4 packed = make_uint4(
+                  pack_bf16x2(r[q * 8 + 0], r[q * 8 + 1]),
+                  pack_bf16x2(r[q * 8 + 2], r[q * 8 + 3]),
+                  pack_bf16x2(r[q * 8 + 4], r[q * 8 + 5]),
+                  pack_bf16x2(r[q * 8 + 6], r[q * 8 + 7]));
+              *reinterpret_cast<uint4 *>(out_row + col + q * 8) = packed;
+            }
+          } else {
+            for (int j = 0; j < 32; ++j)
+              if (col + j < n_limit) out_row[col + j] = f2bf(r[j]);
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(tmem_empty_bar(acc));
+    }
+  }
+
+  __syncwarp();
+  tc_fence_before();
+  __syncthreads();
+  if (*abort_flag != 0) {
+    // Give copies that may still be in flight time to land before the shared
+    // memory of this CTA is recycled, then report.
+    const unsigned long long start = global_timer_ns();
+    while (global_timer_ns() - start < 200000ULL) __nanosleep(1000);
+    if (threadIdx.x == 0) atomicExch(error_word, 1);
+  }
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(
+                     tmem_base),
+                 "r"(kTmemColumns)
+                 : "memory");
+  }
+}
+
+// ---------------------------------------------------------- SIMT fallback
+// Shapes the TMA path cannot take (row pitch not a multiple of 16 bytes, or
+// the tiny test-fixture widths) run on CUDA cores with the same epilogue.
+template <bool kFp8>
+__global__ void __launch_bounds__(256)
+gemm_simt_kernel(const void *__restrict__ a_raw, const void *__restrict__ b_raw,
+                 const EpilogueParams ep, const int M, const int N,
+                 const int K) {
+  __shared__ float a_tile[16][65];
+  __shared__ float b_tile[16][65];
+  const int tx = threadIdx.x % 16, ty = threadIdx.x / 16;
+  const int m0 = blockIdx.y * 64, n0 = blockIdx.x * 64;
+  float acc[4][4] = {};
+  auto load = [&](const void *base, const int row, const int k) -> float {
+    const std::size_t index = static_cast<std::size_t>(row) * K + k;
+    if constexpr (kFp8) {
+      const std::uint8_t code = static_cast<const std::uint8_t *>(base)[index];
+      const unsigned int e = (code >> 3U) & 0xfU, m = code & 7U;
+      const float magnitude =
+          e == 0 ? ldexpf(static_cast<float>(m), -9)
+                 : ldexpf(1.0F + static_cast<float>(m) * 0.125F,
+                          static_cast<int>(e) - 7);
+      return (code & 0x80U) ? -magnitude : magnitude;
+    } else {
+      return bf2f(static_cast<const bf16 *>(base)[index]);
+    }
+  };
+  for (int k0 = 0; k0 < K; k0 += 16) {
+    for (int i = threadIdx.x; i < 64 * 16; i += 256) {
+      const int r = i / 16, k = i % 16;
+      a_tile[k][r] = (m0 + r < M && k0 + k < K) ? load(a_raw, m0 + r, k0 + k) : 0.0F;
+      b_tile[k][r] = (n0 + r < N && k0 + k < K) ? load(b_raw, n0 + r, k0 + k) : 0.0F;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int k = 0; k < 16; ++k) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          acc[i][j] = fmaf(a_tile[k][ty * 4 + i], b_tile[k][tx * 4 + j], acc[i][j]);
+    }
+    __syncthreads();
+  }
+  for (int i = 0; i < 4; ++i) {
+    const int row = m0 + ty * 4 + i;
+    if (row >= M) continue;
+    for (int j = 0; j < 4; ++j) {
+      const int col = n0 + tx * 4 + j;
+      if (col >= N) continue;
+      float value = acc[i][j] * ep.alpha;
+      if (ep.bias_mode == 1) value += bf2f(ep.bias[col]);
+      value = rbf(value);
+      if (ep.bias_mode == 2) value = rbf(value + bf2f(ep.bias[col]));
+      const std::size_t index = static_cast<std::size_t>(row) * ep.ld_out + col;
+      if (ep.residual != nullptr) value = rbf(value + bf2f(ep.residual[index]));
+      ep.out[index] = f2bf(value);
+    }
+  }
+}
+
+// ------------------------------------------------------------ host side
+using EncodeTiled = CUresult (*)(CUtensorMap *, CUtensorMapDataType,
+                                 cuuint32_t, void *, const cuuint64_t *,
+                                 const cuuint64_t *, const cuuint32_t *,
+                                 const cuuint32_t *, CUtensorMapInterleave,
+                                 CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                 CUtensorMapFloatOOBfill);
+
+EncodeTiled encode_tiled() {
+  static EncodeTiled fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void *symbol = nullptr;
+    cudaDriverEntryPointQueryResult result;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &symbol,
+                                cudaEnableDefault, &result) == cudaSuccess &&
+        result == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiled>(symbol);
+  });
+  return fn;
+}
+
+int make_map(CUtensorMap *map, const void *base, const bool fp8,
+             const std::size_t rows, const std::size_t k_elements,
+             const int box_rows) {
+  const EncodeTiled encode = encode_tiled();
+  if (encode == nullptr)
+    return fail(kCuda, "cuTensorMapEncodeTiled is unavailable");
+  const std::size_t element = fp8 ? 1 : 2;
+  const cuuint64_t dims[2] = {k_elements, rows};
+  const cuuint64_t strides[1] = {k_elements * element};
+  const cuuint32_t box[2] = {static_cast<cuuint32_t>(kBlockKBytes / element),
+                             static_cast<cuuint32_t>(box_rows)};
+  const cuuint32_t element_strides[2] = {1, 1};
+  const CUresult result = encode(
+      map, fp8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16,
+      2, const_cast<void *>(base), dims, strides, box, element_strides,
+      CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+      CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (result != CUDA_SUCCESS)
+    return fail(kCuda, "cuTensorMapEncodeTiled failed with code " +
+                           std::to_string(static_cast<int>(result)));
+  return kOk;
+}
+
+struct DeviceState {
+  int *error_word = nullptr;
+  int sm_count = 0;
+  bool attributes_set = false;
+};
+
+DeviceState *device_state(int *status) {
+  static std::mutex mutex;
+  static DeviceState states[64];
+  int device = 0;
+  if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) {
+    *status = fail(kCuda, "cannot query the current CUDA device");
+    return nullptr;
+  }
+  std::lock_guard<std::mutex> lock(mutex);
+  DeviceState &state = states[device];
+  if (state.error_word == nullptr) {
+    if (cudaMalloc(&state.error_word, sizeof(int)) != cudaSuccess ||
+        cudaMemset(state.error_word, 0, sizeof(int)) != cudaSuccess) {
+      *status = fail(kCuda, "cannot allocate the GEMM error word");
+      return nullptr;
+    }
+    cudaDeviceGetAttribute(&state.sm_count, cudaDevAttrMultiProcessorCount,
+                           device);
+    if (state.sm_count <= 0) state.sm_count = kSmCount;
+  }
+  *status = kOk;
+  return &state;
+}
+
+template <bool kFp8, int BN>
+int launch_tc(const void *a, const void *b, const EpilogueParams &ep,
+              const std::size_t M, const std::size_t N, const std::size_t K,
+              cudaStream_t stream) {
+  int status = kOk;
+  DeviceState *const state = device_state(&status);
+  if (state == nullptr) return status;
+  CUtensorMap map_a, map_b;
+  status = make_map(&map_a, a, kFp8, M, K, kBlockM);
+  if (status != kOk) return status;
+  status = make_map(&map_b, b, kFp8, N, K, BN);
+  if (status != kOk) return status;
+  using L = SharedLayout<BN>;
+  static bool configured[64] = {};
+  int device = 0;
+  cudaGetDevice(&device);
+  if (!configured[device]) {
+    if (cudaFuncSetAttribute(gemm_tcgen05_kernel<kFp8, BN>,
+                             cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             L::kTotal) != cudaSuccess)
+      return fail(kCuda, "cannot raise the GEMM shared-memory limit");
+    configured[device] = true;
+  }
+  const std::size_t tiles =
+      ((M + kBlockM - 1) / kBlockM) * ((N + BN - 1) / BN);
+  const unsigned int grid = static_cast<unsigned int>(
+      tiles < static_cast<std::size_t>(state->sm_count) ? tiles
+                                                        : state->sm_count);
+  gemm_tcgen05_kernel<kFp8, BN><<<grid, kGemmThreads, L::kTotal, stream>>>(
+      map_a, map_b, ep, static_cast<int>(M), static_cast<int>(N),
+      static_cast<int>(K * (kFp8 ? 1 : 2)), state->error_word);
+  return check_launch("tcgen05 GEMM kernel");
+}
+
+}  // namespace
+
+int gemm_error_state(cudaStream_t stream) {
+  int status = kOk;
+  DeviceState *const state = device_state(&status);
+  if (state == nullptr) return status;
+  int value = 0;
+  if (cudaMemcpyAsync(&value, state->error_word, sizeof(int),
+                      cudaMemcpyDeviceToHost, stream) != cudaSuccess ||
+      cudaStreamSynchronize(stream) != cudaSuccess)
+    return fail(kCuda, "cannot read the GEMM error word");
+  if (value != 0) {
+    cudaMemsetAsync(state->error_word, 0, sizeof(int), stream);
+    return fail(kCuda, "a tcgen05 GEMM pipeline wait timed out");
+  }
+  return kOk;
+}
+
+int linear(const LinearArgs &args, cudaStream_t stream) {
+  const bool fp8 = args.operand_type == OperandType::kE4m3;
+  if (args.input == nullptr || args.weight == nullptr ||
+      args.output == nullptr || args.in_features == 0 ||
+      args.out_features == 0 || !isfinite(args.alpha))
+    return fail(kInvalidArgument, "linear arguments are invalid");
+  if (args.bias_mode != 0 && args.bias == nullptr)
+    return fail(kInvalidArgument, "linear bias mode needs a bias vector");
+  if (args.gate_mode != 0 &&
+      (args.bias_mode != 0 || args.residual != nullptr))
+    return fail(kInvalidArgument,
+                "gated linear cannot take a bias or a residual");
+  if (args.rows > 0x7fffffffU || args.out_features > 0x7fffffffU ||
+      args.in_features > 0x3fffffffU)
+    return fail(kInvalidArgument, "linear dimensions are too large");
+  if (args.rows == 0) return kOk;
+  const std::size_t out_columns =
+      args.gate_mode != 0 ? args.out_features / 2 : args.out_features;
+  EpilogueParams ep{};
+  ep.out = static_cast<bf16 *>(args.output);
+  ep.bias = static_cast<const bf16 *>(args.bias);
+  ep.residual = static_cast<const bf16 *>(args.residual);
+  ep.ld_out = out_columns;
+  ep.alpha = args.alpha;
+  ep.bias_mode = args.bias_mode;
+  ep.gate_mode = args.gate_mode;
+  const std::size_t pitch = args.in_features * (fp8 ? 1 : 2);
+  const bool tma_ok =
+      pitch % 16 == 0 && pitch >= 128 &&
+      (reinterpret_cast<std::uintptr_t>(args.input) & 15U) == 0 &&
+      (reinterpret_cast<std::uintptr_t>(args.weight) & 15U) == 0 &&
+      args.out_features >= 64 && !args.force_simt;
+  if (tma_ok) {
+    if (args.gate_mode != 0) {
+      if (args.out_features % 256 != 0)
+        return fail(kInvalidArgument,
+                    "gated linear needs the interleaved width to be a "
+                    "multiple of 256");
+      return fp8 ? launch_tc<true, 256>(args.input, args.weight, ep, args.rows,
+                                        args.out_features, args.in_features,
+                                        stream)
+                 : launch_tc<false, 256>(args.input, args.weight, ep,
+                                         args.rows, args.out_features,
+                                         args.in_features, stream);
+    }
+    // Narrow tiles when wide ones would leave most SMs without work.
+    const std::size_t tiles_m = (args.rows + kBlockM - 1) / kBlockM;
+    const std::size_t wide = tiles_m * ((args.out_features + 255) / 256);
+    const bool narrow = args.out_features < 256 || wide < 120;
+    if (narrow)
+      return fp8 ? launch_tc<true, 128>(args.input, args.weight, ep, args.rows,
+                                        args.out_features, args.in_features,
+                                        stream)
+                 : launch_tc<false, 128>(args.input, args.weight, ep,
+                                         args.rows, args.out_features,
+                                         args.in_features, stream);
+    return fp8 ? launch_tc<true, 256>(args.input, args.weight, ep, args.rows,
+                                      args.out_features, args.in_features,
+                                      stream)
+               : launch_tc<false, 256>(args.input, args.weight, ep, args.rows,
+                                       args.out_features, args.in_features,
+                                       stream);
+  }
+  if (args.gate_mode != 0)
+    return fail(kUnsupported,
+                "gated linear is only available on the tensor-core path");
+  const dim3 grid(ceil_div_u(args.out_features, 64), ceil_div_u(args.rows, 64));
+  if (grid.y > 65535)
+    return fail(kInvalidArgument, "linear fallback has too many rows");
+  if (fp8)
+    gemm_simt_kernel<true><<<grid, 256, 0, stream>>>(
+        args.input, args.weight, ep, static_cast<int>(args.rows),
+        static_cast<int>(args.out_features),
+        static_cast<int>(args.in_features));
+  else
+    gemm_simt_kernel<false><<<grid, 256, 0, stream>>>(
+        args.input, args.weight, ep, static_cast<int>(args.rows),
+        static_cast<int>(args.out_features),
+        static_cast<int>(args.in_features));
+  return check_launch("CUDA-core GEMM kernel");
+}
+
+}  // namespace evob

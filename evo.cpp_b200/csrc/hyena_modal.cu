@@ -1,0 +1,377 @@
+// Long-implicit (HCL) Hyena operator: y = x2 * (h * u + D u) with
+// u = bf16(x1 * v) and the per-channel modal filter
+// h[c,t] = sum_m R[c,m] exp(log_pole[c,m] t).
+//
+// Upstream materialises h and convolves with an n = 2T FFT, then recovers the
+// decode state with one complex FFT per (channel, mode)
+// (src/cuda/hyena.cu:562-660, 1262-1456, 1994-2124).  Because the filter is a
+// sum of first-order modes, the same convolution is a linear recurrence
+// s_m[t] = p_m s_m[t-1] + u[t], y[t] = sum_m R_m s_m[t]; here it runs as a
+// three-kernel chunked scan that is linear in T, needs T*C*modes/segment
+// floats of scratch instead of FFT planes, and yields the decode state for free:
+//   1. per (segment, channel pair): end state of the segment from zero,
+//   2. per (channel, mode): serial carry over segments (p^S scaling),
+//   3. per (segment, channel pair): replay from the carried state, read out,
+//      add the direct term, post-gate, store.
+// The four BF16 roundings of the upstream epilogue are kept for initial
+// prefill; continuation chunks keep upstream's single rounding
+// (src/cuda/hyena.cu:534-560).  modal_decode keeps the pinned decode order
+// (separate multiply/add, 32-lane zero-padded tree; src/cuda/hyena.cu:718-761).
+#include "common.cuh"
+#include "ops_internal.hpp"
+
+namespace evob {
+namespace {
+
+constexpr int kThreads = 128;
+
+struct ModalParams {
+  const bf16 *x2, *x1, *value, *projection, *short_filter, *direct;
+  const float *log_poles, *residues;
+  bf16 *output, *pregate;
+  float *state;    // [width, modes]
+  float *scratch;  // [segments, width, modes]
+  int length, width, segment, segments, pairs;
+  bool continue_from_state;
+};
+
+// Streams one channel pair through time, yielding the featurized gate values.
+template <bool kFromProjection>
+struct PairReader {
+  const ModalParams &p;
+  int c0;
+  float prev1[6], prev2[6];  // raw projection rows t-1, t-2 (x2a,x1a,va,x2b,x1b,vb)
+  float sw[6][3];            // featurizer taps per stream of the pair
+
+  __device__ __forceinline__ PairReader(const ModalParams &params, const int channel)
+      : p(params), c0(channel) {}
+
+  __device__ __forceinline__ void load_row(const int t, float (&row)[6]) const {
+    if (t < 0) {
+#pragma unroll
+      for (int i = 0; i < 6; ++i) row[i] = 0.0F;
+      return;
+    }
+    const std::uint32_t *const words = reinterpret_cast<const std::uint32_t *>(
+        p.projection + static_cast<std::size_t>(t) * p.width * 3 + c0 * 3);
+#pragma unroll
+    for (int w = 0; w < 3; ++w) {
+      const std::uint32_t word = words[w];
+      row[2 * w] = __uint_as_float(word << 16U);
+      row[2 * w + 1] = __uint_as_float(word & 0xffff0000U);
+    }
+  }
+
+  __device__ __forceinline__ void start(const int t0) {
+    if constexpr (kFromProjection) {
+#pragma unroll
+      for (int s = 0; s < 6; ++s)
+#pragma unroll
+        for (int j = 0; j < 3; ++j)
+          sw[s][j] = bf2f(p.short_filter[(static_cast<std::size_t>(c0) * 3 + s) * 3 + j]);
+      load_row(t0 - 1, prev1);
+      load_row(t0 - 2, prev2);
+    }
+  }
+
+  // Returns u for both channels and, when requested, the x2 gate.
+  __device__ __forceinline__ void step(const int t, const bool want_x2,
+                                       float &u0, float &u1, float &g0,
+                                       float &g1) {
+    if constexpr (kFromProjection) {
+      float row[6], z[6];
+      load_row(t, row);
+#pragma unroll
+      for (int s = 0; s < 6; ++s) {
+        float a = 0.0F;
+        a = fmaf(prev2[s], sw[s][0], a);
+        a = fmaf(prev1[s], sw[s][1], a);
+        a = fmaf(row[s], sw[s][2], a);
+        z[s] = rbf(a);
+        prev2[s] = prev1[s];
+        prev1[s] = row[s];
+      }
+      u0 = rbf(z[1] * z[2]);
+      u1 = rbf(z[4] * z[5]);
+      g0 = z[0];
+      g1 = z[3];
+    } else {
+      const std::size_t index = static_cast<std::size_t>(t) * p.width + c0;
+      const std::uint32_t a = *reinterpret_cast<const std::uint32_t *>(p.x1 + index);
+      const std::uint32_t b = *reinterpret_cast<const std::uint32_t *>(p.value + index);
+      u0 = rbf(__uint_as_float(a << 16U) * __uint_as_float(b << 16U));
+      u1 = rbf(__uint_as_float(a & 0xffff0000U) * __uint_as_float(b & 0xffff0000U));
+      if (want_x2) {
+        const std::uint32_t g = *reinterpret_cast<const std::uint32_t *>(p.x2 + index);
+        g0 = __uint_as_float(g << 16U);
+        g1 = __uint_as_float(g & 0xffff0000U);
+      }
+    }
+  }
+};
+
+template <int kModes, bool kFromProjection>
+__global__ void __launch_bounds__(kThreads)
+modal_local_kernel(const ModalParams p) {
+  const int index = blockIdx.x * kThreads + threadIdx.x;
+  const int pair = index % p.pairs;
+  const int seg = index / p.pairs;
+  if (seg >= p.segments) return;
+  const int c0 = pair * 2;
+  if (c0 >= p.width) return;
+  float pole[2][kModes], state[2][kModes];
+#pragma unroll
+  for (int c = 0; c < 2; ++c)
+#pragma unroll
+    for (int m = 0; m < kModes; ++m) {
+      pole[c][m] = expf(p.log_poles[static_cast<std::size_t>(c0 + c) * kModes + m]);
+      state[c][m] = 0.0F;
+    }
+  const int t0 = seg * p.segment;
+  const int t1 = min(t0 + p.segment, p.length);
+  PairReader<kFromProjection> reader(p, c0);
+  reader.start(t0);
+  for (int t = t0; t < t1; ++t) {
+    float u0, u1, g0, g1;
+    reader.step(t, false, u0, u1, g0, g1);
+#pragma unroll
+    for (int m = 0; m < kModes; ++m) {
+      state[0][m] = fmaf(pole[0][m], state[0][m], u0);
+      state[1][m] = fmaf(pole[1][m], state[1][m], u1);
+    }
+  }
+  float *const out = p.scratch + (static_cast<std::size_t>(seg) * p.width + c0) * kModes;
+#pragma unroll
+  for (int c = 0; c < 2; ++c)
+#pragma unroll
+    for (int m = 0; m < kModes; ++m) out[c * kModes + m] = state[c][m];
+}
+
+// scratch[seg] holds the segment-local end state on entry and the state carried
+// INTO the segment on exit; the state after the last segment goes to p.state.
+__global__ void modal_carry_kernel(const ModalParams p, const int modes) {
+  const int index = blockIdx.x * blockDim.x + threadIdx.x;
+  if (index >= p.width * modes) return;
+  const float log_pole = p.log_poles[index];
+  const float full_decay = expf(log_pole * static_cast<float>(p.segment));
+  float carry = (p.continue_from_state && p.state != nullptr) ? p.state[index] : 0.0F;
+  for (int seg = 0; seg < p.segments; ++seg) {
+    float *const slot = p.scratch + static_cast<std::size_t>(seg) * p.width * modes + index;
+    const float local = *slot;
+    *slot = carry;
+    const int span = min(p.segment, p.length - seg * p.segment);
+    const float decay =
+        span == p.segment ? full_decay : expf(log_pole * static_cast<float>(span));
+    carry = fmaf(decay, carry, local);
+  }
+  if (p.state != nullptr) p.state[index] = carry;
+}
+
+template <int kModes, bool kFromProjection>
+__global__ void __launch_bounds__(kThreads)
+modal_output_kernel(const ModalParams p) {
+  const int index = blockIdx.x * kThreads + threadIdx.x;
+  const int pair = index % p.pairs;
+  const int seg = index / p.pairs;
+  if (seg >= p.segments) return;
+  const int c0 = pair * 2;
+  if (c0 >= p.width) return;
+  float pole[2][kModes], residue[2][kModes], state[2][kModes];
+  const float *const carried =
+      p.scratch + (static_cast<std::size_t>(seg) * p.width + c0) * kModes;
+#pragma unroll
+  for (int c = 0; c < 2; ++c)
+#pragma unroll
+    for (int m = 0; m < kModes; ++m) {
+      const std::size_t q = static_cast<std::size_t>(c0 + c) * kModes + m;
+      pole[c][m] = expf(p.log_poles[q]);
+      residue[c][m] = p.residues[q];
+      state[c][m] = carried[c * kModes + m];
+    }
+  const float direct0 = bf2f(p.direct[c0]);
+  const float direct1 = bf2f(p.direct[c0 + 1]);
+  const int t0 = seg * p.segment;
+  const int t1 = min(t0 + p.segment, p.length);
+  PairReader<kFromProjection> reader(p, c0);
+  reader.start(t0);
+  for (int t = t0; t < t1; ++t) {
+    float u[2], g[2];
+    reader.step(t, true, u[0], u[1], g[0], g[1]);
+    float result[2];
+#pragma unroll
+    for (int c = 0; c < 2; ++c) {
+      float partial[4] = {0.0F, 0.0F, 0.0F, 0.0F};
+#pragma unroll
+      for (int m = 0; m < kModes; ++m) {
+        state[c][m] = fmaf(pole[c][m], state[c][m], u[c]);
+        partial[m % 4] = fmaf(residue[c][m], state[c][m], partial[m % 4]);
+      }
+      const float modal = ((partial[0] + partial[1]) + partial[2]) + partial[3];
+      const float direct = c == 0 ? direct0 : direct1;
+      if (p.continue_from_state) {
+        result[c] = g[c] * fmaf(direct, u[c], modal);
+      } else {
+        const float mixed = rbf(rbf(modal) + rbf(direct * u[c]));
+        result[c] = mixed * g[c];
+      }
+    }
+    const std::size_t offset = static_cast<std::size_t>(t) * p.width + c0;
+    *reinterpret_cast<std::uint32_t *>(p.output + offset) =
+        pack_bf16x2(result[0], result[1]);
+    if (p.pregate != nullptr)
+      *reinterpret_cast<std::uint32_t *>(p.pregate + offset) =
+          (__float_as_uint(u[0]) >> 16U) | (__float_as_uint(u[1]) & 0xffff0000U);
+  }
+}
+
+__global__ void modal_decode_kernel(const bf16 *__restrict__ x2,
+                                    const bf16 *__restrict__ x1,
+                                    const bf16 *__restrict__ value,
+                                    const bf16 *__restrict__ direct,
+                                    const float *__restrict__ log_poles,
+                                    const float *__restrict__ residues,
+                                    float *__restrict__ state,
+                                    bf16 *__restrict__ pregate,
+                                    bf16 *__restrict__ output, const int width,
+                                    const int modes) {
+  const int channel = blockIdx.x * blockDim.x + threadIdx.x;
+  if (channel >= width) return;
+  const bf16 gated_bf16 = f2bf(bf2f(x1[channel]) * bf2f(value[channel]));
+  if (pregate != nullptr) pregate[channel] = gated_bf16;
+  const float gated = bf2f(gated_bf16);
+  float terms[32];
+#pragma unroll
+  for (int lane = 0; lane < 32; ++lane) terms[lane] = 0.0F;
+#pragma unroll
+  for (int mode = 0; mode < 32; ++mode) {
+    if (mode < modes) {
+      const std::size_t q = static_cast<std::size_t>(channel) * modes + mode;
+      const float updated =
+          __fadd_rn(__fmul_rn(expf(log_poles[q]), state[q]), gated);
+      state[q] = updated;
+      terms[mode] = __fmul_rn(residues[q], updated);
+    }
+  }
+#pragma unroll
+  for (int offset = 16; offset != 0; offset /= 2)
+#pragma unroll
+    for (int lane = 0; lane < 32; ++lane)
+      if (lane < 32 - offset) terms[lane] = __fadd_rn(terms[lane], terms[lane + offset]);
+  const float direct_product = rbf(bf2f(direct[channel]) * gated);
+  const float mixed = __fadd_rn(terms[0], direct_product);
+  output[channel] = f2bf(__fmul_rn(bf2f(x2[channel]), mixed));
+}
+
+int pick_segment(const std::size_t length, const std::size_t width) {
+  // Largest segment that still yields >= ~200k threads; shorter segments cost
+  // more carry scratch, longer ones starve the SMs.
+  const std::size_t pairs = width / 2;
+  for (const int segment : {256, 128, 64, 32, 16}) {
+    const std::size_t segments = (length + segment - 1) / segment;
+    if (segments * pairs >= 200000) return segment;
+  }
+  return 16;
+}
+
+template <int kModes>
+int launch_modal(const ModalParams &p, const bool from_projection,
+                 cudaStream_t stream) {
+  const std::size_t threads = static_cast<std::size_t>(p.segments) * p.pairs;
+  const unsigned int grid = ceil_div_u(threads, kThreads);
+  if (from_projection)
+    modal_local_kernel<kModes, true><<<grid, kThreads, 0, stream>>>(p);
+  else
+    modal_local_kernel<kModes, false><<<grid, kThreads, 0, stream>>>(p);
+  int status = check_launch("modal segment kernel");
+  if (status != kOk) return status;
+  modal_carry_kernel<<<ceil_div_u(static_cast<std::size_t>(p.width) * kModes, 256),
+                       256, 0, stream>>>(p, kModes);
+  status = check_launch("modal carry kernel");
+  if (status != kOk) return status;
+  if (from_projection)
+    modal_output_kernel<kModes, true><<<grid, kThreads, 0, stream>>>(p);
+  else
+    modal_output_kernel<kModes, false><<<grid, kThreads, 0, stream>>>(p);
+  return check_launch("modal output kernel");
+}
+
+}  // namespace
+
+std::size_t modal_scratch_floats(const std::size_t length,
+                                 const std::size_t width,
+                                 const std::size_t modes) {
+  if (length == 0) return 0;
+  const std::size_t segment = pick_segment(length, width);
+  return ((length + segment - 1) / segment) * width * modes;
+}
+
+int modal_prefill(const ModalArgs &a, cudaStream_t stream) {
+  const bool from_projection = a.projection != nullptr;
+  if (a.direct == nullptr || a.log_poles == nullptr || a.residues == nullptr ||
+      a.output == nullptr || a.scratch == nullptr || a.width == 0 ||
+      a.width % 2 != 0 || a.modes == 0)
+    return fail(kInvalidArgument, "modal prefill arguments are invalid");
+  if (from_projection
+          ? (a.short_filter == nullptr || a.short_taps != 3)
+          : (a.x2 == nullptr || a.x1 == nullptr || a.value == nullptr))
+    return fail(kInvalidArgument, "modal prefill inputs are incomplete");
+  if (a.continue_from_state && a.state == nullptr)
+    return fail(kInvalidArgument, "modal continuation needs a state");
+  if (a.length > 0x7fffff00U || a.width > 0x3fffffffU)
+    return fail(kInvalidArgument, "modal prefill dimensions are too large");
+  if (a.length == 0) return kOk;
+  ModalParams p{};
+  p.x2 = static_cast<const bf16 *>(a.x2);
+  p.x1 = static_cast<const bf16 *>(a.x1);
+  p.value = static_cast<const bf16 *>(a.value);
+  p.projection = static_cast<const bf16 *>(a.projection);
+  p.short_filter = static_cast<const bf16 *>(a.short_filter);
+  p.direct = static_cast<const bf16 *>(a.direct);
+  p.log_poles = a.log_poles;
+  p.residues = a.residues;
+  p.output = static_cast<bf16 *>(a.output);
+  p.pregate = static_cast<bf16 *>(a.pregate);
+  p.state = a.state;
+  p.scratch = a.scratch;
+  p.length = static_cast<int>(a.length);
+  p.width = static_cast<int>(a.width);
+  p.segment = pick_segment(a.length, a.width);
+  p.segments = static_cast<int>((a.length + p.segment - 1) / p.segment);
+  p.pairs = static_cast<int>(a.width / 2);
+  p.continue_from_state = a.continue_from_state;
+  int status;
+  switch (a.modes) {
+    case 16: status = launch_modal<16>(p, from_projection, stream); break;
+    case 8: status = launch_modal<8>(p, from_projection, stream); break;
+    case 4: status = launch_modal<4>(p, from_projection, stream); break;
+    case 2: status = launch_modal<2>(p, from_projection, stream); break;
+    case 1: status = launch_modal<1>(p, from_projection, stream); break;
+    default:
+      return fail(kUnsupported, "modal state size must be 1, 2, 4, 8 or 16");
+  }
+  if (status != kOk) return status;
+  if (a.short_cache != nullptr && from_projection && a.short_taps > 1)
+    status = fill_fir_cache(a.projection, a.short_cache, a.length, a.width * 3,
+                            a.short_taps - 1, stream);
+  return status;
+}
+
+int modal_decode(const void *x2, const void *x1, const void *value,
+                 const void *direct, const float *log_poles,
+                 const float *residues, const std::size_t width,
+                 const std::size_t modes, float *state, void *pregate,
+                 void *output, cudaStream_t stream) {
+  if (x2 == nullptr || x1 == nullptr || value == nullptr || direct == nullptr ||
+      log_poles == nullptr || residues == nullptr || state == nullptr ||
+      output == nullptr || width == 0 || modes == 0 || modes > 32)
+    return fail(kInvalidArgument, "modal decode arguments are invalid");
+  modal_decode_kernel<<<ceil_div_u(width, 128), 128, 0, stream>>>(
+      static_cast<const bf16 *>(x2), static_cast<const bf16 *>(x1),
+      static_cast<const bf16 *>(value), static_cast<const bf16 *>(direct),
+      log_poles, residues, state, static_cast<bf16 *>(pregate),
+      static_cast<bf16 *>(output), static_cast<int>(width),
+      static_cast<int>(modes));
+  return check_launch("modal decode kernel");
+}
+
+}  // namespace evob

@@ -1,0 +1,150 @@
+// Host-side launchers of the sm_100a kernels.  All pointers are device
+// pointers on the current device; every function returns an evo_status value
+// and records a message retrievable through evob::last_error().
+#pragma once
+
+#include <cuda_runtime.h>
+
+#include <cstddef>
+#include <cstdint>
+
+namespace evob {
+
+// ---- elementwise.cu
+int quantize_bf16(const void *input, std::size_t elements, float scale,
+                  void *codes, float *dequantized, cudaStream_t stream);
+int quantize_f32(const float *input, std::size_t elements, float scale,
+                 void *codes, cudaStream_t stream);
+int rms_norm(const void *input, const float *scale, std::size_t rows,
+             std::size_t width, float epsilon, void *output, void *codes,
+             float quant_scale, cudaStream_t stream);
+int gelu(const void *input, void *output, std::size_t elements,
+         cudaStream_t stream);
+int gate(const void *first, const void *second, void *output,
+         std::size_t elements, bool apply_gelu, cudaStream_t stream);
+int add(const void *first, const void *second, void *output,
+        std::size_t elements, cudaStream_t stream);
+int add_bias(void *output, const void *bias, std::size_t rows,
+             std::size_t width, cudaStream_t stream);
+int embedding(const std::uint32_t *tokens, const void *table, std::size_t rows,
+              std::size_t width, void *output, cudaStream_t stream);
+int split_triples(const void *projection, std::size_t rows, std::size_t width,
+                  void *x2, void *x1, void *value, cudaStream_t stream);
+int transpose(const void *input, std::size_t rows, std::size_t columns,
+              void *output, cudaStream_t stream);
+
+// ---- qgmma_emulation.cu
+int e4m3_emulated_gemm(const void *input_codes, const void *weight_codes,
+                       std::size_t rows, std::size_t in_features,
+                       std::size_t out_features, float output_scale,
+                       void *output, cudaStream_t stream);
+
+// ---- gemm_tcgen05.cu
+enum class OperandType { kBf16, kE4m3 };
+struct LinearArgs {
+  const void *input = nullptr;   // [rows, in_features] BF16 or E4M3 codes
+  const void *weight = nullptr;  // [out_features, in_features], same type
+  const void *bias = nullptr;    // [out_features] BF16
+  const void *residual = nullptr;  // [rows, out_features] BF16
+  void *output = nullptr;        // [rows, out_features (/2 when gated)] BF16
+  std::size_t rows = 0;
+  std::size_t in_features = 0;
+  std::size_t out_features = 0;
+  OperandType operand_type = OperandType::kBf16;
+  float alpha = 1.0F;  // applied to the F32 accumulator before rounding
+  int bias_mode = 0;   // 0 none, 1 fused F32 add, 2 separate BF16-rounded add
+  int gate_mode = 0;   // 0 none, 1 a*b, 2 gelu(a)*b over 128-column halves
+  bool force_simt = false;
+};
+int linear(const LinearArgs &args, cudaStream_t stream);
+// Synchronises the stream and reports (then clears) a pipeline time-out.
+int gemm_error_state(cudaStream_t stream);
+
+// ---- hyena_fir.cu
+struct GatedFirArgs {
+  // Either three separate [length, width] tensors ...
+  const void *x2 = nullptr;
+  const void *x1 = nullptr;
+  const void *value = nullptr;
+  // ... or the raw projection [length, 3*width] (interleaved x2,x1,v triples)
+  // plus the per-stream 3-tap featurizer filter [3*width, short_taps].
+  const void *projection = nullptr;
+  const void *short_filter = nullptr;
+  std::size_t short_taps = 0;
+  const void *filter = nullptr;   // [groups, taps] BF16 or F32
+  bool filter_is_f32 = false;
+  const void *direct = nullptr;   // [width] BF16, adds direct*u (HCM) or null
+  void *output = nullptr;         // [length, width] BF16
+  void *pregate = nullptr;        // optional [length, width] BF16 (u = x1*v)
+  std::size_t length = 0;
+  std::size_t width = 0;
+  std::size_t groups = 0;
+  std::size_t taps = 0;
+  bool cross_correlation = true;  // HCS: true, HCM: false
+  // Optional F32 caches written for later decode steps.
+  float *inner_cache = nullptr;   // [width, taps-1]
+  float *short_cache = nullptr;   // [3*width, short_taps-1]
+};
+int gated_fir_prefill(const GatedFirArgs &args, cudaStream_t stream);
+
+int fir_prefill(const void *input, const void *filter, bool filter_is_f32,
+                const void *bias, bool multiply_bias, std::size_t length,
+                std::size_t channels, std::size_t groups, std::size_t taps,
+                bool cross_correlation, void *output, float *cache,
+                cudaStream_t stream);
+int fill_fir_cache(const void *input, float *cache, std::size_t length,
+                   std::size_t channels, std::size_t cache_size,
+                   cudaStream_t stream);
+int fir_step(const void *input, const void *filter, bool filter_is_f32,
+             const void *bias, bool multiply_bias, std::size_t length,
+             std::size_t channels, std::size_t groups, std::size_t taps,
+             bool cross_correlation, float *cache, std::size_t cache_length,
+             void *output, cudaStream_t stream);
+
+// ---- hyena_modal.cu
+struct ModalArgs {
+  const void *x2 = nullptr;
+  const void *x1 = nullptr;
+  const void *value = nullptr;
+  const void *projection = nullptr;
+  const void *short_filter = nullptr;
+  std::size_t short_taps = 0;
+  const void *direct = nullptr;      // [width] BF16
+  const float *log_poles = nullptr;  // [width, modes]
+  const float *residues = nullptr;   // [width, modes]
+  void *output = nullptr;            // [length, width] BF16
+  void *pregate = nullptr;           // optional u
+  float *state = nullptr;            // [width, modes] F32 in/out (may be null)
+  float *scratch = nullptr;          // segment states, see modal_scratch_floats
+  float *short_cache = nullptr;
+  std::size_t length = 0;
+  std::size_t width = 0;
+  std::size_t modes = 0;
+  bool continue_from_state = false;  // recurrence-continue numerics
+};
+std::size_t modal_scratch_floats(std::size_t length, std::size_t width,
+                                 std::size_t modes);
+int modal_prefill(const ModalArgs &args, cudaStream_t stream);
+int modal_decode(const void *x2, const void *x1, const void *value,
+                 const void *direct, const float *log_poles,
+                 const float *residues, std::size_t width, std::size_t modes,
+                 float *state, void *pregate, void *output,
+                 cudaStream_t stream);
+
+// ---- attention.cu
+int split_rope_append(const void *qkv, const float *inverse_frequency,
+                      std::size_t rows, std::size_t heads,
+                      std::size_t head_dim, std::size_t position_offset,
+                      float position_scale, bool head_major, void *query,
+                      void *key_cache, void *value_cache,
+                      std::size_t cache_capacity, cudaStream_t stream);
+int causal_attention(const void *query, const void *key_cache,
+                     const void *value_cache, std::size_t rows,
+                     std::size_t total_keys, std::size_t heads,
+                     std::size_t head_dim, void *output, cudaStream_t stream);
+int cached_attention(const void *query, const void *key_cache,
+                     const void *value_cache, std::size_t rows,
+                     std::size_t total_keys, std::size_t heads,
+                     std::size_t head_dim, void *output, cudaStream_t stream);
+
+}  // namespace evob

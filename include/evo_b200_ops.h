@@ -1,0 +1,197 @@
+/* Operator-level C ABI of the B200 StripedHyena2 hot path.
+ *
+ * Every entry point takes raw device pointers on the current CUDA device, a
+ * cudaStream_t passed as void*, and plain sizes; it enqueues work on that
+ * stream and returns an evo_status value (0 = OK, 2 invalid argument,
+ * 5 unsupported, 6 CUDA).  evo_b200_last_error() returns the thread-local
+ * "<code_name>: <message>" text of the most recent failure on this thread.
+ * Buffers are BF16 unless stated otherwise.  Each declaration cites the
+ * upstream evo.cpp operator (path:line in that project) whose contract it
+ * implements; upstream's DeviceBuffer/Stream arguments become pointer + size.
+ */
+#ifndef EVO_B200_OPS_H
+#define EVO_B200_OPS_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(__GNUC__)
+#define EVO_B200_API __attribute__((visibility("default")))
+#else
+#define EVO_B200_API
+#endif
+
+EVO_B200_API const char *evo_b200_last_error(void);
+/* Synchronises the stream; non-zero if a tensor-core GEMM pipeline wait
+ * timed out since the last check (the flag is cleared). */
+EVO_B200_API int evo_b200_check_async_errors(void *stream);
+
+/* include/evo/cuda/ops.hpp:81-103, src/cuda/ops.cu:232-275: E4M3FN RNE
+ * satfinite codes of float(x)*scale; optional F32 dequantised copy. */
+EVO_B200_API int evo_b200_software_e4m3_quantize_bf16(
+    const void *input, size_t elements, float scale, void *codes_u8,
+    float *dequantized_f32, void *stream);
+EVO_B200_API int evo_b200_software_e4m3_quantize_f32_codes(
+    const float *input, size_t elements, float scale, void *codes_u8,
+    void *stream);
+
+/* include/evo/cuda/ops.hpp:104-110, src/cuda/ops.cu:353-441,916-1006:
+ * y = bf16(QGMMA_emulation(E4M3(x*input_scale), w_codes) * output_scale),
+ * bit-exact integer emulation, K a multiple of 32.  codes_scratch holds
+ * rows*in_features bytes. */
+EVO_B200_API int evo_b200_software_e4m3_h100_linear(
+    const void *input, const void *weight_codes, size_t rows,
+    size_t in_features, size_t out_features, float input_scale,
+    float output_scale, void *codes_scratch, void *output, void *stream);
+/* Same operands on the tcgen05 FP8 tensor cores (F32 accumulation): the
+ * tensor-core execution profile of the projection above. */
+EVO_B200_API int evo_b200_e4m3_tensorcore_linear(
+    const void *input, const void *weight_codes, size_t rows,
+    size_t in_features, size_t out_features, float input_scale,
+    float output_scale, void *codes_scratch, void *output, void *stream);
+
+/* include/evo/cuda/ops.hpp:37-68, src/cuda/ops.cu:535-748: y = x W^T with
+ * W [out,in]; bias_mode 0 none, 1 fused into the F32 sum (cuBLASLt BIAS
+ * epilogue upstream), 2 separate BF16-rounded add
+ * (bf16_add_bias_inplace, src/cuda/ops.cu:187-198); residual (optional) is
+ * added last with its own rounding (bf16_add_inplace, ops.cu:175-185).
+ * path 0 = tcgen05 when the shape allows, 1 = CUDA-core kernel. */
+EVO_B200_API int evo_b200_bf16_linear(const void *input, const void *weight,
+                                      const void *bias, const void *residual,
+                                      size_t rows, size_t in_features,
+                                      size_t out_features, int bias_mode,
+                                      int path, void *output, void *stream);
+/* src/cuda/ops.cu:1205-1245 (bf16_mlp first half): gated = act(x W1^T) *
+ * (x W2^T) in one GEMM over a row-interleaved [W1 | W2] weight built by
+ * evo_b200_interleave_gate_weights; activation 0 identity, 1 GELU. */
+EVO_B200_API int evo_b200_bf16_gated_up_projection(
+    const void *input, const void *interleaved_weight, size_t rows,
+    size_t in_features, size_t inner_width, int activation, void *output,
+    void *stream);
+EVO_B200_API int evo_b200_interleave_gate_weights(const void *w1,
+                                                  const void *w2,
+                                                  size_t inner_width,
+                                                  size_t in_features,
+                                                  void *interleaved,
+                                                  void *stream);
+
+/* include/evo/cuda/ops.hpp:111-120, src/cuda/ops.cu:72-113.  output and
+ * codes_u8 are each optional (at least one); codes = E4M3(y*quant_scale). */
+EVO_B200_API int evo_b200_bf16_rms_norm(const void *input, const float *scale,
+                                        size_t rows, size_t width,
+                                        float epsilon, void *output,
+                                        void *codes_u8, float quant_scale,
+                                        void *stream);
+/* include/evo/cuda/ops.hpp:121-135, src/cuda/ops.cu:115-198. */
+EVO_B200_API int evo_b200_bf16_gelu(const void *input, size_t elements,
+                                    void *output, void *stream);
+EVO_B200_API int evo_b200_bf16_gated_elementwise(const void *first,
+                                                 const void *second,
+                                                 size_t elements, int gelu,
+                                                 void *output, void *stream);
+EVO_B200_API int evo_b200_bf16_add(const void *first, const void *second,
+                                   size_t elements, void *output,
+                                   void *stream);
+EVO_B200_API int evo_b200_bf16_add_bias_inplace(void *output, const void *bias,
+                                                size_t rows, size_t width,
+                                                void *stream);
+/* include/evo/cuda/ops.hpp:73-80, src/cuda/ops.cu:200-230. */
+EVO_B200_API int evo_b200_bf16_row_to_column_major(const void *input,
+                                                   size_t rows, size_t columns,
+                                                   void *output, void *stream);
+/* src/cuda/model.cu:269-284. tokens are uint32 ids on the device. */
+EVO_B200_API int evo_b200_embedding(const uint32_t *tokens, const void *table,
+                                    size_t rows, size_t width, void *output,
+                                    void *stream);
+
+/* include/evo/cuda/hyena.hpp (bf16_split_hyena_projection),
+ * src/cuda/hyena.cu:194-208. */
+EVO_B200_API int evo_b200_bf16_split_hyena_projection(
+    const void *projection, size_t rows, size_t width, void *x2, void *x1,
+    void *value, void *stream);
+/* src/cuda/hyena.cu:243-272,1525-1581 (bf16_fir_prefill_direct).  filter is
+ * [groups, taps] BF16 (filter_is_f32 = 0) or F32; orientation 0 =
+ * cross-correlation, 1 = causal convolution; bias_mode 0 add, 1 multiply by
+ * the input; cache (optional) receives the last taps-1 inputs as F32
+ * [channels, taps-1]. */
+EVO_B200_API int evo_b200_bf16_fir_prefill_direct(
+    const void *input, const void *filter, int filter_is_f32, const void *bias,
+    size_t length, size_t channels, size_t groups, size_t taps,
+    int orientation, int bias_mode, void *output, float *cache, void *stream);
+/* src/cuda/hyena.cu:275-416,1583-1652,1737-1790 (bf16_fir_continue_direct /
+ * bf16_fir_decode): length >= 1 new rows against cache_length cached rows;
+ * the cache is advanced afterwards. */
+EVO_B200_API int evo_b200_bf16_fir_continue_direct(
+    const void *input, const void *filter, int filter_is_f32, const void *bias,
+    size_t length, size_t channels, size_t groups, size_t taps,
+    int orientation, int bias_mode, float *cache, size_t cache_length,
+    void *output, void *stream);
+/* include/evo/cuda/hyena.hpp:203-250 (bf16_hcs_prefill, bf16_hcm_prefill,
+ * bf16_hcm_prefill_direct): out = bf16(bf16(fir(bf16(x1*v)) [+ direct*u]) *
+ * x2) in one fused pass.  direct may be NULL (HCS).  pregate (optional)
+ * receives u; inner_cache (optional) the F32 tail of u. */
+EVO_B200_API int evo_b200_bf16_gated_fir_prefill(
+    const void *x2, const void *x1, const void *value, const void *filter,
+    int filter_is_f32, const void *direct, size_t length, size_t width,
+    size_t groups, size_t taps, int orientation, void *pregate,
+    float *inner_cache, void *output, void *stream);
+/* The same operator fed by the raw interleaved projection [length, 3*width]
+ * with the 3-tap featurizer [3*width, 3] applied on the fly
+ * (src/cuda/model.cu:1431-1470 + 1477-1520 in one pass). */
+EVO_B200_API int evo_b200_bf16_projection_gated_fir_prefill(
+    const void *projection, const void *short_filter, const void *filter,
+    int filter_is_f32, const void *direct, size_t length, size_t width,
+    size_t groups, size_t taps, int orientation, void *pregate,
+    float *inner_cache, float *short_cache, void *output, void *stream);
+
+/* include/evo/cuda/hyena.hpp (bf16_hcl_prefill), src/cuda/hyena.cu:1994-2124.
+ * mode 0: initial prefill (state written if non-NULL, four BF16 roundings),
+ * mode 1: continuation from *state (single rounding).  scratch must hold
+ * evo_b200_hcl_scratch_floats(length,width,modes) floats. */
+EVO_B200_API size_t evo_b200_hcl_scratch_floats(size_t length, size_t width,
+                                                size_t modes);
+EVO_B200_API int evo_b200_bf16_hcl_prefill(
+    const void *x2, const void *x1, const void *value, const void *direct,
+    const float *log_poles, const float *residues, size_t length, size_t width,
+    size_t modes, int mode, float *state, float *scratch, void *pregate,
+    void *output, void *stream);
+EVO_B200_API int evo_b200_bf16_projection_hcl_prefill(
+    const void *projection, const void *short_filter, const void *direct,
+    const float *log_poles, const float *residues, size_t length, size_t width,
+    size_t modes, int mode, float *state, float *scratch, float *short_cache,
+    void *pregate, void *output, void *stream);
+/* src/cuda/hyena.cu:718-761,2126-2167 (bf16_hcl_decode). */
+EVO_B200_API int evo_b200_bf16_hcl_decode(
+    const void *x2, const void *x1, const void *value, const void *direct,
+    const float *log_poles, const float *residues, size_t width, size_t modes,
+    float *state, void *pregate, void *output, void *stream);
+
+/* include/evo/cuda/attention.hpp:92-140.  split + RoPE + KV append in one
+ * pass (bf16_split_qkv, bf16_apply_rope, bf16_kv_append;
+ * src/cuda/attention.cu:210-281): qkv [rows, 3*heads*head_dim]; caches are
+ * [capacity, heads, head_dim] and rows are written at position_offset. */
+EVO_B200_API int evo_b200_bf16_split_rope_append(
+    const void *qkv, const float *inverse_frequency, size_t rows, size_t heads,
+    size_t head_dim, size_t position_offset, float position_scale,
+    int head_major, void *query, void *key_cache, void *value_cache,
+    size_t cache_capacity, void *stream);
+/* bf16_flash_causal_attention / bf16_online_causal_attention
+ * (src/cuda/flash_attention.cu:199-441, src/cuda/attention.cu:879-1070). */
+EVO_B200_API int evo_b200_bf16_causal_attention(
+    const void *query, const void *key_cache, const void *value_cache,
+    size_t rows, size_t total_keys, size_t heads, size_t head_dim,
+    void *output, void *stream);
+/* bf16_cached_cross_attention (src/cuda/attention.cu:283-784,1669-1799). */
+EVO_B200_API int evo_b200_bf16_cached_cross_attention(
+    const void *query, const void *key_cache, const void *value_cache,
+    size_t rows, size_t total_keys, size_t heads, size_t head_dim,
+    void *output, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif
