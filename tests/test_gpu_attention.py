@@ -1,0 +1,98 @@
+"""GPU parity of the attention stripe operators against the CPU oracle through
+the operator C ABI (shapes after upstream's tests/test_cuda_attention.cu:
+prefix + chunk, tile boundaries, long-context RoPE positions)."""
+from __future__ import annotations
+
+import numpy as np
+import pytest
+import torch
+
+from gpu_util import (assert_close_bits, dev, dev_bits, empty_bits, host_bits, p, rand_bf16, stream,
+                      ulp_mismatch_report)
+from oracle_lib import ptr
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("head_major", [0, 1])
+@pytest.mark.parametrize("rows,heads,head_dim,offset,scale", [(9, 3, 8, 5, 2.0), (4, 2, 128, 0, 1.0),
+                                                             (3, 2, 128, 1048573, 128.0)])
+def test_split_rope_append(ops, oracle, rows, heads, head_dim, offset, scale, head_major):
+    rng = np.random.default_rng(rows + offset % 97)
+    width = heads * head_dim
+    qkv = rand_bf16(rng, rows, 3 * width)
+    inv = (10000.0 ** (-np.arange(head_dim // 2) * 2.0 / head_dim)).astype(np.float32)
+    base = max(0, offset - 2)           # keep the cache small: it starts at `base`
+    local = offset - base
+    capacity = local + rows
+    q = empty_bits(rows, width)
+    kc, vc = torch.zeros((capacity, width), dtype=torch.int16, device="cuda"), \
+        torch.zeros((capacity, width), dtype=torch.int16, device="cuda")
+    # position_offset is also the cache row; shift the cache pointers so that row
+    # `offset` lands at local row `local`.
+    shift = base * width * 2
+    ops.call("bf16_split_rope_append", p(dev_bits(qkv)), p(dev(inv)), rows, heads, head_dim, offset,
+             scale, head_major, p(q), p(kc) - shift, p(vc) - shift, offset + rows, stream())
+    eq = np.empty((rows, width), np.uint16)
+    ek = np.zeros((offset + rows, width), np.uint16) if offset < 4096 else None
+    if ek is None:
+        # oracle writes at absolute rows; give it a window the same way
+        ek_window = np.zeros((capacity, width), np.uint16)
+        ev_window = np.zeros((capacity, width), np.uint16)
+        oracle.split_rope_append(ptr(qkv), ptr(inv), rows, heads, head_dim, offset, scale, head_major,
+                                 ptr(eq), ek_window.ctypes.data - shift, ev_window.ctypes.data - shift)
+        ek_rows, ev_rows = ek_window[local:], ev_window[local:]
+    else:
+        ev = np.zeros_like(ek)
+        oracle.split_rope_append(ptr(qkv), ptr(inv), rows, heads, head_dim, offset, scale, head_major,
+                                 ptr(eq), ptr(ek), ptr(ev))
+        ek_rows, ev_rows = ek[offset:], ev[offset:]
+    assert np.array_equal(host_bits(vc)[local:], ev_rows)
+    for got, want in ((host_bits(q), eq), (host_bits(kc)[local:], ek_rows)):
+        fraction, gap = ulp_mismatch_report(got, want)
+        # device sincosf vs libm sin/cos and FMA contraction choices: 1 BF16 ulp
+        assert gap <= 1 and fraction < 0.03, (fraction, gap)
+
+
+@pytest.mark.parametrize("rows,prefix,heads,head_dim", [
+    (64, 0, 2, 128), (200, 0, 3, 128), (129, 37, 2, 128), (16, 300, 2, 128), (700, 0, 1, 128),
+    (9, 0, 3, 8), (5, 11, 2, 4), (1, 40, 2, 128)])
+def test_causal_attention(ops, oracle, rows, prefix, heads, head_dim):
+    """Tensor-core flash kernel (head 128, >= 16 rows) and the row-wise kernel.
+    Upstream gates its FlashAttention path against CPU attention at tolerance
+    (tests/test_cuda_attention.cu:265-339); so does this test."""
+    rng = np.random.default_rng(rows * 5 + prefix)
+    width = heads * head_dim
+    total = prefix + rows
+    q = rand_bf16(rng, rows, width)
+    k, v = rand_bf16(rng, total, width), rand_bf16(rng, total, width)
+    out = empty_bits(rows, width)
+    ops.call("bf16_causal_attention", p(dev_bits(q)), p(dev_bits(k)), p(dev_bits(v)), rows, total, heads,
+             head_dim, p(out), stream())
+    expected = np.empty((rows, width), np.uint16)
+    oracle.causal_attention(ptr(q), ptr(k), ptr(v), rows, total, heads, head_dim, ptr(expected))
+    assert_close_bits(host_bits(out), expected, atol=0.02, rtol=0.02, min_cosine=0.9995)
+
+
+@pytest.mark.parametrize("rows,prefix,heads,head_dim", [(1, 0, 2, 128), (1, 2048, 2, 128), (9, 0, 3, 8),
+                                                       (40, 100, 2, 128), (1, 10240, 1, 128)])
+def test_cached_cross_attention(ops, oracle, rows, prefix, heads, head_dim):
+    rng = np.random.default_rng(rows + prefix)
+    width = heads * head_dim
+    total = prefix + rows
+    q = rand_bf16(rng, rows, width)
+    k, v = rand_bf16(rng, total, width), rand_bf16(rng, total, width)
+    out = empty_bits(rows, width)
+    ops.call("bf16_cached_cross_attention", p(dev_bits(q)), p(dev_bits(k)), p(dev_bits(v)), rows, total,
+             heads, head_dim, p(out), stream())
+    expected = np.empty((rows, width), np.uint16)
+    oracle.cached_attention(ptr(q), ptr(k), ptr(v), rows, total, heads, head_dim, ptr(expected))
+    # same BF16 materialisation points; only F32 summation order differs
+    assert_close_bits(host_bits(out), expected, atol=0.01, rtol=0.02, min_cosine=0.9999)
+
+
+def test_attention_rejects_bad_arguments(ops):
+    q = empty_bits(4, 256)
+    assert ops.status("bf16_causal_attention", p(q), p(q), p(q), 4, 2, 2, 128, p(q), stream()) == 2
+    assert ops.status("bf16_split_rope_append", p(q), p(q), 4, 2, 128, 10, 1.0, 0, p(q), p(q), p(q), 8,
+                      stream()) == 2

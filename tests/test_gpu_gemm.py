@@ -1,0 +1,122 @@
+"""GPU parity of the tcgen05 / CUDA-core projections through the C ABI.
+
+Small shapes are checked against the CPU oracle; shapes too large for it are
+checked against an F32 matmul of the same BF16 operands (tolerance 0.02 abs +
+0.02 rel, the gate upstream applies to its cuBLASLt linear,
+tests/test_cuda_ops.cu:252-369)."""
+from __future__ import annotations
+
+import numpy as np
+import pytest
+import torch
+
+from gpu_util import assert_close_bits, dev, dev_bits, empty_bits, host_bits, p, rand_bf16, stream
+from oracle_lib import bf16_to_f32, f32_to_bf16, ptr
+
+pytestmark = pytest.mark.gpu
+
+
+def _linear(ops, x, w, bias, residual, bias_mode, path):
+    rows, inner = x.shape
+    columns = w.shape[0]
+    out = empty_bits(rows, columns)
+    ops.call("bf16_linear", p(x), p(w), p(bias), p(residual), rows, inner, columns, bias_mode,
+             path, p(out), stream())
+    ops.call("check_async_errors", stream())
+    return out
+
+
+@pytest.mark.parametrize("path", [0, 1])
+@pytest.mark.parametrize("rows,inner,columns", [(128, 256, 256), (200, 1920, 640), (16, 4096, 512),
+                                               (1, 256, 128), (333, 320, 1000)])
+def test_bf16_linear_against_oracle(ops, oracle, rows, inner, columns, path):
+    rng = np.random.default_rng(rows + inner + columns)
+    x, w = rand_bf16(rng, rows, inner), rand_bf16(rng, columns, inner, scale=0.05)
+    bias, residual = rand_bf16(rng, columns), rand_bf16(rng, rows, columns)
+    dx, dw, db, dr = dev_bits(x), dev_bits(w), dev_bits(bias), dev_bits(residual)
+    for bias_mode, use_residual in [(0, False), (1, False), (2, True), (1, True)]:
+        out = _linear(ops, dx, dw, db if bias_mode else None, dr if use_residual else None,
+                      bias_mode, path)
+        expected = np.empty((rows, columns), np.uint16)
+        oracle.linear_bf16(ptr(x), ptr(w), ptr(bias) if bias_mode else None,
+                           ptr(residual) if use_residual else None, rows, inner, columns,
+                           bias_mode, ptr(expected))
+        assert_close_bits(host_bits(out), expected, atol=0.02, rtol=0.02, min_cosine=0.9999)
+
+
+def test_bf16_linear_tiny_fixture_shapes_use_cuda_core_path(ops, oracle):
+    """Width 8 / inner 12 (the 50-layer test fixture) cannot be described to TMA."""
+    rng = np.random.default_rng(1)
+    for rows, inner, columns in [(4, 8, 24), (9, 12, 8), (1, 8, 512)]:
+        x, w = rand_bf16(rng, rows, inner), rand_bf16(rng, columns, inner)
+        out = _linear(ops, dev_bits(x), dev_bits(w), None, None, 0, 0)
+        expected = np.empty((rows, columns), np.uint16)
+        oracle.linear_bf16(ptr(x), ptr(w), None, None, rows, inner, columns, 0, ptr(expected))
+        assert_close_bits(host_bits(out), expected, atol=0.02, rtol=0.02)
+
+
+@pytest.mark.parametrize("rows,inner,columns", [(1024, 4096, 4096), (8192, 4096, 512), (2048, 11264, 4096),
+                                               (1000, 1920, 5760)])
+def test_bf16_linear_large_against_f32_matmul(ops, rows, inner, columns):
+    torch.manual_seed(rows)
+    x = torch.randn(rows, inner, device="cuda").bfloat16()
+    w = (torch.randn(columns, inner, device="cuda") * 0.02).bfloat16()
+    out = torch.empty(rows, columns, device="cuda", dtype=torch.bfloat16)
+    ops.call("bf16_linear", p(x), p(w), None, None, rows, inner, columns, 0, 0, p(out), stream())
+    ops.call("check_async_errors", stream())
+    reference = x.float() @ w.float().T
+    error = (out.float() - reference).abs()
+    bound = 0.02 + 0.02 * reference.abs()
+    assert bool((error <= bound).all()), float((error - bound).max())
+    cosine = torch.nn.functional.cosine_similarity(out.float().flatten(), reference.flatten(), dim=0)
+    assert float(cosine) > 0.99995
+
+
+def test_gated_up_projection_matches_two_linears_and_gate(ops, oracle):
+    rng = np.random.default_rng(11)
+    rows, inner, hidden = 150, 256, 384
+    x = rand_bf16(rng, rows, inner)
+    w1, w2 = rand_bf16(rng, hidden, inner, scale=0.08), rand_bf16(rng, hidden, inner, scale=0.08)
+    dx, dw1, dw2 = dev_bits(x), dev_bits(w1), dev_bits(w2)
+    packed = empty_bits(2 * hidden, inner)
+    ops.call("interleave_gate_weights", p(dw1), p(dw2), hidden, inner, p(packed), stream())
+    for activation in (0, 1):
+        out = empty_bits(rows, hidden)
+        ops.call("bf16_gated_up_projection", p(dx), p(packed), rows, inner, hidden, activation,
+                 p(out), stream())
+        ops.call("check_async_errors", stream())
+        first = _linear(ops, dx, dw1, None, None, 0, 0)
+        second = _linear(ops, dx, dw2, None, None, 0, 0)
+        expected = np.empty((rows, hidden), np.uint16)
+        oracle.gate(ptr(host_bits(first)), ptr(host_bits(second)), rows * hidden, activation,
+                    ptr(expected))
+        # same accumulators, same rounding points: identical bits
+        assert np.array_equal(host_bits(out), expected)
+
+
+@pytest.mark.parametrize("rows,inner,columns", [(64, 256, 384), (100, 1920, 5760), (16, 4096, 12288)])
+def test_e4m3_tensorcore_linear_against_exact_products(ops, oracle, rows, inner, columns):
+    rng = np.random.default_rng(columns)
+    x = rand_bf16(rng, rows, inner)
+    w_f = (rng.standard_normal((columns, inner)) * 0.02).astype(np.float32)
+    w_scale = np.float32(448.0 / np.abs(w_f).max())
+    w_codes = np.empty((columns, inner), np.uint8)
+    oracle.quantize_f32(ptr(w_f), w_f.size, float(w_scale), ptr(w_codes))
+    in_scale = np.float32(448.0 / np.abs(bf16_to_f32(x)).max())
+    out_scale = float(np.float32(1.0 / in_scale) * np.float32(1.0 / w_scale))
+    scratch = torch.empty(rows * inner, dtype=torch.uint8, device="cuda")
+    out = empty_bits(rows, columns)
+    ops.call("e4m3_tensorcore_linear", p(dev_bits(x)), p(dev(w_codes)), rows, inner, columns,
+             float(in_scale), out_scale, p(scratch), p(out), stream())
+    ops.call("check_async_errors", stream())
+    if rows * inner * columns <= 1.2e9:
+        expected = np.empty((rows, columns), np.uint16)
+        oracle.e4m3_exact_linear(ptr(x), ptr(w_codes), rows, inner, columns, float(in_scale),
+                                 out_scale, ptr(expected))
+        # exact E4M3 products, F32 accumulation: only summation-order rounding
+        assert_close_bits(host_bits(out), expected, atol=2e-3, rtol=1e-2, min_cosine=0.99999)
+    # and the emulation profile stays within the tolerance gate of the tensor-core one
+    emulated = empty_bits(rows, columns)
+    ops.call("software_e4m3_h100_linear", p(dev_bits(x)), p(dev(w_codes)), rows, inner, columns,
+             float(in_scale), out_scale, p(scratch), p(emulated), stream())
+    assert_close_bits(host_bits(out), host_bits(emulated), atol=0.02, rtol=0.02, min_cosine=0.9999)
