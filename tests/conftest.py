@@ -48,3 +48,12 @@ def ops(pkg):
     if not torch.cuda.is_available():
         pytest.skip("no CUDA device")
     return pkg.ops()
+
+
+@pytest.fixture(autouse=True)
+def _release_device_temporaries():
+    yield
+    for name in ("gpu_util", "oracle_lib"):
+        module = sys.modules.get(name)
+        if module is not None:
+            module.KEEP_ALIVE.clear()

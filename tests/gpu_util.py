@@ -8,9 +8,20 @@ import torch
 from oracle_lib import bf16_to_f32, f32_to_bf16
 
 
+# Device tensors created inline in a call expression must outlive the launch
+# (a freed block is handed to the very next allocation); tests/conftest.py
+# empties this list after every test.
+KEEP_ALIVE: list = []
+
+
+def _keep(tensor: torch.Tensor) -> torch.Tensor:
+    KEEP_ALIVE.append(tensor)
+    return tensor
+
+
 def dev_bits(bits: np.ndarray) -> torch.Tensor:
     """uint16 BF16 bit patterns -> device int16 tensor (same bits)."""
-    return torch.from_numpy(np.ascontiguousarray(bits, dtype=np.uint16).view(np.int16)).cuda()
+    return _keep(torch.from_numpy(np.ascontiguousarray(bits, dtype=np.uint16).view(np.int16)).cuda())
 
 
 def dev(array: np.ndarray) -> torch.Tensor:
@@ -18,8 +29,8 @@ def dev(array: np.ndarray) -> torch.Tensor:
     if array.dtype == np.uint16:
         return dev_bits(array)
     if array.dtype == np.uint32:
-        return torch.from_numpy(array.view(np.int32)).cuda()
-    return torch.from_numpy(array).cuda()
+        return _keep(torch.from_numpy(array.view(np.int32)).cuda())
+    return _keep(torch.from_numpy(array).cuda())
 
 
 def host_bits(tensor: torch.Tensor) -> np.ndarray:
@@ -39,7 +50,10 @@ def stream() -> int:
 
 
 def p(tensor):
-    return None if tensor is None else tensor.data_ptr()
+    if tensor is None:
+        return None
+    KEEP_ALIVE.append(tensor)
+    return tensor.data_ptr()
 
 
 def ulp_mismatch_report(actual_bits: np.ndarray, expected_bits: np.ndarray):

@@ -48,10 +48,16 @@ def bf16_to_f32(bits) -> np.ndarray:
     return (np.ascontiguousarray(bits, dtype=np.uint16).astype(np.uint32) << 16).view(np.float32)
 
 
+# Arrays built inline in a call expression must outlive the foreign call;
+# tests/conftest.py empties this list after every test.
+KEEP_ALIVE: list = []
+
+
 def ptr(array):
     if array is None:
         return None
     assert array.flags["C_CONTIGUOUS"]
+    KEEP_ALIVE.append(array)
     return array.ctypes.data
 
 

