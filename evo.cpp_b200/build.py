@@ -31,8 +31,8 @@ KERNEL_SOURCES = [
 ]
 OPS_SOURCES = KERNEL_SOURCES + ["ops_api.cu"]
 RUNTIME_SOURCES = KERNEL_SOURCES + [
-    "runtime/safetensors.cpp", "runtime/model.cu", "runtime/sampler.cpp",
-    "runtime/c_api.cpp",
+    "runtime/safetensors.cpp", "runtime/model_load.cpp", "runtime/model_weights.cpp",
+    "runtime/model.cu", "runtime/sampler.cpp", "runtime/c_api.cpp",
 ]
 
 

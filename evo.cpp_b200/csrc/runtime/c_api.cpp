@@ -1,0 +1,511 @@
+// The evo_* C ABI (include/evo/evo.h) over the sm_100a runtime.  Behaviour
+// follows upstream src/c_api.cpp: opaque handles, null-safe frees, parameter
+// structs validated through struct_size, thread-local error text, exceptions
+// never cross the boundary, a context is poisoned by any failure after its
+// state may have advanced (src/c_api.cpp:862-1073).
+#include "../../../include/evo/evo.h"
+#include "../../../include/evo/evo_b200.h"
+
+#include <cstring>
+#include <exception>
+#include <memory>
+#include <new>
+#include <string>
+#include <vector>
+
+#include "../common.cuh"
+#include "../ops_internal.hpp"
+#include "model.hpp"
+#include "sampler.hpp"
+
+struct evo_model {
+  std::shared_ptr<evob::ModelFile> file;
+  std::shared_ptr<evob::ModelWeights> weights;
+};
+struct evo_context {
+  std::unique_ptr<evob::Context> context;
+  bool failed = false;
+  std::string profile;
+};
+struct evo_batch {
+  std::size_t capacity = 0;
+  std::vector<std::vector<std::uint8_t>> sequences;
+};
+struct evo_sampler {
+  explicit evo_sampler(const evob::SamplingConfig &config) : sampler(config) {}
+  evob::Sampler sampler;
+};
+
+namespace {
+
+using evob::fail;
+using evob::kOk;
+
+template <typename F>
+evo_status protect(F &&body) {
+  try {
+    const int status = body();
+    if (status == kOk) evob::set_error(kOk, "");
+    return static_cast<evo_status>(status);
+  } catch (const std::bad_alloc &) {
+    return static_cast<evo_status>(fail(evob::kInternal, "out of host memory"));
+  } catch (const std::exception &error) {
+    return static_cast<evo_status>(fail(evob::kInternal, error.what()));
+  } catch (...) {
+    return static_cast<evo_status>(fail(evob::kInternal, "unknown exception"));
+  }
+}
+
+bool valid_status(const evo_status status) {
+  switch (status) {
+    case EVO_STATUS_OK: case EVO_STATUS_INVALID_ARGUMENT: case EVO_STATUS_IO:
+    case EVO_STATUS_MODEL_FORMAT: case EVO_STATUS_UNSUPPORTED: case EVO_STATUS_CUDA:
+    case EVO_STATUS_MPS: case EVO_STATUS_INTERNAL: return true;
+  }
+  return false;
+}
+
+int single_sequence_tokens(const evo_batch *batch, std::vector<std::uint32_t> *tokens) {
+  if (batch->sequences.size() != 1)
+    return fail(evob::kInvalidArgument, "a batch must hold exactly one sequence (batch size 1)");
+  const auto &sequence = batch->sequences.front();
+  if (sequence.empty()) return fail(evob::kInvalidArgument, "sequence is empty");
+  tokens->assign(sequence.begin(), sequence.end());  // identity byte tokenizer
+  return kOk;
+}
+
+}  // namespace
+
+extern "C" {
+
+uint32_t evo_abi_version(void) { return EVO_ABI_VERSION_CURRENT; }
+const char *evo_version_string(void) { return "0.1.0+b200"; }
+
+const char *evo_status_name(const evo_status status) {
+  switch (status) {
+    case EVO_STATUS_OK: return "ok";
+    case EVO_STATUS_INVALID_ARGUMENT: return "invalid_argument";
+    case EVO_STATUS_IO: return "io";
+    case EVO_STATUS_MODEL_FORMAT: return "model_format";
+    case EVO_STATUS_UNSUPPORTED: return "unsupported";
+    case EVO_STATUS_CUDA: return "cuda";
+    case EVO_STATUS_MPS: return "mps";
+    case EVO_STATUS_INTERNAL: return "internal";
+  }
+  return "unknown";
+}
+
+const char *evo_backend_name(const evo_backend backend) {
+  switch (backend) {
+    case EVO_BACKEND_AUTO: return "auto";
+    case EVO_BACKEND_CUDA: return "cuda";
+    case EVO_BACKEND_CPU: return "cpu";
+    case EVO_BACKEND_MPS: return "mps";
+  }
+  return "unknown";
+}
+
+const char *evo_last_error(void) { return evob::last_error(); }
+
+evo_model_params evo_model_default_params(void) {
+  evo_model_params p{};
+  p.struct_size = sizeof(p);
+  p.backend = EVO_BACKEND_AUTO;
+  return p;
+}
+evo_context_params evo_context_default_params(void) {
+  evo_context_params p{};
+  p.struct_size = sizeof(p);
+  p.context_size = 4096;
+  return p;
+}
+evo_sampler_params evo_sampler_default_params(void) {
+  evo_sampler_params p{};
+  p.struct_size = sizeof(p);
+  p.temperature = 1.0F;
+  p.top_k = 1;
+  p.top_p = 1.0F;
+  p.seed = 0;
+  return p;
+}
+evo_embedding_options evo_embedding_default_options(void) {
+  evo_embedding_options o{};
+  o.struct_size = sizeof(o);
+  o.layer = static_cast<size_t>(-1);
+  return o;
+}
+
+evo_status evo_model_load(const char *path, const evo_model_params *params, evo_model **model_out) {
+  return protect([&]() -> int {
+    if (model_out != nullptr) *model_out = nullptr;
+    if (path == nullptr || model_out == nullptr)
+      return fail(evob::kInvalidArgument, "model path and output are required");
+    evo_model_params p = evo_model_default_params();
+    if (params != nullptr) {
+      if (params->struct_size < sizeof(evo_model_params))
+        return fail(evob::kInvalidArgument, "evo_model_params.struct_size is too small");
+      p = *params;
+    }
+    if (p.backend != EVO_BACKEND_AUTO && p.backend != EVO_BACKEND_CUDA)
+      return fail(evob::kUnsupported, "this library provides the CUDA backend only");
+    if (p.device_count != 0 && p.devices == nullptr)
+      return fail(evob::kInvalidArgument, "device list is null");
+    std::vector<int> devices(p.devices, p.devices + p.device_count);
+    if (devices.empty()) devices.push_back(0);
+    auto model = std::make_unique<evo_model>();
+    int status = evob::ModelFile::open(path, &model->file);
+    if (status != kOk) return status;
+    status = evob::load_weights(*model->file, devices,
+                                (p.flags & EVO_MODEL_FLAG_TEST_ONLY_ALLOW_SYNTHETIC) != 0, 0,
+                                &model->weights);
+    if (status != kOk) return status;
+    *model_out = model.release();
+    return kOk;
+  });
+}
+
+void evo_model_free(evo_model *model) { delete model; }
+evo_backend evo_model_backend(const evo_model *model) {
+  return model == nullptr ? EVO_BACKEND_AUTO : EVO_BACKEND_CUDA;
+}
+const char *evo_model_id(const evo_model *model) {
+  return model == nullptr ? "" : model->weights->config.model_id.c_str();
+}
+const char *evo_model_architecture(const evo_model *model) {
+  return model == nullptr ? "" : model->weights->config.architecture.c_str();
+}
+const char *evo_model_profile(const evo_model *model) {
+  return model == nullptr ? "" : model->weights->config.artifact_profile.c_str();
+}
+size_t evo_model_vocab_size(const evo_model *model) {
+  return model == nullptr ? 0 : model->weights->config.vocab;
+}
+size_t evo_model_max_context(const evo_model *model) {
+  return model == nullptr ? 0 : model->weights->config.max_seqlen;
+}
+size_t evo_model_embedding_width(const evo_model *model) {
+  return model == nullptr ? 0 : model->weights->config.width;
+}
+size_t evo_model_layer_count(const evo_model *model) {
+  return model == nullptr ? 0 : model->weights->config.layers;
+}
+
+evo_status evo_model_encode(const evo_model *model, const uint8_t *sequence, size_t length,
+                            uint32_t *tokens, size_t capacity, size_t *count) {
+  return protect([&]() -> int {
+    if (model == nullptr || count == nullptr || (sequence == nullptr && length != 0))
+      return fail(evob::kInvalidArgument, "encode arguments are invalid");
+    *count = length;
+    if (tokens == nullptr) return kOk;
+    if (capacity < length) return fail(evob::kInvalidArgument, "token buffer is too small");
+    for (size_t i = 0; i < length; ++i) tokens[i] = sequence[i];
+    return kOk;
+  });
+}
+
+evo_status evo_model_decode_token(const evo_model *model, uint32_t token, uint8_t *byte_out) {
+  return protect([&]() -> int {
+    if (model == nullptr || byte_out == nullptr)
+      return fail(evob::kInvalidArgument, "decode arguments are invalid");
+    if (token > 255) return fail(evob::kInvalidArgument, "token does not map to a byte");
+    *byte_out = static_cast<uint8_t>(token);
+    return kOk;
+  });
+}
+
+evo_status evo_context_create(const evo_model *model, const evo_context_params *params,
+                              evo_context **context_out) {
+  return protect([&]() -> int {
+    if (context_out != nullptr) *context_out = nullptr;
+    if (model == nullptr || context_out == nullptr)
+      return fail(evob::kInvalidArgument, "model and context output are required");
+    evo_context_params p = evo_context_default_params();
+    if (params != nullptr) {
+      if (params->struct_size < sizeof(evo_context_params))
+        return fail(evob::kInvalidArgument, "evo_context_params.struct_size is too small");
+      p = *params;
+    }
+    if ((p.flags & EVO_CONTEXT_FLAG_FAST_Q8_KV) != 0)
+      return fail(evob::kUnsupported, "the fast-q8-kv profile is not available in this build");
+    const bool tensor_core = (p.flags & EVO_CONTEXT_FLAG_B200_TENSORCORE_FP8) != 0;
+    auto context = std::make_unique<evo_context>();
+    context->profile = tensor_core ? "b200-tc" : "exact";
+    const int status = evob::Context::create(
+        model->weights, p.context_size,
+        tensor_core ? evob::ExecutionProfile::kTensorCore : evob::ExecutionProfile::kExact,
+        (p.flags & EVO_CONTEXT_FLAG_B200_FULL_ARENA) != 0, &context->context);
+    if (status != kOk) return status;
+    *context_out = context.release();
+    return kOk;
+  });
+}
+
+void evo_context_free(evo_context *context) { delete context; }
+size_t evo_context_position(const evo_context *context) {
+  return context == nullptr ? 0 : context->context->position();
+}
+size_t evo_context_capacity(const evo_context *context) {
+  return context == nullptr ? 0 : context->context->context_capacity();
+}
+const char *evo_context_profile(const evo_context *context) {
+  return context == nullptr ? "" : context->profile.c_str();
+}
+
+evo_status evo_context_prefill(evo_context *context, const evo_batch *batch,
+                               evo_logits_callback callback, void *user_data) {
+  return protect([&]() -> int {
+    if (context == nullptr || batch == nullptr || callback == nullptr)
+      return fail(evob::kInvalidArgument, "context, batch and callback are required");
+    if (context->failed || context->context->poisoned())
+      return fail(evob::kInvalidArgument, "context was invalidated by an earlier failure");
+    if (context->context->position() != 0)
+      return fail(evob::kInvalidArgument, "prefill requires a fresh context");
+    std::vector<std::uint32_t> tokens;
+    int status = single_sequence_tokens(batch, &tokens);
+    if (status != kOk) return status;
+    if (tokens.size() > context->context->context_capacity())
+      return fail(evob::kInvalidArgument, "sequence exceeds the context capacity");
+    context->failed = true;  // cleared only if every chunk and callback succeeds
+    const std::size_t capacity = context->context->activation_capacity();
+    const std::size_t columns = context->context->config().vocab;
+    std::vector<float> logits;
+    for (std::size_t offset = 0; offset < tokens.size();) {
+      const std::size_t rows = std::min(capacity, tokens.size() - offset);
+      const std::vector<std::uint32_t> chunk(tokens.begin() + offset, tokens.begin() + offset + rows);
+      status = offset == 0 ? context->context->prefill(chunk, &logits)
+                           : context->context->prefill_chunk(chunk, &logits);
+      if (status != kOk) return status;
+      if (logits.size() != rows * columns)
+        return fail(evob::kInternal, "backend returned incomplete logits");
+      const evo_status callback_status = callback(logits.data(), rows, columns, offset, user_data);
+      if (callback_status != EVO_STATUS_OK)
+        return fail(valid_status(callback_status) ? callback_status : EVO_STATUS_INTERNAL,
+                    "logits consumer aborted prefill");
+      offset += rows;
+    }
+    context->failed = false;
+    return kOk;
+  });
+}
+
+evo_status evo_context_decode(evo_context *context, uint32_t token, evo_logits_callback callback,
+                              void *user_data) {
+  return protect([&]() -> int {
+    if (context == nullptr || callback == nullptr)
+      return fail(evob::kInvalidArgument, "context and callback are required");
+    if (context->failed || context->context->poisoned())
+      return fail(evob::kInvalidArgument, "context was invalidated by an earlier failure");
+    std::vector<float> logits;
+    const std::size_t offset = context->context->position();
+    int status = context->context->decode(token, &logits);
+    if (status != kOk) {
+      if (context->context->poisoned()) context->failed = true;
+      return status;
+    }
+    const evo_status callback_status =
+        callback(logits.data(), 1, context->context->config().vocab, offset, user_data);
+    if (callback_status != EVO_STATUS_OK) {
+      context->failed = true;
+      return fail(valid_status(callback_status) ? callback_status : EVO_STATUS_INTERNAL,
+                  "logits consumer aborted decode");
+    }
+    return kOk;
+  });
+}
+
+static int embed_rows(evo_context *context, const evo_batch *batch, const size_t layer,
+                      std::vector<float> *hidden, std::size_t *rows) {
+  if (context->failed || context->context->poisoned())
+    return fail(evob::kInvalidArgument, "context was invalidated by an earlier failure");
+  std::vector<std::uint32_t> tokens;
+  const int status = single_sequence_tokens(batch, &tokens);
+  if (status != kOk) return status;
+  if (tokens.size() > context->context->activation_capacity())
+    return fail(evob::kUnsupported, "embedding input exceeds the activation arena");
+  *rows = tokens.size();
+  return context->context->prefill_embedding(tokens, layer, hidden);
+}
+
+evo_status evo_context_embed(evo_context *context, const evo_batch *batch, size_t layer,
+                             evo_embedding_callback callback, void *user_data) {
+  return protect([&]() -> int {
+    if (context == nullptr || batch == nullptr || callback == nullptr)
+      return fail(evob::kInvalidArgument, "context, batch and callback are required");
+    std::vector<float> hidden;
+    std::size_t rows = 0;
+    const int status = embed_rows(context, batch, layer, &hidden, &rows);
+    if (status != kOk) return status;
+    const evo_status callback_status =
+        callback(hidden.data(), rows, context->context->config().width, 0, user_data);
+    if (callback_status != EVO_STATUS_OK)
+      return fail(valid_status(callback_status) ? callback_status : EVO_STATUS_INTERNAL,
+                  "embedding consumer aborted");
+    return kOk;
+  });
+}
+
+evo_status evo_context_embed_ex(evo_context *context, const evo_batch *batch,
+                                const evo_embedding_options *options,
+                                evo_embedding_ex_callback callback, void *user_data) {
+  return protect([&]() -> int {
+    if (context == nullptr || batch == nullptr || callback == nullptr || options == nullptr ||
+        options->struct_size < sizeof(evo_embedding_options))
+      return fail(evob::kInvalidArgument, "context, batch, options and callback are required");
+    if (options->preset != nullptr && options->preset[0] != '\0')
+      return fail(evob::kUnsupported, "embedding presets are not defined for StripedHyena2");
+    const std::string pooling = options->pooling == nullptr ? "none" : options->pooling;
+    if (pooling != "none" && pooling != "mean" && pooling != "last")
+      return fail(evob::kUnsupported, "unsupported pooling: " + pooling);
+    std::vector<float> hidden;
+    std::size_t rows = 0;
+    const int status = embed_rows(context, batch, options->layer, &hidden, &rows);
+    if (status != kOk) return status;
+    const std::size_t width = context->context->config().width;
+    std::vector<float> pooled;
+    std::size_t out_rows = rows;
+    const float *data = hidden.data();
+    if (pooling == "mean") {
+      pooled.assign(width, 0.0F);
+      for (std::size_t r = 0; r < rows; ++r)
+        for (std::size_t c = 0; c < width; ++c) pooled[c] += hidden[r * width + c];
+      for (float &v : pooled) v /= static_cast<float>(rows);
+      data = pooled.data();
+      out_rows = 1;
+    } else if (pooling == "last") {
+      data = hidden.data() + (rows - 1) * width;
+      out_rows = 1;
+    }
+    evo_embedding_result_info info{};
+    info.struct_size = sizeof(info);
+    info.resolved_preset = "";
+    info.hidden_tap = "block_output";
+    info.pooling = pooling.c_str();
+    info.layer = options->layer;
+    info.original_length = info.effective_length = info.token_count = rows;
+    info.rows = out_rows;
+    info.columns = width;
+    const evo_status callback_status = callback(data, out_rows, width, 0, &info, user_data);
+    if (callback_status != EVO_STATUS_OK)
+      return fail(valid_status(callback_status) ? callback_status : EVO_STATUS_INTERNAL,
+                  "embedding consumer aborted");
+    return kOk;
+  });
+}
+
+evo_status evo_batch_create(size_t sequence_capacity, evo_batch **batch_out) {
+  return protect([&]() -> int {
+    if (batch_out == nullptr || sequence_capacity == 0)
+      return fail(evob::kInvalidArgument, "batch capacity and output are required");
+    auto *batch = new evo_batch();
+    batch->capacity = sequence_capacity;
+    *batch_out = batch;
+    return kOk;
+  });
+}
+void evo_batch_free(evo_batch *batch) { delete batch; }
+void evo_batch_clear(evo_batch *batch) {
+  if (batch != nullptr) batch->sequences.clear();
+}
+evo_status evo_batch_add_sequence(evo_batch *batch, const uint8_t *sequence, size_t length) {
+  return protect([&]() -> int {
+    if (batch == nullptr || sequence == nullptr || length == 0)
+      return fail(evob::kInvalidArgument, "batch and a non-empty sequence are required");
+    if (batch->sequences.size() >= batch->capacity)
+      return fail(evob::kInvalidArgument, "batch sequence capacity exceeded");
+    batch->sequences.emplace_back(sequence, sequence + length);
+    return kOk;
+  });
+}
+size_t evo_batch_sequence_count(const evo_batch *batch) {
+  return batch == nullptr ? 0 : batch->sequences.size();
+}
+size_t evo_batch_token_count(const evo_batch *batch) {
+  size_t total = 0;
+  if (batch != nullptr)
+    for (const auto &s : batch->sequences) total += s.size();
+  return total;
+}
+
+evo_status evo_sampler_create(const evo_sampler_params *params, evo_sampler **sampler_out) {
+  return protect([&]() -> int {
+    if (sampler_out == nullptr) return fail(evob::kInvalidArgument, "sampler output is required");
+    *sampler_out = nullptr;
+    evo_sampler_params p = evo_sampler_default_params();
+    if (params != nullptr) {
+      if (params->struct_size < sizeof(evo_sampler_params))
+        return fail(evob::kInvalidArgument, "evo_sampler_params.struct_size is too small");
+      p = *params;
+    }
+    evob::SamplingConfig config;
+    config.temperature = p.temperature;
+    config.top_k = p.top_k;
+    config.top_p = p.top_p;
+    config.seed = p.seed;
+    const int status = evob::validate_sampling(config);
+    if (status != kOk) return status;
+    *sampler_out = new evo_sampler(config);
+    return kOk;
+  });
+}
+void evo_sampler_free(evo_sampler *sampler) { delete sampler; }
+evo_status evo_sampler_sample(evo_sampler *sampler, const float *logits, size_t count,
+                              uint32_t *token_out) {
+  return protect([&]() -> int {
+    if (sampler == nullptr) return fail(evob::kInvalidArgument, "sampler is required");
+    return sampler->sampler.sample(logits, count, token_out);
+  });
+}
+
+// ---- extensions (include/evo/evo_b200.h)
+evo_status evo_b200_context_prefill_device(evo_context *context, const uint32_t *device_tokens,
+                                           size_t rows, int stateless,
+                                           const void **device_logits_out) {
+  return protect([&]() -> int {
+    if (context == nullptr) return fail(evob::kInvalidArgument, "context is required");
+    if (context->failed || context->context->poisoned())
+      return fail(evob::kInvalidArgument, "context was invalidated by an earlier failure");
+    const int status = context->context->prefill_device(device_tokens, rows, stateless != 0);
+    if (status != kOk) {
+      context->failed = true;
+      return status;
+    }
+    if (device_logits_out != nullptr) *device_logits_out = context->context->device_logits();
+    return kOk;
+  });
+}
+
+void *evo_b200_context_stream(const evo_context *context) {
+  return context == nullptr ? nullptr : context->context->first_stream();
+}
+
+evo_status evo_b200_context_synchronize(evo_context *context) {
+  return protect([&]() -> int {
+    if (context == nullptr) return fail(evob::kInvalidArgument, "context is required");
+    const int status = context->context->synchronize();
+    if (status != kOk) context->failed = true;
+    return status;
+  });
+}
+
+size_t evo_b200_context_stage_count(const evo_context *context) {
+  return context == nullptr ? 0 : context->context->stages().size();
+}
+
+evo_status evo_b200_context_stage_info(const evo_context *context, size_t index,
+                                       evo_b200_stage_info *info) {
+  return protect([&]() -> int {
+    if (context == nullptr || info == nullptr || info->struct_size < sizeof(evo_b200_stage_info))
+      return fail(evob::kInvalidArgument, "stage query arguments are invalid");
+    const auto stages = context->context->stages();
+    if (index >= stages.size()) return fail(evob::kInvalidArgument, "stage index is out of range");
+    info->device = stages[index].device;
+    info->layer_begin = stages[index].layer_begin;
+    info->layer_end = stages[index].layer_end;
+    info->weight_bytes = stages[index].weight_bytes;
+    info->cache_bytes = stages[index].cache_bytes;
+    info->arena_bytes = stages[index].arena_bytes;
+    return kOk;
+  });
+}
+
+}  // extern "C"

@@ -1,0 +1,524 @@
+// Per-context state and the block graph of the StripedHyena2 forward pass
+// (upstream src/cuda/model.cu:1327-1944 run_mixer / run_blocks / forward and
+// 2148-2366 PipelineModel).  One Stage per GPU owns a stream, an activation
+// arena and the causal state of its blocks (FIR histories, modal state, KV
+// cache).  Stages are chained with stream-ordered peer copies: no host
+// synchronisation between stages, only the final logits read-back blocks.
+#include <algorithm>
+#include <cstring>
+
+#include "../common.cuh"
+#include "../ops_internal.hpp"
+#include "model.hpp"
+
+namespace evob {
+
+namespace {
+constexpr std::size_t kArenaRows = 8192;       // upstream src/cuda/model.cu:31
+constexpr std::size_t kFixtureArenaRows = 8;   // upstream src/cuda/model.cu:32
+
+#define EVOB_TRY(expr)                    \
+  do {                                    \
+    const int status__ = (expr);          \
+    if (status__ != kOk) return status__; \
+  } while (0)
+
+struct DeviceGuard {
+  int previous = 0;
+  explicit DeviceGuard(const int device) {
+    cudaGetDevice(&previous);
+    cudaSetDevice(device);
+  }
+  ~DeviceGuard() { cudaSetDevice(previous); }
+};
+}  // namespace
+
+struct LayerState {
+  float *short_cache = nullptr;  // [3D, short_taps-1]
+  float *inner_cache = nullptr;  // [D, taps-1]
+  float *modal_state = nullptr;  // [D, S]
+  void *key_cache = nullptr, *value_cache = nullptr;  // [context, D] BF16
+};
+
+struct Context::Stage {
+  std::shared_ptr<StageWeights> weights;
+  int device = 0;
+  cudaStream_t stream = nullptr;
+  cudaEvent_t done = nullptr;
+  std::vector<void *> allocations;
+  std::size_t arena_bytes = 0, cache_bytes = 0;
+  // activations
+  void *hidden = nullptr, *residual = nullptr, *normalized = nullptr, *mixer_out = nullptr;
+  void *codes = nullptr, *projection = nullptr, *query = nullptr, *gated = nullptr;
+  void *mlp_first = nullptr, *mlp_second = nullptr;
+  void *short_filtered = nullptr, *x2 = nullptr, *x1 = nullptr, *value = nullptr, *pregate = nullptr;
+  float *modal_scratch = nullptr;
+  std::uint32_t *tokens = nullptr;
+  void *logits = nullptr;
+  std::vector<LayerState> layers;
+
+  int allocate(void **out, const std::size_t bytes, std::size_t *counter) {
+    if (cudaMalloc(out, bytes == 0 ? 16 : bytes) != cudaSuccess)
+      return fail(kCuda, "cannot allocate " + std::to_string(bytes >> 20) + " MiB on device " +
+                             std::to_string(device));
+    allocations.push_back(*out);
+    *counter += bytes;
+    return kOk;
+  }
+  ~Stage() {
+    DeviceGuard guard(device);
+    if (stream != nullptr) cudaStreamSynchronize(stream);
+    for (void *p : allocations) cudaFree(p);
+    if (done != nullptr) cudaEventDestroy(done);
+    if (stream != nullptr) cudaStreamDestroy(stream);
+  }
+};
+
+Context::~Context() = default;
+
+int Context::create(std::shared_ptr<ModelWeights> weights, const std::size_t context_size,
+                    const ExecutionProfile profile, const bool full_arena_for_fixtures,
+                    std::unique_ptr<Context> *out) {
+  if (weights == nullptr || out == nullptr || context_size == 0)
+    return fail(kInvalidArgument, "context arguments are invalid");
+  const ModelConfig &c = weights->config;
+  if (!c.test_fixture && context_size > c.max_seqlen)
+    return fail(kInvalidArgument, "requested context exceeds model maximum of " +
+                                      std::to_string(c.max_seqlen));
+  std::unique_ptr<Context> context(new Context());
+  context->weights_ = weights;
+  context->profile_ = profile;
+  context->context_size_ = context_size;
+  context->arena_rows_ = std::min(
+      context_size, c.test_fixture && !full_arena_for_fixtures ? kFixtureArenaRows : kArenaRows);
+  const std::size_t T = context->arena_rows_, D = c.width, I = c.inner_width;
+  const bool fused_gate = !weights->stages.empty() && !weights->stages[0]->layers.empty() &&
+                          weights->stages[0]->layers[0].l12 != nullptr;
+  for (const auto &stage_weights : weights->stages) {
+    auto stage = std::make_unique<Stage>();
+    stage->weights = stage_weights;
+    stage->device = stage_weights->device;
+    DeviceGuard guard(stage->device);
+    if (cudaStreamCreateWithFlags(&stage->stream, cudaStreamNonBlocking) != cudaSuccess ||
+        cudaEventCreateWithFlags(&stage->done, cudaEventDisableTiming) != cudaSuccess)
+      return fail(kCuda, "cannot create the context stream");
+    std::size_t *arena = &stage->arena_bytes;
+    EVOB_TRY(stage->allocate(&stage->hidden, T * D * 2, arena));
+    EVOB_TRY(stage->allocate(&stage->residual, T * D * 2, arena));
+    EVOB_TRY(stage->allocate(&stage->normalized, T * D * 2, arena));
+    EVOB_TRY(stage->allocate(&stage->mixer_out, T * D * 2, arena));
+    EVOB_TRY(stage->allocate(&stage->query, T * D * 2, arena));
+    EVOB_TRY(stage->allocate(&stage->codes, T * D, arena));
+    EVOB_TRY(stage->allocate(&stage->projection, T * D * 6, arena));
+    EVOB_TRY(stage->allocate(&stage->gated, T * I * 2, arena));
+    if (!fused_gate) {
+      EVOB_TRY(stage->allocate(&stage->mlp_first, T * I * 2, arena));
+      EVOB_TRY(stage->allocate(&stage->mlp_second, T * I * 2, arena));
+    }
+    EVOB_TRY(stage->allocate(&stage->short_filtered, T * D * 6, arena));
+    EVOB_TRY(stage->allocate(&stage->x2, T * D * 2, arena));
+    EVOB_TRY(stage->allocate(&stage->x1, T * D * 2, arena));
+    EVOB_TRY(stage->allocate(&stage->value, T * D * 2, arena));
+    EVOB_TRY(stage->allocate(&stage->pregate, T * D * 2, arena));
+    void *p = nullptr;
+    EVOB_TRY(stage->allocate(&p, modal_scratch_floats(T, D, c.state_size) * 4 + 16, arena));
+    stage->modal_scratch = static_cast<float *>(p);
+    EVOB_TRY(stage->allocate(&p, T * 4, arena));
+    stage->tokens = static_cast<std::uint32_t *>(p);
+    EVOB_TRY(stage->allocate(&stage->logits, T * c.vocab * 2, arena));
+    stage->layers.resize(stage_weights->layers.size());
+    std::size_t *cache = &stage->cache_bytes;
+    for (std::size_t i = 0; i < stage->layers.size(); ++i) {
+      LayerState &state = stage->layers[i];
+      const MixerType type = stage_weights->layers[i].type;
+      if (type == MixerType::kAttention) {
+        EVOB_TRY(stage->allocate(&state.key_cache, context_size * D * 2, cache));
+        EVOB_TRY(stage->allocate(&state.value_cache, context_size * D * 2, cache));
+        continue;
+      }
+      EVOB_TRY(stage->allocate(&p, 3 * D * (c.short_taps - 1) * 4, cache));
+      state.short_cache = static_cast<float *>(p);
+      if (type == MixerType::kHcl) {
+        EVOB_TRY(stage->allocate(&p, D * c.state_size * 4, cache));
+        state.modal_state = static_cast<float *>(p);
+      } else {
+        const std::size_t taps = type == MixerType::kHcs ? c.hcs_taps : c.hcm_taps;
+        EVOB_TRY(stage->allocate(&p, D * (taps - 1) * 4, cache));
+        state.inner_cache = static_cast<float *>(p);
+      }
+    }
+    context->stages_.push_back(std::move(stage));
+  }
+  *out = std::move(context);
+  return kOk;
+}
+
+std::vector<StageAssignment> Context::stages() const {
+  std::vector<StageAssignment> list;
+  for (const auto &stage : stages_) {
+    StageAssignment a;
+    a.device = stage->device;
+    a.layer_begin = stage->weights->layer_begin;
+    a.layer_end = stage->weights->layer_end;
+    a.weight_bytes = stage->weights->weight_bytes;
+    a.cache_bytes = stage->cache_bytes;
+    a.arena_bytes = stage->arena_bytes;
+    list.push_back(a);
+  }
+  return list;
+}
+
+const void *Context::device_logits() const { return stages_.front()->logits; }
+void *Context::first_stream() const { return stages_.front()->stream; }
+
+int Context::synchronize() {
+  int status = kOk;
+  for (const auto &stage : stages_) {
+    DeviceGuard guard(stage->device);
+    if (cudaStreamSynchronize(stage->stream) != cudaSuccess) {
+      status = fail(kCuda, std::string("stream synchronisation failed: ") +
+                               cudaGetErrorString(cudaGetLastError()));
+      break;
+    }
+    const int gemm = gemm_error_state(stage->stream);
+    if (gemm != kOk) status = gemm;
+  }
+  if (status != kOk) {
+    healthy_ = false;
+    state_valid_ = false;
+  }
+  return status;
+}
+
+int Context::run_stage(Stage &s, const std::size_t rows, const Mode mode,
+                       const long capture_layer, std::vector<float> *captured) {
+  const ModelConfig &c = weights_->config;
+  const std::size_t D = c.width, I = c.inner_width;
+  const bool initial = mode == Mode::kPrefill || mode == Mode::kStateless || mode == Mode::kCachedPrefill;
+  const bool stateless = mode == Mode::kStateless;
+  cudaStream_t stream = s.stream;
+  for (std::size_t i = 0; i < s.layers.size(); ++i) {
+    const LayerWeights &w = s.weights->layers[i];
+    LayerState &state = s.layers[i];
+    const bool attention = w.type == MixerType::kAttention;
+    const bool fp8 = !attention && c.fp8_projection;
+    // pre-norm (+ E4M3 codes of the normalised activations for FP8 projections)
+    EVOB_TRY(rms_norm(s.hidden, w.pre_norm, rows, D, c.epsilon, fp8 ? nullptr : s.normalized,
+                      fp8 ? s.codes : nullptr, w.projection_input_scale, stream));
+    // input projection -> [rows, 3D]
+    if (fp8 && profile_ == ExecutionProfile::kExact) {
+      EVOB_TRY(e4m3_emulated_gemm(s.codes, w.projection, rows, D, 3 * D,
+                                  w.projection_output_scale, s.projection, stream));
+    } else {
+      LinearArgs a;
+      a.input = fp8 ? s.codes : s.normalized;
+      a.weight = w.projection;
+      a.output = s.projection;
+      a.rows = rows;
+      a.in_features = D;
+      a.out_features = 3 * D;
+      if (fp8) {
+        a.operand_type = OperandType::kE4m3;
+        a.alpha = w.projection_output_scale;
+      }
+      EVOB_TRY(linear(a, stream));
+    }
+    if (attention) {
+      const std::size_t prefix = initial ? 0 : position_;
+      EVOB_TRY(split_rope_append(s.projection, w.inverse_frequency, rows, c.heads, c.head_dim(),
+                                 prefix, c.rope_scale, false, s.query, state.key_cache,
+                                 state.value_cache, context_size_, stream));
+      const bool cached = mode == Mode::kCachedPrefill ||
+                          ((mode == Mode::kDecode || mode == Mode::kContinue) && cached_attention_);
+      if (cached)
+        EVOB_TRY(cached_attention(s.query, state.key_cache, state.value_cache, rows, prefix + rows,
+                                  c.heads, c.head_dim(), s.mixer_out, stream));
+      else
+        EVOB_TRY(causal_attention(s.query, state.key_cache, state.value_cache, rows, prefix + rows,
+                                  c.heads, c.head_dim(), s.mixer_out, stream));
+    } else if (initial) {
+      if (w.type == MixerType::kHcl) {
+        ModalArgs a;
+        a.projection = s.projection;
+        a.short_filter = w.short_filter;
+        a.short_taps = c.short_taps;
+        a.direct = w.direct;
+        a.log_poles = w.log_poles;
+        a.residues = w.residues;
+        a.output = s.mixer_out;
+        a.state = stateless ? nullptr : state.modal_state;
+        a.scratch = s.modal_scratch;
+        a.short_cache = stateless ? nullptr : state.short_cache;
+        a.length = rows;
+        a.width = D;
+        a.modes = c.state_size;
+        EVOB_TRY(modal_prefill(a, stream));
+      } else {
+        const bool hcs = w.type == MixerType::kHcs;
+        GatedFirArgs a;
+        a.projection = s.projection;
+        a.short_filter = w.short_filter;
+        a.short_taps = c.short_taps;
+        a.filter = w.inner_filter;
+        a.filter_is_f32 = !hcs && c.hcm_filter_f32;
+        a.direct = hcs ? nullptr : w.direct;
+        a.output = s.mixer_out;
+        a.length = rows;
+        a.width = D;
+        a.groups = hcs ? c.hcs_groups : c.hcm_groups;
+        a.taps = hcs ? c.hcs_taps : c.hcm_taps;
+        a.cross_correlation = hcs;
+        a.inner_cache = stateless ? nullptr : state.inner_cache;
+        a.short_cache = stateless ? nullptr : state.short_cache;
+        EVOB_TRY(gated_fir_prefill(a, stream));
+      }
+    } else {
+      // continuation / decode against the causal state
+      const std::size_t short_cached = std::min(position_, c.short_taps - 1);
+      EVOB_TRY(fir_step(s.projection, w.short_filter, false, nullptr, false, rows, 3 * D, 3 * D,
+                        c.short_taps, true, state.short_cache, short_cached, s.short_filtered,
+                        stream));
+      EVOB_TRY(split_triples(s.short_filtered, rows, D, s.x2, s.x1, s.value, stream));
+      if (w.type == MixerType::kHcl) {
+        if (mode == Mode::kDecode) {
+          EVOB_TRY(modal_decode(s.x2, s.x1, s.value, w.direct, w.log_poles, w.residues, D,
+                                c.state_size, state.modal_state, s.pregate, s.mixer_out, stream));
+        } else {
+          ModalArgs a;
+          a.x2 = s.x2;
+          a.x1 = s.x1;
+          a.value = s.value;
+          a.direct = w.direct;
+          a.log_poles = w.log_poles;
+          a.residues = w.residues;
+          a.output = s.mixer_out;
+          a.state = state.modal_state;
+          a.scratch = s.modal_scratch;
+          a.length = rows;
+          a.width = D;
+          a.modes = c.state_size;
+          a.continue_from_state = true;
+          EVOB_TRY(modal_prefill(a, stream));
+        }
+      } else {
+        const bool hcs = w.type == MixerType::kHcs;
+        const std::size_t taps = hcs ? c.hcs_taps : c.hcm_taps;
+        EVOB_TRY(gate(s.x1, s.value, s.pregate, rows * D, false, stream));
+        EVOB_TRY(fir_step(s.pregate, w.inner_filter, !hcs && c.hcm_filter_f32,
+                          hcs ? nullptr : w.direct, !hcs, rows, D,
+                          hcs ? c.hcs_groups : c.hcm_groups, taps, hcs, state.inner_cache,
+                          std::min(position_, taps - 1), s.query, stream));
+        EVOB_TRY(gate(s.query, s.x2, s.mixer_out, rows * D, false, stream));
+      }
+    }
+    // output projection + bias + residual -> residual buffer
+    {
+      LinearArgs a;
+      a.input = s.mixer_out;
+      a.weight = w.out_weight;
+      a.bias = w.out_bias;
+      a.residual = s.hidden;
+      a.output = s.residual;
+      a.rows = rows;
+      a.in_features = D;
+      a.out_features = D;
+      // fused for attention and single-row Hyena, separately rounded otherwise
+      // (upstream src/cuda/model.cu:1768-1799)
+      a.bias_mode = (attention || rows == 1) ? 1 : 2;
+      EVOB_TRY(linear(a, stream));
+    }
+    EVOB_TRY(rms_norm(s.residual, w.post_norm, rows, D, c.epsilon, s.normalized, nullptr, 1.0F,
+                      stream));
+    const std::size_t layer_index = s.weights->layer_begin + i;
+    const bool gelu_block = layer_index == 0;
+    if (w.l12 != nullptr) {
+      LinearArgs a;
+      a.input = s.normalized;
+      a.weight = w.l12;
+      a.output = s.gated;
+      a.rows = rows;
+      a.in_features = D;
+      a.out_features = 2 * I;
+      a.gate_mode = gelu_block ? 2 : 1;
+      EVOB_TRY(linear(a, stream));
+    } else {
+      LinearArgs a;
+      a.input = s.normalized;
+      a.rows = rows;
+      a.in_features = D;
+      a.out_features = I;
+      a.weight = w.l1;
+      a.output = s.mlp_first;
+      EVOB_TRY(linear(a, stream));
+      a.weight = w.l2;
+      a.output = s.mlp_second;
+      EVOB_TRY(linear(a, stream));
+      EVOB_TRY(gate(s.mlp_first, s.mlp_second, s.gated, rows * I, gelu_block, stream));
+    }
+    {
+      LinearArgs a;
+      a.input = s.gated;
+      a.weight = w.l3;
+      a.residual = s.residual;
+      a.output = s.hidden;
+      a.rows = rows;
+      a.in_features = I;
+      a.out_features = D;
+      EVOB_TRY(linear(a, stream));
+    }
+    if (capture_layer >= 0 && static_cast<std::size_t>(capture_layer) == layer_index &&
+        captured != nullptr) {
+      std::vector<std::uint16_t> raw(rows * D);
+      if (cudaMemcpyAsync(raw.data(), s.hidden, raw.size() * 2, cudaMemcpyDeviceToHost, stream) !=
+              cudaSuccess ||
+          cudaStreamSynchronize(stream) != cudaSuccess)
+        return fail(kCuda, "layer capture failed");
+      captured->resize(raw.size());
+      for (std::size_t j = 0; j < raw.size(); ++j) {
+        const std::uint32_t bits = static_cast<std::uint32_t>(raw[j]) << 16U;
+        std::memcpy(&(*captured)[j], &bits, 4);
+      }
+    }
+  }
+  return kOk;
+}
+
+int Context::forward(const std::uint32_t *host_tokens, const std::uint32_t *device_tokens,
+                     const std::size_t rows, const Mode mode, std::vector<float> *logits,
+                     const long capture_layer, std::vector<float> *captured) {
+  const ModelConfig &c = weights_->config;
+  if (!healthy_) return fail(kInvalidArgument, "context was invalidated by an earlier failure");
+  if (rows == 0 || rows > arena_rows_)
+    return fail(kInvalidArgument, "model forward arguments are invalid");
+  const bool initial = mode == Mode::kPrefill || mode == Mode::kStateless || mode == Mode::kCachedPrefill;
+  if (initial) {
+    if (rows > context_size_) return fail(kInvalidArgument, "prompt exceeds the context capacity");
+  } else if (!state_valid_ || position_ > context_size_ || rows > context_size_ - position_ ||
+             (mode == Mode::kDecode && rows != 1)) {
+    return fail(kInvalidArgument,
+                "continuation requires a valid prefill and free context capacity");
+  }
+  if (host_tokens != nullptr)
+    for (std::size_t i = 0; i < rows; ++i)
+      if (host_tokens[i] >= c.vocab)
+        return fail(kInvalidArgument, "token ID exceeds model vocabulary");
+  int status = kOk;
+  Stage &first = *stages_.front();
+  {
+    DeviceGuard guard(first.device);
+    if (host_tokens != nullptr) {
+      if (cudaMemcpyAsync(first.tokens, host_tokens, rows * 4, cudaMemcpyHostToDevice,
+                          first.stream) != cudaSuccess)
+        status = fail(kCuda, "token upload failed");
+      device_tokens = first.tokens;
+    }
+    if (status == kOk)
+      status = embedding(device_tokens, first.weights->embedding, rows, c.width, first.hidden,
+                         first.stream);
+  }
+  for (std::size_t index = 0; index < stages_.size() && status == kOk; ++index) {
+    Stage &stage = *stages_[index];
+    DeviceGuard guard(stage.device);
+    if (index > 0) {
+      Stage &previous = *stages_[index - 1];
+      if (cudaStreamWaitEvent(stage.stream, previous.done, 0) != cudaSuccess ||
+          cudaMemcpyPeerAsync(stage.hidden, stage.device, previous.hidden, previous.device,
+                              rows * c.width * 2, stage.stream) != cudaSuccess)
+        status = fail(kCuda, "stage hand-off failed");
+    }
+    if (status == kOk) status = run_stage(stage, rows, mode, capture_layer, captured);
+    if (status == kOk && cudaEventRecord(stage.done, stage.stream) != cudaSuccess)
+      status = fail(kCuda, "stage hand-off failed");
+  }
+  if (status == kOk) {
+    DeviceGuard guard(first.device);
+    if (stages_.size() > 1) {
+      Stage &last = *stages_.back();
+      if (cudaStreamWaitEvent(first.stream, last.done, 0) != cudaSuccess ||
+          cudaMemcpyPeerAsync(first.hidden, first.device, last.hidden, last.device,
+                              rows * c.width * 2, first.stream) != cudaSuccess)
+        status = fail(kCuda, "stage hand-off failed");
+    }
+    if (status == kOk)
+      status = rms_norm(first.hidden, first.weights->final_norm, rows, c.width, c.epsilon,
+                        first.normalized, nullptr, 1.0F, first.stream);
+    if (status == kOk) {
+      LinearArgs a;
+      a.input = first.normalized;
+      a.weight = first.weights->embedding;  // tied head
+      a.output = first.logits;
+      a.rows = rows;
+      a.in_features = c.width;
+      a.out_features = c.vocab;
+      status = linear(a, first.stream);
+    }
+    if (status == kOk && logits != nullptr) {
+      std::vector<std::uint16_t> raw(rows * c.vocab);
+      if (cudaMemcpyAsync(raw.data(), first.logits, raw.size() * 2, cudaMemcpyDeviceToHost,
+                          first.stream) != cudaSuccess ||
+          cudaStreamSynchronize(first.stream) != cudaSuccess) {
+        status = fail(kCuda, std::string("logits read-back failed: ") +
+                                 cudaGetErrorString(cudaGetLastError()));
+      } else {
+        logits->resize(raw.size());
+        for (std::size_t j = 0; j < raw.size(); ++j) {
+          const std::uint32_t bits = static_cast<std::uint32_t>(raw[j]) << 16U;
+          std::memcpy(&(*logits)[j], &bits, 4);
+        }
+        for (const auto &stage : stages_) {
+          DeviceGuard stage_guard(stage->device);
+          if (status == kOk) status = gemm_error_state(stage->stream);
+        }
+      }
+    }
+  }
+  if (status != kOk) {
+    state_valid_ = false;
+    healthy_ = false;
+    return status;
+  }
+  const bool stateless = mode == Mode::kStateless;
+  position_ = stateless ? 0 : (initial ? rows : position_ + rows);
+  state_valid_ = !stateless;
+  if (initial) cached_attention_ = mode == Mode::kCachedPrefill;
+  return kOk;
+}
+
+int Context::prefill(const std::vector<std::uint32_t> &tokens, std::vector<float> *logits) {
+  if (logits == nullptr) return fail(kInvalidArgument, "logits output is null");
+  return forward(tokens.data(), nullptr, tokens.size(), Mode::kPrefill, logits, -1, nullptr);
+}
+int Context::prefill_stateless(const std::vector<std::uint32_t> &tokens, std::vector<float> *logits) {
+  if (logits == nullptr) return fail(kInvalidArgument, "logits output is null");
+  return forward(tokens.data(), nullptr, tokens.size(), Mode::kStateless, logits, -1, nullptr);
+}
+int Context::prefill_cached(const std::vector<std::uint32_t> &tokens, std::vector<float> *logits) {
+  if (logits == nullptr) return fail(kInvalidArgument, "logits output is null");
+  return forward(tokens.data(), nullptr, tokens.size(), Mode::kCachedPrefill, logits, -1, nullptr);
+}
+int Context::prefill_chunk(const std::vector<std::uint32_t> &tokens, std::vector<float> *logits) {
+  if (logits == nullptr) return fail(kInvalidArgument, "logits output is null");
+  if (state_valid_ && cached_attention_)
+    return fail(kInvalidArgument, "chunk continuation is not available after a cached prefill");
+  return forward(tokens.data(), nullptr, tokens.size(), Mode::kContinue, logits, -1, nullptr);
+}
+int Context::decode(const std::uint32_t token, std::vector<float> *logits) {
+  if (logits == nullptr) return fail(kInvalidArgument, "logits output is null");
+  return forward(&token, nullptr, 1, Mode::kDecode, logits, -1, nullptr);
+}
+int Context::prefill_embedding(const std::vector<std::uint32_t> &tokens, const std::size_t layer,
+                               std::vector<float> *hidden) {
+  if (hidden == nullptr || layer >= weights_->config.layers)
+    return fail(kInvalidArgument, "layer capture index or output is invalid");
+  std::vector<float> logits;
+  return forward(tokens.data(), nullptr, tokens.size(), Mode::kStateless, &logits,
+                 static_cast<long>(layer), hidden);
+}
+int Context::prefill_device(const std::uint32_t *device_tokens, const std::size_t rows,
+                            const bool stateless) {
+  if (device_tokens == nullptr) return fail(kInvalidArgument, "token buffer is null");
+  return forward(nullptr, device_tokens, rows, stateless ? Mode::kStateless : Mode::kPrefill,
+                 nullptr, -1, nullptr);
+}
+
+}  // namespace evob

@@ -1,0 +1,140 @@
+// StripedHyena2 runtime: configuration, device-resident weights, per-context
+// state and the layer pipeline.  Mirrors the public surface of upstream's
+// evo::cuda::PipelineModel (include/evo/cuda/model.hpp:107-229): load,
+// shared-weight contexts, prefill / stateless / cached prefill, chunk
+// continuation, decode, layer capture, stage reporting.
+#pragma once
+
+#include <cuda_runtime.h>
+
+#include <cstddef>
+#include <cstdint>
+#include <memory>
+#include <string>
+#include <vector>
+
+#include "safetensors.hpp"
+
+namespace evob {
+
+enum class MixerType { kHcs, kHcm, kHcl, kAttention };
+
+// How E4M3 Hyena projections are evaluated.  kExact reproduces upstream's
+// software-QGMMA rounding bit for bit; kTensorCore uses tcgen05 FP8 MMAs with
+// F32 accumulation (its own execution profile, tolerance parity).
+enum class ExecutionProfile { kExact, kTensorCore };
+
+struct ModelConfig {
+  std::string architecture, model_id, model_name, artifact_profile;
+  bool test_fixture = false;
+  std::size_t vocab = 0, width = 0, layers = 0, heads = 0, state_size = 0, inner_width = 0;
+  std::size_t short_taps = 0, hcs_taps = 0, hcm_taps = 0, hcs_groups = 0, hcm_groups = 0;
+  std::size_t max_seqlen = 0;
+  float epsilon = 1e-6F, rope_scale = 1.0F, rope_base = 10000.0F;
+  bool fp8_projection = false, hcm_filter_f32 = false, qkv_source_head_major = false;
+  std::vector<MixerType> mixers;  // one per block
+  std::size_t head_dim() const { return width / heads; }
+};
+
+int read_model_config(const ModelFile &file, bool allow_test_fixture, ModelConfig *config);
+
+struct LayerWeights {
+  MixerType type = MixerType::kHcs;
+  const float *pre_norm = nullptr, *post_norm = nullptr;
+  const void *projection = nullptr;  // [3D, D] BF16 or E4M3 codes (Wqkv for attention)
+  float projection_input_scale = 1.0F, projection_output_scale = 1.0F;
+  const void *short_filter = nullptr;   // [3D, short_taps] BF16
+  const void *inner_filter = nullptr;   // [groups, taps] BF16 or F32
+  const void *direct = nullptr;         // [D] BF16 (HCM, HCL)
+  const float *log_poles = nullptr, *residues = nullptr;  // [D, S]
+  const float *inverse_frequency = nullptr;               // [head_dim/2]
+  const void *out_weight = nullptr, *out_bias = nullptr;  // [D, D], [D]
+  const void *l1 = nullptr, *l2 = nullptr, *l3 = nullptr;
+  const void *l12 = nullptr;  // row-interleaved [2I, D] for the fused gate GEMM
+  std::size_t payload_bytes = 0;
+};
+
+// Immutable device weights of one pipeline stage (one GPU).
+struct StageWeights {
+  int device = 0;
+  std::size_t layer_begin = 0, layer_end = 0;
+  std::vector<LayerWeights> layers;
+  const void *embedding = nullptr;    // stage 0 only
+  const float *final_norm = nullptr;  // stage 0 only
+  void *slab = nullptr;
+  std::size_t slab_bytes = 0, weight_bytes = 0;
+  ~StageWeights();
+};
+
+struct ModelWeights {
+  ModelConfig config;
+  std::vector<std::shared_ptr<StageWeights>> stages;
+};
+
+struct StageAssignment {
+  int device = 0;
+  std::size_t layer_begin = 0, layer_end = 0;
+  std::size_t weight_bytes = 0, cache_bytes = 0, arena_bytes = 0;
+};
+
+// Contiguous byte-balanced split of `layers` blocks over `stage_count` stages
+// (upstream src/cuda/model.cu:2419-2469); host-only, unit-testable.
+std::vector<std::pair<std::size_t, std::size_t>> plan_stages(
+    const std::vector<std::size_t> &layer_bytes, std::size_t stage_count, bool even_split);
+
+int load_weights(const ModelFile &file, const std::vector<int> &devices,
+                 bool allow_test_fixture, std::size_t layer_limit,
+                 std::shared_ptr<ModelWeights> *out);
+
+class Context {
+ public:
+  ~Context();
+  static int create(std::shared_ptr<ModelWeights> weights, std::size_t context_size,
+                    ExecutionProfile profile, bool full_arena_for_fixtures,
+                    std::unique_ptr<Context> *out);
+
+  // logits: rows * vocab floats (converted from BF16).
+  int prefill(const std::vector<std::uint32_t> &tokens, std::vector<float> *logits);
+  int prefill_stateless(const std::vector<std::uint32_t> &tokens, std::vector<float> *logits);
+  int prefill_cached(const std::vector<std::uint32_t> &tokens, std::vector<float> *logits);
+  int prefill_chunk(const std::vector<std::uint32_t> &tokens, std::vector<float> *logits);
+  int decode(std::uint32_t token, std::vector<float> *logits);
+  // Block output of `layer` ([rows, width] floats) for a fresh stateless prefill.
+  int prefill_embedding(const std::vector<std::uint32_t> &tokens, std::size_t layer,
+                        std::vector<float> *hidden);
+
+  // Device-resident variant used by the benchmark: tokens already on the
+  // device of stage 0, logits left on the device (BF16 [rows, vocab]).
+  int prefill_device(const std::uint32_t *device_tokens, std::size_t rows, bool stateless);
+  const void *device_logits() const;
+  void *first_stream() const;
+  // Waits for every stage stream and surfaces asynchronous kernel errors.
+  int synchronize();
+
+  std::size_t position() const { return position_; }
+  std::size_t activation_capacity() const { return arena_rows_; }
+  std::size_t context_capacity() const { return context_size_; }
+  const ModelConfig &config() const { return weights_->config; }
+  ExecutionProfile profile() const { return profile_; }
+  std::vector<StageAssignment> stages() const;
+  bool shares_weights_with(const Context &other) const { return weights_ == other.weights_; }
+  bool poisoned() const { return !healthy_; }
+
+ private:
+  struct Stage;
+  enum class Mode { kPrefill, kStateless, kCachedPrefill, kContinue, kDecode };
+  Context() = default;
+  int forward(const std::uint32_t *host_tokens, const std::uint32_t *device_tokens,
+              std::size_t rows, Mode mode, std::vector<float> *logits, long capture_layer,
+              std::vector<float> *captured);
+  int run_stage(Stage &stage, std::size_t rows, Mode mode, long capture_layer,
+                std::vector<float> *captured);
+
+  std::shared_ptr<ModelWeights> weights_;
+  std::vector<std::unique_ptr<Stage>> stages_;
+  ExecutionProfile profile_ = ExecutionProfile::kExact;
+  std::size_t context_size_ = 0, arena_rows_ = 0, position_ = 0;
+  bool state_valid_ = false, cached_attention_ = false, healthy_ = true;
+};
+
+}  // namespace evob

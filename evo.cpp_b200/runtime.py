@@ -1,0 +1,260 @@
+"""ctypes binding of the evo_* model/context C ABI (include/evo/evo.h).
+
+The same binding drives this repository's libevo.so and, in tests and the
+CPU-baseline legs of the benchmark, upstream's own CPU build of the same ABI
+(oracle/_ref/libevo_ref.so) - the two are interchangeable behind it.
+"""
+from __future__ import annotations
+
+import ctypes
+from pathlib import Path
+
+import numpy as np
+
+BACKEND_AUTO, BACKEND_CUDA, BACKEND_CPU = 0, 1, 2
+MODEL_FLAG_ALLOW_SYNTHETIC = 1
+CONTEXT_FLAG_TENSORCORE_FP8 = 1 << 8
+CONTEXT_FLAG_FULL_ARENA = 1 << 9
+
+LOGITS_CALLBACK = ctypes.CFUNCTYPE(ctypes.c_int, ctypes.POINTER(ctypes.c_float), ctypes.c_size_t,
+                                   ctypes.c_size_t, ctypes.c_size_t, ctypes.c_void_p)
+
+
+class ModelParams(ctypes.Structure):
+    _fields_ = [("struct_size", ctypes.c_size_t), ("backend", ctypes.c_int),
+                ("devices", ctypes.POINTER(ctypes.c_int32)), ("device_count", ctypes.c_size_t),
+                ("flags", ctypes.c_uint32)]
+
+
+class ContextParams(ctypes.Structure):
+    _fields_ = [("struct_size", ctypes.c_size_t), ("context_size", ctypes.c_size_t),
+                ("flags", ctypes.c_uint32)]
+
+
+class SamplerParams(ctypes.Structure):
+    _fields_ = [("struct_size", ctypes.c_size_t), ("temperature", ctypes.c_float),
+                ("top_k", ctypes.c_size_t), ("top_p", ctypes.c_float), ("seed", ctypes.c_uint64)]
+
+
+class StageInfo(ctypes.Structure):
+    _fields_ = [("struct_size", ctypes.c_size_t), ("device", ctypes.c_int32),
+                ("layer_begin", ctypes.c_size_t), ("layer_end", ctypes.c_size_t),
+                ("weight_bytes", ctypes.c_size_t), ("cache_bytes", ctypes.c_size_t),
+                ("arena_bytes", ctypes.c_size_t)]
+
+
+class EvoError(RuntimeError):
+    def __init__(self, code: int, message: str):
+        super().__init__(f"[{code}] {message}")
+        self.code = code
+
+
+class EvoLibrary:
+    def __init__(self, path: Path):
+        path = Path(path)
+        if not path.exists():
+            raise FileNotFoundError(f"{path} is missing (build it first; there is no fallback)")
+        lib = self.lib = ctypes.CDLL(str(path))
+        V, Z, I = ctypes.c_void_p, ctypes.c_size_t, ctypes.c_int
+        lib.evo_last_error.restype = ctypes.c_char_p
+        lib.evo_version_string.restype = ctypes.c_char_p
+        lib.evo_abi_version.restype = ctypes.c_uint32
+        lib.evo_model_default_params.restype = ModelParams
+        lib.evo_context_default_params.restype = ContextParams
+        lib.evo_sampler_default_params.restype = SamplerParams
+        lib.evo_model_load.argtypes = [ctypes.c_char_p, ctypes.POINTER(ModelParams), ctypes.POINTER(V)]
+        lib.evo_model_free.argtypes = [V]
+        for name in ("evo_model_id", "evo_model_architecture", "evo_model_profile"):
+            getattr(lib, name).restype = ctypes.c_char_p
+            getattr(lib, name).argtypes = [V]
+        for name in ("evo_model_vocab_size", "evo_model_max_context", "evo_model_embedding_width",
+                     "evo_model_layer_count"):
+            getattr(lib, name).restype = Z
+            getattr(lib, name).argtypes = [V]
+        lib.evo_context_create.argtypes = [V, ctypes.POINTER(ContextParams), ctypes.POINTER(V)]
+        lib.evo_context_free.argtypes = [V]
+        lib.evo_context_position.restype = Z
+        lib.evo_context_position.argtypes = [V]
+        lib.evo_context_capacity.restype = Z
+        lib.evo_context_capacity.argtypes = [V]
+        lib.evo_context_profile.restype = ctypes.c_char_p
+        lib.evo_context_profile.argtypes = [V]
+        lib.evo_context_prefill.argtypes = [V, V, LOGITS_CALLBACK, V]
+        lib.evo_context_decode.argtypes = [V, ctypes.c_uint32, LOGITS_CALLBACK, V]
+        lib.evo_context_embed.argtypes = [V, V, Z, LOGITS_CALLBACK, V]
+        lib.evo_batch_create.argtypes = [Z, ctypes.POINTER(V)]
+        lib.evo_batch_free.argtypes = [V]
+        lib.evo_batch_clear.argtypes = [V]
+        lib.evo_batch_add_sequence.argtypes = [V, ctypes.c_char_p, Z]
+        lib.evo_sampler_create.argtypes = [ctypes.POINTER(SamplerParams), ctypes.POINTER(V)]
+        lib.evo_sampler_free.argtypes = [V]
+        lib.evo_sampler_sample.argtypes = [V, ctypes.POINTER(ctypes.c_float), Z,
+                                           ctypes.POINTER(ctypes.c_uint32)]
+        self.has_extensions = hasattr(lib, "evo_b200_context_prefill_device")
+        if self.has_extensions:
+            lib.evo_b200_context_prefill_device.argtypes = [V, V, Z, I, ctypes.POINTER(V)]
+            lib.evo_b200_context_stream.restype = V
+            lib.evo_b200_context_stream.argtypes = [V]
+            lib.evo_b200_context_synchronize.argtypes = [V]
+            lib.evo_b200_context_stage_count.restype = Z
+            lib.evo_b200_context_stage_count.argtypes = [V]
+            lib.evo_b200_context_stage_info.argtypes = [V, Z, ctypes.POINTER(StageInfo)]
+
+    def check(self, status: int) -> None:
+        if status != 0:
+            raise EvoError(status, (self.lib.evo_last_error() or b"").decode())
+
+    def load(self, path, *, backend=BACKEND_AUTO, devices=None, flags=0) -> "Model":
+        params = self.lib.evo_model_default_params()
+        params.backend = backend
+        params.flags = flags
+        keep = None
+        if devices:
+            keep = (ctypes.c_int32 * len(devices))(*devices)
+            params.devices = ctypes.cast(keep, ctypes.POINTER(ctypes.c_int32))
+            params.device_count = len(devices)
+        handle = ctypes.c_void_p()
+        self.check(self.lib.evo_model_load(str(path).encode(), ctypes.byref(params), ctypes.byref(handle)))
+        return Model(self, handle)
+
+
+class Model:
+    def __init__(self, library: EvoLibrary, handle):
+        self.library, self.handle = library, handle
+
+    def close(self) -> None:
+        if self.handle:
+            self.library.lib.evo_model_free(self.handle)
+            self.handle = None
+
+    @property
+    def vocab(self) -> int:
+        return self.library.lib.evo_model_vocab_size(self.handle)
+
+    @property
+    def width(self) -> int:
+        return self.library.lib.evo_model_embedding_width(self.handle)
+
+    @property
+    def layers(self) -> int:
+        return self.library.lib.evo_model_layer_count(self.handle)
+
+    @property
+    def model_id(self) -> str:
+        return self.library.lib.evo_model_id(self.handle).decode()
+
+    def context(self, context_size: int = 4096, flags: int = 0) -> "Context":
+        params = self.library.lib.evo_context_default_params()
+        params.context_size = context_size
+        params.flags = flags
+        handle = ctypes.c_void_p()
+        self.library.check(self.library.lib.evo_context_create(self.handle, ctypes.byref(params),
+                                                               ctypes.byref(handle)))
+        return Context(self.library, handle, self.vocab, self.width)
+
+
+class Context:
+    def __init__(self, library: EvoLibrary, handle, vocab: int, width: int):
+        self.library, self.handle, self.vocab, self.width = library, handle, vocab, width
+
+    def close(self) -> None:
+        if self.handle:
+            self.library.lib.evo_context_free(self.handle)
+            self.handle = None
+
+    @property
+    def position(self) -> int:
+        return self.library.lib.evo_context_position(self.handle)
+
+    @property
+    def profile(self) -> str:
+        return self.library.lib.evo_context_profile(self.handle).decode()
+
+    def _collect(self, call, columns: int) -> np.ndarray:
+        chunks: list[tuple[int, np.ndarray]] = []
+
+        @LOGITS_CALLBACK
+        def on_rows(data, rows, cols, offset, _user):
+            chunks.append((offset, np.ctypeslib.as_array(data, shape=(rows, cols)).copy()))
+            return 0
+
+        self.library.check(call(on_rows))
+        chunks.sort(key=lambda c: c[0])
+        return np.concatenate([c[1] for c in chunks], axis=0) if chunks else np.zeros((0, columns), np.float32)
+
+    def _batch(self, sequence: bytes):
+        lib = self.library.lib
+        batch = ctypes.c_void_p()
+        self.library.check(lib.evo_batch_create(1, ctypes.byref(batch)))
+        try:
+            self.library.check(lib.evo_batch_add_sequence(batch, sequence, len(sequence)))
+        except Exception:
+            lib.evo_batch_free(batch)
+            raise
+        return batch
+
+    def prefill(self, sequence: bytes) -> np.ndarray:
+        """Chunked prefill of raw bytes; returns F32 logits [tokens, vocab]."""
+        batch = self._batch(bytes(sequence))
+        try:
+            return self._collect(lambda cb: self.library.lib.evo_context_prefill(self.handle, batch, cb, None),
+                                 self.vocab)
+        finally:
+            self.library.lib.evo_batch_free(batch)
+
+    def decode(self, token: int) -> np.ndarray:
+        return self._collect(lambda cb: self.library.lib.evo_context_decode(self.handle, token, cb, None),
+                             self.vocab)[0]
+
+    def embed(self, sequence: bytes, layer: int) -> np.ndarray:
+        batch = self._batch(bytes(sequence))
+        try:
+            return self._collect(lambda cb: self.library.lib.evo_context_embed(self.handle, batch, layer, cb, None),
+                                 self.width)
+        finally:
+            self.library.lib.evo_batch_free(batch)
+
+    # ---- extensions of this repository's library
+    def prefill_device(self, device_tokens: int, rows: int, stateless: bool = True) -> int:
+        out = ctypes.c_void_p()
+        self.library.check(self.library.lib.evo_b200_context_prefill_device(
+            self.handle, device_tokens, rows, int(stateless), ctypes.byref(out)))
+        return out.value
+
+    def stream(self) -> int:
+        return self.library.lib.evo_b200_context_stream(self.handle)
+
+    def synchronize(self) -> None:
+        self.library.check(self.library.lib.evo_b200_context_synchronize(self.handle))
+
+    def stages(self) -> list[StageInfo]:
+        lib = self.library.lib
+        result = []
+        for index in range(lib.evo_b200_context_stage_count(self.handle)):
+            info = StageInfo()
+            info.struct_size = ctypes.sizeof(StageInfo)
+            self.library.check(lib.evo_b200_context_stage_info(self.handle, index, ctypes.byref(info)))
+            result.append(info)
+        return result
+
+
+class Sampler:
+    def __init__(self, library: EvoLibrary, *, temperature=1.0, top_k=1, top_p=1.0, seed=0):
+        self.library = library
+        params = library.lib.evo_sampler_default_params()
+        params.temperature, params.top_k, params.top_p, params.seed = temperature, top_k, top_p, seed
+        self.handle = ctypes.c_void_p()
+        library.check(library.lib.evo_sampler_create(ctypes.byref(params), ctypes.byref(self.handle)))
+
+    def sample(self, logits: np.ndarray) -> int:
+        logits = np.ascontiguousarray(logits, dtype=np.float32)
+        token = ctypes.c_uint32()
+        self.library.check(self.library.lib.evo_sampler_sample(
+            self.handle, logits.ctypes.data_as(ctypes.POINTER(ctypes.c_float)), logits.size,
+            ctypes.byref(token)))
+        return token.value
+
+    def close(self) -> None:
+        if self.handle:
+            self.library.lib.evo_sampler_free(self.handle)
+            self.handle = None

@@ -1,0 +1,47 @@
+/* Extension entry points of the B200 runtime.  They have no counterpart in
+ * upstream evo.cpp's C ABI; they expose what a benchmark or a multi-process
+ * launcher needs beyond it: device-resident token input, the context's CUDA
+ * stream for event timing, and the stage layout of the layer pipeline
+ * (upstream reports the latter through StageAssignment,
+ * include/evo/cuda/model.hpp:94-101, which its C ABI does not export). */
+#ifndef EVO_EVO_B200_H
+#define EVO_EVO_B200_H
+
+#include "evo.h"
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct evo_b200_stage_info {
+  size_t struct_size;
+  int32_t device;
+  size_t layer_begin;
+  size_t layer_end;
+  size_t weight_bytes;
+  size_t cache_bytes;
+  size_t arena_bytes;
+} evo_b200_stage_info;
+
+/* Enqueues one prefill of `rows` token ids that already live on the device of
+ * pipeline stage 0 (uint32, rows <= activation capacity) on the context's
+ * stream and returns without waiting.  BF16 logits [rows, vocab] stay on the
+ * device; *device_logits_out (optional) receives their address.  stateless != 0
+ * keeps no caches (position stays 0); otherwise the context is left ready for
+ * decode.  Call evo_b200_context_synchronize before reading results. */
+EVO_API evo_status evo_b200_context_prefill_device(evo_context *context,
+                                                   const uint32_t *device_tokens, size_t rows,
+                                                   int stateless,
+                                                   const void **device_logits_out);
+/* cudaStream_t of pipeline stage 0 (where a forward pass starts and ends). */
+EVO_API void *evo_b200_context_stream(const evo_context *context);
+/* Waits for all stages and reports asynchronous kernel errors. */
+EVO_API evo_status evo_b200_context_synchronize(evo_context *context);
+EVO_API size_t evo_b200_context_stage_count(const evo_context *context);
+EVO_API evo_status evo_b200_context_stage_info(const evo_context *context, size_t index,
+                                               evo_b200_stage_info *info);
+
+#ifdef __cplusplus
+}
+#endif
+#endif
