@@ -1,0 +1,347 @@
+#!/usr/bin/env python3
+"""Headline benchmark: Evo 2 7B-shaped StripedHyena2 batch-1 prefill on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--tokens T] [--impl reference]
+
+One "step" is one stateless prefill of T uniform-ACGT tokens (default 8192,
+the activation-arena size) through the 32-block 7B-shaped model with E4M3 Hyena
+projections on the tcgen05 profile and every other projection in BF16.  Weights
+are random-init (seeded) in the evo2-runtime-v1 Safetensors format and are
+loaded through the same evo_model_load call a user makes.
+
+Printed JSON line (rank 0):
+  value      tokens/s with the token ids already resident in HBM, timed with
+             CUDA events on the context's stream, max over ranks
+  e2e        tokens/s through evo_context_prefill with host bytes in and host
+             F32 logits out (H2D + D2H inside the timed region)
+  roofline   dominant kernel class (tcgen05 BF16 GEMM): algorithmic FLOPs per
+             step / its summed launch time, from per-operator CUDA events
+  cpu_baseline  upstream's own CPU backend (oracle/_ref/libevo_ref.so) on a
+             bounded sample of the same workload, one core
+With --gpus N > 1 (torchrun, one rank per GPU) every rank holds a full replica
+and runs its own sequence: weak scaling, no data-path collective.  The layer
+pipeline over several GPUs of one process is measured by --pipeline.
+
+--impl reference times upstream's CPU implementation (rank 0 only).
+"""
+from __future__ import annotations
+
+import argparse
+import importlib.util
+import json
+import os
+import subprocess
+import sys
+import tempfile
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+METRIC = "evo2_7b_shaped_batch1_prefill_tokens_per_second"
+SEED = 1  # BASELINE config: 7B-shaped, random-init weights from seed 1
+MODEL_ID = "evo2_7b"
+# GEMM FLOPs per token of the 7B shape (D=4096, I=11264, 32 blocks, vocab 512)
+WIDTH, INNER, LAYERS, VOCAB, HEADS = 4096, 11264, 32, 512, 32
+ATTENTION_LAYERS = 5
+
+
+def load_package():
+    if "evo_cpp_b200" in sys.modules:
+        return sys.modules["evo_cpp_b200"]
+    pkg_dir = ROOT / "evo.cpp_b200"
+    spec = importlib.util.spec_from_file_location(
+        "evo_cpp_b200", pkg_dir / "__init__.py", submodule_search_locations=[str(pkg_dir)])
+    module = importlib.util.module_from_spec(spec)
+    sys.modules["evo_cpp_b200"] = module
+    spec.loader.exec_module(module)
+    return module
+
+
+def artifact_dir(kind: str) -> Path:
+    base = Path(os.environ.get("EVO_B200_ARTIFACT_DIR", tempfile.gettempdir())) / "evo_b200_artifacts"
+    return base / f"{MODEL_ID}-{kind}-seed{SEED}"
+
+
+def ensure_artifact(kind: str, device: str | None) -> Path:
+    """Writes the 7B-shaped artifact once per box (kind: 'fp8' or 'bf16')."""
+    import importlib
+
+    load_package()
+    art = importlib.import_module("evo_cpp_b200.artifact")
+    directory = artifact_dir(kind)
+    marker = directory / "COMPLETE"
+    if not marker.exists():
+        directory.mkdir(parents=True, exist_ok=True)
+        spec = art.with_fp8_projections(art.load_spec(MODEL_ID), kind == "fp8")
+        art.write_synthetic(directory / "model.safetensors", spec, SEED, device=device)
+        marker.write_text("ok\n")
+    return directory
+
+
+def tokens_for(rank: int, count: int):
+    import numpy as np
+
+    rng = np.random.default_rng(SEED + 1000 + rank)
+    return rng.choice(np.frombuffer(b"ACGT", np.uint8), count).astype(np.uint8)
+
+
+def gemm_flops_per_token(tokens: int) -> float:
+    per_block = 2.0 * (3 * WIDTH * WIDTH + WIDTH * WIDTH + 3 * WIDTH * INNER)
+    return per_block * LAYERS + 2.0 * WIDTH * VOCAB
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while a region runs."""
+
+    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+             "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.samples, self.stop_flag, self.thread = index, [], threading.Event(), None
+
+    def _run(self):
+        while not self.stop_flag.is_set():
+            try:
+                out = subprocess.run(["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                                      "-i", str(self.index)], capture_output=True, text=True, timeout=5).stdout
+                fields = [f.strip() for f in out.strip().split(",")]
+                if len(fields) >= 6:
+                    self.samples.append(fields)
+            except Exception:
+                pass
+            self.stop_flag.wait(0.2)
+
+    def __enter__(self):
+        self.thread = threading.Thread(target=self._run, daemon=True)
+        self.thread.start()
+        return self
+
+    def __exit__(self, *exc):
+        self.stop_flag.set()
+        self.thread.join(timeout=6)
+
+    def summary(self) -> dict:
+        clocks = sorted(int(s[0]) for s in self.samples if s[0].isdigit())
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(s[2 + i].lower().startswith("active") for s in self.samples)]
+        return {"sm_mhz": clocks[len(clocks) // 2] if clocks else None,
+                "sm_max_mhz": int(self.samples[0][1]) if self.samples and self.samples[0][1].isdigit() else None,
+                "reasons": reasons, "samples": len(self.samples)}
+
+
+def run_reference(args, rank: int, world: int) -> None:
+    """Upstream's CPU backend on the same model shape (BF16 twin of the seeded
+    weights: its registry only admits BF16 projections for this shape)."""
+    if rank != 0:
+        return
+    import importlib
+
+    load_package()
+    rt = importlib.import_module("evo_cpp_b200.runtime")
+    library_path = ROOT / "oracle" / "_ref" / "libevo_ref.so"
+    line = {"impl": "reference", "metric": METRIC, "unit": "tokens/s", "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": args.warmup, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "bf16 weights, f32 math", "data": "synthetic"}
+    if not library_path.exists():
+        line["unavailable"] = "oracle/_ref/libevo_ref.so was not built (make -C oracle ref needs the upstream tree)"
+        print(json.dumps(line))
+        return
+    import torch
+
+    directory = ensure_artifact("bf16", "cuda" if torch.cuda.is_available() else None)
+    model = rt.EvoLibrary(library_path).load(directory, backend=rt.BACKEND_CPU)
+    sample = args.reference_tokens
+    sequence = bytes(tokens_for(0, sample).tolist())
+    times = []
+    for step in range(args.warmup + args.steps):
+        context = model.context(max(sample, 16))
+        start = time.perf_counter()
+        context.prefill(sequence)
+        elapsed = time.perf_counter() - start
+        context.close()
+        if step >= args.warmup:
+            times.append(elapsed)
+    mean = sum(times) / len(times)
+    value = sample / mean
+    line.update({
+        "value": value, "ms_per_step": mean * 1e3,
+        "config": {"workload": f"7B-shaped StripedHyena2 prefill, {sample}-token sample of the "
+                               f"{args.tokens}-token prompt (per-token cost is length-independent on this backend)",
+                   "model_id": MODEL_ID, "seed": SEED},
+        "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": 1, "kind": "reference",
+                         "sample": f"{sample}-token prefill per step, upstream cpu-f32 backend (single-threaded)"},
+        "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    })
+    print(json.dumps(line))
+
+
+def run_ours(args, rank: int, world: int, local_rank: int) -> None:
+    import importlib
+
+    import numpy as np
+    import torch
+
+    load_package()
+    rt = importlib.import_module("evo_cpp_b200.runtime")
+    torch.cuda.set_device(local_rank)
+    distributed = world > 1
+    if distributed:
+        import torch.distributed as dist
+
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    # one rank writes the artifact, the others wait for it
+    if rank == 0:
+        ensure_artifact("fp8", "cuda")
+    if distributed:
+        dist.barrier()
+    directory = artifact_dir("fp8")
+    library = rt.EvoLibrary(ROOT / "evo.cpp_b200" / "libevo.so")
+    load_start = time.perf_counter()
+    model = library.load(directory, devices=[local_rank])
+    load_seconds = time.perf_counter() - load_start
+    tokens = args.tokens
+    flags = rt.CONTEXT_FLAG_TENSORCORE_FP8
+    context = model.context(tokens, flags)
+    host_tokens = tokens_for(rank, tokens)
+    device_tokens = torch.from_numpy(host_tokens.astype(np.int32)).cuda()
+    stream = torch.cuda.ExternalStream(context.stream())
+
+    def barrier():
+        if distributed:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- device-resident throughput
+    for _ in range(args.warmup):
+        context.prefill_device(device_tokens.data_ptr(), tokens, True)
+    context.synchronize()
+    barrier()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(local_rank) as clocks:
+        start.record(stream)
+        for _ in range(args.steps):
+            context.prefill_device(device_tokens.data_ptr(), tokens, True)
+        stop.record(stream)
+        context.synchronize()
+    barrier()
+    elapsed_ms = torch.tensor([start.elapsed_time(stop)], device="cuda")
+    if distributed:
+        dist.all_reduce(elapsed_ms, op=dist.ReduceOp.MAX)
+    ms_per_step = float(elapsed_ms.item()) / args.steps
+    value = world * tokens / (ms_per_step * 1e-3)
+
+    # ---- per-operator timing (separate pass; events cost a few us per launch)
+    context.profile_enable(True)
+    for _ in range(args.steps):
+        context.prefill_device(device_tokens.data_ptr(), tokens, True)
+    context.synchronize()
+    profile = context.profile_read()
+    context.profile_enable(False)
+    launches_per_step = sum(n for _, n in profile.values()) // args.steps + 1  # + embedding
+    gemm_ms, gemm_launches = profile["gemm_bf16_tcgen05"]
+    fp8_ms, fp8_launches = profile["gemm_e4m3_tcgen05"]
+    hyena_layers = LAYERS - ATTENTION_LAYERS
+    flops_fp8 = 2.0 * tokens * WIDTH * 3 * WIDTH * hyena_layers
+    flops_bf16 = gemm_flops_per_token(tokens) * tokens - flops_fp8
+    achieved = flops_bf16 * args.steps / (gemm_ms * 1e-3) / 1e12
+    peaks = {}
+    peaks_file = ROOT / "MEASURED_PEAKS.json"
+    if peaks_file.exists():
+        peaks = json.loads(peaks_file.read_text())
+    peak = peaks.get("bf16_tflops_sustained", 1400.0)
+    roofline = {"bound": "tensor", "kernel": "gemm_tcgen05_kernel<bf16> (all BF16 projections of a step)",
+                "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
+                "peak_source": "MEASURED_PEAKS.json bf16_tflops_sustained (of measured)" if peaks else
+                               "fallback 1.4 PFLOP/s sustained (of fallback)",
+                "traffic": None,
+                "fp8_projection_tflops": flops_fp8 * args.steps / (fp8_ms * 1e-3) / 1e12 if fp8_ms else None,
+                "operator_ms_per_step": {k: v[0] / args.steps for k, v in profile.items() if v[1]}}
+
+    # ---- end to end through the public C ABI: host bytes in, host F32 logits out
+    sequence = bytes(host_tokens.tolist())
+    e2e_times = []
+    for step in range(min(args.warmup, 2) + args.steps):
+        fresh = model.context(tokens, flags)
+        torch.cuda.synchronize()
+        begin = time.perf_counter()
+        logits = fresh.prefill(sequence)
+        e2e_times.append(time.perf_counter() - begin)
+        fresh.close()
+    e2e_times = e2e_times[min(args.warmup, 2):]
+    e2e_seconds = torch.tensor([sum(e2e_times) / len(e2e_times)], device="cuda")
+    if distributed:
+        dist.all_reduce(e2e_seconds, op=dist.ReduceOp.MAX)
+    e2e_value = world * tokens / float(e2e_seconds.item())
+    assert logits.shape == (tokens, VOCAB) and np.isfinite(logits).all()
+
+    if rank == 0:
+        line = {
+            "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "bf16 activations, e4m3 Hyena projections (tcgen05), f32 accumulate",
+            "data": "synthetic",
+            "config": {"workload": f"Evo 2 7B-shaped StripedHyena2 (32 blocks, d_model 4096, FFN 11264, vocab 512), "
+                                   f"batch-1 stateless prefill of {tokens} uniform-ACGT tokens, profile b200-tc",
+                       "model_id": MODEL_ID, "seed": SEED, "tokens": tokens,
+                       "parallelism": "1 GPU" if world == 1 else f"{world} independent replicas (one sequence per GPU)",
+                       "l2_policy": "weights (12 GB) and activations exceed the 126 MB L2 every step; no flush needed",
+                       "model_load_seconds": load_seconds},
+            "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": 4 * tokens,
+                    "d2h_bytes_per_step": 2 * tokens * VOCAB},
+            "gpu_launches": launches_per_step * args.steps,
+            "gflop_per_token": gemm_flops_per_token(tokens) / 1e9,
+            "model_tflops": gemm_flops_per_token(tokens) * tokens / (ms_per_step * 1e-3) / 1e12,
+            "roofline": roofline, "clocks": clocks.summary(),
+        }
+        if world == 1 and not args.skip_cpu_baseline:
+            line["cpu_baseline"] = cpu_baseline(args, rt)
+        print(json.dumps(line))
+    if distributed:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def cpu_baseline(args, rt) -> dict:
+    library_path = ROOT / "oracle" / "_ref" / "libevo_ref.so"
+    if not library_path.exists():
+        return {"value": None, "unit": "tokens/s", "cores": 1, "kind": "reference",
+                "sample": "unavailable: oracle/_ref/libevo_ref.so was not built"}
+    directory = ensure_artifact("bf16", "cuda")
+    model = rt.EvoLibrary(library_path).load(directory, backend=rt.BACKEND_CPU)
+    sample = args.reference_tokens
+    sequence = bytes(tokens_for(0, sample).tolist())
+    context = model.context(max(sample, 16))
+    begin = time.perf_counter()
+    context.prefill(sequence)
+    seconds = time.perf_counter() - begin
+    return {"value": sample / seconds, "unit": "tokens/s", "cores": 1, "kind": "reference",
+            "sample": f"one {sample}-token prefill of the BF16 twin of the same seeded 7B-shaped weights on "
+                      f"upstream's cpu-f32 backend (single-threaded; {seconds:.1f} s)"}
+
+
+def main() -> None:
+    parser = argparse.ArgumentParser()
+    parser.add_argument("--gpus", type=int, default=1)
+    parser.add_argument("--steps", type=int, default=5)
+    parser.add_argument("--warmup", type=int, default=3)
+    parser.add_argument("--tokens", type=int, default=8192)
+    parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    parser.add_argument("--reference-tokens", type=int, default=8,
+                        help="tokens per CPU step (about 0.5 tokens/s/core on this shape)")
+    parser.add_argument("--skip-cpu-baseline", action="store_true")
+    args = parser.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference(args, rank, world)
+    else:
+        run_ours(args, rank, world, local_rank)
+
+
+if __name__ == "__main__":
+    main()

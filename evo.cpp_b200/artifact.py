@@ -190,6 +190,23 @@ def synthetic_tensors(spec: dict, seed: int, *, weight_std: float = 0.02,
         elif ".filter." in name:
             values = normal(shape, filter_std)
             payload = values.astype(np.float32).tobytes() if dtype == "F32" else _bf16_bytes(values)
+        elif torch_gen is not None and dtype in ("E4M3_SW", "BF16") and math.prod(shape) >= 1 << 16:
+            # large dense weights: draw, round and (for E4M3) quantise on the device
+            import torch
+
+            values = (torch.randn(math.prod(shape), generator=torch_gen, device=device) * weight_std).bfloat16()
+            if dtype == "BF16":
+                payload = values.view(torch.int16).cpu().numpy().tobytes()
+            else:
+                rounded = values.float()
+                w_scale = np.float32(448.0) / np.float32(rounded.abs().max().item())
+                codes = (rounded * float(w_scale)).clamp(-448.0, 448.0).to(torch.float8_e4m3fn)
+                if pending_scale is not None:
+                    scales = np.array([input_scale, np.float32(np.float32(1.0) / np.float32(input_scale)) *
+                                       np.float32(np.float32(1.0) / w_scale)], np.float32)
+                    yield pending_scale[0], "F32", pending_scale[1], scales.tobytes()
+                    pending_scale = None
+                payload = codes.view(torch.uint8).cpu().numpy().tobytes()
         elif dtype == "E4M3_SW":
             values = normal(shape, weight_std)
             rounded = (np.frombuffer(_bf16_bytes(values), np.uint16).astype(np.uint32) << 16).view(np.float32)

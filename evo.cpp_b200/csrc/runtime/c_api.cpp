@@ -487,6 +487,31 @@ evo_status evo_b200_context_synchronize(evo_context *context) {
   });
 }
 
+evo_status evo_b200_context_profile_enable(evo_context *context, int enabled) {
+  return protect([&]() -> int {
+    if (context == nullptr) return fail(evob::kInvalidArgument, "context is required");
+    context->context->set_profiling(enabled != 0);
+    return kOk;
+  });
+}
+
+size_t evo_b200_context_profile_read(const evo_context *context, double *milliseconds,
+                                     uint64_t *launches, size_t capacity) {
+  if (context == nullptr) return 0;
+  double ms[evob::kProfileCategories];
+  std::uint64_t counts[evob::kProfileCategories];
+  context->context->read_profile(ms, counts);
+  for (size_t i = 0; i < capacity && i < static_cast<size_t>(evob::kProfileCategories); ++i) {
+    if (milliseconds != nullptr) milliseconds[i] = ms[i];
+    if (launches != nullptr) launches[i] = counts[i];
+  }
+  return evob::kProfileCategories;
+}
+
+const char *evo_b200_profile_category_name(size_t index) {
+  return evob::profile_category_name(static_cast<int>(index));
+}
+
 size_t evo_b200_context_stage_count(const evo_context *context) {
   return context == nullptr ? 0 : context->context->stages().size();
 }

@@ -23,6 +23,16 @@ constexpr std::size_t kFixtureArenaRows = 8;   // upstream src/cuda/model.cu:32
     if (status__ != kOk) return status__; \
   } while (0)
 
+// Runs one operator launch; when the stage is profiling, brackets it with CUDA
+// events on the stage stream and files the elapsed time under `category`.
+#define EVOB_OP(category, expr)           \
+  do {                                    \
+    s.begin_op(category);                 \
+    const int status__ = (expr);          \
+    s.end_op();                           \
+    if (status__ != kOk) return status__; \
+  } while (0)
+
 struct DeviceGuard {
   int previous = 0;
   explicit DeviceGuard(const int device) {
@@ -57,6 +67,40 @@ struct Context::Stage {
   void *logits = nullptr;
   std::vector<LayerState> layers;
 
+  // ---- optional per-operator timing
+  bool profiling = false;
+  std::vector<cudaEvent_t> events;    // pairs: start, stop
+  std::vector<int> event_category;    // one per pair in use
+  double category_ms[kProfileCategories] = {};
+  std::uint64_t category_launches[kProfileCategories] = {};
+
+  void begin_op(const int category) {
+    if (!profiling) return;
+    const std::size_t pair = event_category.size();
+    while (events.size() < 2 * (pair + 1)) {
+      cudaEvent_t event = nullptr;
+      cudaEventCreate(&event);
+      events.push_back(event);
+    }
+    event_category.push_back(category);
+    cudaEventRecord(events[2 * pair], stream);
+  }
+  void end_op() {
+    if (!profiling || event_category.empty()) return;
+    cudaEventRecord(events[2 * (event_category.size() - 1) + 1], stream);
+  }
+  // Call after the stream has been synchronised.
+  void collect_profile() {
+    for (std::size_t pair = 0; pair < event_category.size(); ++pair) {
+      float ms = 0.0F;
+      if (cudaEventElapsedTime(&ms, events[2 * pair], events[2 * pair + 1]) == cudaSuccess) {
+        category_ms[event_category[pair]] += ms;
+        ++category_launches[event_category[pair]];
+      }
+    }
+    event_category.clear();
+  }
+
   int allocate(void **out, const std::size_t bytes, std::size_t *counter) {
     if (cudaMalloc(out, bytes == 0 ? 16 : bytes) != cudaSuccess)
       return fail(kCuda, "cannot allocate " + std::to_string(bytes >> 20) + " MiB on device " +
@@ -69,6 +113,7 @@ struct Context::Stage {
     DeviceGuard guard(device);
     if (stream != nullptr) cudaStreamSynchronize(stream);
     for (void *p : allocations) cudaFree(p);
+    for (cudaEvent_t event : events) cudaEventDestroy(event);
     if (done != nullptr) cudaEventDestroy(done);
     if (stream != nullptr) cudaStreamDestroy(stream);
   }
@@ -182,12 +227,44 @@ int Context::synchronize() {
     }
     const int gemm = gemm_error_state(stage->stream);
     if (gemm != kOk) status = gemm;
+    stage->collect_profile();
   }
   if (status != kOk) {
     healthy_ = false;
     state_valid_ = false;
   }
   return status;
+}
+
+const char *profile_category_name(const int category) {
+  static const char *const names[kProfileCategories] = {
+      "rms_norm", "gemm_bf16_tcgen05", "gemm_e4m3_tcgen05", "gemm_e4m3_emulated", "hcs_fused_fir",
+      "hcm_fused_fir", "hcl_modal_scan", "attention", "state_step", "elementwise"};
+  return category >= 0 && category < kProfileCategories ? names[category] : "";
+}
+
+void Context::set_profiling(const bool enabled) {
+  for (const auto &stage : stages_) {
+    stage->profiling = enabled;
+    if (enabled) {
+      for (int i = 0; i < kProfileCategories; ++i) {
+        stage->category_ms[i] = 0.0;
+        stage->category_launches[i] = 0;
+      }
+    }
+  }
+}
+
+void Context::read_profile(double (&milliseconds)[kProfileCategories],
+                           std::uint64_t (&launches)[kProfileCategories]) const {
+  for (int i = 0; i < kProfileCategories; ++i) {
+    milliseconds[i] = 0.0;
+    launches[i] = 0;
+    for (const auto &stage : stages_) {
+      milliseconds[i] += stage->category_ms[i];
+      launches[i] += stage->category_launches[i];
+    }
+  }
 }
 
 int Context::run_stage(Stage &s, const std::size_t rows, const Mode mode,
@@ -203,11 +280,11 @@ int Context::run_stage(Stage &s, const std::size_t rows, const Mode mode,
     const bool attention = w.type == MixerType::kAttention;
     const bool fp8 = !attention && c.fp8_projection;
     // pre-norm (+ E4M3 codes of the normalised activations for FP8 projections)
-    EVOB_TRY(rms_norm(s.hidden, w.pre_norm, rows, D, c.epsilon, fp8 ? nullptr : s.normalized,
+    EVOB_OP(kCatNorm, rms_norm(s.hidden, w.pre_norm, rows, D, c.epsilon, fp8 ? nullptr : s.normalized,
                       fp8 ? s.codes : nullptr, w.projection_input_scale, stream));
     // input projection -> [rows, 3D]
     if (fp8 && profile_ == ExecutionProfile::kExact) {
-      EVOB_TRY(e4m3_emulated_gemm(s.codes, w.projection, rows, D, 3 * D,
+      EVOB_OP(kCatGemmEmulated, e4m3_emulated_gemm(s.codes, w.projection, rows, D, 3 * D,
                                   w.projection_output_scale, s.projection, stream));
     } else {
       LinearArgs a;
@@ -221,20 +298,20 @@ int Context::run_stage(Stage &s, const std::size_t rows, const Mode mode,
         a.operand_type = OperandType::kE4m3;
         a.alpha = w.projection_output_scale;
       }
-      EVOB_TRY(linear(a, stream));
+      EVOB_OP(fp8 ? kCatGemmFp8 : kCatGemmBf16, linear(a, stream));
     }
     if (attention) {
       const std::size_t prefix = initial ? 0 : position_;
-      EVOB_TRY(split_rope_append(s.projection, w.inverse_frequency, rows, c.heads, c.head_dim(),
+      EVOB_OP(kCatAttention, split_rope_append(s.projection, w.inverse_frequency, rows, c.heads, c.head_dim(),
                                  prefix, c.rope_scale, false, s.query, state.key_cache,
                                  state.value_cache, context_size_, stream));
       const bool cached = mode == Mode::kCachedPrefill ||
                           ((mode == Mode::kDecode || mode == Mode::kContinue) && cached_attention_);
       if (cached)
-        EVOB_TRY(cached_attention(s.query, state.key_cache, state.value_cache, rows, prefix + rows,
+        EVOB_OP(kCatAttention, cached_attention(s.query, state.key_cache, state.value_cache, rows, prefix + rows,
                                   c.heads, c.head_dim(), s.mixer_out, stream));
       else
-        EVOB_TRY(causal_attention(s.query, state.key_cache, state.value_cache, rows, prefix + rows,
+        EVOB_OP(kCatAttention, causal_attention(s.query, state.key_cache, state.value_cache, rows, prefix + rows,
                                   c.heads, c.head_dim(), s.mixer_out, stream));
     } else if (initial) {
       if (w.type == MixerType::kHcl) {
@@ -252,7 +329,7 @@ int Context::run_stage(Stage &s, const std::size_t rows, const Mode mode,
         a.length = rows;
         a.width = D;
         a.modes = c.state_size;
-        EVOB_TRY(modal_prefill(a, stream));
+        EVOB_OP(kCatModal, modal_prefill(a, stream));
       } else {
         const bool hcs = w.type == MixerType::kHcs;
         GatedFirArgs a;
@@ -270,18 +347,18 @@ int Context::run_stage(Stage &s, const std::size_t rows, const Mode mode,
         a.cross_correlation = hcs;
         a.inner_cache = stateless ? nullptr : state.inner_cache;
         a.short_cache = stateless ? nullptr : state.short_cache;
-        EVOB_TRY(gated_fir_prefill(a, stream));
+        EVOB_OP(hcs ? kCatShortFir : kCatMediumFir, gated_fir_prefill(a, stream));
       }
     } else {
       // continuation / decode against the causal state
       const std::size_t short_cached = std::min(position_, c.short_taps - 1);
-      EVOB_TRY(fir_step(s.projection, w.short_filter, false, nullptr, false, rows, 3 * D, 3 * D,
+      EVOB_OP(kCatStateStep, fir_step(s.projection, w.short_filter, false, nullptr, false, rows, 3 * D, 3 * D,
                         c.short_taps, true, state.short_cache, short_cached, s.short_filtered,
                         stream));
-      EVOB_TRY(split_triples(s.short_filtered, rows, D, s.x2, s.x1, s.value, stream));
+      EVOB_OP(kCatElementwise, split_triples(s.short_filtered, rows, D, s.x2, s.x1, s.value, stream));
       if (w.type == MixerType::kHcl) {
         if (mode == Mode::kDecode) {
-          EVOB_TRY(modal_decode(s.x2, s.x1, s.value, w.direct, w.log_poles, w.residues, D,
+          EVOB_OP(kCatStateStep, modal_decode(s.x2, s.x1, s.value, w.direct, w.log_poles, w.residues, D,
                                 c.state_size, state.modal_state, s.pregate, s.mixer_out, stream));
         } else {
           ModalArgs a;
@@ -298,17 +375,17 @@ int Context::run_stage(Stage &s, const std::size_t rows, const Mode mode,
           a.width = D;
           a.modes = c.state_size;
           a.continue_from_state = true;
-          EVOB_TRY(modal_prefill(a, stream));
+          EVOB_OP(kCatModal, modal_prefill(a, stream));
         }
       } else {
         const bool hcs = w.type == MixerType::kHcs;
         const std::size_t taps = hcs ? c.hcs_taps : c.hcm_taps;
-        EVOB_TRY(gate(s.x1, s.value, s.pregate, rows * D, false, stream));
-        EVOB_TRY(fir_step(s.pregate, w.inner_filter, !hcs && c.hcm_filter_f32,
+        EVOB_OP(kCatElementwise, gate(s.x1, s.value, s.pregate, rows * D, false, stream));
+        EVOB_OP(kCatStateStep, fir_step(s.pregate, w.inner_filter, !hcs && c.hcm_filter_f32,
                           hcs ? nullptr : w.direct, !hcs, rows, D,
                           hcs ? c.hcs_groups : c.hcm_groups, taps, hcs, state.inner_cache,
                           std::min(position_, taps - 1), s.query, stream));
-        EVOB_TRY(gate(s.query, s.x2, s.mixer_out, rows * D, false, stream));
+        EVOB_OP(kCatElementwise, gate(s.query, s.x2, s.mixer_out, rows * D, false, stream));
       }
     }
     // output projection + bias + residual -> residual buffer
@@ -325,9 +402,9 @@ int Context::run_stage(Stage &s, const std::size_t rows, const Mode mode,
       // fused for attention and single-row Hyena, separately rounded otherwise
       // (upstream src/cuda/model.cu:1768-1799)
       a.bias_mode = (attention || rows == 1) ? 1 : 2;
-      EVOB_TRY(linear(a, stream));
+      EVOB_OP(kCatGemmBf16, linear(a, stream));
     }
-    EVOB_TRY(rms_norm(s.residual, w.post_norm, rows, D, c.epsilon, s.normalized, nullptr, 1.0F,
+    EVOB_OP(kCatNorm, rms_norm(s.residual, w.post_norm, rows, D, c.epsilon, s.normalized, nullptr, 1.0F,
                       stream));
     const std::size_t layer_index = s.weights->layer_begin + i;
     const bool gelu_block = layer_index == 0;
@@ -340,7 +417,7 @@ int Context::run_stage(Stage &s, const std::size_t rows, const Mode mode,
       a.in_features = D;
       a.out_features = 2 * I;
       a.gate_mode = gelu_block ? 2 : 1;
-      EVOB_TRY(linear(a, stream));
+      EVOB_OP(kCatGemmBf16, linear(a, stream));
     } else {
       LinearArgs a;
       a.input = s.normalized;
@@ -349,11 +426,11 @@ int Context::run_stage(Stage &s, const std::size_t rows, const Mode mode,
       a.out_features = I;
       a.weight = w.l1;
       a.output = s.mlp_first;
-      EVOB_TRY(linear(a, stream));
+      EVOB_OP(kCatGemmBf16, linear(a, stream));
       a.weight = w.l2;
       a.output = s.mlp_second;
-      EVOB_TRY(linear(a, stream));
-      EVOB_TRY(gate(s.mlp_first, s.mlp_second, s.gated, rows * I, gelu_block, stream));
+      EVOB_OP(kCatGemmBf16, linear(a, stream));
+      EVOB_OP(kCatElementwise, gate(s.mlp_first, s.mlp_second, s.gated, rows * I, gelu_block, stream));
     }
     {
       LinearArgs a;
@@ -364,7 +441,7 @@ int Context::run_stage(Stage &s, const std::size_t rows, const Mode mode,
       a.rows = rows;
       a.in_features = I;
       a.out_features = D;
-      EVOB_TRY(linear(a, stream));
+      EVOB_OP(kCatGemmBf16, linear(a, stream));
     }
     if (capture_layer >= 0 && static_cast<std::size_t>(capture_layer) == layer_index &&
         captured != nullptr) {
@@ -468,6 +545,7 @@ int Context::forward(const std::uint32_t *host_tokens, const std::uint32_t *devi
         for (const auto &stage : stages_) {
           DeviceGuard stage_guard(stage->device);
           if (status == kOk) status = gemm_error_state(stage->stream);
+          stage->collect_profile();
         }
       }
     }

@@ -19,6 +19,22 @@ namespace evob {
 
 enum class MixerType { kHcs, kHcm, kHcl, kAttention };
 
+// Operator classes reported by the optional per-operator timing.
+enum ProfileCategory : int {
+  kCatNorm = 0,        // RMSNorm (+ fused E4M3 quantisation)
+  kCatGemmBf16,        // tcgen05 BF16 projections (Wqkv, out, MLP, head)
+  kCatGemmFp8,         // tcgen05 E4M3 Hyena projections
+  kCatGemmEmulated,    // bit-exact software-QGMMA Hyena projections
+  kCatShortFir,        // HCS (k=7) fused featurizer + FIR + gates
+  kCatMediumFir,       // HCM (k=128) fused featurizer + FIR + gates
+  kCatModal,           // HCL modal scan
+  kCatAttention,       // QKV split/RoPE/append + attention
+  kCatStateStep,       // continuation / decode FIR and state updates
+  kCatElementwise,     // embedding, gates, splits
+  kProfileCategories
+};
+const char *profile_category_name(int category);
+
 // How E4M3 Hyena projections are evaluated.  kExact reproduces upstream's
 // software-QGMMA rounding bit for bit; kTensorCore uses tcgen05 FP8 MMAs with
 // F32 accumulation (its own execution profile, tolerance parity).
@@ -110,6 +126,12 @@ class Context {
   void *first_stream() const;
   // Waits for every stage stream and surfaces asynchronous kernel errors.
   int synchronize();
+  // Per-operator timing (CUDA events around every launch; adds a few
+  // microseconds per operator, so keep it off for throughput measurements).
+  void set_profiling(bool enabled);
+  // Totals accumulated since profiling was enabled, summed over stages.
+  void read_profile(double (&milliseconds)[kProfileCategories],
+                    std::uint64_t (&launches)[kProfileCategories]) const;
 
   std::size_t position() const { return position_; }
   std::size_t activation_capacity() const { return arena_rows_; }

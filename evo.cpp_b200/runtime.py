@@ -99,6 +99,12 @@ class EvoLibrary:
             lib.evo_b200_context_stage_count.restype = Z
             lib.evo_b200_context_stage_count.argtypes = [V]
             lib.evo_b200_context_stage_info.argtypes = [V, Z, ctypes.POINTER(StageInfo)]
+            lib.evo_b200_context_profile_enable.argtypes = [V, I]
+            lib.evo_b200_context_profile_read.restype = Z
+            lib.evo_b200_context_profile_read.argtypes = [V, ctypes.POINTER(ctypes.c_double),
+                                                          ctypes.POINTER(ctypes.c_uint64), Z]
+            lib.evo_b200_profile_category_name.restype = ctypes.c_char_p
+            lib.evo_b200_profile_category_name.argtypes = [Z]
 
     def check(self, status: int) -> None:
         if status != 0:
@@ -226,6 +232,19 @@ class Context:
 
     def synchronize(self) -> None:
         self.library.check(self.library.lib.evo_b200_context_synchronize(self.handle))
+
+    def profile_enable(self, enabled: bool = True) -> None:
+        self.library.check(self.library.lib.evo_b200_context_profile_enable(self.handle, int(enabled)))
+
+    def profile_read(self) -> dict[str, tuple[float, int]]:
+        """{operator class: (milliseconds, launches)} since profiling was enabled."""
+        lib = self.library.lib
+        count = lib.evo_b200_context_profile_read(self.handle, None, None, 0)
+        ms = (ctypes.c_double * count)()
+        launches = (ctypes.c_uint64 * count)()
+        lib.evo_b200_context_profile_read(self.handle, ms, launches, count)
+        return {lib.evo_b200_profile_category_name(i).decode(): (ms[i], int(launches[i]))
+                for i in range(count)}
 
     def stages(self) -> list[StageInfo]:
         lib = self.library.lib

@@ -37,6 +37,16 @@ EVO_API evo_status evo_b200_context_prefill_device(evo_context *context,
 EVO_API void *evo_b200_context_stream(const evo_context *context);
 /* Waits for all stages and reports asynchronous kernel errors. */
 EVO_API evo_status evo_b200_context_synchronize(evo_context *context);
+/* Per-operator timing: while enabled every operator launch is bracketed with
+ * CUDA events on its stage stream (a few microseconds each, so leave it off for
+ * throughput runs).  Enabling clears the totals.  evo_b200_context_profile_read
+ * fills up to `capacity` entries with the milliseconds and launch counts per
+ * operator class accumulated up to the last synchronising call and returns the
+ * number of classes; evo_b200_profile_category_name names class `index`. */
+EVO_API evo_status evo_b200_context_profile_enable(evo_context *context, int enabled);
+EVO_API size_t evo_b200_context_profile_read(const evo_context *context, double *milliseconds,
+                                             uint64_t *launches, size_t capacity);
+EVO_API const char *evo_b200_profile_category_name(size_t index);
 EVO_API size_t evo_b200_context_stage_count(const evo_context *context);
 EVO_API evo_status evo_b200_context_stage_info(const evo_context *context, size_t index,
                                                evo_b200_stage_info *info);
