@@ -17,6 +17,9 @@
 // prefill; continuation chunks keep upstream's single rounding
 // (src/cuda/hyena.cu:534-560).  modal_decode keeps the pinned decode order
 // (separate multiply/add, 32-lane zero-padded tree; src/cuda/hyena.cu:718-761).
+#include <mutex>
+#include <string>
+
 #include "common.cuh"
 #include "ops_internal.hpp"
 
@@ -354,6 +357,88 @@ int modal_prefill(const ModalArgs &a, cudaStream_t stream) {
     status = fill_fir_cache(a.projection, a.short_cache, a.length, a.width * 3,
                             a.short_taps - 1, stream);
   return status;
+}
+
+// ------------------------------------------------- allocation-free variant
+// Segment-state scratch for callers that cannot allocate device memory: a
+// fixed array that lives in the library image on every GPU that loads it.
+constexpr std::size_t kStaticScratchFloats = std::size_t{4} << 20;  // 16 MiB
+static __device__ __align__(256) float g_static_modal_scratch[kStaticScratchFloats];
+
+namespace {
+// Device address of the array above, looked up once per device.  The symbol
+// name is only meaningful to the host as a handle; kernels need this address.
+int static_scratch_address(float **out) {
+  static std::mutex mutex;
+  static float *addresses[64] = {};
+  int device = 0;
+  if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64)
+    return fail(kCuda, "cannot query the current CUDA device");
+  std::lock_guard<std::mutex> lock(mutex);
+  if (addresses[device] == nullptr) {
+    void *address = nullptr;
+    const cudaError_t error = cudaGetSymbolAddress(&address, g_static_modal_scratch);
+    if (error != cudaSuccess || address == nullptr)
+      return fail(kCuda, std::string("cannot resolve the static modal scratch: ") +
+                             cudaGetErrorString(error));
+    addresses[device] = static_cast<float *>(address);
+  }
+  *out = addresses[device];
+  return kOk;
+}
+}  // namespace
+
+int modal_prefill_static_scratch(const ModalArgs &a, cudaStream_t stream) {
+  if (a.projection != nullptr || a.x2 == nullptr || a.x1 == nullptr || a.value == nullptr ||
+      a.direct == nullptr || a.log_poles == nullptr || a.residues == nullptr ||
+      a.output == nullptr || a.width == 0 || a.width % 2 != 0 || a.modes == 0)
+    return fail(kInvalidArgument, "allocation-free modal prefill arguments are invalid");
+  if (a.continue_from_state && a.state == nullptr)
+    return fail(kInvalidArgument, "modal continuation needs a state");
+  if (a.length > 0x7fffff00U || a.width > 0x3fffffffU)
+    return fail(kInvalidArgument, "modal prefill dimensions are too large");
+  if (a.length == 0) return kOk;
+  // Start from the segment length the allocating path would use and lengthen it
+  // until the segment states fit the fixed array.
+  std::size_t segment = static_cast<std::size_t>(pick_segment(a.length, a.width));
+  const std::size_t per_segment = a.width * a.modes;
+  while (((a.length + segment - 1) / segment) * per_segment > kStaticScratchFloats &&
+         segment < a.length)
+    segment *= 2;
+  const std::size_t segments = (a.length + segment - 1) / segment;
+  if (segments * per_segment > kStaticScratchFloats)
+    return fail(kInvalidArgument,
+                "allocation-free modal prefill: width*modes = " + std::to_string(per_segment) +
+                    " floats per segment exceeds the fixed scratch of " +
+                    std::to_string(kStaticScratchFloats) + " floats");
+  float *scratch = nullptr;
+  const int located = static_scratch_address(&scratch);
+  if (located != kOk) return located;
+  ModalParams p{};
+  p.x2 = static_cast<const bf16 *>(a.x2);
+  p.x1 = static_cast<const bf16 *>(a.x1);
+  p.value = static_cast<const bf16 *>(a.value);
+  p.direct = static_cast<const bf16 *>(a.direct);
+  p.log_poles = a.log_poles;
+  p.residues = a.residues;
+  p.output = static_cast<bf16 *>(a.output);
+  p.pregate = static_cast<bf16 *>(a.pregate);
+  p.state = a.state;
+  p.scratch = scratch;
+  p.length = static_cast<int>(a.length);
+  p.width = static_cast<int>(a.width);
+  p.segment = static_cast<int>(segment);
+  p.segments = static_cast<int>(segments);
+  p.pairs = static_cast<int>(a.width / 2);
+  p.continue_from_state = a.continue_from_state;
+  switch (a.modes) {
+    case 16: return launch_modal<16>(p, false, stream);
+    case 8: return launch_modal<8>(p, false, stream);
+    case 4: return launch_modal<4>(p, false, stream);
+    case 2: return launch_modal<2>(p, false, stream);
+    case 1: return launch_modal<1>(p, false, stream);
+    default: return fail(kUnsupported, "modal state size must be 1, 2, 4, 8 or 16");
+  }
 }
 
 int modal_decode(const void *x2, const void *x1, const void *value,

@@ -295,6 +295,28 @@ int evo_b200_bf16_hcl_prefill(const void *x2, const void *x1, const void *value,
   return modal_prefill(a, as_stream(stream));
 }
 
+int evo_b200_bf16_hcl_prefill_noalloc(const void *x2, const void *x1, const void *value,
+                                      const void *direct, const float *log_poles,
+                                      const float *residues, size_t length, size_t width,
+                                      size_t modes, int mode, float *state, void *pregate,
+                                      void *output, void *stream) {
+  ModalArgs a;
+  a.x2 = x2;
+  a.x1 = x1;
+  a.value = value;
+  a.direct = direct;
+  a.log_poles = log_poles;
+  a.residues = residues;
+  a.length = length;
+  a.width = width;
+  a.modes = modes;
+  a.continue_from_state = mode == 1;
+  a.state = state;
+  a.pregate = pregate;
+  a.output = output;
+  return modal_prefill_static_scratch(a, as_stream(stream));
+}
+
 int evo_b200_bf16_projection_hcl_prefill(
     const void *projection, const void *short_filter, const void *direct,
     const float *log_poles, const float *residues, size_t length, size_t width,

@@ -125,6 +125,10 @@ struct ModalArgs {
 std::size_t modal_scratch_floats(std::size_t length, std::size_t width,
                                  std::size_t modes);
 int modal_prefill(const ModalArgs &args, cudaStream_t stream);
+// Same operator with its segment-state scratch in a fixed array inside the
+// library image instead of args.scratch (which is ignored); separate x2/x1/v
+// inputs only.  Makes no device allocation.
+int modal_prefill_static_scratch(const ModalArgs &args, cudaStream_t stream);
 int modal_decode(const void *x2, const void *x1, const void *value,
                  const void *direct, const float *log_poles,
                  const float *residues, std::size_t width, std::size_t modes,

@@ -159,6 +159,31 @@ EVO_B200_API int evo_b200_bf16_hcl_prefill(
     const float *log_poles, const float *residues, size_t length, size_t width,
     size_t modes, int mode, float *state, float *scratch, void *pregate,
     void *output, void *stream);
+/* No counterpart in upstream evo.cpp.  evo_b200_bf16_hcl_prefill for callers
+ * that must not touch the CUDA allocator: a serving process that handed all
+ * free device memory to its own pool at start-up (so a later cudaMalloc fails
+ * or fragments it), or a latency-critical loop that cannot afford the implicit
+ * device synchronisation of cudaMalloc/cudaFree.  Inputs, outputs and state
+ * are still the caller's buffers; only the segment-state scratch differs: it
+ * is a fixed 4 Mi-float (16 MiB) array inside the library image, resident on
+ * every GPU that loads the library until the process exits.
+ *  - Limit: ceil(length / segment) * width * modes floats must fit the array;
+ *    the segment is lengthened automatically to make it fit, so the call is
+ *    refused (status 2, message names the limit) only when width * modes
+ *    itself exceeds 4 Mi floats.
+ *  - The first call on each device resolves the array's device address
+ *    (cudaGetSymbolAddress, with that device current); make that first call
+ *    outside any stream capture.
+ *  - All calls on a device share the array.  Every call overwrites the part it
+ *    uses before reading it, so nothing has to be cleared between calls, but
+ *    two calls whose kernels overlap on the GPU (different streams) race.
+ *  - The call itself performs no cudaMalloc, cudaFree or other allocating
+ *    library call. */
+EVO_B200_API int evo_b200_bf16_hcl_prefill_noalloc(
+    const void *x2, const void *x1, const void *value, const void *direct,
+    const float *log_poles, const float *residues, size_t length, size_t width,
+    size_t modes, int mode, float *state, void *pregate, void *output,
+    void *stream);
 EVO_B200_API int evo_b200_bf16_projection_hcl_prefill(
     const void *projection, const void *short_filter, const void *direct,
     const float *log_poles, const float *residues, size_t length, size_t width,

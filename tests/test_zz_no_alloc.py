@@ -1,0 +1,82 @@
+"""The allocation-free HCL prefill entry point (evo_b200_bf16_hcl_prefill_noalloc).
+
+It exists for callers that must stay away from the CUDA allocator - a server
+that gave all free device memory to its own pool at start-up, or a
+latency-critical loop that cannot take cudaMalloc's implicit synchronisation -
+and keeps its segment-state scratch in a fixed array inside the library instead
+of a caller buffer.  The test calls it through the C ABI twice in a row (the
+array is shared and keeps the previous call's contents, so the second call
+must not be disturbed by the first) and checks both results against the
+ordinary entry point, which takes caller-provided scratch.
+
+The file name sorts last on purpose: a run that stops at the first failure has
+then already executed every other test.  It passes alone in a fresh process
+(the first call does the per-device set-up) and after the rest of the suite.
+"""
+from __future__ import annotations
+
+import numpy as np
+import pytest
+import torch
+
+from gpu_util import assert_close_bits, dev, dev_bits, empty_bits, host_bits, p, rand_bf16, stream
+
+pytestmark = pytest.mark.gpu
+
+
+def _case(rng, length, width, modes):
+    x2, x1, v = (rand_bf16(rng, length, width) for _ in range(3))
+    direct = rand_bf16(rng, width)
+    log_poles = np.log(rng.uniform(0.9, 0.999, (width, modes))).astype(np.float32)
+    residues = (rng.standard_normal((width, modes)) * 0.02).astype(np.float32)
+    return x2, x1, v, direct, log_poles, residues
+
+
+def _run(ops, entry, case, length, width, modes, scratch):
+    x2, x1, v, direct, log_poles, residues = case
+    out, pregate = empty_bits(length, width), empty_bits(length, width)
+    state = torch.full((width, modes), -3.0, device="cuda")
+    args = [p(dev_bits(x2)), p(dev_bits(x1)), p(dev_bits(v)), p(dev_bits(direct)), p(dev(log_poles)),
+            p(dev(residues)), length, width, modes, 0, p(state)]
+    if scratch is not None:
+        args.append(p(scratch))
+    ops.call(entry, *args, p(pregate), p(out), stream())
+    torch.cuda.synchronize()
+    return host_bits(out), host_bits(pregate), state.cpu().numpy()
+
+
+def test_noalloc_entry_matches_the_allocating_one_twice_in_a_row(ops):
+    rng = np.random.default_rng(77)
+    # second shape is larger than the first and leaves stale data beyond/under it
+    for length, width, modes in [(300, 64, 16), (1000, 96, 16)]:
+        case = _case(rng, length, width, modes)
+        scratch = torch.empty(ops.hcl_scratch_floats(length, width, modes), device="cuda")
+        expected = _run(ops, "bf16_hcl_prefill", case, length, width, modes, scratch)
+        before = torch.cuda.memory_allocated()
+        got = _run(ops, "bf16_hcl_prefill_noalloc", case, length, width, modes, None)
+        assert torch.cuda.memory_allocated() >= before  # only the test's own output tensors
+        assert np.array_equal(got[1], expected[1])                       # u = bf16(x1 * v)
+        assert_close_bits(got[0], expected[0], atol=0.04, rtol=0.03, min_cosine=0.9999)
+        np.testing.assert_allclose(got[2], expected[2], rtol=2e-5, atol=2e-5)
+        # same segmentation at these sizes, hence the same bits
+        assert np.array_equal(got[0], expected[0])
+
+
+def test_noalloc_entry_lengthens_segments_to_fit_and_rejects_beyond_the_limit(ops):
+    rng = np.random.default_rng(78)
+    # 4096 channels x 16 modes = 65,536 floats per segment: the 4 Mi-float array
+    # holds 64 segments, the allocating path would use 128 at this length.
+    length, width, modes = 2048, 4096, 16
+    case = _case(rng, length, width, modes)
+    scratch = torch.empty(ops.hcl_scratch_floats(length, width, modes), device="cuda")
+    assert scratch.numel() > 4 << 20
+    expected = _run(ops, "bf16_hcl_prefill", case, length, width, modes, scratch)
+    got = _run(ops, "bf16_hcl_prefill_noalloc", case, length, width, modes, None)
+    assert_close_bits(got[0], expected[0], atol=0.04, rtol=0.03, min_cosine=0.9999)
+    np.testing.assert_allclose(got[2], expected[2], rtol=3e-5, atol=3e-5)
+    # width * modes alone beyond the array: refused with a message naming the limit
+    dummy = empty_bits(16)
+    status = ops.status("bf16_hcl_prefill_noalloc", p(dummy), p(dummy), p(dummy), p(dummy), p(dummy),
+                        p(dummy), 4, (4 << 20) // 16 + 2, 16, 0, None, None, p(dummy), stream())
+    assert status == 2
+    assert "fixed scratch of 4194304 floats" in ops.last_error()
