@@ -19,8 +19,7 @@ Printed JSON line (rank 0):
   cpu_baseline  upstream's own CPU backend (oracle/_ref/libevo_ref.so) on a
              bounded sample of the same workload, one core
 With --gpus N > 1 (torchrun, one rank per GPU) every rank holds a full replica
-and runs its own sequence: weak scaling, no data-path collective.  The layer
-pipeline over several GPUs of one process is measured by --pipeline.
+and runs its own sequence: weak scaling, no data-path collective.
 
 --impl reference times upstream's CPU implementation (rank 0 only).
 """
@@ -76,7 +75,13 @@ def ensure_artifact(kind: str, device: str | None) -> Path:
         spec = art.with_fp8_projections(art.load_spec(MODEL_ID), kind == "fp8")
         art.write_synthetic(directory / "model.safetensors", spec, SEED, device=device)
         marker.write_text("ok\n")
-    return directory
+    return model_entry(directory)
+
+
+def model_entry(directory: Path) -> Path:
+    """The file a loader is pointed at: the shard index, or the single file."""
+    index = directory / "model.safetensors.index.json"
+    return index if index.exists() else directory / "model.safetensors"
 
 
 def tokens_for(rank: int, count: int):
@@ -197,7 +202,7 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> None:
         ensure_artifact("fp8", "cuda")
     if distributed:
         dist.barrier()
-    directory = artifact_dir("fp8")
+    directory = model_entry(artifact_dir("fp8"))
     library = rt.EvoLibrary(ROOT / "evo.cpp_b200" / "libevo.so")
     load_start = time.perf_counter()
     model = library.load(directory, devices=[local_rank])

@@ -107,6 +107,7 @@ flash_causal_kernel(const bf16 *__restrict__ query, const bf16 *__restrict__ key
   for (int i = 0; i < 16; ++i)
 #pragma unroll
     for (int j = 0; j < 4; ++j) o[i][j] = 0.0F;
+  std::uint32_t q_frag[kHeadDim / 16][4];
   float row_max[2] = {-INFINITY, -INFINITY};
   float row_sum[2] = {0.0F, 0.0F};
   const int q_row0 = m0 + warp * 16 + lane / 4;  // and +8
@@ -133,18 +134,22 @@ flash_causal_kernel(const bf16 *__restrict__ query, const bf16 *__restrict__ key
     for (int i = 0; i < 8; ++i)
 #pragma unroll
       for (int j = 0; j < 4; ++j) s[i][j] = 0.0F;
+    if (kb == 0) {
+      // Q fragments stay in registers for the whole key loop.
+#pragma unroll
+      for (int ks = 0; ks < kHeadDim / 16; ++ks)
+        ldmatrix_x4(q_tile + swizzled(warp * 16 + (lane % 16), 2 * ks + lane / 16), q_frag[ks]);
+    }
 #pragma unroll
     for (int ks = 0; ks < kHeadDim / 16; ++ks) {
-      std::uint32_t a[4];
-      ldmatrix_x4(q_tile + swizzled(warp * 16 + (lane % 16), 2 * ks + lane / 16), a);
 #pragma unroll
       for (int np = 0; np < 4; ++np) {
         std::uint32_t b[4];
         ldmatrix_x4(k_tile + swizzled(16 * np + (lane % 8) + (lane / 16) * 8,
                                       2 * ks + ((lane / 8) % 2)),
                     b);
-        mma_bf16(s[2 * np], a, b[0], b[1]);
-        mma_bf16(s[2 * np + 1], a, b[2], b[3]);
+        mma_bf16(s[2 * np], q_frag[ks], b[0], b[1]);
+        mma_bf16(s[2 * np + 1], q_frag[ks], b[2], b[3]);
       }
     }
 

@@ -104,15 +104,28 @@ rms_norm_kernel(const bf16 *__restrict__ input, const float *__restrict__ scale,
                 bf16 *__restrict__ output, std::uint8_t *__restrict__ codes,
                 const std::size_t width, const float epsilon,
                 const float quant_scale) {
-  extern __shared__ unsigned short row_cache[];  // width BF16 values
+  extern __shared__ __align__(16) unsigned short row_cache[];  // width BF16 values
   __shared__ float partial[32];
   const std::size_t row = blockIdx.x;
   const bf16 *const in = input + row * width;
+  // 128-bit row loads when the layout allows; the sum below still visits the
+  // columns in the thread-strided order regardless of how the row was fetched.
+  const bool vectors = width % 8 == 0 &&
+                       (reinterpret_cast<std::uintptr_t>(input) & 15U) == 0 &&
+                       (reinterpret_cast<std::uintptr_t>(scale) & 15U) == 0 &&
+                       (output == nullptr || (reinterpret_cast<std::uintptr_t>(output) & 15U) == 0) &&
+                       (codes == nullptr || (reinterpret_cast<std::uintptr_t>(codes) & 7U) == 0);
+  if (vectors) {
+    for (std::size_t v = threadIdx.x; v < width / 8; v += kThreads)
+      reinterpret_cast<uint4 *>(row_cache)[v] = reinterpret_cast<const uint4 *>(in)[v];
+  } else {
+    for (std::size_t column = threadIdx.x; column < width; column += kThreads)
+      row_cache[column] = __bfloat16_as_ushort(in[column]);
+  }
+  __syncthreads();
   float sum = 0.0F;
   for (std::size_t column = threadIdx.x; column < width; column += kThreads) {
-    const bf16 raw = in[column];
-    row_cache[column] = __bfloat16_as_ushort(raw);
-    const float value = bf2f(raw);
+    const float value = bits2f_bf16(row_cache[column]);
     sum = fmaf(value, value, sum);
   }
   sum = warp_sum_down(sum);
@@ -131,6 +144,42 @@ rms_norm_kernel(const bf16 *__restrict__ input, const float *__restrict__ scale,
   }
   __syncthreads();
   const float denominator = partial[0];
+  if (vectors) {
+    for (std::size_t v = threadIdx.x; v < width / 8; v += kThreads) {
+      Bf16x8 values;
+      values.raw = reinterpret_cast<const uint4 *>(row_cache)[v];
+      const float4 s0 = reinterpret_cast<const float4 *>(scale)[2 * v];
+      const float4 s1 = reinterpret_cast<const float4 *>(scale)[2 * v + 1];
+      const float scales[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+      float results[8];
+      // bf16(x / den) == bf16(x * (1/den)) for every BF16 x and every BF16 den
+      // in [1e-30, 1e30] (checked exhaustively on the host: a BF16 quotient is
+      // never closer than ~2^-17 relative to a BF16 rounding boundary), so the
+      // IEEE division is only kept for denominators outside that range.
+      if (denominator >= 1e-30F && denominator <= 1e30F) {
+        const float reciprocal = __frcp_rn(denominator);
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          results[j] = rbf(rbf(values.get(j) * reciprocal) * rbf(scales[j]));
+      } else {
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          results[j] = rbf(rbf(__fdiv_rn(values.get(j), denominator)) * rbf(scales[j]));
+      }
+      if (output != nullptr)
+        reinterpret_cast<uint4 *>(output + row * width)[v] =
+            make_uint4(pack_bf16x2(results[0], results[1]), pack_bf16x2(results[2], results[3]),
+                       pack_bf16x2(results[4], results[5]), pack_bf16x2(results[6], results[7]));
+      if (codes != nullptr) {
+        unsigned int words[2] = {0U, 0U};
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          words[j / 4] |= static_cast<unsigned int>(e4m3_code(results[j] * quant_scale)) << (8 * (j % 4));
+        reinterpret_cast<uint2 *>(codes + row * width)[v] = make_uint2(words[0], words[1]);
+      }
+    }
+    return;
+  }
   for (std::size_t column = threadIdx.x; column < width; column += kThreads) {
     const float value = bits2f_bf16(row_cache[column]);
     const float column_scale = rbf(scale[column]);

@@ -366,7 +366,7 @@ unsigned int flat_grid(const std::size_t items) {
 
 }  // namespace
 
-int gated_fir_prefill(const GatedFirArgs &a, cudaStream_t stream) {
+int gated_fir_prefill_generic(const GatedFirArgs &a, cudaStream_t stream) {
   const bool from_projection = a.projection != nullptr;
   if (a.filter == nullptr || a.output == nullptr || a.width == 0 ||
       a.groups == 0 || a.taps == 0 || a.taps > kMaxTaps ||

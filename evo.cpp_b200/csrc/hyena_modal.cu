@@ -77,13 +77,44 @@ struct PairReader {
     }
   }
 
-  // Returns u for both channels and, when requested, the x2 gate.
-  __device__ __forceinline__ void step(const int t, const bool want_x2,
-                                       float &u0, float &u1, float &g0,
-                                       float &g1) {
+  // Loads issued for kBatch consecutive rows before any of them is consumed:
+  // the recurrence is a serial dependency chain, so memory latency has to be
+  // covered by independent loads in flight, not by the chain.
+  static constexpr int kBatch = 8;
+
+  __device__ __forceinline__ void fetch(const int t, const int limit, const bool want_x2,
+                                        std::uint32_t (&raw)[kBatch][3]) const {
+#pragma unroll
+    for (int i = 0; i < kBatch; ++i) {
+      const int row = t + i;
+      raw[i][0] = raw[i][1] = raw[i][2] = 0U;
+      if (row < limit) {
+        if constexpr (kFromProjection) {
+          const std::uint32_t *const words = reinterpret_cast<const std::uint32_t *>(
+              p.projection + static_cast<std::size_t>(row) * p.width * 3 + c0 * 3);
+          raw[i][0] = __ldg(words);
+          raw[i][1] = __ldg(words + 1);
+          raw[i][2] = __ldg(words + 2);
+        } else {
+          const std::size_t index = static_cast<std::size_t>(row) * p.width + c0;
+          raw[i][0] = __ldg(reinterpret_cast<const std::uint32_t *>(p.x1 + index));
+          raw[i][1] = __ldg(reinterpret_cast<const std::uint32_t *>(p.value + index));
+          if (want_x2) raw[i][2] = __ldg(reinterpret_cast<const std::uint32_t *>(p.x2 + index));
+        }
+      }
+    }
+  }
+
+  // Consumes one fetched row: u for both channels and the x2 gate.
+  __device__ __forceinline__ void step(const std::uint32_t (&words)[3], float &u0, float &u1,
+                                       float &g0, float &g1) {
     if constexpr (kFromProjection) {
       float row[6], z[6];
-      load_row(t, row);
+#pragma unroll
+      for (int w = 0; w < 3; ++w) {
+        row[2 * w] = __uint_as_float(words[w] << 16U);
+        row[2 * w + 1] = __uint_as_float(words[w] & 0xffff0000U);
+      }
 #pragma unroll
       for (int s = 0; s < 6; ++s) {
         float a = 0.0F;
@@ -99,16 +130,11 @@ struct PairReader {
       g0 = z[0];
       g1 = z[3];
     } else {
-      const std::size_t index = static_cast<std::size_t>(t) * p.width + c0;
-      const std::uint32_t a = *reinterpret_cast<const std::uint32_t *>(p.x1 + index);
-      const std::uint32_t b = *reinterpret_cast<const std::uint32_t *>(p.value + index);
+      const std::uint32_t a = words[0], b = words[1], g = words[2];
       u0 = rbf(__uint_as_float(a << 16U) * __uint_as_float(b << 16U));
       u1 = rbf(__uint_as_float(a & 0xffff0000U) * __uint_as_float(b & 0xffff0000U));
-      if (want_x2) {
-        const std::uint32_t g = *reinterpret_cast<const std::uint32_t *>(p.x2 + index);
-        g0 = __uint_as_float(g << 16U);
-        g1 = __uint_as_float(g & 0xffff0000U);
-      }
+      g0 = __uint_as_float(g << 16U);
+      g1 = __uint_as_float(g & 0xffff0000U);
     }
   }
 };
@@ -134,13 +160,21 @@ modal_local_kernel(const ModalParams p) {
   const int t1 = min(t0 + p.segment, p.length);
   PairReader<kFromProjection> reader(p, c0);
   reader.start(t0);
-  for (int t = t0; t < t1; ++t) {
-    float u0, u1, g0, g1;
-    reader.step(t, false, u0, u1, g0, g1);
+  constexpr int kBatch = PairReader<kFromProjection>::kBatch;
+  for (int t = t0; t < t1; t += kBatch) {
+    std::uint32_t raw[kBatch][3];
+    reader.fetch(t, t1, false, raw);
 #pragma unroll
-    for (int m = 0; m < kModes; ++m) {
-      state[0][m] = fmaf(pole[0][m], state[0][m], u0);
-      state[1][m] = fmaf(pole[1][m], state[1][m], u1);
+    for (int i = 0; i < kBatch; ++i) {
+      if (t + i < t1) {
+        float u0, u1, g0, g1;
+        reader.step(raw[i], u0, u1, g0, g1);
+#pragma unroll
+        for (int m = 0; m < kModes; ++m) {
+          state[0][m] = fmaf(pole[0][m], state[0][m], u0);
+          state[1][m] = fmaf(pole[1][m], state[1][m], u1);
+        }
+      }
     }
   }
   float *const out = p.scratch + (static_cast<std::size_t>(seg) * p.width + c0) * kModes;
@@ -158,14 +192,26 @@ __global__ void modal_carry_kernel(const ModalParams p, const int modes) {
   const float log_pole = p.log_poles[index];
   const float full_decay = expf(log_pole * static_cast<float>(p.segment));
   float carry = (p.continue_from_state && p.state != nullptr) ? p.state[index] : 0.0F;
-  for (int seg = 0; seg < p.segments; ++seg) {
-    float *const slot = p.scratch + static_cast<std::size_t>(seg) * p.width * modes + index;
-    const float local = *slot;
-    *slot = carry;
-    const int span = min(p.segment, p.length - seg * p.segment);
-    const float decay =
-        span == p.segment ? full_decay : expf(log_pole * static_cast<float>(span));
-    carry = fmaf(decay, carry, local);
+  const std::size_t stride = static_cast<std::size_t>(p.width) * modes;
+  // The chain over segments is serial; its loads are not, so they are issued
+  // a batch at a time ahead of the dependent arithmetic.
+  constexpr int kAhead = 16;
+  for (int seg0 = 0; seg0 < p.segments; seg0 += kAhead) {
+    float local[kAhead];
+#pragma unroll
+    for (int i = 0; i < kAhead; ++i)
+      local[i] = seg0 + i < p.segments ? __ldcg(p.scratch + (seg0 + i) * stride + index) : 0.0F;
+#pragma unroll
+    for (int i = 0; i < kAhead; ++i) {
+      const int seg = seg0 + i;
+      if (seg < p.segments) {
+        p.scratch[seg * stride + index] = carry;
+        const int span = min(p.segment, p.length - seg * p.segment);
+        const float decay =
+            span == p.segment ? full_decay : expf(log_pole * static_cast<float>(span));
+        carry = fmaf(decay, carry, local[i]);
+      }
+    }
   }
   if (p.state != nullptr) p.state[index] = carry;
 }
@@ -197,9 +243,16 @@ modal_output_kernel(const ModalParams p) {
   const int t1 = min(t0 + p.segment, p.length);
   PairReader<kFromProjection> reader(p, c0);
   reader.start(t0);
-  for (int t = t0; t < t1; ++t) {
+  constexpr int kBatch = PairReader<kFromProjection>::kBatch;
+  for (int tb = t0; tb < t1; tb += kBatch) {
+   std::uint32_t raw[kBatch][3];
+   reader.fetch(tb, t1, true, raw);
+#pragma unroll
+   for (int i = 0; i < kBatch; ++i) {
+    const int t = tb + i;
+    if (t >= t1) break;
     float u[2], g[2];
-    reader.step(t, true, u[0], u[1], g[0], g[1]);
+    reader.step(raw[i], u[0], u[1], g[0], g[1]);
     float result[2];
 #pragma unroll
     for (int c = 0; c < 2; ++c) {
@@ -224,6 +277,7 @@ modal_output_kernel(const ModalParams p) {
     if (p.pregate != nullptr)
       *reinterpret_cast<std::uint32_t *>(p.pregate + offset) =
           (__float_as_uint(u[0]) >> 16U) | (__float_as_uint(u[1]) & 0xffff0000U);
+   }
   }
 }
 

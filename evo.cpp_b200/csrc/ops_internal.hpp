@@ -85,7 +85,10 @@ struct GatedFirArgs {
   float *inner_cache = nullptr;   // [width, taps-1]
   float *short_cache = nullptr;   // [3*width, short_taps-1]
 };
+// Dispatches to the vectorised / tensor-core kernels of hyena_fir_fused.cu
+// when the layout allows and to the generic kernel of hyena_fir.cu otherwise.
 int gated_fir_prefill(const GatedFirArgs &args, cudaStream_t stream);
+int gated_fir_prefill_generic(const GatedFirArgs &args, cudaStream_t stream);
 
 int fir_prefill(const void *input, const void *filter, bool filter_is_f32,
                 const void *bias, bool multiply_bias, std::size_t length,
