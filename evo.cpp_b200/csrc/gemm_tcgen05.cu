@@ -204,6 +204,21 @@ __device__ __forceinline__ bf16 gelu_round(const float x) {
   }
 }
 
+// Tile order: bands of 16 row-tiles, row-tile fastest inside a band.  The ~148
+// tiles in flight then cover a 16 x 9 patch of the output, so a wave re-reads
+// about 16 A tiles + 9 B tiles from L2 instead of every A tile.
+__device__ __forceinline__ void tile_coordinates(const int tile, const int tiles_m,
+                                                 const int tiles_n, int *tile_m, int *tile_n) {
+  constexpr int kBand = 16;
+  const int per_band = kBand * tiles_n;
+  const int band = tile / per_band;
+  const int first = band * kBand;
+  const int rows = min(kBand, tiles_m - first);
+  const int local = tile - band * per_band;
+  *tile_m = first + local % rows;
+  *tile_n = local / rows;
+}
+
 template <int BN>
 struct SharedLayout {
   static constexpr int kABytes = kBlockM * kBlockKBytes;
@@ -285,8 +300,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
       std::uint32_t phase = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x) {
-        const int m0 = (tile % tiles_m) * kBlockM;
-        const int n0 = (tile / tiles_m) * BN;
+        int tile_m, tile_n;
+        tile_coordinates(tile, tiles_m, tiles_n, &tile_m, &tile_n);
+        const int m0 = tile_m * kBlockM;
+        const int n0 = tile_n * BN;
         for (int kb = 0; kb < k_blocks; ++kb) {
           if (!mbar_wait(empty_bar(stage), phase ^ 1U, abort_flag)) {
             ok = false;
@@ -347,8 +364,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
     const int quarter = warp % 4;
     int local = 0;
     for (int tile = blockIdx.x; tile < tiles; tile += gridDim.x, ++local) {
-      const int m0 = (tile % tiles_m) * kBlockM;
-      const int n0 = (tile / tiles_m) * BN;
+      int tile_m, tile_n;
+      tile_coordinates(tile, tiles_m, tiles_n, &tile_m, &tile_n);
+      const int m0 = tile_m * kBlockM;
+      const int n0 = tile_n * BN;
       const int acc = local & 1;
       const std::uint32_t acc_phase = (local >> 1) & 1U;
       if (!mbar_wait(tmem_full_bar(acc), acc_phase, abort_flag)) break;
