@@ -91,6 +91,24 @@ def tokens_for(rank: int, count: int):
     return rng.choice(np.frombuffer(b"ACGT", np.uint8), count).astype(np.uint8)
 
 
+def max_over_ranks(value: float, device: str, distributed: bool) -> float:
+    """The slowest rank's time: every multi-rank figure is computed from it."""
+    import torch
+
+    holder = torch.tensor([value], dtype=torch.float64, device=device)
+    if distributed:
+        import torch.distributed as dist
+
+        dist.all_reduce(holder, op=dist.ReduceOp.MAX)
+    return float(holder.item())
+
+
+def aggregate_throughput(world: int, tokens_per_rank: int, seconds: float) -> float:
+    """Whole-job tokens/s of `world` replicas that each process tokens_per_rank
+    tokens per step (weak scaling: per-rank work is fixed)."""
+    return world * tokens_per_rank / seconds
+
+
 def gemm_flops_per_token(tokens: int) -> float:
     per_block = 2.0 * (3 * WIDTH * WIDTH + WIDTH * WIDTH + 3 * WIDTH * INNER)
     return per_block * LAYERS + 2.0 * WIDTH * VOCAB
@@ -232,11 +250,8 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> None:
         stop.record(stream)
         context.synchronize()
     barrier()
-    elapsed_ms = torch.tensor([start.elapsed_time(stop)], device="cuda")
-    if distributed:
-        dist.all_reduce(elapsed_ms, op=dist.ReduceOp.MAX)
-    ms_per_step = float(elapsed_ms.item()) / args.steps
-    value = world * tokens / (ms_per_step * 1e-3)
+    ms_per_step = max_over_ranks(start.elapsed_time(stop), "cuda", distributed) / args.steps
+    value = aggregate_throughput(world, tokens, ms_per_step * 1e-3)
 
     # ---- per-operator timing (separate pass; events cost a few us per launch)
     context.profile_enable(True)
@@ -276,11 +291,29 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> None:
         e2e_times.append(time.perf_counter() - begin)
         fresh.close()
     e2e_times = e2e_times[min(args.warmup, 2):]
-    e2e_seconds = torch.tensor([sum(e2e_times) / len(e2e_times)], device="cuda")
-    if distributed:
-        dist.all_reduce(e2e_seconds, op=dist.ReduceOp.MAX)
-    e2e_value = world * tokens / float(e2e_seconds.item())
+    e2e_value = aggregate_throughput(
+        world, tokens, max_over_ranks(sum(e2e_times) / len(e2e_times), "cuda", distributed))
     assert logits.shape == (tokens, VOCAB) and np.isfinite(logits).all()
+
+    # ---- cached decode after a 1,024-token prompt (greedy, host sampler, one
+    # evo_context_decode call per token: logits come back to the host each step)
+    decode = None
+    if rank == 0 and args.decode_tokens > 0:
+        decode = {}
+        for name, profile_flags in (("b200-tc", flags), ("exact", 0)):
+            ctx = model.context(min(tokens, 1024) + args.decode_tokens + 16, profile_flags)
+            prompt_logits = ctx.prefill(sequence[:min(tokens, 1024)])
+            token = int(prompt_logits[-1].argmax())
+            for _ in range(4):
+                token = int(ctx.decode(token).argmax())
+            torch.cuda.synchronize()
+            begin = time.perf_counter()
+            for _ in range(args.decode_tokens):
+                token = int(ctx.decode(token).argmax())
+            seconds = time.perf_counter() - begin
+            decode[name] = {"tokens_per_second": args.decode_tokens / seconds,
+                            "ms_per_token": seconds / args.decode_tokens * 1e3}
+            ctx.close()
 
     if rank == 0:
         line = {
@@ -300,6 +333,7 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> None:
             "gflop_per_token": gemm_flops_per_token(tokens) / 1e9,
             "model_tflops": gemm_flops_per_token(tokens) * tokens / (ms_per_step * 1e-3) / 1e12,
             "roofline": roofline, "clocks": clocks.summary(),
+            "cached_decode_after_1024_token_prompt": decode,
         }
         if world == 1 and not args.skip_cpu_baseline:
             line["cpu_baseline"] = cpu_baseline(args, rt)
@@ -337,6 +371,8 @@ def main() -> None:
     parser.add_argument("--reference-tokens", type=int, default=8,
                         help="tokens per CPU step (about 0.5 tokens/s/core on this shape)")
     parser.add_argument("--skip-cpu-baseline", action="store_true")
+    parser.add_argument("--decode-tokens", type=int, default=64,
+                        help="cached-decode steps timed after a 1,024-token prompt (0 disables)")
     args = parser.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     rank = int(os.environ.get("RANK", "0"))

@@ -26,7 +26,7 @@ FLAGS = [
 ]
 
 KERNEL_SOURCES = [
-    "errors.cu", "elementwise.cu", "qgmma_emulation.cu", "gemm_tcgen05.cu",
+    "errors.cu", "elementwise.cu", "qgmma_emulation.cu", "gemm_tcgen05.cu", "gemv.cu",
     "hyena_fir.cu", "hyena_fir_fused.cu", "hyena_modal.cu", "attention.cu", "attention_flash.cu",
 ]
 OPS_SOURCES = KERNEL_SOURCES + ["ops_api.cu"]
@@ -90,6 +90,21 @@ def build(force: bool = False) -> dict[str, Path]:
                 "-Xlinker", f"--version-script={CSRC / 'runtime' / 'evo.map'}",
                 "-Xlinker", "-soname=libevo.so.1"])
         outputs["evo"] = lib
+        soname = HERE / "libevo.so.1"
+        if not soname.exists():
+            soname.symlink_to("libevo.so")
+        # command-line driver: links only against the public C ABI of libevo.so
+        cli_source = CSRC / "runtime" / "cli_main.cpp"
+        cli = HERE / "evo"
+        if cli_source.exists() and (force or not cli.exists()
+                                    or cli.stat().st_mtime < max(cli_source.stat().st_mtime,
+                                                                 lib.stat().st_mtime)):
+            cmd = [os.environ.get("CXX", "g++"), "-O2", "-std=c++17", "-o", str(cli), str(cli_source),
+                   f"-L{HERE}", "-l:libevo.so", "-Wl,-rpath,$ORIGIN"]
+            result = subprocess.run(cmd, capture_output=True, text=True)
+            if result.returncode != 0:
+                raise RuntimeError(f"CLI build failed:\n{result.stdout}\n{result.stderr}")
+        outputs["cli"] = cli
     return outputs
 
 

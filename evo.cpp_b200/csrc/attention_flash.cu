@@ -256,14 +256,10 @@ int flash_causal_attention(const void *query, const void *key_cache,
     if ((reinterpret_cast<std::uintptr_t>(p) & 15U) != 0)
       return fail(kInvalidArgument, "flash attention buffers must be 16-byte aligned");
   constexpr int smem = 5 * kTileBytes;
-  static bool configured = false;
-  if (!configured) {
-    if (cudaFuncSetAttribute(flash_causal_kernel,
-                             cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             smem) != cudaSuccess)
-      return fail(kCuda, "cannot raise the flash attention shared-memory limit");
-    configured = true;
-  }
+  // per device and cheap: set on every call
+  if (cudaFuncSetAttribute(flash_causal_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                           smem) != cudaSuccess)
+    return fail(kCuda, "cannot raise the flash attention shared-memory limit");
   const dim3 grid(ceil_div_u(rows, kBlockM), static_cast<unsigned int>(heads));
   flash_causal_kernel<<<grid, kFlashThreads, smem, stream>>>(
       static_cast<const bf16 *>(query), static_cast<const bf16 *>(key_cache),

@@ -671,6 +671,7 @@ int linear(const LinearArgs &args, cudaStream_t stream) {
       args.in_features > 0x3fffffffU)
     return fail(kInvalidArgument, "linear dimensions are too large");
   if (args.rows == 0) return kOk;
+  if (small_batch_linear_applicable(args)) return small_batch_linear(args, stream);
   const std::size_t out_columns =
       args.gate_mode != 0 ? args.out_features / 2 : args.out_features;
   EpilogueParams ep{};

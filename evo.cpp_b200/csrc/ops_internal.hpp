@@ -57,6 +57,9 @@ struct LinearArgs {
   bool force_simt = false;
 };
 int linear(const LinearArgs &args, cudaStream_t stream);
+// gemv.cu: weight-streaming kernel that linear() uses for 1..8 rows.
+bool small_batch_linear_applicable(const LinearArgs &args);
+int small_batch_linear(const LinearArgs &args, cudaStream_t stream);
 // Synchronises the stream and reports (then clears) a pipeline time-out.
 int gemm_error_state(cudaStream_t stream);
 

@@ -512,6 +512,23 @@ const char *evo_b200_profile_category_name(size_t index) {
   return evob::profile_category_name(static_cast<int>(index));
 }
 
+evo_status evo_b200_plan_stages(const size_t *layer_bytes, size_t layers, size_t stages,
+                                int even_split, size_t *begins, size_t *ends) {
+  return protect([&]() -> int {
+    if (layer_bytes == nullptr || begins == nullptr || ends == nullptr || stages == 0 ||
+        stages > 8 || layers < stages)
+      return fail(evob::kInvalidArgument, "stage plan needs 1..8 stages and a layer per stage");
+    const auto plan = evob::plan_stages(std::vector<std::size_t>(layer_bytes, layer_bytes + layers),
+                                        stages, even_split != 0);
+    if (plan.size() != stages) return fail(evob::kInternal, "stage planning failed");
+    for (size_t i = 0; i < stages; ++i) {
+      begins[i] = plan[i].first;
+      ends[i] = plan[i].second;
+    }
+    return kOk;
+  });
+}
+
 size_t evo_b200_context_stage_count(const evo_context *context) {
   return context == nullptr ? 0 : context->context->stages().size();
 }

@@ -1,0 +1,379 @@
+// `evo` command-line driver for the CUDA path: run / score / bench, written
+// against the public C ABI only (include/evo/evo.h + evo_b200.h).  Mirrors the
+// surface of upstream's CUDA CLI (src/cli.cpp:98-173,
+// src/cuda/inference_cli.cpp:199-263, 341-700, 1310-1345): the same
+// sub-commands and legacy flag form, score JSONL fields, bench JSONL schema
+// (include/evo/benchmark.hpp, src/benchmark.cpp:41-100), raw-byte generation on
+// stdout and one `evo_metrics {...}` line on stderr.  Exit code = evo_status.
+#include <algorithm>
+#include <chrono>
+#include <cmath>
+#include <cstdint>
+#include <cstdio>
+#include <cstring>
+#include <fstream>
+#include <iomanip>
+#include <iostream>
+#include <limits>
+#include <sstream>
+#include <string>
+#include <vector>
+
+#include "../../../include/evo/evo.h"
+#include "../../../include/evo/evo_b200.h"
+
+namespace {
+
+struct Options {
+  std::string command = "run", model, prompt, input, profile = "exact", output_format = "raw",
+              name = "generated";
+  std::vector<int32_t> gpus{0};
+  size_t tokens = 0, context = 4096, warmup = 1, repetitions = 5, top_k = 1;
+  float temperature = 1.0F, top_p = 1.0F;
+  uint64_t seed = 0;
+  bool allow_fixture = false;
+};
+
+struct Record {
+  std::string name, format;
+  std::string bytes;
+};
+
+[[noreturn]] void die(const int code, const std::string &message) {
+  std::cerr << "evo: " << message << '\n';
+  std::exit(code);
+}
+
+void check(const evo_status status, const char *what) {
+  if (status != EVO_STATUS_OK) die(static_cast<int>(status), std::string(what) + ": " + evo_last_error());
+}
+
+double seconds_since(const std::chrono::steady_clock::time_point start) {
+  return std::chrono::duration<double>(std::chrono::steady_clock::now() - start).count();
+}
+
+void json_string(std::ostream &out, const std::string &text) {
+  out.put('"');
+  for (const unsigned char c : text) {
+    if (c == '"' || c == '\\') out << '\\' << c;
+    else if (c < 0x20) out << "\\u" << std::hex << std::setw(4) << std::setfill('0') << int(c) << std::dec;
+    else out.put(static_cast<char>(c));
+  }
+  out.put('"');
+}
+
+// FASTA ('>'), strict four-line FASTQ ('@') or one raw record; CRLF is
+// normalised; white space inside a sequence line is an error
+// (upstream include/evo/sequence_io.hpp:22-29, docs/sequence-inputs.md:16-33).
+std::vector<Record> read_records(const std::string &path, const size_t limit) {
+  std::ifstream file(path, std::ios::binary);
+  if (!file) die(EVO_STATUS_IO, "cannot open input: " + path);
+  std::vector<std::string> lines;
+  for (std::string line; std::getline(file, line);) {
+    if (!line.empty() && line.back() == '\r') line.pop_back();
+    lines.push_back(line);
+  }
+  while (!lines.empty() && lines.back().empty()) lines.pop_back();
+  if (lines.empty()) die(EVO_STATUS_INVALID_ARGUMENT, "input holds no sequence");
+  const auto validate = [&](const std::string &sequence) {
+    for (const unsigned char c : sequence)
+      if (c == ' ' || c == '\t') die(EVO_STATUS_INVALID_ARGUMENT, "white space inside a sequence line");
+    if (sequence.size() > limit)
+      die(EVO_STATUS_INVALID_ARGUMENT, "sequence exceeds --ctx " + std::to_string(limit));
+  };
+  std::vector<Record> records;
+  if (lines[0][0] == '>') {
+    for (const std::string &line : lines) {
+      if (!line.empty() && line[0] == '>') records.push_back({line.substr(1), "fasta", ""});
+      else records.back().bytes += line;
+    }
+  } else if (lines[0][0] == '@') {
+    if (lines.size() % 4 != 0) die(EVO_STATUS_INVALID_ARGUMENT, "FASTQ input is not a multiple of four lines");
+    for (size_t i = 0; i < lines.size(); i += 4) {
+      if (lines[i].empty() || lines[i][0] != '@' || lines[i + 2].empty() || lines[i + 2][0] != '+' ||
+          lines[i + 1].size() != lines[i + 3].size())
+        die(EVO_STATUS_INVALID_ARGUMENT, "malformed FASTQ record");
+      records.push_back({lines[i].substr(1), "fastq", lines[i + 1]});
+    }
+  } else {
+    Record record{"sequence", "raw", ""};
+    for (const std::string &line : lines) record.bytes += line;
+    records.push_back(record);
+  }
+  for (const Record &record : records) {
+    if (record.bytes.empty()) die(EVO_STATUS_INVALID_ARGUMENT, "empty sequence record");
+    validate(record.bytes);
+  }
+  return records;
+}
+
+uint64_t fnv1a64(const std::string &bytes) {
+  uint64_t hash = 1469598103934665603ULL;
+  for (const unsigned char c : bytes) {
+    hash ^= c;
+    hash *= 1099511628211ULL;
+  }
+  return hash;
+}
+
+struct Collected {
+  std::vector<float> logits;
+  size_t rows = 0, columns = 0;
+};
+
+evo_status collect(const float *logits, size_t rows, size_t columns, size_t, void *user) {
+  auto *sink = static_cast<Collected *>(user);
+  sink->logits.insert(sink->logits.end(), logits, logits + rows * columns);
+  sink->rows += rows;
+  sink->columns = columns;
+  return EVO_STATUS_OK;
+}
+
+// log-softmax of one target in double precision over F32 logits
+// (upstream src/cuda/inference_cli.cpp:199-224).
+double log_probability(const float *logits, const size_t vocab, const uint32_t target) {
+  float maximum = -std::numeric_limits<float>::infinity();
+  for (size_t i = 0; i < vocab; ++i) {
+    if (!std::isfinite(logits[i])) die(EVO_STATUS_INTERNAL, "model produced a non-finite score logit");
+    maximum = std::max(maximum, logits[i]);
+  }
+  double normalizer = 0.0;
+  for (size_t i = 0; i < vocab; ++i)
+    normalizer += std::exp(static_cast<double>(logits[i]) - static_cast<double>(maximum));
+  return static_cast<double>(logits[target]) - static_cast<double>(maximum) - std::log(normalizer);
+}
+
+Options parse(int argc, char **argv) {
+  Options o;
+  int first = 1;
+  if (argc > 1 && argv[1][0] != '-') {
+    o.command = argv[1];
+    first = 2;
+  }
+  const auto value = [&](int &i) -> std::string {
+    if (i + 1 >= argc) die(EVO_STATUS_INVALID_ARGUMENT, std::string("missing value for ") + argv[i]);
+    return argv[++i];
+  };
+  for (int i = first; i < argc; ++i) {
+    const std::string a = argv[i];
+    if (a == "-m" || a == "--model") o.model = value(i);
+    else if (a == "-p" || a == "--prompt") o.prompt = value(i);
+    else if (a == "-n") o.tokens = std::stoull(value(i));
+    else if (a == "--input") o.input = value(i);
+    else if (a == "--score") { o.command = "score"; o.input = value(i); }
+    else if (a == "--ctx") o.context = std::stoull(value(i));
+    else if (a == "--profile") o.profile = value(i);
+    else if (a == "--backend") { if (value(i) == "cpu") die(EVO_STATUS_UNSUPPORTED, "this build provides the CUDA backend only"); }
+    else if (a == "--temp") o.temperature = std::stof(value(i));
+    else if (a == "--top-k") o.top_k = std::stoull(value(i));
+    else if (a == "--top-p") o.top_p = std::stof(value(i));
+    else if (a == "--seed") o.seed = std::stoull(value(i));
+    else if (a == "--warmup") o.warmup = std::stoull(value(i));
+    else if (a == "--repetitions") o.repetitions = std::stoull(value(i));
+    else if (a == "--output-format") o.output_format = value(i);
+    else if (a == "--name") o.name = value(i);
+    else if (a == "--allow-test-fixture") o.allow_fixture = true;
+    else if (a == "--gpu") {
+      o.gpus.clear();
+      std::stringstream list(value(i));
+      for (std::string item; std::getline(list, item, ',');) o.gpus.push_back(std::stoi(item));
+    } else if (a == "--version") { std::cout << evo_version_string() << '\n'; std::exit(0); }
+    else if (a == "--help" || a == "-h") {
+      std::cout << "usage:\n  evo run -m MODEL -p DNA -n TOKENS [--ctx N --gpu 0,1 --profile exact|b200-tc]\n"
+                   "  evo score -m MODEL --input FASTA_FASTQ_OR_TEXT\n"
+                   "  evo bench -m MODEL --input FASTA_FASTQ_OR_TEXT [--warmup N --repetitions N]\n";
+      std::exit(0);
+    } else die(EVO_STATUS_INVALID_ARGUMENT, "unknown option " + a);
+  }
+  if (o.model.empty()) die(EVO_STATUS_INVALID_ARGUMENT, "a model path is required (-m)");
+  if (o.profile != "exact" && o.profile != "b200-tc")
+    die(EVO_STATUS_UNSUPPORTED, "profile must be exact or b200-tc");
+  return o;
+}
+
+struct Metrics {
+  double load_seconds = 0, prefill_seconds = 0, decode_seconds = 0;
+  size_t prefill_tokens = 0, decode_tokens = 0;
+};
+
+evo_context *new_context(const evo_model *model, const Options &o) {
+  evo_context_params params = evo_context_default_params();
+  params.context_size = o.context;
+  if (o.profile == "b200-tc") params.flags |= EVO_CONTEXT_FLAG_B200_TENSORCORE_FP8;
+  evo_context *context = nullptr;
+  check(evo_context_create(model, &params, &context), "context");
+  return context;
+}
+
+Collected prefill(evo_context *context, const std::string &bytes) {
+  evo_batch *batch = nullptr;
+  check(evo_batch_create(1, &batch), "batch");
+  check(evo_batch_add_sequence(batch, reinterpret_cast<const uint8_t *>(bytes.data()), bytes.size()),
+        "batch");
+  Collected sink;
+  const evo_status status = evo_context_prefill(context, batch, collect, &sink);
+  evo_batch_free(batch);
+  check(status, "prefill");
+  return sink;
+}
+
+void print_metrics(const Metrics &m, const Options &o, const evo_context *context) {
+  const auto rate = [](const size_t n, const double s) { return s > 0 ? static_cast<double>(n) / s : 0.0; };
+  std::cerr << "evo_metrics {\"model_load_seconds\":" << std::setprecision(9) << m.load_seconds
+            << ",\"prefill_tokens\":" << m.prefill_tokens << ",\"prefill_seconds\":" << m.prefill_seconds
+            << ",\"prefill_tokens_per_second\":" << rate(m.prefill_tokens, m.prefill_seconds)
+            << ",\"teacher_force_tokens\":0,\"teacher_force_seconds\":0,\"teacher_force_tokens_per_second\":0"
+            << ",\"decode_tokens\":" << m.decode_tokens << ",\"decode_seconds\":" << m.decode_seconds
+            << ",\"decode_tokens_per_second\":" << rate(m.decode_tokens, m.decode_seconds)
+            << ",\"kv_cache\":\"bf16_contiguous\",\"profile\":\"" << o.profile
+            << "\",\"retained_logits_peak_bytes\":0,\"gpus\":[";
+  const size_t stages = context == nullptr ? 0 : evo_b200_context_stage_count(context);
+  for (size_t i = 0; i < stages; ++i) {
+    evo_b200_stage_info info{};
+    info.struct_size = sizeof(info);
+    if (evo_b200_context_stage_info(context, i, &info) != EVO_STATUS_OK) break;
+    std::cerr << (i ? "," : "") << "{\"device\":" << info.device << ",\"layers\":[" << info.layer_begin
+              << ',' << info.layer_end << "],\"weights_bytes\":" << info.weight_bytes
+              << ",\"cache_bytes\":" << info.cache_bytes << ",\"arena_bytes\":" << info.arena_bytes << '}';
+  }
+  std::cerr << "]}\n";
+}
+
+}  // namespace
+
+int main(int argc, char **argv) {
+  const Options o = parse(argc, argv);
+  Metrics metrics;
+  evo_model_params mp = evo_model_default_params();
+  mp.backend = EVO_BACKEND_CUDA;
+  mp.devices = o.gpus.data();
+  mp.device_count = o.gpus.size();
+  if (o.allow_fixture) mp.flags |= EVO_MODEL_FLAG_TEST_ONLY_ALLOW_SYNTHETIC;
+  evo_model *model = nullptr;
+  const auto load_start = std::chrono::steady_clock::now();
+  check(evo_model_load(o.model.c_str(), &mp, &model), "model");
+  metrics.load_seconds = seconds_since(load_start);
+  const size_t vocab = evo_model_vocab_size(model);
+  evo_context *last_context = nullptr;
+
+  if (o.command == "score") {
+    if (o.input.empty()) die(EVO_STATUS_INVALID_ARGUMENT, "score needs --input");
+    for (const Record &record : read_records(o.input, o.context)) {
+      if (record.bytes.size() < 2) die(EVO_STATUS_INVALID_ARGUMENT, "scoring needs at least two tokens");
+      if (last_context != nullptr) evo_context_free(last_context);
+      last_context = new_context(model, o);
+      const auto start = std::chrono::steady_clock::now();
+      const Collected out = prefill(last_context, record.bytes);
+      metrics.prefill_seconds += seconds_since(start);
+      metrics.prefill_tokens += record.bytes.size();
+      std::vector<double> scores;
+      for (size_t t = 0; t + 1 < record.bytes.size(); ++t)
+        scores.push_back(log_probability(out.logits.data() + t * vocab, vocab,
+                                         static_cast<unsigned char>(record.bytes[t + 1])));
+      double total = 0.0;
+      for (const double s : scores) total += s;
+      const double mean = total / static_cast<double>(scores.size());
+      const double perplexity = std::exp(-mean);
+      std::cout << "{\"name\":";
+      json_string(std::cout, record.name);
+      std::cout << ",\"input_format\":\"" << record.format << "\",\"backend\":\"cuda\",\"profile\":\""
+                << o.profile << "\",\"model_id\":";
+      const std::string id = evo_model_id(model);
+      if (id.empty()) std::cout << "null"; else json_string(std::cout, id);
+      std::cout << ",\"tokens\":" << record.bytes.size() << ",\"scored_tokens\":" << scores.size()
+                << ",\"log_likelihood\":" << std::setprecision(17) << total
+                << ",\"mean_log_likelihood\":" << mean << ",\"perplexity\":";
+      if (std::isfinite(perplexity)) std::cout << perplexity; else std::cout << "null";
+      std::cout << ",\"token_log_likelihoods\":[";
+      for (size_t i = 0; i < scores.size(); ++i) std::cout << (i ? "," : "") << scores[i];
+      std::cout << "]}\n";
+    }
+  } else if (o.command == "bench") {
+    if (o.input.empty()) die(EVO_STATUS_INVALID_ARGUMENT, "bench needs --input");
+    if (o.repetitions == 0) die(EVO_STATUS_INVALID_ARGUMENT, "--repetitions must be positive");
+    const Record record = read_records(o.input, o.context).front();
+    std::vector<double> samples;
+    for (size_t i = 0; i < o.warmup + o.repetitions; ++i) {
+      if (last_context != nullptr) evo_context_free(last_context);
+      last_context = new_context(model, o);
+      const auto start = std::chrono::steady_clock::now();
+      prefill(last_context, record.bytes);
+      const double seconds = seconds_since(start);
+      if (i >= o.warmup) {
+        samples.push_back(seconds);
+        metrics.prefill_seconds += seconds;
+        metrics.prefill_tokens += record.bytes.size();
+      }
+    }
+    std::vector<double> sorted = samples;
+    std::sort(sorted.begin(), sorted.end());
+    const double median = sorted.size() % 2 ? sorted[sorted.size() / 2]
+                                            : 0.5 * (sorted[sorted.size() / 2 - 1] + sorted[sorted.size() / 2]);
+    std::ostringstream hash;
+    hash << "fnv1a64:" << std::hex << std::setw(16) << std::setfill('0') << fnv1a64(record.bytes);
+    std::cout << "{\"schema_version\":1,\"command\":\"bench\",\"model_path\":";
+    json_string(std::cout, o.model);
+    std::cout << ",\"model_id\":";
+    const std::string id = evo_model_id(model);
+    if (id.empty()) std::cout << "null"; else json_string(std::cout, id);
+    std::cout << ",\"architecture\":";
+    json_string(std::cout, evo_model_architecture(model));
+    std::cout << ",\"artifact_profile\":";
+    json_string(std::cout, evo_model_profile(model));
+    std::cout << ",\"execution_profile\":\"" << o.profile << "\",\"backend\":\"cuda\",\"input\":{\"path\":";
+    json_string(std::cout, o.input);
+    std::cout << ",\"name\":";
+    json_string(std::cout, record.name);
+    std::cout << ",\"format\":\"" << record.format << "\",\"identity\":\"" << hash.str()
+              << "\"},\"context_size\":" << o.context << ",\"warmup\":" << o.warmup
+              << ",\"repetitions\":" << o.repetitions << ",\"tokens\":" << record.bytes.size()
+              << ",\"timing_scope\":\"prefill_with_host_logits\",\"samples_seconds\":["
+              << std::setprecision(17);
+    for (size_t i = 0; i < samples.size(); ++i) std::cout << (i ? "," : "") << samples[i];
+    std::cout << "],\"statistic\":\"median\",\"median_seconds\":" << median
+              << ",\"median_tokens_per_second\":" << static_cast<double>(record.bytes.size()) / median
+              << "}\n";
+  } else if (o.command == "run") {
+    if (o.prompt.empty()) die(EVO_STATUS_INVALID_ARGUMENT, "run needs a prompt (-p)");
+    if (o.prompt.size() + o.tokens > o.context)
+      die(EVO_STATUS_INVALID_ARGUMENT, "prompt plus generated tokens exceed --ctx");
+    evo_sampler_params sp = evo_sampler_default_params();
+    sp.temperature = o.temperature;
+    sp.top_k = o.top_k;
+    sp.top_p = o.top_p;
+    sp.seed = o.seed;
+    evo_sampler *sampler = nullptr;
+    check(evo_sampler_create(&sp, &sampler), "sampler");
+    last_context = new_context(model, o);
+    auto start = std::chrono::steady_clock::now();
+    Collected out = prefill(last_context, o.prompt);
+    metrics.prefill_seconds = seconds_since(start);
+    metrics.prefill_tokens = o.prompt.size();
+    std::vector<float> logits(out.logits.end() - static_cast<std::ptrdiff_t>(vocab), out.logits.end());
+    std::string generated;
+    start = std::chrono::steady_clock::now();
+    for (size_t i = 0; i < o.tokens; ++i) {
+      uint32_t token = 0;
+      check(evo_sampler_sample(sampler, logits.data(), vocab, &token), "sample");
+      uint8_t byte = 0;
+      check(evo_model_decode_token(model, token, &byte), "decode token");
+      generated.push_back(static_cast<char>(byte));
+      if (i + 1 == o.tokens) break;
+      Collected step;
+      check(evo_context_decode(last_context, token, collect, &step), "decode");
+      logits = step.logits;
+      ++metrics.decode_tokens;
+    }
+    metrics.decode_seconds = seconds_since(start);
+    if (o.output_format == "fasta") std::cout << '>' << o.name << '\n' << generated << '\n';
+    else std::cout << generated;
+    std::cout.flush();
+    evo_sampler_free(sampler);
+  } else {
+    die(EVO_STATUS_UNSUPPORTED, "unknown command " + o.command + " (run, score, bench)");
+  }
+  print_metrics(metrics, o, last_context);
+  if (last_context != nullptr) evo_context_free(last_context);
+  evo_model_free(model);
+  return 0;
+}

@@ -47,6 +47,13 @@ EVO_API evo_status evo_b200_context_profile_enable(evo_context *context, int ena
 EVO_API size_t evo_b200_context_profile_read(const evo_context *context, double *milliseconds,
                                              uint64_t *launches, size_t capacity);
 EVO_API const char *evo_b200_profile_category_name(size_t index);
+/* Host-only: the contiguous pipeline split used at load time.  layer_bytes[i] is
+ * the tensor payload of block i; even_split != 0 selects the equal-count split
+ * used for test fixtures.  Writes `stages` [begin, end) pairs; needs no GPU.
+ * (Upstream computes the same split inside PipelineModel::load,
+ * src/cuda/model.cu:2419-2469.) */
+EVO_API evo_status evo_b200_plan_stages(const size_t *layer_bytes, size_t layers, size_t stages,
+                                        int even_split, size_t *begins, size_t *ends);
 EVO_API size_t evo_b200_context_stage_count(const evo_context *context);
 EVO_API evo_status evo_b200_context_stage_info(const evo_context *context, size_t index,
                                                evo_b200_stage_info *info);

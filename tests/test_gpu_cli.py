@@ -1,0 +1,104 @@
+"""The `evo` command-line driver (score / run / bench) on the tiny fixture:
+byte-for-byte token handling, score arithmetic, output schemas and
+deterministic greedy generation (after upstream's tests/test_cuda_cli.py:
+141-144, 399-543, 448-487, 69-84)."""
+from __future__ import annotations
+
+import json
+import subprocess
+from pathlib import Path
+
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+ROOT = Path(__file__).resolve().parent.parent
+EVO = ROOT / "evo.cpp_b200" / "evo"
+MODEL = ROOT / "tests" / "golden" / "tiny" / "tiny.safetensors"
+
+
+def run(*args, check=True):
+    import torch
+
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    result = subprocess.run([str(EVO), *args, "-m", str(MODEL), "--allow-test-fixture"],
+                            capture_output=True, timeout=300)
+    if check:
+        assert result.returncode == 0, result.stderr.decode()
+    return result
+
+
+def metrics_line(stderr: bytes) -> dict:
+    lines = [l for l in stderr.decode().splitlines() if l.startswith("evo_metrics ")]
+    assert len(lines) == 1
+    return json.loads(lines[0][len("evo_metrics "):])
+
+
+def test_score_matches_log_softmax_of_the_golden_logits(tmp_path):
+    tokens = bytes([2, 5, 7, 3])
+    raw = tmp_path / "prompt.txt"
+    raw.write_bytes(tokens)
+    result = run("score", "--input", str(raw), "--ctx", "64")
+    record = json.loads(result.stdout.decode())
+    assert record["tokens"] == 4 and record["scored_tokens"] == 3
+    assert (record["backend"], record["profile"], record["input_format"]) == ("cuda", "exact", "raw")
+    assert record["model_id"] is None
+    golden = np.fromfile(ROOT / "tests" / "golden" / "tiny" / "logits.f32", "<f4").reshape(4, 512)
+    z = golden.astype(np.float64)
+    expected = [z[t, tokens[t + 1]] - z[t].max() - np.log(np.exp(z[t] - z[t].max()).sum()) for t in range(3)]
+    np.testing.assert_allclose(record["token_log_likelihoods"], expected, atol=0.08)
+    assert abs(record["log_likelihood"] - sum(record["token_log_likelihoods"])) < 1e-9
+    assert abs(record["mean_log_likelihood"] - record["log_likelihood"] / 3) < 1e-12
+    assert abs(record["perplexity"] - np.exp(-record["mean_log_likelihood"])) < 1e-9
+    metrics = metrics_line(result.stderr)
+    assert metrics["prefill_tokens"] == 4 and metrics["kv_cache"] == "bf16_contiguous"
+    assert metrics["gpus"][0]["layers"] == [0, 50]
+
+    # FASTA with two records and CRLF line ends; FASTQ; white space is refused
+    fasta = tmp_path / "two.fa"
+    fasta.write_bytes(b">first\r\nAC\r\nGT\r\n>second\r\nTTGA\r\n")
+    records = [json.loads(l) for l in run("score", "--input", str(fasta), "--ctx", "64").stdout.decode().splitlines()]
+    assert [(r["name"], r["tokens"], r["input_format"]) for r in records] == [("first", 4, "fasta"), ("second", 4, "fasta")]
+    fastq = tmp_path / "one.fq"
+    fastq.write_bytes(b"@read\nACGT\n+\nIIII\n")
+    assert json.loads(run("score", "--input", str(fastq), "--ctx", "64").stdout.decode())["input_format"] == "fastq"
+    spaced = tmp_path / "bad.txt"
+    spaced.write_bytes(b"AC GT\n")
+    assert run("score", "--input", str(spaced), "--ctx", "64", check=False).returncode == 2
+    assert run("score", "--input", str(fasta), "--ctx", "3", check=False).returncode == 2
+
+
+def test_greedy_generation_is_deterministic_and_legacy_form_agrees():
+    first = run("run", "-p", "ACGT", "-n", "12", "--ctx", "64", check=False)
+    if first.returncode == 2 and b"does not map to a byte" in first.stderr:
+        # the random fixture may emit a token above 255, which (as upstream) is
+        # an error; the refusal itself must then be reproducible
+        again = run("run", "-p", "ACGT", "-n", "12", "--ctx", "64", check=False)
+        assert again.returncode == 2 and again.stderr == first.stderr
+        return
+    assert first.returncode == 0, first.stderr.decode()
+    second = run("run", "-p", "ACGT", "-n", "12", "--ctx", "64")
+    legacy = run("-p", "ACGT", "-n", "12", "--ctx", "64")
+    assert len(first.stdout) == 12
+    assert first.stdout == second.stdout == legacy.stdout
+    metrics = metrics_line(first.stderr)
+    assert metrics["prefill_tokens"] == 4 and metrics["decode_tokens"] == 11
+    fasta = run("run", "-p", "ACGT", "-n", "5", "--ctx", "64", "--output-format", "fasta", "--name", "g")
+    assert fasta.stdout.startswith(b">g\n") and fasta.stdout.endswith(b"\n")
+    assert run("run", "-p", "ACGT", "-n", "80", "--ctx", "64", check=False).returncode == 2
+
+
+def test_bench_report_schema(tmp_path):
+    raw = tmp_path / "dna.txt"
+    raw.write_bytes(b"ACGTACGTAC")
+    report = json.loads(run("bench", "--input", str(raw), "--ctx", "64", "--warmup", "1",
+                            "--repetitions", "3").stdout.decode())
+    assert report["schema_version"] == 1 and report["command"] == "bench"
+    assert report["architecture"] == "StripedHyena2Test" and report["artifact_profile"] == "evo2-runtime-v1"
+    assert report["execution_profile"] == "exact" and report["backend"] == "cuda"
+    assert report["tokens"] == 10 and report["repetitions"] == 3 and len(report["samples_seconds"]) == 3
+    assert report["timing_scope"] == "prefill_with_host_logits" and report["statistic"] == "median"
+    assert report["input"]["identity"].startswith("fnv1a64:") and len(report["input"]["identity"]) == 24
+    assert abs(report["median_tokens_per_second"] - 10 / report["median_seconds"]) < 1e-6

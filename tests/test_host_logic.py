@@ -1,0 +1,194 @@
+"""Host-side logic that needs no GPU: the model-level ABI's symbol table, the
+pipeline stage planner, the Safetensors reader's refusals, the sampler, and
+the multi-rank aggregation used by the benchmark (gloo, world size 2)."""
+from __future__ import annotations
+
+import ctypes
+import importlib
+import json
+import re
+import struct
+import subprocess
+import sys
+from pathlib import Path
+
+import numpy as np
+import pytest
+
+ROOT = Path(__file__).resolve().parent.parent
+
+# The 39 symbols of upstream's stable C ABI (tests/test_c_api_symbols.py:12-52 there).
+UPSTREAM_SYMBOLS = """evo_abi_version evo_version_string evo_status_name evo_backend_name evo_last_error
+evo_model_default_params evo_context_default_params evo_sampler_default_params
+evo_embedding_default_options evo_model_load evo_model_free evo_model_backend evo_model_id
+evo_model_architecture evo_model_profile evo_model_vocab_size evo_model_max_context
+evo_model_embedding_width evo_model_layer_count evo_model_encode evo_model_decode_token
+evo_context_create evo_context_free evo_context_position evo_context_capacity evo_context_profile
+evo_context_prefill evo_context_decode evo_context_embed evo_context_embed_ex evo_batch_create
+evo_batch_free evo_batch_clear evo_batch_add_sequence evo_batch_sequence_count
+evo_batch_token_count evo_sampler_create evo_sampler_free evo_sampler_sample""".split()
+
+
+@pytest.fixture(scope="module")
+def rt(pkg):
+    return importlib.import_module("evo_cpp_b200.runtime")
+
+
+@pytest.fixture(scope="module")
+def evo(rt, pkg):
+    return rt.EvoLibrary(pkg.EVO_LIBRARY)
+
+
+def test_libevo_exports_upstream_abi_and_declared_extensions(pkg):
+    assert len(UPSTREAM_SYMBOLS) == 39
+    out = subprocess.run(["nm", "-D", "--defined-only", str(pkg.EVO_LIBRARY)], check=True,
+                         capture_output=True, text=True).stdout
+    exported = {line.split()[-1].split("@")[0] for line in out.splitlines() if line.strip()}
+    header = (ROOT / "include" / "evo" / "evo.h").read_text()
+    declared = set(re.findall(r"\b(evo_\w+)\s*\(", re.sub(r"/\*.*?\*/", "", header, flags=re.S)))
+    declared -= {"evo_logits_callback", "evo_embedding_callback", "evo_embedding_ex_callback",
+                 "evo_status"}  # callback typedefs: `typedef evo_status (*name)(...)`
+    assert declared == set(UPSTREAM_SYMBOLS)
+    extensions = set(re.findall(r"\b(evo_b200_\w+)\s*\(", re.sub(
+        r"/\*.*?\*/", "", (ROOT / "include" / "evo" / "evo_b200.h").read_text(), flags=re.S)))
+    assert exported == set(UPSTREAM_SYMBOLS) | extensions, exported ^ (set(UPSTREAM_SYMBOLS) | extensions)
+    lib = ctypes.CDLL(str(pkg.EVO_LIBRARY))
+    lib.evo_abi_version.restype = ctypes.c_uint32
+    assert lib.evo_abi_version() == (1 << 24) | (5 << 16)
+    lib.evo_status_name.restype = ctypes.c_char_p
+    assert [lib.evo_status_name(c) for c in (0, 2, 3, 4, 5, 6, 7, 70)] == [
+        b"ok", b"invalid_argument", b"io", b"model_format", b"unsupported", b"cuda", b"mps", b"internal"]
+
+
+def plan(evo, layer_bytes, stages, even):
+    n = len(layer_bytes)
+    sizes = (ctypes.c_size_t * n)(*layer_bytes)
+    begins, ends = (ctypes.c_size_t * stages)(), (ctypes.c_size_t * stages)()
+    fn = evo.lib.evo_b200_plan_stages
+    fn.argtypes = [ctypes.c_void_p, ctypes.c_size_t, ctypes.c_size_t, ctypes.c_int, ctypes.c_void_p,
+                   ctypes.c_void_p]
+    status = fn(sizes, n, stages, int(even), begins, ends)
+    return status, list(zip(begins, ends))
+
+
+def test_stage_planner(evo):
+    # fixtures: equal counts, remainder to the first stages (upstream
+    # tests/test_cuda_pipeline.cu:178-209: 50 layers -> 25/25 and 13/13/12/12)
+    assert plan(evo, [1] * 50, 2, True) == (0, [(0, 25), (25, 50)])
+    assert plan(evo, [1] * 50, 4, True) == (0, [(0, 13), (13, 26), (26, 38), (38, 50)])
+    # byte-balanced greedy split: contiguous, at least one layer each, covers everything
+    rng = np.random.default_rng(0)
+    for stages in range(1, 9):
+        sizes = rng.integers(1, 100, 32).tolist()
+        status, stage_list = plan(evo, sizes, stages, False)
+        assert status == 0 and stage_list[0][0] == 0 and stage_list[-1][1] == 32
+        assert all(b < e for b, e in stage_list)
+        assert all(stage_list[i][1] == stage_list[i + 1][0] for i in range(stages - 1))
+        loads = [sum(sizes[b:e]) for b, e in stage_list]
+        assert max(loads) <= sum(sizes) / stages + 2 * max(sizes)
+    # uniform 7B-like blocks over 4 stages: 8 each
+    assert plan(evo, [10] * 32, 4, False)[1] == [(0, 8), (8, 16), (16, 24), (24, 32)]
+    assert plan(evo, [1, 1], 3, False)[0] == 2 and plan(evo, [1] * 9, 9, False)[0] == 2
+
+
+def test_model_reader_refusals(evo, rt, tmp_path):
+    """Bad containers are refused before any device work (status codes as upstream)."""
+    with pytest.raises(rt.EvoError) as err:
+        evo.load(tmp_path / "missing.safetensors")
+    assert err.value.code == 3
+    truncated = tmp_path / "short.safetensors"
+    truncated.write_bytes(b"\x10")
+    with pytest.raises(rt.EvoError) as err:
+        evo.load(truncated)
+    assert err.value.code == 4
+    header = json.dumps({"__metadata__": {"evo2.profile": "s:evo2-runtime-v1"},
+                         "t": {"dtype": "F16", "shape": [2], "data_offsets": [0, 4]}}).encode()
+    header += b" " * (-len(header) % 8)
+    bad_dtype = tmp_path / "dtype.safetensors"
+    bad_dtype.write_bytes(struct.pack("<Q", len(header)) + header + b"\0" * 4)
+    with pytest.raises(rt.EvoError) as err:
+        evo.load(bad_dtype)
+    assert err.value.code == 4 and "dtype" in str(err.value)
+    header = json.dumps({"t": {"dtype": "F32", "shape": [2], "data_offsets": [0, 8]}}).encode()
+    header += b" " * (-len(header) % 8)
+    trailing = tmp_path / "trailing.safetensors"
+    trailing.write_bytes(struct.pack("<Q", len(header)) + header + b"\0" * 12)
+    with pytest.raises(rt.EvoError) as err:
+        evo.load(trailing)
+    assert err.value.code == 4
+    with pytest.raises(rt.EvoError) as err:   # the CPU backend is not part of this library
+        evo.load(ROOT / "tests" / "golden" / "tiny" / "tiny.safetensors", backend=rt.BACKEND_CPU)
+    assert err.value.code == 5
+
+
+def mt19937_64_first_output(seed: int) -> int:
+    """First output of the 64-bit Mersenne Twister (the generator the C++
+    standard fixes as std::mt19937_64), from its published recurrence."""
+    mask = (1 << 64) - 1
+    state = [seed & mask]
+    for i in range(1, 312):
+        state.append((6364136223846793005 * (state[-1] ^ (state[-1] >> 62)) + i) & mask)
+    for i in range(312):
+        x = (state[i] & 0xFFFFFFFF80000000) | (state[(i + 1) % 312] & 0x7FFFFFFF)
+        state[i] = state[(i + 156) % 312] ^ (x >> 1) ^ (0xB5026F5AA96619E9 if x & 1 else 0)
+    y = state[0]
+    y ^= (y >> 29) & 0x5555555555555555
+    y ^= (y << 17) & 0x71D67FFFEDA60000
+    y ^= (y << 37) & 0xFFF7EEE000000000
+    y ^= y >> 43
+    return y & mask
+
+
+def test_sampler_matches_upstream_rule(evo, rt):
+    assert mt19937_64_first_output(5489) == 14514284786278117030  # the standard's check value seed
+    logits = np.array([0.5, 2.0, 2.0, -1.0, 1.5], np.float32)
+    assert rt.Sampler(evo).sample(logits) == 1                     # argmax, lowest index on ties
+    for seed in (0, 7):
+        sampler = rt.Sampler(evo, temperature=0.7, top_k=0, top_p=0.9, seed=seed)
+        order = sorted(range(5), key=lambda i: (-logits[i], i))
+        weights = [float(np.exp(np.float64(logits[i]) / np.float64(np.float32(0.7)) -
+                                np.float64(logits[order[0]]) / np.float64(np.float32(0.7)))) for i in order]
+        total, cumulative, keep = sum(weights), 0.0, 0
+        while keep < len(weights) and cumulative / total < float(np.float32(0.9)):
+            cumulative += weights[keep]
+            keep += 1
+        first = mt19937_64_first_output(seed)
+        draw = (first >> 11) * 2.0 ** -53 * cumulative
+        running, expected = 0.0, order[keep - 1]
+        for i in range(keep):
+            running += weights[i]
+            if draw < running:
+                expected = order[i]
+                break
+        assert sampler.sample(logits) == expected
+    with pytest.raises(rt.EvoError):
+        rt.Sampler(evo, temperature=0.0)
+    with pytest.raises(rt.EvoError):
+        rt.Sampler(evo, top_k=9).sample(logits)
+
+
+WORKER = """
+import sys, importlib.util
+sys.path.insert(0, {root!r})
+spec = importlib.util.spec_from_file_location("bench", {root!r} + "/bench.py")
+bench = importlib.util.module_from_spec(spec); spec.loader.exec_module(bench)
+import torch.distributed as dist
+dist.init_process_group("gloo", init_method="tcp://127.0.0.1:{port}", rank={rank}, world_size=2)
+slowest = bench.max_over_ranks([10.0, 14.0][{rank}], "cpu", True)
+value = bench.aggregate_throughput(2, 8192, slowest * 1e-3)
+assert slowest == 14.0, slowest
+print(value)
+dist.destroy_process_group()
+"""
+
+
+def test_two_rank_aggregation_over_gloo():
+    """Replica ranks report the slowest rank's time; throughput is the sum of
+    what all ranks processed in that time."""
+    port = 29500 + (hash(str(ROOT)) % 400)
+    procs = [subprocess.Popen([sys.executable, "-c", WORKER.format(root=str(ROOT), port=port, rank=rank)],
+                              stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True) for rank in range(2)]
+    outputs = [p.communicate(timeout=180) for p in procs]
+    assert all(p.returncode == 0 for p in procs), outputs
+    for out, _ in outputs:
+        assert abs(float(out.strip().splitlines()[-1]) - 2 * 8192 / 0.014) < 1e-6
