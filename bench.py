@@ -315,6 +315,29 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> None:
                             "ms_per_token": seconds / args.decode_tokens * 1e3}
             ctx.close()
 
+    # ---- layer pipeline of ONE sequence over several GPUs of this process
+    # (chunk wavefront, stream-ordered peer copies; strong scaling of batch 1)
+    pipeline = None
+    if world == 1 and args.pipeline_gpus > 1 and torch.cuda.device_count() >= args.pipeline_gpus:
+        context.close()
+        model.close()
+        piped_model = library.load(directory, devices=list(range(args.pipeline_gpus)))
+        piped = piped_model.context(tokens, flags)
+        for _ in range(args.warmup):
+            piped.prefill_device(device_tokens.data_ptr(), tokens, True)
+        piped.synchronize()
+        piped_stream = torch.cuda.ExternalStream(piped.stream())
+        begin_event, end_event = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        begin_event.record(piped_stream)
+        for _ in range(args.steps):
+            piped.prefill_device(device_tokens.data_ptr(), tokens, True)
+        end_event.record(piped_stream)
+        piped.synchronize()
+        piped_ms = begin_event.elapsed_time(end_event) / args.steps
+        pipeline = {"gpus": args.pipeline_gpus, "ms_per_step": piped_ms,
+                    "tokens_per_second": tokens / (piped_ms * 1e-3),
+                    "speedup_over_one_gpu": ms_per_step / piped_ms,
+                    "stages": [[s.device, s.layer_begin, s.layer_end] for s in piped.stages()]}
     if rank == 0:
         line = {
             "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
@@ -334,6 +357,7 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> None:
             "model_tflops": gemm_flops_per_token(tokens) * tokens / (ms_per_step * 1e-3) / 1e12,
             "roofline": roofline, "clocks": clocks.summary(),
             "cached_decode_after_1024_token_prompt": decode,
+            "layer_pipeline": pipeline,
         }
         if world == 1 and not args.skip_cpu_baseline:
             line["cpu_baseline"] = cpu_baseline(args, rt)
@@ -371,6 +395,9 @@ def main() -> None:
     parser.add_argument("--reference-tokens", type=int, default=8,
                         help="tokens per CPU step (about 0.5 tokens/s/core on this shape)")
     parser.add_argument("--skip-cpu-baseline", action="store_true")
+    parser.add_argument("--pipeline-gpus", type=int, default=0,
+                        help="also time the same prefill as a layer pipeline over this many GPUs of "
+                             "one process (needs that many visible GPUs; only with --gpus 1)")
     parser.add_argument("--decode-tokens", type=int, default=64,
                         help="cached-decode steps timed after a 1,024-token prompt (0 disables)")
     args = parser.parse_args()

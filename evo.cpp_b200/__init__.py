@@ -42,6 +42,8 @@ OPS_SIGNATURES: dict[str, list] = {
     "evo_b200_bf16_fir_prefill_direct": [_P, _P, _I, _P, _Z, _Z, _Z, _Z, _I, _I, _P, _P, _P],
     "evo_b200_bf16_fir_continue_direct": [_P, _P, _I, _P, _Z, _Z, _Z, _Z, _I, _I, _P, _Z, _P, _P],
     "evo_b200_bf16_gated_fir_prefill": [_P, _P, _P, _P, _I, _P, _Z, _Z, _Z, _Z, _I, _P, _P, _P, _P],
+    "evo_b200_bf16_gated_fir_prefill_window": [_P, _P, _P, _P, _I, _P, _Z, _Z, _Z, _Z, _Z, _I, _P, _P, _P],
+    "evo_b200_bf16_hcl_prefill_window": [_P, _P, _P, _P, _P, _P, _Z, _Z, _Z, _Z, _P, _P, _P, _P],
     "evo_b200_bf16_projection_gated_fir_prefill": [_P, _P, _P, _I, _P, _Z, _Z, _Z, _Z, _I, _P, _P, _P, _P, _P],
     "evo_b200_bf16_hcl_prefill": [_P, _P, _P, _P, _P, _P, _Z, _Z, _Z, _I, _P, _P, _P, _P, _P],
     "evo_b200_bf16_hcl_prefill_noalloc": [_P, _P, _P, _P, _P, _P, _Z, _Z, _Z, _I, _P, _P, _P, _P],

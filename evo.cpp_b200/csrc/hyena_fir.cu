@@ -43,7 +43,7 @@ struct FusedParams {
   bf16 *output;
   bf16 *pregate;
   float *inner_cache;
-  int length, width, taps, padded_taps, channels_per_group;
+  int length, row_begin, width, taps, padded_taps, channels_per_group;
   bool filter_is_f32, cross_correlation;
 };
 
@@ -79,7 +79,7 @@ gated_fir_kernel(const FusedParams p) {
   float2 *const h_tile =
       reinterpret_cast<float2 *>(x2_tile + kTileT * kTilePairs);
 
-  const int t0 = blockIdx.x * kTileT;
+  const int t0 = p.row_begin + blockIdx.x * kTileT;
   const int pair0 = blockIdx.y * kTilePairs;
   const int lane_pair = threadIdx.x % kTilePairs;
   const int sub = threadIdx.x / kTilePairs;  // 0..7
@@ -383,8 +383,10 @@ int gated_fir_prefill_generic(const GatedFirArgs &a, cudaStream_t stream) {
                         stream) != cudaSuccess)
       return fail(kCuda, "cannot clear the FIR cache");
   }
-  if (a.length == 0) return kOk;
+  if (a.row_begin > a.length) return fail(kInvalidArgument, "gated FIR row window is invalid");
+  if (a.length == a.row_begin) return kOk;
   FusedParams p{};
+  p.row_begin = static_cast<int>(a.row_begin);
   p.x2 = static_cast<const bf16 *>(a.x2);
   p.x1 = static_cast<const bf16 *>(a.x1);
   p.value = static_cast<const bf16 *>(a.value);
@@ -406,7 +408,7 @@ int gated_fir_prefill_generic(const GatedFirArgs &a, cudaStream_t stream) {
   const std::size_t smem = static_cast<std::size_t>(kTileT + halo) * kTilePairs * 4 +
                            static_cast<std::size_t>(kTileT) * kTilePairs * 4 +
                            static_cast<std::size_t>(p.padded_taps) * kTilePairs * 8;
-  const dim3 grid(ceil_div_u(a.length, kTileT), ceil_div_u(a.width / 2, kTilePairs));
+  const dim3 grid(ceil_div_u(a.length - a.row_begin, kTileT), ceil_div_u(a.width / 2, kTilePairs));
   if (grid.y > 65535) return fail(kInvalidArgument, "gated FIR is too wide");
   auto *const kernel = from_projection ? gated_fir_kernel<true> : gated_fir_kernel<false>;
   if (smem > 48 * 1024 &&

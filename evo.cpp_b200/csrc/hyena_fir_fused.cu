@@ -36,7 +36,7 @@ struct Params {
   const void *filter;
   bf16 *output, *pregate;
   float *inner_cache;
-  int length, width, taps, padded_taps, channels_per_group;
+  int length, row_begin, width, taps, padded_taps, channels_per_group;
   bool filter_is_f32, cross_correlation;
 };
 
@@ -91,8 +91,11 @@ __device__ __forceinline__ void build_tiles(const Params &p, unsigned char *u_ti
     uint4 packed = make_uint4(pack_exact(u[0], u[1]), pack_exact(u[2], u[3]),
                               pack_exact(u[4], u[5]), pack_exact(u[6], u[7]));
     *reinterpret_cast<uint4 *>(u_tile + tile_offset(r, chunk)) = packed;
-    if (t >= t_own && t < p.length && channel_ok) {
-      if (p.pregate != nullptr)
+    // The first CTA of a row window also owns the history rows it recomputes,
+    // so that the decode history is complete even for windows shorter than it.
+    const bool owns = t >= t_own || (blockIdx.x == 0 && t >= 0);
+    if (owns && t < p.length && channel_ok) {
+      if (p.pregate != nullptr && t >= t_own)
         *reinterpret_cast<uint4 *>(p.pregate + static_cast<std::size_t>(t) * p.width + c0) = packed;
       if (p.inner_cache != nullptr && real_halo > 0) {
         const int slot = t - (p.length - real_halo);
@@ -220,7 +223,7 @@ gated_fir_simt_kernel(const Params p) {
   unsigned char *const u_tile = smem;
   unsigned char *const x2_tile = u_tile + (TT + halo) * kRowBytes;
   float2 *const h_tile = reinterpret_cast<float2 *>(x2_tile + TT * kRowBytes);  // [delay][pair]
-  const int t0 = blockIdx.x * TT;
+  const int t0 = p.row_begin + blockIdx.x * TT;
   const int c_tile = blockIdx.y * kChannels;
   const int pair = threadIdx.x % 32;
   const int sub = threadIdx.x / 32;
@@ -316,7 +319,7 @@ gated_fir_mma_kernel(const Params p) {
   unsigned char *const x2_tile = u_tile + (TT + kMmaHalo) * kRowBytes;
   unsigned short *const h_s =
       reinterpret_cast<unsigned short *>(x2_tile + TT * kRowBytes);  // [4 blocks][128] BF16 bits
-  const int t0 = blockIdx.x * TT;
+  const int t0 = p.row_begin + blockIdx.x * TT;
   const int c_tile = blockIdx.y * kChannels;
   const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
   const int block16 = warp % 4;             // 16-channel block of the tile
@@ -400,7 +403,7 @@ int launch(Kernel kernel, const Params &p, const int tile_rows, const std::size_
   if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                            static_cast<int>(smem)) != cudaSuccess)
     return fail(kCuda, "cannot raise the fused FIR shared-memory limit");
-  const dim3 grid(ceil_div_u(p.length, tile_rows), ceil_div_u(p.width, kChannels));
+  const dim3 grid(ceil_div_u(p.length - p.row_begin, tile_rows), ceil_div_u(p.width, kChannels));
   if (grid.y > 65535) return fail(kInvalidArgument, "gated FIR is too wide");
   kernel<<<grid, kThreads, smem, stream>>>(p);
   return check_launch(what);
@@ -419,7 +422,7 @@ int gated_fir_prefill(const GatedFirArgs &a, cudaStream_t stream) {
                          aligned16(a.x1) && aligned16(a.value));
   if (!inputs_ok || a.filter == nullptr || a.output == nullptr || a.width == 0 || a.groups == 0 ||
       a.width % 8 != 0 || a.width % a.groups != 0 || a.taps == 0 || a.taps > 128 ||
-      a.length == 0 || a.length > 0x7fff0000U || !aligned16(a.output) ||
+      a.length == 0 || a.row_begin >= a.length || a.length > 0x7fff0000U || !aligned16(a.output) ||
       (a.pregate != nullptr && !aligned16(a.pregate)))
     return gated_fir_prefill_generic(a, stream);  // validates and reports
   if (a.inner_cache != nullptr && a.taps > 1 &&
@@ -437,6 +440,7 @@ int gated_fir_prefill(const GatedFirArgs &a, cudaStream_t stream) {
   p.pregate = static_cast<bf16 *>(a.pregate);
   p.inner_cache = a.inner_cache;
   p.length = static_cast<int>(a.length);
+  p.row_begin = static_cast<int>(a.row_begin);
   p.width = static_cast<int>(a.width);
   p.taps = static_cast<int>(a.taps);
   p.padded_taps = static_cast<int>((a.taps + kRun - 1) / kRun * kRun);

@@ -34,7 +34,7 @@ struct ModalParams {
   bf16 *output, *pregate;
   float *state;    // [width, modes]
   float *scratch;  // [segments, width, modes]
-  int length, width, segment, segments, pairs;
+  int length, row_begin, width, segment, segments, pairs;
   bool continue_from_state;
 };
 
@@ -156,7 +156,7 @@ modal_local_kernel(const ModalParams p) {
       pole[c][m] = expf(p.log_poles[static_cast<std::size_t>(c0 + c) * kModes + m]);
       state[c][m] = 0.0F;
     }
-  const int t0 = seg * p.segment;
+  const int t0 = p.row_begin + seg * p.segment;
   const int t1 = min(t0 + p.segment, p.length);
   PairReader<kFromProjection> reader(p, c0);
   reader.start(t0);
@@ -206,7 +206,7 @@ __global__ void modal_carry_kernel(const ModalParams p, const int modes) {
       const int seg = seg0 + i;
       if (seg < p.segments) {
         p.scratch[seg * stride + index] = carry;
-        const int span = min(p.segment, p.length - seg * p.segment);
+        const int span = min(p.segment, p.length - p.row_begin - seg * p.segment);
         const float decay =
             span == p.segment ? full_decay : expf(log_pole * static_cast<float>(span));
         carry = fmaf(decay, carry, local[i]);
@@ -239,7 +239,7 @@ modal_output_kernel(const ModalParams p) {
     }
   const float direct0 = bf2f(p.direct[c0]);
   const float direct1 = bf2f(p.direct[c0 + 1]);
-  const int t0 = seg * p.segment;
+  const int t0 = p.row_begin + seg * p.segment;
   const int t1 = min(t0 + p.segment, p.length);
   PairReader<kFromProjection> reader(p, c0);
   reader.start(t0);
@@ -374,9 +374,9 @@ int modal_prefill(const ModalArgs &a, cudaStream_t stream) {
     return fail(kInvalidArgument, "modal prefill inputs are incomplete");
   if (a.continue_from_state && a.state == nullptr)
     return fail(kInvalidArgument, "modal continuation needs a state");
-  if (a.length > 0x7fffff00U || a.width > 0x3fffffffU)
+  if (a.length > 0x7fffff00U || a.width > 0x3fffffffU || a.row_begin > a.length)
     return fail(kInvalidArgument, "modal prefill dimensions are too large");
-  if (a.length == 0) return kOk;
+  if (a.length == a.row_begin) return kOk;
   ModalParams p{};
   p.x2 = static_cast<const bf16 *>(a.x2);
   p.x1 = static_cast<const bf16 *>(a.x1);
@@ -392,8 +392,9 @@ int modal_prefill(const ModalArgs &a, cudaStream_t stream) {
   p.scratch = a.scratch;
   p.length = static_cast<int>(a.length);
   p.width = static_cast<int>(a.width);
-  p.segment = pick_segment(a.length, a.width);
-  p.segments = static_cast<int>((a.length + p.segment - 1) / p.segment);
+  p.row_begin = static_cast<int>(a.row_begin);
+  p.segment = pick_segment(a.length - a.row_begin, a.width);
+  p.segments = static_cast<int>((a.length - a.row_begin + p.segment - 1) / p.segment);
   p.pairs = static_cast<int>(a.width / 2);
   p.continue_from_state = a.continue_from_state;
   int status;

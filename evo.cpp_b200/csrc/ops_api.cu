@@ -241,6 +241,53 @@ int evo_b200_bf16_gated_fir_prefill(const void *x2, const void *x1,
   return gated_fir_prefill(a, as_stream(stream));
 }
 
+int evo_b200_bf16_gated_fir_prefill_window(const void *x2, const void *x1, const void *value,
+                                           const void *filter, int filter_is_f32,
+                                           const void *direct, size_t row_begin, size_t length,
+                                           size_t width, size_t groups, size_t taps,
+                                           int orientation, float *inner_cache, void *output,
+                                           void *stream) {
+  GatedFirArgs a;
+  a.x2 = x2;
+  a.x1 = x1;
+  a.value = value;
+  a.filter = filter;
+  a.filter_is_f32 = filter_is_f32 != 0;
+  a.direct = direct;
+  a.row_begin = row_begin;
+  a.length = length;
+  a.width = width;
+  a.groups = groups;
+  a.taps = taps;
+  a.cross_correlation = orientation == 0;
+  a.inner_cache = inner_cache;
+  a.output = output;
+  return gated_fir_prefill(a, as_stream(stream));
+}
+
+int evo_b200_bf16_hcl_prefill_window(const void *x2, const void *x1, const void *value,
+                                     const void *direct, const float *log_poles,
+                                     const float *residues, size_t row_begin, size_t length,
+                                     size_t width, size_t modes, float *state, float *scratch,
+                                     void *output, void *stream) {
+  ModalArgs a;
+  a.x2 = x2;
+  a.x1 = x1;
+  a.value = value;
+  a.direct = direct;
+  a.log_poles = log_poles;
+  a.residues = residues;
+  a.row_begin = row_begin;
+  a.length = length;
+  a.width = width;
+  a.modes = modes;
+  a.continue_from_state = true;
+  a.state = state;
+  a.scratch = scratch;
+  a.output = output;
+  return modal_prefill(a, as_stream(stream));
+}
+
 int evo_b200_bf16_projection_gated_fir_prefill(
     const void *projection, const void *short_filter, const void *filter,
     int filter_is_f32, const void *direct, size_t length, size_t width,

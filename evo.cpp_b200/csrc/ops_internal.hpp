@@ -80,6 +80,10 @@ struct GatedFirArgs {
   void *output = nullptr;         // [length, width] BF16
   void *pregate = nullptr;        // optional [length, width] BF16 (u = x1*v)
   std::size_t length = 0;
+  // Rows [row_begin, length) are produced; rows before row_begin are history
+  // that is still present in the same input buffers (chunked prefill inside
+  // one activation arena).
+  std::size_t row_begin = 0;
   std::size_t width = 0;
   std::size_t groups = 0;
   std::size_t taps = 0;
@@ -124,6 +128,7 @@ struct ModalArgs {
   float *scratch = nullptr;          // segment states, see modal_scratch_floats
   float *short_cache = nullptr;
   std::size_t length = 0;
+  std::size_t row_begin = 0;  // rows [row_begin, length) are produced (see GatedFirArgs)
   std::size_t width = 0;
   std::size_t modes = 0;
   bool continue_from_state = false;  // recurrence-continue numerics

@@ -48,6 +48,11 @@ struct LayerState {
   float *inner_cache = nullptr;  // [D, taps-1]
   float *modal_state = nullptr;  // [D, S]
   void *key_cache = nullptr, *value_cache = nullptr;  // [context, D] BF16
+  // Pipelines only: the last projection rows of the previous wavefront chunk
+  // ([history_rows, 3D] BF16).  The projection arena is shared by all blocks of
+  // a stage, so a block's own history is parked here between chunks.
+  void *history = nullptr;
+  std::size_t history_rows = 0;
 };
 
 struct Context::Stage {
@@ -99,6 +104,20 @@ struct Context::Stage {
       }
     }
     event_category.clear();
+  }
+
+  // Advances (or rewinds) every row-indexed activation pointer by `rows`.
+  void shift_rows(const long rows, const std::size_t D, const std::size_t I) {
+    const auto move = [rows](void *&pointer, const std::size_t row_bytes) {
+      if (pointer != nullptr)
+        pointer = static_cast<unsigned char *>(pointer) + rows * static_cast<long>(row_bytes);
+    };
+    for (void **p : {&hidden, &residual, &normalized, &mixer_out, &query, &x2, &x1, &value, &pregate})
+      move(*p, D * 2);
+    move(codes, D);
+    move(projection, D * 6);
+    move(short_filtered, D * 6);
+    for (void **p : {&gated, &mlp_first, &mlp_second}) move(*p, I * 2);
   }
 
   int allocate(void **out, const std::size_t bytes, std::size_t *counter) {
@@ -183,6 +202,13 @@ int Context::create(std::shared_ptr<ModelWeights> weights, const std::size_t con
       }
       EVOB_TRY(stage->allocate(&p, 3 * D * (c.short_taps - 1) * 4, cache));
       state.short_cache = static_cast<float *>(p);
+      if (weights->stages.size() > 1) {
+        const std::size_t taps = type == MixerType::kHcs ? c.hcs_taps
+                                 : type == MixerType::kHcm ? c.hcm_taps : 1;
+        // the fused kernels stage a 16-row-aligned halo plus the featurizer's two rows
+        state.history_rows = (taps + 15) / 16 * 16 + (c.short_taps - 1);
+        EVOB_TRY(stage->allocate(&state.history, state.history_rows * 3 * D * 2 + 16, cache));
+      }
       if (type == MixerType::kHcl) {
         EVOB_TRY(stage->allocate(&p, D * c.state_size * 4, cache));
         state.modal_state = static_cast<float *>(p);
@@ -193,6 +219,19 @@ int Context::create(std::shared_ptr<ModelWeights> weights, const std::size_t con
       }
     }
     context->stages_.push_back(std::move(stage));
+  }
+  // Direct peer copies between neighbouring stages (and last -> first for the
+  // head); without peer access the copies still work, staged by the driver.
+  for (std::size_t i = 0; i < context->stages_.size() && context->stages_.size() > 1; ++i) {
+    const int a = context->stages_[i]->device;
+    const int b = context->stages_[(i + 1) % context->stages_.size()]->device;
+    for (const auto &[from, to] : {std::pair<int, int>{a, b}, std::pair<int, int>{b, a}}) {
+      int possible = 0;
+      if (from == to || cudaDeviceCanAccessPeer(&possible, from, to) != cudaSuccess || !possible) continue;
+      DeviceGuard guard(from);
+      const cudaError_t error = cudaDeviceEnablePeerAccess(to, 0);
+      if (error != cudaSuccess) cudaGetLastError();  // already enabled or refused: both fine
+    }
   }
   *out = std::move(context);
   return kOk;
@@ -267,12 +306,23 @@ void Context::read_profile(double (&milliseconds)[kProfileCategories],
   }
 }
 
+// `window_begin` > 0 (Mode::kWindow) means: the stage's activation pointers have
+// been advanced by window_begin rows by the caller and this call produces rows
+// [window_begin, window_begin + rows) of a prefill whose earlier rows are still
+// in the same arena buffers.  The fused Hyena kernels then read their history
+// straight from those earlier rows.
 int Context::run_stage(Stage &s, const std::size_t rows, const Mode mode,
-                       const long capture_layer, std::vector<float> *captured) {
+                       const long capture_layer, std::vector<float> *captured,
+                       const std::size_t window_begin) {
   const ModelConfig &c = weights_->config;
   const std::size_t D = c.width, I = c.inner_width;
-  const bool initial = mode == Mode::kPrefill || mode == Mode::kStateless || mode == Mode::kCachedPrefill;
+  const bool window = mode == Mode::kWindow;
+  const bool initial = mode == Mode::kPrefill || mode == Mode::kStateless ||
+                       mode == Mode::kCachedPrefill || window;
   const bool stateless = mode == Mode::kStateless;
+  const auto rewind = [&](void *advanced, const std::size_t row_bytes) -> void * {
+    return static_cast<unsigned char *>(advanced) - window_begin * row_bytes;
+  };
   cudaStream_t stream = s.stream;
   for (std::size_t i = 0; i < s.layers.size(); ++i) {
     const LayerWeights &w = s.weights->layers[i];
@@ -301,7 +351,7 @@ int Context::run_stage(Stage &s, const std::size_t rows, const Mode mode,
       EVOB_OP(fp8 ? kCatGemmFp8 : kCatGemmBf16, linear(a, stream));
     }
     if (attention) {
-      const std::size_t prefix = initial ? 0 : position_;
+      const std::size_t prefix = window ? window_begin : (initial ? 0 : position_);
       EVOB_OP(kCatAttention, split_rope_append(s.projection, w.inverse_frequency, rows, c.heads, c.head_dim(),
                                  prefix, c.rope_scale, false, s.query, state.key_cache,
                                  state.value_cache, context_size_, stream));
@@ -314,33 +364,47 @@ int Context::run_stage(Stage &s, const std::size_t rows, const Mode mode,
         EVOB_OP(kCatAttention, causal_attention(s.query, state.key_cache, state.value_cache, rows, prefix + rows,
                                   c.heads, c.head_dim(), s.mixer_out, stream));
     } else if (initial) {
+      unsigned char *const projection_base =
+          static_cast<unsigned char *>(rewind(s.projection, D * 6));
+      if (window && state.history != nullptr && window_begin > 0) {
+        // bring this block's own history back under the window
+        const std::size_t have = std::min(state.history_rows, window_begin);
+        if (cudaMemcpyAsync(projection_base + (window_begin - have) * D * 6,
+                            static_cast<unsigned char *>(state.history) +
+                                (state.history_rows - have) * D * 6,
+                            have * D * 6, cudaMemcpyDeviceToDevice, stream) != cudaSuccess)
+          return fail(kCuda, "projection history restore failed");
+      }
       if (w.type == MixerType::kHcl) {
         ModalArgs a;
-        a.projection = s.projection;
+        a.projection = rewind(s.projection, D * 6);
         a.short_filter = w.short_filter;
         a.short_taps = c.short_taps;
         a.direct = w.direct;
         a.log_poles = w.log_poles;
         a.residues = w.residues;
-        a.output = s.mixer_out;
+        a.output = rewind(s.mixer_out, D * 2);
         a.state = stateless ? nullptr : state.modal_state;
         a.scratch = s.modal_scratch;
         a.short_cache = stateless ? nullptr : state.short_cache;
-        a.length = rows;
+        a.length = window_begin + rows;
+        a.row_begin = window_begin;
+        a.continue_from_state = window && window_begin > 0;
         a.width = D;
         a.modes = c.state_size;
         EVOB_OP(kCatModal, modal_prefill(a, stream));
       } else {
         const bool hcs = w.type == MixerType::kHcs;
         GatedFirArgs a;
-        a.projection = s.projection;
+        a.projection = rewind(s.projection, D * 6);
         a.short_filter = w.short_filter;
         a.short_taps = c.short_taps;
         a.filter = w.inner_filter;
         a.filter_is_f32 = !hcs && c.hcm_filter_f32;
         a.direct = hcs ? nullptr : w.direct;
-        a.output = s.mixer_out;
-        a.length = rows;
+        a.output = rewind(s.mixer_out, D * 2);
+        a.length = window_begin + rows;
+        a.row_begin = window_begin;
         a.width = D;
         a.groups = hcs ? c.hcs_groups : c.hcm_groups;
         a.taps = hcs ? c.hcs_taps : c.hcm_taps;
@@ -348,6 +412,15 @@ int Context::run_stage(Stage &s, const std::size_t rows, const Mode mode,
         a.inner_cache = stateless ? nullptr : state.inner_cache;
         a.short_cache = stateless ? nullptr : state.short_cache;
         EVOB_OP(hcs ? kCatShortFir : kCatMediumFir, gated_fir_prefill(a, stream));
+      }
+      if (window && state.history != nullptr) {
+        const std::size_t end = window_begin + rows;
+        const std::size_t keep = std::min(state.history_rows, end);
+        if (cudaMemcpyAsync(static_cast<unsigned char *>(state.history) +
+                                (state.history_rows - keep) * D * 6,
+                            projection_base + (end - keep) * D * 6, keep * D * 6,
+                            cudaMemcpyDeviceToDevice, stream) != cudaSuccess)
+          return fail(kCuda, "projection history save failed");
       }
     } else {
       // continuation / decode against the causal state
@@ -460,6 +533,43 @@ int Context::run_stage(Stage &s, const std::size_t rows, const Mode mode,
   return kOk;
 }
 
+int Context::run_wavefront(const std::size_t rows, const Mode /*mode*/, const long /*capture_layer*/,
+                           std::vector<float> * /*captured*/) {
+  const ModelConfig &c = weights_->config;
+  const std::size_t D = c.width, I = c.inner_width;
+  std::size_t chunk = wavefront_chunk_;
+  if (chunk == 0) {
+    // enough chunks to fill the pipeline (about two per stage), none so small
+    // that the tensor-core tiles run half empty
+    chunk = (rows / (2 * stages_.size()) + 255) / 256 * 256;
+    chunk = std::max<std::size_t>(512, std::min<std::size_t>(chunk, 2048));
+  }
+  for (std::size_t begin = 0; begin < rows; begin += chunk) {
+    const std::size_t count = std::min(chunk, rows - begin);
+    for (std::size_t index = 0; index < stages_.size(); ++index) {
+      Stage &stage = *stages_[index];
+      DeviceGuard guard(stage.device);
+      if (index > 0) {
+        Stage &previous = *stages_[index - 1];
+        // the wait binds to the record of this chunk on the previous stage,
+        // issued just before; later records of the same event do not affect it
+        if (cudaStreamWaitEvent(stage.stream, previous.done, 0) != cudaSuccess ||
+            cudaMemcpyPeerAsync(static_cast<unsigned char *>(stage.hidden) + begin * D * 2, stage.device,
+                                static_cast<unsigned char *>(previous.hidden) + begin * D * 2,
+                                previous.device, count * D * 2, stage.stream) != cudaSuccess)
+          return fail(kCuda, "stage hand-off failed");
+      }
+      stage.shift_rows(static_cast<long>(begin), D, I);
+      const int status = run_stage(stage, count, Mode::kWindow, -1, nullptr, begin);
+      stage.shift_rows(-static_cast<long>(begin), D, I);
+      if (status != kOk) return status;
+      if (cudaEventRecord(stage.done, stage.stream) != cudaSuccess)
+        return fail(kCuda, "stage hand-off failed");
+    }
+  }
+  return kOk;
+}
+
 int Context::forward(const std::uint32_t *host_tokens, const std::uint32_t *device_tokens,
                      const std::size_t rows, const Mode mode, std::vector<float> *logits,
                      const long capture_layer, std::vector<float> *captured) {
@@ -493,7 +603,10 @@ int Context::forward(const std::uint32_t *host_tokens, const std::uint32_t *devi
       status = embedding(device_tokens, first.weights->embedding, rows, c.width, first.hidden,
                          first.stream);
   }
-  for (std::size_t index = 0; index < stages_.size() && status == kOk; ++index) {
+  const bool wavefront = stages_.size() > 1 && (mode == Mode::kPrefill || mode == Mode::kStateless) &&
+                         rows >= 512 && capture_layer < 0;
+  if (wavefront && status == kOk) status = run_wavefront(rows, mode, capture_layer, captured);
+  for (std::size_t index = 0; index < stages_.size() && status == kOk && !wavefront; ++index) {
     Stage &stage = *stages_[index];
     DeviceGuard guard(stage.device);
     if (index > 0) {

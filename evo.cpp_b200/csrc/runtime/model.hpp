@@ -144,13 +144,18 @@ class Context {
 
  private:
   struct Stage;
-  enum class Mode { kPrefill, kStateless, kCachedPrefill, kContinue, kDecode };
+  enum class Mode { kPrefill, kStateless, kCachedPrefill, kContinue, kDecode, kWindow };
   Context() = default;
   int forward(const std::uint32_t *host_tokens, const std::uint32_t *device_tokens,
               std::size_t rows, Mode mode, std::vector<float> *logits, long capture_layer,
               std::vector<float> *captured);
   int run_stage(Stage &stage, std::size_t rows, Mode mode, long capture_layer,
-                std::vector<float> *captured);
+                std::vector<float> *captured, std::size_t window_begin = 0);
+  // Chunk wavefront over the pipeline stages: chunk j runs on stage s while
+  // chunk j+1 runs on stage s-1 (legal because every mixer carries causal
+  // state).  Used for initial prefills on more than one stage.
+  int run_wavefront(std::size_t rows, Mode mode, long capture_layer, std::vector<float> *captured);
+  std::size_t wavefront_chunk_ = 0;  // 0 = choose from rows and stage count
 
   std::shared_ptr<ModelWeights> weights_;
   std::vector<std::unique_ptr<Stage>> stages_;

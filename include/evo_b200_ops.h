@@ -139,6 +139,22 @@ EVO_B200_API int evo_b200_bf16_gated_fir_prefill(
     int filter_is_f32, const void *direct, size_t length, size_t width,
     size_t groups, size_t taps, int orientation, void *pregate,
     float *inner_cache, void *output, void *stream);
+/* Row-window forms used by chunked prefill inside one activation arena
+ * (upstream's continuation operators bf16_hcs_continue / bf16_hcm_continue /
+ * HclPrefillMode::kRecurrenceContinue, include/evo/cuda/hyena.hpp:216-250, keep
+ * the history in F32 caches instead): only rows [row_begin, length) are
+ * produced; earlier rows of the same input buffers are the history.  For the
+ * HCL form *state must hold the modal state after row_begin-1 (mode 1). */
+EVO_B200_API int evo_b200_bf16_gated_fir_prefill_window(
+    const void *x2, const void *x1, const void *value, const void *filter,
+    int filter_is_f32, const void *direct, size_t row_begin, size_t length,
+    size_t width, size_t groups, size_t taps, int orientation,
+    float *inner_cache, void *output, void *stream);
+EVO_B200_API int evo_b200_bf16_hcl_prefill_window(
+    const void *x2, const void *x1, const void *value, const void *direct,
+    const float *log_poles, const float *residues, size_t row_begin,
+    size_t length, size_t width, size_t modes, float *state, float *scratch,
+    void *output, void *stream);
 /* The same operator fed by the raw interleaved projection [length, 3*width]
  * with the 3-tap featurizer [3*width, 3] applied on the fly
  * (src/cuda/model.cu:1431-1470 + 1477-1520 in one pass). */
