@@ -18,8 +18,14 @@ Printed JSON line (rank 0):
              step / its summed launch time, from per-operator CUDA events
   cpu_baseline  upstream's own CPU backend (oracle/_ref/libevo_ref.so) on a
              bounded sample of the same workload, one core
-With --gpus N > 1 (torchrun, one rank per GPU) every rank holds a full replica
-and runs its own sequence: weak scaling, no data-path collective.
+With --gpus N > 1 (torchrun, one rank per GPU) the ranks form the layer
+pipeline of ONE model: rank r holds stage r of the byte-balanced block split and
+the prompt flows through them as a chunk wavefront, hidden rows handed over with
+NCCL send/recv (strong scaling: total work per step is fixed).  The K timed
+prompts are streamed back to back, so a stage starts prompt k+1 while later
+stages finish prompt k; the isolated latency of one prompt is reported beside
+it as single_prompt.  --multi-gpu replicas instead gives every rank a full
+replica and its own sequence (weak scaling, no data-path exchange).
 
 --impl reference times upstream's CPU implementation (rank 0 only).
 """
@@ -367,6 +373,154 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> None:
         dist.destroy_process_group()
 
 
+def run_pipeline(args, rank: int, world: int, local_rank: int) -> None:
+    """One pipeline stage per rank; see the module docstring."""
+    import importlib
+
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+
+    load_package()
+    rt = importlib.import_module("evo_cpp_b200.runtime")
+    pipe = importlib.import_module("evo_cpp_b200.pipeline")
+    torch.cuda.set_device(local_rank)
+    # no device_id: point-to-point pairs then get their own communicators, so a
+    # stage's send to its successor never queues behind its receive
+    dist.init_process_group("nccl")
+
+    def barrier():
+        dist.barrier(device_ids=[local_rank])
+        torch.cuda.synchronize()
+
+    if rank == 0:
+        ensure_artifact("fp8", "cuda")
+    barrier()
+    directory = model_entry(artifact_dir("fp8"))
+    library = rt.EvoLibrary(ROOT / "evo.cpp_b200" / "libevo.so")
+    load_start = time.perf_counter()
+    model = library.load_slice(directory, local_rank, rank, world)
+    load_seconds = time.perf_counter() - load_start
+    tokens = args.tokens
+    flags = rt.CONTEXT_FLAG_TENSORCORE_FP8
+    context = model.context(tokens, flags)
+    host_tokens = tokens_for(0, tokens)
+    pinned_tokens = torch.from_numpy(host_tokens.astype(np.int32)).pin_memory()
+    device_tokens = pinned_tokens.cuda()
+    pinned_logits = torch.empty((tokens, VOCAB), dtype=torch.int16).pin_memory()
+    stage = pipe.ContextStage(context, device_tokens)
+    driver = pipe.StagePipeline(stage, pipe.alias_hidden_rows(context, tokens, WIDTH, "cuda"), rank, world,
+                                chunk=args.pipeline_chunk)
+    stream = torch.cuda.ExternalStream(context.stream())
+    last = rank == world - 1
+
+    def elapsed_max(start, stop) -> float:
+        return max_over_ranks(start.elapsed_time(stop), "cuda", True)
+
+    with torch.cuda.stream(stream):
+        for _ in range(args.warmup):
+            driver.step(tokens)
+        context.synchronize()
+        barrier()
+        # ---- K prompts streamed back to back
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        with ClockSampler(local_rank) as clocks:
+            start.record(stream)
+            for _ in range(args.steps):
+                driver.step(tokens)
+            stop.record(stream)
+            context.synchronize()
+        barrier()
+        ms_per_step = elapsed_max(start, stop) / args.steps
+        # ---- one prompt at a time (latency of a single batch-1 prefill)
+        isolated = []
+        for _ in range(args.steps):
+            barrier()
+            start.record(stream)
+            driver.step(tokens)
+            stop.record(stream)
+            context.synchronize()
+            isolated.append(elapsed_max(start, stop))
+        single_ms = sum(isolated) / len(isolated)
+        # ---- per-operator timing
+        barrier()
+        context.profile_enable(True)
+        for _ in range(args.steps):
+            driver.step(tokens)
+        context.synchronize()
+        profile = context.profile_read()
+        context.profile_enable(False)
+        # ---- end to end: pinned host tokens in on rank 0, logits out to pinned
+        # host memory on the last rank, every step
+        barrier()
+        begin = time.perf_counter()
+        for _ in range(args.steps):
+            if rank == 0:
+                device_tokens.copy_(pinned_tokens, non_blocking=True)
+            driver.step(tokens)
+            if last:
+                raw = torch.as_tensor(pipe.DeviceRows(stage.logits_address, tokens, VOCAB), device="cuda")
+                pinned_logits.copy_(raw, non_blocking=True)
+        driver.drain()
+        context.synchronize()
+        barrier()
+        e2e_seconds = max_over_ranks(time.perf_counter() - begin, "cuda", True) / args.steps
+    if last:
+        bits = pinned_logits.numpy().astype(np.uint16).astype(np.uint32) << 16
+        assert np.isfinite(bits.view(np.float32)).all()
+
+    totals = torch.tensor([sum(n for _, n in profile.values()) + (1 if rank == 0 else 0) * args.steps,
+                           profile["gemm_bf16_tcgen05"][0], profile["gemm_e4m3_tcgen05"][0]],
+                          dtype=torch.float64, device="cuda")
+    dist.all_reduce(totals)
+    per_operator = torch.tensor([profile[name][0] for name in sorted(profile)], dtype=torch.float64, device="cuda")
+    dist.all_reduce(per_operator)
+    layout = [None] * world
+    info = context.stages()[0]
+    dist.all_gather_object(layout, [rank, int(info.layer_begin), int(info.layer_end),
+                                    round(info.weight_bytes / 2**30, 2)])
+    if rank == 0:
+        launches, gemm_ms, fp8_ms = (float(x) for x in totals.tolist())
+        hyena_layers = LAYERS - ATTENTION_LAYERS
+        flops_fp8 = 2.0 * tokens * WIDTH * 3 * WIDTH * hyena_layers
+        flops_bf16 = gemm_flops_per_token(tokens) * tokens - flops_fp8
+        achieved = flops_bf16 * args.steps / (gemm_ms * 1e-3) / 1e12
+        peaks_file = ROOT / "MEASURED_PEAKS.json"
+        peaks = json.loads(peaks_file.read_text()) if peaks_file.exists() else {}
+        peak = peaks.get("bf16_tflops_sustained", 1400.0)
+        line = {
+            "metric": METRIC, "value": tokens / (ms_per_step * 1e-3), "unit": "tokens/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None,
+            "dtype": "bf16 activations, e4m3 Hyena projections (tcgen05), f32 accumulate", "data": "synthetic",
+            "config": {"workload": f"Evo 2 7B-shaped StripedHyena2 (32 blocks, d_model 4096, FFN 11264, vocab 512), "
+                                   f"batch-1 stateless prefill of {tokens} uniform-ACGT tokens, profile b200-tc",
+                       "model_id": MODEL_ID, "seed": SEED, "tokens": tokens,
+                       "parallelism": f"pp{world}: one pipeline stage per rank, chunk wavefront, NCCL send/recv of "
+                                      f"hidden rows; the {args.steps} timed prompts streamed back to back",
+                       "stages": layout, "windows": pipe.window_plan(tokens, world, args.pipeline_chunk),
+                       "l2_policy": "weights and activations exceed the 126 MB L2 every step; no flush needed",
+                       "model_load_seconds": load_seconds},
+            "single_prompt": {"ms": single_ms, "tokens_per_second": tokens / (single_ms * 1e-3),
+                              "note": "one prompt at a time, barrier between prompts, slowest rank"},
+            "e2e": {"value": tokens / e2e_seconds, "unit": "tokens/s", "h2d_bytes_per_step": 4 * tokens,
+                    "d2h_bytes_per_step": 2 * tokens * VOCAB},
+            "gpu_launches": int(launches),
+            "roofline": {"bound": "tensor", "kernel": "gemm_tcgen05_kernel<bf16> (all BF16 projections, all ranks)",
+                         "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
+                         "peak_source": "MEASURED_PEAKS.json bf16_tflops_sustained (of measured)" if peaks else
+                                        "fallback 1.4 PFLOP/s sustained (of fallback)",
+                         "traffic": None,
+                         "fp8_projection_tflops": flops_fp8 * args.steps / (fp8_ms * 1e-3) / 1e12 if fp8_ms else None,
+                         "operator_ms_per_step_summed_over_ranks": {
+                             name: ms / args.steps for name, ms in zip(sorted(profile), per_operator.tolist()) if ms}},
+            "clocks": clocks.summary(),
+        }
+        print(json.dumps(line))
+    barrier()
+    dist.destroy_process_group()
+
+
 def cpu_baseline(args, rt) -> dict:
     library_path = ROOT / "oracle" / "_ref" / "libevo_ref.so"
     if not library_path.exists():
@@ -398,6 +552,11 @@ def main() -> None:
     parser.add_argument("--pipeline-gpus", type=int, default=0,
                         help="also time the same prefill as a layer pipeline over this many GPUs of "
                              "one process (needs that many visible GPUs; only with --gpus 1)")
+    parser.add_argument("--multi-gpu", default="pipeline", choices=["pipeline", "replicas"],
+                        help="what --gpus N > 1 ranks do: stages of one layer pipeline (default) or "
+                             "independent full replicas")
+    parser.add_argument("--pipeline-chunk", type=int, default=0,
+                        help="rows per wavefront window (0: about two windows per stage, 512..2048)")
     parser.add_argument("--decode-tokens", type=int, default=64,
                         help="cached-decode steps timed after a 1,024-token prompt (0 disables)")
     args = parser.parse_args()
@@ -407,6 +566,8 @@ def main() -> None:
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     if args.impl == "reference":
         run_reference(args, rank, world)
+    elif world > 1 and args.multi_gpu == "pipeline":
+        run_pipeline(args, rank, world, local_rank)
     else:
         run_ours(args, rank, world, local_rank)
 

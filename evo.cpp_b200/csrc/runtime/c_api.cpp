@@ -8,6 +8,7 @@
 
 #include <cstring>
 #include <exception>
+#include <functional>
 #include <memory>
 #include <new>
 #include <string>
@@ -548,6 +549,56 @@ evo_status evo_b200_context_stage_info(const evo_context *context, size_t index,
     info->arena_bytes = stages[index].arena_bytes;
     return kOk;
   });
+}
+
+evo_status evo_b200_model_load_slice(const char *path, int32_t device, size_t slice_index,
+                                     size_t slice_count, uint32_t flags, evo_model **model_out) {
+  return protect([&]() -> int {
+    if (model_out != nullptr) *model_out = nullptr;
+    if (path == nullptr || model_out == nullptr)
+      return fail(evob::kInvalidArgument, "model path and output are required");
+    if (slice_count < 2)
+      return fail(evob::kInvalidArgument, "a sliced pipeline has at least two slices; use evo_model_load");
+    auto model = std::make_unique<evo_model>();
+    int status = evob::ModelFile::open(path, &model->file);
+    if (status != kOk) return status;
+    status = evob::load_weights(*model->file, {device},
+                                (flags & EVO_MODEL_FLAG_TEST_ONLY_ALLOW_SYNTHETIC) != 0, 0,
+                                &model->weights, slice_index, slice_count);
+    if (status != kOk) return status;
+    *model_out = model.release();
+    return kOk;
+  });
+}
+
+static evo_status slice_call(evo_context *context, const std::function<int(evob::Context &)> &call) {
+  return protect([&]() -> int {
+    if (context == nullptr) return fail(evob::kInvalidArgument, "context is required");
+    if (context->failed || context->context->poisoned())
+      return fail(evob::kInvalidArgument, "context was invalidated by an earlier failure");
+    const int status = call(*context->context);
+    if (status != kOk && context->context->poisoned()) context->failed = true;
+    return status;
+  });
+}
+
+evo_status evo_b200_context_slice_embed(evo_context *context, const uint32_t *device_tokens,
+                                        size_t row_begin, size_t rows) {
+  return slice_call(context, [&](evob::Context &c) { return c.slice_embed(device_tokens, row_begin, rows); });
+}
+evo_status evo_b200_context_slice_run(evo_context *context, size_t row_begin, size_t rows) {
+  return slice_call(context, [&](evob::Context &c) { return c.slice_run(row_begin, rows); });
+}
+evo_status evo_b200_context_slice_head(evo_context *context, size_t row_begin, size_t rows,
+                                       const void **device_logits_out) {
+  return slice_call(context, [&](evob::Context &c) {
+    const int status = c.slice_head(row_begin, rows);
+    if (status == kOk && device_logits_out != nullptr) *device_logits_out = c.device_logits();
+    return status;
+  });
+}
+void *evo_b200_context_slice_hidden(const evo_context *context) {
+  return context == nullptr ? nullptr : context->context->slice_hidden();
 }
 
 }  // extern "C"

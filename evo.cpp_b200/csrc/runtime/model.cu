@@ -202,7 +202,7 @@ int Context::create(std::shared_ptr<ModelWeights> weights, const std::size_t con
       }
       EVOB_TRY(stage->allocate(&p, 3 * D * (c.short_taps - 1) * 4, cache));
       state.short_cache = static_cast<float *>(p);
-      if (weights->stages.size() > 1) {
+      if (weights->stages.size() > 1 || weights->slice_count > 1) {
         const std::size_t taps = type == MixerType::kHcs ? c.hcs_taps
                                  : type == MixerType::kHcm ? c.hcm_taps : 1;
         // the fused kernels stage a 16-row-aligned halo plus the featurizer's two rows
@@ -575,6 +575,8 @@ int Context::forward(const std::uint32_t *host_tokens, const std::uint32_t *devi
                      const long capture_layer, std::vector<float> *captured) {
   const ModelConfig &c = weights_->config;
   if (!healthy_) return fail(kInvalidArgument, "context was invalidated by an earlier failure");
+  if (weights_->slice_count > 1)
+    return fail(kInvalidArgument, "this model holds one pipeline slice: drive it with the slice calls");
   if (rows == 0 || rows > arena_rows_)
     return fail(kInvalidArgument, "model forward arguments are invalid");
   const bool initial = mode == Mode::kPrefill || mode == Mode::kStateless || mode == Mode::kCachedPrefill;
@@ -673,6 +675,66 @@ int Context::forward(const std::uint32_t *host_tokens, const std::uint32_t *devi
   state_valid_ = !stateless;
   if (initial) cached_attention_ = mode == Mode::kCachedPrefill;
   return kOk;
+}
+
+void *Context::slice_hidden() const { return stages_.front()->hidden; }
+
+int Context::slice_embed(const std::uint32_t *device_tokens, const std::size_t row_begin,
+                         const std::size_t rows) {
+  Stage &stage = *stages_.front();
+  if (!healthy_) return fail(kInvalidArgument, "context was invalidated by an earlier failure");
+  if (device_tokens == nullptr || rows == 0 || row_begin + rows > arena_rows_ ||
+      stage.weights->embedding == nullptr || stage.weights->layer_begin != 0)
+    return fail(kInvalidArgument, "slice_embed needs the first slice, a token buffer and rows inside the arena");
+  DeviceGuard guard(stage.device);
+  return embedding(device_tokens, stage.weights->embedding, rows, weights_->config.width,
+                   static_cast<unsigned char *>(stage.hidden) + row_begin * weights_->config.width * 2,
+                   stage.stream);
+}
+
+int Context::slice_run(const std::size_t row_begin, const std::size_t rows) {
+  const ModelConfig &c = weights_->config;
+  Stage &stage = *stages_.front();
+  if (!healthy_) return fail(kInvalidArgument, "context was invalidated by an earlier failure");
+  if (stages_.size() != 1 || weights_->slice_count < 2)
+    return fail(kInvalidArgument, "slice_run needs a model loaded as one slice of a pipeline");
+  if (rows == 0 || row_begin + rows > arena_rows_ || row_begin + rows > context_size_ ||
+      (row_begin != 0 && row_begin != position_))
+    return fail(kInvalidArgument, "slice windows must be contiguous, ascending and inside the arena");
+  DeviceGuard guard(stage.device);
+  state_valid_ = false;  // decode across processes is not provided
+  stage.shift_rows(static_cast<long>(row_begin), c.width, c.inner_width);
+  const int status = run_stage(stage, rows, Mode::kWindow, -1, nullptr, row_begin);
+  stage.shift_rows(-static_cast<long>(row_begin), c.width, c.inner_width);
+  if (status != kOk) {
+    healthy_ = false;
+    return status;
+  }
+  position_ = row_begin + rows;
+  return kOk;
+}
+
+int Context::slice_head(const std::size_t row_begin, const std::size_t rows) {
+  const ModelConfig &c = weights_->config;
+  Stage &stage = *stages_.front();
+  if (!healthy_) return fail(kInvalidArgument, "context was invalidated by an earlier failure");
+  if (rows == 0 || row_begin + rows > arena_rows_ || stage.weights->embedding == nullptr ||
+      stage.weights->layer_end != c.layers)
+    return fail(kInvalidArgument, "slice_head needs the last slice and rows inside the arena");
+  DeviceGuard guard(stage.device);
+  unsigned char *const hidden = static_cast<unsigned char *>(stage.hidden) + row_begin * c.width * 2;
+  unsigned char *const normalized = static_cast<unsigned char *>(stage.normalized) + row_begin * c.width * 2;
+  int status = rms_norm(hidden, stage.weights->final_norm, rows, c.width, c.epsilon, normalized, nullptr,
+                        1.0F, stage.stream);
+  if (status != kOk) return status;
+  LinearArgs a;
+  a.input = normalized;
+  a.weight = stage.weights->embedding;  // tied head
+  a.output = static_cast<unsigned char *>(stage.logits) + row_begin * c.vocab * 2;
+  a.rows = rows;
+  a.in_features = c.width;
+  a.out_features = c.vocab;
+  return linear(a, stage.stream);
 }
 
 int Context::prefill(const std::vector<std::uint32_t> &tokens, std::vector<float> *logits) {

@@ -75,8 +75,8 @@ struct StageWeights {
   int device = 0;
   std::size_t layer_begin = 0, layer_end = 0;
   std::vector<LayerWeights> layers;
-  const void *embedding = nullptr;    // stage 0 only
-  const float *final_norm = nullptr;  // stage 0 only
+  const void *embedding = nullptr;    // stage 0 (and the last slice of a per-process pipeline)
+  const float *final_norm = nullptr;  // same
   void *slab = nullptr;
   std::size_t slab_bytes = 0, weight_bytes = 0;
   ~StageWeights();
@@ -85,6 +85,9 @@ struct StageWeights {
 struct ModelWeights {
   ModelConfig config;
   std::vector<std::shared_ptr<StageWeights>> stages;
+  // Per-process pipelines: this process holds stage `slice_index` of
+  // `slice_count` (one StageWeights); 0 / 1 for a model held by one process.
+  std::size_t slice_index = 0, slice_count = 1;
 };
 
 struct StageAssignment {
@@ -100,7 +103,8 @@ std::vector<std::pair<std::size_t, std::size_t>> plan_stages(
 
 int load_weights(const ModelFile &file, const std::vector<int> &devices,
                  bool allow_test_fixture, std::size_t layer_limit,
-                 std::shared_ptr<ModelWeights> *out);
+                 std::shared_ptr<ModelWeights> *out, std::size_t slice_index = 0,
+                 std::size_t slice_count = 1);
 
 class Context {
  public:
@@ -124,6 +128,20 @@ class Context {
   int prefill_device(const std::uint32_t *device_tokens, std::size_t rows, bool stateless);
   const void *device_logits() const;
   void *first_stream() const;
+
+  // ---- one stage of a pipeline spread over processes (slice_count > 1).
+  // The launcher moves hidden rows between processes (NCCL send/recv straight
+  // from / into slice_hidden()); each call below enqueues on the stage stream
+  // and returns.  Rows are produced window by window in ascending order:
+  //   slice 0:      slice_embed(tokens, b, n); slice_run(b, n); send rows
+  //   slice i:      receive rows; slice_run(b, n); send rows
+  //   last slice:   receive rows; slice_run(b, n); ... slice_head(0, total)
+  int slice_embed(const std::uint32_t *device_tokens, std::size_t row_begin, std::size_t rows);
+  int slice_run(std::size_t row_begin, std::size_t rows);
+  int slice_head(std::size_t row_begin, std::size_t rows);
+  void *slice_hidden() const;  // [activation_capacity, width] BF16
+  std::size_t slice_index() const { return weights_->slice_index; }
+  std::size_t slice_count() const { return weights_->slice_count; }
   // Waits for every stage stream and surfaces asynchronous kernel errors.
   int synchronize();
   // Per-operator timing (CUDA events around every launch; adds a few

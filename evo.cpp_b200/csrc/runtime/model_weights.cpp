@@ -210,8 +210,13 @@ StageWeights::~StageWeights() {
 
 int load_weights(const ModelFile &file, const std::vector<int> &devices,
                  const bool allow_test_fixture, const std::size_t layer_limit,
-                 std::shared_ptr<ModelWeights> *out) {
+                 std::shared_ptr<ModelWeights> *out, const std::size_t slice_index,
+                 const std::size_t slice_count) {
   if (out == nullptr) return fail(kInvalidArgument, "model output is null");
+  const bool sliced = slice_count > 1;
+  if (slice_count == 0 || slice_count > 8 || slice_index >= slice_count ||
+      (sliced && devices.size() != 1))
+    return fail(kInvalidArgument, "a pipeline slice is one of 1..8 stages on exactly one device");
   if (devices.empty() || devices.size() > 8)
     return fail(kInvalidArgument, "the layer pipeline takes 1 to 8 CUDA devices");
   int device_count = 0;
@@ -229,7 +234,8 @@ int load_weights(const ModelFile &file, const std::vector<int> &devices,
   if (status != kOk) return status;
   ModelConfig &c = weights->config;
   const std::size_t layers = layer_limit == 0 ? c.layers : layer_limit;
-  if (layers > c.layers || layers < devices.size())
+  const std::size_t stage_count = sliced ? slice_count : devices.size();
+  if (layers > c.layers || layers < stage_count)
     return fail(kInvalidArgument, "CUDA layer limit must cover at least one layer per device");
 
   // exact tensor set
@@ -251,14 +257,19 @@ int load_weights(const ModelFile &file, const std::vector<int> &devices,
     if (expected_names.count(view.name) == 0)
       return fail(kModelFormat, "artifact holds an unexpected tensor: " + view.name);
 
-  const auto plan = plan_stages(layer_bytes, devices.size(), c.test_fixture);
-  if (plan.size() != devices.size()) return fail(kInternal, "stage planning failed");
+  const auto plan = plan_stages(layer_bytes, stage_count, c.test_fixture);
+  if (plan.size() != stage_count) return fail(kInternal, "stage planning failed");
+  weights->slice_index = slice_index;
+  weights->slice_count = slice_count;
   int previous_device = 0;
   cudaGetDevice(&previous_device);
   std::vector<unsigned char> host_scratch;
-  for (std::size_t s = 0; s < devices.size() && status == kOk; ++s) {
+  for (std::size_t s = 0; s < stage_count && status == kOk; ++s) {
+    if (sliced && s != slice_index) continue;
     auto stage = std::make_shared<StageWeights>();
-    stage->device = devices[s];
+    stage->device = sliced ? devices[0] : devices[s];
+    // the tied head runs where the last block runs
+    const bool holds_embedding = s == 0 || (sliced && s + 1 == stage_count);
     stage->layer_begin = plan[s].first;
     stage->layer_end = plan[s].second;
     stage->layers.resize(stage->layer_end - stage->layer_begin);
@@ -279,7 +290,7 @@ int load_weights(const ModelFile &file, const std::vector<int> &devices,
           break;
         }
       }
-      if (s == 0) {
+      if (holds_embedding) {
         const void *p = nullptr;
         status = up.tensor(*embedding, &stage->embedding);
         if (status == kOk) status = up.tensor(*norm, &p);
@@ -298,7 +309,7 @@ int load_weights(const ModelFile &file, const std::vector<int> &devices,
         cudaStreamDestroy(up.stream);
       }
     }
-    stage->weight_bytes = (s == 0 ? embedding->bytes + unembed->bytes + norm->bytes : 0);
+    stage->weight_bytes = (holds_embedding ? embedding->bytes + unembed->bytes + norm->bytes : 0);
     for (const LayerWeights &w : stage->layers) stage->weight_bytes += w.payload_bytes;
     weights->stages.push_back(std::move(stage));
   }

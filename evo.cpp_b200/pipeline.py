@@ -1,0 +1,128 @@
+"""Layer pipeline with one stage per process (torchrun: one rank per GPU).
+
+Rank r holds stage r of the byte-balanced split of the blocks
+(``evo_b200_model_load_slice``).  A prompt moves through the stages as a chunk
+wavefront: rank r receives the hidden rows of window j from rank r-1, runs its
+blocks over them, and sends them on while rank r-1 already works on window
+j+1.  That is legal because every mixer is causal and carries its state from
+window to window.  The hand-off is ``torch.distributed`` point-to-point
+(NCCL over NVLink on GPUs; gloo in the CPU tests of this schedule): receives
+are ordered on the stage's compute stream, sends are asynchronous so a stage
+never waits for its successor unless it is about to overwrite rows still in
+flight.
+
+Upstream runs the same stage plan inside one process and hands the whole
+sequence from device to device (src/cuda/model.cu:3148-3212); the wavefront is
+this implementation's addition.
+"""
+from __future__ import annotations
+
+from typing import Protocol
+
+
+def window_plan(rows: int, stages: int, chunk: int = 0) -> list[tuple[int, int]]:
+    """[(begin, count)] windows of one prompt: about two windows per stage so the
+    pipeline fills, each a multiple of 256 rows in [512, 2048] so the
+    tensor-core tiles stay full.  Matches the in-process wavefront of the
+    runtime library."""
+    if rows <= 0 or stages <= 0:
+        raise ValueError("rows and stages must be positive")
+    if chunk <= 0:
+        chunk = (rows // (2 * stages) + 255) // 256 * 256
+        chunk = max(512, min(chunk, 2048))
+    return [(begin, min(chunk, rows - begin)) for begin in range(0, rows, chunk)]
+
+
+class Stage(Protocol):
+    """What the schedule needs from the local stage (all calls enqueue work)."""
+
+    def embed(self, begin: int, count: int) -> None: ...   # first stage: tokens -> hidden rows
+    def run(self, begin: int, count: int) -> None: ...     # this stage's blocks over hidden rows
+    def head(self, rows: int) -> None: ...                 # last stage: final norm + logits
+
+
+class StagePipeline:
+    """Drives one rank's part of the wavefront.
+
+    ``hidden`` is a [capacity, width] tensor aliasing the stage's hidden-row
+    buffer; windows are sent from and received into its row slices directly.
+    """
+
+    def __init__(self, stage: Stage, hidden, rank: int, world: int, group=None, chunk: int = 0):
+        if not 0 <= rank < world:
+            raise ValueError("rank outside the pipeline")
+        self.stage, self.hidden, self.rank, self.world = stage, hidden, rank, world
+        self.group, self.chunk = group, chunk
+        self.in_flight: dict[int, object] = {}   # window begin -> pending send of those rows
+        self.last_rows = None
+
+    def step(self, rows: int) -> None:
+        """One prompt of `rows` tokens through this rank's stage."""
+        import torch.distributed as dist
+
+        if rows > self.hidden.shape[0]:
+            raise ValueError("prompt exceeds the hidden-row capacity")
+        if rows != self.last_rows:
+            self.drain()       # a different window layout: nothing may still be in flight
+            self.last_rows = rows
+        for begin, count in window_plan(rows, self.world, self.chunk):
+            pending = self.in_flight.pop(begin, None)
+            if pending is not None:
+                pending.wait()  # these rows are about to be overwritten
+            window = self.hidden[begin:begin + count]
+            if self.rank == 0:
+                self.stage.embed(begin, count)
+            else:
+                dist.recv(window, src=self._peer(self.rank - 1), group=self.group)
+            self.stage.run(begin, count)
+            if self.rank + 1 < self.world:
+                self.in_flight[begin] = dist.isend(window, dst=self._peer(self.rank + 1), group=self.group)
+        if self.rank + 1 == self.world:
+            self.stage.head(rows)
+
+    def drain(self) -> None:
+        for pending in self.in_flight.values():
+            pending.wait()
+        self.in_flight.clear()
+
+    def _peer(self, pipeline_rank: int) -> int:
+        import torch.distributed as dist
+
+        if self.group is None:
+            return pipeline_rank
+        return dist.get_global_rank(self.group, pipeline_rank)
+
+
+class DeviceRows:
+    """CUDA-array-interface view of a BF16 [rows, width] device buffer owned by
+    the runtime library, so torch can alias it without a copy."""
+
+    def __init__(self, address: int, rows: int, width: int):
+        self.__cuda_array_interface__ = {"shape": (rows, width), "typestr": "<i2", "data": (address, False),
+                                         "version": 2, "strides": None}
+
+
+def alias_hidden_rows(context, rows: int, width: int, device):
+    """torch BF16 [rows, width] tensor over the context's hidden-row buffer."""
+    import torch
+
+    raw = torch.as_tensor(DeviceRows(context.slice_hidden(), rows, width), device=device)
+    return raw.view(torch.bfloat16)
+
+
+class ContextStage:
+    """`Stage` over a sliced runtime context; `tokens` is a device int32/uint32
+    tensor holding the prompt (used by the first stage only)."""
+
+    def __init__(self, context, tokens=None):
+        self.context, self.tokens = context, tokens
+        self.logits_address = None
+
+    def embed(self, begin: int, count: int) -> None:
+        self.context.slice_embed(self.tokens.data_ptr() + 4 * begin, begin, count)
+
+    def run(self, begin: int, count: int) -> None:
+        self.context.slice_run(begin, count)
+
+    def head(self, rows: int) -> None:
+        self.logits_address = self.context.slice_head(0, rows)

@@ -105,6 +105,13 @@ class EvoLibrary:
                                                           ctypes.POINTER(ctypes.c_uint64), Z]
             lib.evo_b200_profile_category_name.restype = ctypes.c_char_p
             lib.evo_b200_profile_category_name.argtypes = [Z]
+            lib.evo_b200_model_load_slice.argtypes = [ctypes.c_char_p, ctypes.c_int32, Z, Z,
+                                                      ctypes.c_uint32, ctypes.POINTER(V)]
+            lib.evo_b200_context_slice_embed.argtypes = [V, V, Z, Z]
+            lib.evo_b200_context_slice_run.argtypes = [V, Z, Z]
+            lib.evo_b200_context_slice_head.argtypes = [V, Z, Z, ctypes.POINTER(V)]
+            lib.evo_b200_context_slice_hidden.restype = V
+            lib.evo_b200_context_slice_hidden.argtypes = [V]
 
     def check(self, status: int) -> None:
         if status != 0:
@@ -121,6 +128,13 @@ class EvoLibrary:
             params.device_count = len(devices)
         handle = ctypes.c_void_p()
         self.check(self.lib.evo_model_load(str(path).encode(), ctypes.byref(params), ctypes.byref(handle)))
+        return Model(self, handle)
+
+    def load_slice(self, path, device: int, slice_index: int, slice_count: int, flags=0) -> "Model":
+        """Stage `slice_index` of a `slice_count`-process layer pipeline on `device`."""
+        handle = ctypes.c_void_p()
+        self.check(self.lib.evo_b200_model_load_slice(str(path).encode(), device, slice_index, slice_count,
+                                                      flags, ctypes.byref(handle)))
         return Model(self, handle)
 
 
@@ -245,6 +259,21 @@ class Context:
         lib.evo_b200_context_profile_read(self.handle, ms, launches, count)
         return {lib.evo_b200_profile_category_name(i).decode(): (ms[i], int(launches[i]))
                 for i in range(count)}
+
+    def slice_embed(self, device_tokens: int, row_begin: int, rows: int) -> None:
+        self.library.check(self.library.lib.evo_b200_context_slice_embed(self.handle, device_tokens, row_begin, rows))
+
+    def slice_run(self, row_begin: int, rows: int) -> None:
+        self.library.check(self.library.lib.evo_b200_context_slice_run(self.handle, row_begin, rows))
+
+    def slice_head(self, row_begin: int, rows: int) -> int:
+        out = ctypes.c_void_p()
+        self.library.check(self.library.lib.evo_b200_context_slice_head(self.handle, row_begin, rows,
+                                                                        ctypes.byref(out)))
+        return out.value
+
+    def slice_hidden(self) -> int:
+        return self.library.lib.evo_b200_context_slice_hidden(self.handle)
 
     def stages(self) -> list[StageInfo]:
         lib = self.library.lib

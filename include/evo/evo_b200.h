@@ -58,6 +58,40 @@ EVO_API size_t evo_b200_context_stage_count(const evo_context *context);
 EVO_API evo_status evo_b200_context_stage_info(const evo_context *context, size_t index,
                                                evo_b200_stage_info *info);
 
+
+/* ---- one pipeline stage per process (torchrun / MPI style launchers).
+ * Upstream runs its layer pipeline inside one process
+ * (src/cuda/model.cu:2419-2469 plans the stages, :3148-3212 hands the hidden
+ * rows from device to device); these calls expose one stage of the same plan
+ * so that each process owns one GPU and the launcher moves the hidden rows
+ * (NCCL send/recv or any peer copy) between them.
+ *
+ * evo_b200_model_load_slice loads stage `slice_index` of the `slice_count`-way
+ * split of the artifact onto `device` (the first slice also holds the
+ * embedding, the last slice the tied head and final norm).  A context of such a
+ * model serves windowed prefills only: whole-model calls are refused.
+ *
+ * Per window of rows [row_begin, row_begin + rows), in ascending contiguous
+ * order starting at 0, all enqueued on evo_b200_context_stream():
+ *   first slice:  slice_embed(tokens) -> slice_run -> send hidden rows
+ *   middle:       receive hidden rows -> slice_run -> send hidden rows
+ *   last slice:   receive hidden rows -> slice_run; after the last window
+ *                 slice_head(0, total) leaves BF16 logits [total, vocab] on
+ *                 the device.
+ * evo_b200_context_slice_hidden is the [activation rows, width] BF16 buffer
+ * the rows are read from and received into (row r at byte r * width * 2).
+ * slice_embed's device_tokens points at the ids of the window (rows uint32). */
+EVO_API evo_status evo_b200_model_load_slice(const char *path, int32_t device, size_t slice_index,
+                                             size_t slice_count, uint32_t flags,
+                                             evo_model **model_out);
+EVO_API evo_status evo_b200_context_slice_embed(evo_context *context,
+                                                const uint32_t *device_tokens, size_t row_begin,
+                                                size_t rows);
+EVO_API evo_status evo_b200_context_slice_run(evo_context *context, size_t row_begin, size_t rows);
+EVO_API evo_status evo_b200_context_slice_head(evo_context *context, size_t row_begin, size_t rows,
+                                               const void **device_logits_out);
+EVO_API void *evo_b200_context_slice_hidden(const evo_context *context);
+
 #ifdef __cplusplus
 }
 #endif
