@@ -61,6 +61,79 @@ __global__ void split_rope_append_kernel(
   }
 }
 
+// Vectorised form: a thread owns 8 rotation pairs (two 16-byte runs) of
+// kHeads consecutive heads of one token, so the sines and cosines - which do
+// not depend on the head - are computed once per kHeads heads and every
+// access is a 128-bit one.  Same expressions as the scalar kernel above.
+template <int kHeads>
+__global__ void __launch_bounds__(256)
+split_rope_append_vec_kernel(const bf16 *__restrict__ qkv, const float *__restrict__ inverse_frequency,
+                             bf16 *__restrict__ query, bf16 *__restrict__ key_cache,
+                             bf16 *__restrict__ value_cache, const std::size_t rows,
+                             const std::size_t heads, const std::size_t head_dim,
+                             const std::size_t position_offset, const float position_scale,
+                             const bool head_major) {
+  const std::size_t half = head_dim / 2;
+  const std::size_t width = heads * head_dim;
+  const std::size_t groups = half / 8;
+  const std::size_t head_blocks = heads / kHeads;
+  const std::size_t total = rows * head_blocks * groups;
+  const std::size_t stride = static_cast<std::size_t>(blockDim.x) * gridDim.x;
+  for (std::size_t i = static_cast<std::size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+       i += stride) {
+    const std::size_t pair = (i % groups) * 8;
+    const std::size_t head_block = (i / groups) % head_blocks;
+    const std::size_t token = i / (groups * head_blocks);
+    const float position = static_cast<float>(position_offset + token) / position_scale;
+    float sine[8], cosine[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      sincosf(position * inverse_frequency[pair + j], &sine[j], &cosine[j]);
+      sine[j] = rbf(sine[j]);
+      cosine[j] = rbf(cosine[j]);
+    }
+    const bf16 *const source = qkv + token * width * 3;
+    const auto rotate = [&](const Bf16x8 &low, const Bf16x8 &high, bf16 *const out) {
+      uint4 first, second;
+      unsigned int *const f = &first.x, *const g = &second.x;
+#pragma unroll
+      for (int j = 0; j < 8; j += 2) {
+        const float a0 = low.get(j), b0 = high.get(j), a1 = low.get(j + 1), b1 = high.get(j + 1);
+        f[j / 2] = pack_bf16x2(a0 * cosine[j] - b0 * sine[j], a1 * cosine[j + 1] - b1 * sine[j + 1]);
+        g[j / 2] = pack_bf16x2(b0 * cosine[j] + a0 * sine[j], b1 * cosine[j + 1] + a1 * sine[j + 1]);
+      }
+      *reinterpret_cast<uint4 *>(out + pair) = first;
+      *reinterpret_cast<uint4 *>(out + half + pair) = second;
+    };
+#pragma unroll
+    for (int h = 0; h < kHeads; ++h) {
+      const std::size_t head = head_block * kHeads + h;
+      std::size_t q_at, k_at, v_at;
+      if (head_major) {
+        q_at = head * 3 * head_dim;
+        k_at = q_at + head_dim;
+        v_at = k_at + head_dim;
+      } else {
+        q_at = head * head_dim;
+        k_at = width + q_at;
+        v_at = 2 * width + q_at;
+      }
+      Bf16x8 q_low, q_high, k_low, k_high;
+      q_low.raw = *reinterpret_cast<const uint4 *>(source + q_at + pair);
+      q_high.raw = *reinterpret_cast<const uint4 *>(source + q_at + half + pair);
+      k_low.raw = *reinterpret_cast<const uint4 *>(source + k_at + pair);
+      k_high.raw = *reinterpret_cast<const uint4 *>(source + k_at + half + pair);
+      const uint4 v_low = *reinterpret_cast<const uint4 *>(source + v_at + pair);
+      const uint4 v_high = *reinterpret_cast<const uint4 *>(source + v_at + half + pair);
+      const std::size_t cache = (position_offset + token) * width + head * head_dim;
+      rotate(q_low, q_high, query + token * width + head * head_dim);
+      rotate(k_low, k_high, key_cache + cache);
+      *reinterpret_cast<uint4 *>(value_cache + cache + pair) = v_low;
+      *reinterpret_cast<uint4 *>(value_cache + cache + half + pair) = v_high;
+    }
+  }
+}
+
 constexpr int kRowThreads = 128;
 
 __device__ __forceinline__ float block_reduce(float value, float *scratch,
@@ -177,9 +250,22 @@ int split_rope_append(const void *qkv, const float *inverse_frequency,
   if (position_offset + rows > cache_capacity)
     return fail(kInvalidArgument, "KV cache capacity exceeded");
   if (rows == 0) return kOk;
+  const std::size_t cap = static_cast<std::size_t>(kSmCount) * 16;
+  const auto aligned = [](const void *p) { return reinterpret_cast<std::uintptr_t>(p) % 16 == 0; };
+  if (head_dim % 16 == 0 && aligned(qkv) && aligned(query) && aligned(key_cache) && aligned(value_cache)) {
+    const bool four = heads % 4 == 0;
+    const std::size_t threads = rows * (heads / (four ? 4 : 1)) * (head_dim / 16);
+    const std::size_t wanted = (threads + 255) / 256;
+    const unsigned int grid = static_cast<unsigned int>(wanted > cap ? cap : wanted);
+    const auto kernel = four ? split_rope_append_vec_kernel<4> : split_rope_append_vec_kernel<1>;
+    kernel<<<grid, 256, 0, stream>>>(static_cast<const bf16 *>(qkv), inverse_frequency,
+                                     static_cast<bf16 *>(query), static_cast<bf16 *>(key_cache),
+                                     static_cast<bf16 *>(value_cache), rows, heads, head_dim,
+                                     position_offset, position_scale, head_major);
+    return check_launch("QKV split/RoPE/append kernel");
+  }
   const std::size_t elements = rows * heads * (head_dim / 2);
   const std::size_t blocks = (elements + 255) / 256;
-  const std::size_t cap = static_cast<std::size_t>(kSmCount) * 16;
   split_rope_append_kernel<<<static_cast<unsigned int>(blocks > cap ? cap : blocks),
                              256, 0, stream>>>(
       static_cast<const bf16 *>(qkv), inverse_frequency,

@@ -5,10 +5,10 @@
 //
 //  phase A  A 64-channel x (TT + halo) time tile of u = bf16(x1*v) and a
 //           64 x TT tile of the x2 gate are built in shared memory with 128-bit
-//           global loads.  When fed by the raw interleaved projection each
-//           thread walks consecutive rows of one 8-channel chunk with the two
-//           previous rows held in registers, so the 3-tap featurizer costs one
-//           48-byte load per row and chunk instead of three.
+//           global loads.  When fed by the raw interleaved projection, its
+//           columns of the tile are staged through shared memory in 32-row slabs
+//           with cp.async (double buffered) and the 3-tap featurizer runs from
+//           there, one (row, 8-channel chunk) per thread.
 //  phase B  HCS and every odd configuration: CUDA-core FMAs, oldest tap first,
 //           bit-identical to the generic kernel and to upstream's direct FIR.
 //           HCM with BF16 filters shared by groups of 16k channels: the
@@ -65,12 +65,39 @@ __device__ __forceinline__ float element(const std::uint32_t (&words)[N], const 
   return (i & 1) ? hi(words[i >> 1]) : lo(words[i >> 1]);
 }
 
-__device__ __forceinline__ void load48(const bf16 *p, std::uint32_t (&w)[12]) {
+constexpr int kSlabRows = kThreads / kChunks;       // 32 featurized rows per slab
+constexpr int kRawRowBytes = kChannels * 3 * 2;     // 384: the tile's columns of one projection row
+constexpr int kRawSlabBytes = (kSlabRows + 2) * kRawRowBytes;
+constexpr int kRawBytes = 2 * kRawSlabBytes;        // double buffer
+
+__device__ __forceinline__ void load48_shared(const unsigned char *p, std::uint32_t (&w)[12]) {
   const uint4 *v = reinterpret_cast<const uint4 *>(p);
-  const uint4 a = __ldg(v), b = __ldg(v + 1), c = __ldg(v + 2);
+  const uint4 a = v[0], b = v[1], c = v[2];
   w[0] = a.x; w[1] = a.y; w[2] = a.z; w[3] = a.w;
   w[4] = b.x; w[5] = b.y; w[6] = b.z; w[7] = b.w;
   w[8] = c.x; w[9] = c.y; w[10] = c.z; w[11] = c.w;
+}
+
+// Starts the copy of projection rows [t_first, t_first + kSlabRows + 2) x the
+// tile's 192 columns into `slab`; rows outside [0, length) and columns beyond
+// the width arrive as zeros.  One commit group per call.
+__device__ __forceinline__ void issue_raw_slab(const Params &p, unsigned char *slab, const int t_first,
+                                               const int c_tile) {
+  const std::size_t width3 = static_cast<std::size_t>(p.width) * 3;
+  const std::size_t column0 = static_cast<std::size_t>(c_tile) * 3;
+  for (int item = threadIdx.x; item < (kSlabRows + 2) * 24; item += kThreads) {
+    const int j = item / 24, chunk = item % 24;
+    const int t = t_first + j;
+    const std::size_t column = column0 + chunk * 8;
+    const bool valid = t >= 0 && t < p.length && column + 8 <= width3;
+    const bf16 *const source = valid ? p.projection + static_cast<std::size_t>(t) * width3 + column : p.projection;
+    const std::uint32_t destination =
+        static_cast<std::uint32_t>(__cvta_generic_to_shared(slab + j * kRawRowBytes + chunk * 16));
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(destination), "l"(source),
+                 "r"(valid ? 16U : 0U)
+                 : "memory");
+  }
+  asm volatile("cp.async.commit_group;" ::: "memory");
 }
 
 // Builds u rows [0, rows) (tile row r <-> time t_first + r) and, for tile rows
@@ -78,7 +105,7 @@ __device__ __forceinline__ void load48(const bf16 *p, std::uint32_t (&w)[12]) {
 // and the F32 decode history for rows this CTA owns (t >= t_own).
 template <bool kProj>
 __device__ __forceinline__ void build_tiles(const Params &p, unsigned char *u_tile,
-                                            unsigned char *x2_tile, const int rows,
+                                            unsigned char *x2_tile, unsigned char *raw, const int rows,
                                             const int t_first, const int gate_first_row,
                                             const int t_own, const int c_tile) {
   const int chunk = threadIdx.x % kChunks;
@@ -135,14 +162,12 @@ __device__ __forceinline__ void build_tiles(const Params &p, unsigned char *u_ti
       emit(r, t, u, g, have_gate);
     }
   } else {
-    // 8 chunks x 32 row segments; each thread walks its segment in time order.
-    constexpr int kSegments = kThreads / kChunks;
-    const int segment = threadIdx.x / kChunks;
-    const int per_segment = (rows + kSegments - 1) / kSegments;
-    const int r_begin = segment * per_segment;
-    const int r_end = min(rows, r_begin + per_segment);
-    if (r_begin >= r_end) return;
-    const std::size_t width3 = static_cast<std::size_t>(p.width) * 3;
+    // The raw projection columns of the tile (64 channels x 3 streams = 384
+    // contiguous bytes per row) are staged through shared memory in slabs of
+    // kSlabRows rows with cp.async, double buffered, so the global loads of the
+    // next slab are in flight while this one is featurized and no thread ever
+    // waits on its own loads.  One (row, 8-channel chunk) item per thread.
+    const int item_row = threadIdx.x / kChunks;
     std::uint32_t weights[36];  // 24 streams x 3 taps, packed BF16 pairs
     if (channel_ok) {
       const uint4 *w = reinterpret_cast<const uint4 *>(p.short_filter + static_cast<std::size_t>(c0) * 9);
@@ -152,46 +177,48 @@ __device__ __forceinline__ void build_tiles(const Params &p, unsigned char *u_ti
         weights[4 * i] = v.x; weights[4 * i + 1] = v.y; weights[4 * i + 2] = v.z; weights[4 * i + 3] = v.w;
       }
     }
-    std::uint32_t prev2[12] = {}, prev1[12] = {}, current[12];
-    auto fetch = [&](const int t, std::uint32_t (&row)[12]) {
-      if (channel_ok && t >= 0 && t < p.length)
-        load48(p.projection + static_cast<std::size_t>(t) * width3 + static_cast<std::size_t>(c0) * 3, row);
-      else {
-#pragma unroll
-        for (int i = 0; i < 12; ++i) row[i] = 0U;
+    const int slabs = (rows + kSlabRows - 1) / kSlabRows;
+    issue_raw_slab(p, raw, t_first - 2, c_tile);
+    for (int slab = 0; slab < slabs; ++slab) {
+      unsigned char *const buffer = raw + (slab & 1) * kRawSlabBytes;
+      if (slab + 1 < slabs) {
+        issue_raw_slab(p, raw + ((slab + 1) & 1) * kRawSlabBytes, t_first + (slab + 1) * kSlabRows - 2, c_tile);
+        asm volatile("cp.async.wait_group 1;" ::: "memory");
+      } else {
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
       }
-    };
-    fetch(t_first + r_begin - 2, prev2);
-    fetch(t_first + r_begin - 1, prev1);
-    for (int r = r_begin; r < r_end; ++r) {
-      const int t = t_first + r;
-      fetch(t, current);
-      const bool live = channel_ok && t >= 0 && t < p.length;
-      const bool have_gate = r >= gate_first_row;
-      float u[8] = {}, g[8] = {};
-      if (live) {
+      __syncthreads();
+      const int r = slab * kSlabRows + item_row;
+      if (r < rows) {
+        const int t = t_first + r;
+        const bool live = channel_ok && t >= 0 && t < p.length;
+        const bool have_gate = r >= gate_first_row;
+        float u[8] = {}, g[8] = {};
+        if (live) {
+          std::uint32_t prev2[12], prev1[12], current[12];
+          const unsigned char *const base = buffer + item_row * kRawRowBytes + chunk * 48;
+          load48_shared(base, prev2);
+          load48_shared(base + kRawRowBytes, prev1);
+          load48_shared(base + 2 * kRawRowBytes, current);
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          float z[3];
+          for (int i = 0; i < 8; ++i) {
+            float z[3];
 #pragma unroll
-          for (int s = 0; s < 3; ++s) {
-            const int idx = 3 * i + s;
-            float acc = 0.0F;
-            acc = fmaf(element(prev2, idx), element(weights, idx * 3), acc);
-            acc = fmaf(element(prev1, idx), element(weights, idx * 3 + 1), acc);
-            acc = fmaf(element(current, idx), element(weights, idx * 3 + 2), acc);
-            z[s] = rbf(acc);
+            for (int st = 0; st < 3; ++st) {
+              const int idx = 3 * i + st;
+              float acc = 0.0F;
+              acc = fmaf(element(prev2, idx), element(weights, idx * 3), acc);
+              acc = fmaf(element(prev1, idx), element(weights, idx * 3 + 1), acc);
+              acc = fmaf(element(current, idx), element(weights, idx * 3 + 2), acc);
+              z[st] = rbf(acc);
+            }
+            u[i] = rbf(z[1] * z[2]);
+            g[i] = z[0];
           }
-          u[i] = rbf(z[1] * z[2]);
-          g[i] = z[0];
         }
+        emit(r, t, u, g, have_gate);
       }
-      emit(r, t, u, g, have_gate);
-#pragma unroll
-      for (int i = 0; i < 12; ++i) {
-        prev2[i] = prev1[i];
-        prev1[i] = current[i];
-      }
+      __syncthreads();  // the other buffer is refilled at the top of the next round
     }
   }
 }
@@ -216,7 +243,7 @@ __device__ __forceinline__ void store_tile(const Params &p, const unsigned char 
 
 // ------------------------------------------------------------ CUDA cores
 template <bool kProj, int TT>
-__global__ void __launch_bounds__(kThreads)
+__global__ void __launch_bounds__(kThreads, 2)
 gated_fir_simt_kernel(const Params p) {
   extern __shared__ __align__(128) unsigned char smem[];
   const int halo = p.padded_taps - 1;
@@ -241,7 +268,8 @@ gated_fir_simt_kernel(const Params p) {
     }
     h_tile[d * 32 + pair] = h;
   }
-  build_tiles<kProj>(p, u_tile, x2_tile, TT + halo, t0 - halo, halo, t0, c_tile);
+  build_tiles<kProj>(p, u_tile, x2_tile, reinterpret_cast<unsigned char *>(h_tile + p.padded_taps * 32),
+                     TT + halo, t0 - halo, halo, t0, c_tile);
   __syncthreads();
 
   float direct0 = 0.0F, direct1 = 0.0F;
@@ -312,7 +340,7 @@ __device__ __forceinline__ void mma_bf16(float (&d)[4], const std::uint32_t (&a)
 constexpr int kMmaHalo = 128;  // history rows staged before the tile (>= taps-1, 16-aligned)
 
 template <bool kProj, int TT>
-__global__ void __launch_bounds__(kThreads)
+__global__ void __launch_bounds__(kThreads, 2)
 gated_fir_mma_kernel(const Params p) {
   extern __shared__ __align__(128) unsigned char smem[];
   unsigned char *const u_tile = smem;
@@ -335,7 +363,8 @@ gated_fir_mma_kernel(const Params p) {
           p.filter)[static_cast<std::size_t>(channel / p.channels_per_group) * p.taps + d]);
     h_s[i] = bits;
   }
-  build_tiles<kProj>(p, u_tile, x2_tile, TT + kMmaHalo, t0 - kMmaHalo, kMmaHalo, t0, c_tile);
+  build_tiles<kProj>(p, u_tile, x2_tile, reinterpret_cast<unsigned char *>(h_s + 4 * 128),
+                     TT + kMmaHalo, t0 - kMmaHalo, kMmaHalo, t0, c_tile);
   __syncthreads();
 
   // Toeplitz fragments: H[m][k] = h[128 + m - k] over k in [0, 144).
@@ -452,21 +481,24 @@ int gated_fir_prefill(const GatedFirArgs &a, cudaStream_t stream) {
                       p.channels_per_group % 16 == 0;
   if (tensor) {
     constexpr int TT = 256;
-    const std::size_t smem = (TT + kMmaHalo) * kRowBytes + TT * kRowBytes + 4 * 128 * 2;
+    const std::size_t smem = (TT + kMmaHalo) * kRowBytes + TT * kRowBytes + 4 * 128 * 2 +
+                             (from_projection ? kRawBytes : 0);
     status = from_projection
                  ? launch(gated_fir_mma_kernel<true, TT>, p, TT, smem, stream, "fused Toeplitz FIR kernel")
                  : launch(gated_fir_mma_kernel<false, TT>, p, TT, smem, stream, "fused Toeplitz FIR kernel");
   } else if (p.padded_taps <= 32) {
     constexpr int TT = 256;
     const std::size_t smem = (TT + p.padded_taps - 1) * kRowBytes + TT * kRowBytes +
-                             static_cast<std::size_t>(p.padded_taps) * 32 * sizeof(float2);
+                             static_cast<std::size_t>(p.padded_taps) * 32 * sizeof(float2) +
+                             (from_projection ? kRawBytes : 0);
     status = from_projection
                  ? launch(gated_fir_simt_kernel<true, TT>, p, TT, smem, stream, "fused FIR kernel")
                  : launch(gated_fir_simt_kernel<false, TT>, p, TT, smem, stream, "fused FIR kernel");
   } else {
     constexpr int TT = 128;
     const std::size_t smem = (TT + p.padded_taps - 1) * kRowBytes + TT * kRowBytes +
-                             static_cast<std::size_t>(p.padded_taps) * 32 * sizeof(float2);
+                             static_cast<std::size_t>(p.padded_taps) * 32 * sizeof(float2) +
+                             (from_projection ? kRawBytes : 0);
     status = from_projection
                  ? launch(gated_fir_simt_kernel<true, TT>, p, TT, smem, stream, "fused FIR kernel")
                  : launch(gated_fir_simt_kernel<false, TT>, p, TT, smem, stream, "fused FIR kernel");

@@ -319,6 +319,276 @@ __global__ void modal_decode_kernel(const bf16 *__restrict__ x2,
   output[channel] = f2bf(__fmul_rn(bf2f(x2[channel]), mixed));
 }
 
+// ---------------------------------------------------------------- tiled scan
+// The same local / output passes with the inputs staged through shared memory.
+// A CTA owns 64 channels x kLanes consecutive segments and walks them in slabs
+// of kSlab rows: cp.async copies the next slab's rows (double buffered) while
+// the current one is featurized cooperatively with 128-bit accesses - one
+// (segment lane, row, 8-channel chunk) per thread - into packed (u, x2) words;
+// then every thread advances the recurrence of ONE channel of one segment lane
+// over the slab's rows, reading its word per row from shared memory, and the
+// finished rows leave through a shared tile with 128-bit stores.  No thread
+// waits on a global load of its own, and the per-thread state is 3*modes
+// registers instead of 6*modes, which is what lets two CTAs share an SM.
+constexpr int kScanThreads = 256;
+constexpr int kTileChannels = 64;
+constexpr int kLanes = 4;
+constexpr int kSlab = 8;
+constexpr int kProjRowBytes = kTileChannels * 3 * 2;                      // 384
+constexpr int kProjStageBytes = kLanes * (kSlab + 2) * kProjRowBytes;     // 15360
+constexpr int kPlainRowBytes = kTileChannels * 2;                         // 128
+constexpr int kPlainStageBytes = 3 * kLanes * kSlab * kPlainRowBytes;     // 12288
+constexpr int kWordTileBytes = kLanes * kSlab * kTileChannels * 4;        // 8192
+constexpr int kOutTileBytes = kLanes * kSlab * kTileChannels * 2;         // 4096
+constexpr int kWeightBytes = 8 * 36 * 4;                                  // 1152
+
+template <bool kFromProjection>
+constexpr int tiled_smem_bytes() {
+  return 2 * (kFromProjection ? kProjStageBytes : kPlainStageBytes) + kWordTileBytes + kOutTileBytes +
+         (kFromProjection ? kWeightBytes : 0);
+}
+
+__device__ __forceinline__ void async_copy16(void *shared, const void *global, const bool valid) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(
+                   static_cast<std::uint32_t>(__cvta_generic_to_shared(shared))),
+               "l"(global), "r"(valid ? 16U : 0U)
+               : "memory");
+}
+
+// Starts the copies of slab `slab` (rows slab*kSlab .. +kSlab of every segment
+// lane, plus the two featurizer history rows when projection-fed).
+template <bool kFromProjection, bool kNeedGate>
+__device__ __forceinline__ void issue_modal_slab(const ModalParams &p, unsigned char *stage,
+                                                 const int seg0, const int slab, const int c_tile) {
+  if constexpr (kFromProjection) {
+    const std::size_t width3 = static_cast<std::size_t>(p.width) * 3;
+    const std::size_t column0 = static_cast<std::size_t>(c_tile) * 3;
+    for (int item = threadIdx.x; item < kLanes * (kSlab + 2) * 24; item += kScanThreads) {
+      const int chunk = item % 24, j = (item / 24) % (kSlab + 2), lane = item / (24 * (kSlab + 2));
+      const int seg = seg0 + lane;
+      const int t = p.row_begin + seg * p.segment + slab * kSlab + j - 2;
+      const std::size_t column = column0 + chunk * 8;
+      const bool valid = seg < p.segments && t >= 0 && t < p.length && column + 8 <= width3;
+      async_copy16(stage + (lane * (kSlab + 2) + j) * kProjRowBytes + chunk * 16,
+                   valid ? p.projection + static_cast<std::size_t>(t) * width3 + column : p.projection, valid);
+    }
+  } else {
+    constexpr int kStreams = kNeedGate ? 3 : 2;
+    for (int item = threadIdx.x; item < kStreams * kLanes * kSlab * 8; item += kScanThreads) {
+      const int chunk = item % 8, j = (item / 8) % kSlab, lane = (item / (8 * kSlab)) % kLanes;
+      const int stream = item / (8 * kSlab * kLanes);
+      const int seg = seg0 + lane;
+      const int t = p.row_begin + seg * p.segment + slab * kSlab + j;
+      const int channel = c_tile + chunk * 8;
+      const bool valid = seg < p.segments && t < p.length && channel < p.width;
+      const bf16 *const base = stream == 0 ? p.x1 : (stream == 1 ? p.value : p.x2);
+      async_copy16(stage + ((stream * kLanes + lane) * kSlab + j) * kPlainRowBytes + chunk * 16,
+                   valid ? base + static_cast<std::size_t>(t) * p.width + channel : base, valid);
+    }
+  }
+  asm volatile("cp.async.commit_group;" ::: "memory");
+}
+
+template <int kModes, bool kFromProjection, bool kOutput>
+__global__ void __launch_bounds__(kScanThreads, 2)
+modal_tiled_kernel(const ModalParams p) {
+  extern __shared__ __align__(128) unsigned char smem[];
+  constexpr int kStageBytes = kFromProjection ? kProjStageBytes : kPlainStageBytes;
+  unsigned char *const stages = smem;
+  std::uint32_t *const words = reinterpret_cast<std::uint32_t *>(smem + 2 * kStageBytes);
+  unsigned short *const out_tile = reinterpret_cast<unsigned short *>(smem + 2 * kStageBytes + kWordTileBytes);
+  std::uint32_t *const weights =
+      reinterpret_cast<std::uint32_t *>(smem + 2 * kStageBytes + kWordTileBytes + kOutTileBytes);
+  const int seg0 = blockIdx.x * kLanes;
+  const int c_tile = blockIdx.y * kTileChannels;
+  const int lane = threadIdx.x / kTileChannels;  // segment lane of both roles
+
+  // ---- scan role: channel `channel` of segment seg0 + lane
+  const int channel = c_tile + threadIdx.x % kTileChannels;
+  const int seg = seg0 + lane;
+  const bool scans = channel < p.width && seg < p.segments;
+  const int t0 = p.row_begin + seg * p.segment;
+  const int t1 = min(t0 + p.segment, p.length);
+  float pole[kModes], residue[kModes], state[kModes];
+  float direct = 0.0F;
+#pragma unroll
+  for (int m = 0; m < kModes; ++m) {
+    pole[m] = residue[m] = state[m] = 0.0F;
+    if (scans) {
+      const std::size_t q = static_cast<std::size_t>(channel) * kModes + m;
+      pole[m] = expf(p.log_poles[q]);
+      if constexpr (kOutput) {
+        residue[m] = p.residues[q];
+        state[m] = p.scratch[(static_cast<std::size_t>(seg) * p.width + channel) * kModes + m];
+      }
+    }
+  }
+  if constexpr (kOutput)
+    if (scans) direct = bf2f(p.direct[channel]);
+
+  // ---- featurize / store role: row item_row, channels item_c0 .. +8 of the lane
+  const int item_chunk = threadIdx.x % 8;
+  const int item_row = (threadIdx.x / 8) % kSlab;
+  const int item_c0 = c_tile + item_chunk * 8;
+  const bool item_ok = item_c0 < p.width && seg < p.segments;
+  if constexpr (kFromProjection) {
+    if (threadIdx.x < 72) {
+      const int chunk = threadIdx.x / 9, part = threadIdx.x % 9;
+      uint4 v = make_uint4(0U, 0U, 0U, 0U);
+      if (c_tile + chunk * 8 < p.width)
+        v = __ldg(reinterpret_cast<const uint4 *>(p.short_filter +
+                                                  static_cast<std::size_t>(c_tile + chunk * 8) * 9) + part);
+      *reinterpret_cast<uint4 *>(weights + chunk * 36 + part * 4) = v;
+    }
+  }
+  const int slabs = p.segment / kSlab;
+  issue_modal_slab<kFromProjection, kOutput>(p, stages, seg0, 0, c_tile);
+  for (int slab = 0; slab < slabs; ++slab) {
+    const unsigned char *const stage = stages + (slab & 1) * kStageBytes;
+    if (slab + 1 < slabs) {
+      issue_modal_slab<kFromProjection, kOutput>(p, stages + ((slab + 1) & 1) * kStageBytes, seg0, slab + 1,
+                                                 c_tile);
+      asm volatile("cp.async.wait_group 1;" ::: "memory");
+    } else {
+      asm volatile("cp.async.wait_group 0;" ::: "memory");
+    }
+    __syncthreads();
+    {  // featurize one (lane, row, chunk) item into packed words: u low, x2 high
+      float u[8], g[8];
+      if constexpr (kFromProjection) {
+        const unsigned char *const base =
+            stage + (lane * (kSlab + 2) + item_row) * kProjRowBytes + item_chunk * 48;
+        std::uint32_t rows[3][12];
+#pragma unroll
+        for (int r = 0; r < 3; ++r)
+#pragma unroll
+          for (int v = 0; v < 3; ++v) {
+            const uint4 x = *reinterpret_cast<const uint4 *>(base + r * kProjRowBytes + v * 16);
+            rows[r][4 * v] = x.x; rows[r][4 * v + 1] = x.y; rows[r][4 * v + 2] = x.z; rows[r][4 * v + 3] = x.w;
+          }
+        const std::uint32_t *const w = weights + item_chunk * 36;
+        auto value_of = [](const std::uint32_t word, const int index) {
+          return (index & 1) ? __uint_as_float(word & 0xffff0000U) : __uint_as_float(word << 16U);
+        };
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          float z[3];
+#pragma unroll
+          for (int st = kOutput ? 0 : 1; st < 3; ++st) {
+            const int idx = 3 * i + st;
+            float acc = 0.0F;
+#pragma unroll
+            for (int tap = 0; tap < 3; ++tap) {
+              const int wi = idx * 3 + tap;
+              acc = fmaf(value_of(rows[tap][idx >> 1], idx), value_of(w[wi >> 1], wi), acc);
+            }
+            z[st] = rbf(acc);
+          }
+          u[i] = rbf(z[1] * z[2]);
+          g[i] = kOutput ? z[0] : 0.0F;
+        }
+      } else {
+        const unsigned char *const base = stage + (lane * kSlab + item_row) * kPlainRowBytes + item_chunk * 16;
+        Bf16x8 a, b, c;
+        a.raw = *reinterpret_cast<const uint4 *>(base);
+        b.raw = *reinterpret_cast<const uint4 *>(base + kLanes * kSlab * kPlainRowBytes);
+        c.raw = make_uint4(0U, 0U, 0U, 0U);
+        if constexpr (kOutput) c.raw = *reinterpret_cast<const uint4 *>(base + 2 * kLanes * kSlab * kPlainRowBytes);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          u[i] = rbf(a.get(i) * b.get(i));
+          g[i] = c.get(i);
+        }
+      }
+      std::uint32_t packed[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i)
+        packed[i] = (__float_as_uint(u[i]) >> 16U) | (__float_as_uint(g[i]) & 0xffff0000U);
+      uint4 *const destination = reinterpret_cast<uint4 *>(
+          words + (lane * kSlab + item_row) * kTileChannels + item_chunk * 8);
+      destination[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+      destination[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+      if constexpr (kOutput) {
+        const int t = t0 + slab * kSlab + item_row;
+        if (p.pregate != nullptr && item_ok && t < t1)
+          *reinterpret_cast<uint4 *>(p.pregate + static_cast<std::size_t>(t) * p.width + item_c0) =
+              make_uint4((packed[0] & 0xffffU) | (packed[1] << 16U), (packed[2] & 0xffffU) | (packed[3] << 16U),
+                         (packed[4] & 0xffffU) | (packed[5] << 16U), (packed[6] & 0xffffU) | (packed[7] << 16U));
+      }
+    }
+    __syncthreads();
+    if (scans) {
+#pragma unroll
+      for (int r = 0; r < kSlab; ++r) {
+        const int t = t0 + slab * kSlab + r;
+        if (t < t1) {
+          const std::uint32_t word = words[(lane * kSlab + r) * kTileChannels + threadIdx.x % kTileChannels];
+          const float u = __uint_as_float(word << 16U);
+          if constexpr (kOutput) {
+            const float g = __uint_as_float(word & 0xffff0000U);
+            float partial[4] = {0.0F, 0.0F, 0.0F, 0.0F};
+#pragma unroll
+            for (int m = 0; m < kModes; ++m) {
+              state[m] = fmaf(pole[m], state[m], u);
+              partial[m % 4] = fmaf(residue[m], state[m], partial[m % 4]);
+            }
+            const float modal = ((partial[0] + partial[1]) + partial[2]) + partial[3];
+            float result;
+            if (p.continue_from_state)
+              result = g * fmaf(direct, u, modal);
+            else
+              result = rbf(rbf(modal) + rbf(direct * u)) * g;
+            out_tile[(lane * kSlab + r) * kTileChannels + threadIdx.x % kTileChannels] =
+                __bfloat16_as_ushort(__float2bfloat16_rn(result));
+          } else {
+#pragma unroll
+            for (int m = 0; m < kModes; ++m) state[m] = fmaf(pole[m], state[m], u);
+          }
+        }
+      }
+    }
+    if constexpr (kOutput) {
+      __syncthreads();
+      const int t = t0 + slab * kSlab + item_row;
+      if (item_ok && t < t1)
+        *reinterpret_cast<uint4 *>(p.output + static_cast<std::size_t>(t) * p.width + item_c0) =
+            *reinterpret_cast<const uint4 *>(out_tile + (lane * kSlab + item_row) * kTileChannels + item_chunk * 8);
+    }
+  }
+  if constexpr (!kOutput) {
+    if (scans) {
+      float *const out = p.scratch + (static_cast<std::size_t>(seg) * p.width + channel) * kModes;
+#pragma unroll
+      for (int m = 0; m < kModes; ++m) out[m] = state[m];
+    }
+  }
+}
+
+bool tiled_scan_applies(const ModalParams &p, const bool from_projection) {
+  const auto aligned = [](const void *q) { return (reinterpret_cast<std::uintptr_t>(q) & 15U) == 0; };
+  if (p.width % 8 != 0 || p.segment % kSlab != 0 || !aligned(p.output) ||
+      (p.pregate != nullptr && !aligned(p.pregate)))
+    return false;
+  return from_projection ? aligned(p.projection) && aligned(p.short_filter)
+                         : aligned(p.x1) && aligned(p.value) && aligned(p.x2);
+}
+
+template <int kModes, bool kFromProjection>
+int launch_tiled(const ModalParams &p, cudaStream_t stream) {
+  constexpr int smem = tiled_smem_bytes<kFromProjection>();
+  static_assert(smem <= 48 * 1024, "the tiled modal scan is sized for the default shared-memory limit");
+  const dim3 grid(ceil_div_u(p.segments, kLanes), ceil_div_u(p.width, kTileChannels));
+  if (grid.y > 65535) return fail(kInvalidArgument, "modal prefill is too wide");
+  modal_tiled_kernel<kModes, kFromProjection, false><<<grid, kScanThreads, smem, stream>>>(p);
+  int status = check_launch("modal segment kernel");
+  if (status != kOk) return status;
+  modal_carry_kernel<<<ceil_div_u(static_cast<std::size_t>(p.width) * kModes, 256), 256, 0, stream>>>(p, kModes);
+  status = check_launch("modal carry kernel");
+  if (status != kOk) return status;
+  modal_tiled_kernel<kModes, kFromProjection, true><<<grid, kScanThreads, smem, stream>>>(p);
+  return check_launch("modal output kernel");
+}
+
 int pick_segment(const std::size_t length, const std::size_t width) {
   // Largest segment that still yields >= ~200k threads; shorter segments cost
   // more carry scratch, longer ones starve the SMs.
@@ -333,6 +603,8 @@ int pick_segment(const std::size_t length, const std::size_t width) {
 template <int kModes>
 int launch_modal(const ModalParams &p, const bool from_projection,
                  cudaStream_t stream) {
+  if (tiled_scan_applies(p, from_projection))
+    return from_projection ? launch_tiled<kModes, true>(p, stream) : launch_tiled<kModes, false>(p, stream);
   const std::size_t threads = static_cast<std::size_t>(p.segments) * p.pairs;
   const unsigned int grid = ceil_div_u(threads, kThreads);
   if (from_projection)

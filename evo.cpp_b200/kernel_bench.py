@@ -120,6 +120,43 @@ def bench_gemm(ops, timer, rows, inner, outer, kind):
     return report(name, ms, flops=flops, rows=rows, inner=inner, outer=outer)
 
 
+def bench_hyena_projection(ops, timer, length, channels, which):
+    """The forms the model runs: fed by the interleaved [length, 3*channels]
+    projection, 3-tap featurizer applied on the fly, decode caches written."""
+    gen = torch.Generator(device="cuda").manual_seed(1)
+    projection = torch.randn(length, 3 * channels, device="cuda", generator=gen).bfloat16()
+    short = (torch.randn(3 * channels, 3, device="cuda", generator=gen) * 0.3).bfloat16()
+    out = torch.empty(length, channels, device="cuda", dtype=torch.bfloat16)
+    short_cache = torch.zeros(3 * channels, 2, device="cuda")
+    groups = max(1, channels // 16)
+    fused_bytes = 8.0 * length * channels
+    lines = []
+    for name, taps, orientation in (("hcs", 7, 0), ("hcm", 128, 1)):
+        if which not in (name, "all"):
+            continue
+        h = (torch.randn(groups, taps, device="cuda", generator=gen) * 0.02).bfloat16()
+        d = (torch.randn(channels, device="cuda", generator=gen) * 0.02).bfloat16() if orientation else None
+        cache = torch.zeros(channels, taps - 1, device="cuda")
+        ms = timer(lambda: ops.call("bf16_projection_gated_fir_prefill", p(projection), p(short), p(h), 0, p(d),
+                                    length, channels, groups, taps, orientation, None, p(cache), p(short_cache),
+                                    p(out), stream()))
+        lines.append(report(f"{name}_projection_fed_k{taps}", ms, bytes_moved=fused_bytes,
+                            flops=2.0 * taps * length * channels, length=length, channels=channels))
+    if which in ("hcl", "all"):
+        modes = 16
+        d = (torch.randn(channels, device="cuda", generator=gen) * 0.02).bfloat16()
+        log_poles = (torch.rand(channels, modes, device="cuda", generator=gen) * 0.099 + 0.9).log().float()
+        residues = (torch.randn(channels, modes, device="cuda", generator=gen) * 0.02).float()
+        scratch = torch.empty(ops.hcl_scratch_floats(length, channels, modes), device="cuda")
+        state = torch.zeros(channels, modes, device="cuda")
+        ms = timer(lambda: ops.call("bf16_projection_hcl_prefill", p(projection), p(short), p(d), p(log_poles),
+                                    p(residues), length, channels, modes, 0, p(state), p(scratch), p(short_cache),
+                                    None, p(out), stream()))
+        lines.append(report("hcl_projection_fed_modal_scan", ms, bytes_moved=fused_bytes,
+                            flops=64.0 * length * channels, length=length, channels=channels))
+    return lines
+
+
 def bench_hyena(ops, timer, length, channels, which):
     gen = torch.Generator(device="cuda").manual_seed(1)
     x2, x1, v = (torch.randn(length, channels, device="cuda", generator=gen).bfloat16() for _ in range(3))
@@ -185,6 +222,8 @@ def main() -> None:
     parser.add_argument("--length", type=int, default=8192)
     parser.add_argument("--channels", type=int, default=4096)
     parser.add_argument("--op", default="all", choices=["hcs", "hcm", "hcl", "all"])
+    parser.add_argument("--fed", default="separate", choices=["separate", "projection"],
+                        help="hyena: separate x2/x1/v inputs, or the interleaved projection as in the model")
     parser.add_argument("--width", type=int, default=4096)
     parser.add_argument("--heads", type=int, default=32)
     parser.add_argument("--iters", type=int, default=10)
@@ -194,7 +233,8 @@ def main() -> None:
     if args.what == "gemm":
         bench_gemm(ops, timer, args.rows, args.inner, args.outer, args.type)
     elif args.what == "hyena":
-        bench_hyena(ops, timer, args.length, args.channels, args.op)
+        (bench_hyena_projection if args.fed == "projection" else bench_hyena)(
+            ops, timer, args.length, args.channels, args.op)
     elif args.what == "norm":
         bench_norm(ops, timer, args.rows, args.width)
     elif args.what == "attention":
