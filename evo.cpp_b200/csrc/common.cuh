@@ -43,7 +43,11 @@ __device__ __forceinline__ bf16 f2bf(const float v) {
 }
 // Round an F32 value to BF16 precision and widen it again.
 __device__ __forceinline__ float rbf(const float v) {
-  return __bfloat162float(__float2bfloat16_rn(v));
+  // one instruction: the packed convert puts bf16(v) in the upper half and
+  // bf16(+0) in the lower half, which is the F32 bit pattern of the result
+  unsigned int bits;
+  asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(bits) : "f"(v), "f"(0.0F));
+  return __uint_as_float(bits);
 }
 __device__ __forceinline__ float bits2f_bf16(const unsigned short bits) {
   return __uint_as_float(static_cast<unsigned int>(bits) << 16U);

@@ -21,6 +21,7 @@
 //           shared memory and stored with 128-bit writes.
 #include "common.cuh"
 #include "ops_internal.hpp"
+#include "projection_featurizer.cuh"
 
 namespace evob {
 namespace {
@@ -69,36 +70,46 @@ constexpr int kSlabRows = kThreads / kChunks;       // 32 featurized rows per sl
 constexpr int kRawRowBytes = kChannels * 3 * 2;     // 384: the tile's columns of one projection row
 constexpr int kRawSlabBytes = (kSlabRows + 2) * kRawRowBytes;
 constexpr int kRawBytes = 2 * kRawSlabBytes;        // double buffer
+constexpr int kSlabCopies = (kSlabRows + 2) * 24;   // 16-byte copies per slab
+constexpr int kCopiesPerThread = (kSlabCopies + kThreads - 1) / kThreads;
 
-__device__ __forceinline__ void load48_shared(const unsigned char *p, std::uint32_t (&w)[12]) {
-  const uint4 *v = reinterpret_cast<const uint4 *>(p);
-  const uint4 a = v[0], b = v[1], c = v[2];
-  w[0] = a.x; w[1] = a.y; w[2] = a.z; w[3] = a.w;
-  w[4] = b.x; w[5] = b.y; w[6] = b.z; w[7] = b.w;
-  w[8] = c.x; w[9] = c.y; w[10] = c.z; w[11] = c.w;
-}
+// A thread's share of the 16-byte copies of a slab.  Which (row, chunk) a
+// thread copies does not change from slab to slab, so everything but the time
+// bound is worked out once.
+struct SlabCopies {
+  std::size_t source[kCopiesPerThread];    // element offset from row t_first of the slab
+  std::uint32_t destination[kCopiesPerThread];  // byte offset inside a slab buffer
+  int row[kCopiesPerThread];               // slab row, or a large negative number when unused
 
-// Starts the copy of projection rows [t_first, t_first + kSlabRows + 2) x the
-// tile's 192 columns into `slab`; rows outside [0, length) and columns beyond
-// the width arrive as zeros.  One commit group per call.
-__device__ __forceinline__ void issue_raw_slab(const Params &p, unsigned char *slab, const int t_first,
-                                               const int c_tile) {
-  const std::size_t width3 = static_cast<std::size_t>(p.width) * 3;
-  const std::size_t column0 = static_cast<std::size_t>(c_tile) * 3;
-  for (int item = threadIdx.x; item < (kSlabRows + 2) * 24; item += kThreads) {
-    const int j = item / 24, chunk = item % 24;
-    const int t = t_first + j;
-    const std::size_t column = column0 + chunk * 8;
-    const bool valid = t >= 0 && t < p.length && column + 8 <= width3;
-    const bf16 *const source = valid ? p.projection + static_cast<std::size_t>(t) * width3 + column : p.projection;
-    const std::uint32_t destination =
-        static_cast<std::uint32_t>(__cvta_generic_to_shared(slab + j * kRawRowBytes + chunk * 16));
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(destination), "l"(source),
-                 "r"(valid ? 16U : 0U)
-                 : "memory");
+  __device__ __forceinline__ void plan(const Params &p, const int c_tile) {
+    const std::size_t width3 = static_cast<std::size_t>(p.width) * 3;
+#pragma unroll
+    for (int k = 0; k < kCopiesPerThread; ++k) {
+      const int item = threadIdx.x + k * kThreads;
+      const int j = item / 24, chunk = item % 24;
+      const std::size_t column = static_cast<std::size_t>(c_tile) * 3 + chunk * 8;
+      const bool used = item < kSlabCopies && column + 8 <= width3;
+      row[k] = used ? j : -0x40000000;
+      source[k] = static_cast<std::size_t>(j) * width3 + column;
+      destination[k] = static_cast<std::uint32_t>(j * kRawRowBytes + chunk * 16);
+    }
   }
-  asm volatile("cp.async.commit_group;" ::: "memory");
-}
+  // Rows outside [0, length) and unused copies arrive as zeros.  One commit group.
+  __device__ __forceinline__ void issue(const Params &p, unsigned char *slab, const int t_first) const {
+    const std::uint32_t base = static_cast<std::uint32_t>(__cvta_generic_to_shared(slab));
+    const bf16 *const first = p.projection + static_cast<long long>(t_first) * (static_cast<long long>(p.width) * 3);
+#pragma unroll
+    for (int k = 0; k < kCopiesPerThread; ++k) {
+      if (threadIdx.x + k * kThreads >= kSlabCopies) break;
+      const bool valid = static_cast<unsigned int>(t_first + row[k]) < static_cast<unsigned int>(p.length);
+      const bf16 *const from = valid ? first + source[k] : p.projection;
+      asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(base + destination[k]), "l"(from),
+                   "r"(valid ? 16U : 0U)
+                   : "memory");
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  }
+};
 
 // Builds u rows [0, rows) (tile row r <-> time t_first + r) and, for tile rows
 // >= gate_first_row, the x2 gate rows.  Also emits the optional pregate copy
@@ -113,10 +124,10 @@ __device__ __forceinline__ void build_tiles(const Params &p, unsigned char *u_ti
   const bool channel_ok = c0 < p.width;  // width is a multiple of 8
   const int real_halo = p.taps - 1;
 
-  auto emit = [&](const int r, const int t, const float (&u)[8], const float (&g)[8],
+  // u, g: packed BF16 pairs of channels (2j, 2j+1) of the chunk
+  auto emit = [&](const int r, const int t, const std::uint32_t (&u)[4], const std::uint32_t (&g)[4],
                   const bool have_gate) {
-    uint4 packed = make_uint4(pack_exact(u[0], u[1]), pack_exact(u[2], u[3]),
-                              pack_exact(u[4], u[5]), pack_exact(u[6], u[7]));
+    const uint4 packed = make_uint4(u[0], u[1], u[2], u[3]);
     *reinterpret_cast<uint4 *>(u_tile + tile_offset(r, chunk)) = packed;
     // The first CTA of a row window also owns the history rows it recomputes,
     // so that the decode history is complete even for windows shorter than it.
@@ -129,20 +140,19 @@ __device__ __forceinline__ void build_tiles(const Params &p, unsigned char *u_ti
         if (slot >= 0) {
 #pragma unroll
           for (int i = 0; i < 8; ++i)
-            p.inner_cache[static_cast<std::size_t>(c0 + i) * real_halo + slot] = u[i];
+            p.inner_cache[static_cast<std::size_t>(c0 + i) * real_halo + slot] = element(u, i);
         }
       }
     }
     if (have_gate)
       *reinterpret_cast<uint4 *>(x2_tile + tile_offset(r - gate_first_row, chunk)) =
-          make_uint4(pack_exact(g[0], g[1]), pack_exact(g[2], g[3]), pack_exact(g[4], g[5]),
-                     pack_exact(g[6], g[7]));
+          make_uint4(g[0], g[1], g[2], g[3]);
   };
 
   if constexpr (!kProj) {
     for (int r = threadIdx.x / kChunks; r < rows; r += kThreads / kChunks) {
       const int t = t_first + r;
-      float u[8] = {}, g[8] = {};
+      std::uint32_t u[4] = {}, g[4] = {};
       const bool live = channel_ok && t >= 0 && t < p.length;
       const bool have_gate = r >= gate_first_row;
       if (live) {
@@ -151,12 +161,11 @@ __device__ __forceinline__ void build_tiles(const Params &p, unsigned char *u_ti
         a.raw = __ldg(reinterpret_cast<const uint4 *>(p.x1 + index));
         b.raw = __ldg(reinterpret_cast<const uint4 *>(p.value + index));
 #pragma unroll
-        for (int i = 0; i < 8; ++i) u[i] = rbf(a.get(i) * b.get(i));
+        for (int j = 0; j < 4; ++j)
+          u[j] = round_pair_bf16(a.get(2 * j) * b.get(2 * j), a.get(2 * j + 1) * b.get(2 * j + 1));
         if (have_gate) {
-          Bf16x8 c;
-          c.raw = __ldg(reinterpret_cast<const uint4 *>(p.x2 + index));
-#pragma unroll
-          for (int i = 0; i < 8; ++i) g[i] = c.get(i);
+          const uint4 c = __ldg(reinterpret_cast<const uint4 *>(p.x2 + index));
+          g[0] = c.x; g[1] = c.y; g[2] = c.z; g[3] = c.w;
         }
       }
       emit(r, t, u, g, have_gate);
@@ -168,21 +177,16 @@ __device__ __forceinline__ void build_tiles(const Params &p, unsigned char *u_ti
     // next slab are in flight while this one is featurized and no thread ever
     // waits on its own loads.  One (row, 8-channel chunk) item per thread.
     const int item_row = threadIdx.x / kChunks;
-    std::uint32_t weights[36];  // 24 streams x 3 taps, packed BF16 pairs
-    if (channel_ok) {
-      const uint4 *w = reinterpret_cast<const uint4 *>(p.short_filter + static_cast<std::size_t>(c0) * 9);
-#pragma unroll
-      for (int i = 0; i < 9; ++i) {
-        const uint4 v = __ldg(w + i);
-        weights[4 * i] = v.x; weights[4 * i + 1] = v.y; weights[4 * i + 2] = v.z; weights[4 * i + 3] = v.w;
-      }
-    }
+    PackedTaps taps;
+    if (channel_ok) taps.load_global(p.short_filter, c0);
+    SlabCopies copies;
+    copies.plan(p, c_tile);
     const int slabs = (rows + kSlabRows - 1) / kSlabRows;
-    issue_raw_slab(p, raw, t_first - 2, c_tile);
+    copies.issue(p, raw, t_first - 2);
     for (int slab = 0; slab < slabs; ++slab) {
-      unsigned char *const buffer = raw + (slab & 1) * kRawSlabBytes;
+      const unsigned char *const buffer = raw + (slab & 1) * kRawSlabBytes;
       if (slab + 1 < slabs) {
-        issue_raw_slab(p, raw + ((slab + 1) & 1) * kRawSlabBytes, t_first + (slab + 1) * kSlabRows - 2, c_tile);
+        copies.issue(p, raw + ((slab + 1) & 1) * kRawSlabBytes, t_first + (slab + 1) * kSlabRows - 2);
         asm volatile("cp.async.wait_group 1;" ::: "memory");
       } else {
         asm volatile("cp.async.wait_group 0;" ::: "memory");
@@ -193,28 +197,11 @@ __device__ __forceinline__ void build_tiles(const Params &p, unsigned char *u_ti
         const int t = t_first + r;
         const bool live = channel_ok && t >= 0 && t < p.length;
         const bool have_gate = r >= gate_first_row;
-        float u[8] = {}, g[8] = {};
+        std::uint32_t u[4] = {}, g[4] = {};
         if (live) {
-          std::uint32_t prev2[12], prev1[12], current[12];
           const unsigned char *const base = buffer + item_row * kRawRowBytes + chunk * 48;
-          load48_shared(base, prev2);
-          load48_shared(base + kRawRowBytes, prev1);
-          load48_shared(base + 2 * kRawRowBytes, current);
-#pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            float z[3];
-#pragma unroll
-            for (int st = 0; st < 3; ++st) {
-              const int idx = 3 * i + st;
-              float acc = 0.0F;
-              acc = fmaf(element(prev2, idx), element(weights, idx * 3), acc);
-              acc = fmaf(element(prev1, idx), element(weights, idx * 3 + 1), acc);
-              acc = fmaf(element(current, idx), element(weights, idx * 3 + 2), acc);
-              z[st] = rbf(acc);
-            }
-            u[i] = rbf(z[1] * z[2]);
-            g[i] = z[0];
-          }
+          const unsigned char *const history[3] = {base, base + kRawRowBytes, base + 2 * kRawRowBytes};
+          featurize_chunk<true>(history, taps, u, g);
         }
         emit(r, t, u, g, have_gate);
       }

@@ -22,6 +22,7 @@
 
 #include "common.cuh"
 #include "ops_internal.hpp"
+#include "projection_featurizer.cuh"
 
 namespace evob {
 namespace {
@@ -355,39 +356,70 @@ __device__ __forceinline__ void async_copy16(void *shared, const void *global, c
                : "memory");
 }
 
-// Starts the copies of slab `slab` (rows slab*kSlab .. +kSlab of every segment
-// lane, plus the two featurizer history rows when projection-fed).
+// A thread's share of the 16-byte copies of a slab; the (lane, row, chunk) a
+// thread copies is the same for every slab, so only the row bound is checked
+// per slab.
 template <bool kFromProjection, bool kNeedGate>
-__device__ __forceinline__ void issue_modal_slab(const ModalParams &p, unsigned char *stage,
-                                                 const int seg0, const int slab, const int c_tile) {
-  if constexpr (kFromProjection) {
-    const std::size_t width3 = static_cast<std::size_t>(p.width) * 3;
-    const std::size_t column0 = static_cast<std::size_t>(c_tile) * 3;
-    for (int item = threadIdx.x; item < kLanes * (kSlab + 2) * 24; item += kScanThreads) {
-      const int chunk = item % 24, j = (item / 24) % (kSlab + 2), lane = item / (24 * (kSlab + 2));
-      const int seg = seg0 + lane;
-      const int t = p.row_begin + seg * p.segment + slab * kSlab + j - 2;
-      const std::size_t column = column0 + chunk * 8;
-      const bool valid = seg < p.segments && t >= 0 && t < p.length && column + 8 <= width3;
-      async_copy16(stage + (lane * (kSlab + 2) + j) * kProjRowBytes + chunk * 16,
-                   valid ? p.projection + static_cast<std::size_t>(t) * width3 + column : p.projection, valid);
-    }
-  } else {
-    constexpr int kStreams = kNeedGate ? 3 : 2;
-    for (int item = threadIdx.x; item < kStreams * kLanes * kSlab * 8; item += kScanThreads) {
-      const int chunk = item % 8, j = (item / 8) % kSlab, lane = (item / (8 * kSlab)) % kLanes;
-      const int stream = item / (8 * kSlab * kLanes);
-      const int seg = seg0 + lane;
-      const int t = p.row_begin + seg * p.segment + slab * kSlab + j;
-      const int channel = c_tile + chunk * 8;
-      const bool valid = seg < p.segments && t < p.length && channel < p.width;
-      const bf16 *const base = stream == 0 ? p.x1 : (stream == 1 ? p.value : p.x2);
-      async_copy16(stage + ((stream * kLanes + lane) * kSlab + j) * kPlainRowBytes + chunk * 16,
-                   valid ? base + static_cast<std::size_t>(t) * p.width + channel : base, valid);
+struct ModalCopies {
+  static constexpr int kTotal =
+      kFromProjection ? kLanes * (kSlab + 2) * 24 : (kNeedGate ? 3 : 2) * kLanes * kSlab * 8;
+  static constexpr int kPerThread = (kTotal + kScanThreads - 1) / kScanThreads;
+  const bf16 *source[kPerThread];   // address of the copy for slab 0 (may be out of range: see row)
+  std::uint32_t destination[kPerThread];
+  int row[kPerThread];              // time of the copy for slab 0; a huge value when unused
+
+  __device__ __forceinline__ void plan(const ModalParams &p, const int seg0, const int c_tile) {
+#pragma unroll
+    for (int k = 0; k < kPerThread; ++k) {
+      const int item = threadIdx.x + k * kScanThreads;
+      int lane, j, t, column_elements;
+      const bf16 *base;
+      std::size_t pitch;
+      bool used = item < kTotal;
+      if constexpr (kFromProjection) {
+        const int chunk = item % 24;
+        j = (item / 24) % (kSlab + 2);
+        lane = item / (24 * (kSlab + 2));
+        t = p.row_begin + (seg0 + lane) * p.segment + j - 2;
+        pitch = static_cast<std::size_t>(p.width) * 3;
+        column_elements = c_tile * 3 + chunk * 8;
+        used = used && static_cast<std::size_t>(column_elements) + 8 <= pitch;
+        base = p.projection;
+        destination[k] = static_cast<std::uint32_t>((lane * (kSlab + 2) + j) * kProjRowBytes + chunk * 16);
+      } else {
+        const int chunk = item % 8;
+        j = (item / 8) % kSlab;
+        lane = (item / (8 * kSlab)) % kLanes;
+        const int stream = item / (8 * kSlab * kLanes);
+        t = p.row_begin + (seg0 + lane) * p.segment + j;
+        pitch = static_cast<std::size_t>(p.width);
+        column_elements = c_tile + chunk * 8;
+        used = used && column_elements < p.width;
+        base = stream == 0 ? p.x1 : (stream == 1 ? p.value : p.x2);
+        destination[k] =
+            static_cast<std::uint32_t>(((stream * kLanes + lane) * kSlab + j) * kPlainRowBytes + chunk * 16);
+      }
+      used = used && seg0 + lane < p.segments;
+      row[k] = used ? t : 0x40000000;
+      source[k] = base + static_cast<long long>(t) * static_cast<long long>(pitch) + column_elements;
     }
   }
-  asm volatile("cp.async.commit_group;" ::: "memory");
-}
+  __device__ __forceinline__ void issue(const ModalParams &p, unsigned char *stage, const int slab) const {
+    const std::uint32_t base = static_cast<std::uint32_t>(__cvta_generic_to_shared(stage));
+    const std::size_t advance = static_cast<std::size_t>(slab) * kSlab *
+                                (kFromProjection ? static_cast<std::size_t>(p.width) * 3 : p.width);
+#pragma unroll
+    for (int k = 0; k < kPerThread; ++k) {
+      if (threadIdx.x + k * kScanThreads >= kTotal) break;
+      const bool valid = static_cast<unsigned int>(row[k] + slab * kSlab) < static_cast<unsigned int>(p.length);
+      const bf16 *const from = valid ? source[k] + advance : p.direct;
+      asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(base + destination[k]), "l"(from),
+                   "r"(valid ? 16U : 0U)
+                   : "memory");
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  }
+};
 
 template <int kModes, bool kFromProjection, bool kOutput>
 __global__ void __launch_bounds__(kScanThreads, 2)
@@ -402,9 +434,10 @@ modal_tiled_kernel(const ModalParams p) {
   const int seg0 = blockIdx.x * kLanes;
   const int c_tile = blockIdx.y * kTileChannels;
   const int lane = threadIdx.x / kTileChannels;  // segment lane of both roles
+  const int column = threadIdx.x % kTileChannels;
 
   // ---- scan role: channel `channel` of segment seg0 + lane
-  const int channel = c_tile + threadIdx.x % kTileChannels;
+  const int channel = c_tile + column;
   const int seg = seg0 + lane;
   const bool scans = channel < p.width && seg < p.segments;
   const int t0 = p.row_begin + seg * p.segment;
@@ -441,88 +474,66 @@ modal_tiled_kernel(const ModalParams p) {
       *reinterpret_cast<uint4 *>(weights + chunk * 36 + part * 4) = v;
     }
   }
+  ModalCopies<kFromProjection, kOutput> copies;
+  copies.plan(p, seg0, c_tile);
   const int slabs = p.segment / kSlab;
-  issue_modal_slab<kFromProjection, kOutput>(p, stages, seg0, 0, c_tile);
+  copies.issue(p, stages, 0);
   for (int slab = 0; slab < slabs; ++slab) {
     const unsigned char *const stage = stages + (slab & 1) * kStageBytes;
     if (slab + 1 < slabs) {
-      issue_modal_slab<kFromProjection, kOutput>(p, stages + ((slab + 1) & 1) * kStageBytes, seg0, slab + 1,
-                                                 c_tile);
+      copies.issue(p, stages + ((slab + 1) & 1) * kStageBytes, slab + 1);
       asm volatile("cp.async.wait_group 1;" ::: "memory");
     } else {
       asm volatile("cp.async.wait_group 0;" ::: "memory");
     }
     __syncthreads();
     {  // featurize one (lane, row, chunk) item into packed words: u low, x2 high
-      float u[8], g[8];
+      std::uint32_t u[4], g[4] = {0U, 0U, 0U, 0U};
       if constexpr (kFromProjection) {
         const unsigned char *const base =
             stage + (lane * (kSlab + 2) + item_row) * kProjRowBytes + item_chunk * 48;
-        std::uint32_t rows[3][12];
-#pragma unroll
-        for (int r = 0; r < 3; ++r)
-#pragma unroll
-          for (int v = 0; v < 3; ++v) {
-            const uint4 x = *reinterpret_cast<const uint4 *>(base + r * kProjRowBytes + v * 16);
-            rows[r][4 * v] = x.x; rows[r][4 * v + 1] = x.y; rows[r][4 * v + 2] = x.z; rows[r][4 * v + 3] = x.w;
-          }
-        const std::uint32_t *const w = weights + item_chunk * 36;
-        auto value_of = [](const std::uint32_t word, const int index) {
-          return (index & 1) ? __uint_as_float(word & 0xffff0000U) : __uint_as_float(word << 16U);
-        };
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          float z[3];
-#pragma unroll
-          for (int st = kOutput ? 0 : 1; st < 3; ++st) {
-            const int idx = 3 * i + st;
-            float acc = 0.0F;
-#pragma unroll
-            for (int tap = 0; tap < 3; ++tap) {
-              const int wi = idx * 3 + tap;
-              acc = fmaf(value_of(rows[tap][idx >> 1], idx), value_of(w[wi >> 1], wi), acc);
-            }
-            z[st] = rbf(acc);
-          }
-          u[i] = rbf(z[1] * z[2]);
-          g[i] = kOutput ? z[0] : 0.0F;
-        }
+        const unsigned char *const history[3] = {base, base + kProjRowBytes, base + 2 * kProjRowBytes};
+        PackedTaps taps;
+        taps.load_shared(weights + item_chunk * 36);
+        featurize_chunk<kOutput>(history, taps, u, g);
       } else {
         const unsigned char *const base = stage + (lane * kSlab + item_row) * kPlainRowBytes + item_chunk * 16;
-        Bf16x8 a, b, c;
+        Bf16x8 a, b;
         a.raw = *reinterpret_cast<const uint4 *>(base);
         b.raw = *reinterpret_cast<const uint4 *>(base + kLanes * kSlab * kPlainRowBytes);
-        c.raw = make_uint4(0U, 0U, 0U, 0U);
-        if constexpr (kOutput) c.raw = *reinterpret_cast<const uint4 *>(base + 2 * kLanes * kSlab * kPlainRowBytes);
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          u[i] = rbf(a.get(i) * b.get(i));
-          g[i] = c.get(i);
+        for (int j = 0; j < 4; ++j)
+          u[j] = round_pair_bf16(a.get(2 * j) * b.get(2 * j), a.get(2 * j + 1) * b.get(2 * j + 1));
+        if constexpr (kOutput) {
+          const uint4 c = *reinterpret_cast<const uint4 *>(base + 2 * kLanes * kSlab * kPlainRowBytes);
+          g[0] = c.x; g[1] = c.y; g[2] = c.z; g[3] = c.w;
         }
       }
-      std::uint32_t packed[8];
-#pragma unroll
-      for (int i = 0; i < 8; ++i)
-        packed[i] = (__float_as_uint(u[i]) >> 16U) | (__float_as_uint(g[i]) & 0xffff0000U);
       uint4 *const destination = reinterpret_cast<uint4 *>(
           words + (lane * kSlab + item_row) * kTileChannels + item_chunk * 8);
-      destination[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
-      destination[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+      // word of channel c = u_c | x2_c << 16
+      destination[0] = make_uint4(__byte_perm(u[0], g[0], 0x5410), __byte_perm(u[0], g[0], 0x7632),
+                                  __byte_perm(u[1], g[1], 0x5410), __byte_perm(u[1], g[1], 0x7632));
+      destination[1] = make_uint4(__byte_perm(u[2], g[2], 0x5410), __byte_perm(u[2], g[2], 0x7632),
+                                  __byte_perm(u[3], g[3], 0x5410), __byte_perm(u[3], g[3], 0x7632));
       if constexpr (kOutput) {
         const int t = t0 + slab * kSlab + item_row;
         if (p.pregate != nullptr && item_ok && t < t1)
           *reinterpret_cast<uint4 *>(p.pregate + static_cast<std::size_t>(t) * p.width + item_c0) =
-              make_uint4((packed[0] & 0xffffU) | (packed[1] << 16U), (packed[2] & 0xffffU) | (packed[3] << 16U),
-                         (packed[4] & 0xffffU) | (packed[5] << 16U), (packed[6] & 0xffffU) | (packed[7] << 16U));
+              make_uint4(u[0], u[1], u[2], u[3]);
       }
     }
     __syncthreads();
     if (scans) {
+      const int first = t0 + slab * kSlab;
+      const std::uint32_t *const my_words = words + lane * kSlab * kTileChannels + column;
+      unsigned short *const my_out = out_tile + lane * kSlab * kTileChannels + column;
+      // rows of this slab inside the segment (all of them except in the last segment)
+      const int live = min(kSlab, t1 - first);
 #pragma unroll
       for (int r = 0; r < kSlab; ++r) {
-        const int t = t0 + slab * kSlab + r;
-        if (t < t1) {
-          const std::uint32_t word = words[(lane * kSlab + r) * kTileChannels + threadIdx.x % kTileChannels];
+        if (r < live) {
+          const std::uint32_t word = my_words[r * kTileChannels];
           const float u = __uint_as_float(word << 16U);
           if constexpr (kOutput) {
             const float g = __uint_as_float(word & 0xffff0000U);
@@ -538,8 +549,7 @@ modal_tiled_kernel(const ModalParams p) {
               result = g * fmaf(direct, u, modal);
             else
               result = rbf(rbf(modal) + rbf(direct * u)) * g;
-            out_tile[(lane * kSlab + r) * kTileChannels + threadIdx.x % kTileChannels] =
-                __bfloat16_as_ushort(__float2bfloat16_rn(result));
+            my_out[r * kTileChannels] = static_cast<unsigned short>(__float_as_uint(rbf(result)) >> 16U);
           } else {
 #pragma unroll
             for (int m = 0; m < kModes; ++m) state[m] = fmaf(pole[m], state[m], u);
