@@ -51,6 +51,7 @@ OPS_SIGNATURES: dict[str, list] = {
     "evo_b200_bf16_hcl_decode": [_P, _P, _P, _P, _P, _P, _Z, _Z, _P, _P, _P, _P],
     "evo_b200_bf16_split_rope_append": [_P, _P, _Z, _Z, _Z, _Z, _F, _I, _P, _P, _P, _Z, _P],
     "evo_b200_bf16_causal_attention": [_P, _P, _P, _Z, _Z, _Z, _Z, _P, _P],
+    "evo_b200_bf16_causal_attention_mma_sync": [_P, _P, _P, _Z, _Z, _Z, _Z, _P, _P],
     "evo_b200_bf16_cached_cross_attention": [_P, _P, _P, _Z, _Z, _Z, _Z, _P, _P],
 }
 

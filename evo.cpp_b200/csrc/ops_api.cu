@@ -421,6 +421,14 @@ int evo_b200_bf16_causal_attention(const void *query, const void *key_cache,
                           heads, head_dim, output, as_stream(stream));
 }
 
+int evo_b200_bf16_causal_attention_mma_sync(const void *query, const void *key_cache,
+                                            const void *value_cache, size_t rows,
+                                            size_t total_keys, size_t heads,
+                                            size_t head_dim, void *output, void *stream) {
+  return causal_attention_mma_sync(query, key_cache, value_cache, rows, total_keys,
+                                   heads, head_dim, output, as_stream(stream));
+}
+
 int evo_b200_bf16_cached_cross_attention(const void *query,
                                          const void *key_cache,
                                          const void *value_cache, size_t rows,

@@ -157,6 +157,12 @@ int causal_attention(const void *query, const void *key_cache,
                      const void *value_cache, std::size_t rows,
                      std::size_t total_keys, std::size_t heads,
                      std::size_t head_dim, void *output, cudaStream_t stream);
+// Warp-level MMA / row-wise implementation of the same contract (what
+// causal_attention falls back to below 128 rows or for other head sizes).
+int causal_attention_mma_sync(const void *query, const void *key_cache,
+                              const void *value_cache, std::size_t rows,
+                              std::size_t total_keys, std::size_t heads,
+                              std::size_t head_dim, void *output, cudaStream_t stream);
 int cached_attention(const void *query, const void *key_cache,
                      const void *value_cache, std::size_t rows,
                      std::size_t total_keys, std::size_t heads,

@@ -226,6 +226,13 @@ EVO_B200_API int evo_b200_bf16_causal_attention(
     const void *query, const void *key_cache, const void *value_cache,
     size_t rows, size_t total_keys, size_t heads, size_t head_dim,
     void *output, void *stream);
+/* Same contract on warp-level MMAs (head size 128, >= 16 rows) or the row-wise
+ * kernel: what evo_b200_bf16_causal_attention uses below 128 rows and for
+ * other head sizes; exported as a cross-check of the tcgen05 kernel. */
+EVO_B200_API int evo_b200_bf16_causal_attention_mma_sync(
+    const void *query, const void *key_cache, const void *value_cache,
+    size_t rows, size_t total_keys, size_t heads, size_t head_dim,
+    void *output, void *stream);
 /* bf16_cached_cross_attention (src/cuda/attention.cu:283-784,1669-1799). */
 EVO_B200_API int evo_b200_bf16_cached_cross_attention(
     const void *query, const void *key_cache, const void *value_cache,

@@ -76,6 +76,31 @@ def test_causal_attention(ops, oracle, rows, prefix, heads, head_dim):
     assert_close_bits(host_bits(out), expected, atol=0.02, rtol=0.02, min_cosine=0.9995)
 
 
+@pytest.mark.parametrize("rows,prefix,heads", [(128, 0, 1), (1024, 0, 3), (2048, 512, 2), (1000, 77, 2),
+                                               (4096, 0, 1), (300, 1300, 2)])
+def test_tcgen05_attention_matches_warp_mma_kernel(ops, rows, prefix, heads):
+    """>= 128 rows of head size 128 run on the tcgen05 kernel; the warp-level MMA
+    kernel computes the same contract with different tiling and summation order."""
+    gen = torch.Generator(device="cuda").manual_seed(rows + prefix)
+    width, total = heads * 128, prefix + rows
+    q = torch.randn(rows, width, device="cuda", generator=gen).bfloat16()
+    k = torch.randn(total, width, device="cuda", generator=gen).bfloat16()
+    v = torch.randn(total, width, device="cuda", generator=gen).bfloat16()
+    out, check = torch.full_like(q, 7.0), torch.full_like(q, -7.0)
+    ops.call("bf16_causal_attention", p(q), p(k), p(v), rows, total, heads, 128, p(out), stream())
+    ops.call("bf16_causal_attention_mma_sync", p(q), p(k), p(v), rows, total, heads, 128, p(check), stream())
+    ops.call("check_async_errors", stream())
+    a, b = out.float(), check.float()
+    assert torch.isfinite(a).all()
+    assert (a - b).abs().max().item() < 0.03, (a - b).abs().max().item()
+    assert torch.nn.functional.cosine_similarity(a.flatten(), b.flatten(), dim=0).item() > 0.9999
+    # and against plain F32 softmax attention for the first head
+    scores = (q[:, :128].float() @ k[:, :128].float().T) / 128 ** 0.5
+    visible = torch.arange(total, device="cuda")[None, :] <= (prefix + torch.arange(rows, device="cuda"))[:, None]
+    reference = torch.softmax(scores.masked_fill(~visible, float("-inf")), dim=-1) @ v[:, :128].float()
+    assert (a[:, :128] - reference).abs().max().item() < 0.03
+
+
 @pytest.mark.parametrize("rows,prefix,heads,head_dim", [(1, 0, 2, 128), (1, 2048, 2, 128), (9, 0, 3, 8),
                                                        (40, 100, 2, 128), (1, 10240, 1, 128)])
 def test_cached_cross_attention(ops, oracle, rows, prefix, heads, head_dim):
