@@ -12,11 +12,14 @@
 //              tile ahead of the softmax; then O_j = P_j V_j with P_j read
 //              from shared memory (K-major) and V_j used in place as an
 //              MN-major operand, into a third TMEM buffer.
-//   warps 2-5  softmax: one thread per query row (TMEM lane), so row maxima
-//              and sums need no shuffles.  Two passes over the scores in TMEM
-//              (max, then exp2 / sum / BF16 pack), P_j written to shared memory
-//              in the swizzled K-major layout, O_j added into a register
-//              accumulator with the usual running-max rescale.
+//   warps 2-17 softmax: a thread owns a quarter of one query row (its TMEM
+//              lane; four warps share a lane quarter and split the 128 columns), so
+//              row maxima and sums need no shuffles - the four parts exchange
+//              one maximum per tile through shared memory.  Scores are read
+//              from TMEM once and kept in registers (max, then exp2 / sum /
+//              BF16 pack), P_j written to shared memory in the swizzled K-major layout, O_j
+//              added into a register accumulator with the usual running-max
+//              rescale.
 // Score buffers, the P tile and the O_j buffer are handed back and forth with
 // mbarriers; every wait is time-bounded and raises the same sticky error word
 // as the projection kernels.
@@ -31,7 +34,11 @@ namespace evob {
 namespace {
 using namespace tc;
 
-constexpr int kThreads = 192;
+constexpr int kSides = 2;                         // softmax warps per TMEM lane quarter
+constexpr int kSideColumns = 128 / kSides;        // keys / output dimensions per softmax warp and tile
+constexpr int kThreads = 64 + 128 * kSides;       // TMA warp, MMA warp, 4 * kSides softmax warps
+constexpr int kSideChunks = kSideColumns / 32;    // 32-column TMEM loads per softmax thread and tile
+static_assert(kSideColumns % 32 == 0 && kSideColumns <= 64, "sides are one or two 32-column TMEM loads");
 constexpr int kTile = 128;                    // query rows per CTA and keys per tile
 constexpr int kHalfBytes = kTile * 128;       // one 64-column box: 128 rows x 128 bytes
 constexpr int kTileBytes = 2 * kHalfBytes;    // 32 KiB
@@ -40,16 +47,17 @@ constexpr int kKOffset = kTileBytes;                    // 2 stages
 constexpr int kVOffset = kKOffset + 2 * kTileBytes;     // 2 stages
 constexpr int kPOffset = kVOffset + 2 * kTileBytes;
 constexpr int kBarrierOffset = kPOffset + kTileBytes;
-constexpr int kBarriers = 16;
+constexpr int kBarriers = 21;
 constexpr int kTmemPtrOffset = kBarrierOffset + kBarriers * 8;
 constexpr int kAbortOffset = kTmemPtrOffset + 8;
-constexpr int kSmemBytes = kAbortOffset + 8 + 1024;  // + alignment slack
+constexpr int kExchangeOffset = kAbortOffset + 16;                // 2 x 2 x 128 floats
+constexpr int kSmemBytes = kExchangeOffset + 2 * kSides * kTile * 4 + 1024;  // + alignment slack
 constexpr std::uint32_t kTmemColumns = 512;            // S0 | S1 | O | unused
 constexpr std::uint32_t kScoreColumns = 128;
 
 enum Barrier : int {
   kQFull = 0, kKFull = 1, kKEmpty = 3, kVFull = 5, kVEmpty = 7, kSFull = 9, kSEmpty = 11,
-  kPFull = 13, kOFull = 14, kOEmpty = 15
+  kPFull = 13, kOFull = 14, kOEmpty = 15, kMaxReady = 16 /* one per lane quarter */, kSumReady = 20
 };
 
 // V tile as the B operand of O = P V: N (head dimension) is the contiguous
@@ -112,11 +120,13 @@ flash_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
       mbar_init(bar(kVFull + s), 1);
       mbar_init(bar(kVEmpty + s), 1);
       mbar_init(bar(kSFull + s), 1);
-      mbar_init(bar(kSEmpty + s), 4);
+      mbar_init(bar(kSEmpty + s), 4 * kSides);
     }
-    mbar_init(bar(kPFull), 4);
+    mbar_init(bar(kPFull), 4 * kSides);
     mbar_init(bar(kOFull), 1);
-    mbar_init(bar(kOEmpty), 4);
+    mbar_init(bar(kOEmpty), 4 * kSides);
+    for (int q = 0; q < 4; ++q) mbar_init(bar(kMaxReady + q), kSides);
+    mbar_init(bar(kSumReady), 4 * kSides);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -199,29 +209,38 @@ flash_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
       }
     }
   } else {
+    // kSides softmax warps share each TMEM lane quarter and split the columns:
+    // side s takes keys / output dimensions s*kSideColumns .. of every tile.  A
+    // row's maximum is the one value the sides exchange per tile (through
+    // shared memory, behind a bounded mbarrier wait).
     const int quarter = warp % 4;
+    const int side = (warp - 2) / 4;
     const int row = quarter * 32 + lane;                    // query row inside the block = TMEM lane
     const std::uint32_t lane_base = static_cast<std::uint32_t>(quarter * 32) << 16U;
+    const std::uint32_t column_base = static_cast<std::uint32_t>(side * kSideColumns);
     const int position = prefix + q0 + row;                 // last key this row may see
     const float scale_log2 = 1.4426950408889634F * rsqrtf(static_cast<float>(kTile));
-    float accumulator[kTile];
+    float accumulator[kSideColumns];
 #pragma unroll
-    for (int i = 0; i < kTile; ++i) accumulator[i] = 0.0F;
+    for (int i = 0; i < kSideColumns; ++i) accumulator[i] = 0.0F;
     float running_max = -INFINITY, running_sum = 0.0F, previous_alpha = 1.0F;
-    unsigned char *const p_row = smem + kPOffset + row * 128;  // row inside a 64-key half
+    // this side's keys of the row: 16-byte chunks first_chunk .. of one 64-key half of the P tile
+    unsigned char *const p_row = smem + kPOffset + (side * kSideColumns / 64) * kHalfBytes + row * 128;
+    const int first_chunk = (side * kSideColumns % 64) / 8;
+    float *const exchange = reinterpret_cast<float *>(smem + kExchangeOffset);  // [2 tiles][kSides][128 rows]
     bool ok = true;
 
     // O_reg = O_reg * alpha + (P V of the tile that just finished)
     auto absorb_output = [&](const float alpha) {
+      std::uint32_t v[kSideChunks][32];
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        std::uint32_t v[32];
-        tmem_load_32(tmem_o + lane_base + c * 32, v);
-        tmem_load_wait();
+      for (int c = 0; c < kSideChunks; ++c) tmem_load_32(tmem_o + lane_base + column_base + c * 32, v[c]);
+      tmem_load_wait();
+#pragma unroll
+      for (int c = 0; c < kSideChunks; ++c)
 #pragma unroll
         for (int i = 0; i < 32; ++i)
-          accumulator[c * 32 + i] = fmaf(accumulator[c * 32 + i], alpha, __uint_as_float(v[i]));
-      }
+          accumulator[c * 32 + i] = fmaf(accumulator[c * 32 + i], alpha, __uint_as_float(v[c][i]));
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar(kOEmpty));
@@ -234,23 +253,44 @@ flash_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
         break;
       }
       tc_fence_after();
-      const std::uint32_t scores = tmem_base + s * kScoreColumns + lane_base;
-      const int key0 = j * kTile;
-      const bool boundary = key0 + kTile - 1 > prefix + q0;  // some key hidden from some row
-      // pass 1: row maximum
-      float tile_max = -INFINITY;
+      const int key0 = j * kTile + side * kSideColumns;
+      const bool boundary = j * kTile + kTile - 1 > prefix + q0;  // some key hidden from some row
+      // this side's scores stay in registers from here to the P store
+      std::uint32_t v[kSideColumns];
+      {
+        std::uint32_t chunk[kSideChunks][32];
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        std::uint32_t v[32];
-        tmem_load_32(scores + c * 32, v);
+        for (int c = 0; c < kSideChunks; ++c)
+          tmem_load_32(tmem_base + s * kScoreColumns + lane_base + column_base + c * 32, chunk[c]);
         tmem_load_wait();
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          float value = __uint_as_float(v[i]);
-          if (boundary && key0 + c * 32 + i > position) value = -INFINITY;
-          tile_max = fmaxf(tile_max, value);
-        }
+        for (int c = 0; c < kSideChunks; ++c)
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[c * 32 + i] = chunk[c][i];
       }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(kSEmpty + s));  // the score buffer may be overwritten
+      if (boundary) {
+#pragma unroll
+        for (int i = 0; i < kSideColumns; ++i)
+          if (key0 + i > position) v[i] = 0xff800000U;  // -inf
+      }
+      float partial_max[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+      for (int i = 0; i < kSideColumns; ++i) partial_max[i % 4] = fmaxf(partial_max[i % 4], __uint_as_float(v[i]));
+      const float side_max = fmaxf(fmaxf(partial_max[0], partial_max[1]), fmaxf(partial_max[2], partial_max[3]));
+      exchange[(s * kSides + side) * kTile + row] = side_max;
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(kMaxReady + quarter));
+      if (!mbar_wait(bar(kMaxReady + quarter), j & 1U, abort_flag)) {
+        ok = false;
+        break;
+      }
+      float tile_max = side_max;
+#pragma unroll
+      for (int other = 1; other < kSides; ++other)
+        tile_max = fmaxf(tile_max, exchange[(s * kSides + ((side + other) % kSides)) * kTile + row]);
       const float new_max = fmaxf(running_max, tile_max);
       const float alpha = fast_exp2((running_max - new_max) * scale_log2);
       const float bias = -new_max * scale_log2;
@@ -263,62 +303,52 @@ flash_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
         tc_fence_after();
         absorb_output(previous_alpha);
       }
-      // pass 2: probabilities, row sum, BF16 pack into the swizzled P tile
-      float tile_sum = 0.0F;
+      // probabilities, partial row sum, BF16 pack into the swizzled P tile
+      float partial_sum[4] = {0.0F, 0.0F, 0.0F, 0.0F};
+      std::uint32_t packed[kSideColumns / 2];
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        std::uint32_t v[32];
-        tmem_load_32(scores + c * 32, v);
-        tmem_load_wait();
-        std::uint32_t packed[16];
-#pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          float a = __uint_as_float(v[i]), b = __uint_as_float(v[i + 1]);
-          if (boundary) {
-            if (key0 + c * 32 + i > position) a = -INFINITY;
-            if (key0 + c * 32 + i + 1 > position) b = -INFINITY;
-          }
-          const float pa = fast_exp2(fmaf(a, scale_log2, bias));
-          const float pb = fast_exp2(fmaf(b, scale_log2, bias));
-          tile_sum += pa + pb;
-          packed[i / 2] = round_pair_bf16(pa, pb);
-        }
-        // keys 32c .. 32c+31 of this row: four 16-byte chunks of half c / 2
-        unsigned char *const half = p_row + (c / 2) * kHalfBytes;
-#pragma unroll
-        for (int q = 0; q < 4; ++q) {
-          const int chunk = (c % 2) * 4 + q;
-          *reinterpret_cast<uint4 *>(half + ((chunk ^ (row & 7)) << 4)) =
-              make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
-        }
+      for (int i = 0; i < kSideColumns; i += 2) {
+        const float px = fast_exp2(fmaf(__uint_as_float(v[i]), scale_log2, bias));
+        const float py = fast_exp2(fmaf(__uint_as_float(v[i + 1]), scale_log2, bias));
+        partial_sum[(i / 2) % 4] += px + py;
+        // BF16 by integer round-half-up (probabilities are finite and >= 0): keeps
+        // the conversion off the transcendental unit, which the exp2 above saturates
+        packed[i / 2] = __byte_perm(__float_as_uint(px) + 0x8000U, __float_as_uint(py) + 0x8000U, 0x7632);
       }
-      // P visible to the tensor core (async proxy); scores consumed
+#pragma unroll
+      for (int q = 0; q < kSideColumns / 8; ++q)
+        *reinterpret_cast<uint4 *>(p_row + (((first_chunk + q) ^ (row & 7)) << 4)) =
+            make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
+      // P visible to the tensor core (async proxy)
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-      tc_fence_before();
       __syncwarp();
-      if (lane == 0) {
-        mbar_arrive(bar(kPFull));
-        mbar_arrive(bar(kSEmpty + s));
-      }
-      running_sum = fmaf(running_sum, alpha, tile_sum);
+      if (lane == 0) mbar_arrive(bar(kPFull));
+      running_sum = fmaf(running_sum, alpha, (partial_sum[0] + partial_sum[1]) + (partial_sum[2] + partial_sum[3]));
       running_max = new_max;
       previous_alpha = alpha;
     }
     if (ok && tiles > 0 && mbar_wait(bar(kOFull), (tiles - 1) & 1U, abort_flag)) {
       tc_fence_after();
       absorb_output(previous_alpha);
-      if (q0 + row < rows) {
-        const float inverse = 1.0F / running_sum;
-        bf16 *const out = output + static_cast<std::size_t>(q0 + row) * (static_cast<std::size_t>(heads) * kTile) +
-                          static_cast<std::size_t>(head) * kTile;
+      // the row sum is the sum of the sides' partial sums
+      exchange[side * kTile + row] = running_sum;
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(kSumReady));
+      if (mbar_wait(bar(kSumReady), 0U, abort_flag) && q0 + row < rows) {
+        float total = 0.0F;
 #pragma unroll
-        for (int q = 0; q < kTile / 8; ++q) {
-          uint4 packed;
-          packed.x = round_pair_bf16(accumulator[8 * q] * inverse, accumulator[8 * q + 1] * inverse);
-          packed.y = round_pair_bf16(accumulator[8 * q + 2] * inverse, accumulator[8 * q + 3] * inverse);
-          packed.z = round_pair_bf16(accumulator[8 * q + 4] * inverse, accumulator[8 * q + 5] * inverse);
-          packed.w = round_pair_bf16(accumulator[8 * q + 6] * inverse, accumulator[8 * q + 7] * inverse);
-          *reinterpret_cast<uint4 *>(out + 8 * q) = packed;
+        for (int other = 0; other < kSides; ++other) total += exchange[other * kTile + row];
+        const float inverse = 1.0F / total;
+        bf16 *const out = output + static_cast<std::size_t>(q0 + row) * (static_cast<std::size_t>(heads) * kTile) +
+                          static_cast<std::size_t>(head) * kTile + side * kSideColumns;
+#pragma unroll
+        for (int q = 0; q < kSideColumns / 8; ++q) {
+          uint4 word;
+          word.x = round_pair_bf16(accumulator[8 * q] * inverse, accumulator[8 * q + 1] * inverse);
+          word.y = round_pair_bf16(accumulator[8 * q + 2] * inverse, accumulator[8 * q + 3] * inverse);
+          word.z = round_pair_bf16(accumulator[8 * q + 4] * inverse, accumulator[8 * q + 5] * inverse);
+          word.w = round_pair_bf16(accumulator[8 * q + 6] * inverse, accumulator[8 * q + 7] * inverse);
+          *reinterpret_cast<uint4 *>(out + 8 * q) = word;
         }
       }
     }
