@@ -84,6 +84,11 @@ __host__ __device__ constexpr std::uint32_t instruction_descriptor(const bool b_
   return d;
 }
 
+__device__ __forceinline__ float max3(const float a, const float b, const float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
 __device__ __forceinline__ float fast_exp2(const float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -278,7 +283,8 @@ flash_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
       }
       float partial_max[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-      for (int i = 0; i < kSideColumns; ++i) partial_max[i % 4] = fmaxf(partial_max[i % 4], __uint_as_float(v[i]));
+      for (int i = 0; i < kSideColumns; i += 2)
+        partial_max[(i / 2) % 4] = max3(partial_max[(i / 2) % 4], __uint_as_float(v[i]), __uint_as_float(v[i + 1]));
       const float side_max = fmaxf(fmaxf(partial_max[0], partial_max[1]), fmaxf(partial_max[2], partial_max[3]));
       exchange[(s * kSides + side) * kTile + row] = side_max;
       __syncwarp();
