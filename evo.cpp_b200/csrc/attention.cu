@@ -299,11 +299,19 @@ int causal_attention_mma_sync(const void *query, const void *key_cache,
                             heads, head_dim, output, stream);
 }
 
+bool attention_decode_applicable(const void *query, const void *key_cache, const void *value_cache,
+                                 std::size_t rows, std::size_t total_keys, std::size_t heads,
+                                 std::size_t head_dim, const void *output);
+int attention_decode(const void *query, const void *key_cache, const void *value_cache, std::size_t rows,
+                     std::size_t total_keys, std::size_t heads, void *output, cudaStream_t stream);
+
 int causal_attention(const void *query, const void *key_cache,
                      const void *value_cache, const std::size_t rows,
                      const std::size_t total_keys, const std::size_t heads,
                      const std::size_t head_dim, void *output,
                      cudaStream_t stream) {
+  if (attention_decode_applicable(query, key_cache, value_cache, rows, total_keys, heads, head_dim, output))
+    return attention_decode(query, key_cache, value_cache, rows, total_keys, heads, output, stream);
   if (head_dim == 128 && query != nullptr && key_cache != nullptr && value_cache != nullptr &&
       output != nullptr &&
       flash_tcgen05_applicable(query, key_cache, value_cache, rows, total_keys, heads, output))

@@ -2,8 +2,8 @@
 // At these sizes a projection is a weight stream: every weight byte is read
 // once and the arithmetic is negligible, so the tensor-core tile kernel (which
 // launches one CTA per 128 x 256 tile and leaves most SMs idle) is replaced by
-// a kernel in which each warp owns a few weight rows, the lanes split K in
-// 16-byte chunks, and partial sums are folded with shuffles.  Same epilogue
+// a kernel in which a CTA owns a few weight rows, its threads split K in
+// 16-byte chunks, and partial sums are folded with shuffles and shared memory.  Same epilogue
 // contract as the tile kernel (scale, fused or separately rounded bias,
 // residual, gate over row-interleaved up-projections).
 #include <cuda_fp8.h>
@@ -16,7 +16,6 @@ namespace {
 
 constexpr int kThreads = 256;
 constexpr int kMaxRows = 8;
-constexpr int kColumnsPerWarp = 4;
 
 struct GemvParams {
   const void *x;       // [rows, K] BF16 or E4M3 codes
@@ -67,10 +66,14 @@ __device__ __forceinline__ bf16 gelu_round_small(const float x) {
   }
 }
 
-// kRows is a compile-time bound on the rows held in registers.
+constexpr int kColumnsPerWarp = 4;
+
+// Wide projections: each warp owns kColumnsPerWarp weight rows and its lanes
+// split K; there are enough warps to cover the latency without splitting K
+// across a CTA.  kRows is a compile-time bound on the rows held in registers.
 template <bool kFp8, int kRows>
 __global__ void __launch_bounds__(kThreads)
-gemv_kernel(const GemvParams p) {
+gemv_warp_kernel(const GemvParams p) {
   constexpr int kPerChunk = kFp8 ? 16 : 8;   // elements per 16-byte chunk
   const int warp = (blockIdx.x * kThreads + threadIdx.x) / 32;
   const int lane = threadIdx.x % 32;
@@ -97,6 +100,7 @@ gemv_kernel(const GemvParams p) {
   const std::size_t row_bytes = static_cast<std::size_t>(p.K) * (kFp8 ? 1 : 2);
   const unsigned char *const wb = static_cast<const unsigned char *>(p.w);
   const unsigned char *const xb = static_cast<const unsigned char *>(p.x);
+#pragma unroll(kRows <= 2 ? 2 : 1)
   for (int chunk = lane; chunk < chunks; chunk += 32) {
     uint4 wraw[kColumnsPerWarp];
 #pragma unroll
@@ -153,12 +157,123 @@ gemv_kernel(const GemvParams p) {
   }
 }
 
+// A CTA owns kColumns weight rows and its eight warps split K between them, so
+// the whole weight slab of the CTA (kColumns x K) is requested within the first
+// couple of loop iterations - at one row a projection is a latency problem as
+// much as a bandwidth one.  Per-warp partial sums are folded with shuffles,
+// then across warps through shared memory; the last step applies the same
+// epilogue as the tile kernel.  kRows is a compile-time bound on the rows held
+// in registers.
+constexpr int kColumns = 8;
+constexpr int kWarps = kThreads / 32;
+
+template <bool kFp8, int kRows>
+__global__ void __launch_bounds__(kThreads)
+gemv_kernel(const GemvParams p) {
+  constexpr int kPerChunk = kFp8 ? 16 : 8;   // elements per 16-byte chunk
+  __shared__ float partial[kWarps][kColumns][kRows];
+  const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+  const bool gated = p.gate_mode != 0;
+  // Output columns handled by this CTA.  When gated, the weight holds blocks
+  // of 128 first-projection rows followed by the matching 128 second-projection
+  // rows; an output column needs one row of each.
+  const int out_columns = gated ? p.N / 2 : p.N;
+  const int per_cta = gated ? kColumns / 2 : kColumns;
+  const int column0 = blockIdx.x * per_cta;
+  int weight_row[kColumns];
+#pragma unroll
+  for (int c = 0; c < kColumns; ++c) {
+    const int column = min(column0 + (gated ? c / 2 : c), out_columns - 1);
+    weight_row[c] = gated ? (column / 128) * 256 + column % 128 + (c % 2) * 128 : column;
+  }
+  float acc[kColumns][kRows];
+#pragma unroll
+  for (int c = 0; c < kColumns; ++c)
+#pragma unroll
+    for (int r = 0; r < kRows; ++r) acc[c][r] = 0.0F;
+  const int chunks = p.K / kPerChunk;
+  const std::size_t row_bytes = static_cast<std::size_t>(p.K) * (kFp8 ? 1 : 2);
+  const unsigned char *const wb = static_cast<const unsigned char *>(p.w);
+  const unsigned char *const xb = static_cast<const unsigned char *>(p.x);
+#pragma unroll(kRows <= 2 ? 2 : 1)
+  for (int chunk = threadIdx.x; chunk < chunks; chunk += kThreads) {
+    uint4 wraw[kColumns];
+#pragma unroll
+    for (int c = 0; c < kColumns; ++c)
+      wraw[c] = __ldcs(reinterpret_cast<const uint4 *>(wb + weight_row[c] * row_bytes) + chunk);
+#pragma unroll
+    for (int r = 0; r < kRows; ++r) {
+      if (r < p.rows) {
+        float xv[kPerChunk];
+        unpack16<kFp8>(__ldg(reinterpret_cast<const uint4 *>(xb + r * row_bytes) + chunk), xv);
+#pragma unroll
+        for (int c = 0; c < kColumns; ++c) {
+          float wv[kPerChunk];
+          unpack16<kFp8>(wraw[c], wv);
+#pragma unroll
+          for (int i = 0; i < kPerChunk; ++i) acc[c][r] = fmaf(xv[i], wv[i], acc[c][r]);
+        }
+      }
+    }
+  }
+#pragma unroll
+  for (int c = 0; c < kColumns; ++c)
+#pragma unroll
+    for (int r = 0; r < kRows; ++r) {
+#pragma unroll
+      for (int offset = 16; offset > 0; offset /= 2)
+        acc[c][r] += __shfl_xor_sync(0xffffffffU, acc[c][r], offset);
+      if (lane == 0) partial[warp][c][r] = acc[c][r];
+    }
+  __syncthreads();
+  // one thread per (row, output column of the CTA)
+  const int item = threadIdx.x;
+  if (item >= per_cta * kRows) return;
+  const int r = item / per_cta, local = item % per_cta;
+  const int column = column0 + local;
+  if (r >= p.rows || column >= out_columns) return;
+  const auto total = [&](const int c) {
+    float sum = 0.0F;
+#pragma unroll
+    for (int w = 0; w < kWarps; ++w) sum += partial[w][c][r];
+    return sum;
+  };
+  bf16 *const out_row = p.out + static_cast<std::size_t>(r) * out_columns;
+  if (gated) {
+    const float first = total(2 * local) * p.alpha, second = rbf(total(2 * local + 1) * p.alpha);
+    const float activated = p.gate_mode == 2 ? bf2f(gelu_round_small(first)) : rbf(first);
+    out_row[column] = f2bf(activated * second);
+  } else {
+    float value = total(local) * p.alpha;
+    if (p.bias_mode == 1) value += bf2f(p.bias[column]);
+    value = rbf(value);
+    if (p.bias_mode == 2) value = rbf(value + bf2f(p.bias[column]));
+    if (p.residual != nullptr)
+      value = rbf(value + bf2f(p.residual[static_cast<std::size_t>(r) * out_columns + column]));
+    out_row[column] = f2bf(value);
+  }
+}
+
 template <bool kFp8>
 int launch_gemv(const GemvParams &p, cudaStream_t stream) {
   const int out_columns = p.gate_mode != 0 ? p.N / 2 : p.N;
-  const int per_warp = p.gate_mode != 0 ? kColumnsPerWarp / 2 : kColumnsPerWarp;
-  const int warps = (out_columns + per_warp - 1) / per_warp;
-  const unsigned int grid = static_cast<unsigned int>((warps + kThreads / 32 - 1) / (kThreads / 32));
+  // enough warps for the warp-per-rows form?  (about 16 per SM)
+  const int warp_columns = p.gate_mode != 0 ? kColumnsPerWarp / 2 : kColumnsPerWarp;
+  const int warps = (out_columns + warp_columns - 1) / warp_columns;
+  if (warps >= kSmCount * 16) {
+    const unsigned int grid = static_cast<unsigned int>((warps + kThreads / 32 - 1) / (kThreads / 32));
+    if (p.rows == 1)
+      gemv_warp_kernel<kFp8, 1><<<grid, kThreads, 0, stream>>>(p);
+    else if (p.rows <= 2)
+      gemv_warp_kernel<kFp8, 2><<<grid, kThreads, 0, stream>>>(p);
+    else if (p.rows <= 4)
+      gemv_warp_kernel<kFp8, 4><<<grid, kThreads, 0, stream>>>(p);
+    else
+      gemv_warp_kernel<kFp8, 8><<<grid, kThreads, 0, stream>>>(p);
+    return check_launch("small-batch projection kernel");
+  }
+  const int per_cta = p.gate_mode != 0 ? kColumns / 2 : kColumns;
+  const unsigned int grid = static_cast<unsigned int>((out_columns + per_cta - 1) / per_cta);
   if (p.rows == 1)
     gemv_kernel<kFp8, 1><<<grid, kThreads, 0, stream>>>(p);
   else if (p.rows <= 2)

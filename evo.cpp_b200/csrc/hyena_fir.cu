@@ -358,6 +358,60 @@ __global__ void advance_cache_kernel(const bf16 *__restrict__ input,
   }
 }
 
+// Single-step form (cached decode) for long filters with a full history: one
+// warp per channel.  Lane L owns history entries L, 32+L, 64+L, ... - exactly
+// the terms[] slots of fir_step_kernel - and the 32-slot tree is folded with
+// shuffles in the same order, so the result is bit-identical; the history row
+// is read once, coalesced, and written back shifted by one with the new sample
+// appended, which replaces the separate cache-advance launch.
+__global__ void __launch_bounds__(kThreads)
+fir_decode_warp_kernel(const bf16 *__restrict__ input, const void *__restrict__ filter,
+                       const bool filter_is_f32, const bf16 *__restrict__ bias,
+                       const bool multiply_bias, float *__restrict__ cache, bf16 *__restrict__ output,
+                       const int channels, const int channels_per_group, const int taps,
+                       const bool cross_correlation) {
+  const int channel = (blockIdx.x * kThreads + threadIdx.x) / 32;
+  const int lane = threadIdx.x % 32;
+  if (channel >= channels) return;
+  const int cache_size = taps - 1;
+  const std::size_t group = channel / channels_per_group;
+  float *const row = cache + static_cast<std::size_t>(channel) * cache_size;
+  float history[4];  // taps <= 128
+  float term = 0.0F;
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    const int a = 32 * k + lane;
+    history[k] = a < cache_size ? row[a] : 0.0F;
+    if (a < cache_size) {
+      const int tap = cross_correlation ? a : cache_size - a;
+      term = __fadd_rn(term, __fmul_rn(history[k], load_filter(filter, filter_is_f32, group * taps + tap)));
+    }
+  }
+#pragma unroll
+  for (int offset = 16; offset != 0; offset /= 2) {
+    const float other = __shfl_down_sync(0xffffffffU, term, offset);
+    if (lane < offset) term = __fadd_rn(term, other);
+  }
+  const float current = bf2f(input[channel]);
+  __syncwarp();  // every lane has read its entries before any is overwritten
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    const int a = 32 * k + lane;
+    if (a >= 1 && a < cache_size) row[a - 1] = history[k];
+  }
+  if (lane == 0) {
+    row[cache_size - 1] = current;
+    const int current_tap = cross_correlation ? cache_size : 0;
+    float total = __fadd_rn(
+        __fmul_rn(current, load_filter(filter, filter_is_f32, group * taps + current_tap)), term);
+    if (bias != nullptr) {
+      const float b = bf2f(bias[channel]);
+      total = __fadd_rn(total, multiply_bias ? __fmul_rn(b, current) : b);
+    }
+    output[channel] = f2bf(total);
+  }
+}
+
 unsigned int flat_grid(const std::size_t items) {
   const std::size_t blocks = (items + kThreads - 1) / kThreads;
   const std::size_t cap = static_cast<std::size_t>(kSmCount) * 16;
@@ -474,6 +528,13 @@ int fir_step(const void *input, const void *filter, const bool filter_is_f32,
       cache == nullptr || channels == 0 || groups == 0 || taps < 2 ||
       channels % groups != 0 || cache_length > taps - 1 || length == 0)
     return fail(kInvalidArgument, "FIR step arguments are invalid");
+  if (length == 1 && taps > 33 && taps <= 128 && cache_length == taps - 1 && channels <= 0x3fffffU) {
+    fir_decode_warp_kernel<<<ceil_div_u(channels * 32, kThreads), kThreads, 0, stream>>>(
+        static_cast<const bf16 *>(input), filter, filter_is_f32, static_cast<const bf16 *>(bias),
+        multiply_bias, cache, static_cast<bf16 *>(output), static_cast<int>(channels),
+        static_cast<int>(channels / groups), static_cast<int>(taps), cross_correlation);
+    return check_launch("FIR decode kernel");
+  }
   fir_step_kernel<<<flat_grid(length * channels), kThreads, 0, stream>>>(
       static_cast<const bf16 *>(input), filter, filter_is_f32,
       static_cast<const bf16 *>(bias), multiply_bias, cache,

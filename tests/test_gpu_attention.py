@@ -58,7 +58,8 @@ def test_split_rope_append(ops, oracle, rows, heads, head_dim, offset, scale, he
 
 @pytest.mark.parametrize("rows,prefix,heads,head_dim", [
     (64, 0, 2, 128), (200, 0, 3, 128), (129, 37, 2, 128), (16, 300, 2, 128), (700, 0, 1, 128),
-    (9, 0, 3, 8), (5, 11, 2, 4), (1, 40, 2, 128)])
+    (9, 0, 3, 8), (5, 11, 2, 4), (1, 40, 2, 128), (1, 2000, 3, 128), (5, 1000, 2, 128), (8, 0, 2, 128),
+    (3, 5, 1, 128)])
 def test_causal_attention(ops, oracle, rows, prefix, heads, head_dim):
     """Tensor-core flash kernel (head 128, >= 16 rows) and the row-wise kernel.
     Upstream gates its FlashAttention path against CPU attention at tolerance
