@@ -475,6 +475,22 @@ evo_status evo_b200_context_prefill_device(evo_context *context, const uint32_t 
   });
 }
 
+evo_status evo_b200_context_continue_device(evo_context *context, const uint32_t *device_tokens,
+                                            size_t rows, const void **device_logits_out) {
+  return protect([&]() -> int {
+    if (context == nullptr) return fail(evob::kInvalidArgument, "context is required");
+    if (context->failed || context->context->poisoned())
+      return fail(evob::kInvalidArgument, "context was invalidated by an earlier failure");
+    const int status = context->context->continue_device(device_tokens, rows);
+    if (status != kOk) {
+      if (context->context->poisoned()) context->failed = true;
+      return status;
+    }
+    if (device_logits_out != nullptr) *device_logits_out = context->context->device_logits();
+    return kOk;
+  });
+}
+
 void *evo_b200_context_stream(const evo_context *context) {
   return context == nullptr ? nullptr : context->context->first_stream();
 }

@@ -43,6 +43,11 @@ struct DeviceGuard {
 };
 }  // namespace
 
+// Rows of history kept in front of a continuation chunk inside the activation
+// buffers (>= the longest filter's reach of 127 + 2 featurizer rows, and a
+// multiple of 16 so the tensor-core FIR tiles keep their alignment).
+constexpr std::size_t kHistoryPad = 144;
+
 struct LayerState {
   float *short_cache = nullptr;  // [3D, short_taps-1]
   float *inner_cache = nullptr;  // [D, taps-1]
@@ -155,7 +160,7 @@ int Context::create(std::shared_ptr<ModelWeights> weights, const std::size_t con
   context->context_size_ = context_size;
   context->arena_rows_ = std::min(
       context_size, c.test_fixture && !full_arena_for_fixtures ? kFixtureArenaRows : kArenaRows);
-  const std::size_t T = context->arena_rows_, D = c.width, I = c.inner_width;
+  const std::size_t T = context->arena_rows_ + kHistoryPad, D = c.width, I = c.inner_width;
   const bool fused_gate = !weights->stages.empty() && !weights->stages[0]->layers.empty() &&
                           weights->stages[0]->layers[0].l12 != nullptr;
   for (const auto &stage_weights : weights->stages) {
@@ -202,12 +207,14 @@ int Context::create(std::shared_ptr<ModelWeights> weights, const std::size_t con
       }
       EVOB_TRY(stage->allocate(&p, 3 * D * (c.short_taps - 1) * 4, cache));
       state.short_cache = static_cast<float *>(p);
-      if (weights->stages.size() > 1 || weights->slice_count > 1) {
+      {
         const std::size_t taps = type == MixerType::kHcs ? c.hcs_taps
                                  : type == MixerType::kHcm ? c.hcm_taps : 1;
         // the fused kernels stage a 16-row-aligned halo plus the featurizer's two rows
-        state.history_rows = (taps + 15) / 16 * 16 + (c.short_taps - 1);
+        state.history_rows = std::min(kHistoryPad, (taps + 15) / 16 * 16 + (c.short_taps - 1));
         EVOB_TRY(stage->allocate(&state.history, state.history_rows * 3 * D * 2 + 16, cache));
+        if (cudaMemset(state.history, 0, state.history_rows * 3 * D * 2) != cudaSuccess)
+          return fail(kCuda, "cannot clear the projection history");
       }
       if (type == MixerType::kHcl) {
         EVOB_TRY(stage->allocate(&p, D * c.state_size * 4, cache));
@@ -313,7 +320,7 @@ void Context::read_profile(double (&milliseconds)[kProfileCategories],
 // straight from those earlier rows.
 int Context::run_stage(Stage &s, const std::size_t rows, const Mode mode,
                        const long capture_layer, std::vector<float> *captured,
-                       const std::size_t window_begin) {
+                       const std::size_t window_begin, const std::size_t window_position) {
   const ModelConfig &c = weights_->config;
   const std::size_t D = c.width, I = c.inner_width;
   const bool window = mode == Mode::kWindow;
@@ -351,7 +358,7 @@ int Context::run_stage(Stage &s, const std::size_t rows, const Mode mode,
       EVOB_OP(fp8 ? kCatGemmFp8 : kCatGemmBf16, linear(a, stream));
     }
     if (attention) {
-      const std::size_t prefix = window ? window_begin : (initial ? 0 : position_);
+      const std::size_t prefix = window ? window_position : (initial ? 0 : position_);
       EVOB_OP(kCatAttention, split_rope_append(s.projection, w.inverse_frequency, rows, c.heads, c.head_dim(),
                                  prefix, c.rope_scale, false, s.query, state.key_cache,
                                  state.value_cache, context_size_, stream));
@@ -366,7 +373,7 @@ int Context::run_stage(Stage &s, const std::size_t rows, const Mode mode,
     } else if (initial) {
       unsigned char *const projection_base =
           static_cast<unsigned char *>(rewind(s.projection, D * 6));
-      if (window && state.history != nullptr && window_begin > 0) {
+      if (window && state.history != nullptr && window_position > 0 && window_begin > 0) {
         // bring this block's own history back under the window
         const std::size_t have = std::min(state.history_rows, window_begin);
         if (cudaMemcpyAsync(projection_base + (window_begin - have) * D * 6,
@@ -389,7 +396,7 @@ int Context::run_stage(Stage &s, const std::size_t rows, const Mode mode,
         a.short_cache = stateless ? nullptr : state.short_cache;
         a.length = window_begin + rows;
         a.row_begin = window_begin;
-        a.continue_from_state = window && window_begin > 0;
+        a.continue_from_state = window && window_position > 0;
         a.width = D;
         a.modes = c.state_size;
         EVOB_OP(kCatModal, modal_prefill(a, stream));
@@ -412,6 +419,16 @@ int Context::run_stage(Stage &s, const std::size_t rows, const Mode mode,
         a.inner_cache = stateless ? nullptr : state.inner_cache;
         a.short_cache = stateless ? nullptr : state.short_cache;
         EVOB_OP(hcs ? kCatShortFir : kCatMediumFir, gated_fir_prefill(a, stream));
+      }
+      if (!window && !stateless && state.history != nullptr) {
+        // leave the tail of this prompt as history for a later continuation chunk
+        const std::size_t keep = std::min(state.history_rows, rows);
+        if ((keep < state.history_rows &&
+             cudaMemsetAsync(state.history, 0, (state.history_rows - keep) * D * 6, stream) != cudaSuccess) ||
+            cudaMemcpyAsync(static_cast<unsigned char *>(state.history) + (state.history_rows - keep) * D * 6,
+                            projection_base + (rows - keep) * D * 6, keep * D * 6, cudaMemcpyDeviceToDevice,
+                            stream) != cudaSuccess)
+          return fail(kCuda, "projection history save failed");
       }
       if (window && state.history != nullptr) {
         const std::size_t end = window_begin + rows;
@@ -560,7 +577,7 @@ int Context::run_wavefront(const std::size_t rows, const Mode /*mode*/, const lo
           return fail(kCuda, "stage hand-off failed");
       }
       stage.shift_rows(static_cast<long>(begin), D, I);
-      const int status = run_stage(stage, count, Mode::kWindow, -1, nullptr, begin);
+      const int status = run_stage(stage, count, Mode::kWindow, -1, nullptr, begin, begin);
       stage.shift_rows(-static_cast<long>(begin), D, I);
       if (status != kOk) return status;
       if (cudaEventRecord(stage.done, stage.stream) != cudaSuccess)
@@ -593,6 +610,25 @@ int Context::forward(const std::uint32_t *host_tokens, const std::uint32_t *devi
         return fail(kInvalidArgument, "token ID exceeds model vocabulary");
   int status = kOk;
   Stage &first = *stages_.front();
+  // A continuation chunk of more than a few rows runs through the fused
+  // prefill kernels as a row window: its rows sit kHistoryPad rows into the
+  // activation buffers and every Hyena block puts its own last projection rows
+  // in front of them.  (Short chunks and the exact cached-attention profile
+  // keep the step kernels.)
+  const bool continuation_window =
+      mode == Mode::kContinue && rows >= 16 && !cached_attention_ && capture_layer < 0;
+  struct ShiftBack {
+    Context *context;
+    bool active;
+    ~ShiftBack() {
+      if (!active) return;
+      const ModelConfig &config = context->weights_->config;
+      for (auto &stage : context->stages_)
+        stage->shift_rows(-static_cast<long>(kHistoryPad), config.width, config.inner_width);
+    }
+  } shift_back{this, continuation_window};
+  if (continuation_window)
+    for (auto &stage : stages_) stage->shift_rows(static_cast<long>(kHistoryPad), c.width, c.inner_width);
   {
     DeviceGuard guard(first.device);
     if (host_tokens != nullptr) {
@@ -618,7 +654,10 @@ int Context::forward(const std::uint32_t *host_tokens, const std::uint32_t *devi
                               rows * c.width * 2, stage.stream) != cudaSuccess)
         status = fail(kCuda, "stage hand-off failed");
     }
-    if (status == kOk) status = run_stage(stage, rows, mode, capture_layer, captured);
+    if (status == kOk)
+      status = continuation_window
+                   ? run_stage(stage, rows, Mode::kWindow, -1, nullptr, kHistoryPad, position_)
+                   : run_stage(stage, rows, mode, capture_layer, captured);
     if (status == kOk && cudaEventRecord(stage.done, stage.stream) != cudaSuccess)
       status = fail(kCuda, "stage hand-off failed");
   }
@@ -704,7 +743,7 @@ int Context::slice_run(const std::size_t row_begin, const std::size_t rows) {
   DeviceGuard guard(stage.device);
   state_valid_ = false;  // decode across processes is not provided
   stage.shift_rows(static_cast<long>(row_begin), c.width, c.inner_width);
-  const int status = run_stage(stage, rows, Mode::kWindow, -1, nullptr, row_begin);
+  const int status = run_stage(stage, rows, Mode::kWindow, -1, nullptr, row_begin, row_begin);
   stage.shift_rows(-static_cast<long>(row_begin), c.width, c.inner_width);
   if (status != kOk) {
     healthy_ = false;
@@ -766,6 +805,12 @@ int Context::prefill_embedding(const std::vector<std::uint32_t> &tokens, const s
   std::vector<float> logits;
   return forward(tokens.data(), nullptr, tokens.size(), Mode::kStateless, &logits,
                  static_cast<long>(layer), hidden);
+}
+int Context::continue_device(const std::uint32_t *device_tokens, const std::size_t rows) {
+  if (device_tokens == nullptr) return fail(kInvalidArgument, "token buffer is null");
+  if (state_valid_ && cached_attention_)
+    return fail(kInvalidArgument, "chunk continuation is not available after a cached prefill");
+  return forward(nullptr, device_tokens, rows, Mode::kContinue, nullptr, -1, nullptr);
 }
 int Context::prefill_device(const std::uint32_t *device_tokens, const std::size_t rows,
                             const bool stateless) {

@@ -126,6 +126,8 @@ class Context {
   // Device-resident variant used by the benchmark: tokens already on the
   // device of stage 0, logits left on the device (BF16 [rows, vocab]).
   int prefill_device(const std::uint32_t *device_tokens, std::size_t rows, bool stateless);
+  // Next chunk of the same sequence, same conventions (needs a non-stateless prefill before).
+  int continue_device(const std::uint32_t *device_tokens, std::size_t rows);
   const void *device_logits() const;
   void *first_stream() const;
 
@@ -168,7 +170,8 @@ class Context {
               std::size_t rows, Mode mode, std::vector<float> *logits, long capture_layer,
               std::vector<float> *captured);
   int run_stage(Stage &stage, std::size_t rows, Mode mode, long capture_layer,
-                std::vector<float> *captured, std::size_t window_begin = 0);
+                std::vector<float> *captured, std::size_t window_begin = 0,
+                std::size_t window_position = 0);
   // Chunk wavefront over the pipeline stages: chunk j runs on stage s while
   // chunk j+1 runs on stage s-1 (legal because every mixer carries causal
   // state).  Used for initial prefills on more than one stage.

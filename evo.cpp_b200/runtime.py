@@ -93,6 +93,7 @@ class EvoLibrary:
         self.has_extensions = hasattr(lib, "evo_b200_context_prefill_device")
         if self.has_extensions:
             lib.evo_b200_context_prefill_device.argtypes = [V, V, Z, I, ctypes.POINTER(V)]
+            lib.evo_b200_context_continue_device.argtypes = [V, V, Z, ctypes.POINTER(V)]
             lib.evo_b200_context_stream.restype = V
             lib.evo_b200_context_stream.argtypes = [V]
             lib.evo_b200_context_synchronize.argtypes = [V]
@@ -239,6 +240,12 @@ class Context:
         out = ctypes.c_void_p()
         self.library.check(self.library.lib.evo_b200_context_prefill_device(
             self.handle, device_tokens, rows, int(stateless), ctypes.byref(out)))
+        return out.value
+
+    def continue_device(self, device_tokens: int, rows: int) -> int:
+        out = ctypes.c_void_p()
+        self.library.check(self.library.lib.evo_b200_context_continue_device(
+            self.handle, device_tokens, rows, ctypes.byref(out)))
         return out.value
 
     def stream(self) -> int:

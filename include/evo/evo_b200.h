@@ -33,6 +33,14 @@ EVO_API evo_status evo_b200_context_prefill_device(evo_context *context,
                                                    const uint32_t *device_tokens, size_t rows,
                                                    int stateless,
                                                    const void **device_logits_out);
+/* The next `rows` tokens of the same sequence (after a non-stateless prefill or
+ * an earlier continuation): same conventions as evo_b200_context_prefill_device.
+ * This is what evo_context_prefill does for every chunk after the first when a
+ * prompt is longer than the activation capacity (upstream:
+ * PipelineModel::prefill_chunk, include/evo/cuda/model.hpp:150-170). */
+EVO_API evo_status evo_b200_context_continue_device(evo_context *context,
+                                                    const uint32_t *device_tokens, size_t rows,
+                                                    const void **device_logits_out);
 /* cudaStream_t of pipeline stage 0 (where a forward pass starts and ends). */
 EVO_API void *evo_b200_context_stream(const evo_context *context);
 /* Waits for all stages and reports asynchronous kernel errors. */

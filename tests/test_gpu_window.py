@@ -97,3 +97,41 @@ def test_wavefront_pipeline_matches_single_gpu(pkg, tmp_path_factory):
         step_single, step_piped = single.decode(token), piped.decode(token)
         assert np.abs(step_single - step_piped).mean() < 0.05
         token = int(step_single.argmax())
+
+
+def test_chunk_continuation_matches_single_prefill(pkg, tmp_path_factory):
+    """A prompt fed as 700 + 512 + 100 + 188 rows (continuation chunks run through
+    the fused kernels as row windows behind their carried history) against the
+    same prompt in one pass; decode continues from either."""
+    rt = importlib.import_module("evo_cpp_b200.runtime")
+    art = importlib.import_module("evo_cpp_b200.artifact")
+    pipe = importlib.import_module("evo_cpp_b200.pipeline")
+    evo = rt.EvoLibrary(pkg.EVO_LIBRARY)
+    directory = tmp_path_factory.mktemp("chunks")
+    spec = art.fixture_spec(width=256, layers=8, heads=2, inner=512, hcs_groups=16, hcm_groups=16, fp8=True)
+    art.write_synthetic(directory / "model.safetensors", spec, seed=9, weight_std=0.05, filter_std=0.3)
+    rng = np.random.default_rng(31)
+    host_tokens = rng.choice(np.frombuffer(b"ACGT", np.uint8), 1500)
+    flags = rt.CONTEXT_FLAG_FULL_ARENA | rt.CONTEXT_FLAG_TENSORCORE_FP8
+    model = evo.load(directory / "model.safetensors", devices=[0], flags=rt.MODEL_FLAG_ALLOW_SYNTHETIC)
+    whole = model.context(2048, flags)
+    expected = whole.prefill(bytes(host_tokens.tolist()))
+    tokens = torch.from_numpy(host_tokens.astype(np.int32)).cuda()
+    chunked = model.context(2048, flags)
+    chunked.prefill_device(tokens.data_ptr(), 700, stateless=False)
+    begin = 700
+    for count in (512, 100, 188):
+        logits_address = chunked.continue_device(tokens.data_ptr() + 4 * begin, count)
+        chunked.synchronize()
+        raw = torch.as_tensor(pipe.DeviceRows(logits_address, count, 512), device="cuda")
+        got = ((raw.to(torch.int32) & 0xFFFF) << 16).view(torch.float32).cpu().numpy().astype(np.float64)
+        want = expected[begin:begin + count].astype(np.float64)
+        cosine = (got * want).sum() / (np.linalg.norm(got) * np.linalg.norm(want))
+        assert cosine > 0.9995 and np.abs(got - want).mean() < 0.05, (begin, cosine, np.abs(got - want).mean())
+        begin += count
+    assert chunked.position == 1500
+    token = int(expected[-1].argmax())
+    for _ in range(3):
+        a, b = whole.decode(token), chunked.decode(token)
+        assert np.abs(a - b).mean() < 0.05
+        token = int(a.argmax())
