@@ -49,6 +49,23 @@ MODEL_ID = "evo2_7b"
 # GEMM FLOPs per token of the 7B shape (D=4096, I=11264, 32 blocks, vocab 512)
 WIDTH, INNER, LAYERS, VOCAB, HEADS = 4096, 11264, 32, 512, 32
 ATTENTION_LAYERS = 5
+SHAPE_TEXT = "Evo 2 7B-shaped StripedHyena2 (32 blocks, d_model 4096, FFN 11264, vocab 512)"
+
+# --model: the other shape BASELINE.json names (seed 2, 50 blocks, E4M3 Hyena projections)
+MODELS = {
+    "evo2_7b": dict(seed=1, width=4096, inner=11264, layers=32, heads=32, attention_layers=5, label="7B"),
+    "evo2_40b": dict(seed=2, width=8192, inner=22528, layers=50, heads=64, attention_layers=8, label="40B"),
+}
+
+
+def select_model(name: str) -> None:
+    global METRIC, SEED, MODEL_ID, WIDTH, INNER, LAYERS, HEADS, ATTENTION_LAYERS, SHAPE_TEXT
+    m = MODELS[name]
+    MODEL_ID, SEED = name, m["seed"]
+    WIDTH, INNER, LAYERS, HEADS, ATTENTION_LAYERS = m["width"], m["inner"], m["layers"], m["heads"], m["attention_layers"]
+    METRIC = f"{name}_shaped_batch1_prefill_tokens_per_second"
+    SHAPE_TEXT = (f"Evo 2 {m['label']}-shaped StripedHyena2 ({LAYERS} blocks, d_model {WIDTH}, FFN {INNER}, "
+                  f"vocab {VOCAB})")
 
 
 def load_package():
@@ -321,6 +338,32 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> None:
                             "ms_per_token": seconds / args.decode_tokens * 1e3}
             ctx.close()
 
+    # ---- a prompt longer than the activation capacity: 8,192-row chunks, the
+    # first as a prefill, the rest as continuations (KV caches and Hyena state
+    # carried); token ids resident on the device, one timed pass after a warm-up
+    long_prompt = None
+    if rank == 0 and args.long_tokens > tokens:
+        total = args.long_tokens
+        long_tokens = torch.from_numpy(tokens_for(7, total).astype(np.int32)).cuda()
+        ctx = model.context(total, flags)
+        long_stream = torch.cuda.ExternalStream(ctx.stream())
+
+        def run_long():
+            ctx.prefill_device(long_tokens.data_ptr(), tokens, False)
+            for begin in range(tokens, total, tokens):
+                ctx.continue_device(long_tokens.data_ptr() + 4 * begin, min(tokens, total - begin))
+
+        run_long()
+        ctx.synchronize()
+        begin_event, end_event = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        begin_event.record(long_stream)
+        run_long()
+        end_event.record(long_stream)
+        ctx.synchronize()
+        long_ms = begin_event.elapsed_time(end_event)
+        long_prompt = {"tokens": total, "chunk": tokens, "ms": long_ms, "tokens_per_second": total / (long_ms * 1e-3)}
+        ctx.close()
+
     # ---- layer pipeline of ONE sequence over several GPUs of this process
     # (chunk wavefront, stream-ordered peer copies; strong scaling of batch 1)
     pipeline = None
@@ -350,7 +393,7 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> None:
             "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "bf16 activations, e4m3 Hyena projections (tcgen05), f32 accumulate",
             "data": "synthetic",
-            "config": {"workload": f"Evo 2 7B-shaped StripedHyena2 (32 blocks, d_model 4096, FFN 11264, vocab 512), "
+            "config": {"workload": f"{SHAPE_TEXT}, "
                                    f"batch-1 stateless prefill of {tokens} uniform-ACGT tokens, profile b200-tc",
                        "model_id": MODEL_ID, "seed": SEED, "tokens": tokens,
                        "parallelism": "1 GPU" if world == 1 else f"{world} independent replicas (one sequence per GPU)",
@@ -364,6 +407,7 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> None:
             "roofline": roofline, "clocks": clocks.summary(),
             "cached_decode_after_1024_token_prompt": decode,
             "layer_pipeline": pipeline,
+            "long_prompt_chunked_prefill": long_prompt,
         }
         if world == 1 and not args.skip_cpu_baseline:
             line["cpu_baseline"] = cpu_baseline(args, rt)
@@ -469,6 +513,31 @@ def run_pipeline(args, rank: int, world: int, local_rank: int) -> None:
         bits = pinned_logits.numpy().astype(np.uint16).astype(np.uint32) << 16
         assert np.isfinite(bits.view(np.float32)).all()
 
+    # ---- a prompt longer than the activation capacity through the same pipeline:
+    # windows wrap around the hidden-row buffers, state is carried per stage
+    long_prompt = None
+    if args.long_tokens > tokens:
+        total = args.long_tokens
+        long_context = model.context(total, flags)
+        long_device_tokens = torch.from_numpy(tokens_for(7, total).astype(np.int32)).cuda()
+        long_stage = pipe.ContextStage(long_context, long_device_tokens)
+        long_driver = pipe.StagePipeline(long_stage, pipe.alias_hidden_rows(long_context, tokens, WIDTH, "cuda"),
+                                         rank, world, chunk=args.pipeline_chunk)
+        long_stream = torch.cuda.ExternalStream(long_context.stream())
+        with torch.cuda.stream(long_stream):
+            long_driver.step(total)
+            long_driver.drain()
+            long_context.synchronize()
+            barrier()
+            start.record(long_stream)
+            long_driver.step(total)
+            long_driver.drain()
+            stop.record(long_stream)
+            long_context.synchronize()
+            long_ms = elapsed_max(start, stop)
+        long_prompt = {"tokens": total, "ms": long_ms, "tokens_per_second": total / (long_ms * 1e-3),
+                       "windows": len(pipe.window_plan(total, world, args.pipeline_chunk))}
+
     totals = torch.tensor([sum(n for _, n in profile.values()) + (1 if rank == 0 else 0) * args.steps,
                            profile["gemm_bf16_tcgen05"][0], profile["gemm_e4m3_tcgen05"][0]],
                           dtype=torch.float64, device="cuda")
@@ -493,7 +562,7 @@ def run_pipeline(args, rank: int, world: int, local_rank: int) -> None:
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None,
             "dtype": "bf16 activations, e4m3 Hyena projections (tcgen05), f32 accumulate", "data": "synthetic",
-            "config": {"workload": f"Evo 2 7B-shaped StripedHyena2 (32 blocks, d_model 4096, FFN 11264, vocab 512), "
+            "config": {"workload": f"{SHAPE_TEXT}, "
                                    f"batch-1 stateless prefill of {tokens} uniform-ACGT tokens, profile b200-tc",
                        "model_id": MODEL_ID, "seed": SEED, "tokens": tokens,
                        "parallelism": f"pp{world}: one pipeline stage per rank, chunk wavefront, NCCL send/recv of "
@@ -515,6 +584,7 @@ def run_pipeline(args, rank: int, world: int, local_rank: int) -> None:
                          "operator_ms_per_step_summed_over_ranks": {
                              name: ms / args.steps for name, ms in zip(sorted(profile), per_operator.tolist()) if ms}},
             "clocks": clocks.summary(),
+            "long_prompt_chunked_prefill": long_prompt,
         }
         print(json.dumps(line))
     barrier()
@@ -557,9 +627,14 @@ def main() -> None:
                              "independent full replicas")
     parser.add_argument("--pipeline-chunk", type=int, default=0,
                         help="rows per wavefront window (0: about two windows per stage, 512..2048)")
+    parser.add_argument("--model", default="evo2_7b", choices=sorted(MODELS),
+                        help="model shape (the headline metric is quoted on evo2_7b)")
+    parser.add_argument("--long-tokens", type=int, default=0,
+                        help="also time a chunked prefill of this many tokens (> --tokens; 0 disables)")
     parser.add_argument("--decode-tokens", type=int, default=64,
                         help="cached-decode steps timed after a 1,024-token prompt (0 disables)")
     args = parser.parse_args()
+    select_model(args.model)
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))

@@ -373,6 +373,13 @@ int Context::run_stage(Stage &s, const std::size_t rows, const Mode mode,
     } else if (initial) {
       unsigned char *const projection_base =
           static_cast<unsigned char *>(rewind(s.projection, D * 6));
+      if (window && window_position == 0 && window_begin > 0) {
+        // first window of a sequence placed behind stale rows: its history is zeros
+        const std::size_t have = std::min(state.history_rows, window_begin);
+        if (cudaMemsetAsync(projection_base + (window_begin - have) * D * 6, 0, have * D * 6, stream) !=
+            cudaSuccess)
+          return fail(kCuda, "projection history clear failed");
+      }
       if (window && state.history != nullptr && window_position > 0 && window_begin > 0) {
         // bring this block's own history back under the window
         const std::size_t have = std::min(state.history_rows, window_begin);
@@ -716,60 +723,74 @@ int Context::forward(const std::uint32_t *host_tokens, const std::uint32_t *devi
   return kOk;
 }
 
-void *Context::slice_hidden() const { return stages_.front()->hidden; }
+// Sequence position p of a sliced context lives at row kHistoryPad +
+// p % activation_capacity of the activation buffers: windows of a prompt that
+// fits the arena keep distinct rows (sends of earlier windows may still be in
+// flight), longer prompts wrap around, and every Hyena block finds room for its
+// carried history in front of the window.  slice_hidden() points at the row of
+// position 0.
+void *Context::slice_hidden() const {
+  return static_cast<unsigned char *>(stages_.front()->hidden) + kHistoryPad * weights_->config.width * 2;
+}
 
-int Context::slice_embed(const std::uint32_t *device_tokens, const std::size_t row_begin,
+int Context::slice_embed(const std::uint32_t *device_tokens, const std::size_t position,
                          const std::size_t rows) {
   Stage &stage = *stages_.front();
   if (!healthy_) return fail(kInvalidArgument, "context was invalidated by an earlier failure");
-  if (device_tokens == nullptr || rows == 0 || row_begin + rows > arena_rows_ ||
+  const std::size_t offset = position % arena_rows_;
+  if (device_tokens == nullptr || rows == 0 || offset + rows > arena_rows_ ||
       stage.weights->embedding == nullptr || stage.weights->layer_begin != 0)
-    return fail(kInvalidArgument, "slice_embed needs the first slice, a token buffer and rows inside the arena");
+    return fail(kInvalidArgument, "slice_embed needs the first slice, a token buffer and a window inside the arena");
   DeviceGuard guard(stage.device);
   return embedding(device_tokens, stage.weights->embedding, rows, weights_->config.width,
-                   static_cast<unsigned char *>(stage.hidden) + row_begin * weights_->config.width * 2,
+                   static_cast<unsigned char *>(stage.hidden) + (kHistoryPad + offset) * weights_->config.width * 2,
                    stage.stream);
 }
 
-int Context::slice_run(const std::size_t row_begin, const std::size_t rows) {
+int Context::slice_run(const std::size_t position, const std::size_t rows) {
   const ModelConfig &c = weights_->config;
   Stage &stage = *stages_.front();
   if (!healthy_) return fail(kInvalidArgument, "context was invalidated by an earlier failure");
   if (stages_.size() != 1 || weights_->slice_count < 2)
     return fail(kInvalidArgument, "slice_run needs a model loaded as one slice of a pipeline");
-  if (rows == 0 || row_begin + rows > arena_rows_ || row_begin + rows > context_size_ ||
-      (row_begin != 0 && row_begin != position_))
-    return fail(kInvalidArgument, "slice windows must be contiguous, ascending and inside the arena");
+  const std::size_t offset = position % arena_rows_;
+  if (rows == 0 || offset + rows > arena_rows_ || position + rows > context_size_ ||
+      (position != 0 && position != position_))
+    return fail(kInvalidArgument,
+                "slice windows must be contiguous, ascending, inside the context and not straddle the arena");
   DeviceGuard guard(stage.device);
   state_valid_ = false;  // decode across processes is not provided
-  stage.shift_rows(static_cast<long>(row_begin), c.width, c.inner_width);
-  const int status = run_stage(stage, rows, Mode::kWindow, -1, nullptr, row_begin, row_begin);
-  stage.shift_rows(-static_cast<long>(row_begin), c.width, c.inner_width);
+  const std::size_t first_row = kHistoryPad + offset;
+  stage.shift_rows(static_cast<long>(first_row), c.width, c.inner_width);
+  const int status = run_stage(stage, rows, Mode::kWindow, -1, nullptr, first_row, position);
+  stage.shift_rows(-static_cast<long>(first_row), c.width, c.inner_width);
   if (status != kOk) {
     healthy_ = false;
     return status;
   }
-  position_ = row_begin + rows;
+  position_ = position + rows;
   return kOk;
 }
 
-int Context::slice_head(const std::size_t row_begin, const std::size_t rows) {
+int Context::slice_head(const std::size_t position, const std::size_t rows) {
   const ModelConfig &c = weights_->config;
   Stage &stage = *stages_.front();
   if (!healthy_) return fail(kInvalidArgument, "context was invalidated by an earlier failure");
-  if (rows == 0 || row_begin + rows > arena_rows_ || stage.weights->embedding == nullptr ||
+  const std::size_t offset = position % arena_rows_;
+  if (rows == 0 || offset + rows > arena_rows_ || stage.weights->embedding == nullptr ||
       stage.weights->layer_end != c.layers)
-    return fail(kInvalidArgument, "slice_head needs the last slice and rows inside the arena");
+    return fail(kInvalidArgument, "slice_head needs the last slice and a window inside the arena");
   DeviceGuard guard(stage.device);
-  unsigned char *const hidden = static_cast<unsigned char *>(stage.hidden) + row_begin * c.width * 2;
-  unsigned char *const normalized = static_cast<unsigned char *>(stage.normalized) + row_begin * c.width * 2;
+  unsigned char *const hidden = static_cast<unsigned char *>(stage.hidden) + (kHistoryPad + offset) * c.width * 2;
+  unsigned char *const normalized =
+      static_cast<unsigned char *>(stage.normalized) + (kHistoryPad + offset) * c.width * 2;
   int status = rms_norm(hidden, stage.weights->final_norm, rows, c.width, c.epsilon, normalized, nullptr,
                         1.0F, stage.stream);
   if (status != kOk) return status;
   LinearArgs a;
   a.input = normalized;
   a.weight = stage.weights->embedding;  // tied head
-  a.output = static_cast<unsigned char *>(stage.logits) + row_begin * c.vocab * 2;
+  a.output = static_cast<unsigned char *>(stage.logits) + offset * c.vocab * 2;
   a.rows = rows;
   a.in_features = c.width;
   a.out_features = c.vocab;

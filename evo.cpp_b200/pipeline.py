@@ -22,14 +22,15 @@ from typing import Protocol
 
 def window_plan(rows: int, stages: int, chunk: int = 0) -> list[tuple[int, int]]:
     """[(begin, count)] windows of one prompt: about two windows per stage so the
-    pipeline fills, each a multiple of 256 rows in [512, 2048] so the
-    tensor-core tiles stay full.  Matches the in-process wavefront of the
-    runtime library."""
+    pipeline fills, each a power of two in [512, 2048] rows so the tensor-core
+    tiles stay full and the windows divide the activation capacity (prompts
+    longer than it wrap around)."""
     if rows <= 0 or stages <= 0:
         raise ValueError("rows and stages must be positive")
     if chunk <= 0:
-        chunk = (rows // (2 * stages) + 255) // 256 * 256
-        chunk = max(512, min(chunk, 2048))
+        chunk = 512
+        while chunk < 2048 and chunk * 2 * stages < rows:
+            chunk *= 2
     return [(begin, min(chunk, rows - begin)) for begin in range(0, rows, chunk)]
 
 
@@ -38,14 +39,15 @@ class Stage(Protocol):
 
     def embed(self, begin: int, count: int) -> None: ...   # first stage: tokens -> hidden rows
     def run(self, begin: int, count: int) -> None: ...     # this stage's blocks over hidden rows
-    def head(self, rows: int) -> None: ...                 # last stage: final norm + logits
+    def head(self, begin: int, count: int) -> None: ...    # last stage: final norm + logits of the window
 
 
 class StagePipeline:
     """Drives one rank's part of the wavefront.
 
     ``hidden`` is a [capacity, width] tensor aliasing the stage's hidden-row
-    buffer; windows are sent from and received into its row slices directly.
+    buffer; the window at sequence position p is sent from and received into
+    rows p % capacity .. directly (prompts longer than the capacity wrap).
     """
 
     def __init__(self, stage: Stage, hidden, rank: int, world: int, group=None, chunk: int = 0):
@@ -60,25 +62,28 @@ class StagePipeline:
         """One prompt of `rows` tokens through this rank's stage."""
         import torch.distributed as dist
 
-        if rows > self.hidden.shape[0]:
-            raise ValueError("prompt exceeds the hidden-row capacity")
+        capacity = self.hidden.shape[0]
+        plan = window_plan(rows, self.world, self.chunk)
+        if rows > capacity and any(capacity % count for _, count in plan[:-1]):
+            raise ValueError("windows of a prompt longer than the hidden-row capacity must divide it")
         if rows != self.last_rows:
             self.drain()       # a different window layout: nothing may still be in flight
             self.last_rows = rows
-        for begin, count in window_plan(rows, self.world, self.chunk):
-            pending = self.in_flight.pop(begin, None)
+        for begin, count in plan:
+            row = begin % capacity
+            pending = self.in_flight.pop(row, None)
             if pending is not None:
                 pending.wait()  # these rows are about to be overwritten
-            window = self.hidden[begin:begin + count]
+            window = self.hidden[row:row + count]
             if self.rank == 0:
                 self.stage.embed(begin, count)
             else:
                 dist.recv(window, src=self._peer(self.rank - 1), group=self.group)
             self.stage.run(begin, count)
             if self.rank + 1 < self.world:
-                self.in_flight[begin] = dist.isend(window, dst=self._peer(self.rank + 1), group=self.group)
-        if self.rank + 1 == self.world:
-            self.stage.head(rows)
+                self.in_flight[row] = dist.isend(window, dst=self._peer(self.rank + 1), group=self.group)
+            else:
+                self.stage.head(begin, count)
 
     def drain(self) -> None:
         for pending in self.in_flight.values():
@@ -124,5 +129,5 @@ class ContextStage:
     def run(self, begin: int, count: int) -> None:
         self.context.slice_run(begin, count)
 
-    def head(self, rows: int) -> None:
-        self.logits_address = self.context.slice_head(0, rows)
+    def head(self, begin: int, count: int) -> None:
+        self.logits_address = self.context.slice_head(begin, count)

@@ -79,24 +79,28 @@ EVO_API evo_status evo_b200_context_stage_info(const evo_context *context, size_
  * embedding, the last slice the tied head and final norm).  A context of such a
  * model serves windowed prefills only: whole-model calls are refused.
  *
- * Per window of rows [row_begin, row_begin + rows), in ascending contiguous
- * order starting at 0, all enqueued on evo_b200_context_stream():
+ * Per window of `rows` tokens starting at sequence position `position`, in
+ * ascending contiguous order starting at 0, all enqueued on
+ * evo_b200_context_stream():
  *   first slice:  slice_embed(tokens) -> slice_run -> send hidden rows
  *   middle:       receive hidden rows -> slice_run -> send hidden rows
- *   last slice:   receive hidden rows -> slice_run; after the last window
- *                 slice_head(0, total) leaves BF16 logits [total, vocab] on
- *                 the device.
- * evo_b200_context_slice_hidden is the [activation rows, width] BF16 buffer
- * the rows are read from and received into (row r at byte r * width * 2).
+ *   last slice:   receive hidden rows -> slice_run -> slice_head, which leaves
+ *                 the window's BF16 logits on the device.
+ * Position p lives at row p % capacity of evo_b200_context_slice_hidden (a
+ * [capacity, width] BF16 buffer, capacity = the context's activation rows) and
+ * of the logits buffer; a window may not straddle the end of that buffer, so
+ * prompts longer than the capacity use windows that divide it.  State (KV
+ * caches, FIR histories, modal states) is carried from window to window.
  * slice_embed's device_tokens points at the ids of the window (rows uint32). */
 EVO_API evo_status evo_b200_model_load_slice(const char *path, int32_t device, size_t slice_index,
                                              size_t slice_count, uint32_t flags,
                                              evo_model **model_out);
 EVO_API evo_status evo_b200_context_slice_embed(evo_context *context,
-                                                const uint32_t *device_tokens, size_t row_begin,
+                                                const uint32_t *device_tokens, size_t position,
                                                 size_t rows);
-EVO_API evo_status evo_b200_context_slice_run(evo_context *context, size_t row_begin, size_t rows);
-EVO_API evo_status evo_b200_context_slice_head(evo_context *context, size_t row_begin, size_t rows,
+EVO_API evo_status evo_b200_context_slice_run(evo_context *context, size_t position, size_t rows);
+/* *device_logits_out: start of the logits buffer (row = position % capacity). */
+EVO_API evo_status evo_b200_context_slice_head(evo_context *context, size_t position, size_t rows,
                                                const void **device_logits_out);
 EVO_API void *evo_b200_context_slice_hidden(const evo_context *context);
 

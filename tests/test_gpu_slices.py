@@ -65,6 +65,29 @@ def test_three_slices_on_one_gpu_match_the_whole_model(pkg, tmp_path_factory):
     cosine = (a * e).sum() / (np.linalg.norm(a) * np.linalg.norm(e))
     assert cosine > 0.9995 and np.abs(a - e).mean() < 0.05, (cosine, np.abs(a - e).mean())
 
+    # a prompt longer than the activation capacity (8 rows for fixtures without the
+    # full-arena flag): every window wraps around to the same rows
+    small = [model.context(64, rt.CONTEXT_FLAG_TENSORCORE_FP8) for model in slices]
+    small_hidden = [pipe.alias_hidden_rows(c, 8, width, "cuda") for c in small]
+    short_expected = evo.load(path, devices=[0], flags=rt.MODEL_FLAG_ALLOW_SYNTHETIC).context(
+        64, rt.CONTEXT_FLAG_TENSORCORE_FP8).prefill(bytes(host_tokens[:50].tolist()))
+    collected = np.zeros((50, 512), np.float32)
+    for begin in range(0, 50, 8):
+        count = min(8, 50 - begin)
+        small[0].slice_embed(tokens.data_ptr() + 4 * begin, begin, count)
+        for index, context in enumerate(small):
+            if index > 0:
+                small[index - 1].synchronize()
+                with torch.cuda.stream(torch.cuda.ExternalStream(context.stream())):
+                    small_hidden[index][:count].copy_(small_hidden[index - 1][:count])
+            context.slice_run(begin, count)
+        address = small[2].slice_head(begin, count)
+        small[2].synchronize()
+        window = torch.as_tensor(pipe.DeviceRows(address, 8, 512), device="cuda")[:count]
+        collected[begin:begin + count] = bf16_rows(window.to(torch.int32) & 0xFFFF)
+    a, e = collected.astype(np.float64), short_expected.astype(np.float64)
+    assert (a * e).sum() / (np.linalg.norm(a) * np.linalg.norm(e)) > 0.9995 and np.abs(a - e).mean() < 0.05
+
     # misuse is refused with a clear status, and leaves the context usable
     with pytest.raises(rt.EvoError):
         contexts[1].slice_embed(tokens.data_ptr(), 0, 16)       # not the first slice

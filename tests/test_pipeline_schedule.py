@@ -23,7 +23,9 @@ def test_window_plan_covers_the_prompt(pkg):
         assert all(plan[i][0] + plan[i][1] == plan[i + 1][0] for i in range(len(plan) - 1))
         assert all(count % 256 == 0 and 512 <= count <= 2048 for _, count in plan[:-1])
     assert pipeline.window_plan(8192, 2) == [(i * 2048, 2048) for i in range(4)]
+    assert pipeline.window_plan(8192, 4) == [(i * 1024, 1024) for i in range(8)]
     assert pipeline.window_plan(8192, 8) == [(i * 512, 512) for i in range(16)]
+    assert all(8192 % count == 0 for _, count in pipeline.window_plan(131072, 8))
     assert pipeline.window_plan(1000, 2, chunk=300) == [(0, 300), (300, 300), (600, 300), (900, 100)]
     with pytest.raises(ValueError):
         pipeline.window_plan(0, 2)
@@ -43,22 +45,26 @@ class RunningSumStage:
     # blocks of this stage: y[t] = (rank + 2) * x[t] + carry, carry += sum of the window's inputs
     def __init__(self, hidden, tokens):
         self.hidden, self.tokens, self.carry, self.calls, self.logits = hidden, tokens, 0.0, [], None
+    # position p lives at hidden row p % capacity (prompts longer than the buffer wrap around)
     def embed(self, begin, count):
-        self.hidden[begin:begin + count] = self.tokens[begin:begin + count, None].to(self.hidden.dtype)
+        row = begin % len(self.hidden)
+        self.hidden[row:row + count] = self.tokens[begin:begin + count, None].to(self.hidden.dtype)
     def run(self, begin, count):
         if begin == 0:
-            self.carry = 0.0
-        rows = self.hidden[begin:begin + count]
+            self.carry, self.logits = 0.0, torch.zeros(len(self.tokens), self.hidden.shape[1], dtype=torch.float64)
+        row = begin % len(self.hidden)
+        rows = self.hidden[row:row + count]
         total = float(rows.sum())
         rows.mul_(rank + 2).add_(self.carry)
         self.carry += total
         self.calls.append((begin, count))
-    def head(self, rows):
-        self.logits = self.hidden[:rows].clone()
+    def head(self, begin, count):
+        row = begin % len(self.hidden)
+        self.logits[begin:begin + count] = self.hidden[row:row + count]
 
 rows, width = 1300, 3
 tokens = torch.arange(rows, dtype=torch.float64) % 7
-hidden = torch.zeros(2048, width, dtype=torch.float64)
+hidden = torch.zeros(1024, width, dtype=torch.float64)   # shorter than the prompt: the third window wraps
 stage = RunningSumStage(hidden, tokens)
 pipe = StagePipeline(stage, hidden, rank, world, chunk=512)
 for _ in range(2):  # two prompts back to back: rows still in flight must not be overwritten
