@@ -610,6 +610,9 @@ def cpu_baseline(args, rt) -> dict:
 
 
 def main() -> None:
+    # NCCL prints its version banner on stdout at NCCL_DEBUG=VERSION; stdout carries the JSON line only
+    if os.environ.get("NCCL_DEBUG", "VERSION").upper() == "VERSION":
+        os.environ["NCCL_DEBUG"] = "WARN"
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
     parser.add_argument("--steps", type=int, default=5)

@@ -53,7 +53,12 @@ OPS_SIGNATURES: dict[str, list] = {
     "evo_b200_bf16_causal_attention": [_P, _P, _P, _Z, _Z, _Z, _Z, _P, _P],
     "evo_b200_bf16_causal_attention_mma_sync": [_P, _P, _P, _Z, _Z, _Z, _Z, _P, _P],
     "evo_b200_bf16_cached_cross_attention": [_P, _P, _P, _Z, _Z, _Z, _Z, _P, _P],
+    "evo_b200_linear_executor_create": [_I, ctypes.POINTER(_P)],
+    "evo_b200_linear_executor_linear": [_P, _P, _Z, _Z, _P, _I, _Z, _Z, _P, _I, _Z, _P],
 }
+# entry points that do not return a status
+OPS_OTHER = ("evo_b200_last_error", "evo_b200_hcl_scratch_floats", "evo_b200_linear_executor_free",
+             "evo_b200_linear_executor_name", "evo_b200_linear_executor_cached_bytes")
 
 
 class OpsError(RuntimeError):
@@ -74,6 +79,11 @@ class Ops:
         self.lib.evo_b200_last_error.restype = ctypes.c_char_p
         self.lib.evo_b200_hcl_scratch_floats.restype = _Z
         self.lib.evo_b200_hcl_scratch_floats.argtypes = [_Z, _Z, _Z]
+        self.lib.evo_b200_linear_executor_free.restype = None
+        self.lib.evo_b200_linear_executor_free.argtypes = [_P]
+        self.lib.evo_b200_linear_executor_name.restype = ctypes.c_char_p
+        self.lib.evo_b200_linear_executor_cached_bytes.restype = _Z
+        self.lib.evo_b200_linear_executor_cached_bytes.argtypes = [_P]
         for name, argtypes in OPS_SIGNATURES.items():
             fn = getattr(self.lib, name)
             fn.restype = _I

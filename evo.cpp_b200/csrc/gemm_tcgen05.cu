@@ -43,6 +43,13 @@ struct EpilogueParams {
   float alpha;
   int bias_mode;  // 0 none, 1 fused into the F32 sum, 2 separate BF16 add
   int gate_mode;  // 0 none, 1 first*second halves, 2 gelu(first)*second
+  // F32 result mode (split-precision products): out_f32 = [out_f32 +] alpha*acc [+ bias_f32]
+  float *out_f32;
+  const float *bias_f32;
+  int accumulate_f32;
+  // B's K coordinate wraps after this many K blocks (0: never): A = [x0 | x1 | ...] against
+  // the same weight columns
+  int weight_wrap_blocks;
 };
 
 using namespace tc;
@@ -185,8 +192,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
           const std::uint32_t b_dst = a_dst + L::kABytes;
           mbar_expect_tx(full_bar(stage), L::kStageBytes);
           const int k_elem = kFp8 ? kb * kBlockKBytes : kb * (kBlockKBytes / 2);
+          const int kb_b = ep.weight_wrap_blocks > 0 ? kb % ep.weight_wrap_blocks : kb;
+          const int k_elem_b = kFp8 ? kb_b * kBlockKBytes : kb_b * (kBlockKBytes / 2);
           tma_load_2d(a_dst, &map_a, full_bar(stage), k_elem, m0);
-          tma_load_2d(b_dst, &map_b, full_bar(stage), k_elem, n0);
+          tma_load_2d(b_dst, &map_b, full_bar(stage), k_elem_b, n0);
           if (++stage == kStages) {
             stage = 0;
             phase ^= 1U;
@@ -257,6 +266,21 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
         tmem_load_wait();
         const int col = gated ? n0 / 2 + c * 32 : n0 + c * 32;
         const int n_limit = gated ? N / 2 : N;
+        if (ep.out_f32 != nullptr) {
+          if (row < M && col < n_limit) {
+            float *const out_row = ep.out_f32 + static_cast<std::size_t>(row) * ep.ld_out;
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              if (col + j < n_limit) {
+                float value = __uint_as_float(v[j]) * ep.alpha;
+                if (ep.bias_f32 != nullptr) value += ep.bias_f32[col + j];
+                if (ep.accumulate_f32 != 0) value += out_row[col + j];
+                out_row[col + j] = value;
+              }
+            }
+          }
+          continue;
+        }
         if (row < M && col < n_limit) {
           bf16 *const out_row = ep.out + static_cast<std::size_t>(row) * ep.ld_out;
           float r[32];
@@ -479,13 +503,15 @@ template <bool kFp8, int BN>
 int launch_tc(const void *a, const void *b, const EpilogueParams &ep,
               const std::size_t M, const std::size_t N, const std::size_t K,
               cudaStream_t stream) {
+  // the weight is [N, K], or [N, wrap width] when its K coordinate wraps
+  const std::size_t weight_k = ep.weight_wrap_blocks > 0 ? static_cast<std::size_t>(ep.weight_wrap_blocks) * 64 : K;
   int status = kOk;
   DeviceState *const state = device_state(&status);
   if (state == nullptr) return status;
   CUtensorMap map_a, map_b;
   status = make_map(&map_a, a, kFp8, M, K, kBlockM);
   if (status != kOk) return status;
-  status = make_map(&map_b, b, kFp8, N, K, BN);
+  status = make_map(&map_b, b, kFp8, N, weight_k, BN);
   if (status != kOk) return status;
   using L = SharedLayout<BN>;
   static bool configured[64] = {};
@@ -543,7 +569,7 @@ int gemm_error_state(cudaStream_t stream) {
 int linear(const LinearArgs &args, cudaStream_t stream) {
   const bool fp8 = args.operand_type == OperandType::kE4m3;
   if (args.input == nullptr || args.weight == nullptr ||
-      args.output == nullptr || args.in_features == 0 ||
+      (args.output == nullptr && args.output_f32 == nullptr) || args.in_features == 0 ||
       args.out_features == 0 || !isfinite(args.alpha))
     return fail(kInvalidArgument, "linear arguments are invalid");
   if (args.bias_mode != 0 && args.bias == nullptr)
@@ -556,7 +582,11 @@ int linear(const LinearArgs &args, cudaStream_t stream) {
       args.in_features > 0x3fffffffU)
     return fail(kInvalidArgument, "linear dimensions are too large");
   if (args.rows == 0) return kOk;
-  if (small_batch_linear_applicable(args)) return small_batch_linear(args, stream);
+  if (args.output_f32 != nullptr &&
+      (fp8 || args.gate_mode != 0 || args.bias_mode != 0 || args.residual != nullptr))
+    return fail(kInvalidArgument, "the F32-result mode takes BF16 operands and no BF16 epilogue");
+  if (args.output_f32 == nullptr && small_batch_linear_applicable(args))
+    return small_batch_linear(args, stream);
   const std::size_t out_columns =
       args.gate_mode != 0 ? args.out_features / 2 : args.out_features;
   EpilogueParams ep{};
@@ -567,6 +597,14 @@ int linear(const LinearArgs &args, cudaStream_t stream) {
   ep.alpha = args.alpha;
   ep.bias_mode = args.bias_mode;
   ep.gate_mode = args.gate_mode;
+  ep.out_f32 = args.output_f32;
+  ep.bias_f32 = args.bias_f32;
+  ep.accumulate_f32 = args.accumulate_f32 ? 1 : 0;
+  if (args.weight_wrap_features != 0) {
+    if (args.weight_wrap_features % 64 != 0 || args.output_f32 == nullptr)
+      return fail(kInvalidArgument, "weight wrap needs whole K blocks and the F32-result mode");
+    ep.weight_wrap_blocks = static_cast<int>(args.weight_wrap_features / 64);
+  }
   const std::size_t pitch = args.in_features * (fp8 ? 1 : 2);
   const bool tma_ok =
       pitch % 16 == 0 && pitch >= 128 &&

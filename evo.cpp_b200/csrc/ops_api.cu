@@ -439,4 +439,24 @@ int evo_b200_bf16_cached_cross_attention(const void *query,
                           heads, head_dim, output, as_stream(stream));
 }
 
+// ---- LinearExecutor offload (src/linear_executor.hpp:13-28)
+int evo_b200_linear_executor_create(int device, evo_b200_linear_executor **executor_out) {
+  return linear_executor_create(device, reinterpret_cast<LinearExecutorState **>(executor_out));
+}
+void evo_b200_linear_executor_free(evo_b200_linear_executor *executor) {
+  linear_executor_free(reinterpret_cast<LinearExecutorState *>(executor));
+}
+const char *evo_b200_linear_executor_name(void) { return "b200-tcgen05-bf16x3"; }
+size_t evo_b200_linear_executor_cached_bytes(evo_b200_linear_executor *executor) {
+  return linear_executor_cached_bytes(reinterpret_cast<LinearExecutorState *>(executor));
+}
+int evo_b200_linear_executor_linear(evo_b200_linear_executor *executor, const float *input, size_t rows,
+                                    size_t input_width, const void *weight, int weight_dtype,
+                                    size_t weight_elements, size_t output_width, const void *bias,
+                                    int bias_dtype, size_t bias_elements, float *output) {
+  return linear_executor_linear(reinterpret_cast<LinearExecutorState *>(executor), input, rows, input_width,
+                                weight, weight_dtype, weight_elements, output_width, bias, bias_dtype,
+                                bias_elements, output);
+}
+
 }  // extern "C"

@@ -55,6 +55,17 @@ struct LinearArgs {
   int bias_mode = 0;   // 0 none, 1 fused F32 add, 2 separate BF16-rounded add
   int gate_mode = 0;   // 0 none, 1 a*b, 2 gelu(a)*b over 128-column halves
   bool force_simt = false;
+  // F32-result mode (BF16 operands, tensor-core path only): the F32 accumulator
+  // times alpha, plus bias_f32, is stored (or added) to output_f32 [rows,
+  // out_features] without any BF16 rounding.  weight_wrap_features = W makes the
+  // weight's K coordinate wrap every W input features, so an input that is
+  // several planes side by side, [x0 | x1 | ...] with in_features = planes * W,
+  // is multiplied against the same [out_features, W] weight: the sum of the
+  // planes' products in one accumulator.
+  float *output_f32 = nullptr;
+  const float *bias_f32 = nullptr;
+  bool accumulate_f32 = false;
+  std::size_t weight_wrap_features = 0;
 };
 int linear(const LinearArgs &args, cudaStream_t stream);
 // gemv.cu: weight-streaming kernel that linear() uses for 1..8 rows.
@@ -167,5 +178,15 @@ int cached_attention(const void *query, const void *key_cache,
                      const void *value_cache, std::size_t rows,
                      std::size_t total_keys, std::size_t heads,
                      std::size_t head_dim, void *output, cudaStream_t stream);
+
+// ---- linear_executor.cu: dense-linear offload with upstream's LinearExecutor contract
+struct LinearExecutorState;
+int linear_executor_create(int device, LinearExecutorState **out);
+void linear_executor_free(LinearExecutorState *state);
+std::size_t linear_executor_cached_bytes(LinearExecutorState *state);
+int linear_executor_linear(LinearExecutorState *state, const float *input, std::size_t rows,
+                           std::size_t input_width, const void *weight, int weight_dtype,
+                           std::size_t weight_elements, std::size_t output_width, const void *bias,
+                           int bias_dtype, std::size_t bias_elements, float *output);
 
 }  // namespace evob

@@ -239,6 +239,30 @@ EVO_B200_API int evo_b200_bf16_cached_cross_attention(
     size_t rows, size_t total_keys, size_t heads, size_t head_dim,
     void *output, void *stream);
 
+/* ---- Dense-linear offload with the contract of upstream's LinearExecutor
+ * (src/linear_executor.hpp:13-28; called from cpu::linear,
+ * src/cpu/model.cpp:284-302): F32 host activations [rows, input_width], a host
+ * weight [output_width, input_width] row-major (dtype 0 = F32, 1 = BF16: upstream
+ * TensorDType kF32 / kBF16), optional bias (same dtypes), F32 host output
+ * [rows, output_width].  F32 arithmetic is kept by splitting operands into
+ * BF16 planes on the tensor cores.  Device copies of weights are cached by
+ * host address for the executor's lifetime (as upstream's Metal executor does,
+ * src/mps/model.mm:218-238), so the mapped model file must outlive it; calls
+ * are serialised internally and return when the output is written.  Outputs
+ * narrower than 64 columns are refused with status 5 (keep them on the host).
+ * There is one stream and one weight cache per executor; create one executor
+ * per GPU. */
+typedef struct evo_b200_linear_executor evo_b200_linear_executor;
+EVO_B200_API int evo_b200_linear_executor_create(int device, evo_b200_linear_executor **executor_out);
+EVO_B200_API void evo_b200_linear_executor_free(evo_b200_linear_executor *executor);
+EVO_B200_API const char *evo_b200_linear_executor_name(void);
+EVO_B200_API size_t evo_b200_linear_executor_cached_bytes(evo_b200_linear_executor *executor);
+EVO_B200_API int evo_b200_linear_executor_linear(
+    evo_b200_linear_executor *executor, const float *input, size_t rows,
+    size_t input_width, const void *weight, int weight_dtype,
+    size_t weight_elements, size_t output_width, const void *bias,
+    int bias_dtype, size_t bias_elements, float *output);
+
 #ifdef __cplusplus
 }
 #endif

@@ -1,0 +1,88 @@
+"""Dense-linear offload with upstream's LinearExecutor contract
+(src/linear_executor.hpp:13-28): F32 host activations, F32 or BF16 host weights,
+optional bias, F32 host output - F32-level accuracy from BF16-plane products on
+the tensor cores, weights cached by host address."""
+from __future__ import annotations
+
+import ctypes
+
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+F32, BF16 = 0, 1
+
+
+def to_bf16_bits(values: np.ndarray) -> np.ndarray:
+    bits = values.astype(np.float32).view(np.uint32).astype(np.uint64)
+    return (((bits + 0x7FFF + ((bits >> 16) & 1)) >> 16) & 0xFFFF).astype(np.uint16)
+
+
+def widen(bits: np.ndarray) -> np.ndarray:
+    return (bits.astype(np.uint32) << 16).view(np.float32)
+
+
+@pytest.fixture()
+def executor(ops):
+    handle = ctypes.c_void_p()
+    ops.call("linear_executor_create", 0, ctypes.byref(handle))
+    yield handle
+    ops.lib.evo_b200_linear_executor_free(handle)
+
+
+def run(ops, executor, x, weight, weight_dtype, bias=None, bias_dtype=F32):
+    rows, k = x.shape
+    n = weight.shape[0]
+    out = np.empty((rows, n), np.float32)
+    ops.call("linear_executor_linear", executor, x.ctypes.data, rows, k, weight.ctypes.data, weight_dtype,
+             weight.size, n, None if bias is None else bias.ctypes.data, bias_dtype,
+             0 if bias is None else bias.size, out.ctypes.data)
+    return out
+
+
+@pytest.mark.parametrize("rows,k,n", [(1, 512, 384), (37, 1000, 200), (300, 4096, 1024), (130, 72, 64)])
+@pytest.mark.parametrize("weight_dtype", [BF16, F32])
+def test_matches_float64_reference(ops, executor, rows, k, n, weight_dtype):
+    rng = np.random.default_rng(rows + k + weight_dtype)
+    x = np.ascontiguousarray(rng.standard_normal((rows, k)).astype(np.float32) * 3.0)
+    w32 = (rng.standard_normal((n, k)) * 0.05).astype(np.float32)
+    if weight_dtype == BF16:
+        weight = to_bf16_bits(w32)
+        w_value = widen(weight)
+        bias = to_bf16_bits((rng.standard_normal(n) * 0.5).astype(np.float32))
+        bias_value, bias_dtype = widen(bias), BF16
+    else:
+        weight, w_value = w32, w32
+        bias = (rng.standard_normal(n) * 0.5).astype(np.float32)
+        bias_value, bias_dtype = bias, F32
+    got = run(ops, executor, x, weight, weight_dtype, bias, bias_dtype)
+    want = x.astype(np.float64) @ w_value.astype(np.float64).T + bias_value.astype(np.float64)
+    # F32 accumulation of k products: error budget ~ sqrt(k) * 2^-24 of the absolute sum
+    budget = (np.abs(x).astype(np.float64) @ np.abs(w_value).astype(np.float64).T + np.abs(bias_value)) * 4e-7
+    assert np.all(np.abs(got - want) <= budget + 1e-7), float(np.max(np.abs(got - want) / (budget + 1e-7)))
+    # without a bias, and again from the cache: identical bits
+    first = run(ops, executor, x, weight, weight_dtype)
+    cached_before = ops.lib.evo_b200_linear_executor_cached_bytes(executor)
+    second = run(ops, executor, x, weight, weight_dtype)
+    assert np.array_equal(first, second)
+    assert ops.lib.evo_b200_linear_executor_cached_bytes(executor) == cached_before > 0
+    assert np.all(np.abs(first - (want - bias_value)) <= budget + 1e-7)
+
+
+def test_contract_errors(ops, executor):
+    assert ops.lib.evo_b200_linear_executor_name() == b"b200-tcgen05-bf16x3"
+    x = np.zeros((2, 64), np.float32)
+    w = np.zeros((64, 64), np.float32)
+    out = np.zeros((2, 64), np.float32)
+    # inconsistent dimensions: upstream's "internal" status
+    assert ops.status("linear_executor_linear", executor, x.ctypes.data, 2, 64, w.ctypes.data, F32, 100, 64, None,
+                      0, 0, out.ctypes.data) == 70
+    assert ops.status("linear_executor_linear", executor, x.ctypes.data, 2, 64, w.ctypes.data, 2, w.size, 64, None,
+                      0, 0, out.ctypes.data) == 5      # E4M3 weights stay on the host
+    narrow = np.zeros((8, 64), np.float32)
+    assert ops.status("linear_executor_linear", executor, x.ctypes.data, 2, 64, narrow.ctypes.data, F32, narrow.size,
+                      8, None, 0, 0, out.ctypes.data) == 5
+    assert ops.status("linear_executor_linear", executor, None, 2, 64, w.ctypes.data, F32, w.size, 64, None, 0, 0,
+                      out.ctypes.data) == 2
+    handle = ctypes.c_void_p()
+    assert ops.status("linear_executor_create", 99, ctypes.byref(handle)) == 2
