@@ -22,6 +22,7 @@
 #include <cuda.h>
 
 #include <mutex>
+#include <type_traits>
 
 #include "common.cuh"
 #include "ops_internal.hpp"
@@ -624,23 +625,26 @@ int linear(const LinearArgs &args, cudaStream_t stream) {
                                          args.rows, args.out_features,
                                          args.in_features, stream);
     }
-    // Narrow tiles when wide ones would leave most SMs without work.
+    // Narrower tiles when wide ones would leave most SMs without work.
     const std::size_t tiles_m = (args.rows + kBlockM - 1) / kBlockM;
-    const std::size_t wide = tiles_m * ((args.out_features + 255) / 256);
-    const bool narrow = args.out_features < 256 || wide < 120;
-    if (narrow)
-      return fp8 ? launch_tc<true, 128>(args.input, args.weight, ep, args.rows,
-                                        args.out_features, args.in_features,
-                                        stream)
-                 : launch_tc<false, 128>(args.input, args.weight, ep,
-                                         args.rows, args.out_features,
-                                         args.in_features, stream);
-    return fp8 ? launch_tc<true, 256>(args.input, args.weight, ep, args.rows,
-                                      args.out_features, args.in_features,
-                                      stream)
-               : launch_tc<false, 256>(args.input, args.weight, ep, args.rows,
-                                       args.out_features, args.in_features,
-                                       stream);
+    // (Measured: below 128 columns the shorter weight tiles put fewer bytes in
+    // flight per CTA and lose more than the extra CTAs win, except for narrow
+    // outputs, so 64 and 32 are used only when the output itself is that narrow.)
+    int bn = 256;
+    if (tiles_m * ((args.out_features + 255) / 256) < 120) bn = 128;
+    while (bn > 32 && args.out_features < static_cast<std::size_t>(bn)) bn /= 2;
+    const auto launch = [&](auto fp8_tag, auto bn_tag) {
+      return launch_tc<decltype(fp8_tag)::value, decltype(bn_tag)::value>(
+          args.input, args.weight, ep, args.rows, args.out_features, args.in_features, stream);
+    };
+    using F = std::false_type;
+    using T = std::true_type;
+    switch (bn) {
+      case 256: return fp8 ? launch(T{}, std::integral_constant<int, 256>{}) : launch(F{}, std::integral_constant<int, 256>{});
+      case 128: return fp8 ? launch(T{}, std::integral_constant<int, 128>{}) : launch(F{}, std::integral_constant<int, 128>{});
+      case 64: return fp8 ? launch(T{}, std::integral_constant<int, 64>{}) : launch(F{}, std::integral_constant<int, 64>{});
+      default: return fp8 ? launch(T{}, std::integral_constant<int, 32>{}) : launch(F{}, std::integral_constant<int, 32>{});
+    }
   }
   if (args.gate_mode != 0)
     return fail(kUnsupported,

@@ -12,7 +12,9 @@
 //   y = [x0 | x1 | x2] . W^T                      (BF16 weights: one launch)
 //   y = x012 . W0^T + x01 . W1^T + x0 . W2^T      (F32 weights: three launches)
 // runs on the tcgen05 projection kernel in its F32-result mode, the weight's K
-// coordinate wrapping so the planes of x meet the same weight columns.
+// coordinate wrapping so the planes of x meet the same weight columns.  What is
+// left of the error is the tensor-core accumulator's truncation when it aligns
+// partial sums: a few 1e-6 of sum(|x||w|) at K = 4096.
 #include <cuda_runtime.h>
 
 #include <map>

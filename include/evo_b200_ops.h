@@ -244,8 +244,9 @@ EVO_B200_API int evo_b200_bf16_cached_cross_attention(
  * src/cpu/model.cpp:284-302): F32 host activations [rows, input_width], a host
  * weight [output_width, input_width] row-major (dtype 0 = F32, 1 = BF16: upstream
  * TensorDType kF32 / kBF16), optional bias (same dtypes), F32 host output
- * [rows, output_width].  F32 arithmetic is kept by splitting operands into
- * BF16 planes on the tensor cores.  Device copies of weights are cached by
+ * [rows, output_width].  Operands are split into BF16 planes (exact to 2^-24)
+ * and multiplied on the tensor cores; their accumulator truncates, so results
+ * agree with F32 arithmetic to a few 1e-6 of sum(|x||w|).  Device copies of weights are cached by
  * host address for the executor's lifetime (as upstream's Metal executor does,
  * src/mps/model.mm:218-238), so the mapped model file must outlive it; calls
  * are serialised internally and return when the output is written.  Outputs
