@@ -71,8 +71,11 @@ split_rope_append_vec_kernel(const bf16 *__restrict__ qkv, const float *__restri
                              bf16 *__restrict__ query, bf16 *__restrict__ key_cache,
                              bf16 *__restrict__ value_cache, const std::size_t rows,
                              const std::size_t heads, const std::size_t head_dim,
-                             const std::size_t position_offset, const float position_scale,
-                             const bool head_major) {
+                             const std::size_t static_position_offset, const float position_scale,
+                             const bool head_major, const int *__restrict__ dynamic_position) {
+  // replayed launches (CUDA graphs) read the position from device memory
+  const std::size_t position_offset =
+      dynamic_position != nullptr ? static_cast<std::size_t>(*dynamic_position) : static_position_offset;
   const std::size_t half = head_dim / 2;
   const std::size_t width = heads * head_dim;
   const std::size_t groups = half / 8;
@@ -242,7 +245,8 @@ int split_rope_append(const void *qkv, const float *inverse_frequency,
                       const std::size_t position_offset,
                       const float position_scale, const bool head_major,
                       void *query, void *key_cache, void *value_cache,
-                      const std::size_t cache_capacity, cudaStream_t stream) {
+                      const std::size_t cache_capacity, cudaStream_t stream,
+                      const int *dynamic_position) {
   if (qkv == nullptr || inverse_frequency == nullptr || query == nullptr ||
       key_cache == nullptr || value_cache == nullptr || heads == 0 ||
       head_dim == 0 || head_dim % 2 != 0 || !(position_scale > 0.0F))
@@ -261,9 +265,11 @@ int split_rope_append(const void *qkv, const float *inverse_frequency,
     kernel<<<grid, 256, 0, stream>>>(static_cast<const bf16 *>(qkv), inverse_frequency,
                                      static_cast<bf16 *>(query), static_cast<bf16 *>(key_cache),
                                      static_cast<bf16 *>(value_cache), rows, heads, head_dim,
-                                     position_offset, position_scale, head_major);
+                                     position_offset, position_scale, head_major, dynamic_position);
     return check_launch("QKV split/RoPE/append kernel");
   }
+  if (dynamic_position != nullptr)
+    return fail(kUnsupported, "a device-side position needs the vectorised split kernel");
   const std::size_t elements = rows * heads * (head_dim / 2);
   const std::size_t blocks = (elements + 255) / 256;
   split_rope_append_kernel<<<static_cast<unsigned int>(blocks > cap ? cap : blocks),
@@ -303,15 +309,19 @@ bool attention_decode_applicable(const void *query, const void *key_cache, const
                                  std::size_t rows, std::size_t total_keys, std::size_t heads,
                                  std::size_t head_dim, const void *output);
 int attention_decode(const void *query, const void *key_cache, const void *value_cache, std::size_t rows,
-                     std::size_t total_keys, std::size_t heads, void *output, cudaStream_t stream);
+                     std::size_t total_keys, std::size_t heads, void *output, cudaStream_t stream,
+                     const int *dynamic_prefix);
 
 int causal_attention(const void *query, const void *key_cache,
                      const void *value_cache, const std::size_t rows,
                      const std::size_t total_keys, const std::size_t heads,
                      const std::size_t head_dim, void *output,
-                     cudaStream_t stream) {
+                     cudaStream_t stream, const int *dynamic_prefix) {
   if (attention_decode_applicable(query, key_cache, value_cache, rows, total_keys, heads, head_dim, output))
-    return attention_decode(query, key_cache, value_cache, rows, total_keys, heads, output, stream);
+    return attention_decode(query, key_cache, value_cache, rows, total_keys, heads, output, stream,
+                            dynamic_prefix);
+  if (dynamic_prefix != nullptr)
+    return fail(kUnsupported, "a device-side prefix needs the split-KV attention kernel");
   if (head_dim == 128 && query != nullptr && key_cache != nullptr && value_cache != nullptr &&
       output != nullptr &&
       flash_tcgen05_applicable(query, key_cache, value_cache, rows, total_keys, heads, output))

@@ -46,7 +46,9 @@ __device__ __forceinline__ void merge(float &m, float &l, float &acc, const floa
 __global__ void __launch_bounds__(kDecodeThreads)
 attention_decode_kernel(const bf16 *__restrict__ query, const bf16 *__restrict__ key_cache,
                         const bf16 *__restrict__ value_cache, bf16 *__restrict__ output, const int rows,
-                        const int total_keys, const int heads) {
+                        const int static_total_keys, const int heads, const int *__restrict__ dynamic_prefix) {
+  // replayed launches (CUDA graphs) read the number of keys already cached from device memory
+  const int total_keys = dynamic_prefix != nullptr ? *dynamic_prefix + rows : static_total_keys;
   __shared__ float warp_partials[kWarps][kPartial];
   __shared__ float cta_partial[kPartial];
   cg::cluster_group cluster = cg::this_cluster();
@@ -162,7 +164,8 @@ bool attention_decode_applicable(const void *query, const void *key_cache, const
 }
 
 int attention_decode(const void *query, const void *key_cache, const void *value_cache, const std::size_t rows,
-                     const std::size_t total_keys, const std::size_t heads, void *output, cudaStream_t stream) {
+                     const std::size_t total_keys, const std::size_t heads, void *output, cudaStream_t stream,
+                     const int *dynamic_prefix) {
   cudaLaunchConfig_t config{};
   config.gridDim = dim3(kSplits, static_cast<unsigned int>(heads), static_cast<unsigned int>(rows));
   config.blockDim = dim3(kDecodeThreads);
@@ -178,7 +181,7 @@ int attention_decode(const void *query, const void *key_cache, const void *value
   const cudaError_t error = cudaLaunchKernelEx(
       &config, attention_decode_kernel, static_cast<const bf16 *>(query), static_cast<const bf16 *>(key_cache),
       static_cast<const bf16 *>(value_cache), static_cast<bf16 *>(output), static_cast<int>(rows),
-      static_cast<int>(total_keys), static_cast<int>(heads));
+      static_cast<int>(total_keys), static_cast<int>(heads), dynamic_prefix);
   if (error != cudaSuccess)
     return fail(kCuda, std::string("attention decode kernel launch failed: ") + cudaGetErrorString(error));
   return check_launch("attention decode kernel");

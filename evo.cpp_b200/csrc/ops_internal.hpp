@@ -163,11 +163,17 @@ int split_rope_append(const void *qkv, const float *inverse_frequency,
                       std::size_t head_dim, std::size_t position_offset,
                       float position_scale, bool head_major, void *query,
                       void *key_cache, void *value_cache,
-                      std::size_t cache_capacity, cudaStream_t stream);
+                      std::size_t cache_capacity, cudaStream_t stream,
+                      const int *dynamic_position = nullptr);
+// dynamic_position / dynamic_prefix (optional, device int): the position of the
+// first row, read by the kernel at run time instead of the host value - for
+// launches recorded once and replayed (CUDA graphs).  Only the small-row kernels
+// take it.
 int causal_attention(const void *query, const void *key_cache,
                      const void *value_cache, std::size_t rows,
                      std::size_t total_keys, std::size_t heads,
-                     std::size_t head_dim, void *output, cudaStream_t stream);
+                     std::size_t head_dim, void *output, cudaStream_t stream,
+                     const int *dynamic_prefix = nullptr);
 // Warp-level MMA / row-wise implementation of the same contract (what
 // causal_attention falls back to below 128 rows or for other head sizes).
 int causal_attention_mma_sync(const void *query, const void *key_cache,

@@ -5,6 +5,7 @@
 // cache).  Stages are chained with stream-ordered peer copies: no host
 // synchronisation between stages, only the final logits read-back blocks.
 #include <algorithm>
+#include <cstdlib>
 #include <cstring>
 
 #include "../common.cuh"
@@ -143,7 +144,68 @@ struct Context::Stage {
   }
 };
 
-Context::~Context() = default;
+Context::~Context() {
+  if (decode_graph_ != nullptr) cudaGraphExecDestroy(static_cast<cudaGraphExec_t>(decode_graph_));
+}
+
+// One decode step as a replayed CUDA graph.  The step's launches depend on the
+// position only through the RoPE angle / KV append index and the number of
+// cached keys, which the small-row attention kernels read from device memory,
+// and through the FIR history counts, which are constant once the history is
+// full; everything else is fixed addresses.  Returns kOk with *launched = false
+// when the step has to take the ordinary path.
+int Context::decode_step_graph(const std::uint32_t *host_token, bool *launched) {
+  *launched = false;
+  const ModelConfig &c = weights_->config;
+  Stage &first = *stages_.front();
+  DeviceGuard guard(first.device);
+  cudaStream_t stream = first.stream;
+  decode_position_host_ = static_cast<int>(position_);
+  if (cudaMemcpyAsync(first.tokens, host_token, 4, cudaMemcpyHostToDevice, stream) != cudaSuccess ||
+      cudaMemcpyAsync(device_position_, &decode_position_host_, 4, cudaMemcpyHostToDevice, stream) != cudaSuccess)
+    return fail(kCuda, "token upload failed");
+  if (decode_graph_ == nullptr) {
+    if (cudaStreamBeginCapture(stream, cudaStreamCaptureModeThreadLocal) != cudaSuccess) {
+      cudaGetLastError();
+      decode_graph_allowed_ = false;
+      return kOk;
+    }
+    dynamic_position_ = device_position_;
+    int status = embedding(first.tokens, first.weights->embedding, 1, c.width, first.hidden, stream);
+    if (status == kOk) status = run_stage(first, 1, Mode::kDecode, -1, nullptr);
+    if (status == kOk)
+      status = rms_norm(first.hidden, first.weights->final_norm, 1, c.width, c.epsilon, first.normalized,
+                        nullptr, 1.0F, stream);
+    if (status == kOk) {
+      LinearArgs a;
+      a.input = first.normalized;
+      a.weight = first.weights->embedding;  // tied head
+      a.output = first.logits;
+      a.rows = 1;
+      a.in_features = c.width;
+      a.out_features = c.vocab;
+      status = linear(a, stream);
+    }
+    dynamic_position_ = nullptr;
+    cudaGraph_t graph = nullptr;
+    const cudaError_t ended = cudaStreamEndCapture(stream, &graph);
+    cudaGraphExec_t executable = nullptr;
+    if (status != kOk || ended != cudaSuccess || graph == nullptr ||
+        cudaGraphInstantiate(&executable, graph, 0) != cudaSuccess) {
+      // nothing ran: the step falls back to ordinary launches, for good
+      cudaGetLastError();
+      if (graph != nullptr) cudaGraphDestroy(graph);
+      decode_graph_allowed_ = false;
+      return kOk;
+    }
+    cudaGraphDestroy(graph);
+    decode_graph_ = executable;
+  }
+  if (cudaGraphLaunch(static_cast<cudaGraphExec_t>(decode_graph_), stream) != cudaSuccess)
+    return fail(kCuda, std::string("decode graph launch failed: ") + cudaGetErrorString(cudaGetLastError()));
+  *launched = true;
+  return kOk;
+}
 
 int Context::create(std::shared_ptr<ModelWeights> weights, const std::size_t context_size,
                     const ExecutionProfile profile, const bool full_arena_for_fixtures,
@@ -226,6 +288,15 @@ int Context::create(std::shared_ptr<ModelWeights> weights, const std::size_t con
       }
     }
     context->stages_.push_back(std::move(stage));
+  }
+  {
+    Stage &first = *context->stages_.front();
+    DeviceGuard guard(first.device);
+    void *p = nullptr;
+    EVOB_TRY(first.allocate(&p, 16, &first.arena_bytes));
+    context->device_position_ = static_cast<int *>(p);
+    const char *const graphs = std::getenv("EVO_B200_DECODE_GRAPH");
+    context->decode_graph_allowed_ = graphs == nullptr || std::string(graphs) != "0";
   }
   // Direct peer copies between neighbouring stages (and last -> first for the
   // head); without peer access the copies still work, staged by the driver.
@@ -361,7 +432,8 @@ int Context::run_stage(Stage &s, const std::size_t rows, const Mode mode,
       const std::size_t prefix = window ? window_position : (initial ? 0 : position_);
       EVOB_OP(kCatAttention, split_rope_append(s.projection, w.inverse_frequency, rows, c.heads, c.head_dim(),
                                  prefix, c.rope_scale, false, s.query, state.key_cache,
-                                 state.value_cache, context_size_, stream));
+                                 state.value_cache, context_size_, stream,
+                                 mode == Mode::kDecode ? dynamic_position_ : nullptr));
       const bool cached = mode == Mode::kCachedPrefill ||
                           ((mode == Mode::kDecode || mode == Mode::kContinue) && cached_attention_);
       if (cached)
@@ -369,7 +441,8 @@ int Context::run_stage(Stage &s, const std::size_t rows, const Mode mode,
                                   c.heads, c.head_dim(), s.mixer_out, stream));
       else
         EVOB_OP(kCatAttention, causal_attention(s.query, state.key_cache, state.value_cache, rows, prefix + rows,
-                                  c.heads, c.head_dim(), s.mixer_out, stream));
+                                  c.heads, c.head_dim(), s.mixer_out, stream,
+                                  mode == Mode::kDecode ? dynamic_position_ : nullptr));
     } else if (initial) {
       unsigned char *const projection_base =
           static_cast<unsigned char *>(rewind(s.projection, D * 6));
@@ -636,7 +709,12 @@ int Context::forward(const std::uint32_t *host_tokens, const std::uint32_t *devi
   } shift_back{this, continuation_window};
   if (continuation_window)
     for (auto &stage : stages_) stage->shift_rows(static_cast<long>(kHistoryPad), c.width, c.inner_width);
-  {
+  bool graph_step = false;
+  if (decode_graph_allowed_ && mode == Mode::kDecode && stages_.size() == 1 && host_tokens != nullptr &&
+      !first.profiling && !cached_attention_ && c.head_dim() == 128 && capture_layer < 0 &&
+      position_ >= std::max({c.short_taps, c.hcs_taps, c.hcm_taps}))
+    status = decode_step_graph(host_tokens, &graph_step);
+  if (!graph_step && status == kOk) {
     DeviceGuard guard(first.device);
     if (host_tokens != nullptr) {
       if (cudaMemcpyAsync(first.tokens, host_tokens, rows * 4, cudaMemcpyHostToDevice,
@@ -651,7 +729,7 @@ int Context::forward(const std::uint32_t *host_tokens, const std::uint32_t *devi
   const bool wavefront = stages_.size() > 1 && (mode == Mode::kPrefill || mode == Mode::kStateless) &&
                          rows >= 512 && capture_layer < 0;
   if (wavefront && status == kOk) status = run_wavefront(rows, mode, capture_layer, captured);
-  for (std::size_t index = 0; index < stages_.size() && status == kOk && !wavefront; ++index) {
+  for (std::size_t index = 0; index < stages_.size() && status == kOk && !wavefront && !graph_step; ++index) {
     Stage &stage = *stages_[index];
     DeviceGuard guard(stage.device);
     if (index > 0) {
@@ -677,10 +755,10 @@ int Context::forward(const std::uint32_t *host_tokens, const std::uint32_t *devi
                               rows * c.width * 2, first.stream) != cudaSuccess)
         status = fail(kCuda, "stage hand-off failed");
     }
-    if (status == kOk)
+    if (status == kOk && !graph_step)
       status = rms_norm(first.hidden, first.weights->final_norm, rows, c.width, c.epsilon,
                         first.normalized, nullptr, 1.0F, first.stream);
-    if (status == kOk) {
+    if (status == kOk && !graph_step) {
       LinearArgs a;
       a.input = first.normalized;
       a.weight = first.weights->embedding;  // tied head

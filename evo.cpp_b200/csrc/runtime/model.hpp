@@ -177,6 +177,14 @@ class Context {
   // state).  Used for initial prefills on more than one stage.
   int run_wavefront(std::size_t rows, Mode mode, long capture_layer, std::vector<float> *captured);
   std::size_t wavefront_chunk_ = 0;  // 0 = choose from rows and stage count
+  // Cached decode as a replayed CUDA graph (single-stage contexts, head size
+  // 128, history full; EVO_B200_DECODE_GRAPH=0 turns it off).
+  int decode_step_graph(const std::uint32_t *host_token, bool *launched);
+  void *decode_graph_ = nullptr;          // cudaGraphExec_t
+  int *device_position_ = nullptr;        // position of the decoded token, read by replayed kernels
+  const int *dynamic_position_ = nullptr; // == device_position_ while the graph is being recorded
+  int decode_position_host_ = 0;
+  bool decode_graph_allowed_ = true;
 
   std::shared_ptr<ModelWeights> weights_;
   std::vector<std::unique_ptr<Stage>> stages_;

@@ -135,3 +135,28 @@ def test_chunk_continuation_matches_single_prefill(pkg, tmp_path_factory):
         a, b = whole.decode(token), chunked.decode(token)
         assert np.abs(a - b).mean() < 0.05
         token = int(a.argmax())
+
+
+def test_decode_graph_replay_is_bit_identical(pkg, tmp_path_factory, monkeypatch):
+    """Cached decode is recorded once as a CUDA graph and replayed (position read
+    from device memory); the same steps with ordinary launches give the same bits."""
+    rt = importlib.import_module("evo_cpp_b200.runtime")
+    art = importlib.import_module("evo_cpp_b200.artifact")
+    evo = rt.EvoLibrary(pkg.EVO_LIBRARY)
+    directory = tmp_path_factory.mktemp("graph")
+    spec = art.fixture_spec(width=256, layers=8, heads=2, inner=512, hcs_groups=16, hcm_groups=16, fp8=True)
+    art.write_synthetic(directory / "model.safetensors", spec, seed=12, weight_std=0.05, filter_std=0.3)
+    model = evo.load(directory / "model.safetensors", devices=[0], flags=rt.MODEL_FLAG_ALLOW_SYNTHETIC)
+    prompt = bytes(np.random.default_rng(3).choice(np.frombuffer(b"ACGT", np.uint8), 300).tolist())
+    for flags in (rt.CONTEXT_FLAG_FULL_ARENA | rt.CONTEXT_FLAG_TENSORCORE_FP8, rt.CONTEXT_FLAG_FULL_ARENA):
+        monkeypatch.setenv("EVO_B200_DECODE_GRAPH", "0")
+        plain = model.context(1024, flags)
+        monkeypatch.delenv("EVO_B200_DECODE_GRAPH")
+        replayed = model.context(1024, flags)
+        token = int(plain.prefill(prompt)[-1].argmax())
+        assert int(replayed.prefill(prompt)[-1].argmax()) == token
+        for _ in range(12):
+            a, b = plain.decode(token), replayed.decode(token)
+            assert np.array_equal(a, b)
+            token = int(a.argmax())
+        assert plain.position == replayed.position == 312
