@@ -92,6 +92,13 @@ __global__ void quantize_bf16_vec_kernel(const uint4 *__restrict__ input,
 // order as upstream (thread-strided columns, shuffle-down tree, 8 warp
 // partials through a second tree; src/cuda/ops.cu:72-96) so that the BF16
 // rounding chain sees bit-identical sums.
+// BF16 of two F32 values in one instruction: `low` in bits 0-15, `high` in bits 16-31.
+__device__ __forceinline__ std::uint32_t round_pair(const float low, const float high) {
+  std::uint32_t packed;
+  asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(packed) : "f"(high), "f"(low));
+  return packed;
+}
+
 __device__ __forceinline__ float warp_sum_down(float value) {
 #pragma unroll
   for (int offset = 16; offset > 0; offset /= 2)
@@ -158,6 +165,16 @@ rms_norm_kernel(const bf16 *__restrict__ input, const float *__restrict__ scale,
       // IEEE division is only kept for denominators outside that range.
       if (denominator >= 1e-30F && denominator <= 1e30F) {
         const float reciprocal = __frcp_rn(denominator);
+        if (codes == nullptr) {
+          // no codes wanted: round the products two at a time straight into the packed result
+          std::uint32_t packed[4];
+#pragma unroll
+          for (int j = 0; j < 8; j += 2)
+            packed[j / 2] = round_pair(rbf(values.get(j) * reciprocal) * rbf(scales[j]),
+                                       rbf(values.get(j + 1) * reciprocal) * rbf(scales[j + 1]));
+          reinterpret_cast<uint4 *>(output + row * width)[v] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+          continue;
+        }
 #pragma unroll
         for (int j = 0; j < 8; ++j)
           results[j] = rbf(rbf(values.get(j) * reciprocal) * rbf(scales[j]));
