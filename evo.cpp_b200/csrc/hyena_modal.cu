@@ -35,6 +35,9 @@ struct ModalParams {
   bf16 *output, *pregate;
   float *state;    // [width, modes]
   float *scratch;  // [segments, width, modes]
+  // optional [length, width] packed (u | x2 << 16) words: written by the
+  // projection-fed local pass, read by the output pass instead of featurizing again
+  std::uint32_t *words;
   int length, row_begin, width, segment, segments, pairs;
   bool continue_from_state;
 };
@@ -495,7 +498,13 @@ modal_tiled_kernel(const ModalParams p) {
         const unsigned char *const history[3] = {base, base + kProjRowBytes, base + 2 * kProjRowBytes};
         PackedTaps taps;
         taps.load_shared(weights + item_chunk * 36);
-        featurize_chunk<kOutput>(history, taps, u, g);
+        if constexpr (kOutput) {
+          featurize_chunk<true>(history, taps, u, g);
+        } else {
+          // the local pass needs only u, unless it also leaves the words for the output pass
+          if (p.words != nullptr) featurize_chunk<true>(history, taps, u, g);
+          else featurize_chunk<false>(history, taps, u, g);
+        }
       } else {
         const unsigned char *const base = stage + (lane * kSlab + item_row) * kPlainRowBytes + item_chunk * 16;
         Bf16x8 a, b;
@@ -516,6 +525,14 @@ modal_tiled_kernel(const ModalParams p) {
                                   __byte_perm(u[1], g[1], 0x5410), __byte_perm(u[1], g[1], 0x7632));
       destination[1] = make_uint4(__byte_perm(u[2], g[2], 0x5410), __byte_perm(u[2], g[2], 0x7632),
                                   __byte_perm(u[3], g[3], 0x5410), __byte_perm(u[3], g[3], 0x7632));
+      if constexpr (kFromProjection && !kOutput) {
+        const int t = t0 + slab * kSlab + item_row;
+        if (p.words != nullptr && item_ok && t < t1) {
+          uint4 *const out = reinterpret_cast<uint4 *>(p.words + static_cast<std::size_t>(t) * p.width + item_c0);
+          out[0] = destination[0];
+          out[1] = destination[1];
+        }
+      }
       if constexpr (kOutput) {
         const int t = t0 + slab * kSlab + item_row;
         if (p.pregate != nullptr && item_ok && t < t1)
@@ -574,6 +591,109 @@ modal_tiled_kernel(const ModalParams p) {
   }
 }
 
+// Output pass from the stored (u, x2) words: no featurizer, no raw staging -
+// the words of the next slab are copied in while this one is scanned.
+
+template <int kModes>
+__global__ void __launch_bounds__(kScanThreads, 3)
+modal_words_output_kernel(const ModalParams p) {
+  __shared__ __align__(16) std::uint32_t stages[2][kLanes * kSlab * kTileChannels];
+  __shared__ __align__(16) unsigned short out_tile[kLanes * kSlab * kTileChannels];
+  const int seg0 = blockIdx.x * kLanes;
+  const int c_tile = blockIdx.y * kTileChannels;
+  const int lane = threadIdx.x / kTileChannels;
+  const int column = threadIdx.x % kTileChannels;
+  const int channel = c_tile + column;
+  const int seg = seg0 + lane;
+  const bool scans = channel < p.width && seg < p.segments;
+  const int t0 = p.row_begin + seg * p.segment;
+  const int t1 = min(t0 + p.segment, p.length);
+  float pole[kModes], residue[kModes], state[kModes];
+  float direct = 0.0F;
+#pragma unroll
+  for (int m = 0; m < kModes; ++m) {
+    pole[m] = residue[m] = state[m] = 0.0F;
+    if (scans) {
+      const std::size_t q = static_cast<std::size_t>(channel) * kModes + m;
+      pole[m] = expf(p.log_poles[q]);
+      residue[m] = p.residues[q];
+      state[m] = p.scratch[(static_cast<std::size_t>(seg) * p.width + channel) * kModes + m];
+    }
+  }
+  if (scans) direct = bf2f(p.direct[channel]);
+  // copy / store role: row item_row of the lane, two 16-byte chunks (8 channels) per thread
+  const int item_chunk = threadIdx.x % 8;
+  const int item_row = (threadIdx.x / 8) % kSlab;
+  const int item_c0 = c_tile + item_chunk * 8;
+  const bool item_ok = item_c0 < p.width && seg < p.segments;
+  const auto issue = [&](const int slab, std::uint32_t *const stage) {
+    const int t = t0 + slab * kSlab + item_row;
+    const bool valid = item_ok && t < t1;
+    const std::uint32_t *const source =
+        valid ? p.words + static_cast<std::size_t>(t) * p.width + item_c0 : p.words;
+    std::uint32_t *const target = stage + (lane * kSlab + item_row) * kTileChannels + item_chunk * 8;
+    async_copy16(target, source, valid);
+    async_copy16(target + 4, source + 4, valid);
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+  const int slabs = p.segment / kSlab;
+  issue(0, stages[0]);
+  for (int slab = 0; slab < slabs; ++slab) {
+    const std::uint32_t *const stage = stages[slab & 1];
+    if (slab + 1 < slabs) {
+      issue(slab + 1, stages[(slab + 1) & 1]);
+      asm volatile("cp.async.wait_group 1;" ::: "memory");
+    } else {
+      asm volatile("cp.async.wait_group 0;" ::: "memory");
+    }
+    __syncthreads();
+    if (p.pregate != nullptr) {
+      const int t = t0 + slab * kSlab + item_row;
+      if (item_ok && t < t1) {
+        const std::uint32_t *const w = stage + (lane * kSlab + item_row) * kTileChannels + item_chunk * 8;
+        *reinterpret_cast<uint4 *>(p.pregate + static_cast<std::size_t>(t) * p.width + item_c0) =
+            make_uint4(__byte_perm(w[0], w[1], 0x5410), __byte_perm(w[2], w[3], 0x5410),
+                       __byte_perm(w[4], w[5], 0x5410), __byte_perm(w[6], w[7], 0x5410));
+      }
+    }
+    if (scans) {
+      const std::uint32_t *const my_words = stage + lane * kSlab * kTileChannels + column;
+      unsigned short *const my_out = out_tile + lane * kSlab * kTileChannels + column;
+      const int live = min(kSlab, t1 - (t0 + slab * kSlab));
+#pragma unroll
+      for (int r = 0; r < kSlab; ++r) {
+        if (r < live) {
+          const std::uint32_t word = my_words[r * kTileChannels];
+          const float u = __uint_as_float(word << 16U);
+          const float g = __uint_as_float(word & 0xffff0000U);
+          float partial[4] = {0.0F, 0.0F, 0.0F, 0.0F};
+#pragma unroll
+          for (int m = 0; m < kModes; ++m) {
+            state[m] = fmaf(pole[m], state[m], u);
+            partial[m % 4] = fmaf(residue[m], state[m], partial[m % 4]);
+          }
+          const float modal = ((partial[0] + partial[1]) + partial[2]) + partial[3];
+          float result;
+          if (p.continue_from_state)
+            result = g * fmaf(direct, u, modal);
+          else
+            result = rbf(rbf(modal) + rbf(direct * u)) * g;
+          my_out[r * kTileChannels] = static_cast<unsigned short>(__float_as_uint(rbf(result)) >> 16U);
+        }
+      }
+    }
+    __syncthreads();
+    {
+      const int t = t0 + slab * kSlab + item_row;
+      if (item_ok && t < t1)
+        *reinterpret_cast<uint4 *>(p.output + static_cast<std::size_t>(t) * p.width + item_c0) =
+            *reinterpret_cast<const uint4 *>(out_tile + (lane * kSlab + item_row) * kTileChannels + item_chunk * 8);
+    }
+    // the next round's scan writes out_tile only after its own barrier; the stage buffer
+    // refilled next round is the one scanned two rounds ago
+  }
+}
+
 bool tiled_scan_applies(const ModalParams &p, const bool from_projection) {
   const auto aligned = [](const void *q) { return (reinterpret_cast<std::uintptr_t>(q) & 15U) == 0; };
   if (p.width % 8 != 0 || p.segment % kSlab != 0 || !aligned(p.output) ||
@@ -595,7 +715,10 @@ int launch_tiled(const ModalParams &p, cudaStream_t stream) {
   modal_carry_kernel<<<ceil_div_u(static_cast<std::size_t>(p.width) * kModes, 256), 256, 0, stream>>>(p, kModes);
   status = check_launch("modal carry kernel");
   if (status != kOk) return status;
-  modal_tiled_kernel<kModes, kFromProjection, true><<<grid, kScanThreads, smem, stream>>>(p);
+  if (kFromProjection && p.words != nullptr)
+    modal_words_output_kernel<kModes><<<grid, kScanThreads, 0, stream>>>(p);
+  else
+    modal_tiled_kernel<kModes, kFromProjection, true><<<grid, kScanThreads, smem, stream>>>(p);
   return check_launch("modal output kernel");
 }
 
@@ -641,7 +764,8 @@ std::size_t modal_scratch_floats(const std::size_t length,
                                  const std::size_t modes) {
   if (length == 0) return 0;
   const std::size_t segment = pick_segment(length, width);
-  return ((length + segment - 1) / segment) * width * modes;
+  // segment states, then one packed (u, x2) word per element for the projection-fed form
+  return ((length + segment - 1) / segment) * width * modes + length * width;
 }
 
 int modal_prefill(const ModalArgs &a, cudaStream_t stream) {
@@ -679,6 +803,14 @@ int modal_prefill(const ModalArgs &a, cudaStream_t stream) {
   p.segments = static_cast<int>((a.length - a.row_begin + p.segment - 1) / p.segment);
   p.pairs = static_cast<int>(a.width / 2);
   p.continue_from_state = a.continue_from_state;
+  // the words follow the segment states in the caller's scratch (sized by modal_scratch_floats
+  // for the whole length; the segment states of this call take at most that function's first term)
+  if (from_projection && a.width % 4 == 0) {
+    const std::size_t full_segment = static_cast<std::size_t>(pick_segment(a.length, a.width));
+    const std::size_t state_floats = ((a.length + full_segment - 1) / full_segment) * a.width * a.modes;
+    if (static_cast<std::size_t>(p.segments) * a.width * a.modes <= state_floats)
+      p.words = reinterpret_cast<std::uint32_t *>(a.scratch + state_floats);
+  }
   int status;
   switch (a.modes) {
     case 16: status = launch_modal<16>(p, from_projection, stream); break;
