@@ -55,6 +55,7 @@ SHAPE_TEXT = "Evo 2 7B-shaped StripedHyena2 (32 blocks, d_model 4096, FFN 11264,
 MODELS = {
     "evo2_7b": dict(seed=1, width=4096, inner=11264, layers=32, heads=32, attention_layers=5, label="7B"),
     "evo2_40b": dict(seed=2, width=8192, inner=22528, layers=50, heads=64, attention_layers=8, label="40B"),
+    "evo2_1b_base": dict(seed=0, width=1920, inner=5120, layers=25, heads=15, attention_layers=4, label="1B"),
 }
 
 

@@ -1,16 +1,19 @@
-// `evo` command-line driver for the CUDA path: run / score / bench, written
+// `evo` command-line driver for the CUDA path: run / score / bench / embed, written
 // against the public C ABI only (include/evo/evo.h + evo_b200.h).  Mirrors the
 // surface of upstream's CUDA CLI (src/cli.cpp:98-173,
 // src/cuda/inference_cli.cpp:199-263, 341-700, 1310-1345): the same
 // sub-commands and legacy flag form, score JSONL fields, bench JSONL schema
 // (include/evo/benchmark.hpp, src/benchmark.cpp:41-100), raw-byte generation on
-// stdout and one `evo_metrics {...}` line on stderr.  Exit code = evo_status.
+// stdout and one `evo_metrics {...}` line on stderr; `embed` writes one NPY v1
+// F32 matrix per record plus an embeddings.jsonl manifest into an empty or new
+// directory (src/cuda/inference_cli.cpp:278-337, 972-1108).  Exit code = evo_status.
 #include <algorithm>
 #include <chrono>
 #include <cmath>
 #include <cstdint>
 #include <cstdio>
 #include <cstring>
+#include <filesystem>
 #include <fstream>
 #include <iomanip>
 #include <iostream>
@@ -26,7 +29,8 @@ namespace {
 
 struct Options {
   std::string command = "run", model, prompt, input, profile = "exact", output_format = "raw",
-              name = "generated";
+              name = "generated", output, pooling = "none";
+  size_t layer = static_cast<size_t>(-1);
   std::vector<int32_t> gpus{0};
   size_t tokens = 0, context = 4096, warmup = 1, repetitions = 5, top_k = 1;
   float temperature = 1.0F, top_p = 1.0F;
@@ -143,6 +147,40 @@ double log_probability(const float *logits, const size_t vocab, const uint32_t t
   return static_cast<double>(logits[target]) - static_cast<double>(maximum) - std::log(normalizer);
 }
 
+struct Matrix {
+  std::vector<float> values;
+  size_t rows = 0, columns = 0;
+};
+
+evo_status collect_matrix(const float *values, size_t rows, size_t columns, size_t, const evo_embedding_result_info *,
+                          void *user) {
+  auto *matrix = static_cast<Matrix *>(user);
+  matrix->values.insert(matrix->values.end(), values, values + rows * columns);
+  matrix->rows += rows;
+  matrix->columns = columns;
+  return EVO_STATUS_OK;
+}
+
+// NPY format version 1.0: magic, version, little-endian header length, a Python
+// dict literal padded with spaces so the data starts on a 64-byte boundary.
+void write_npy(const std::filesystem::path &path, const Matrix &matrix) {
+  std::ostringstream dict;
+  dict << "{'descr': '<f4', 'fortran_order': False, 'shape': (" << matrix.rows << ", " << matrix.columns << "), }";
+  std::string header = dict.str();
+  const size_t unpadded = 10 + header.size() + 1;
+  header.append((64 - unpadded % 64) % 64, ' ');
+  header.push_back('\n');
+  std::ofstream out(path, std::ios::binary | std::ios::trunc);
+  const unsigned char prefix[10] = {0x93, 'N', 'U', 'M', 'P', 'Y', 1, 0,
+                                    static_cast<unsigned char>(header.size() & 0xff),
+                                    static_cast<unsigned char>(header.size() >> 8)};
+  out.write(reinterpret_cast<const char *>(prefix), 10);
+  out.write(header.data(), static_cast<std::streamsize>(header.size()));
+  out.write(reinterpret_cast<const char *>(matrix.values.data()),
+            static_cast<std::streamsize>(matrix.values.size() * sizeof(float)));
+  if (!out) die(EVO_STATUS_IO, "cannot write '" + path.string() + "'");
+}
+
 Options parse(int argc, char **argv) {
   Options o;
   int first = 1;
@@ -172,6 +210,9 @@ Options parse(int argc, char **argv) {
     else if (a == "--repetitions") o.repetitions = std::stoull(value(i));
     else if (a == "--output-format") o.output_format = value(i);
     else if (a == "--name") o.name = value(i);
+    else if (a == "--output") o.output = value(i);
+    else if (a == "--layer") o.layer = std::stoull(value(i));
+    else if (a == "--pooling") o.pooling = value(i);
     else if (a == "--allow-test-fixture") o.allow_fixture = true;
     else if (a == "--gpu") {
       o.gpus.clear();
@@ -181,7 +222,9 @@ Options parse(int argc, char **argv) {
     else if (a == "--help" || a == "-h") {
       std::cout << "usage:\n  evo run -m MODEL -p DNA -n TOKENS [--ctx N --gpu 0,1 --profile exact|b200-tc]\n"
                    "  evo score -m MODEL --input FASTA_FASTQ_OR_TEXT\n"
-                   "  evo bench -m MODEL --input FASTA_FASTQ_OR_TEXT [--warmup N --repetitions N]\n";
+                   "  evo bench -m MODEL --input FASTA_FASTQ_OR_TEXT [--warmup N --repetitions N]\n"
+                   "  evo embed -m MODEL --input FASTA_FASTQ_OR_TEXT --output DIR --layer N "
+                   "--pooling none|mean|last\n";
       std::exit(0);
     } else die(EVO_STATUS_INVALID_ARGUMENT, "unknown option " + a);
   }
@@ -287,6 +330,61 @@ int main(int argc, char **argv) {
       std::cout << ",\"token_log_likelihoods\":[";
       for (size_t i = 0; i < scores.size(); ++i) std::cout << (i ? "," : "") << scores[i];
       std::cout << "]}\n";
+    }
+  } else if (o.command == "embed") {
+    if (o.input.empty() || o.output.empty()) die(EVO_STATUS_INVALID_ARGUMENT, "embed needs --input and --output");
+    if (o.layer == static_cast<size_t>(-1)) die(EVO_STATUS_INVALID_ARGUMENT, "embed needs --layer");
+    if (o.pooling != "none" && o.pooling != "mean" && o.pooling != "last")
+      die(EVO_STATUS_INVALID_ARGUMENT, "--pooling must be none, mean or last");
+    namespace fs = std::filesystem;
+    const fs::path directory{o.output};
+    std::error_code error;
+    if (fs::exists(directory, error)) {
+      if (error || !fs::is_directory(directory, error))
+        die(EVO_STATUS_INVALID_ARGUMENT, "embedding output exists and is not a directory: '" + o.output + "'");
+      if (fs::directory_iterator(directory, error) != fs::directory_iterator{})
+        die(EVO_STATUS_INVALID_ARGUMENT, "embedding output directory must be empty: '" + o.output + "'");
+    } else if (error || !fs::create_directories(directory, error) || error) {
+      die(EVO_STATUS_IO, "cannot create embedding output directory '" + o.output + "'");
+    }
+    std::ofstream manifest(directory / "embeddings.jsonl", std::ios::binary | std::ios::trunc);
+    if (!manifest) die(EVO_STATUS_IO, "cannot open embedding manifest");
+    size_t record_index = 0;
+    for (const Record &record : read_records(o.input, o.context)) {
+      if (record.bytes.empty()) die(EVO_STATUS_INVALID_ARGUMENT, "embedding record '" + record.name + "' is empty");
+      if (last_context != nullptr) evo_context_free(last_context);
+      last_context = new_context(model, o);
+      evo_batch *batch = nullptr;
+      check(evo_batch_create(1, &batch), "batch");
+      check(evo_batch_add_sequence(batch, reinterpret_cast<const uint8_t *>(record.bytes.data()),
+                                   record.bytes.size()), "batch");
+      evo_embedding_options options = evo_embedding_default_options();
+      options.layer = o.layer;
+      options.pooling = o.pooling.c_str();
+      Matrix matrix;
+      const auto start = std::chrono::steady_clock::now();
+      const evo_status status = evo_context_embed_ex(last_context, batch, &options, collect_matrix, &matrix);
+      evo_batch_free(batch);
+      check(status, "embed");
+      metrics.prefill_seconds += seconds_since(start);
+      metrics.prefill_tokens += record.bytes.size();
+      std::ostringstream filename;
+      filename << std::setw(6) << std::setfill('0') << record_index << ".npy";
+      write_npy(directory / filename.str(), matrix);
+      manifest << "{\"record_index\":" << record_index << ",\"name\":";
+      json_string(manifest, record.name);
+      manifest << ",\"input_format\":\"" << record.format << "\",\"file\":";
+      json_string(manifest, filename.str());
+      manifest << ",\"source_tokens\":" << record.bytes.size() << ",\"shape\":[" << matrix.rows << ','
+               << matrix.columns << "],\"layer\":" << o.layer << ",\"point\":\"block_output\",\"pooling\":\""
+               << o.pooling << "\",\"dtype\":\"float32\",\"backend\":\"cuda\",\"profile\":\"" << o.profile
+               << "\",\"test_fixture\":" << (o.allow_fixture ? "true" : "false") << ",\"model_id\":";
+      const std::string id = evo_model_id(model);
+      if (id.empty()) manifest << "null"; else json_string(manifest, id);
+      manifest << "}\n";
+      manifest.flush();
+      if (!manifest) die(EVO_STATUS_IO, "cannot write the embedding manifest");
+      ++record_index;
     }
   } else if (o.command == "bench") {
     if (o.input.empty()) die(EVO_STATUS_INVALID_ARGUMENT, "bench needs --input");

@@ -102,3 +102,29 @@ def test_bench_report_schema(tmp_path):
     assert report["timing_scope"] == "prefill_with_host_logits" and report["statistic"] == "median"
     assert report["input"]["identity"].startswith("fnv1a64:") and len(report["input"]["identity"]) == 24
     assert abs(report["median_tokens_per_second"] - 10 / report["median_seconds"]) < 1e-6
+
+
+def test_embed_writes_npy_matrices_and_manifest(tmp_path):
+    """`evo embed`: one NPY v1 F32 matrix per record and an embeddings.jsonl manifest
+    (upstream src/cuda/inference_cli.cpp:278-303, 972-1108); rows agree with the
+    C ABI's evo_context_embed and pooling reduces them."""
+    fasta = tmp_path / "records.fa"
+    fasta.write_bytes(b">first\n\x02\x05\x07\x03\n>second\n\x09\x0b\x0d\n")
+    out = tmp_path / "emb"
+    run("embed", "--input", str(fasta), "--output", str(out), "--layer", "30", "--ctx", "64")
+    lines = [json.loads(l) for l in (out / "embeddings.jsonl").read_text().splitlines()]
+    assert [l["file"] for l in lines] == ["000000.npy", "000001.npy"]
+    assert lines[0]["name"] == "first" and lines[0]["source_tokens"] == 4 and lines[0]["shape"] == [4, 8]
+    assert (lines[0]["layer"], lines[0]["point"], lines[0]["pooling"], lines[0]["dtype"]) == (
+        30, "block_output", "none", "float32")
+    first = np.load(out / "000000.npy")
+    assert first.shape == (4, 8) and first.dtype == np.float32 and np.isfinite(first).all()
+    assert np.load(out / "000001.npy").shape == (3, 8)
+    pooled_dir = tmp_path / "mean"
+    run("embed", "--input", str(fasta), "--output", str(pooled_dir), "--layer", "30", "--pooling", "mean",
+        "--ctx", "64")
+    pooled = np.load(pooled_dir / "000000.npy")
+    assert pooled.shape == (1, 8)
+    np.testing.assert_allclose(pooled[0], first.mean(axis=0), rtol=1e-6, atol=1e-7)
+    # a non-empty output directory is refused (status 2), as upstream does
+    assert run("embed", "--input", str(fasta), "--output", str(out), "--layer", "30", check=False).returncode == 2
