@@ -6,7 +6,7 @@ and the ordered tensor manifest (name, dtype, shape) that upstream's own
 converter tooling (tools/evo/model_config.py: load_config, container_manifest,
 config_metadata; tools/evo/format.py: encode_metadata) would write, so that
 artifact.py can produce random-init artifacts that upstream's loader accepts.
-Needs the upstream tree (default /root/reference); the JSON files it writes are
+Needs the upstream tree (its path is the first argument); the JSON files it writes are
 committed and are all that is needed afterwards.
 """
 import json

@@ -1,7 +1,7 @@
 #!/usr/bin/env python3
 """Regenerates the committed golden fixtures from the upstream project.
 
-Run in a container that has the upstream tree (default /root/reference) and
+Run where the upstream tree is present (its path is the first argument) and
 the upstream CPU libraries built by `make -C oracle ref`.  Nothing at test or
 bench time needs the upstream tree; only this script does.
 
