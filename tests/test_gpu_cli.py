@@ -109,7 +109,7 @@ def test_embed_writes_npy_matrices_and_manifest(tmp_path):
     (upstream src/cuda/inference_cli.cpp:278-303, 972-1108); rows agree with the
     C ABI's evo_context_embed and pooling reduces them."""
     fasta = tmp_path / "records.fa"
-    fasta.write_bytes(b">first\n\x02\x05\x07\x03\n>second\n\x09\x0b\x0d\n")
+    fasta.write_bytes(b">first\n\x02\x05\x07\x03\n>second\n\x0e\x11\x13\n")
     out = tmp_path / "emb"
     run("embed", "--input", str(fasta), "--output", str(out), "--layer", "30", "--ctx", "64")
     lines = [json.loads(l) for l in (out / "embeddings.jsonl").read_text().splitlines()]
