@@ -229,7 +229,9 @@ __device__ __forceinline__ void store_tile(const Params &p, const unsigned char 
 }
 
 // ------------------------------------------------------------ CUDA cores
-template <bool kProj, int TT>
+// R = outputs per thread and the tap padding unit: 8 for the short filters
+// (k <= 8, so k = 7 costs 8 FMAs per output, not 16), 16 otherwise.
+template <bool kProj, int TT, int R>
 __global__ void __launch_bounds__(kThreads, 2)
 gated_fir_simt_kernel(const Params p) {
   extern __shared__ __align__(128) unsigned char smem[];
@@ -264,33 +266,33 @@ gated_fir_simt_kernel(const Params p) {
     direct0 = bf2f(p.direct[c0]);
     direct1 = bf2f(p.direct[c0 + 1]);
   }
-  for (int pass = 0; pass < TT / 128; ++pass) {
-    const int run0 = pass * 128 + sub * kRun;
+  for (int pass = 0; pass < TT / (8 * R); ++pass) {
+    const int run0 = pass * (8 * R) + sub * R;
     if (t0 + run0 >= p.length) break;
-    float acc0[kRun], acc1[kRun];
+    float acc0[R], acc1[R];
 #pragma unroll
-    for (int r = 0; r < kRun; ++r) acc0[r] = acc1[r] = 0.0F;
-    for (int d0 = p.padded_taps - kRun; d0 >= 0; d0 -= kRun) {
-      const int base = halo + run0 - d0 - (kRun - 1);
-      float w0[2 * kRun - 1], w1[2 * kRun - 1];
+    for (int r = 0; r < R; ++r) acc0[r] = acc1[r] = 0.0F;
+    for (int d0 = p.padded_taps - R; d0 >= 0; d0 -= R) {
+      const int base = halo + run0 - d0 - (R - 1);
+      float w0[2 * R - 1], w1[2 * R - 1];
 #pragma unroll
-      for (int i = 0; i < 2 * kRun - 1; ++i) {
+      for (int i = 0; i < 2 * R - 1; ++i) {
         const std::uint32_t packed = tile_pair(u_tile, base + i, pair);
         w0[i] = lo(packed);
         w1[i] = hi(packed);
       }
 #pragma unroll
-      for (int dd = kRun - 1; dd >= 0; --dd) {  // oldest input first
+      for (int dd = R - 1; dd >= 0; --dd) {  // oldest input first
         const float2 h = h_tile[(d0 + dd) * 32 + pair];
 #pragma unroll
-        for (int r = 0; r < kRun; ++r) {
-          acc0[r] = fmaf(w0[r - dd + kRun - 1], h.x, acc0[r]);
-          acc1[r] = fmaf(w1[r - dd + kRun - 1], h.y, acc1[r]);
+        for (int r = 0; r < R; ++r) {
+          acc0[r] = fmaf(w0[r - dd + R - 1], h.x, acc0[r]);
+          acc1[r] = fmaf(w1[r - dd + R - 1], h.y, acc1[r]);
         }
       }
     }
 #pragma unroll
-    for (int r = 0; r < kRun; ++r) {
+    for (int r = 0; r < R; ++r) {
       const int row = run0 + r;
       float y0 = acc0[r], y1 = acc1[r];
       if (p.direct != nullptr) {
@@ -459,7 +461,8 @@ int gated_fir_prefill(const GatedFirArgs &a, cudaStream_t stream) {
   p.row_begin = static_cast<int>(a.row_begin);
   p.width = static_cast<int>(a.width);
   p.taps = static_cast<int>(a.taps);
-  p.padded_taps = static_cast<int>((a.taps + kRun - 1) / kRun * kRun);
+  const std::size_t run = a.taps <= 8 ? 8 : kRun;
+  p.padded_taps = static_cast<int>((a.taps + run - 1) / run * run);
   p.channels_per_group = static_cast<int>(a.width / a.groups);
   p.filter_is_f32 = a.filter_is_f32;
   p.cross_correlation = a.cross_correlation;
@@ -473,22 +476,30 @@ int gated_fir_prefill(const GatedFirArgs &a, cudaStream_t stream) {
     status = from_projection
                  ? launch(gated_fir_mma_kernel<true, TT>, p, TT, smem, stream, "fused Toeplitz FIR kernel")
                  : launch(gated_fir_mma_kernel<false, TT>, p, TT, smem, stream, "fused Toeplitz FIR kernel");
+  } else if (p.padded_taps <= 8) {
+    constexpr int TT = 256;
+    const std::size_t smem = (TT + p.padded_taps - 1) * kRowBytes + TT * kRowBytes +
+                             static_cast<std::size_t>(p.padded_taps) * 32 * sizeof(float2) +
+                             (from_projection ? kRawBytes : 0);
+    status = from_projection
+                 ? launch(gated_fir_simt_kernel<true, TT, 8>, p, TT, smem, stream, "fused FIR kernel")
+                 : launch(gated_fir_simt_kernel<false, TT, 8>, p, TT, smem, stream, "fused FIR kernel");
   } else if (p.padded_taps <= 32) {
     constexpr int TT = 256;
     const std::size_t smem = (TT + p.padded_taps - 1) * kRowBytes + TT * kRowBytes +
                              static_cast<std::size_t>(p.padded_taps) * 32 * sizeof(float2) +
                              (from_projection ? kRawBytes : 0);
     status = from_projection
-                 ? launch(gated_fir_simt_kernel<true, TT>, p, TT, smem, stream, "fused FIR kernel")
-                 : launch(gated_fir_simt_kernel<false, TT>, p, TT, smem, stream, "fused FIR kernel");
+                 ? launch(gated_fir_simt_kernel<true, TT, 16>, p, TT, smem, stream, "fused FIR kernel")
+                 : launch(gated_fir_simt_kernel<false, TT, 16>, p, TT, smem, stream, "fused FIR kernel");
   } else {
     constexpr int TT = 128;
     const std::size_t smem = (TT + p.padded_taps - 1) * kRowBytes + TT * kRowBytes +
                              static_cast<std::size_t>(p.padded_taps) * 32 * sizeof(float2) +
                              (from_projection ? kRawBytes : 0);
     status = from_projection
-                 ? launch(gated_fir_simt_kernel<true, TT>, p, TT, smem, stream, "fused FIR kernel")
-                 : launch(gated_fir_simt_kernel<false, TT>, p, TT, smem, stream, "fused FIR kernel");
+                 ? launch(gated_fir_simt_kernel<true, TT, 16>, p, TT, smem, stream, "fused FIR kernel")
+                 : launch(gated_fir_simt_kernel<false, TT, 16>, p, TT, smem, stream, "fused FIR kernel");
   }
   if (status != kOk) return status;
   if (a.short_cache != nullptr && from_projection && a.short_taps > 1)
