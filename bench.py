@@ -320,7 +320,12 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> None:
                 "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
                 "peak_source": "MEASURED_PEAKS.json bf16_tflops_sustained (of measured)" if peaks else
                                "fallback 1.4 PFLOP/s sustained (of fallback)",
-                "traffic": None,
+                # DRAM read + write of one launch of this kernel from the committed ncu capture
+                # (M=8192 K=4096 N=8192: 256 MB algorithmic); the step's launches have other shapes
+                "traffic": 442.7e6,
+                "traffic_case": "ncu capture of gemm_tcgen05_kernel<bf16,256> at M=8192 K=4096 N=8192 "
+                                "(profiles/gemm_tcgen05_bf16_8192x4096x8192_full.md): 332.1 MB read + 110.6 MB "
+                                "written against 256 MB algorithmic",
                 "fp8_projection_tflops": flops_fp8 * args.steps / (fp8_ms * 1e-3) / 1e12 if fp8_ms else None,
                 "operator_ms_per_step": {k: v[0] / args.steps for k, v in profile.items() if v[1]}}
 
