@@ -29,6 +29,7 @@ OPS_SIGNATURES: dict[str, list] = {
     "evo_b200_software_e4m3_h100_linear": [_P, _P, _Z, _Z, _Z, _F, _F, _P, _P, _P],
     "evo_b200_e4m3_tensorcore_linear": [_P, _P, _Z, _Z, _Z, _F, _F, _P, _P, _P],
     "evo_b200_bf16_linear": [_P, _P, _P, _P, _Z, _Z, _Z, _I, _I, _P, _P],
+    "evo_b200_bf16_linear_split_k": [_P, _P, _P, _P, _Z, _Z, _Z, _I, _I, _P, _Z, _P, _P],
     "evo_b200_bf16_gated_up_projection": [_P, _P, _Z, _Z, _Z, _I, _P, _P],
     "evo_b200_interleave_gate_weights": [_P, _P, _Z, _Z, _P, _P],
     "evo_b200_bf16_rms_norm": [_P, _P, _Z, _Z, _F, _P, _P, _F, _P],

@@ -51,6 +51,11 @@ struct EpilogueParams {
   // B's K coordinate wraps after this many K blocks (0: never): A = [x0 | x1 | ...] against
   // the same weight columns
   int weight_wrap_blocks;
+  // Split-K (few rows: more CTAs pulling on the weight stream).  Tile t covers K blocks
+  // [split * per, (split + 1) * per) with split = t / (tiles_m * tiles_n) and writes its F32
+  // partial sums to out_f32 + split * partial_stride; a second kernel adds them up in order.
+  int split_k;
+  std::size_t partial_stride;
 };
 
 using namespace tc;
@@ -171,8 +176,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
 
   const int tiles_m = (M + kBlockM - 1) / kBlockM;
   const int tiles_n = (N + BN - 1) / BN;
-  const int tiles = tiles_m * tiles_n;
+  const int splits = ep.split_k > 1 ? ep.split_k : 1;
+  const int tiles_mn = tiles_m * tiles_n;
+  const int tiles = tiles_mn * splits;
   const int k_blocks = (K_bytes + kBlockKBytes - 1) / kBlockKBytes;
+  const int k_per_split = k_blocks / splits;  // the host picks a split count that divides
 
   if (warp == 0) {
     if (lane == 0) {
@@ -181,10 +189,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
       bool ok = true;
       for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x) {
         int tile_m, tile_n;
-        tile_coordinates(tile, tiles_m, tiles_n, &tile_m, &tile_n);
+        tile_coordinates(tile % tiles_mn, tiles_m, tiles_n, &tile_m, &tile_n);
         const int m0 = tile_m * kBlockM;
         const int n0 = tile_n * BN;
-        for (int kb = 0; kb < k_blocks; ++kb) {
+        const int kb_begin = (tile / tiles_mn) * k_per_split;
+        for (int kb = kb_begin; kb < kb_begin + k_per_split; ++kb) {
           if (!mbar_wait(empty_bar(stage), phase ^ 1U, abort_flag)) {
             ok = false;
             break;
@@ -218,7 +227,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
         if (!mbar_wait(tmem_empty_bar(acc), acc_phase ^ 1U, abort_flag)) break;
         tc_fence_after();
         const std::uint32_t tmem_d = tmem_base + acc * BN;
-        for (int kb = 0; kb < k_blocks; ++kb) {
+        for (int kb = 0; kb < k_per_split; ++kb) {
           if (!mbar_wait(full_bar(stage), phase, abort_flag)) {
             ok = false;
             break;
@@ -247,9 +256,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
     int local = 0;
     for (int tile = blockIdx.x; tile < tiles; tile += gridDim.x, ++local) {
       int tile_m, tile_n;
-      tile_coordinates(tile, tiles_m, tiles_n, &tile_m, &tile_n);
+      tile_coordinates(tile % tiles_mn, tiles_m, tiles_n, &tile_m, &tile_n);
       const int m0 = tile_m * kBlockM;
       const int n0 = tile_n * BN;
+      const int split = tile / tiles_mn;
       const int acc = local & 1;
       const std::uint32_t acc_phase = (local >> 1) & 1U;
       if (!mbar_wait(tmem_full_bar(acc), acc_phase, abort_flag)) break;
@@ -269,7 +279,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
         const int n_limit = gated ? N / 2 : N;
         if (ep.out_f32 != nullptr) {
           if (row < M && col < n_limit) {
-            float *const out_row = ep.out_f32 + static_cast<std::size_t>(row) * ep.ld_out;
+            float *const out_row = ep.out_f32 + static_cast<std::size_t>(split) * ep.partial_stride +
+                                   static_cast<std::size_t>(row) * ep.ld_out;
 #pragma unroll
             for (int j = 0; j < 32; ++j) {
               if (col + j < n_limit) {
@@ -425,6 +436,43 @@ gemm_simt_kernel(const void *__restrict__ a_raw, const void *__restrict__ b_raw,
   }
 }
 
+// Second step of split-K: adds the partial sums of one output element in split
+// order and applies the epilogue of the tile kernel (same expressions, same
+// BF16 rounding points), including the gate over 128-column halves.
+__global__ void __launch_bounds__(256)
+splitk_finish_kernel(const float *__restrict__ partials, const int splits, const std::size_t partial_stride,
+                     const EpilogueParams ep, const int M, const int N) {
+  const bool gated = ep.gate_mode != 0;
+  const int out_columns = gated ? N / 2 : N;
+  const std::size_t total = static_cast<std::size_t>(M) * out_columns;
+  const std::size_t stride = static_cast<std::size_t>(blockDim.x) * gridDim.x;
+  for (std::size_t i = static_cast<std::size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
+    const int row = static_cast<int>(i / out_columns), col = static_cast<int>(i % out_columns);
+    const auto sum = [&](const int column) {
+      float value = 0.0F;
+      for (int s = 0; s < splits; ++s)
+        value += partials[static_cast<std::size_t>(s) * partial_stride + static_cast<std::size_t>(row) * N + column];
+      return value * ep.alpha;
+    };
+    float result;
+    if (gated) {
+      const int first_column = (col / 128) * 256 + col % 128;
+      const float value = sum(first_column);
+      const float first = ep.gate_mode == 2 ? bf2f(gelu_round(value)) : rbf(value);
+      const float second = rbf(sum(first_column + 128));
+      result = rbf(first * second);
+    } else {
+      float value = sum(col);
+      if (ep.bias_mode == 1) value += bf2f(ep.bias[col]);
+      value = rbf(value);
+      if (ep.bias_mode == 2) value = rbf(value + bf2f(ep.bias[col]));
+      if (ep.residual != nullptr) value = rbf(value + bf2f(ep.residual[static_cast<std::size_t>(row) * ep.ld_out + col]));
+      result = value;
+    }
+    ep.out[static_cast<std::size_t>(row) * ep.ld_out + col] = f2bf(result);
+  }
+}
+
 // ------------------------------------------------------------ host side
 using EncodeTiled = CUresult (*)(CUtensorMap *, CUtensorMapDataType,
                                  cuuint32_t, void *, const cuuint64_t *,
@@ -526,7 +574,7 @@ int launch_tc(const void *a, const void *b, const EpilogueParams &ep,
     configured[device] = true;
   }
   const std::size_t tiles =
-      ((M + kBlockM - 1) / kBlockM) * ((N + BN - 1) / BN);
+      ((M + kBlockM - 1) / kBlockM) * ((N + BN - 1) / BN) * static_cast<std::size_t>(ep.split_k > 1 ? ep.split_k : 1);
   const unsigned int grid = static_cast<unsigned int>(
       tiles < static_cast<std::size_t>(state->sm_count) ? tiles
                                                         : state->sm_count);
@@ -612,6 +660,50 @@ int linear(const LinearArgs &args, cudaStream_t stream) {
       (reinterpret_cast<std::uintptr_t>(args.input) & 15U) == 0 &&
       (reinterpret_cast<std::uintptr_t>(args.weight) & 15U) == 0 &&
       args.out_features >= 64 && !args.force_simt;
+  // (measured: pays off up to a few dozen rows; at 128 rows the partial-sum traffic outweighs it)
+  if (tma_ok && args.split_workspace != nullptr && args.output_f32 == nullptr && args.rows <= 32 &&
+      pitch % kBlockKBytes == 0 && (args.gate_mode == 0 || args.out_features % 256 == 0)) {
+    // One row tile: the projection is a weight stream.  Split K so that enough CTAs pull on it,
+    // F32 partials in the caller's workspace, summed in split order by a second kernel.
+    const int bn = args.gate_mode != 0 ? 256 : 128;  // a gated tile holds both 128-column halves
+    const std::size_t tiles_n = (args.out_features + bn - 1) / bn;
+    const std::size_t k_blocks = pitch / kBlockKBytes;
+    int split = 1;
+    for (const int candidate : {8, 4, 2}) {
+      if (k_blocks % candidate == 0 && k_blocks / candidate >= 8 && tiles_n * candidate <= 2 * kSmCount &&
+          static_cast<std::size_t>(candidate) * args.rows * args.out_features * sizeof(float) <=
+              args.split_workspace_bytes) {
+        split = candidate;
+        break;
+      }
+    }
+    if (split > 1 && tiles_n < 120) {
+      EpilogueParams partial{};
+      partial.ld_out = args.out_features;
+      partial.alpha = 1.0F;
+      partial.out_f32 = static_cast<float *>(args.split_workspace);
+      partial.split_k = split;
+      partial.partial_stride = args.rows * args.out_features;
+      int status;
+      if (bn == 256)
+        status = fp8 ? launch_tc<true, 256>(args.input, args.weight, partial, args.rows, args.out_features,
+                                            args.in_features, stream)
+                     : launch_tc<false, 256>(args.input, args.weight, partial, args.rows, args.out_features,
+                                             args.in_features, stream);
+      else
+        status = fp8 ? launch_tc<true, 128>(args.input, args.weight, partial, args.rows, args.out_features,
+                                            args.in_features, stream)
+                     : launch_tc<false, 128>(args.input, args.weight, partial, args.rows, args.out_features,
+                                             args.in_features, stream);
+      if (status != kOk) return status;
+      const std::size_t outputs = args.rows * out_columns;
+      splitk_finish_kernel<<<static_cast<unsigned int>((outputs + 255) / 256 > 2048 ? 2048 : (outputs + 255) / 256),
+                             256, 0, stream>>>(static_cast<const float *>(args.split_workspace), split,
+                                               partial.partial_stride, ep, static_cast<int>(args.rows),
+                                               static_cast<int>(args.out_features));
+      return check_launch("split-K finishing kernel");
+    }
+  }
   if (tma_ok) {
     if (args.gate_mode != 0) {
       if (args.out_features % 256 != 0)

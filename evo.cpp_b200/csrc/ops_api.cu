@@ -116,6 +116,30 @@ int evo_b200_bf16_linear(const void *input, const void *weight,
   return linear(args, as_stream(stream));
 }
 
+int evo_b200_bf16_linear_split_k(const void *input, const void *weight, const void *bias,
+                                 const void *residual, size_t rows, size_t in_features,
+                                 size_t out_features, int bias_mode, int gate_mode,
+                                 void *workspace, size_t workspace_bytes, void *output,
+                                 void *stream) {
+  if (gate_mode < 0 || gate_mode > 2) return fail(kInvalidArgument, "gate mode must be 0, 1 or 2");
+  if (bias != nullptr && bias_mode != 1 && bias_mode != 2)
+    return fail(kInvalidArgument, "linear bias mode must be 1 or 2");
+  LinearArgs args;
+  args.input = input;
+  args.weight = weight;
+  args.bias = bias;
+  args.residual = residual;
+  args.output = output;
+  args.rows = rows;
+  args.in_features = in_features;
+  args.out_features = out_features;
+  args.bias_mode = bias == nullptr ? 0 : bias_mode;
+  args.gate_mode = gate_mode;
+  args.split_workspace = workspace;
+  args.split_workspace_bytes = workspace_bytes;
+  return linear(args, as_stream(stream));
+}
+
 int evo_b200_bf16_gated_up_projection(const void *input, const void *weight,
                                       size_t rows, size_t in_features,
                                       size_t inner_width, int activation,

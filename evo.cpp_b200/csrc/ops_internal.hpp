@@ -62,6 +62,12 @@ struct LinearArgs {
   // several planes side by side, [x0 | x1 | ...] with in_features = planes * W,
   // is multiplied against the same [out_features, W] weight: the sum of the
   // planes' products in one accumulator.
+  // Optional scratch for split-K at <= 32 rows (the projection is then a weight
+  // stream and needs more CTAs than it has output tiles): F32 partial sums,
+  // up to 8 * rows * out_features floats are used when they fit.  Owned by the
+  // caller, one per stream.
+  void *split_workspace = nullptr;
+  std::size_t split_workspace_bytes = 0;
   float *output_f32 = nullptr;
   const float *bias_f32 = nullptr;
   bool accumulate_f32 = false;

@@ -48,6 +48,7 @@ struct DeviceGuard {
 // buffers (>= the longest filter's reach of 127 + 2 featurizer rows, and a
 // multiple of 16 so the tensor-core FIR tiles keep their alignment).
 constexpr std::size_t kHistoryPad = 144;
+constexpr std::size_t kSplitWorkspaceBytes = std::size_t{64} << 20;
 
 struct LayerState {
   float *short_cache = nullptr;  // [3D, short_taps-1]
@@ -74,6 +75,7 @@ struct Context::Stage {
   void *mlp_first = nullptr, *mlp_second = nullptr;
   void *short_filtered = nullptr, *x2 = nullptr, *x1 = nullptr, *value = nullptr, *pregate = nullptr;
   float *modal_scratch = nullptr;
+  void *split_workspace = nullptr;  // F32 partial sums of split-K projections (<= 128 rows)
   std::uint32_t *tokens = nullptr;
   void *logits = nullptr;
   std::vector<LayerState> layers;
@@ -178,6 +180,8 @@ int Context::decode_step_graph(const std::uint32_t *host_token, bool *launched) 
                         nullptr, 1.0F, stream);
     if (status == kOk) {
       LinearArgs a;
+      a.split_workspace = first.split_workspace;
+      a.split_workspace_bytes = kSplitWorkspaceBytes;
       a.input = first.normalized;
       a.weight = first.weights->embedding;  // tied head
       a.output = first.logits;
@@ -257,6 +261,7 @@ int Context::create(std::shared_ptr<ModelWeights> weights, const std::size_t con
     EVOB_TRY(stage->allocate(&p, T * 4, arena));
     stage->tokens = static_cast<std::uint32_t *>(p);
     EVOB_TRY(stage->allocate(&stage->logits, T * c.vocab * 2, arena));
+    EVOB_TRY(stage->allocate(&stage->split_workspace, kSplitWorkspaceBytes, arena));
     stage->layers.resize(stage_weights->layers.size());
     std::size_t *cache = &stage->cache_bytes;
     for (std::size_t i = 0; i < stage->layers.size(); ++i) {
@@ -416,6 +421,8 @@ int Context::run_stage(Stage &s, const std::size_t rows, const Mode mode,
                                   w.projection_output_scale, s.projection, stream));
     } else {
       LinearArgs a;
+      a.split_workspace = s.split_workspace;
+      a.split_workspace_bytes = kSplitWorkspaceBytes;
       a.input = fp8 ? s.codes : s.normalized;
       a.weight = w.projection;
       a.output = s.projection;
@@ -561,6 +568,8 @@ int Context::run_stage(Stage &s, const std::size_t rows, const Mode mode,
     // output projection + bias + residual -> residual buffer
     {
       LinearArgs a;
+      a.split_workspace = s.split_workspace;
+      a.split_workspace_bytes = kSplitWorkspaceBytes;
       a.input = s.mixer_out;
       a.weight = w.out_weight;
       a.bias = w.out_bias;
@@ -580,6 +589,8 @@ int Context::run_stage(Stage &s, const std::size_t rows, const Mode mode,
     const bool gelu_block = layer_index == 0;
     if (w.l12 != nullptr) {
       LinearArgs a;
+      a.split_workspace = s.split_workspace;
+      a.split_workspace_bytes = kSplitWorkspaceBytes;
       a.input = s.normalized;
       a.weight = w.l12;
       a.output = s.gated;
@@ -590,6 +601,8 @@ int Context::run_stage(Stage &s, const std::size_t rows, const Mode mode,
       EVOB_OP(kCatGemmBf16, linear(a, stream));
     } else {
       LinearArgs a;
+      a.split_workspace = s.split_workspace;
+      a.split_workspace_bytes = kSplitWorkspaceBytes;
       a.input = s.normalized;
       a.rows = rows;
       a.in_features = D;
@@ -604,6 +617,8 @@ int Context::run_stage(Stage &s, const std::size_t rows, const Mode mode,
     }
     {
       LinearArgs a;
+      a.split_workspace = s.split_workspace;
+      a.split_workspace_bytes = kSplitWorkspaceBytes;
       a.input = s.gated;
       a.weight = w.l3;
       a.residual = s.residual;
@@ -760,6 +775,8 @@ int Context::forward(const std::uint32_t *host_tokens, const std::uint32_t *devi
                         first.normalized, nullptr, 1.0F, first.stream);
     if (status == kOk && !graph_step) {
       LinearArgs a;
+      a.split_workspace = first.split_workspace;
+      a.split_workspace_bytes = kSplitWorkspaceBytes;
       a.input = first.normalized;
       a.weight = first.weights->embedding;  // tied head
       a.output = first.logits;
@@ -866,6 +883,8 @@ int Context::slice_head(const std::size_t position, const std::size_t rows) {
                         1.0F, stage.stream);
   if (status != kOk) return status;
   LinearArgs a;
+  a.split_workspace = stage.split_workspace;
+  a.split_workspace_bytes = kSplitWorkspaceBytes;
   a.input = normalized;
   a.weight = stage.weights->embedding;  // tied head
   a.output = static_cast<unsigned char *>(stage.logits) + offset * c.vocab * 2;

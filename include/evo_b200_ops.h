@@ -65,6 +65,20 @@ EVO_B200_API int evo_b200_bf16_linear(const void *input, const void *weight,
                                       size_t rows, size_t in_features,
                                       size_t out_features, int bias_mode,
                                       int path, void *output, void *stream);
+/* The same projection with scratch for split-K (no upstream counterpart:
+ * cuBLASLt owns its workspace there).  At 9..32 rows a projection is a weight
+ * stream with fewer output tiles than SMs; with a workspace the K dimension is
+ * split over up to 8 CTAs per tile, F32 partial sums go to the workspace
+ * (split * rows * out_features floats are needed, less is fine: fewer or no
+ * splits) and are added in split order.  gate_mode 0 none, 1 / 2 = the gated
+ * up-projection of evo_b200_bf16_gated_up_projection (identity / GELU) with
+ * out_features = 2 * inner width.  The workspace must not be shared by calls
+ * that may overlap on the GPU. */
+EVO_B200_API int evo_b200_bf16_linear_split_k(
+    const void *input, const void *weight, const void *bias,
+    const void *residual, size_t rows, size_t in_features, size_t out_features,
+    int bias_mode, int gate_mode, void *workspace, size_t workspace_bytes,
+    void *output, void *stream);
 /* src/cuda/ops.cu:1205-1245 (bf16_mlp first half): gated = act(x W1^T) *
  * (x W2^T) in one GEMM over a row-interleaved [W1 | W2] weight built by
  * evo_b200_interleave_gate_weights; activation 0 identity, 1 GELU. */

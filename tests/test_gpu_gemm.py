@@ -126,3 +126,59 @@ def test_e4m3_tensorcore_linear_against_exact_products(ops, oracle, rows, inner,
     ops.call("software_e4m3_h100_linear", p(dev_bits(x)), p(dev(w_codes)), rows, inner, columns,
              float(in_scale), out_scale, p(scratch), p(emulated), stream())
     assert_close_bits(host_bits(out), host_bits(emulated), atol=0.02, rtol=0.02, min_cosine=0.9999)
+
+
+@pytest.mark.parametrize("rows,inner,columns", [(16, 4096, 4096), (32, 4096, 12288), (24, 11264, 4096),
+                                               (31, 4096, 512), (9, 2048, 1024)])
+def test_split_k_projection_against_f32_matmul(ops, rows, inner, columns):
+    """9..32 rows with a workspace: K is split over several CTAs per tile, F32 partials are
+    added in split order; bias, residual and their rounding points as in the one-pass kernel."""
+    torch.manual_seed(rows + columns)
+    x = torch.randn(rows, inner, device="cuda").bfloat16()
+    w = (torch.randn(columns, inner, device="cuda") * 0.02).bfloat16()
+    bias = (torch.randn(columns, device="cuda") * 0.5).bfloat16()
+    residual = torch.randn(rows, columns, device="cuda").bfloat16()
+    workspace = torch.empty(8 * rows * columns, device="cuda")
+    out = torch.empty(rows, columns, device="cuda", dtype=torch.bfloat16)
+    plain = torch.empty_like(out)
+    for bias_mode in (1, 2):
+        ops.call("bf16_linear_split_k", p(x), p(w), p(bias), p(residual), rows, inner, columns, bias_mode, 0,
+                 p(workspace), workspace.numel() * 4, p(out), stream())
+        ops.call("bf16_linear", p(x), p(w), p(bias), p(residual), rows, inner, columns, bias_mode, 0, p(plain),
+                 stream())
+        ops.call("check_async_errors", stream())
+        reference = x.float() @ w.float().T + bias.float() + residual.float()
+        error = (out.float() - reference).abs()
+        assert bool((error <= 0.03 + 0.02 * reference.abs()).all()), float(error.max())
+        # the one-pass kernel rounds the same sums: at most a BF16 ulp apart where F32 sums differ
+        assert float((out.float() - plain.float()).abs().max()) <= 0.07
+        assert float((out != plain).float().mean()) < 0.05
+    # a workspace too small for any split falls back to the one-pass kernel: identical bits
+    ops.call("bf16_linear_split_k", p(x), p(w), p(bias), p(residual), rows, inner, columns, 2, 0, p(workspace), 64,
+             p(out), stream())
+    assert torch.equal(out, plain)
+
+
+def test_split_k_gated_up_projection(ops):
+    torch.manual_seed(5)
+    rows, inner, hidden = 28, 4096, 2048
+    x = torch.randn(rows, inner, device="cuda").bfloat16()
+    w1 = (torch.randn(hidden, inner, device="cuda") * 0.02).bfloat16()
+    w2 = (torch.randn(hidden, inner, device="cuda") * 0.02).bfloat16()
+    packed = torch.empty(2 * hidden, inner, device="cuda", dtype=torch.bfloat16)
+    ops.call("interleave_gate_weights", p(w1), p(w2), hidden, inner, p(packed), stream())
+    workspace = torch.empty(8 * rows * 2 * hidden, device="cuda")
+    for activation in (0, 1):
+        split = torch.empty(rows, hidden, device="cuda", dtype=torch.bfloat16)
+        fused = torch.empty_like(split)
+        ops.call("bf16_linear_split_k", p(x), p(packed), None, None, rows, inner, 2 * hidden, 0, activation + 1,
+                 p(workspace), workspace.numel() * 4, p(split), stream())
+        ops.call("bf16_gated_up_projection", p(x), p(packed), rows, inner, hidden, activation, p(fused), stream())
+        ops.call("check_async_errors", stream())
+        first = (x.float() @ w1.float().T).bfloat16().float()
+        if activation == 1:
+            first = torch.nn.functional.gelu(first).bfloat16().float()
+        reference = first * (x.float() @ w2.float().T).bfloat16().float()
+        assert float((split.float() - reference).abs().max()) < 0.05
+        assert float((split.float() - fused.float()).abs().max()) < 0.05
+        assert float((split != fused).float().mean()) < 0.05
