@@ -710,8 +710,8 @@ int Context::forward(const std::uint32_t *host_tokens, const std::uint32_t *devi
   // activation buffers and every Hyena block puts its own last projection rows
   // in front of them.  (Short chunks and the exact cached-attention profile
   // keep the step kernels.)
-  const bool continuation_window =
-      mode == Mode::kContinue && rows >= 16 && !cached_attention_ && capture_layer < 0;
+  const bool continuation_window = mode == Mode::kContinue && rows >= 16 && !cached_attention_ &&
+                                   capture_layer < 0 && history_current_;
   struct ShiftBack {
     Context *context;
     bool active;
@@ -812,6 +812,9 @@ int Context::forward(const std::uint32_t *host_tokens, const std::uint32_t *devi
     return status;
   }
   const bool stateless = mode == Mode::kStateless;
+  // the per-block projection history is written by the fused prefill kernels only: steps taken
+  // with the step kernels (decode, short continuations) leave it behind the sequence
+  history_current_ = (initial && !stateless) || continuation_window;
   position_ = stateless ? 0 : (initial ? rows : position_ + rows);
   state_valid_ = !stateless;
   if (initial) cached_attention_ = mode == Mode::kCachedPrefill;

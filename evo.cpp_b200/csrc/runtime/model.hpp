@@ -191,6 +191,7 @@ class Context {
   ExecutionProfile profile_ = ExecutionProfile::kExact;
   std::size_t context_size_ = 0, arena_rows_ = 0, position_ = 0;
   bool state_valid_ = false, cached_attention_ = false, healthy_ = true;
+  bool history_current_ = false;  // per-block projection history covers the rows up to position_
 };
 
 }  // namespace evob

@@ -160,3 +160,33 @@ def test_decode_graph_replay_is_bit_identical(pkg, tmp_path_factory, monkeypatch
             assert np.array_equal(a, b)
             token = int(a.argmax())
         assert plain.position == replayed.position == 312
+
+
+def test_continuation_after_decode_steps_uses_current_state(pkg, tmp_path_factory):
+    """prefill -> a few decode steps -> a 100-row continuation chunk: the decode steps do not
+    update the fused kernels' carried projection history, so the chunk must fall back to the step
+    kernels and still agree with one pass over the whole sequence."""
+    rt = importlib.import_module("evo_cpp_b200.runtime")
+    art = importlib.import_module("evo_cpp_b200.artifact")
+    pipe = importlib.import_module("evo_cpp_b200.pipeline")
+    evo = rt.EvoLibrary(pkg.EVO_LIBRARY)
+    directory = tmp_path_factory.mktemp("mixed")
+    spec = art.fixture_spec(width=256, layers=8, heads=2, inner=512, hcs_groups=16, hcm_groups=16, fp8=True)
+    art.write_synthetic(directory / "model.safetensors", spec, seed=21, weight_std=0.05, filter_std=0.3)
+    model = evo.load(directory / "model.safetensors", devices=[0], flags=rt.MODEL_FLAG_ALLOW_SYNTHETIC)
+    flags = rt.CONTEXT_FLAG_FULL_ARENA | rt.CONTEXT_FLAG_TENSORCORE_FP8
+    rng = np.random.default_rng(8)
+    sequence = rng.choice(np.frombuffer(b"ACGT", np.uint8), 403)
+    expected = model.context(1024, flags).prefill(bytes(sequence.tolist()))
+    context = model.context(1024, flags)
+    context.prefill(bytes(sequence[:300].tolist()))
+    for token in sequence[300:303]:
+        context.decode(int(token))
+    tokens = torch.from_numpy(sequence.astype(np.int32)).cuda()
+    address = context.continue_device(tokens.data_ptr() + 4 * 303, 100)
+    context.synchronize()
+    raw = torch.as_tensor(pipe.DeviceRows(address, 100, 512), device="cuda")
+    got = ((raw.to(torch.int32) & 0xFFFF) << 16).view(torch.float32).cpu().numpy().astype(np.float64)
+    want = expected[303:403].astype(np.float64)
+    cosine = (got * want).sum() / (np.linalg.norm(got) * np.linalg.norm(want))
+    assert cosine > 0.9995 and np.abs(got - want).mean() < 0.05, (cosine, np.abs(got - want).mean())
