@@ -19,6 +19,12 @@
 //           H[m][k] = h[128 + m - k] is the same nine fragments for every tile.
 //  phase C  direct term, BF16 round, x2 post-gate, BF16 round, staged through
 //           shared memory and stored with 128-bit writes.
+//
+// Filters of up to 8 taps whose groups are multiples of 4 channels (HCS) do not
+// use tiles at all: gated_fir_stream_kernel keeps the whole sliding window in
+// registers and reads every input once.
+#include <algorithm>
+
 #include "common.cuh"
 #include "ops_internal.hpp"
 #include "projection_featurizer.cuh"
@@ -415,6 +421,229 @@ gated_fir_mma_kernel(const Params p) {
   store_tile(p, x2_tile, TT, t0, c_tile);
 }
 
+// ------------------------------------------------------- register streaming
+// Short filters (k <= 8): no shared memory at all.  A thread owns four
+// neighbouring channels and walks down a segment of rows; the 3-tap featurizer
+// history (two raw rows) and the last k-1 values of u live in registers, so
+// every input element is loaded exactly once per segment (plus k+1 warm-up rows
+// per segment) with 8-byte loads, and the loads of the next kUnroll rows are in
+// flight while the current ones are computed.  Same FMA order and rounding
+// points as the tiled kernel above.
+constexpr int kStreamThreads = 128;
+
+// kC/2 packed pairs from 4-byte-aligned (kC = 2) or 8-byte-aligned (kC = 4) memory
+template <int kC>
+__device__ __forceinline__ void load_pairs(const bf16 *source, std::uint32_t *words) {
+  if constexpr (kC == 4) {
+    const uint2 v = __ldcs(reinterpret_cast<const uint2 *>(source));
+    words[0] = v.x;
+    words[1] = v.y;
+  } else {
+    words[0] = __ldcs(reinterpret_cast<const unsigned int *>(source));
+  }
+}
+template <int kC>
+__device__ __forceinline__ void store_pairs(bf16 *target, const std::uint32_t *words) {
+  if constexpr (kC == 4)
+    *reinterpret_cast<uint2 *>(target) = make_uint2(words[0], words[1]);
+  else
+    *reinterpret_cast<unsigned int *>(target) = words[0];
+}
+
+template <bool kProj, int kTaps, int kC, int kUnroll>
+__global__ void __launch_bounds__(kStreamThreads)
+gated_fir_stream_kernel(const Params p, const int segment_rows) {
+  constexpr int kHalo = kTaps - 1;
+  constexpr int kWarm = kProj ? kHalo + 2 : kHalo;
+  constexpr int kPairs = kC / 2;
+  constexpr int kWords = 3 * kPairs;  // words of one row: 3 kC raw columns, or x1 | v | x2
+  const int c0 = (blockIdx.x * kStreamThreads + threadIdx.x) * kC;
+  if (c0 >= p.width) return;
+  const int t_own = p.row_begin + blockIdx.y * segment_rows;
+  const int t_end = min(p.length, t_own + segment_rows);
+  if (t_own >= t_end) return;
+
+  // h[d] multiplies u[t - d]; taps beyond the filter are zero
+  float h[kTaps];
+  {
+    const std::size_t base = static_cast<std::size_t>(c0 / p.channels_per_group) * p.taps;
+#pragma unroll
+    for (int d = 0; d < kTaps; ++d)
+      h[d] = d < p.taps ? filter_value(p.filter, p.filter_is_f32,
+                                       base + (p.cross_correlation ? p.taps - 1 - d : d))
+                        : 0.0F;
+  }
+  const bool has_direct = p.direct != nullptr;
+  float direct[kC];
+#pragma unroll
+  for (int c = 0; c < kC; ++c) direct[c] = has_direct ? bf2f(p.direct[c0 + c]) : 0.0F;
+  // featurizer taps of the 3 kC columns, [column][tap] as stored
+  float st[kProj ? 3 * kC : 1][3];
+  if constexpr (kProj) {
+    const unsigned int *const source =
+        reinterpret_cast<const unsigned int *>(p.short_filter + static_cast<std::size_t>(c0) * 9);
+#pragma unroll
+    for (int i = 0; i < 9 * kPairs; ++i) {
+      const unsigned int w = __ldg(source + i);
+      st[(2 * i) / 3][(2 * i) % 3] = lo(w);
+      st[(2 * i + 1) / 3][(2 * i + 1) % 3] = hi(w);
+    }
+  }
+
+  struct Row {
+    std::uint32_t w[kWords];
+  };
+  const auto load_row = [&](const int t, const bool wanted) {
+    Row row;
+#pragma unroll
+    for (int i = 0; i < kWords; ++i) row.w[i] = 0U;
+    if (wanted && t >= 0) {
+      if constexpr (kProj) {
+        const bf16 *const source =
+            p.projection + static_cast<std::size_t>(t) * 3 * p.width + static_cast<std::size_t>(c0) * 3;
+#pragma unroll
+        for (int i = 0; i < 3; ++i) load_pairs<kC>(source + i * kC, row.w + i * kPairs);
+      } else {
+        const std::size_t index = static_cast<std::size_t>(t) * p.width + c0;
+        load_pairs<kC>(p.x1 + index, row.w);
+        load_pairs<kC>(p.value + index, row.w + kPairs);
+        if (t >= t_own) load_pairs<kC>(p.x2 + index, row.w + 2 * kPairs);
+      }
+    }
+    return row;
+  };
+
+  float xh[2][kProj ? 3 * kC : 1];   // raw rows t-2, t-1
+#pragma unroll
+  for (int i = 0; i < (kProj ? 3 * kC : 1); ++i) xh[0][i] = xh[1][i] = 0.0F;
+  float uw[kHalo > 0 ? kHalo : 1][kC];  // uw[d - 1] = u[t - d]
+#pragma unroll
+  for (int d = 0; d < (kHalo > 0 ? kHalo : 1); ++d)
+#pragma unroll
+    for (int c = 0; c < kC; ++c) uw[d][c] = 0.0F;
+  const int real_halo = p.taps - 1;
+  const int t_first = t_own - kWarm;
+
+  Row next[kUnroll];
+#pragma unroll
+  for (int i = 0; i < kUnroll; ++i) next[i] = load_row(t_first + i, t_first + i < t_end);
+  for (int base = t_first; base < t_end; base += kUnroll) {
+    Row rows[kUnroll];
+#pragma unroll
+    for (int i = 0; i < kUnroll; ++i) rows[i] = next[i];
+#pragma unroll
+    for (int i = 0; i < kUnroll; ++i) next[i] = load_row(base + kUnroll + i, base + kUnroll + i < t_end);
+#pragma unroll
+    for (int i = 0; i < kUnroll; ++i) {
+      const int t = base + i;
+      float u[kC], gate[kC];
+      if constexpr (kProj) {
+        float x[3 * kC], z[3 * kC];
+#pragma unroll
+        for (int w = 0; w < kWords; ++w) {
+          x[2 * w] = lo(rows[i].w[w]);
+          x[2 * w + 1] = hi(rows[i].w[w]);
+        }
+#pragma unroll
+        for (int column = 0; column < 3 * kC; ++column) {
+          // fmaf with +0, not a multiply: the sign of a zero result must match the FMA chain
+          float acc = fmaf(xh[0][column], st[column][0], 0.0F);
+          acc = fmaf(xh[1][column], st[column][1], acc);
+          z[column] = rbf(fmaf(x[column], st[column][2], acc));
+          xh[0][column] = xh[1][column];
+          xh[1][column] = x[column];
+        }
+#pragma unroll
+        for (int c = 0; c < kC; ++c) {
+          gate[c] = z[3 * c];
+          u[c] = rbf(z[3 * c + 1] * z[3 * c + 2]);
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < kPairs; ++j) {
+          const std::uint32_t x1 = rows[i].w[j], v = rows[i].w[kPairs + j], g = rows[i].w[2 * kPairs + j];
+          u[2 * j] = rbf(lo(x1) * lo(v));
+          u[2 * j + 1] = rbf(hi(x1) * hi(v));
+          gate[2 * j] = lo(g);
+          gate[2 * j + 1] = hi(g);
+        }
+      }
+      const bool in_segment = t >= t_own && t < t_end;
+      if (in_segment) {
+        float y[kC];
+#pragma unroll
+        for (int c = 0; c < kC; ++c) {
+          float acc = 0.0F;
+#pragma unroll
+          for (int d = kHalo; d >= 1; --d) acc = fmaf(uw[d - 1][c], h[d], acc);  // oldest input first
+          acc = fmaf(u[c], h[0], acc);
+          if (has_direct) acc = fmaf(direct[c], u[c], acc);
+          y[c] = rbf(acc) * gate[c];
+        }
+        std::uint32_t packed[kPairs];
+#pragma unroll
+        for (int j = 0; j < kPairs; ++j) packed[j] = round_pair_bf16(y[2 * j], y[2 * j + 1]);
+        store_pairs<kC>(p.output + static_cast<std::size_t>(t) * p.width + c0, packed);
+        if (p.pregate != nullptr) {
+#pragma unroll
+          for (int j = 0; j < kPairs; ++j) packed[j] = pack_exact(u[2 * j], u[2 * j + 1]);
+          store_pairs<kC>(p.pregate + static_cast<std::size_t>(t) * p.width + c0, packed);
+        }
+      }
+      // The first segment of a row window also owns the history rows it
+      // recomputes, so that the decode history is complete even for windows
+      // shorter than it.
+      if (p.inner_cache != nullptr && real_halo > 0 && t < t_end &&
+          (t >= t_own || (blockIdx.y == 0 && t >= 0 && t >= t_own - kHalo))) {
+        const int slot = t - (p.length - real_halo);
+        if (slot >= 0) {
+#pragma unroll
+          for (int c = 0; c < kC; ++c) p.inner_cache[static_cast<std::size_t>(c0 + c) * real_halo + slot] = u[c];
+        }
+      }
+#pragma unroll
+      for (int d = kHalo - 1; d >= 1; --d)
+#pragma unroll
+        for (int c = 0; c < kC; ++c) uw[d][c] = uw[d - 1][c];
+      if constexpr (kHalo > 0) {
+#pragma unroll
+        for (int c = 0; c < kC; ++c) uw[0][c] = u[c];
+      }
+    }
+  }
+}
+
+template <bool kProj, int kTaps, int kC, int kUnroll>
+int launch_stream(const Params &p, cudaStream_t stream) {
+  const auto kernel = gated_fir_stream_kernel<kProj, kTaps, kC, kUnroll>;
+  static const int resident = [&] {
+    int blocks = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&blocks, kernel, kStreamThreads, 0) != cudaSuccess ||
+        blocks < 1)
+      blocks = 1;
+    return blocks;
+  }();
+  // One wave of CTAs: as many row segments as fill every SM once, none shorter
+  // than 32 rows (each segment recomputes k+1 warm-up rows).
+  const int rows = p.length - p.row_begin;
+  const int across = static_cast<int>(ceil_div_u(p.width, kStreamThreads * kC));
+  int segments = std::max(1, kSmCount * resident / across);
+  segments = std::max(1, std::min(segments, rows / 32));
+  const int segment_rows = (rows + segments - 1) / segments;
+  const dim3 grid(across, ceil_div_u(rows, segment_rows));
+  kernel<<<grid, kStreamThreads, 0, stream>>>(p, segment_rows);
+  return check_launch("streaming FIR kernel");
+}
+
+template <bool kProj>
+int launch_stream_taps(const Params &p, cudaStream_t stream) {
+  // k = 7 is the shape of every released model; other short filters pad to 8.
+  // Four channels per thread with four rows of loads in flight measured best
+  // (against two channels, or eight rows).
+  if (p.taps == 7) return launch_stream<kProj, 7, 4, 4>(p, stream);
+  return launch_stream<kProj, 8, 4, 4>(p, stream);
+}
+
 template <typename Kernel>
 int launch(Kernel kernel, const Params &p, const int tile_rows, const std::size_t smem,
            cudaStream_t stream, const char *what) {
@@ -476,6 +705,8 @@ int gated_fir_prefill(const GatedFirArgs &a, cudaStream_t stream) {
     status = from_projection
                  ? launch(gated_fir_mma_kernel<true, TT>, p, TT, smem, stream, "fused Toeplitz FIR kernel")
                  : launch(gated_fir_mma_kernel<false, TT>, p, TT, smem, stream, "fused Toeplitz FIR kernel");
+  } else if (p.taps <= 8 && p.channels_per_group % 4 == 0) {
+    status = from_projection ? launch_stream_taps<true>(p, stream) : launch_stream_taps<false>(p, stream);
   } else if (p.padded_taps <= 8) {
     constexpr int TT = 256;
     const std::size_t smem = (TT + p.padded_taps - 1) * kRowBytes + TT * kRowBytes +
