@@ -24,6 +24,7 @@
 // use tiles at all: gated_fir_stream_kernel keeps the whole sliding window in
 // registers and reads every input once.
 #include <algorithm>
+#include <type_traits>
 
 #include "common.cuh"
 #include "ops_internal.hpp"
@@ -43,6 +44,7 @@ struct Params {
   const void *filter;
   bf16 *output, *pregate;
   float *inner_cache;
+  float *short_cache;  // streaming kernel only: F32 [3 width, 2] raw projection history
   int length, row_begin, width, taps, padded_taps, channels_per_group;
   bool filter_is_f32, cross_correlation;
 };
@@ -450,11 +452,19 @@ __device__ __forceinline__ void store_pairs(bf16 *target, const std::uint32_t *w
     *reinterpret_cast<unsigned int *>(target) = words[0];
 }
 
-template <bool kProj, int kTaps, int kC, int kUnroll>
-__global__ void __launch_bounds__(kStreamThreads)
+// Product of two packed BF16 pairs, each rounded once: the same bits as
+// widening, multiplying in F32 (exact for BF16 operands) and rounding back.
+__device__ __forceinline__ std::uint32_t mul_pairs(const std::uint32_t a, const std::uint32_t b) {
+  std::uint32_t d;
+  asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+  return d;
+}
+
+template <bool kProj, int kTaps, int kC, int kUnroll, int kResident>
+__global__ void __launch_bounds__(kStreamThreads, kResident)
 gated_fir_stream_kernel(const Params p, const int segment_rows) {
   constexpr int kHalo = kTaps - 1;
-  constexpr int kWarm = kProj ? kHalo + 2 : kHalo;
+  constexpr int kWarm = ((kProj ? kHalo + 2 : kHalo) + kUnroll - 1) / kUnroll * kUnroll;
   constexpr int kPairs = kC / 2;
   constexpr int kWords = 3 * kPairs;  // words of one row: 3 kC raw columns, or x1 | v | x2
   const int c0 = (blockIdx.x * kStreamThreads + threadIdx.x) * kC;
@@ -493,22 +503,26 @@ gated_fir_stream_kernel(const Params p, const int segment_rows) {
   struct Row {
     std::uint32_t w[kWords];
   };
-  const auto load_row = [&](const int t, const bool wanted) {
+  // kChecked: the row may lie before the sequence, before this segment (no x2
+  // needed) or behind its end
+  const auto load_row = [&](auto checked, const int t) {
+    constexpr bool kChecked = decltype(checked)::value;
     Row row;
+    if constexpr (kChecked) {
 #pragma unroll
-    for (int i = 0; i < kWords; ++i) row.w[i] = 0U;
-    if (wanted && t >= 0) {
-      if constexpr (kProj) {
-        const bf16 *const source =
-            p.projection + static_cast<std::size_t>(t) * 3 * p.width + static_cast<std::size_t>(c0) * 3;
+      for (int i = 0; i < kWords; ++i) row.w[i] = 0U;
+      if (t < 0 || t >= t_end) return row;
+    }
+    if constexpr (kProj) {
+      const bf16 *const source =
+          p.projection + static_cast<std::size_t>(t) * 3 * p.width + static_cast<std::size_t>(c0) * 3;
 #pragma unroll
-        for (int i = 0; i < 3; ++i) load_pairs<kC>(source + i * kC, row.w + i * kPairs);
-      } else {
-        const std::size_t index = static_cast<std::size_t>(t) * p.width + c0;
-        load_pairs<kC>(p.x1 + index, row.w);
-        load_pairs<kC>(p.value + index, row.w + kPairs);
-        if (t >= t_own) load_pairs<kC>(p.x2 + index, row.w + 2 * kPairs);
-      }
+      for (int i = 0; i < 3; ++i) load_pairs<kC>(source + i * kC, row.w + i * kPairs);
+    } else {
+      const std::size_t index = static_cast<std::size_t>(t) * p.width + c0;
+      load_pairs<kC>(p.x1 + index, row.w);
+      load_pairs<kC>(p.value + index, row.w + kPairs);
+      if (!kChecked || t >= t_own) load_pairs<kC>(p.x2 + index, row.w + 2 * kPairs);
     }
     return row;
   };
@@ -522,54 +536,58 @@ gated_fir_stream_kernel(const Params p, const int segment_rows) {
 #pragma unroll
     for (int c = 0; c < kC; ++c) uw[d][c] = 0.0F;
   const int real_halo = p.taps - 1;
+  // first row whose u belongs to the decode history
+  const int cache_begin = (p.inner_cache != nullptr && real_halo > 0) ? p.length - real_halo : p.length;
   const int t_first = t_own - kWarm;
 
   Row next[kUnroll];
-#pragma unroll
-  for (int i = 0; i < kUnroll; ++i) next[i] = load_row(t_first + i, t_first + i < t_end);
-  for (int base = t_first; base < t_end; base += kUnroll) {
+  const auto run_group = [&](auto checked, const int base) {
+    constexpr bool kChecked = decltype(checked)::value;
     Row rows[kUnroll];
 #pragma unroll
     for (int i = 0; i < kUnroll; ++i) rows[i] = next[i];
 #pragma unroll
-    for (int i = 0; i < kUnroll; ++i) next[i] = load_row(base + kUnroll + i, base + kUnroll + i < t_end);
+    for (int i = 0; i < kUnroll; ++i) next[i] = load_row(checked, base + kUnroll + i);
 #pragma unroll
     for (int i = 0; i < kUnroll; ++i) {
       const int t = base + i;
-      float u[kC], gate[kC];
+      std::uint32_t u_pair[kPairs], gate_pair[kPairs];
       if constexpr (kProj) {
-        float x[3 * kC], z[3 * kC];
+        float z[3 * kC];
 #pragma unroll
         for (int w = 0; w < kWords; ++w) {
-          x[2 * w] = lo(rows[i].w[w]);
-          x[2 * w + 1] = hi(rows[i].w[w]);
+#pragma unroll
+          for (int half = 0; half < 2; ++half) {
+            const int column = 2 * w + half;
+            const float x = half == 0 ? lo(rows[i].w[w]) : hi(rows[i].w[w]);
+            // fmaf with +0, not a multiply: the sign of a zero result must match the FMA chain
+            float acc = fmaf(xh[0][column], st[column][0], 0.0F);
+            acc = fmaf(xh[1][column], st[column][1], acc);
+            z[column] = fmaf(x, st[column][2], acc);
+            xh[0][column] = xh[1][column];
+            xh[1][column] = x;
+          }
         }
 #pragma unroll
-        for (int column = 0; column < 3 * kC; ++column) {
-          // fmaf with +0, not a multiply: the sign of a zero result must match the FMA chain
-          float acc = fmaf(xh[0][column], st[column][0], 0.0F);
-          acc = fmaf(xh[1][column], st[column][1], acc);
-          z[column] = rbf(fmaf(x[column], st[column][2], acc));
-          xh[0][column] = xh[1][column];
-          xh[1][column] = x[column];
-        }
-#pragma unroll
-        for (int c = 0; c < kC; ++c) {
-          gate[c] = z[3 * c];
-          u[c] = rbf(z[3 * c + 1] * z[3 * c + 2]);
+        for (int j = 0; j < kPairs; ++j) {
+          const int a = 6 * j, b = 6 * j + 3;  // first columns (x2, x1, v) of the two channels
+          gate_pair[j] = round_pair_bf16(z[a], z[b]);
+          u_pair[j] = mul_pairs(round_pair_bf16(z[a + 1], z[b + 1]), round_pair_bf16(z[a + 2], z[b + 2]));
         }
       } else {
 #pragma unroll
         for (int j = 0; j < kPairs; ++j) {
-          const std::uint32_t x1 = rows[i].w[j], v = rows[i].w[kPairs + j], g = rows[i].w[2 * kPairs + j];
-          u[2 * j] = rbf(lo(x1) * lo(v));
-          u[2 * j + 1] = rbf(hi(x1) * hi(v));
-          gate[2 * j] = lo(g);
-          gate[2 * j + 1] = hi(g);
+          u_pair[j] = mul_pairs(rows[i].w[j], rows[i].w[kPairs + j]);
+          gate_pair[j] = rows[i].w[2 * kPairs + j];
         }
       }
-      const bool in_segment = t >= t_own && t < t_end;
-      if (in_segment) {
+      float u[kC];
+#pragma unroll
+      for (int j = 0; j < kPairs; ++j) {
+        u[2 * j] = lo(u_pair[j]);
+        u[2 * j + 1] = hi(u_pair[j]);
+      }
+      if (!kChecked || (t >= t_own && t < t_end)) {
         float y[kC];
 #pragma unroll
         for (int c = 0; c < kC; ++c) {
@@ -578,25 +596,31 @@ gated_fir_stream_kernel(const Params p, const int segment_rows) {
           for (int d = kHalo; d >= 1; --d) acc = fmaf(uw[d - 1][c], h[d], acc);  // oldest input first
           acc = fmaf(u[c], h[0], acc);
           if (has_direct) acc = fmaf(direct[c], u[c], acc);
-          y[c] = rbf(acc) * gate[c];
+          y[c] = acc;
         }
         std::uint32_t packed[kPairs];
 #pragma unroll
-        for (int j = 0; j < kPairs; ++j) packed[j] = round_pair_bf16(y[2 * j], y[2 * j + 1]);
+        for (int j = 0; j < kPairs; ++j)
+          packed[j] = mul_pairs(round_pair_bf16(y[2 * j], y[2 * j + 1]), gate_pair[j]);
         store_pairs<kC>(p.output + static_cast<std::size_t>(t) * p.width + c0, packed);
-        if (p.pregate != nullptr) {
+        if (p.pregate != nullptr) store_pairs<kC>(p.pregate + static_cast<std::size_t>(t) * p.width + c0, u_pair);
+      }
+      if constexpr (kChecked && kProj) {
+        // raw rows length-2 and length-1 are the featurizer's decode history
+        if (p.short_cache != nullptr && t == p.length - 1) {
 #pragma unroll
-          for (int j = 0; j < kPairs; ++j) packed[j] = pack_exact(u[2 * j], u[2 * j + 1]);
-          store_pairs<kC>(p.pregate + static_cast<std::size_t>(t) * p.width + c0, packed);
+          for (int column = 0; column < 3 * kC; ++column)
+            *reinterpret_cast<float2 *>(p.short_cache + (static_cast<std::size_t>(c0) * 3 + column) * 2) =
+                make_float2(xh[0][column], xh[1][column]);
         }
       }
-      // The first segment of a row window also owns the history rows it
-      // recomputes, so that the decode history is complete even for windows
-      // shorter than it.
-      if (p.inner_cache != nullptr && real_halo > 0 && t < t_end &&
-          (t >= t_own || (blockIdx.y == 0 && t >= 0 && t >= t_own - kHalo))) {
-        const int slot = t - (p.length - real_halo);
-        if (slot >= 0) {
+      if constexpr (kChecked) {
+        // The first segment of a row window also owns the history rows it
+        // recomputes, so that the decode history is complete even for windows
+        // shorter than it.
+        if (t >= cache_begin && t < t_end &&
+            (t >= t_own || (blockIdx.y == 0 && t >= 0 && t >= t_own - kHalo))) {
+          const int slot = t - cache_begin;
 #pragma unroll
           for (int c = 0; c < kC; ++c) p.inner_cache[static_cast<std::size_t>(c0 + c) * real_halo + slot] = u[c];
         }
@@ -610,12 +634,24 @@ gated_fir_stream_kernel(const Params p, const int segment_rows) {
         for (int c = 0; c < kC; ++c) uw[0][c] = u[c];
       }
     }
-  }
+  };
+
+  constexpr std::true_type kCheckedRows{};
+  constexpr std::false_type kPlainRows{};
+#pragma unroll
+  for (int i = 0; i < kUnroll; ++i) next[i] = load_row(kCheckedRows, t_first + i);
+  int base = t_first;
+  for (; base < t_own; base += kUnroll) run_group(kCheckedRows, base);  // warm-up: kWarm is a multiple of kUnroll
+  // steady state: this group and the one being fetched lie inside the segment,
+  // in front of the rows that feed the decode history
+  const int plain_end = min(t_end, cache_begin);
+  for (; base + 2 * kUnroll <= plain_end; base += kUnroll) run_group(kPlainRows, base);
+  for (; base < t_end; base += kUnroll) run_group(kCheckedRows, base);
 }
 
-template <bool kProj, int kTaps, int kC, int kUnroll>
+template <bool kProj, int kTaps, int kC, int kUnroll, int kResident>
 int launch_stream(const Params &p, cudaStream_t stream) {
-  const auto kernel = gated_fir_stream_kernel<kProj, kTaps, kC, kUnroll>;
+  const auto kernel = gated_fir_stream_kernel<kProj, kTaps, kC, kUnroll, kResident>;
   static const int resident = [&] {
     int blocks = 0;
     if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&blocks, kernel, kStreamThreads, 0) != cudaSuccess ||
@@ -640,8 +676,10 @@ int launch_stream_taps(const Params &p, cudaStream_t stream) {
   // k = 7 is the shape of every released model; other short filters pad to 8.
   // Four channels per thread with four rows of loads in flight measured best
   // (against two channels, or eight rows).
-  if (p.taps == 7) return launch_stream<kProj, 7, 4, 4>(p, stream);
-  return launch_stream<kProj, 8, 4, 4>(p, stream);
+  // The projection-fed form needs ~200 registers: two resident CTAs without
+  // spills measured faster than three with.
+  if (p.taps == 7) return launch_stream<kProj, 7, 4, 4, kProj ? 2 : 4>(p, stream);
+  return launch_stream<kProj, 8, 4, 4, kProj ? 2 : 4>(p, stream);
 }
 
 template <typename Kernel>
@@ -672,7 +710,10 @@ int gated_fir_prefill(const GatedFirArgs &a, cudaStream_t stream) {
       a.length == 0 || a.row_begin >= a.length || a.length > 0x7fff0000U || !aligned16(a.output) ||
       (a.pregate != nullptr && !aligned16(a.pregate)))
     return gated_fir_prefill_generic(a, stream);  // validates and reports
-  if (a.inner_cache != nullptr && a.taps > 1 &&
+  // the streaming kernel writes every history slot that has a row and the
+  // featurizer history itself
+  const bool streaming = a.taps <= 8 && (a.width / a.groups) % 4 == 0;
+  if (a.inner_cache != nullptr && a.taps > 1 && (!streaming || a.length < a.taps - 1) &&
       cudaMemsetAsync(a.inner_cache, 0, a.width * (a.taps - 1) * sizeof(float), stream) != cudaSuccess)
     return fail(kCuda, "cannot clear the FIR cache");
   Params p{};
@@ -705,7 +746,8 @@ int gated_fir_prefill(const GatedFirArgs &a, cudaStream_t stream) {
     status = from_projection
                  ? launch(gated_fir_mma_kernel<true, TT>, p, TT, smem, stream, "fused Toeplitz FIR kernel")
                  : launch(gated_fir_mma_kernel<false, TT>, p, TT, smem, stream, "fused Toeplitz FIR kernel");
-  } else if (p.taps <= 8 && p.channels_per_group % 4 == 0) {
+  } else if (streaming) {
+    p.short_cache = from_projection && a.short_taps == 3 ? a.short_cache : nullptr;
     status = from_projection ? launch_stream_taps<true>(p, stream) : launch_stream_taps<false>(p, stream);
   } else if (p.padded_taps <= 8) {
     constexpr int TT = 256;
@@ -733,7 +775,7 @@ int gated_fir_prefill(const GatedFirArgs &a, cudaStream_t stream) {
                  : launch(gated_fir_simt_kernel<false, TT, 16>, p, TT, smem, stream, "fused FIR kernel");
   }
   if (status != kOk) return status;
-  if (a.short_cache != nullptr && from_projection && a.short_taps > 1)
+  if (a.short_cache != nullptr && from_projection && a.short_taps > 1 && p.short_cache == nullptr)
     status = fill_fir_cache(a.projection, a.short_cache, a.length, a.width * 3, a.short_taps - 1, stream);
   return status;
 }

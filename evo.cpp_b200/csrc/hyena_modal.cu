@@ -7,18 +7,20 @@
 // (src/cuda/hyena.cu:562-660, 1262-1456, 1994-2124).  Because the filter is a
 // sum of first-order modes, the same convolution is a linear recurrence
 // s_m[t] = p_m s_m[t-1] + u[t], y[t] = sum_m R_m s_m[t]; here it runs as a
-// three-kernel chunked scan that is linear in T, needs T*C*modes/segment
-// floats of scratch instead of FFT planes, and yields the decode state for free:
+// two-kernel chunked scan that is linear in T, needs one state per segment of
+// scratch instead of FFT planes, and yields the decode state for free:
 //   1. per (segment, channel pair): end state of the segment from zero,
-//   2. per (channel, mode): serial carry over segments (p^S scaling),
-//   3. per (segment, channel pair): replay from the carried state, read out,
-//      add the direct term, post-gate, store.
+//   2. per (segment, channel pair): fold the end states of the earlier
+//      segments into the carried-in state (p^S scaling), replay from it, read
+//      out, add the direct term, post-gate, store.
 // The four BF16 roundings of the upstream epilogue are kept for initial
 // prefill; continuation chunks keep upstream's single rounding
 // (src/cuda/hyena.cu:534-560).  modal_decode keeps the pinned decode order
 // (separate multiply/add, 32-lane zero-padded tree; src/cuda/hyena.cu:718-761).
+#include <algorithm>
 #include <mutex>
 #include <string>
+#include <type_traits>
 
 #include "common.cuh"
 #include "ops_internal.hpp"
@@ -27,263 +29,17 @@
 namespace evob {
 namespace {
 
-constexpr int kThreads = 128;
-
 struct ModalParams {
   const bf16 *x2, *x1, *value, *projection, *short_filter, *direct;
   const float *log_poles, *residues;
   bf16 *output, *pregate;
   float *state;    // [width, modes]
-  float *scratch;  // [segments, width, modes]
-  // optional [length, width] packed (u | x2 << 16) words: written by the
-  // projection-fed local pass, read by the output pass instead of featurizing again
-  std::uint32_t *words;
+  float *scratch;  // [segments + 1, width, modes]
+  float *short_cache;          // optional F32 [3 width, 2] raw projection history for decode
+  std::size_t scratch_floats;  // capacity of scratch
   int length, row_begin, width, segment, segments, pairs;
   bool continue_from_state;
 };
-
-// Streams one channel pair through time, yielding the featurized gate values.
-template <bool kFromProjection>
-struct PairReader {
-  const ModalParams &p;
-  int c0;
-  float prev1[6], prev2[6];  // raw projection rows t-1, t-2 (x2a,x1a,va,x2b,x1b,vb)
-  float sw[6][3];            // featurizer taps per stream of the pair
-
-  __device__ __forceinline__ PairReader(const ModalParams &params, const int channel)
-      : p(params), c0(channel) {}
-
-  __device__ __forceinline__ void load_row(const int t, float (&row)[6]) const {
-    if (t < 0) {
-#pragma unroll
-      for (int i = 0; i < 6; ++i) row[i] = 0.0F;
-      return;
-    }
-    const std::uint32_t *const words = reinterpret_cast<const std::uint32_t *>(
-        p.projection + static_cast<std::size_t>(t) * p.width * 3 + c0 * 3);
-#pragma unroll
-    for (int w = 0; w < 3; ++w) {
-      const std::uint32_t word = words[w];
-      row[2 * w] = __uint_as_float(word << 16U);
-      row[2 * w + 1] = __uint_as_float(word & 0xffff0000U);
-    }
-  }
-
-  __device__ __forceinline__ void start(const int t0) {
-    if constexpr (kFromProjection) {
-#pragma unroll
-      for (int s = 0; s < 6; ++s)
-#pragma unroll
-        for (int j = 0; j < 3; ++j)
-          sw[s][j] = bf2f(p.short_filter[(static_cast<std::size_t>(c0) * 3 + s) * 3 + j]);
-      load_row(t0 - 1, prev1);
-      load_row(t0 - 2, prev2);
-    }
-  }
-
-  // Loads issued for kBatch consecutive rows before any of them is consumed:
-  // the recurrence is a serial dependency chain, so memory latency has to be
-  // covered by independent loads in flight, not by the chain.
-  static constexpr int kBatch = 8;
-
-  __device__ __forceinline__ void fetch(const int t, const int limit, const bool want_x2,
-                                        std::uint32_t (&raw)[kBatch][3]) const {
-#pragma unroll
-    for (int i = 0; i < kBatch; ++i) {
-      const int row = t + i;
-      raw[i][0] = raw[i][1] = raw[i][2] = 0U;
-      if (row < limit) {
-        if constexpr (kFromProjection) {
-          const std::uint32_t *const words = reinterpret_cast<const std::uint32_t *>(
-              p.projection + static_cast<std::size_t>(row) * p.width * 3 + c0 * 3);
-          raw[i][0] = __ldg(words);
-          raw[i][1] = __ldg(words + 1);
-          raw[i][2] = __ldg(words + 2);
-        } else {
-          const std::size_t index = static_cast<std::size_t>(row) * p.width + c0;
-          raw[i][0] = __ldg(reinterpret_cast<const std::uint32_t *>(p.x1 + index));
-          raw[i][1] = __ldg(reinterpret_cast<const std::uint32_t *>(p.value + index));
-          if (want_x2) raw[i][2] = __ldg(reinterpret_cast<const std::uint32_t *>(p.x2 + index));
-        }
-      }
-    }
-  }
-
-  // Consumes one fetched row: u for both channels and the x2 gate.
-  __device__ __forceinline__ void step(const std::uint32_t (&words)[3], float &u0, float &u1,
-                                       float &g0, float &g1) {
-    if constexpr (kFromProjection) {
-      float row[6], z[6];
-#pragma unroll
-      for (int w = 0; w < 3; ++w) {
-        row[2 * w] = __uint_as_float(words[w] << 16U);
-        row[2 * w + 1] = __uint_as_float(words[w] & 0xffff0000U);
-      }
-#pragma unroll
-      for (int s = 0; s < 6; ++s) {
-        float a = 0.0F;
-        a = fmaf(prev2[s], sw[s][0], a);
-        a = fmaf(prev1[s], sw[s][1], a);
-        a = fmaf(row[s], sw[s][2], a);
-        z[s] = rbf(a);
-        prev2[s] = prev1[s];
-        prev1[s] = row[s];
-      }
-      u0 = rbf(z[1] * z[2]);
-      u1 = rbf(z[4] * z[5]);
-      g0 = z[0];
-      g1 = z[3];
-    } else {
-      const std::uint32_t a = words[0], b = words[1], g = words[2];
-      u0 = rbf(__uint_as_float(a << 16U) * __uint_as_float(b << 16U));
-      u1 = rbf(__uint_as_float(a & 0xffff0000U) * __uint_as_float(b & 0xffff0000U));
-      g0 = __uint_as_float(g << 16U);
-      g1 = __uint_as_float(g & 0xffff0000U);
-    }
-  }
-};
-
-template <int kModes, bool kFromProjection>
-__global__ void __launch_bounds__(kThreads)
-modal_local_kernel(const ModalParams p) {
-  const int index = blockIdx.x * kThreads + threadIdx.x;
-  const int pair = index % p.pairs;
-  const int seg = index / p.pairs;
-  if (seg >= p.segments) return;
-  const int c0 = pair * 2;
-  if (c0 >= p.width) return;
-  float pole[2][kModes], state[2][kModes];
-#pragma unroll
-  for (int c = 0; c < 2; ++c)
-#pragma unroll
-    for (int m = 0; m < kModes; ++m) {
-      pole[c][m] = expf(p.log_poles[static_cast<std::size_t>(c0 + c) * kModes + m]);
-      state[c][m] = 0.0F;
-    }
-  const int t0 = p.row_begin + seg * p.segment;
-  const int t1 = min(t0 + p.segment, p.length);
-  PairReader<kFromProjection> reader(p, c0);
-  reader.start(t0);
-  constexpr int kBatch = PairReader<kFromProjection>::kBatch;
-  for (int t = t0; t < t1; t += kBatch) {
-    std::uint32_t raw[kBatch][3];
-    reader.fetch(t, t1, false, raw);
-#pragma unroll
-    for (int i = 0; i < kBatch; ++i) {
-      if (t + i < t1) {
-        float u0, u1, g0, g1;
-        reader.step(raw[i], u0, u1, g0, g1);
-#pragma unroll
-        for (int m = 0; m < kModes; ++m) {
-          state[0][m] = fmaf(pole[0][m], state[0][m], u0);
-          state[1][m] = fmaf(pole[1][m], state[1][m], u1);
-        }
-      }
-    }
-  }
-  float *const out = p.scratch + (static_cast<std::size_t>(seg) * p.width + c0) * kModes;
-#pragma unroll
-  for (int c = 0; c < 2; ++c)
-#pragma unroll
-    for (int m = 0; m < kModes; ++m) out[c * kModes + m] = state[c][m];
-}
-
-// scratch[seg] holds the segment-local end state on entry and the state carried
-// INTO the segment on exit; the state after the last segment goes to p.state.
-__global__ void modal_carry_kernel(const ModalParams p, const int modes) {
-  const int index = blockIdx.x * blockDim.x + threadIdx.x;
-  if (index >= p.width * modes) return;
-  const float log_pole = p.log_poles[index];
-  const float full_decay = expf(log_pole * static_cast<float>(p.segment));
-  float carry = (p.continue_from_state && p.state != nullptr) ? p.state[index] : 0.0F;
-  const std::size_t stride = static_cast<std::size_t>(p.width) * modes;
-  // The chain over segments is serial; its loads are not, so they are issued
-  // a batch at a time ahead of the dependent arithmetic.
-  constexpr int kAhead = 16;
-  for (int seg0 = 0; seg0 < p.segments; seg0 += kAhead) {
-    float local[kAhead];
-#pragma unroll
-    for (int i = 0; i < kAhead; ++i)
-      local[i] = seg0 + i < p.segments ? __ldcg(p.scratch + (seg0 + i) * stride + index) : 0.0F;
-#pragma unroll
-    for (int i = 0; i < kAhead; ++i) {
-      const int seg = seg0 + i;
-      if (seg < p.segments) {
-        p.scratch[seg * stride + index] = carry;
-        const int span = min(p.segment, p.length - p.row_begin - seg * p.segment);
-        const float decay =
-            span == p.segment ? full_decay : expf(log_pole * static_cast<float>(span));
-        carry = fmaf(decay, carry, local[i]);
-      }
-    }
-  }
-  if (p.state != nullptr) p.state[index] = carry;
-}
-
-template <int kModes, bool kFromProjection>
-__global__ void __launch_bounds__(kThreads)
-modal_output_kernel(const ModalParams p) {
-  const int index = blockIdx.x * kThreads + threadIdx.x;
-  const int pair = index % p.pairs;
-  const int seg = index / p.pairs;
-  if (seg >= p.segments) return;
-  const int c0 = pair * 2;
-  if (c0 >= p.width) return;
-  float pole[2][kModes], residue[2][kModes], state[2][kModes];
-  const float *const carried =
-      p.scratch + (static_cast<std::size_t>(seg) * p.width + c0) * kModes;
-#pragma unroll
-  for (int c = 0; c < 2; ++c)
-#pragma unroll
-    for (int m = 0; m < kModes; ++m) {
-      const std::size_t q = static_cast<std::size_t>(c0 + c) * kModes + m;
-      pole[c][m] = expf(p.log_poles[q]);
-      residue[c][m] = p.residues[q];
-      state[c][m] = carried[c * kModes + m];
-    }
-  const float direct0 = bf2f(p.direct[c0]);
-  const float direct1 = bf2f(p.direct[c0 + 1]);
-  const int t0 = p.row_begin + seg * p.segment;
-  const int t1 = min(t0 + p.segment, p.length);
-  PairReader<kFromProjection> reader(p, c0);
-  reader.start(t0);
-  constexpr int kBatch = PairReader<kFromProjection>::kBatch;
-  for (int tb = t0; tb < t1; tb += kBatch) {
-   std::uint32_t raw[kBatch][3];
-   reader.fetch(tb, t1, true, raw);
-#pragma unroll
-   for (int i = 0; i < kBatch; ++i) {
-    const int t = tb + i;
-    if (t >= t1) break;
-    float u[2], g[2];
-    reader.step(raw[i], u[0], u[1], g[0], g[1]);
-    float result[2];
-#pragma unroll
-    for (int c = 0; c < 2; ++c) {
-      float partial[4] = {0.0F, 0.0F, 0.0F, 0.0F};
-#pragma unroll
-      for (int m = 0; m < kModes; ++m) {
-        state[c][m] = fmaf(pole[c][m], state[c][m], u[c]);
-        partial[m % 4] = fmaf(residue[c][m], state[c][m], partial[m % 4]);
-      }
-      const float modal = ((partial[0] + partial[1]) + partial[2]) + partial[3];
-      const float direct = c == 0 ? direct0 : direct1;
-      if (p.continue_from_state) {
-        result[c] = g[c] * fmaf(direct, u[c], modal);
-      } else {
-        const float mixed = rbf(rbf(modal) + rbf(direct * u[c]));
-        result[c] = mixed * g[c];
-      }
-    }
-    const std::size_t offset = static_cast<std::size_t>(t) * p.width + c0;
-    *reinterpret_cast<std::uint32_t *>(p.output + offset) =
-        pack_bf16x2(result[0], result[1]);
-    if (p.pregate != nullptr)
-      *reinterpret_cast<std::uint32_t *>(p.pregate + offset) =
-          (__float_as_uint(u[0]) >> 16U) | (__float_as_uint(u[1]) & 0xffff0000U);
-   }
-  }
-}
 
 __global__ void modal_decode_kernel(const bf16 *__restrict__ x2,
                                     const bf16 *__restrict__ x1,
@@ -323,438 +79,306 @@ __global__ void modal_decode_kernel(const bf16 *__restrict__ x2,
   output[channel] = f2bf(__fmul_rn(bf2f(x2[channel]), mixed));
 }
 
-// ---------------------------------------------------------------- tiled scan
-// The same local / output passes with the inputs staged through shared memory.
-// A CTA owns 64 channels x kLanes consecutive segments and walks them in slabs
-// of kSlab rows: cp.async copies the next slab's rows (double buffered) while
-// the current one is featurized cooperatively with 128-bit accesses - one
-// (segment lane, row, 8-channel chunk) per thread - into packed (u, x2) words;
-// then every thread advances the recurrence of ONE channel of one segment lane
-// over the slab's rows, reading its word per row from shared memory, and the
-// finished rows leave through a shared tile with 128-bit stores.  No thread
-// waits on a global load of its own, and the per-thread state is 3*modes
-// registers instead of 6*modes, which is what lets two CTAs share an SM.
-constexpr int kScanThreads = 256;
-constexpr int kTileChannels = 64;
-constexpr int kLanes = 4;
-constexpr int kSlab = 8;
-constexpr int kProjRowBytes = kTileChannels * 3 * 2;                      // 384
-constexpr int kProjStageBytes = kLanes * (kSlab + 2) * kProjRowBytes;     // 15360
-constexpr int kPlainRowBytes = kTileChannels * 2;                         // 128
-constexpr int kPlainStageBytes = 3 * kLanes * kSlab * kPlainRowBytes;     // 12288
-constexpr int kWordTileBytes = kLanes * kSlab * kTileChannels * 4;        // 8192
-constexpr int kOutTileBytes = kLanes * kSlab * kTileChannels * 2;         // 4096
-constexpr int kWeightBytes = 8 * 36 * 4;                                  // 1152
+// -------------------------------------------------------- register streaming
+// Two kernels, no shared memory.  A thread owns one channel pair and walks down
+// one segment of rows with the featurizer history, the poles and the 2 x modes
+// states in registers; the loads of the next kUnroll rows are in flight while
+// the current ones are consumed, so every input element is read once per pass
+// with nothing staged.  The grid is one wave: as many segments as fill every SM
+// once.
+//   pass 1 (kOutput = false)  end state of each segment but the last, from zero
+//   pass 2 (kOutput = true)   every thread first folds the end states of the
+//                             segments before its own into its carried-in state
+//                             (a serial chain of at most `segments` steps per
+//                             mode), then replays its segment, reads out, applies
+//                             the epilogue and stores; the thread of the last
+//                             segment leaves the decode state and the featurizer
+//                             history behind.
+// scratch: [segments] local end states, then one slot for the state carried into
+// the first segment of a continuation (copied there by pass 1, because pass 2
+// overwrites p.state while other segments may still have to read it).
+constexpr int kStreamThreads = 128;
 
-template <bool kFromProjection>
-constexpr int tiled_smem_bytes() {
-  return 2 * (kFromProjection ? kProjStageBytes : kPlainStageBytes) + kWordTileBytes + kOutTileBytes +
-         (kFromProjection ? kWeightBytes : 0);
+__device__ __forceinline__ std::uint32_t mul_pairs(const std::uint32_t a, const std::uint32_t b) {
+  std::uint32_t d;  // both products rounded once: the bits of rbf(float(a) * float(b))
+  asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+  return d;
 }
-
-__device__ __forceinline__ void async_copy16(void *shared, const void *global, const bool valid) {
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(
-                   static_cast<std::uint32_t>(__cvta_generic_to_shared(shared))),
-               "l"(global), "r"(valid ? 16U : 0U)
-               : "memory");
+__device__ __forceinline__ std::uint32_t add_pairs(const std::uint32_t a, const std::uint32_t b) {
+  std::uint32_t d;  // sums of BF16 values rounded once: the bits of rbf(float(a) + float(b))
+  asm("add.rn.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+  return d;
 }
+__device__ __forceinline__ float pair_lo(const std::uint32_t w) { return __uint_as_float(w << 16U); }
+__device__ __forceinline__ float pair_hi(const std::uint32_t w) { return __uint_as_float(w & 0xffff0000U); }
 
-// A thread's share of the 16-byte copies of a slab; the (lane, row, chunk) a
-// thread copies is the same for every slab, so only the row bound is checked
-// per slab.
-template <bool kFromProjection, bool kNeedGate>
-struct ModalCopies {
-  static constexpr int kTotal =
-      kFromProjection ? kLanes * (kSlab + 2) * 24 : (kNeedGate ? 3 : 2) * kLanes * kSlab * 8;
-  static constexpr int kPerThread = (kTotal + kScanThreads - 1) / kScanThreads;
-  const bf16 *source[kPerThread];   // address of the copy for slab 0 (may be out of range: see row)
-  std::uint32_t destination[kPerThread];
-  int row[kPerThread];              // time of the copy for slab 0; a huge value when unused
+template <int kModes, bool kProj, bool kOutput, int kUnroll>
+__global__ void __launch_bounds__(kStreamThreads, kOutput ? 2 : 3)
+modal_stream_kernel(const ModalParams p) {
+  constexpr int kC = 2;             // a channel pair per thread: one 32-bit word per stream and row
+  constexpr int kColumns = 3 * kC;  // projection-fed: (x2, x1, v) per channel; else x1 | v | x2
+  const int c0 = (blockIdx.x * kStreamThreads + threadIdx.x) * kC;
+  if (c0 >= p.width) return;
+  const int seg = blockIdx.y;
+  const int t_own = p.row_begin + seg * p.segment;
+  const int t_end = min(p.length, t_own + p.segment);
+  const std::size_t per_segment = static_cast<std::size_t>(p.width) * kModes;
+  const std::size_t mine = static_cast<std::size_t>(c0) * kModes;  // the thread's kC x kModes values are contiguous
 
-  __device__ __forceinline__ void plan(const ModalParams &p, const int seg0, const int c_tile) {
+  float pole[kC][kModes], state[kC][kModes];
+  [[maybe_unused]] float residue[kC][kModes];
+  if constexpr (kOutput) {
+    const float *const initial =
+        p.continue_from_state ? (p.segments > 1 ? p.scratch + p.segments * per_segment : p.state) : nullptr;
 #pragma unroll
-    for (int k = 0; k < kPerThread; ++k) {
-      const int item = threadIdx.x + k * kScanThreads;
-      int lane, j, t, column_elements;
-      const bf16 *base;
-      std::size_t pitch;
-      bool used = item < kTotal;
-      if constexpr (kFromProjection) {
-        const int chunk = item % 24;
-        j = (item / 24) % (kSlab + 2);
-        lane = item / (24 * (kSlab + 2));
-        t = p.row_begin + (seg0 + lane) * p.segment + j - 2;
-        pitch = static_cast<std::size_t>(p.width) * 3;
-        column_elements = c_tile * 3 + chunk * 8;
-        used = used && static_cast<std::size_t>(column_elements) + 8 <= pitch;
-        base = p.projection;
-        destination[k] = static_cast<std::uint32_t>((lane * (kSlab + 2) + j) * kProjRowBytes + chunk * 16);
-      } else {
-        const int chunk = item % 8;
-        j = (item / 8) % kSlab;
-        lane = (item / (8 * kSlab)) % kLanes;
-        const int stream = item / (8 * kSlab * kLanes);
-        t = p.row_begin + (seg0 + lane) * p.segment + j;
-        pitch = static_cast<std::size_t>(p.width);
-        column_elements = c_tile + chunk * 8;
-        used = used && column_elements < p.width;
-        base = stream == 0 ? p.x1 : (stream == 1 ? p.value : p.x2);
-        destination[k] =
-            static_cast<std::uint32_t>(((stream * kLanes + lane) * kSlab + j) * kPlainRowBytes + chunk * 16);
-      }
-      used = used && seg0 + lane < p.segments;
-      row[k] = used ? t : 0x40000000;
-      source[k] = base + static_cast<long long>(t) * static_cast<long long>(pitch) + column_elements;
-    }
-  }
-  __device__ __forceinline__ void issue(const ModalParams &p, unsigned char *stage, const int slab) const {
-    const std::uint32_t base = static_cast<std::uint32_t>(__cvta_generic_to_shared(stage));
-    const std::size_t advance = static_cast<std::size_t>(slab) * kSlab *
-                                (kFromProjection ? static_cast<std::size_t>(p.width) * 3 : p.width);
+    for (int c = 0; c < kC; ++c)
 #pragma unroll
-    for (int k = 0; k < kPerThread; ++k) {
-      if (threadIdx.x + k * kScanThreads >= kTotal) break;
-      const bool valid = static_cast<unsigned int>(row[k] + slab * kSlab) < static_cast<unsigned int>(p.length);
-      const bf16 *const from = valid ? source[k] + advance : p.direct;
-      asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(base + destination[k]), "l"(from),
-                   "r"(valid ? 16U : 0U)
-                   : "memory");
-    }
-    asm volatile("cp.async.commit_group;" ::: "memory");
-  }
-};
-
-template <int kModes, bool kFromProjection, bool kOutput>
-__global__ void __launch_bounds__(kScanThreads, 2)
-modal_tiled_kernel(const ModalParams p) {
-  extern __shared__ __align__(128) unsigned char smem[];
-  constexpr int kStageBytes = kFromProjection ? kProjStageBytes : kPlainStageBytes;
-  unsigned char *const stages = smem;
-  std::uint32_t *const words = reinterpret_cast<std::uint32_t *>(smem + 2 * kStageBytes);
-  unsigned short *const out_tile = reinterpret_cast<unsigned short *>(smem + 2 * kStageBytes + kWordTileBytes);
-  std::uint32_t *const weights =
-      reinterpret_cast<std::uint32_t *>(smem + 2 * kStageBytes + kWordTileBytes + kOutTileBytes);
-  const int seg0 = blockIdx.x * kLanes;
-  const int c_tile = blockIdx.y * kTileChannels;
-  const int lane = threadIdx.x / kTileChannels;  // segment lane of both roles
-  const int column = threadIdx.x % kTileChannels;
-
-  // ---- scan role: channel `channel` of segment seg0 + lane
-  const int channel = c_tile + column;
-  const int seg = seg0 + lane;
-  const bool scans = channel < p.width && seg < p.segments;
-  const int t0 = p.row_begin + seg * p.segment;
-  const int t1 = min(t0 + p.segment, p.length);
-  float pole[kModes], residue[kModes], state[kModes];
-  float direct = 0.0F;
+      for (int m = 0; m < kModes; ++m)
+        state[c][m] = initial != nullptr ? __ldcg(initial + mine + c * kModes + m) : 0.0F;
+    if (seg > 0) {
+      float decay[kC][kModes];
 #pragma unroll
-  for (int m = 0; m < kModes; ++m) {
-    pole[m] = residue[m] = state[m] = 0.0F;
-    if (scans) {
-      const std::size_t q = static_cast<std::size_t>(channel) * kModes + m;
-      pole[m] = expf(p.log_poles[q]);
-      if constexpr (kOutput) {
-        residue[m] = p.residues[q];
-        state[m] = p.scratch[(static_cast<std::size_t>(seg) * p.width + channel) * kModes + m];
+      for (int c = 0; c < kC; ++c)
+#pragma unroll
+        for (int m = 0; m < kModes; ++m)
+          decay[c][m] = expf(p.log_poles[mine + c * kModes + m] * static_cast<float>(p.segment));
+      for (int j = 0; j < seg; ++j) {
+        const float *const local = p.scratch + j * per_segment + mine;
+#pragma unroll
+        for (int c = 0; c < kC; ++c)
+#pragma unroll
+          for (int m = 0; m < kModes; ++m)
+            state[c][m] = fmaf(decay[c][m], state[c][m], __ldcg(local + c * kModes + m));
       }
     }
+  } else {
+    if (seg == 0 && p.continue_from_state) {
+      float *const slot = p.scratch + p.segments * per_segment + mine;
+#pragma unroll
+      for (int i = 0; i < kC * kModes; ++i) slot[i] = p.state[mine + i];
+    }
+#pragma unroll
+    for (int c = 0; c < kC; ++c)
+#pragma unroll
+      for (int m = 0; m < kModes; ++m) state[c][m] = 0.0F;
   }
-  if constexpr (kOutput)
-    if (scans) direct = bf2f(p.direct[channel]);
+#pragma unroll
+  for (int c = 0; c < kC; ++c)
+#pragma unroll
+    for (int m = 0; m < kModes; ++m) {
+      pole[c][m] = expf(p.log_poles[mine + c * kModes + m]);
+      if constexpr (kOutput) residue[c][m] = p.residues[mine + c * kModes + m];
+    }
+  [[maybe_unused]] std::uint32_t direct_pair = 0U;
+  [[maybe_unused]] float direct[kC] = {0.0F, 0.0F};
+  if constexpr (kOutput) {
+    direct_pair = *reinterpret_cast<const std::uint32_t *>(p.direct + c0);
+    direct[0] = pair_lo(direct_pair);
+    direct[1] = pair_hi(direct_pair);
+  }
 
-  // ---- featurize / store role: row item_row, channels item_c0 .. +8 of the lane
-  const int item_chunk = threadIdx.x % 8;
-  const int item_row = (threadIdx.x / 8) % kSlab;
-  const int item_c0 = c_tile + item_chunk * 8;
-  const bool item_ok = item_c0 < p.width && seg < p.segments;
-  if constexpr (kFromProjection) {
-    if (threadIdx.x < 72) {
-      const int chunk = threadIdx.x / 9, part = threadIdx.x % 9;
-      uint4 v = make_uint4(0U, 0U, 0U, 0U);
-      if (c_tile + chunk * 8 < p.width)
-        v = __ldg(reinterpret_cast<const uint4 *>(p.short_filter +
-                                                  static_cast<std::size_t>(c_tile + chunk * 8) * 9) + part);
-      *reinterpret_cast<uint4 *>(weights + chunk * 36 + part * 4) = v;
-    }
-  }
-  ModalCopies<kFromProjection, kOutput> copies;
-  copies.plan(p, seg0, c_tile);
-  const int slabs = p.segment / kSlab;
-  copies.issue(p, stages, 0);
-  for (int slab = 0; slab < slabs; ++slab) {
-    const unsigned char *const stage = stages + (slab & 1) * kStageBytes;
-    if (slab + 1 < slabs) {
-      copies.issue(p, stages + ((slab + 1) & 1) * kStageBytes, slab + 1);
-      asm volatile("cp.async.wait_group 1;" ::: "memory");
-    } else {
-      asm volatile("cp.async.wait_group 0;" ::: "memory");
-    }
-    __syncthreads();
-    {  // featurize one (lane, row, chunk) item into packed words: u low, x2 high
-      std::uint32_t u[4], g[4] = {0U, 0U, 0U, 0U};
-      if constexpr (kFromProjection) {
-        const unsigned char *const base =
-            stage + (lane * (kSlab + 2) + item_row) * kProjRowBytes + item_chunk * 48;
-        const unsigned char *const history[3] = {base, base + kProjRowBytes, base + 2 * kProjRowBytes};
-        PackedTaps taps;
-        taps.load_shared(weights + item_chunk * 36);
-        if constexpr (kOutput) {
-          featurize_chunk<true>(history, taps, u, g);
-        } else {
-          // the local pass needs only u, unless it also leaves the words for the output pass
-          if (p.words != nullptr) featurize_chunk<true>(history, taps, u, g);
-          else featurize_chunk<false>(history, taps, u, g);
-        }
-      } else {
-        const unsigned char *const base = stage + (lane * kSlab + item_row) * kPlainRowBytes + item_chunk * 16;
-        Bf16x8 a, b;
-        a.raw = *reinterpret_cast<const uint4 *>(base);
-        b.raw = *reinterpret_cast<const uint4 *>(base + kLanes * kSlab * kPlainRowBytes);
-#pragma unroll
-        for (int j = 0; j < 4; ++j)
-          u[j] = round_pair_bf16(a.get(2 * j) * b.get(2 * j), a.get(2 * j + 1) * b.get(2 * j + 1));
-        if constexpr (kOutput) {
-          const uint4 c = *reinterpret_cast<const uint4 *>(base + 2 * kLanes * kSlab * kPlainRowBytes);
-          g[0] = c.x; g[1] = c.y; g[2] = c.z; g[3] = c.w;
-        }
-      }
-      uint4 *const destination = reinterpret_cast<uint4 *>(
-          words + (lane * kSlab + item_row) * kTileChannels + item_chunk * 8);
-      // word of channel c = u_c | x2_c << 16
-      destination[0] = make_uint4(__byte_perm(u[0], g[0], 0x5410), __byte_perm(u[0], g[0], 0x7632),
-                                  __byte_perm(u[1], g[1], 0x5410), __byte_perm(u[1], g[1], 0x7632));
-      destination[1] = make_uint4(__byte_perm(u[2], g[2], 0x5410), __byte_perm(u[2], g[2], 0x7632),
-                                  __byte_perm(u[3], g[3], 0x5410), __byte_perm(u[3], g[3], 0x7632));
-      if constexpr (kFromProjection && !kOutput) {
-        const int t = t0 + slab * kSlab + item_row;
-        if (p.words != nullptr && item_ok && t < t1) {
-          uint4 *const out = reinterpret_cast<uint4 *>(p.words + static_cast<std::size_t>(t) * p.width + item_c0);
-          out[0] = destination[0];
-          out[1] = destination[1];
-        }
-      }
-      if constexpr (kOutput) {
-        const int t = t0 + slab * kSlab + item_row;
-        if (p.pregate != nullptr && item_ok && t < t1)
-          *reinterpret_cast<uint4 *>(p.pregate + static_cast<std::size_t>(t) * p.width + item_c0) =
-              make_uint4(u[0], u[1], u[2], u[3]);
-      }
-    }
-    __syncthreads();
-    if (scans) {
-      const int first = t0 + slab * kSlab;
-      const std::uint32_t *const my_words = words + lane * kSlab * kTileChannels + column;
-      unsigned short *const my_out = out_tile + lane * kSlab * kTileChannels + column;
-      // rows of this slab inside the segment (all of them except in the last segment)
-      const int live = min(kSlab, t1 - first);
-#pragma unroll
-      for (int r = 0; r < kSlab; ++r) {
-        if (r < live) {
-          const std::uint32_t word = my_words[r * kTileChannels];
-          const float u = __uint_as_float(word << 16U);
-          if constexpr (kOutput) {
-            const float g = __uint_as_float(word & 0xffff0000U);
-            float partial[4] = {0.0F, 0.0F, 0.0F, 0.0F};
-#pragma unroll
-            for (int m = 0; m < kModes; ++m) {
-              state[m] = fmaf(pole[m], state[m], u);
-              partial[m % 4] = fmaf(residue[m], state[m], partial[m % 4]);
-            }
-            const float modal = ((partial[0] + partial[1]) + partial[2]) + partial[3];
-            float result;
-            if (p.continue_from_state)
-              result = g * fmaf(direct, u, modal);
-            else
-              result = rbf(rbf(modal) + rbf(direct * u)) * g;
-            my_out[r * kTileChannels] = static_cast<unsigned short>(__float_as_uint(rbf(result)) >> 16U);
-          } else {
-#pragma unroll
-            for (int m = 0; m < kModes; ++m) state[m] = fmaf(pole[m], state[m], u);
-          }
-        }
-      }
-    }
-    if constexpr (kOutput) {
-      __syncthreads();
-      const int t = t0 + slab * kSlab + item_row;
-      if (item_ok && t < t1)
-        *reinterpret_cast<uint4 *>(p.output + static_cast<std::size_t>(t) * p.width + item_c0) =
-            *reinterpret_cast<const uint4 *>(out_tile + (lane * kSlab + item_row) * kTileChannels + item_chunk * 8);
-    }
-  }
-  if constexpr (!kOutput) {
-    if (scans) {
-      float *const out = p.scratch + (static_cast<std::size_t>(seg) * p.width + channel) * kModes;
-#pragma unroll
-      for (int m = 0; m < kModes; ++m) out[m] = state[m];
-    }
-  }
-}
-
-// Output pass from the stored (u, x2) words: no featurizer, no raw staging -
-// the words of the next slab are copied in while this one is scanned.
-
-template <int kModes>
-__global__ void __launch_bounds__(kScanThreads, 3)
-modal_words_output_kernel(const ModalParams p) {
-  __shared__ __align__(16) std::uint32_t stages[2][kLanes * kSlab * kTileChannels];
-  __shared__ __align__(16) unsigned short out_tile[kLanes * kSlab * kTileChannels];
-  const int seg0 = blockIdx.x * kLanes;
-  const int c_tile = blockIdx.y * kTileChannels;
-  const int lane = threadIdx.x / kTileChannels;
-  const int column = threadIdx.x % kTileChannels;
-  const int channel = c_tile + column;
-  const int seg = seg0 + lane;
-  const bool scans = channel < p.width && seg < p.segments;
-  const int t0 = p.row_begin + seg * p.segment;
-  const int t1 = min(t0 + p.segment, p.length);
-  float pole[kModes], residue[kModes], state[kModes];
-  float direct = 0.0F;
-#pragma unroll
-  for (int m = 0; m < kModes; ++m) {
-    pole[m] = residue[m] = state[m] = 0.0F;
-    if (scans) {
-      const std::size_t q = static_cast<std::size_t>(channel) * kModes + m;
-      pole[m] = expf(p.log_poles[q]);
-      residue[m] = p.residues[q];
-      state[m] = p.scratch[(static_cast<std::size_t>(seg) * p.width + channel) * kModes + m];
-    }
-  }
-  if (scans) direct = bf2f(p.direct[channel]);
-  // copy / store role: row item_row of the lane, two 16-byte chunks (8 channels) per thread
-  const int item_chunk = threadIdx.x % 8;
-  const int item_row = (threadIdx.x / 8) % kSlab;
-  const int item_c0 = c_tile + item_chunk * 8;
-  const bool item_ok = item_c0 < p.width && seg < p.segments;
-  const auto issue = [&](const int slab, std::uint32_t *const stage) {
-    const int t = t0 + slab * kSlab + item_row;
-    const bool valid = item_ok && t < t1;
-    const std::uint32_t *const source =
-        valid ? p.words + static_cast<std::size_t>(t) * p.width + item_c0 : p.words;
-    std::uint32_t *const target = stage + (lane * kSlab + item_row) * kTileChannels + item_chunk * 8;
-    async_copy16(target, source, valid);
-    async_copy16(target + 4, source + 4, valid);
-    asm volatile("cp.async.commit_group;" ::: "memory");
+  struct Row {
+    std::uint32_t w[3];  // projection-fed: (x2a x1a) (va x2b) (x1b vb); else x1 | v | x2 pairs
   };
-  const int slabs = p.segment / kSlab;
-  issue(0, stages[0]);
-  for (int slab = 0; slab < slabs; ++slab) {
-    const std::uint32_t *const stage = stages[slab & 1];
-    if (slab + 1 < slabs) {
-      issue(slab + 1, stages[(slab + 1) & 1]);
-      asm volatile("cp.async.wait_group 1;" ::: "memory");
-    } else {
-      asm volatile("cp.async.wait_group 0;" ::: "memory");
+  const auto load_row = [&](auto checked, const int t) {
+    constexpr bool kChecked = decltype(checked)::value;
+    Row row;
+    row.w[0] = row.w[1] = row.w[2] = 0U;
+    if constexpr (kChecked) {
+      if (t < 0 || t >= t_end) return row;
     }
-    __syncthreads();
-    if (p.pregate != nullptr) {
-      const int t = t0 + slab * kSlab + item_row;
-      if (item_ok && t < t1) {
-        const std::uint32_t *const w = stage + (lane * kSlab + item_row) * kTileChannels + item_chunk * 8;
-        *reinterpret_cast<uint4 *>(p.pregate + static_cast<std::size_t>(t) * p.width + item_c0) =
-            make_uint4(__byte_perm(w[0], w[1], 0x5410), __byte_perm(w[2], w[3], 0x5410),
-                       __byte_perm(w[4], w[5], 0x5410), __byte_perm(w[6], w[7], 0x5410));
-      }
-    }
-    if (scans) {
-      const std::uint32_t *const my_words = stage + lane * kSlab * kTileChannels + column;
-      unsigned short *const my_out = out_tile + lane * kSlab * kTileChannels + column;
-      const int live = min(kSlab, t1 - (t0 + slab * kSlab));
+    if constexpr (kProj) {
+      const bf16 *const source =
+          p.projection + static_cast<std::size_t>(t) * 3 * p.width + static_cast<std::size_t>(c0) * 3;
 #pragma unroll
-      for (int r = 0; r < kSlab; ++r) {
-        if (r < live) {
-          const std::uint32_t word = my_words[r * kTileChannels];
-          const float u = __uint_as_float(word << 16U);
-          const float g = __uint_as_float(word & 0xffff0000U);
+      for (int i = 0; i < 3; ++i) row.w[i] = __ldcs(reinterpret_cast<const unsigned int *>(source) + i);
+    } else {
+      const std::size_t index = static_cast<std::size_t>(t) * p.width + c0;
+      row.w[0] = __ldcs(reinterpret_cast<const unsigned int *>(p.x1 + index));
+      row.w[1] = __ldcs(reinterpret_cast<const unsigned int *>(p.value + index));
+      if constexpr (kOutput) row.w[2] = __ldcs(reinterpret_cast<const unsigned int *>(p.x2 + index));
+    }
+    return row;
+  };
+  // projection-fed rows as one F32 value per column
+  const auto columns_of = [](const Row &row, float (&x)[kColumns]) {
+#pragma unroll
+    for (int w = 0; w < 3; ++w) {
+      x[2 * w] = pair_lo(row.w[w]);
+      x[2 * w + 1] = pair_hi(row.w[w]);
+    }
+  };
+  constexpr std::true_type kCheckedRows{};
+  constexpr std::false_type kPlainRows{};
+
+  // featurizer: taps [column][tap] of the thread's columns, raw rows t-2 and t-1
+  [[maybe_unused]] float st[kColumns][3], xh[2][kColumns];
+  if constexpr (kProj) {
+#pragma unroll
+    for (int i = 0; i < kColumns * 3; ++i)
+      st[i / 3][i % 3] = bf2f(p.short_filter[static_cast<std::size_t>(c0) * 9 + i]);
+#pragma unroll
+    for (int k = 0; k < 2; ++k) {
+      // t_end only bounds rows behind the segment; these lie in front of it
+      const int t = t_own - 2 + k;
+      Row row;
+      row.w[0] = row.w[1] = row.w[2] = 0U;
+      if (t >= 0) {
+        const bf16 *const source =
+            p.projection + static_cast<std::size_t>(t) * 3 * p.width + static_cast<std::size_t>(c0) * 3;
+#pragma unroll
+        for (int i = 0; i < 3; ++i) row.w[i] = __ldg(reinterpret_cast<const unsigned int *>(source) + i);
+      }
+      columns_of(row, xh[k]);
+    }
+  }
+
+  Row next[kUnroll];
+  const auto run_group = [&](auto checked, const int base) {
+    constexpr bool kChecked = decltype(checked)::value;
+    Row rows[kUnroll];
+#pragma unroll
+    for (int i = 0; i < kUnroll; ++i) rows[i] = next[i];
+#pragma unroll
+    for (int i = 0; i < kUnroll; ++i) next[i] = load_row(checked, base + kUnroll + i);
+#pragma unroll
+    for (int i = 0; i < kUnroll; ++i) {
+      const int t = base + i;
+      if (kChecked && t >= t_end) break;
+      std::uint32_t u_pair;  // u and the x2 gate of the pair, packed BF16
+      [[maybe_unused]] std::uint32_t gate_pair = 0U;
+      if constexpr (kProj) {
+        float x[kColumns], z[kColumns];
+        columns_of(rows[i], x);
+#pragma unroll
+        for (int column = 0; column < kColumns; ++column) {
+          if (!kOutput && column % 3 == 0) continue;  // the x2 gate is not needed for the state
+          // fmaf with +0, not a multiply: the sign of a zero result must match the FMA chain
+          float acc = fmaf(xh[0][column], st[column][0], 0.0F);
+          acc = fmaf(xh[1][column], st[column][1], acc);
+          z[column] = fmaf(x[column], st[column][2], acc);
+          xh[0][column] = xh[1][column];
+          xh[1][column] = x[column];
+        }
+        if constexpr (kOutput) gate_pair = round_pair_bf16(z[0], z[3]);
+        u_pair = mul_pairs(round_pair_bf16(z[1], z[4]), round_pair_bf16(z[2], z[5]));
+      } else {
+        u_pair = mul_pairs(rows[i].w[0], rows[i].w[1]);
+        gate_pair = rows[i].w[2];
+      }
+      const float u[kC] = {pair_lo(u_pair), pair_hi(u_pair)};
+      if constexpr (!kOutput) {
+#pragma unroll
+        for (int m = 0; m < kModes; ++m)
+#pragma unroll
+          for (int c = 0; c < kC; ++c) state[c][m] = fmaf(pole[c][m], state[c][m], u[c]);
+      } else {
+        float modal[kC];
+#pragma unroll
+        for (int c = 0; c < kC; ++c) {
           float partial[4] = {0.0F, 0.0F, 0.0F, 0.0F};
 #pragma unroll
           for (int m = 0; m < kModes; ++m) {
-            state[m] = fmaf(pole[m], state[m], u);
-            partial[m % 4] = fmaf(residue[m], state[m], partial[m % 4]);
+            state[c][m] = fmaf(pole[c][m], state[c][m], u[c]);
+            partial[m % 4] = fmaf(residue[c][m], state[c][m], partial[m % 4]);
           }
-          const float modal = ((partial[0] + partial[1]) + partial[2]) + partial[3];
-          float result;
-          if (p.continue_from_state)
-            result = g * fmaf(direct, u, modal);
-          else
-            result = rbf(rbf(modal) + rbf(direct * u)) * g;
-          my_out[r * kTileChannels] = static_cast<unsigned short>(__float_as_uint(rbf(result)) >> 16U);
+          modal[c] = ((partial[0] + partial[1]) + partial[2]) + partial[3];
+        }
+        const std::size_t offset = static_cast<std::size_t>(t) * p.width + c0;
+        std::uint32_t result;
+        if (p.continue_from_state) {
+          result = pack_bf16x2(pair_lo(gate_pair) * fmaf(direct[0], u[0], modal[0]),
+                               pair_hi(gate_pair) * fmaf(direct[1], u[1], modal[1]));
+        } else {
+          // bf16(bf16(bf16(modal) + bf16(D u)) x2), each step one rounding of an exact result
+          const std::uint32_t mixed =
+              add_pairs(round_pair_bf16(modal[0], modal[1]), mul_pairs(direct_pair, u_pair));
+          result = mul_pairs(mixed, gate_pair);
+        }
+        *reinterpret_cast<std::uint32_t *>(p.output + offset) = result;
+        if (p.pregate != nullptr) *reinterpret_cast<std::uint32_t *>(p.pregate + offset) = u_pair;
+        if constexpr (kChecked && kProj) {
+          // raw rows length-2 and length-1 are the featurizer's decode history
+          if (p.short_cache != nullptr && t == p.length - 1) {
+#pragma unroll
+            for (int column = 0; column < kColumns; ++column)
+              *reinterpret_cast<float2 *>(p.short_cache + (static_cast<std::size_t>(c0) * 3 + column) * 2) =
+                  make_float2(xh[0][column], xh[1][column]);
+          }
         }
       }
     }
-    __syncthreads();
-    {
-      const int t = t0 + slab * kSlab + item_row;
-      if (item_ok && t < t1)
-        *reinterpret_cast<uint4 *>(p.output + static_cast<std::size_t>(t) * p.width + item_c0) =
-            *reinterpret_cast<const uint4 *>(out_tile + (lane * kSlab + item_row) * kTileChannels + item_chunk * 8);
+  };
+
+#pragma unroll
+  for (int i = 0; i < kUnroll; ++i) next[i] = load_row(kCheckedRows, t_own + i);
+  int base = t_own;
+  for (; base + 2 * kUnroll <= t_end; base += kUnroll) run_group(kPlainRows, base);
+  for (; base < t_end; base += kUnroll) run_group(kCheckedRows, base);
+
+  if constexpr (kOutput) {
+    if (t_end == p.length && p.state != nullptr) {
+#pragma unroll
+      for (int c = 0; c < kC; ++c)
+#pragma unroll
+        for (int m = 0; m < kModes; ++m) p.state[mine + c * kModes + m] = state[c][m];
     }
-    // the next round's scan writes out_tile only after its own barrier; the stage buffer
-    // refilled next round is the one scanned two rounds ago
+  } else {
+    float *const out = p.scratch + seg * per_segment + mine;
+#pragma unroll
+    for (int c = 0; c < kC; ++c)
+#pragma unroll
+      for (int m = 0; m < kModes; ++m) out[c * kModes + m] = state[c][m];
   }
 }
 
-bool tiled_scan_applies(const ModalParams &p, const bool from_projection) {
-  const auto aligned = [](const void *q) { return (reinterpret_cast<std::uintptr_t>(q) & 15U) == 0; };
-  if (p.width % 8 != 0 || p.segment % kSlab != 0 || !aligned(p.output) ||
-      (p.pregate != nullptr && !aligned(p.pregate)))
-    return false;
-  return from_projection ? aligned(p.projection) && aligned(p.short_filter)
-                         : aligned(p.x1) && aligned(p.value) && aligned(p.x2);
+// Segment length of the one-wave grid for `rows` rows: as many segments as the
+// output pass has resident CTAs, none shorter than 64 rows, no more than the
+// scratch holds.
+// Eight rows of loads in flight per thread: with four the kernels waited on
+// memory (12 KB in flight per SM), twelve cost the projection-fed form registers.
+constexpr int kStreamUnroll = 8;
+
+template <int kModes, bool kProj>
+int stream_segments(const int rows, const int width, const std::size_t scratch_floats) {
+  static const int resident = [] {
+    int blocks = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(
+            &blocks, modal_stream_kernel<kModes, kProj, true, kStreamUnroll>, kStreamThreads, 0) != cudaSuccess ||
+        blocks < 1)
+      blocks = 1;
+    return blocks;
+  }();
+  const int across = static_cast<int>(ceil_div_u(width / 2, kStreamThreads));
+  int segments = std::max(1, kSmCount * resident / across);
+  segments = std::min(segments, std::max(1, rows / 64));
+  const std::size_t per_segment = static_cast<std::size_t>(width) * kModes;
+  const std::size_t capacity = scratch_floats / per_segment;  // local states + the carried-in slot
+  if (capacity < 2) return 1;
+  return static_cast<int>(std::min<std::size_t>(segments, capacity - 1));
 }
 
-template <int kModes, bool kFromProjection>
-int launch_tiled(const ModalParams &p, cudaStream_t stream) {
-  constexpr int smem = tiled_smem_bytes<kFromProjection>();
-  static_assert(smem <= 48 * 1024, "the tiled modal scan is sized for the default shared-memory limit");
-  const dim3 grid(ceil_div_u(p.segments, kLanes), ceil_div_u(p.width, kTileChannels));
-  if (grid.y > 65535) return fail(kInvalidArgument, "modal prefill is too wide");
-  modal_tiled_kernel<kModes, kFromProjection, false><<<grid, kScanThreads, smem, stream>>>(p);
-  int status = check_launch("modal segment kernel");
-  if (status != kOk) return status;
-  modal_carry_kernel<<<ceil_div_u(static_cast<std::size_t>(p.width) * kModes, 256), 256, 0, stream>>>(p, kModes);
-  status = check_launch("modal carry kernel");
-  if (status != kOk) return status;
-  if (kFromProjection && p.words != nullptr)
-    modal_words_output_kernel<kModes><<<grid, kScanThreads, 0, stream>>>(p);
-  else
-    modal_tiled_kernel<kModes, kFromProjection, true><<<grid, kScanThreads, smem, stream>>>(p);
+template <int kModes, bool kProj>
+int launch_stream(ModalParams p, cudaStream_t stream) {
+  const int rows = p.length - p.row_begin;
+  const int segments = stream_segments<kModes, kProj>(rows, p.width, p.scratch_floats);
+  p.segment = (rows + segments - 1) / segments;
+  p.segments = (rows + p.segment - 1) / p.segment;
+  const unsigned int across = ceil_div_u(p.width / 2, kStreamThreads);
+  if (p.segments > 1) {
+    modal_stream_kernel<kModes, kProj, false, kStreamUnroll>
+        <<<dim3(across, p.segments - 1), kStreamThreads, 0, stream>>>(p);
+    const int status = check_launch("modal segment-state kernel");
+    if (status != kOk) return status;
+  }
+  modal_stream_kernel<kModes, kProj, true, kStreamUnroll>
+      <<<dim3(across, p.segments), kStreamThreads, 0, stream>>>(p);
   return check_launch("modal output kernel");
-}
-
-int pick_segment(const std::size_t length, const std::size_t width) {
-  // Largest segment that still yields >= ~200k threads; shorter segments cost
-  // more carry scratch, longer ones starve the SMs.
-  const std::size_t pairs = width / 2;
-  for (const int segment : {256, 128, 64, 32, 16}) {
-    const std::size_t segments = (length + segment - 1) / segment;
-    if (segments * pairs >= 200000) return segment;
-  }
-  return 16;
 }
 
 template <int kModes>
-int launch_modal(const ModalParams &p, const bool from_projection,
-                 cudaStream_t stream) {
-  if (tiled_scan_applies(p, from_projection))
-    return from_projection ? launch_tiled<kModes, true>(p, stream) : launch_tiled<kModes, false>(p, stream);
-  const std::size_t threads = static_cast<std::size_t>(p.segments) * p.pairs;
-  const unsigned int grid = ceil_div_u(threads, kThreads);
-  if (from_projection)
-    modal_local_kernel<kModes, true><<<grid, kThreads, 0, stream>>>(p);
-  else
-    modal_local_kernel<kModes, false><<<grid, kThreads, 0, stream>>>(p);
-  int status = check_launch("modal segment kernel");
-  if (status != kOk) return status;
-  modal_carry_kernel<<<ceil_div_u(static_cast<std::size_t>(p.width) * kModes, 256),
-                       256, 0, stream>>>(p, kModes);
-  status = check_launch("modal carry kernel");
-  if (status != kOk) return status;
-  if (from_projection)
-    modal_output_kernel<kModes, true><<<grid, kThreads, 0, stream>>>(p);
-  else
-    modal_output_kernel<kModes, false><<<grid, kThreads, 0, stream>>>(p);
-  return check_launch("modal output kernel");
+int launch_modal(const ModalParams &p, const bool from_projection, cudaStream_t stream) {
+  return from_projection ? launch_stream<kModes, true>(p, stream) : launch_stream<kModes, false>(p, stream);
 }
 
 }  // namespace
@@ -762,10 +386,13 @@ int launch_modal(const ModalParams &p, const bool from_projection,
 std::size_t modal_scratch_floats(const std::size_t length,
                                  const std::size_t width,
                                  const std::size_t modes) {
-  if (length == 0) return 0;
-  const std::size_t segment = pick_segment(length, width);
-  // segment states, then one packed (u, x2) word per element for the projection-fed form
-  return ((length + segment - 1) / segment) * width * modes + length * width;
+  if (length == 0 || width == 0) return 0;
+  // One end state per segment of the one-wave grid (at most four resident CTAs
+  // per SM, segments of at least 64 rows) and the carried-in slot.
+  const std::size_t across = (width / 2 + kStreamThreads - 1) / kStreamThreads;
+  const std::size_t segments =
+      std::max<std::size_t>(1, std::min<std::size_t>(length / 64, static_cast<std::size_t>(kSmCount) * 4 / across));
+  return (segments + 2) * width * modes;
 }
 
 int modal_prefill(const ModalArgs &a, cudaStream_t stream) {
@@ -799,18 +426,11 @@ int modal_prefill(const ModalArgs &a, cudaStream_t stream) {
   p.length = static_cast<int>(a.length);
   p.width = static_cast<int>(a.width);
   p.row_begin = static_cast<int>(a.row_begin);
-  p.segment = pick_segment(a.length - a.row_begin, a.width);
-  p.segments = static_cast<int>((a.length - a.row_begin + p.segment - 1) / p.segment);
   p.pairs = static_cast<int>(a.width / 2);
   p.continue_from_state = a.continue_from_state;
-  // the words follow the segment states in the caller's scratch (sized by modal_scratch_floats
-  // for the whole length; the segment states of this call take at most that function's first term)
-  if (from_projection && a.width % 4 == 0) {
-    const std::size_t full_segment = static_cast<std::size_t>(pick_segment(a.length, a.width));
-    const std::size_t state_floats = ((a.length + full_segment - 1) / full_segment) * a.width * a.modes;
-    if (static_cast<std::size_t>(p.segments) * a.width * a.modes <= state_floats)
-      p.words = reinterpret_cast<std::uint32_t *>(a.scratch + state_floats);
-  }
+  // sized by the rows of this call: a caller's buffer holds at least this much for any window of its length
+  p.scratch_floats = modal_scratch_floats(a.length - a.row_begin, a.width, a.modes);
+  p.short_cache = from_projection ? a.short_cache : nullptr;  // short_taps == 3 was checked above
   int status;
   switch (a.modes) {
     case 16: status = launch_modal<16>(p, from_projection, stream); break;
@@ -821,10 +441,6 @@ int modal_prefill(const ModalArgs &a, cudaStream_t stream) {
     default:
       return fail(kUnsupported, "modal state size must be 1, 2, 4, 8 or 16");
   }
-  if (status != kOk) return status;
-  if (a.short_cache != nullptr && from_projection && a.short_taps > 1)
-    status = fill_fir_cache(a.projection, a.short_cache, a.length, a.width * 3,
-                            a.short_taps - 1, stream);
   return status;
 }
 
@@ -867,15 +483,8 @@ int modal_prefill_static_scratch(const ModalArgs &a, cudaStream_t stream) {
   if (a.length > 0x7fffff00U || a.width > 0x3fffffffU)
     return fail(kInvalidArgument, "modal prefill dimensions are too large");
   if (a.length == 0) return kOk;
-  // Start from the segment length the allocating path would use and lengthen it
-  // until the segment states fit the fixed array.
-  std::size_t segment = static_cast<std::size_t>(pick_segment(a.length, a.width));
   const std::size_t per_segment = a.width * a.modes;
-  while (((a.length + segment - 1) / segment) * per_segment > kStaticScratchFloats &&
-         segment < a.length)
-    segment *= 2;
-  const std::size_t segments = (a.length + segment - 1) / segment;
-  if (segments * per_segment > kStaticScratchFloats)
+  if (per_segment > kStaticScratchFloats)
     return fail(kInvalidArgument,
                 "allocation-free modal prefill: width*modes = " + std::to_string(per_segment) +
                     " floats per segment exceeds the fixed scratch of " +
@@ -896,10 +505,9 @@ int modal_prefill_static_scratch(const ModalArgs &a, cudaStream_t stream) {
   p.scratch = scratch;
   p.length = static_cast<int>(a.length);
   p.width = static_cast<int>(a.width);
-  p.segment = static_cast<int>(segment);
-  p.segments = static_cast<int>(segments);
   p.pairs = static_cast<int>(a.width / 2);
   p.continue_from_state = a.continue_from_state;
+  p.scratch_floats = kStaticScratchFloats;  // fewer, longer segments when the array holds fewer states
   switch (a.modes) {
     case 16: return launch_modal<16>(p, false, stream);
     case 8: return launch_modal<8>(p, false, stream);

@@ -10,7 +10,7 @@
 Inputs are seeded synthetic tensors with the shapes and value distributions of
 the reference workloads (BF16 N(0,1) activations, N(0,0.02) weights, modal poles
 with radius U[0.9,0.999)).  Every timed launch is preceded by an L2 flush (a
-256 MiB write) and timed with CUDA events on the launching stream; the median
+256 MiB write, then a 256 MiB read so that no dirty lines are left) and timed with CUDA events on the launching stream; the median
 of --iters launches is reported as one JSON line per operator with the
 algorithmic bytes or FLOPs and the fraction of the measured peak
 (MEASURED_PEAKS.json at the repository root when present).
@@ -53,6 +53,7 @@ class Timer:
     def __init__(self, iters: int, warmup: int = 3):
         self.iters, self.warmup = iters, warmup
         self.flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+        self.clean = torch.zeros(64 << 20, dtype=torch.int32, device="cuda")
 
     def __call__(self, launch) -> float:
         """Median milliseconds of `launch()` (which enqueues on the current stream)."""
@@ -61,7 +62,12 @@ class Timer:
         torch.cuda.synchronize()
         times = []
         for _ in range(self.iters):
+            # Cold L2 without pending write-backs: the write pass evicts everything,
+            # the read pass then replaces its dirty lines with clean ones (a timed
+            # kernel that evicts 126 MB of dirty lines pays ~15 us of DRAM writes
+            # that are not its own).
             self.flush.zero_()
+            self.clean.sum()
             start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             start.record()
             launch()
