@@ -6,6 +6,7 @@
 #include "../../../include/evo/evo.h"
 #include "../../../include/evo/evo_b200.h"
 
+#include <algorithm>
 #include <cstring>
 #include <exception>
 #include <functional>
@@ -18,6 +19,7 @@
 #include "../ops_internal.hpp"
 #include "model.hpp"
 #include "sampler.hpp"
+#include "variant.hpp"
 
 struct evo_model {
   std::shared_ptr<evob::ModelFile> file;
@@ -487,6 +489,46 @@ evo_status evo_b200_context_continue_device(evo_context *context, const uint32_t
       return status;
     }
     if (device_logits_out != nullptr) *device_logits_out = context->context->device_logits();
+    return kOk;
+  });
+}
+
+evo_status evo_b200_variant_window_make(const char *sequence, size_t sequence_length, size_t position_1based,
+                                        const char *reference, size_t reference_length, const char *alternate,
+                                        size_t alternate_length, size_t maximum_tokens,
+                                        evo_b200_variant_window *window, char *reference_window,
+                                        char *alternate_window, size_t window_capacity) {
+  return protect([&]() -> int {
+    if (sequence == nullptr || reference == nullptr || alternate == nullptr || window == nullptr ||
+        window->struct_size < sizeof(evo_b200_variant_window))
+      return fail(evob::kInvalidArgument, "variant window arguments are invalid");
+    evob::VariantWindow made;
+    const int status = evob::make_variant_window({sequence, sequence_length}, position_1based,
+                                                 {reference, reference_length}, {alternate, alternate_length},
+                                                 maximum_tokens, &made);
+    if (status != kOk) return status;
+    if ((reference_window != nullptr || alternate_window != nullptr) &&
+        window_capacity < std::max(made.reference.size(), made.alternate.size()))
+      return fail(evob::kInvalidArgument, "variant window buffers are too small");
+    window->reference_start = made.reference_start;
+    window->reference_end = made.reference_end;
+    window->variant_offset = made.variant_offset;
+    window->reference_length = made.reference.size();
+    window->alternate_length = made.alternate.size();
+    if (reference_window != nullptr) std::memcpy(reference_window, made.reference.data(), made.reference.size());
+    if (alternate_window != nullptr) std::memcpy(alternate_window, made.alternate.data(), made.alternate.size());
+    return kOk;
+  });
+}
+
+evo_status evo_b200_reverse_complement(const char *sequence, size_t length, char *output) {
+  return protect([&]() -> int {
+    if (sequence == nullptr || output == nullptr)
+      return fail(evob::kInvalidArgument, "reverse-complement arguments are invalid");
+    std::string reversed;
+    const int status = evob::reverse_complement({sequence, length}, &reversed);
+    if (status != kOk) return status;
+    std::memcpy(output, reversed.data(), reversed.size());
     return kOk;
   });
 }

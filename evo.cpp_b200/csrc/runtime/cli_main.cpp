@@ -36,6 +36,9 @@ struct Options {
   float temperature = 1.0F, top_p = 1.0F;
   uint64_t seed = 0;
   bool allow_fixture = false;
+  // variant-score (inline form)
+  std::string sequence, reference_allele, alternate_allele, strand = "both", normalization = "sum";
+  size_t position = 0, window = 0;
 };
 
 struct Record {
@@ -214,6 +217,13 @@ Options parse(int argc, char **argv) {
     else if (a == "--layer") o.layer = std::stoull(value(i));
     else if (a == "--pooling") o.pooling = value(i);
     else if (a == "--allow-test-fixture") o.allow_fixture = true;
+    else if (a == "--sequence") o.sequence = value(i);
+    else if (a == "--position") o.position = std::stoull(value(i));
+    else if (a == "--ref") o.reference_allele = value(i);
+    else if (a == "--alt") o.alternate_allele = value(i);
+    else if (a == "--window") o.window = std::stoull(value(i));
+    else if (a == "--strand") o.strand = value(i);
+    else if (a == "--normalization") o.normalization = value(i);
     else if (a == "--gpu") {
       o.gpus.clear();
       std::stringstream list(value(i));
@@ -224,7 +234,9 @@ Options parse(int argc, char **argv) {
                    "  evo score -m MODEL --input FASTA_FASTQ_OR_TEXT\n"
                    "  evo bench -m MODEL --input FASTA_FASTQ_OR_TEXT [--warmup N --repetitions N]\n"
                    "  evo embed -m MODEL --input FASTA_FASTQ_OR_TEXT --output DIR --layer N "
-                   "--pooling none|mean|last\n";
+                   "--pooling none|mean|last\n"
+                   "  evo variant-score -m MODEL --sequence DNA --position POS --ref REF --alt ALT "
+                   "[--window N --strand forward|reverse|both --normalization sum|mean]\n";
       std::exit(0);
     } else die(EVO_STATUS_INVALID_ARGUMENT, "unknown option " + a);
   }
@@ -280,6 +292,37 @@ void print_metrics(const Metrics &m, const Options &o, const evo_context *contex
               << ",\"cache_bytes\":" << info.cache_bytes << ",\"arena_bytes\":" << info.arena_bytes << '}';
   }
   std::cerr << "]}\n";
+}
+
+
+// Sum (or mean) of next-token log-likelihoods of one window, as `evo score`
+// computes them (upstream src/cuda/inference_cli.cpp:762-799 scores both windows
+// of a strand with its sequence scorer).
+struct WindowScore {
+  double log_likelihood = 0.0;
+  size_t scored_tokens = 0;
+};
+
+WindowScore score_window(const evo_model *model, const Options &o, const std::string &bytes, const size_t vocab,
+                         Metrics *metrics, evo_context **last_context) {
+  if (*last_context != nullptr) evo_context_free(*last_context);
+  *last_context = new_context(model, o);
+  const auto start = std::chrono::steady_clock::now();
+  const Collected out = prefill(*last_context, bytes);
+  metrics->prefill_seconds += seconds_since(start);
+  metrics->prefill_tokens += bytes.size();
+  WindowScore score;
+  for (size_t t = 0; t + 1 < bytes.size(); ++t)
+    score.log_likelihood += log_probability(out.logits.data() + t * vocab, vocab,
+                                            static_cast<unsigned char>(bytes[t + 1]));
+  score.scored_tokens = bytes.size() - 1;
+  return score;
+}
+
+std::string reverse_complement_of(const std::string &sequence) {
+  std::string out(sequence.size(), '\0');
+  check(evo_b200_reverse_complement(sequence.data(), sequence.size(), out.data()), "reverse complement");
+  return out;
 }
 
 }  // namespace
@@ -386,6 +429,75 @@ int main(int argc, char **argv) {
       if (!manifest) die(EVO_STATUS_IO, "cannot write the embedding manifest");
       ++record_index;
     }
+  } else if (o.command == "variant-score") {
+    // Inline form of upstream's variant-effect driver (src/cuda/inference_cli.cpp:801-937):
+    // delta = LL(alternate window) - LL(reference window) per strand, averaged over strands.
+    if (o.sequence.empty() || o.position == 0 || o.reference_allele.empty() || o.alternate_allele.empty())
+      die(EVO_STATUS_INVALID_ARGUMENT, "variant-score needs --sequence, --position (1-based), --ref and --alt");
+    if (o.strand != "forward" && o.strand != "reverse" && o.strand != "both")
+      die(EVO_STATUS_INVALID_ARGUMENT, "--strand must be one of forward, reverse, or both");
+    if (o.normalization != "sum" && o.normalization != "mean")
+      die(EVO_STATUS_INVALID_ARGUMENT, "--normalization must be one of sum or mean");
+    const size_t window_tokens = o.window == 0 ? o.context : o.window;
+    if (window_tokens > o.context) die(EVO_STATUS_INVALID_ARGUMENT, "--window must not exceed --ctx");
+    evo_b200_variant_window window{};
+    window.struct_size = sizeof(window);
+    std::string reference(window_tokens, '\0'), alternate(window_tokens, '\0');
+    check(evo_b200_variant_window_make(o.sequence.data(), o.sequence.size(), o.position,
+                                       o.reference_allele.data(), o.reference_allele.size(),
+                                       o.alternate_allele.data(), o.alternate_allele.size(), window_tokens,
+                                       &window, reference.data(), alternate.data(), window_tokens),
+          "variant window");
+    reference.resize(window.reference_length);
+    alternate.resize(window.alternate_length);
+    struct Strand {
+      const char *name;
+      WindowScore reference, alternate;
+      double delta;
+    };
+    std::vector<Strand> strands;
+    const auto score_strand = [&](const char *name, const std::string &ref, const std::string &alt) {
+      Strand strand{name, score_window(model, o, ref, vocab, &metrics, &last_context),
+                    score_window(model, o, alt, vocab, &metrics, &last_context), 0.0};
+      if (o.normalization == "mean") {
+        strand.reference.log_likelihood /= static_cast<double>(strand.reference.scored_tokens);
+        strand.alternate.log_likelihood /= static_cast<double>(strand.alternate.scored_tokens);
+      }
+      strand.delta = strand.alternate.log_likelihood - strand.reference.log_likelihood;
+      strands.push_back(strand);
+    };
+    if (o.strand != "reverse") score_strand("+", reference, alternate);
+    if (o.strand != "forward") score_strand("-", reverse_complement_of(reference), reverse_complement_of(alternate));
+    double aggregate = 0.0;
+    for (const Strand &strand : strands) aggregate += strand.delta;
+    aggregate /= static_cast<double>(strands.size());
+    std::cout << "{\"source\":\"inline\",\"position\":" << o.position
+              << ",\"position_coordinate_system\":\"1-based\",\"reference\":";
+    json_string(std::cout, o.reference_allele);
+    std::cout << ",\"alternate\":";
+    json_string(std::cout, o.alternate_allele);
+    std::cout << ",\"window\":{\"start\":" << window.reference_start << ",\"end\":" << window.reference_end
+              << ",\"coordinate_system\":\"0-based-half-open\",\"reference_sequence\":";
+    json_string(std::cout, reference);
+    std::cout << ",\"alternate_sequence\":";
+    json_string(std::cout, alternate);
+    std::cout << ",\"reference_tokens\":" << reference.size() << ",\"alternate_tokens\":" << alternate.size()
+              << "},\"normalization\":\"" << (o.normalization == "sum" ? "sum_log_likelihood" : "mean_log_likelihood")
+              << "\",\"backend\":\"cuda\",\"profile\":\"" << o.profile << "\",\"test_fixture\":"
+              << (o.allow_fixture ? "true" : "false") << ",\"model_id\":";
+    const std::string id = evo_model_id(model);
+    if (id.empty()) std::cout << "null"; else json_string(std::cout, id);
+    std::cout << ",\"strands\":[" << std::setprecision(17);
+    for (size_t i = 0; i < strands.size(); ++i) {
+      const Strand &strand = strands[i];
+      std::cout << (i ? "," : "") << "{\"strand\":\"" << strand.name << "\",\"reference_log_likelihood\":"
+                << strand.reference.log_likelihood << ",\"alternate_log_likelihood\":"
+                << strand.alternate.log_likelihood << ",\"reference_scored_tokens\":"
+                << strand.reference.scored_tokens << ",\"alternate_scored_tokens\":"
+                << strand.alternate.scored_tokens << ",\"delta\":" << strand.delta << '}';
+    }
+    std::cout << "],\"aggregation\":\"" << (strands.size() == 1 ? "single_strand" : "mean_across_strands")
+              << "\",\"score\":" << aggregate << "}\n";
   } else if (o.command == "bench") {
     if (o.input.empty()) die(EVO_STATUS_INVALID_ARGUMENT, "bench needs --input");
     if (o.repetitions == 0) die(EVO_STATUS_INVALID_ARGUMENT, "--repetitions must be positive");
@@ -468,7 +580,7 @@ int main(int argc, char **argv) {
     std::cout.flush();
     evo_sampler_free(sampler);
   } else {
-    die(EVO_STATUS_UNSUPPORTED, "unknown command " + o.command + " (run, score, bench)");
+    die(EVO_STATUS_UNSUPPORTED, "unknown command " + o.command + " (run, score, bench, embed, variant-score)");
   }
   print_metrics(metrics, o, last_context);
   if (last_context != nullptr) evo_context_free(last_context);

@@ -67,6 +67,35 @@ EVO_API evo_status evo_b200_context_stage_info(const evo_context *context, size_
                                                evo_b200_stage_info *info);
 
 
+/* ---- variant-effect windows (host-only; need no GPU).
+ * The sequence logic of upstream's `evo variant-score` driver
+ * (src/variant.cpp:69-174, called from src/cuda/inference_cli.cpp:801-815):
+ * the allele at 1-based `position` of `sequence` must equal `reference`; the
+ * window keeps the allele and as much flank as `maximum_tokens` allows, half
+ * on each side, a side that runs out of sequence ceding its share to the other.
+ * `reference_window` / `alternate_window` receive the window with either allele
+ * in place (capacity `window_capacity` bytes each, no terminator); all
+ * sequences are IUPAC DNA, case kept.  EVO_STATUS_INVALID_ARGUMENT with
+ * evo_last_error() set on a mismatch, a non-IUPAC byte, or a window that cannot
+ * hold both alleles and two tokens. */
+typedef struct evo_b200_variant_window {
+  size_t struct_size;
+  size_t reference_start; /* 0-based half-open span of the window on `sequence` */
+  size_t reference_end;
+  size_t variant_offset;  /* offset of the allele inside either window */
+  size_t reference_length;
+  size_t alternate_length;
+} evo_b200_variant_window;
+EVO_API evo_status evo_b200_variant_window_make(const char *sequence, size_t sequence_length,
+                                                size_t position_1based, const char *reference,
+                                                size_t reference_length, const char *alternate,
+                                                size_t alternate_length, size_t maximum_tokens,
+                                                evo_b200_variant_window *window, char *reference_window,
+                                                char *alternate_window, size_t window_capacity);
+/* Reverse complement of IUPAC DNA (upstream src/variant.cpp:86-101); `output` holds `length` bytes. */
+EVO_API evo_status evo_b200_reverse_complement(const char *sequence, size_t length, char *output);
+
+
 /* ---- one pipeline stage per process (torchrun / MPI style launchers).
  * Upstream runs its layer pipeline inside one process
  * (src/cuda/model.cu:2419-2469 plans the stages, :3148-3212 hands the hidden

@@ -128,3 +128,44 @@ def test_embed_writes_npy_matrices_and_manifest(tmp_path):
     np.testing.assert_allclose(pooled[0], first.mean(axis=0), rtol=1e-6, atol=1e-7)
     # a non-empty output directory is refused (status 2), as upstream does
     assert run("embed", "--input", str(fasta), "--output", str(out), "--layer", "30", check=False).returncode == 2
+
+
+def test_variant_score_is_the_difference_of_two_window_scores(tmp_path):
+    """`evo variant-score` (inline form): the windows of upstream's
+    tests/test_frontend.cpp:415-420, strand scores equal to `evo score` of the same
+    windows, reverse strand = reverse complements, aggregate = mean of the deltas."""
+    result = run("variant-score", "--sequence", "AACCGGTT", "--position", "3", "--ref", "C", "--alt", "T",
+                 "--window", "6", "--ctx", "64")
+    record = json.loads(result.stdout.decode())
+    window = record["window"]
+    assert (window["start"], window["end"], window["reference_sequence"], window["alternate_sequence"]) == (
+        0, 6, "AACCGG", "AATCGG")
+    assert record["source"] == "inline" and record["normalization"] == "sum_log_likelihood"
+    assert record["aggregation"] == "mean_across_strands" and [s["strand"] for s in record["strands"]] == ["+", "-"]
+
+    def scored(sequence: str) -> float:
+        raw = tmp_path / f"{sequence}.txt"
+        raw.write_bytes(sequence.encode())
+        return json.loads(run("score", "--input", str(raw), "--ctx", "64").stdout.decode())["log_likelihood"]
+
+    forward, reverse = record["strands"]
+    assert abs(forward["reference_log_likelihood"] - scored("AACCGG")) < 1e-9
+    assert abs(forward["alternate_log_likelihood"] - scored("AATCGG")) < 1e-9
+    assert abs(reverse["reference_log_likelihood"] - scored("CCGGTT")) < 1e-9
+    assert abs(reverse["alternate_log_likelihood"] - scored("CCGATT")) < 1e-9
+    for strand in record["strands"]:
+        assert strand["reference_scored_tokens"] == strand["alternate_scored_tokens"] == 5
+        assert abs(strand["delta"] - (strand["alternate_log_likelihood"] - strand["reference_log_likelihood"])) < 1e-12
+    assert abs(record["score"] - (forward["delta"] + reverse["delta"]) / 2) < 1e-12
+
+    single = json.loads(run("variant-score", "--sequence", "AACCGG", "--position", "3", "--ref", "C", "--alt",
+                            "CTT", "--window", "5", "--strand", "forward", "--normalization", "mean",
+                            "--ctx", "64").stdout.decode())
+    assert single["aggregation"] == "single_strand" and single["normalization"] == "mean_log_likelihood"
+    assert (single["window"]["reference_sequence"], single["window"]["alternate_sequence"]) == ("ACC", "ACTTC")
+    assert single["strands"][0]["reference_scored_tokens"] == 2
+    assert single["strands"][0]["alternate_scored_tokens"] == 4
+
+    refused = run("variant-score", "--sequence", "AACCGG", "--position", "3", "--ref", "G", "--alt", "T",
+                  "--ctx", "64", check=False)
+    assert refused.returncode == 2 and b"does not match" in refused.stderr

@@ -192,3 +192,82 @@ def test_two_rank_aggregation_over_gloo():
     assert all(p.returncode == 0 for p in procs), outputs
     for out, _ in outputs:
         assert abs(float(out.strip().splitlines()[-1]) - 2 * 8192 / 0.014) < 1e-6
+
+
+def _variant_window(evo, sequence, position, ref, alt, maximum):
+    class Window(ctypes.Structure):
+        _fields_ = [(name, ctypes.c_size_t) for name in (
+            "struct_size", "reference_start", "reference_end", "variant_offset", "reference_length",
+            "alternate_length")]
+    fn = evo.lib.evo_b200_variant_window_make
+    fn.argtypes = [ctypes.c_char_p, ctypes.c_size_t, ctypes.c_size_t, ctypes.c_char_p, ctypes.c_size_t,
+                   ctypes.c_char_p, ctypes.c_size_t, ctypes.c_size_t, ctypes.c_void_p, ctypes.c_char_p,
+                   ctypes.c_char_p, ctypes.c_size_t]
+    window = Window(struct_size=ctypes.sizeof(Window))
+    capacity = max(maximum, 1)
+    reference, alternate = ctypes.create_string_buffer(capacity), ctypes.create_string_buffer(capacity)
+    status = fn(sequence, len(sequence), position, ref, len(ref), alt, len(alt), maximum,
+                ctypes.byref(window), reference, alternate, capacity)
+    if status != 0:
+        evo.lib.evo_last_error.restype = ctypes.c_char_p
+        return status, evo.lib.evo_last_error().decode()
+    return 0, (reference.raw[:window.reference_length], alternate.raw[:window.alternate_length],
+               window.reference_start, window.reference_end, window.variant_offset)
+
+
+def _reverse_complement(evo, sequence):
+    fn = evo.lib.evo_b200_reverse_complement
+    fn.argtypes = [ctypes.c_char_p, ctypes.c_size_t, ctypes.c_char_p]
+    out = ctypes.create_string_buffer(max(len(sequence), 1))
+    status = fn(sequence, len(sequence), out)
+    if status != 0:
+        evo.lib.evo_last_error.restype = ctypes.c_char_p
+        return status, evo.lib.evo_last_error().decode()
+    return 0, out.raw[:len(sequence)]
+
+
+def test_variant_windows_match_upstream_known_answers(evo):
+    """The known answers of upstream's tests/test_frontend.cpp:400-433."""
+    assert _reverse_complement(evo, b"ACGTN") == (0, b"NACGT")
+    assert _reverse_complement(evo, b"RYSWKMBDHVN") == (0, b"NBDHVKMWSRY")
+    assert _reverse_complement(evo, b"acgt") == (0, b"acgt")
+    status, message = _reverse_complement(evo, b"ACGU")
+    assert status == 2 and "offset 3" in message
+    assert _variant_window(evo, b"AACCGGTT", 3, b"C", b"T", 6) == (0, (b"AACCGG", b"AATCGG", 0, 6, 2))
+    assert _variant_window(evo, b"AACCGG", 3, b"C", b"CTT", 5) == (0, (b"ACC", b"ACTTC", 1, 4, 1))
+    status, message = _variant_window(evo, b"AACCGG", 3, b"G", b"T", 5)
+    assert status == 2 and "does not match" in message
+    status, message = _variant_window(evo, b"A", 1, b"A", b"T", 2)
+    assert status == 2 and "two tokens" in message
+
+
+def test_variant_window_properties(evo):
+    """Seeded random loci: the window contains the allele at the stated offset, never exceeds
+    the budget, uses the whole budget when the sequence allows it, and the flanks of the two
+    windows are the same bytes of the input."""
+    rng = np.random.default_rng(11)
+    for _ in range(300):
+        length = int(rng.integers(2, 60))
+        sequence = bytes(rng.choice(np.frombuffer(b"ACGTNacgt", np.uint8), length).tolist())
+        start = int(rng.integers(0, length))
+        ref = sequence[start:start + int(rng.integers(1, min(4, length - start) + 1))]
+        alt = bytes(rng.choice(np.frombuffer(b"ACGT", np.uint8), int(rng.integers(1, 5))).tolist())
+        maximum = int(rng.integers(1, 40))
+        status, result = _variant_window(evo, sequence, start + 1, ref, alt, maximum)
+        core = max(len(ref), len(alt))
+        if maximum < core or maximum < 2:
+            assert status == 2
+            continue
+        if status != 0:  # only a window of fewer than two tokens may still be refused
+            assert "two tokens" in result
+            continue
+        reference, alternate, begin, end, offset = result
+        assert reference == sequence[begin:end] and begin + offset == start
+        assert alternate == sequence[begin:start] + alt + sequence[start + len(ref):end]
+        assert max(len(reference), len(alternate)) <= maximum
+        flank = (end - begin) - len(ref)
+        assert flank == min(maximum - core, length - len(ref))
+        # a side gives up budget only when it runs out of sequence
+        left, right = offset, end - (start + len(ref))
+        if left < (maximum - core) // 2:
+            assert begin == 0 or right == length - (start + len(ref))
