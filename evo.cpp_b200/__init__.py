@@ -50,6 +50,7 @@ OPS_SIGNATURES: dict[str, list] = {
     "evo_b200_bf16_hcl_prefill_noalloc": [_P, _P, _P, _P, _P, _P, _Z, _Z, _Z, _I, _P, _P, _P, _P],
     "evo_b200_bf16_projection_hcl_prefill": [_P, _P, _P, _P, _P, _Z, _Z, _Z, _I, _P, _P, _P, _P, _P, _P],
     "evo_b200_bf16_hcl_decode": [_P, _P, _P, _P, _P, _P, _Z, _Z, _P, _P, _P, _P],
+    "evo_b200_bf16_hyena_decode_mixer": [_P, _P, _P, _P, _P, _I, _Z, _Z, _I, _P, _P, _P, _Z, _P, _Z, _P, _P],
     "evo_b200_bf16_split_rope_append": [_P, _P, _Z, _Z, _Z, _Z, _F, _I, _P, _P, _P, _Z, _P],
     "evo_b200_bf16_causal_attention": [_P, _P, _P, _Z, _Z, _Z, _Z, _P, _P],
     "evo_b200_bf16_causal_attention_mma_sync": [_P, _P, _P, _Z, _Z, _Z, _Z, _P, _P],

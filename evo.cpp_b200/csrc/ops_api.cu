@@ -240,6 +240,31 @@ int evo_b200_bf16_fir_continue_direct(const void *input, const void *filter,
                   cache_length, output, as_stream(stream));
 }
 
+int evo_b200_bf16_hyena_decode_mixer(const void *projection, const void *short_filter, float *short_cache,
+                                     const void *direct, const void *filter, int filter_is_f32,
+                                     size_t groups, size_t taps, int orientation, float *inner_cache,
+                                     const float *log_poles, const float *residues, size_t modes,
+                                     float *modal_state, size_t width, void *output, void *stream) {
+  DecodeMixerArgs a;
+  a.projection = projection;
+  a.short_filter = short_filter;
+  a.short_cache = short_cache;
+  a.direct = direct;
+  a.filter = filter;
+  a.filter_is_f32 = filter_is_f32 != 0;
+  a.groups = groups;
+  a.taps = taps;
+  a.cross_correlation = orientation == 0;
+  a.inner_cache = inner_cache;
+  a.log_poles = log_poles;
+  a.residues = residues;
+  a.modes = modes;
+  a.modal_state = modal_state;
+  a.width = width;
+  a.output = output;
+  return hyena_decode_mixer(a, as_stream(stream));
+}
+
 int evo_b200_bf16_gated_fir_prefill(const void *x2, const void *x1,
                                     const void *value, const void *filter,
                                     int filter_is_f32, const void *direct,

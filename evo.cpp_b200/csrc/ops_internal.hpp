@@ -157,6 +157,27 @@ int modal_prefill(const ModalArgs &args, cudaStream_t stream);
 // library image instead of args.scratch (which is ignored); separate x2/x1/v
 // inputs only.  Makes no device allocation.
 int modal_prefill_static_scratch(const ModalArgs &args, cudaStream_t stream);
+// One cached-decode step of a whole Hyena mixer (featurizer step, split, gate,
+// inner FIR or modal step with their cache updates, post-gate) in one launch;
+// bit-identical to the unfused sequence.  All histories must be full.  Set
+// log_poles for the modal (HCL) form, filter for the FIR (HCS / HCM) forms.
+struct DecodeMixerArgs {
+  const void *projection = nullptr;    // [3 width] BF16, (x2, x1, v) per channel
+  const void *short_filter = nullptr;  // [3 width, 3] BF16
+  float *short_cache = nullptr;        // [3 width, 2] F32, advanced
+  const void *direct = nullptr;        // [width] BF16 (HCM, HCL)
+  const void *filter = nullptr;        // [groups, taps]
+  bool filter_is_f32 = false;
+  std::size_t groups = 0, taps = 0;
+  bool cross_correlation = false;
+  float *inner_cache = nullptr;        // [width, taps-1] F32, advanced
+  const float *log_poles = nullptr, *residues = nullptr;  // [width, modes]
+  std::size_t modes = 0;
+  float *modal_state = nullptr;        // [width, modes] F32, advanced
+  void *output = nullptr;              // [width] BF16
+  std::size_t width = 0;
+};
+int hyena_decode_mixer(const DecodeMixerArgs &args, cudaStream_t stream);
 int modal_decode(const void *x2, const void *x1, const void *value,
                  const void *direct, const float *log_poles,
                  const float *residues, std::size_t width, std::size_t modes,

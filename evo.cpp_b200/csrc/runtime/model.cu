@@ -526,6 +526,33 @@ int Context::run_stage(Stage &s, const std::size_t rows, const Mode mode,
                             cudaMemcpyDeviceToDevice, stream) != cudaSuccess)
           return fail(kCuda, "projection history save failed");
       }
+    } else if (mode == Mode::kDecode && rows == 1 && c.short_taps == 3 &&
+               position_ >= std::max({c.short_taps, c.hcs_taps, c.hcm_taps}) &&
+               (w.type == MixerType::kHcl ? c.state_size <= 32 : (w.type == MixerType::kHcs ? c.hcs_taps : c.hcm_taps) <= 128)) {
+      // one token against full histories: the whole mixer in one launch
+      DecodeMixerArgs a;
+      a.projection = s.projection;
+      a.short_filter = w.short_filter;
+      a.short_cache = state.short_cache;
+      a.output = s.mixer_out;
+      a.width = D;
+      if (w.type == MixerType::kHcl) {
+        a.direct = w.direct;
+        a.log_poles = w.log_poles;
+        a.residues = w.residues;
+        a.modes = c.state_size;
+        a.modal_state = state.modal_state;
+      } else {
+        const bool hcs = w.type == MixerType::kHcs;
+        a.direct = hcs ? nullptr : w.direct;
+        a.filter = w.inner_filter;
+        a.filter_is_f32 = !hcs && c.hcm_filter_f32;
+        a.groups = hcs ? c.hcs_groups : c.hcm_groups;
+        a.taps = hcs ? c.hcs_taps : c.hcm_taps;
+        a.cross_correlation = hcs;
+        a.inner_cache = state.inner_cache;
+      }
+      EVOB_OP(kCatStateStep, hyena_decode_mixer(a, stream));
     } else {
       // continuation / decode against the causal state
       const std::size_t short_cached = std::min(position_, c.short_taps - 1);

@@ -219,6 +219,20 @@ EVO_B200_API int evo_b200_bf16_projection_hcl_prefill(
     const float *log_poles, const float *residues, size_t length, size_t width,
     size_t modes, int mode, float *state, float *scratch, float *short_cache,
     void *pregate, void *output, void *stream);
+/* One cached-decode step of a whole Hyena mixer in one launch (no upstream
+ * counterpart: upstream runs the featurizer step, split, gate, bf16_fir_decode
+ * or bf16_hcl_decode and the post-gate as separate launches,
+ * src/cuda/model.cu:1471-1560).  Bit-identical to that sequence.  projection is
+ * the token's [3 width] input projection; short_cache [3 width, 2], inner_cache
+ * [width, taps-1] and modal_state [width, modes] are advanced in place and must
+ * hold full histories.  FIR form: filter set, log_poles NULL (direct optional);
+ * modal form: log_poles, residues, direct and modal_state set. */
+EVO_B200_API int evo_b200_bf16_hyena_decode_mixer(
+    const void *projection, const void *short_filter, float *short_cache,
+    const void *direct, const void *filter, int filter_is_f32, size_t groups,
+    size_t taps, int orientation, float *inner_cache, const float *log_poles,
+    const float *residues, size_t modes, float *modal_state, size_t width,
+    void *output, void *stream);
 /* src/cuda/hyena.cu:718-761,2126-2167 (bf16_hcl_decode). */
 EVO_B200_API int evo_b200_bf16_hcl_decode(
     const void *x2, const void *x1, const void *value, const void *direct,

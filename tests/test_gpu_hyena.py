@@ -253,3 +253,56 @@ def test_hcl_decode_reduction_tree_known_answer(ops):
     assert bf16_to_f32(host_bits(out))[0] == np.float32(-0.240234375)
     assert bf16_to_f32(host_bits(gated))[0] == 0.0
     assert np.array_equal(state.cpu().numpy(), np.ones(16, np.float32))
+
+
+@pytest.mark.parametrize("kind", ["hcs", "hcm", "hcm_f32", "hcl"])
+def test_fused_decode_mixer_matches_the_unfused_launches_bit_for_bit(ops, kind):
+    """One launch per mixer and token (featurizer step, split, gate, inner FIR or modal step,
+    cache updates, post-gate) against the separate operators the runtime used before, over
+    several consecutive tokens so that the in-place cache updates are exercised too."""
+    rng = np.random.default_rng({"hcs": 1, "hcm": 2, "hcm_f32": 3, "hcl": 4}[kind])
+    width, modes = 96, 16
+    taps = 7 if kind == "hcs" else 128
+    groups = 6 if kind != "hcl" else 1
+    short_filter = dev_bits(rand_bf16(rng, 3 * width, 3))
+    direct = None if kind == "hcs" else dev_bits(rand_bf16(rng, width))
+    if kind == "hcm_f32":
+        inner = dev((rng.standard_normal((groups, taps)) * 0.1).astype(np.float32))
+    else:
+        inner = dev_bits(rand_bf16(rng, groups, taps))
+    log_poles = dev(np.log(rng.uniform(0.9, 0.999, (width, modes))).astype(np.float32))
+    residues = dev((rng.standard_normal((width, modes)) * 0.02).astype(np.float32))
+    caches = []
+    for _ in range(2):  # fused, unfused: identical starting histories
+        seed = np.random.default_rng(99)
+        caches.append(dict(short=dev(seed.standard_normal((3 * width, 2)).astype(np.float32)),
+                           inner=dev(seed.standard_normal((width, taps - 1)).astype(np.float32)),
+                           modal=dev(seed.standard_normal((width, modes)).astype(np.float32))))
+    fused, plain = caches
+    for step in range(5):
+        projection = dev_bits(rand_bf16(rng, 3 * width))
+        out_fused, out_plain = empty_bits(width), empty_bits(width)
+        if kind == "hcl":
+            ops.call("bf16_hyena_decode_mixer", p(projection), p(short_filter), p(fused["short"]), p(direct),
+                     None, 0, 0, 0, 0, None, p(log_poles), p(residues), modes, p(fused["modal"]), width,
+                     p(out_fused), stream())
+        else:
+            ops.call("bf16_hyena_decode_mixer", p(projection), p(short_filter), p(fused["short"]), p(direct),
+                     p(inner), int(kind == "hcm_f32"), groups, taps, 0 if kind == "hcs" else 1, p(fused["inner"]),
+                     None, None, 0, None, width, p(out_fused), stream())
+        filtered = empty_bits(3 * width)
+        ops.call("bf16_fir_continue_direct", p(projection), p(short_filter), 0, None, 1, 3 * width, 3 * width, 3,
+                 0, 0, p(plain["short"]), 2, p(filtered), stream())
+        x2, x1, v, u, y = (empty_bits(width) for _ in range(5))
+        ops.call("bf16_split_hyena_projection", p(filtered), 1, width, p(x2), p(x1), p(v), stream())
+        if kind == "hcl":
+            ops.call("bf16_hcl_decode", p(x2), p(x1), p(v), p(direct), p(log_poles), p(residues), width, modes,
+                     p(plain["modal"]), None, p(out_plain), stream())
+        else:
+            ops.call("bf16_gated_elementwise", p(x1), p(v), width, 0, p(u), stream())
+            ops.call("bf16_fir_continue_direct", p(u), p(inner), int(kind == "hcm_f32"), p(direct), 1, width,
+                     groups, taps, 0 if kind == "hcs" else 1, 1, p(plain["inner"]), taps - 1, p(y), stream())
+            ops.call("bf16_gated_elementwise", p(y), p(x2), width, 0, p(out_plain), stream())
+        assert np.array_equal(host_bits(out_fused), host_bits(out_plain)), (kind, step)
+        for name in ("short", "inner", "modal"):
+            assert torch.equal(fused[name], plain[name]), (kind, step, name)
