@@ -126,7 +126,7 @@ template <bool kProj>
 __device__ __forceinline__ void build_tiles(const Params &p, unsigned char *u_tile,
                                             unsigned char *x2_tile, unsigned char *raw, const int rows,
                                             const int t_first, const int gate_first_row,
-                                            const int t_own, const int c_tile) {
+                                            const int t_own, const int c_tile, const bool first_of_window) {
   const int chunk = threadIdx.x % kChunks;
   const int c0 = c_tile + chunk * 8;
   const bool channel_ok = c0 < p.width;  // width is a multiple of 8
@@ -139,7 +139,7 @@ __device__ __forceinline__ void build_tiles(const Params &p, unsigned char *u_ti
     *reinterpret_cast<uint4 *>(u_tile + tile_offset(r, chunk)) = packed;
     // The first CTA of a row window also owns the history rows it recomputes,
     // so that the decode history is complete even for windows shorter than it.
-    const bool owns = t >= t_own || (blockIdx.x == 0 && t >= 0);
+    const bool owns = t >= t_own || (first_of_window && t >= 0);
     if (owns && t < p.length && channel_ok) {
       if (p.pregate != nullptr && t >= t_own)
         *reinterpret_cast<uint4 *>(p.pregate + static_cast<std::size_t>(t) * p.width + c0) = packed;
@@ -266,7 +266,7 @@ gated_fir_simt_kernel(const Params p) {
     h_tile[d * 32 + pair] = h;
   }
   build_tiles<kProj>(p, u_tile, x2_tile, reinterpret_cast<unsigned char *>(h_tile + p.padded_taps * 32),
-                     TT + halo, t0 - halo, halo, t0, c_tile);
+                     TT + halo, t0 - halo, halo, t0, c_tile, blockIdx.x == 0);
   __syncthreads();
 
   float direct0 = 0.0F, direct1 = 0.0F;
@@ -336,15 +336,18 @@ __device__ __forceinline__ void mma_bf16(float (&d)[4], const std::uint32_t (&a)
 
 constexpr int kMmaHalo = 128;  // history rows staged before the tile (>= taps-1, 16-aligned)
 
+// A CTA walks `tiles_per_cta` consecutive TT-row tiles of its 64 channels: only
+// the first one builds its 128 history rows from global memory, the later ones
+// keep the last 128 rows of u of the tile before (a 16 KB copy inside shared
+// memory instead of 128 rows of loads and featurizer work).
 template <bool kProj, int TT>
 __global__ void __launch_bounds__(kThreads, 2)
-gated_fir_mma_kernel(const Params p) {
+gated_fir_mma_kernel(const Params p, const int tiles_per_cta) {
   extern __shared__ __align__(128) unsigned char smem[];
   unsigned char *const u_tile = smem;
   unsigned char *const x2_tile = u_tile + (TT + kMmaHalo) * kRowBytes;
   unsigned short *const h_s =
       reinterpret_cast<unsigned short *>(x2_tile + TT * kRowBytes);  // [4 blocks][128] BF16 bits
-  const int t0 = p.row_begin + blockIdx.x * TT;
   const int c_tile = blockIdx.y * kChannels;
   const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
   const int block16 = warp % 4;             // 16-channel block of the tile
@@ -360,24 +363,8 @@ gated_fir_mma_kernel(const Params p) {
           p.filter)[static_cast<std::size_t>(channel / p.channels_per_group) * p.taps + d]);
     h_s[i] = bits;
   }
-  build_tiles<kProj>(p, u_tile, x2_tile, reinterpret_cast<unsigned char *>(h_s + 4 * 128),
-                     TT + kMmaHalo, t0 - kMmaHalo, kMmaHalo, t0, c_tile);
   __syncthreads();
 
-  // Toeplitz fragments: H[m][k] = h[128 + m - k] over k in [0, 144).
-  const unsigned short *const h = h_s + block16 * 128;
-  auto tap = [&](const int delay) -> std::uint32_t {
-    return (delay >= 0 && delay < 128) ? h[delay] : 0U;
-  };
-  std::uint32_t a_frag[9][4];
-#pragma unroll
-  for (int j = 0; j < 9; ++j) {
-    const int d = 128 + g - (16 * j + 2 * q);  // row g, k = 16j + 2q
-    a_frag[j][0] = tap(d) | (tap(d - 1) << 16U);
-    a_frag[j][1] = tap(d + 8) | (tap(d + 7) << 16U);
-    a_frag[j][2] = tap(d - 8) | (tap(d - 9) << 16U);
-    a_frag[j][3] = a_frag[j][0];
-  }
   const int channel0 = c_tile + block16 * 16;
   float direct[2][2] = {};
   if (p.direct != nullptr && channel0 < p.width) {
@@ -388,39 +375,74 @@ gated_fir_mma_kernel(const Params p) {
     }
   }
   const std::uint32_t u_base = static_cast<std::uint32_t>(__cvta_generic_to_shared(u_tile));
+  unsigned char *const raw = reinterpret_cast<unsigned char *>(h_s + 4 * 128);
   constexpr int kTilesPerWarp = TT / 32;
-  for (int mt = 0; mt < kTilesPerWarp; ++mt) {
-    const int row0 = part * (TT / 2) + 16 * mt;  // first output row of this m-tile
-    if (t0 + row0 >= p.length) break;
-    float acc[2][4] = {};
+  static_assert(TT >= kMmaHalo && TT % 8 == 0, "history rows move without overlapping, swizzle unchanged");
+
+  for (int step = 0; step < tiles_per_cta; ++step) {
+    const int t0 = p.row_begin + (blockIdx.x * tiles_per_cta + step) * TT;
+    if (t0 >= p.length) break;
+    if (step > 0) {
+      // rows [TT, TT + 128) of the previous tile are this tile's history
+      for (int i = threadIdx.x; i < kMmaHalo * kRowBytes / 16; i += kThreads)
+        reinterpret_cast<uint4 *>(u_tile)[i] = reinterpret_cast<const uint4 *>(u_tile + TT * kRowBytes)[i];
+      __syncthreads();
+    }
+    // one call site: the first tile also builds its history rows
+    const int skip = step == 0 ? 0 : kMmaHalo;
+    build_tiles<kProj>(p, u_tile + skip * kRowBytes, x2_tile, raw, TT + kMmaHalo - skip, t0 - kMmaHalo + skip,
+                       kMmaHalo - skip, t0, c_tile, step == 0 && blockIdx.x == 0);
+    __syncthreads();
+    // Toeplitz fragments: H[m][k] = h[128 + m - k] over k in [0, 144).  Rebuilt
+    // per tile (27 shared-memory loads) so that they do not occupy registers
+    // while the featurizer runs.
+    const unsigned short *const h = h_s + block16 * 128;
+    auto tap = [&](const int delay) -> std::uint32_t {
+      return (delay >= 0 && delay < 128) ? h[delay] : 0U;
+    };
+    std::uint32_t a_frag[9][4];
 #pragma unroll
     for (int j = 0; j < 9; ++j) {
-      std::uint32_t b[4];
-      const int row = row0 + 16 * j + (lane % 8) + ((lane / 8) % 2) * 8;
-      ldmatrix_x4_trans(u_base + tile_offset(row, 2 * block16 + lane / 16), b);
-      mma_bf16(acc[0], a_frag[j], b[0], b[1]);
-      mma_bf16(acc[1], a_frag[j], b[2], b[3]);
+      const int d = 128 + g - (16 * j + 2 * q);  // row g, k = 16j + 2q
+      a_frag[j][0] = tap(d) | (tap(d - 1) << 16U);
+      a_frag[j][1] = tap(d + 8) | (tap(d + 7) << 16U);
+      a_frag[j][2] = tap(d - 8) | (tap(d - 9) << 16U);
+      a_frag[j][3] = a_frag[j][0];
     }
+    for (int mt = 0; mt < kTilesPerWarp; ++mt) {
+      const int row0 = part * (TT / 2) + 16 * mt;  // first output row of this m-tile
+      if (t0 + row0 >= p.length) break;
+      float acc[2][4] = {};
 #pragma unroll
-    for (int nt = 0; nt < 2; ++nt)
-#pragma unroll
-      for (int half = 0; half < 2; ++half) {
-        const int row = row0 + g + 8 * half;
-        const int pair = 8 * block16 + 4 * nt + q;
-        float y0 = acc[nt][2 * half], y1 = acc[nt][2 * half + 1];
-        if (p.direct != nullptr) {
-          const std::uint32_t packed = tile_pair(u_tile, kMmaHalo + row, pair);
-          y0 = fmaf(direct[nt][0], lo(packed), y0);
-          y1 = fmaf(direct[nt][1], hi(packed), y1);
-        }
-        std::uint32_t *const slot = reinterpret_cast<std::uint32_t *>(
-            x2_tile + tile_offset(row, pair >> 2) + ((pair & 3) << 2));
-        const std::uint32_t gate = *slot;
-        *slot = pack_bf16x2(rbf(y0) * lo(gate), rbf(y1) * hi(gate));
+      for (int j = 0; j < 9; ++j) {
+        std::uint32_t b[4];
+        const int row = row0 + 16 * j + (lane % 8) + ((lane / 8) % 2) * 8;
+        ldmatrix_x4_trans(u_base + tile_offset(row, 2 * block16 + lane / 16), b);
+        mma_bf16(acc[0], a_frag[j], b[0], b[1]);
+        mma_bf16(acc[1], a_frag[j], b[2], b[3]);
       }
+#pragma unroll
+      for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+          const int row = row0 + g + 8 * half;
+          const int pair = 8 * block16 + 4 * nt + q;
+          float y0 = acc[nt][2 * half], y1 = acc[nt][2 * half + 1];
+          if (p.direct != nullptr) {
+            const std::uint32_t packed = tile_pair(u_tile, kMmaHalo + row, pair);
+            y0 = fmaf(direct[nt][0], lo(packed), y0);
+            y1 = fmaf(direct[nt][1], hi(packed), y1);
+          }
+          std::uint32_t *const slot = reinterpret_cast<std::uint32_t *>(
+              x2_tile + tile_offset(row, pair >> 2) + ((pair & 3) << 2));
+          const std::uint32_t gate = *slot;
+          *slot = pack_bf16x2(rbf(y0) * lo(gate), rbf(y1) * hi(gate));
+        }
+    }
+    __syncthreads();
+    store_tile(p, x2_tile, TT, t0, c_tile);
+    __syncthreads();  // both tiles are rewritten by the next step
   }
-  __syncthreads();
-  store_tile(p, x2_tile, TT, t0, c_tile);
 }
 
 // ------------------------------------------------------- register streaming
@@ -694,6 +716,33 @@ int launch(Kernel kernel, const Params &p, const int tile_rows, const std::size_
   return check_launch(what);
 }
 
+// Grid of the Toeplitz kernel: each CTA walks as many consecutive tiles as it
+// takes for the grid to fit the resident slots once ...
+template <bool kProj, int TT>
+int launch_mma(const Params &p, const std::size_t smem, cudaStream_t stream) {
+  const auto kernel = gated_fir_mma_kernel<kProj, TT>;
+  if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) !=
+      cudaSuccess)
+    return fail(kCuda, "cannot raise the fused FIR shared-memory limit");
+  static const int resident = [&] {
+    int blocks = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&blocks, kernel, kThreads, smem) != cudaSuccess || blocks < 1)
+      blocks = 1;
+    return blocks;
+  }();
+  const unsigned int tiles = ceil_div_u(p.length - p.row_begin, TT);
+  const unsigned int across = ceil_div_u(p.width, kChannels);
+  if (across > 65535) return fail(kInvalidArgument, "gated FIR is too wide");
+  const unsigned int slots = static_cast<unsigned int>(kSmCount * resident);
+  const unsigned int segments = std::max(1U, std::min(tiles, slots / std::max(1U, across)));
+  // ... but no more than 8 tiles each: longer walks keep the two CTAs of an SM in
+  // the same phase (both loading, then both on the tensor cores) and measured slower.
+  const int tiles_per_cta = std::min(8, static_cast<int>(ceil_div_u(tiles, segments)));
+  const dim3 grid(ceil_div_u(tiles, tiles_per_cta), across);
+  kernel<<<grid, kThreads, smem, stream>>>(p, tiles_per_cta);
+  return check_launch("fused Toeplitz FIR kernel");
+}
+
 bool aligned16(const void *ptr) { return (reinterpret_cast<std::uintptr_t>(ptr) & 15U) == 0; }
 
 }  // namespace
@@ -743,9 +792,7 @@ int gated_fir_prefill(const GatedFirArgs &a, cudaStream_t stream) {
     constexpr int TT = 256;
     const std::size_t smem = (TT + kMmaHalo) * kRowBytes + TT * kRowBytes + 4 * 128 * 2 +
                              (from_projection ? kRawBytes : 0);
-    status = from_projection
-                 ? launch(gated_fir_mma_kernel<true, TT>, p, TT, smem, stream, "fused Toeplitz FIR kernel")
-                 : launch(gated_fir_mma_kernel<false, TT>, p, TT, smem, stream, "fused Toeplitz FIR kernel");
+    status = from_projection ? launch_mma<true, TT>(p, smem, stream) : launch_mma<false, TT>(p, smem, stream);
   } else if (streaming) {
     p.short_cache = from_projection && a.short_taps == 3 ? a.short_cache : nullptr;
     status = from_projection ? launch_stream_taps<true>(p, stream) : launch_stream_taps<false>(p, stream);
