@@ -9,6 +9,8 @@
 // src/cuda/model.cu:269-284).
 #include <cuda_fp8.h>
 
+#include <algorithm>
+
 #include "common.cuh"
 #include "ops_internal.hpp"
 
@@ -106,32 +108,19 @@ __device__ __forceinline__ float warp_sum_down(float value) {
   return value;
 }
 
-__global__ void __launch_bounds__(kThreads)
-rms_norm_kernel(const bf16 *__restrict__ input, const float *__restrict__ scale,
-                bf16 *__restrict__ output, std::uint8_t *__restrict__ codes,
-                const std::size_t width, const float epsilon,
-                const float quant_scale) {
-  extern __shared__ __align__(16) unsigned short row_cache[];  // width BF16 values
-  __shared__ float partial[32];
-  const std::size_t row = blockIdx.x;
-  const bf16 *const in = input + row * width;
-  // 128-bit row loads when the layout allows; the sum below still visits the
-  // columns in the thread-strided order regardless of how the row was fetched.
-  const bool vectors = width % 8 == 0 &&
-                       (reinterpret_cast<std::uintptr_t>(input) & 15U) == 0 &&
-                       (reinterpret_cast<std::uintptr_t>(scale) & 15U) == 0 &&
-                       (output == nullptr || (reinterpret_cast<std::uintptr_t>(output) & 15U) == 0) &&
-                       (codes == nullptr || (reinterpret_cast<std::uintptr_t>(codes) & 7U) == 0);
-  if (vectors) {
-    for (std::size_t v = threadIdx.x; v < width / 8; v += kThreads)
-      reinterpret_cast<uint4 *>(row_cache)[v] = reinterpret_cast<const uint4 *>(in)[v];
-  } else {
-    for (std::size_t column = threadIdx.x; column < width; column += kThreads)
-      row_cache[column] = __bfloat16_as_ushort(in[column]);
-  }
-  __syncthreads();
+// Packs two values that are already BF16-representable (no rounding needed).
+__device__ __forceinline__ std::uint32_t pack_exact_pair(const float low, const float high) {
+  return (__float_as_uint(low) >> 16U) | (__float_as_uint(high) & 0xffff0000U);
+}
+
+// Sum of squares of the cached row in the pinned order, then the BF16 chain
+// down to the denominator.  Two block-wide barriers; every thread returns it.
+__device__ __forceinline__ float row_denominator(const unsigned short *row_cache, const std::size_t width,
+                                                 const float epsilon, float *partial) {
   float sum = 0.0F;
-  for (std::size_t column = threadIdx.x; column < width; column += kThreads) {
+  const int columns = static_cast<int>(width);  // <= 24576
+#pragma unroll 8
+  for (int column = threadIdx.x; column < columns; column += kThreads) {
     const float value = bits2f_bf16(row_cache[column]);
     sum = fmaf(value, value, sum);
   }
@@ -150,53 +139,111 @@ rms_norm_kernel(const bf16 *__restrict__ input, const float *__restrict__ scale,
     }
   }
   __syncthreads();
-  const float denominator = partial[0];
-  if (vectors) {
-    for (std::size_t v = threadIdx.x; v < width / 8; v += kThreads) {
+  return partial[0];
+}
+
+// Normalises the cached row 8 columns per thread and step (width % 8 == 0, 16-byte
+// aligned pointers) and stores BF16 values and / or E4M3 codes.
+__device__ __forceinline__ void store_normalized_row(const unsigned short *row_cache, const float *scale,
+                                                     const std::uint32_t *scale_pairs,
+                                                     const float denominator, const std::size_t width,
+                                                     bf16 *out_row, std::uint8_t *codes_row,
+                                                     const float quant_scale) {
+  const int vectors = static_cast<int>(width / 8);
+  // bf16(x / den) == bf16(x * (1/den)) for every BF16 x and every BF16 den
+  // in [1e-30, 1e30] (checked exhaustively on the host: a BF16 quotient is
+  // never closer than ~2^-17 relative to a BF16 rounding boundary), so the
+  // IEEE division is only kept for denominators outside that range.
+  const bool by_reciprocal = denominator >= 1e-30F && denominator <= 1e30F;
+  const float reciprocal = __frcp_rn(denominator);
+  const auto load = [&](const int v, Bf16x8 &values, float (&scales)[8]) {
+    values.raw = reinterpret_cast<const uint4 *>(row_cache)[v];
+    const float4 s0 = __ldg(reinterpret_cast<const float4 *>(scale) + 2 * v);
+    const float4 s1 = __ldg(reinterpret_cast<const float4 *>(scale) + 2 * v + 1);
+    scales[0] = s0.x; scales[1] = s0.y; scales[2] = s0.z; scales[3] = s0.w;
+    scales[4] = s1.x; scales[5] = s1.y; scales[6] = s1.z; scales[7] = s1.w;
+  };
+  if (by_reciprocal && codes_row == nullptr) {
+    // no codes wanted: bf16(x / den) two at a time, then one packed BF16 multiply with the
+    // BF16 scale pair (a product of BF16 values rounded once, as the scalar chain does)
+#pragma unroll 2
+    for (int v = threadIdx.x; v < vectors; v += kThreads) {
       Bf16x8 values;
       values.raw = reinterpret_cast<const uint4 *>(row_cache)[v];
-      const float4 s0 = reinterpret_cast<const float4 *>(scale)[2 * v];
-      const float4 s1 = reinterpret_cast<const float4 *>(scale)[2 * v + 1];
-      const float scales[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
-      float results[8];
-      // bf16(x / den) == bf16(x * (1/den)) for every BF16 x and every BF16 den
-      // in [1e-30, 1e30] (checked exhaustively on the host: a BF16 quotient is
-      // never closer than ~2^-17 relative to a BF16 rounding boundary), so the
-      // IEEE division is only kept for denominators outside that range.
-      if (denominator >= 1e-30F && denominator <= 1e30F) {
-        const float reciprocal = __frcp_rn(denominator);
-        if (codes == nullptr) {
-          // no codes wanted: round the products two at a time straight into the packed result
-          std::uint32_t packed[4];
+      const uint4 pairs = reinterpret_cast<const uint4 *>(scale_pairs)[v];
+      const std::uint32_t scales[4] = {pairs.x, pairs.y, pairs.z, pairs.w};
+      std::uint32_t packed[4];
 #pragma unroll
-          for (int j = 0; j < 8; j += 2)
-            packed[j / 2] = round_pair(rbf(values.get(j) * reciprocal) * rbf(scales[j]),
-                                       rbf(values.get(j + 1) * reciprocal) * rbf(scales[j + 1]));
-          reinterpret_cast<uint4 *>(output + row * width)[v] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
-          continue;
-        }
-#pragma unroll
-        for (int j = 0; j < 8; ++j)
-          results[j] = rbf(rbf(values.get(j) * reciprocal) * rbf(scales[j]));
-      } else {
-#pragma unroll
-        for (int j = 0; j < 8; ++j)
-          results[j] = rbf(rbf(__fdiv_rn(values.get(j), denominator)) * rbf(scales[j]));
+      for (int j = 0; j < 4; ++j) {
+        const std::uint32_t normalized =
+            round_pair(values.get(2 * j) * reciprocal, values.get(2 * j + 1) * reciprocal);
+        asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(packed[j]) : "r"(normalized), "r"(scales[j]));
       }
-      if (output != nullptr)
-        reinterpret_cast<uint4 *>(output + row * width)[v] =
-            make_uint4(pack_bf16x2(results[0], results[1]), pack_bf16x2(results[2], results[3]),
-                       pack_bf16x2(results[4], results[5]), pack_bf16x2(results[6], results[7]));
-      if (codes != nullptr) {
-        unsigned int words[2] = {0U, 0U};
-#pragma unroll
-        for (int j = 0; j < 8; ++j)
-          words[j / 4] |= static_cast<unsigned int>(e4m3_code(results[j] * quant_scale)) << (8 * (j % 4));
-        reinterpret_cast<uint2 *>(codes + row * width)[v] = make_uint2(words[0], words[1]);
-      }
+      reinterpret_cast<uint4 *>(out_row)[v] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
     }
     return;
   }
+  if (by_reciprocal) {
+    // with codes: the same packed chain, then two E4M3 codes per conversion
+#pragma unroll 2
+    for (int v = threadIdx.x; v < vectors; v += kThreads) {
+      Bf16x8 values;
+      values.raw = reinterpret_cast<const uint4 *>(row_cache)[v];
+      const uint4 pairs = reinterpret_cast<const uint4 *>(scale_pairs)[v];
+      const std::uint32_t scales[4] = {pairs.x, pairs.y, pairs.z, pairs.w};
+      std::uint32_t packed[4];
+      unsigned int words[2] = {0U, 0U};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const std::uint32_t normalized =
+            round_pair(values.get(2 * j) * reciprocal, values.get(2 * j + 1) * reciprocal);
+        asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(packed[j]) : "r"(normalized), "r"(scales[j]));
+        const float2 scaled = make_float2(__uint_as_float(packed[j] << 16U) * quant_scale,
+                                          __uint_as_float(packed[j] & 0xffff0000U) * quant_scale);
+        const unsigned int two = __nv_cvt_float2_to_fp8x2(scaled, __NV_SATFINITE, __NV_E4M3);  // .x in the low byte
+        words[j / 2] |= two << (16 * (j % 2));
+      }
+      if (out_row != nullptr)
+        reinterpret_cast<uint4 *>(out_row)[v] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+      reinterpret_cast<uint2 *>(codes_row)[v] = make_uint2(words[0], words[1]);
+    }
+    return;
+  }
+  for (int v = threadIdx.x; v < vectors; v += kThreads) {
+    Bf16x8 values;
+    float scales[8], results[8];
+    load(v, values, scales);
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+      results[j] = rbf(rbf(__fdiv_rn(values.get(j), denominator)) * rbf(scales[j]));
+    if (out_row != nullptr)
+      reinterpret_cast<uint4 *>(out_row)[v] =
+          make_uint4(pack_exact_pair(results[0], results[1]), pack_exact_pair(results[2], results[3]),
+                     pack_exact_pair(results[4], results[5]), pack_exact_pair(results[6], results[7]));
+    if (codes_row != nullptr) {
+      unsigned int words[2] = {0U, 0U};
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        words[j / 4] |= static_cast<unsigned int>(e4m3_code(results[j] * quant_scale)) << (8 * (j % 4));
+      reinterpret_cast<uint2 *>(codes_row)[v] = make_uint2(words[0], words[1]);
+    }
+  }
+}
+
+// Generic form: one block per row, any width and alignment.
+__global__ void __launch_bounds__(kThreads)
+rms_norm_kernel(const bf16 *__restrict__ input, const float *__restrict__ scale,
+                bf16 *__restrict__ output, std::uint8_t *__restrict__ codes,
+                const std::size_t width, const float epsilon,
+                const float quant_scale) {
+  extern __shared__ __align__(16) unsigned short row_cache[];  // width BF16 values
+  __shared__ float partial[32];
+  const std::size_t row = blockIdx.x;
+  const bf16 *const in = input + row * width;
+  for (std::size_t column = threadIdx.x; column < width; column += kThreads)
+    row_cache[column] = __bfloat16_as_ushort(in[column]);
+  __syncthreads();
+  const float denominator = row_denominator(row_cache, width, epsilon, partial);
   for (std::size_t column = threadIdx.x; column < width; column += kThreads) {
     const float value = bits2f_bf16(row_cache[column]);
     const float column_scale = rbf(scale[column]);
@@ -205,6 +252,51 @@ rms_norm_kernel(const bf16 *__restrict__ input, const float *__restrict__ scale,
     if (output != nullptr) output[row * width + column] = result;
     if (codes != nullptr)
       codes[row * width + column] = e4m3_code(bf2f(result) * quant_scale);
+  }
+}
+
+// Vector form (width % 8 == 0, 16-byte aligned pointers): persistent blocks, each
+// walking rows blockIdx.x, blockIdx.x + gridDim.x, ...  The next row of a block
+// is copied into the other half of the shared row cache with cp.async while
+// the current one is reduced and normalised, so a block always has a row of
+// loads in flight instead of waiting for them at the start of every row.
+__global__ void __launch_bounds__(kThreads)
+rms_norm_stream_kernel(const bf16 *__restrict__ input, const float *__restrict__ scale,
+                       bf16 *__restrict__ output, std::uint8_t *__restrict__ codes, const std::size_t rows,
+                       const std::size_t width, const float epsilon, const float quant_scale) {
+  extern __shared__ __align__(16) unsigned short row_cache[];  // 2 x width BF16 values, then width BF16 scales
+  __shared__ float partial[32];
+  std::uint32_t *const scale_pairs = reinterpret_cast<std::uint32_t *>(row_cache + 2 * width);
+  for (std::size_t i = threadIdx.x; i < width / 2; i += kThreads)
+    scale_pairs[i] = round_pair(scale[2 * i], scale[2 * i + 1]);  // visible after the first barrier below
+  const auto fetch = [&](const std::size_t row, unsigned short *target) {
+    const uint4 *const source = reinterpret_cast<const uint4 *>(input + row * width);
+    for (std::size_t v = threadIdx.x; v < width / 8; v += kThreads) {
+      const std::uint32_t address =
+          static_cast<std::uint32_t>(__cvta_generic_to_shared(reinterpret_cast<uint4 *>(target) + v));
+      asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(address), "l"(source + v) : "memory");
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+  std::size_t row = blockIdx.x;
+  if (row >= rows) return;
+  fetch(row, row_cache);
+  for (int parity = 0; row < rows; row += gridDim.x, parity ^= 1) {
+    unsigned short *const current = row_cache + parity * width;
+    const std::size_t next = row + gridDim.x;
+    // A thread's copies land in the chunks that only this thread reads in the
+    // store phase; the strided reads of the reduction are fenced by its barriers.
+    if (next < rows) {
+      fetch(next, row_cache + (parity ^ 1) * width);
+      asm volatile("cp.async.wait_group 1;" ::: "memory");
+    } else {
+      asm volatile("cp.async.wait_group 0;" ::: "memory");
+    }
+    __syncthreads();
+    const float denominator = row_denominator(current, width, epsilon, partial);
+    store_normalized_row(current, scale, scale_pairs, denominator, width,
+                         output == nullptr ? nullptr : output + row * width,
+                         codes == nullptr ? nullptr : codes + row * width, quant_scale);
   }
 }
 
@@ -380,6 +472,28 @@ int rms_norm(const void *input, const float *scale, const std::size_t rows,
   if (codes != nullptr && (!(quant_scale > 0.0F) || !isfinite(quant_scale)))
     return fail(kInvalidArgument, "RMSNorm quantisation scale is invalid");
   if (rows == 0) return kOk;
+  const auto aligned = [](const void *q, const std::uintptr_t mask) {
+    return (reinterpret_cast<std::uintptr_t>(q) & mask) == 0;
+  };
+  const bool vectors = width % 8 == 0 && aligned(input, 15) && aligned(scale, 15) &&
+                       (output == nullptr || aligned(output, 15)) && (codes == nullptr || aligned(codes, 7));
+  if (vectors) {
+    const std::size_t smem = 3 * width * sizeof(unsigned short);
+    if (smem + 1024 > 48 * 1024 &&  // the static reduction buffer counts against the default limit too
+        cudaFuncSetAttribute(rms_norm_stream_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             static_cast<int>(smem)) != cudaSuccess)
+      return fail(kCuda, "cannot raise the RMSNorm shared-memory limit");
+    int resident = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&resident, rms_norm_stream_kernel, kThreads, smem) !=
+            cudaSuccess ||
+        resident < 1)
+      resident = 1;
+    const std::size_t grid = std::min<std::size_t>(rows, static_cast<std::size_t>(kSmCount) * resident);
+    rms_norm_stream_kernel<<<static_cast<unsigned int>(grid), kThreads, smem, stream>>>(
+        static_cast<const bf16 *>(input), scale, static_cast<bf16 *>(output), static_cast<std::uint8_t *>(codes),
+        rows, width, epsilon, quant_scale);
+    return check_launch("RMSNorm kernel");
+  }
   rms_norm_kernel<<<static_cast<unsigned int>(rows), kThreads,
                     width * sizeof(unsigned short), stream>>>(
       static_cast<const bf16 *>(input), scale, static_cast<bf16 *>(output),

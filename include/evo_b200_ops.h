@@ -197,10 +197,10 @@ EVO_B200_API int evo_b200_bf16_hcl_prefill(
  * are still the caller's buffers; only the segment-state scratch differs: it
  * is a fixed 4 Mi-float (16 MiB) array inside the library image, resident on
  * every GPU that loads the library until the process exits.
- *  - Limit: ceil(length / segment) * width * modes floats must fit the array;
- *    the segment is lengthened automatically to make it fit, so the call is
- *    refused (status 2, message names the limit) only when width * modes
- *    itself exceeds 4 Mi floats.
+ *  - Limit: one state of width * modes floats per row segment plus one must
+ *    fit the array; fewer, longer segments are used when they do not, so the
+ *    call is refused (status 2, message names the limit) only when width *
+ *    modes itself exceeds 4 Mi floats.
  *  - The first call on each device resolves the array's device address
  *    (cudaGetSymbolAddress, with that device current); make that first call
  *    outside any stream capture.
