@@ -375,6 +375,159 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
   }
 }
 
+// --------------------------------------------------- few tokens (swap-AB)
+// At up to 128 tokens a projection is a weight stream, and the tile kernel above
+// pulls on it badly: its 128-row MMA spends a full tile of tensor time on every
+// weight block whether 16 or 128 of the rows are tokens, and it has only
+// N / 256 tiles to spread over the SMs.  Here the roles are swapped: the weight
+// rows are the M = 128 operand, the tokens the N = BT operand (16..128), so the
+// tensor time per weight byte falls with the token count, a CTA owns 128 weight
+// rows x one K slice, and K is split until enough CTAs pull on the stream.  The
+// CTAs leave raw F32 partial sums [split][token][weight row]; the finishing
+// kernel adds them in split order and applies the epilogue.
+constexpr int kSwapStages = 6;
+
+template <int BT>
+struct SwapLayout {
+  static constexpr int kWBytes = kBlockM * kBlockKBytes;  // 128 weight rows x 128 bytes of K
+  static constexpr int kXBytes = BT * kBlockKBytes;
+  static constexpr int kStageBytes = kWBytes + kXBytes;
+  static constexpr int kBarrierOffset = kSwapStages * kStageBytes;
+  static constexpr int kBarrierCount = 2 * kSwapStages + 1;  // full[], empty[], accumulator ready
+  static constexpr int kTmemPtrOffset = kBarrierOffset + kBarrierCount * 8;
+  static constexpr int kAbortOffset = kTmemPtrOffset + 8;
+  static constexpr int kTotal = kAbortOffset + 8 + 1024;  // + alignment slack
+};
+
+template <bool kFp8, int BT>
+__global__ void __launch_bounds__(kGemmThreads)
+gemm_swap_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
+                 float *const partials, const std::size_t partial_stride, const int M, const int N,
+                 const int tiles_n, const int k_per_split, int *const error_word) {
+  using L = SwapLayout<BT>;
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char *const smem = reinterpret_cast<unsigned char *>(
+      (reinterpret_cast<std::uintptr_t>(smem_raw) + 1023U) & ~static_cast<std::uintptr_t>(1023U));
+  const std::uint32_t smem_base = smem_u32(smem);
+  const std::uint32_t bar_base = smem_base + L::kBarrierOffset;
+  auto full_bar = [&](const int s) { return bar_base + 8U * s; };
+  auto empty_bar = [&](const int s) { return bar_base + 8U * (kSwapStages + s); };
+  const std::uint32_t ready_bar = bar_base + 8U * (2 * kSwapStages);
+  volatile std::uint32_t *const tmem_ptr = reinterpret_cast<volatile std::uint32_t *>(smem + L::kTmemPtrOffset);
+  volatile int *const abort_flag = reinterpret_cast<volatile int *>(smem + L::kAbortOffset);
+  const int warp = threadIdx.x / 32;
+  const int lane = threadIdx.x % 32;
+  constexpr std::uint32_t kTmemColumns = BT < 32 ? 32 : BT;  // power of two, at least 32
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kSwapStages; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    mbar_init(ready_bar, 1);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::
+                     "r"(smem_u32(const_cast<std::uint32_t *>(tmem_ptr))),
+                 "r"(kTmemColumns)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const std::uint32_t tmem_base = *tmem_ptr;
+
+  const int tile_n = blockIdx.x % tiles_n;
+  const int split = blockIdx.x / tiles_n;
+  const int n0 = tile_n * kBlockM;
+  const int kb_begin = split * k_per_split;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      int stage = 0;
+      std::uint32_t phase = 0;
+      for (int kb = kb_begin; kb < kb_begin + k_per_split; ++kb) {
+        if (!mbar_wait(empty_bar(stage), phase ^ 1U, abort_flag)) break;
+        const std::uint32_t w_dst = smem_base + stage * L::kStageBytes;
+        mbar_expect_tx(full_bar(stage), L::kStageBytes);
+        const int k_elem = kFp8 ? kb * kBlockKBytes : kb * (kBlockKBytes / 2);
+        tma_load_2d(w_dst, &map_w, full_bar(stage), k_elem, n0);
+        tma_load_2d(w_dst + L::kWBytes, &map_x, full_bar(stage), k_elem, 0);
+        if (++stage == kSwapStages) {
+          stage = 0;
+          phase ^= 1U;
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr std::uint32_t idesc = instruction_descriptor<kFp8, BT>();
+      int stage = 0;
+      std::uint32_t phase = 0;
+      bool ok = true;
+      for (int kb = 0; kb < k_per_split; ++kb) {
+        if (!mbar_wait(full_bar(stage), phase, abort_flag)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        const std::uint32_t w_addr = smem_base + stage * L::kStageBytes;
+        const std::uint64_t w_desc = smem_descriptor(w_addr);
+        const std::uint64_t x_desc = smem_descriptor(w_addr + L::kWBytes);
+#pragma unroll
+        for (int k = 0; k < kBlockKBytes / 32; ++k)
+          tc_mma<kFp8>(tmem_base, w_desc + 2U * k, x_desc + 2U * k, idesc, (kb | k) != 0 ? 1U : 0U);
+        tc_commit(empty_bar(stage));
+        if (++stage == kSwapStages) {
+          stage = 0;
+          phase ^= 1U;
+        }
+      }
+      if (ok) tc_commit(ready_bar);
+    }
+  } else {
+    const int quarter = warp % 4;
+    if (mbar_wait(ready_bar, 0U, abort_flag)) {
+      tc_fence_after();
+      const int n = n0 + quarter * 32 + lane;  // this thread's weight row = output column
+      const std::uint32_t taddr = tmem_base + (static_cast<std::uint32_t>(quarter * 32) << 16U);
+      float *const out = partials + static_cast<std::size_t>(split) * partial_stride + n;
+      for (int c = 0; c < (BT + 31) / 32; ++c) {
+        std::uint32_t v[32];
+        tmem_load_32(taddr + c * 32, v);
+        tmem_load_wait();
+        if (n < N) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const int token = c * 32 + j;
+            // consecutive lanes hold consecutive output columns: 128-byte stores
+            if (token < M && token < BT) out[static_cast<std::size_t>(token) * N] = __uint_as_float(v[j]);
+          }
+        }
+      }
+    }
+    tc_fence_before();
+  }
+
+  __syncwarp();
+  tc_fence_before();
+  __syncthreads();
+  if (*abort_flag != 0) {
+    const unsigned long long start = global_timer_ns();
+    while (global_timer_ns() - start < 200000ULL) __nanosleep(1000);
+    if (threadIdx.x == 0) atomicExch(error_word, 1);
+  }
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemColumns)
+                 : "memory");
+  }
+}
+
 // ---------------------------------------------------------- SIMT fallback
 // Shapes the TMA path cannot take (row pitch not a multiple of 16 bytes, or
 // the tiny test-fixture widths) run on CUDA cores with the same epilogue.
@@ -584,6 +737,35 @@ int launch_tc(const void *a, const void *b, const EpilogueParams &ep,
   return check_launch("tcgen05 GEMM kernel");
 }
 
+template <bool kFp8, int BT>
+int launch_swap(const void *x, const void *w, float *partials, const std::size_t M, const std::size_t N,
+                const std::size_t K, const int split, cudaStream_t stream) {
+  int status = kOk;
+  DeviceState *const state = device_state(&status);
+  if (state == nullptr) return status;
+  CUtensorMap map_w, map_x;
+  status = make_map(&map_w, w, kFp8, N, K, kBlockM);
+  if (status != kOk) return status;
+  status = make_map(&map_x, x, kFp8, M, K, BT);
+  if (status != kOk) return status;
+  using L = SwapLayout<BT>;
+  static bool configured[64] = {};
+  int device = 0;
+  cudaGetDevice(&device);
+  if (!configured[device]) {
+    if (cudaFuncSetAttribute(gemm_swap_kernel<kFp8, BT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             L::kTotal) != cudaSuccess)
+      return fail(kCuda, "cannot raise the GEMM shared-memory limit");
+    configured[device] = true;
+  }
+  const int tiles_n = static_cast<int>((N + kBlockM - 1) / kBlockM);
+  const int k_blocks = static_cast<int>(K * (kFp8 ? 1 : 2) / kBlockKBytes);
+  gemm_swap_kernel<kFp8, BT><<<static_cast<unsigned int>(tiles_n * split), kGemmThreads, L::kTotal, stream>>>(
+      map_w, map_x, partials, M * N, static_cast<int>(M), static_cast<int>(N), tiles_n, k_blocks / split,
+      state->error_word);
+  return check_launch("tcgen05 few-token GEMM kernel");
+}
+
 }  // namespace
 
 namespace tc {
@@ -660,6 +842,48 @@ int linear(const LinearArgs &args, cudaStream_t stream) {
       (reinterpret_cast<std::uintptr_t>(args.input) & 15U) == 0 &&
       (reinterpret_cast<std::uintptr_t>(args.weight) & 15U) == 0 &&
       args.out_features >= 64 && !args.force_simt;
+  // (measured at 128 rows: 27.6 / 31.8 us against 34.8 / 71.7 us for 4096x4096 / 4096x11264 weights, but
+  // 48 / 75 us against 37 / 61 us for 12288 / 22528 weight rows, where the tile kernel has enough tiles
+  // and the partial sums cost more than the swap saves; at 16 rows 17 / 28 / 28 / 44 us against 33 / 72 / 37 / 59 us)
+  if (tma_ok && args.split_workspace != nullptr && args.output_f32 == nullptr &&
+      (args.rows <= 64 || (args.rows <= 128 && args.out_features <= 8192)) &&
+      pitch % kBlockKBytes == 0 && args.weight_wrap_features == 0 &&
+      (args.gate_mode == 0 || args.out_features % 256 == 0)) {
+    // Few tokens: weights as the 128-row operand, tokens as the narrow one, K split until
+    // enough CTAs pull on the weight stream; partial sums limited to ~a quarter of the weight bytes.
+    const std::size_t tiles_n = (args.out_features + kBlockM - 1) / kBlockM;
+    const std::size_t k_blocks = pitch / kBlockKBytes;
+    int split = 1;
+    for (const int candidate : {8, 4, 2}) {
+      if (k_blocks % candidate == 0 && k_blocks / candidate >= 8 && tiles_n * candidate <= 2 * kSmCount &&
+          static_cast<std::size_t>(candidate) * args.rows * 32 <= pitch &&
+          static_cast<std::size_t>(candidate) * args.rows * args.out_features * sizeof(float) <=
+              args.split_workspace_bytes) {
+        split = candidate;
+        break;
+      }
+    }
+    if (args.rows * args.out_features * sizeof(float) <= args.split_workspace_bytes) {
+      float *const partials = static_cast<float *>(args.split_workspace);
+      const auto launch = [&](auto fp8_tag, auto bt_tag) {
+        return launch_swap<decltype(fp8_tag)::value, decltype(bt_tag)::value>(
+            args.input, args.weight, partials, args.rows, args.out_features, args.in_features, split, stream);
+      };
+      using F = std::false_type;
+      using T = std::true_type;
+      int status;
+      if (args.rows <= 16) status = fp8 ? launch(T{}, std::integral_constant<int, 16>{}) : launch(F{}, std::integral_constant<int, 16>{});
+      else if (args.rows <= 32) status = fp8 ? launch(T{}, std::integral_constant<int, 32>{}) : launch(F{}, std::integral_constant<int, 32>{});
+      else if (args.rows <= 64) status = fp8 ? launch(T{}, std::integral_constant<int, 64>{}) : launch(F{}, std::integral_constant<int, 64>{});
+      else status = fp8 ? launch(T{}, std::integral_constant<int, 128>{}) : launch(F{}, std::integral_constant<int, 128>{});
+      if (status != kOk) return status;
+      const std::size_t outputs = args.rows * out_columns;
+      splitk_finish_kernel<<<static_cast<unsigned int>((outputs + 255) / 256 > 2048 ? 2048 : (outputs + 255) / 256),
+                             256, 0, stream>>>(partials, split, args.rows * args.out_features, ep,
+                                               static_cast<int>(args.rows), static_cast<int>(args.out_features));
+      return check_launch("split-K finishing kernel");
+    }
+  }
   // (measured: pays off up to a few dozen rows; at 128 rows the partial-sum traffic outweighs it)
   if (tma_ok && args.split_workspace != nullptr && args.output_f32 == nullptr && args.rows <= 32 &&
       pitch % kBlockKBytes == 0 && (args.gate_mode == 0 || args.out_features % 256 == 0)) {

@@ -129,10 +129,13 @@ def test_e4m3_tensorcore_linear_against_exact_products(ops, oracle, rows, inner,
 
 
 @pytest.mark.parametrize("rows,inner,columns", [(16, 4096, 4096), (32, 4096, 12288), (24, 11264, 4096),
-                                               (31, 4096, 512), (9, 2048, 1024)])
+                                               (31, 4096, 512), (9, 2048, 1024), (64, 4096, 4096),
+                                               (100, 1920, 5760), (128, 4096, 22528), (128, 11264, 4096),
+                                               (48, 4096, 512), (33, 4096, 200)])
 def test_split_k_projection_against_f32_matmul(ops, rows, inner, columns):
-    """9..32 rows with a workspace: K is split over several CTAs per tile, F32 partials are
-    added in split order; bias, residual and their rounding points as in the one-pass kernel."""
+    """9..128 rows with a workspace: the weights are the 128-row tensor-core operand and the tokens
+    the narrow one, K is split over several CTAs per 128 weight rows, F32 partials are added in
+    split order; bias, residual and their rounding points as in the one-pass kernel."""
     torch.manual_seed(rows + columns)
     x = torch.randn(rows, inner, device="cuda").bfloat16()
     w = (torch.randn(columns, inner, device="cuda") * 0.02).bfloat16()
@@ -161,7 +164,11 @@ def test_split_k_projection_against_f32_matmul(ops, rows, inner, columns):
 
 def test_split_k_gated_up_projection(ops):
     torch.manual_seed(5)
-    rows, inner, hidden = 28, 4096, 2048
+    for rows, inner, hidden in ((28, 4096, 2048), (100, 4096, 11264)):
+        _check_split_k_gated(ops, rows, inner, hidden)
+
+
+def _check_split_k_gated(ops, rows, inner, hidden):
     x = torch.randn(rows, inner, device="cuda").bfloat16()
     w1 = (torch.randn(hidden, inner, device="cuda") * 0.02).bfloat16()
     w2 = (torch.randn(hidden, inner, device="cuda") * 0.02).bfloat16()
@@ -179,6 +186,7 @@ def test_split_k_gated_up_projection(ops):
         if activation == 1:
             first = torch.nn.functional.gelu(first).bfloat16().float()
         reference = first * (x.float() @ w2.float().T).bfloat16().float()
-        assert float((split.float() - reference).abs().max()) < 0.05
-        assert float((split.float() - fused.float()).abs().max()) < 0.05
+        # a BF16 ulp of the product where a factor rounded the other way (values reach ~10 at 1.1 M outputs)
+        assert bool(((split.float() - reference).abs() <= 0.05 + 0.02 * reference.abs()).all())
+        assert bool(((split.float() - fused.float()).abs() <= 0.05 + 0.02 * fused.float().abs()).all())
         assert float((split != fused).float().mean()) < 0.05
