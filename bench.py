@@ -304,7 +304,9 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> None:
     context.synchronize()
     profile = context.profile_read()
     context.profile_enable(False)
-    launches_per_step = sum(n for _, n in profile.values()) // args.steps + 1  # + embedding
+    # operator calls of the runtime; the modal scan is two kernels per call, plus the embedding
+    launches_per_step = (sum(n for _, n in profile.values()) + profile.get("hcl_modal_scan", (0, 0))[1]) \
+        // args.steps + 1
     gemm_ms, gemm_launches = profile["gemm_bf16_tcgen05"]
     fp8_ms, fp8_launches = profile["gemm_e4m3_tcgen05"]
     hyena_layers = LAYERS - ATTENTION_LAYERS
