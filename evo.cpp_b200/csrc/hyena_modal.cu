@@ -142,13 +142,27 @@ modal_stream_kernel(const ModalParams p) {
 #pragma unroll
         for (int m = 0; m < kModes; ++m)
           decay[c][m] = expf(p.log_poles[mine + c * kModes + m] * static_cast<float>(p.segment));
-      for (int j = 0; j < seg; ++j) {
-        const float *const local = p.scratch + j * per_segment + mine;
+      // The chain over segments is serial, its loads are not: four segments' end states are
+      // requested before the first dependent FMA, so the fold costs seg / 4 round trips to L2.
+      constexpr int kAhead = 4;
+      for (int j0 = 0; j0 < seg; j0 += kAhead) {
+        float local[kAhead][kC * kModes];
 #pragma unroll
-        for (int c = 0; c < kC; ++c)
+        for (int i = 0; i < kAhead; ++i) {
+          const float *const source = p.scratch + (j0 + i) * per_segment + mine;
 #pragma unroll
-          for (int m = 0; m < kModes; ++m)
-            state[c][m] = fmaf(decay[c][m], state[c][m], __ldcg(local + c * kModes + m));
+          for (int q = 0; q < kC * kModes; ++q) local[i][q] = j0 + i < seg ? __ldcg(source + q) : 0.0F;
+        }
+#pragma unroll
+        for (int i = 0; i < kAhead; ++i) {
+          if (j0 + i < seg) {
+#pragma unroll
+            for (int c = 0; c < kC; ++c)
+#pragma unroll
+              for (int m = 0; m < kModes; ++m)
+                state[c][m] = fmaf(decay[c][m], state[c][m], local[i][c * kModes + m]);
+          }
+        }
       }
     }
   } else {
