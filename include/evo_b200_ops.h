@@ -66,11 +66,13 @@ EVO_B200_API int evo_b200_bf16_linear(const void *input, const void *weight,
                                       size_t out_features, int bias_mode,
                                       int path, void *output, void *stream);
 /* The same projection with scratch for split-K (no upstream counterpart:
- * cuBLASLt owns its workspace there).  At 9..32 rows a projection is a weight
- * stream with fewer output tiles than SMs; with a workspace the K dimension is
- * split over up to 8 CTAs per tile, F32 partial sums go to the workspace
- * (split * rows * out_features floats are needed, less is fine: fewer or no
- * splits) and are added in split order.  gate_mode 0 none, 1 / 2 = the gated
+ * cuBLASLt owns its workspace there).  At 9..128 rows a projection is a weight
+ * stream with fewer output tiles than SMs; with a workspace the weights become
+ * the 128-row tensor-core operand and the tokens the narrow one, the K
+ * dimension is split over up to 8 CTAs per 128 weight rows, F32 partial sums
+ * go to the workspace (split * rows * out_features floats are needed, less is
+ * fine: fewer splits, or the one-pass kernel when not even one fits) and are
+ * added in split order.  gate_mode 0 none, 1 / 2 = the gated
  * up-projection of evo_b200_bf16_gated_up_projection (identity / GELU) with
  * out_features = 2 * inner width.  The workspace must not be shared by calls
  * that may overlap on the GPU. */
