@@ -271,3 +271,24 @@ def test_variant_window_properties(evo):
         left, right = offset, end - (start + len(ref))
         if left < (maximum - core) // 2:
             assert begin == 0 or right == length - (start + len(ref))
+
+
+def test_modal_scratch_size_is_monotonic_and_bounded(pkg):
+    """The HCL scratch holds one state per row segment of the one-wave grid plus the carried-in
+    slot: it grows with the length until the grid is full, never shrinks (a buffer sized for a
+    prompt serves every window of it), and stays far below one state per 64 rows for long prompts."""
+    lib = ctypes.CDLL(str(pkg.OPS_LIBRARY))
+    fn = lib.evo_b200_hcl_scratch_floats
+    fn.restype = ctypes.c_size_t
+    fn.argtypes = [ctypes.c_size_t] * 3
+    for width, modes in ((4096, 16), (8192, 16), (96, 16), (64, 2)):
+        previous = 0
+        for length in (0, 1, 63, 64, 65, 128, 1000, 8192, 8336, 131072, 1 << 20):
+            floats = fn(length, width, modes)
+            assert floats >= previous, (width, length)
+            previous = floats
+            if length:
+                assert floats >= 3 * width * modes                     # at least one segment and the slot
+                assert floats <= (length // 64 + 3) * width * modes    # never more than a state per 64 rows
+        assert fn(1 << 20, width, modes) == fn(131072, width, modes)   # bounded by the grid, not by the length
+    assert fn(1 << 20, 4096, 16) * 4 <= 16 << 20                      # 7B shape: below the 16 MiB static array
