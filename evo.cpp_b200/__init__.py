@@ -38,7 +38,7 @@ OPS_SIGNATURES: dict[str, list] = {
     "evo_b200_bf16_add": [_P, _P, _Z, _P, _P],
     "evo_b200_bf16_add_bias_inplace": [_P, _P, _Z, _Z, _P],
     "evo_b200_bf16_row_to_column_major": [_P, _Z, _Z, _P, _P],
-    "evo_b200_embedding": [_P, _P, _Z, _Z, _P, _P],
+    "evo_b200_embedding": [_P, _P, _Z, _Z, _Z, _P, _P],
     "evo_b200_bf16_split_hyena_projection": [_P, _Z, _Z, _P, _P, _P, _P],
     "evo_b200_bf16_fir_prefill_direct": [_P, _P, _I, _P, _Z, _Z, _Z, _Z, _I, _I, _P, _P, _P],
     "evo_b200_bf16_fir_continue_direct": [_P, _P, _I, _P, _Z, _Z, _Z, _Z, _I, _I, _P, _Z, _P, _P],
@@ -57,10 +57,12 @@ OPS_SIGNATURES: dict[str, list] = {
     "evo_b200_bf16_cached_cross_attention": [_P, _P, _P, _Z, _Z, _Z, _Z, _P, _P],
     "evo_b200_linear_executor_create": [_I, ctypes.POINTER(_P)],
     "evo_b200_linear_executor_linear": [_P, _P, _Z, _Z, _P, _I, _Z, _Z, _P, _I, _Z, _P],
+    "evo_b200_e4m3_encode_array": [_P, _Z, _F, _P],
 }
 # entry points that do not return a status
 OPS_OTHER = ("evo_b200_last_error", "evo_b200_hcl_scratch_floats", "evo_b200_linear_executor_free",
-             "evo_b200_linear_executor_name", "evo_b200_linear_executor_cached_bytes")
+             "evo_b200_linear_executor_name", "evo_b200_linear_executor_cached_bytes",
+             "evo_b200_e4m3_encode", "evo_b200_e4m3_decode", "evo_b200_e4m3_scaled_roundtrip")
 
 
 class OpsError(RuntimeError):
@@ -86,6 +88,12 @@ class Ops:
         self.lib.evo_b200_linear_executor_name.restype = ctypes.c_char_p
         self.lib.evo_b200_linear_executor_cached_bytes.restype = _Z
         self.lib.evo_b200_linear_executor_cached_bytes.argtypes = [_P]
+        self.lib.evo_b200_e4m3_encode.restype = ctypes.c_uint8
+        self.lib.evo_b200_e4m3_encode.argtypes = [_F]
+        self.lib.evo_b200_e4m3_decode.restype = _F
+        self.lib.evo_b200_e4m3_decode.argtypes = [ctypes.c_uint8]
+        self.lib.evo_b200_e4m3_scaled_roundtrip.restype = _F
+        self.lib.evo_b200_e4m3_scaled_roundtrip.argtypes = [_F, _F]
         for name, argtypes in OPS_SIGNATURES.items():
             fn = getattr(self.lib, name)
             fn.restype = _I

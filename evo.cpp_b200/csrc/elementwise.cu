@@ -375,18 +375,29 @@ __global__ void add_bias_kernel(bf16 *__restrict__ output,
     output[i] = f2bf(bf2f(output[i]) + bf2f(bias[i % width]));
 }
 
+// An id outside the table is never used as an index: its row is written as
+// zeros and bit 1 of the per-device error word is raised, which the next
+// gemm_error_state() reports as an invalid argument.
 __global__ void embedding_kernel(const std::uint32_t *__restrict__ tokens,
                                  const bf16 *__restrict__ table,
                                  bf16 *__restrict__ output,
                                  const std::size_t rows,
-                                 const std::size_t width) {
+                                 const std::size_t width,
+                                 const std::size_t vocabulary,
+                                 int *const error_word) {
   const std::size_t elements = rows * width;
   const std::size_t stride = static_cast<std::size_t>(blockDim.x) * gridDim.x;
   for (std::size_t i = static_cast<std::size_t>(blockIdx.x) * blockDim.x +
                        threadIdx.x;
        i < elements; i += stride) {
     const std::size_t row = i / width;
-    output[i] = table[static_cast<std::size_t>(tokens[row]) * width + i % width];
+    const std::size_t id = tokens[row];
+    if (id < vocabulary) {
+      output[i] = table[id * width + i % width];
+    } else {
+      output[i] = __ushort_as_bfloat16(0);
+      if (i % width == 0) atomicOr(error_word, 2);
+    }
   }
 }
 
@@ -553,14 +564,18 @@ int add_bias(void *output, const void *bias, const std::size_t rows,
 }
 
 int embedding(const std::uint32_t *tokens, const void *table,
-              const std::size_t rows, const std::size_t width, void *output,
-              cudaStream_t stream) {
-  if (tokens == nullptr || table == nullptr || output == nullptr || width == 0)
+              const std::size_t rows, const std::size_t width,
+              const std::size_t vocabulary, void *output, cudaStream_t stream) {
+  if (tokens == nullptr || table == nullptr || output == nullptr || width == 0 ||
+      vocabulary == 0)
     return fail(kInvalidArgument, "embedding arguments are invalid");
   if (rows == 0) return kOk;
+  int status = kOk;
+  int *const error_word = device_error_word(&status);
+  if (error_word == nullptr) return status;
   embedding_kernel<<<grid_for(rows * width), kThreads, 0, stream>>>(
       tokens, static_cast<const bf16 *>(table), static_cast<bf16 *>(output),
-      rows, width);
+      rows, width, vocabulary, error_word);
   return check_launch("embedding kernel");
 }
 

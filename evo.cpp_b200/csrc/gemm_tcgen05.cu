@@ -364,7 +364,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
     // memory of this CTA is recycled, then report.
     const unsigned long long start = global_timer_ns();
     while (global_timer_ns() - start < 200000ULL) __nanosleep(1000);
-    if (threadIdx.x == 0) atomicExch(error_word, 1);
+    if (threadIdx.x == 0) atomicOr(error_word, 1);
   }
   if (warp == 1) {
     tc_fence_after();
@@ -519,7 +519,7 @@ gemm_swap_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
   if (*abort_flag != 0) {
     const unsigned long long start = global_timer_ns();
     while (global_timer_ns() - start < 200000ULL) __nanosleep(1000);
-    if (threadIdx.x == 0) atomicExch(error_word, 1);
+    if (threadIdx.x == 0) atomicOr(error_word, 1);
   }
   if (warp == 1) {
     tc_fence_after();
@@ -792,10 +792,13 @@ int gemm_error_state(cudaStream_t stream) {
     return fail(kCuda, "cannot read the GEMM error word");
   if (value != 0) {
     cudaMemsetAsync(state->error_word, 0, sizeof(int), stream);
-    return fail(kCuda, "a tcgen05 GEMM pipeline wait timed out");
+    if ((value & 1) != 0) return fail(kCuda, "a tcgen05 GEMM pipeline wait timed out");
+    return fail(kInvalidArgument, "token ID exceeds model vocabulary");
   }
   return kOk;
 }
+
+int *device_error_word(int *status) { return tc::error_word(status, nullptr); }
 
 int linear(const LinearArgs &args, cudaStream_t stream) {
   const bool fp8 = args.operand_type == OperandType::kE4m3;

@@ -13,8 +13,9 @@
 // after the post-gate.  Taps are accumulated oldest-input-first with FMA, the
 // order of upstream's direct kernel.
 //
-// fir_prefill / fir_step are the unfused operators with upstream's exact
-// decode/continue reduction tree (src/cuda/hyena.cu:275-416).
+// fir_prefill / fir_step are the unfused operators (sliding register window
+// per channel; warp per output with upstream's pinned decode/continue
+// reduction tree as a shuffle fold, src/cuda/hyena.cu:275-416).
 #include "common.cuh"
 #include "ops_internal.hpp"
 
@@ -220,147 +221,159 @@ gated_fir_kernel(const FusedParams p) {
 }
 
 // -------------------------------------------------------------- unfused
-__global__ void fill_cache_kernel(const bf16 *__restrict__ input,
-                                  float *__restrict__ cache,
-                                  const std::size_t length,
-                                  const std::size_t channels,
-                                  const std::size_t cache_size) {
-  const std::size_t elements = channels * cache_size;
-  const std::size_t valid = length < cache_size ? length : cache_size;
-  const std::size_t leading = cache_size - valid;
-  const std::size_t stride = static_cast<std::size_t>(blockDim.x) * gridDim.x;
-  for (std::size_t i = static_cast<std::size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
-       i < elements; i += stride) {
-    const std::size_t channel = i / cache_size;
-    const std::size_t slot = i % cache_size;
-    cache[i] = slot < leading
-                   ? 0.0F
-                   : bf2f(input[(length - valid + slot - leading) * channels + channel]);
+// History cache of a depthwise FIR: per channel the last cache_size inputs in
+// chronological order, left-padded with zeros.  A warp owns a channel, reads
+// the row it is about to shift into registers (lane L holds slots L, 32+L, ...),
+// and writes slot s from slot s+length of the old row or, past its end, from
+// the new rows - so a fill after a prefill (`fresh`: the old row counts as
+// zeros) and an advance after a continuation chunk are the same kernel.
+constexpr int kHistorySlotsPerLane = 8;  // cache_size <= 256
+
+__global__ void __launch_bounds__(kThreads)
+history_update_kernel(const bf16 *__restrict__ input, float *__restrict__ cache, const int length,
+                      const int channels, const int cache_size, const bool fresh) {
+  const int channel = (blockIdx.x * kThreads + threadIdx.x) / 32;
+  const int lane = threadIdx.x % 32;
+  if (channel >= channels) return;
+  float *const row = cache + static_cast<std::size_t>(channel) * cache_size;
+  float moved[kHistorySlotsPerLane];
+#pragma unroll
+  for (int k = 0; k < kHistorySlotsPerLane; ++k) {
+    const int slot = 32 * k + lane;
+    const long source = static_cast<long>(slot) + length;
+    moved[k] = 0.0F;
+    if (slot >= cache_size) continue;
+    if (source < cache_size) {
+      if (!fresh) moved[k] = row[source];
+    } else {
+      moved[k] = bf2f(input[static_cast<std::size_t>(source - cache_size) * channels + channel]);
+    }
+  }
+  __syncwarp();  // all old slots are in registers before any is overwritten
+#pragma unroll
+  for (int k = 0; k < kHistorySlotsPerLane; ++k) {
+    const int slot = 32 * k + lane;
+    if (slot < cache_size) row[slot] = moved[k];
   }
 }
 
-__global__ void fir_prefill_kernel(const bf16 *__restrict__ input,
-                                   const void *__restrict__ filter,
-                                   const bool filter_is_f32,
-                                   const bf16 *__restrict__ bias,
-                                   const bool multiply_bias,
-                                   bf16 *__restrict__ output,
-                                   const std::size_t length,
-                                   const std::size_t channels,
-                                   const std::size_t channels_per_group,
-                                   const std::size_t taps,
-                                   const bool cross_correlation) {
-  const std::size_t elements = length * channels;
-  const std::size_t stride = static_cast<std::size_t>(blockDim.x) * gridDim.x;
-  for (std::size_t i = static_cast<std::size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
-       i < elements; i += stride) {
-    const std::size_t time = i / channels;
-    const std::size_t channel = i % channels;
-    const std::size_t group = channel / channels_per_group;
-    float total = 0.0F;
-    for (std::size_t tap = 0; tap < taps; ++tap) {
-      const std::size_t delay = cross_correlation ? taps - 1 - tap : tap;
-      if (time >= delay)
-        total = fmaf(bf2f(input[(time - delay) * channels + channel]),
-                     load_filter(filter, filter_is_f32, group * taps + tap), total);
+// Unfused prefill FIR.  A thread owns one channel and a run of kRows
+// consecutive outputs; the taps are the outer loop, and the kRows inputs that
+// meet tap j are a register window that slides by one row from tap to tap (one
+// new load per tap instead of kRows).  Each output still accumulates its taps
+// in index order 0..taps-1 with one FMA per tap and skips the taps that reach
+// before the sequence start, which is the summation upstream's direct kernel
+// defines (src/cuda/hyena.cu:243-272).
+constexpr int kRows = 8;
+
+template <bool kCross>
+__global__ void __launch_bounds__(kThreads)
+fir_run_kernel(const bf16 *__restrict__ input, const void *__restrict__ filter, const bool filter_is_f32,
+               const bf16 *__restrict__ bias, const bool multiply_bias, bf16 *__restrict__ output,
+               const std::size_t length, const std::size_t channels, const std::size_t channels_per_group,
+               const int taps) {
+  const std::size_t runs = (length + kRows - 1) / kRows;
+  const std::size_t item = static_cast<std::size_t>(blockIdx.x) * kThreads + threadIdx.x;
+  if (item >= runs * channels) return;
+  const std::size_t channel = item % channels;
+  const long first = static_cast<long>(item / channels) * kRows;
+  const std::size_t group = channel / channels_per_group;
+  const auto sample = [&](const long row) -> float {
+    return row >= 0 && row < static_cast<long>(length) ? bf2f(input[static_cast<std::size_t>(row) * channels + channel])
+                                                       : 0.0F;
+  };
+  // delay of tap j: taps-1-j (cross-correlation) or j (convolution)
+  int delay = kCross ? taps - 1 : 0;
+  float window[kRows], total[kRows];
+#pragma unroll
+  for (int r = 0; r < kRows; ++r) {
+    window[r] = sample(first + r - delay);
+    total[r] = 0.0F;
+  }
+  for (int tap = 0; tap < taps; ++tap) {
+    const float weight = load_filter(filter, filter_is_f32, group * taps + tap);
+#pragma unroll
+    for (int r = 0; r < kRows; ++r)
+      if (first + r >= delay) total[r] = fmaf(window[r], weight, total[r]);
+    if (tap + 1 == taps) break;
+    if constexpr (kCross) {
+      --delay;
+#pragma unroll
+      for (int r = 0; r + 1 < kRows; ++r) window[r] = window[r + 1];
+      window[kRows - 1] = sample(first + kRows - 1 - delay);
+    } else {
+      ++delay;
+#pragma unroll
+      for (int r = kRows - 1; r > 0; --r) window[r] = window[r - 1];
+      window[0] = sample(first - delay);
     }
+  }
+#pragma unroll
+  for (int r = 0; r < kRows; ++r) {
+    const long row = first + r;
+    if (row >= static_cast<long>(length)) break;
+    const std::size_t at = static_cast<std::size_t>(row) * channels + channel;
+    float value = total[r];
     if (bias != nullptr) {
       const float b = bf2f(bias[channel]);
-      total = multiply_bias ? fmaf(b, bf2f(input[i]), total) : total + b;
+      value = multiply_bias ? fmaf(b, bf2f(input[at]), value) : value + b;
     }
-    output[i] = f2bf(total);
+    output[at] = f2bf(value);
   }
 }
 
-// Continuation / decode step against the F32 history cache.  Products are
-// rounded separately and summed into 32 strided lanes, then folded by a
-// 16/8/4/2/1 tree - the reduction upstream pins (src/cuda/hyena.cu:275-330).
-__global__ void fir_step_kernel(const bf16 *__restrict__ input,
-                                const void *__restrict__ filter,
-                                const bool filter_is_f32,
-                                const bf16 *__restrict__ bias,
-                                const bool multiply_bias,
-                                const float *__restrict__ cache,
-                                bf16 *__restrict__ output,
-                                const std::size_t length,
-                                const std::size_t channels,
-                                const std::size_t channels_per_group,
-                                const std::size_t taps,
-                                const std::size_t cached,
-                                const bool cross_correlation) {
-  const std::size_t elements = length * channels;
-  const std::size_t cache_size = taps - 1;
-  const std::size_t stride = static_cast<std::size_t>(blockDim.x) * gridDim.x;
-  for (std::size_t i = static_cast<std::size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
-       i < elements; i += stride) {
-    const std::size_t time = i / channels;
-    const std::size_t channel = i % channels;
-    const std::size_t group = channel / channels_per_group;
-    const std::size_t total_history = cached + time;
-    const std::size_t active = total_history < cache_size ? total_history : cache_size;
-    const std::size_t begin = total_history - active;
-    float terms[32];
-#pragma unroll
-    for (int lane = 0; lane < 32; ++lane) terms[lane] = 0.0F;
-    for (std::size_t a0 = 0; a0 < active; a0 += 32) {
-#pragma unroll
-      for (int lane = 0; lane < 32; ++lane) {
-        const std::size_t a = a0 + lane;
-        if (a < active) {
-          const std::size_t history = begin + a;
-          const float source =
-              history < cached
-                  ? cache[channel * cache_size + cache_size - cached + history]
-                  : bf2f(input[(history - cached) * channels + channel]);
-          const std::size_t tap = cross_correlation ? a : active - a;
-          terms[lane] = __fadd_rn(
-              terms[lane],
-              __fmul_rn(source, load_filter(filter, filter_is_f32, group * taps + tap)));
-        }
-      }
-    }
-#pragma unroll
-    for (int offset = 16; offset != 0; offset /= 2)
-#pragma unroll
-      for (int lane = 0; lane < offset; ++lane)
-        terms[lane] = __fadd_rn(terms[lane], terms[lane + offset]);
-    const float current = bf2f(input[i]);
-    const std::size_t current_tap = cross_correlation ? active : 0;
-    float total = __fadd_rn(
-        __fmul_rn(current, load_filter(filter, filter_is_f32, group * taps + current_tap)),
-        terms[0]);
-    if (bias != nullptr) {
-      const float b = bf2f(bias[channel]);
-      total = __fadd_rn(total, multiply_bias ? __fmul_rn(b, current) : b);
-    }
-    output[i] = f2bf(total);
+// Continuation rows against the F32 history cache with the reduction upstream
+// pins for its cached FIR (src/cuda/hyena.cu:275-330): every product rounded by
+// itself, history entry a added into slot a % 32 in ascending a, the 32 slots
+// folded 16/8/4/2/1, then the current sample's product, then the bias term.  A
+// warp owns one (row, channel) output and a lane is a slot, so the slots are
+// the lanes' private sums and the fold is five shuffles.  History entries come
+// from the cache while they predate this chunk and from the chunk's own earlier
+// rows after that.
+__global__ void __launch_bounds__(kThreads)
+fir_rows_warp_kernel(const bf16 *__restrict__ input, const void *__restrict__ filter, const bool filter_is_f32,
+                     const bf16 *__restrict__ bias, const bool multiply_bias, const float *__restrict__ cache,
+                     bf16 *__restrict__ output, const std::size_t length, const std::size_t channels,
+                     const std::size_t channels_per_group, const int taps, const int cached,
+                     const bool cross_correlation) {
+  const std::size_t item = (static_cast<std::size_t>(blockIdx.x) * kThreads + threadIdx.x) / 32;
+  const int lane = threadIdx.x % 32;
+  if (item >= length * channels) return;
+  const std::size_t channel = item % channels;
+  const long row = static_cast<long>(item / channels);
+  const std::size_t group = channel / channels_per_group;
+  const int cache_size = taps - 1;
+  const long seen = cached + row;                       // inputs before this row
+  const int active = static_cast<int>(seen < cache_size ? seen : cache_size);
+  const long oldest = seen - active;                    // index of history entry 0 among the seen inputs
+  float slot = 0.0F;
+  for (int a = lane; a < active; a += 32) {
+    const long index = oldest + a;
+    const float source = index < cached
+                             ? cache[channel * cache_size + (cache_size - cached) + index]
+                             : bf2f(input[static_cast<std::size_t>(index - cached) * channels + channel]);
+    const int tap = cross_correlation ? a : active - a;
+    slot = __fadd_rn(slot, __fmul_rn(source, load_filter(filter, filter_is_f32, group * taps + tap)));
   }
-}
-
-__global__ void advance_cache_kernel(const bf16 *__restrict__ input,
-                                     float *__restrict__ cache,
-                                     const std::size_t length,
-                                     const std::size_t channels,
-                                     const std::size_t cache_size) {
-  const std::size_t stride = static_cast<std::size_t>(blockDim.x) * gridDim.x;
-  for (std::size_t channel = static_cast<std::size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
-       channel < channels; channel += stride) {
-    float *const row = cache + channel * cache_size;
-    if (length >= cache_size) {
-      for (std::size_t s = 0; s < cache_size; ++s)
-        row[s] = bf2f(input[(length - cache_size + s) * channels + channel]);
-      continue;
-    }
-    const std::size_t retained = cache_size - length;
-    for (std::size_t s = 0; s < retained; ++s) row[s] = row[s + length];
-    for (std::size_t t = 0; t < length; ++t)
-      row[retained + t] = bf2f(input[t * channels + channel]);
+#pragma unroll
+  for (int offset = 16; offset != 0; offset /= 2) {
+    const float other = __shfl_down_sync(0xffffffffU, slot, offset);
+    if (lane < offset) slot = __fadd_rn(slot, other);
   }
+  if (lane != 0) return;
+  const float current = bf2f(input[item]);
+  const int current_tap = cross_correlation ? active : 0;
+  float total = __fadd_rn(__fmul_rn(current, load_filter(filter, filter_is_f32, group * taps + current_tap)), slot);
+  if (bias != nullptr) {
+    const float b = bf2f(bias[channel]);
+    total = __fadd_rn(total, multiply_bias ? __fmul_rn(b, current) : b);
+  }
+  output[item] = f2bf(total);
 }
 
 // Single-step form (cached decode) for long filters with a full history: one
 // warp per channel.  Lane L owns history entries L, 32+L, 64+L, ... - exactly
-// the terms[] slots of fir_step_kernel - and the 32-slot tree is folded with
+// the slots of fir_rows_warp_kernel - and the 32-slot tree is folded with
 // shuffles in the same order, so the result is bit-identical; the history row
 // is read once, coalesced, and written back shifted by one with the new sample
 // appended, which replaces the separate cache-advance launch.
@@ -410,12 +423,6 @@ fir_decode_warp_kernel(const bf16 *__restrict__ input, const void *__restrict__ 
     }
     output[channel] = f2bf(total);
   }
-}
-
-unsigned int flat_grid(const std::size_t items) {
-  const std::size_t blocks = (items + kThreads - 1) / kThreads;
-  const std::size_t cap = static_cast<std::size_t>(kSmCount) * 16;
-  return static_cast<unsigned int>(blocks < 1 ? 1 : (blocks > cap ? cap : blocks));
 }
 
 }  // namespace
@@ -472,12 +479,21 @@ int gated_fir_prefill_generic(const GatedFirArgs &a, cudaStream_t stream) {
   kernel<<<grid, kThreads, smem, stream>>>(p);
   int status = check_launch("gated FIR kernel");
   if (status != kOk) return status;
-  if (a.short_cache != nullptr && from_projection && a.short_taps > 1) {
-    fill_cache_kernel<<<flat_grid(a.width * 3 * (a.short_taps - 1)), kThreads, 0, stream>>>(
-        p.projection, a.short_cache, a.length, a.width * 3, a.short_taps - 1);
-    status = check_launch("short FIR cache fill kernel");
-  }
+  if (a.short_cache != nullptr && from_projection && a.short_taps > 1)
+    status = fill_fir_cache(p.projection, a.short_cache, a.length, a.width * 3, a.short_taps - 1, stream);
   return status;
+}
+
+// fresh: the cache holds nothing yet (fill after a prefill); otherwise it is
+// shifted by `length` and the new rows are appended.
+static int update_history(const void *input, float *cache, const std::size_t length, const std::size_t channels,
+                          const std::size_t cache_size, const bool fresh, cudaStream_t stream) {
+  if (cache_size > 32 * kHistorySlotsPerLane || channels > 0x3ffffffU || length > 0x7fffff00U)
+    return fail(kInvalidArgument, "FIR history is longer than 256 entries or the tensor is too large");
+  history_update_kernel<<<ceil_div_u(channels * 32, kThreads), kThreads, 0, stream>>>(
+      static_cast<const bf16 *>(input), cache, static_cast<int>(length), static_cast<int>(channels),
+      static_cast<int>(cache_size), fresh);
+  return check_launch("FIR history kernel");
 }
 
 int fill_fir_cache(const void *input, float *cache, const std::size_t length,
@@ -486,9 +502,7 @@ int fill_fir_cache(const void *input, float *cache, const std::size_t length,
   if (input == nullptr || cache == nullptr || channels == 0)
     return fail(kInvalidArgument, "FIR cache fill arguments are invalid");
   if (cache_size == 0) return kOk;
-  fill_cache_kernel<<<flat_grid(channels * cache_size), kThreads, 0, stream>>>(
-      static_cast<const bf16 *>(input), cache, length, channels, cache_size);
-  return check_launch("FIR cache fill kernel");
+  return update_history(input, cache, length, channels, cache_size, true, stream);
 }
 
 int fir_prefill(const void *input, const void *filter, const bool filter_is_f32,
@@ -500,20 +514,18 @@ int fir_prefill(const void *input, const void *filter, const bool filter_is_f32,
   if (input == nullptr || filter == nullptr || output == nullptr ||
       channels == 0 || groups == 0 || taps == 0 || channels % groups != 0)
     return fail(kInvalidArgument, "FIR prefill arguments are invalid");
+  if (taps > 0x7fffffffU) return fail(kInvalidArgument, "FIR prefill arguments are invalid");
   if (length != 0) {
-    fir_prefill_kernel<<<flat_grid(length * channels), kThreads, 0, stream>>>(
-        static_cast<const bf16 *>(input), filter, filter_is_f32,
-        static_cast<const bf16 *>(bias), multiply_bias,
-        static_cast<bf16 *>(output), length, channels, channels / groups, taps,
-        cross_correlation);
+    const std::size_t items = (length + kRows - 1) / kRows * channels;
+    if ((items + kThreads - 1) / kThreads > 0x7fffffffU) return fail(kInvalidArgument, "FIR prefill is too large");
+    auto *const kernel = cross_correlation ? fir_run_kernel<true> : fir_run_kernel<false>;
+    kernel<<<ceil_div_u(items, kThreads), kThreads, 0, stream>>>(
+        static_cast<const bf16 *>(input), filter, filter_is_f32, static_cast<const bf16 *>(bias), multiply_bias,
+        static_cast<bf16 *>(output), length, channels, channels / groups, static_cast<int>(taps));
     const int status = check_launch("FIR prefill kernel");
     if (status != kOk) return status;
   }
-  if (cache != nullptr && taps > 1) {
-    fill_cache_kernel<<<flat_grid(channels * (taps - 1)), kThreads, 0, stream>>>(
-        static_cast<const bf16 *>(input), cache, length, channels, taps - 1);
-    return check_launch("FIR cache fill kernel");
-  }
+  if (cache != nullptr && taps > 1) return update_history(input, cache, length, channels, taps - 1, true, stream);
   return kOk;
 }
 
@@ -535,16 +547,15 @@ int fir_step(const void *input, const void *filter, const bool filter_is_f32,
         static_cast<int>(channels / groups), static_cast<int>(taps), cross_correlation);
     return check_launch("FIR decode kernel");
   }
-  fir_step_kernel<<<flat_grid(length * channels), kThreads, 0, stream>>>(
-      static_cast<const bf16 *>(input), filter, filter_is_f32,
-      static_cast<const bf16 *>(bias), multiply_bias, cache,
-      static_cast<bf16 *>(output), length, channels, channels / groups, taps,
-      cache_length, cross_correlation);
-  int status = check_launch("FIR step kernel");
+  const std::size_t warps = length * channels;
+  if (warps > 0x3ffffffU || taps > 0x7fffffffU) return fail(kInvalidArgument, "FIR step is too large");
+  fir_rows_warp_kernel<<<ceil_div_u(warps * 32, kThreads), kThreads, 0, stream>>>(
+      static_cast<const bf16 *>(input), filter, filter_is_f32, static_cast<const bf16 *>(bias), multiply_bias,
+      cache, static_cast<bf16 *>(output), length, channels, channels / groups, static_cast<int>(taps),
+      static_cast<int>(cache_length), cross_correlation);
+  const int status = check_launch("FIR step kernel");
   if (status != kOk) return status;
-  advance_cache_kernel<<<flat_grid(channels), kThreads, 0, stream>>>(
-      static_cast<const bf16 *>(input), cache, length, channels, taps - 1);
-  return check_launch("FIR cache advance kernel");
+  return update_history(input, cache, length, channels, taps - 1, false, stream);
 }
 
 }  // namespace evob

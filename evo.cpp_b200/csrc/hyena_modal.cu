@@ -41,42 +41,79 @@ struct ModalParams {
   bool continue_from_state;
 };
 
-__global__ void modal_decode_kernel(const bf16 *__restrict__ x2,
-                                    const bf16 *__restrict__ x1,
-                                    const bf16 *__restrict__ value,
-                                    const bf16 *__restrict__ direct,
-                                    const float *__restrict__ log_poles,
-                                    const float *__restrict__ residues,
-                                    float *__restrict__ state,
-                                    bf16 *__restrict__ pregate,
-                                    bf16 *__restrict__ output, const int width,
-                                    const int modes) {
-  const int channel = blockIdx.x * blockDim.x + threadIdx.x;
+// One decode step of the modal recurrence.  A warp owns a channel and lane m
+// its mode m: the state update is a separate multiply and add, the read-out
+// terms R_m s_m sit in lanes 0..modes-1 of a zero-padded 32-lane shuffle-down
+// fold - upstream's pinned order (src/cuda/hyena.cu:718-761) is literally a
+// warp reduction, so the lanes are the reduction slots.
+constexpr int kDecodeThreads = 256;
+
+__global__ void __launch_bounds__(kDecodeThreads)
+modal_decode_warp_kernel(const bf16 *__restrict__ x2, const bf16 *__restrict__ x1, const bf16 *__restrict__ value,
+                         const bf16 *__restrict__ direct, const float *__restrict__ log_poles,
+                         const float *__restrict__ residues, float *__restrict__ state, bf16 *__restrict__ pregate,
+                         bf16 *__restrict__ output, const int width, const int modes) {
+  const int channel = (blockIdx.x * kDecodeThreads + threadIdx.x) / 32;
+  const int lane = threadIdx.x % 32;
   if (channel >= width) return;
-  const bf16 gated_bf16 = f2bf(bf2f(x1[channel]) * bf2f(value[channel]));
-  if (pregate != nullptr) pregate[channel] = gated_bf16;
-  const float gated = bf2f(gated_bf16);
-  float terms[32];
-#pragma unroll
-  for (int lane = 0; lane < 32; ++lane) terms[lane] = 0.0F;
-#pragma unroll
-  for (int mode = 0; mode < 32; ++mode) {
-    if (mode < modes) {
-      const std::size_t q = static_cast<std::size_t>(channel) * modes + mode;
-      const float updated =
-          __fadd_rn(__fmul_rn(expf(log_poles[q]), state[q]), gated);
-      state[q] = updated;
-      terms[mode] = __fmul_rn(residues[q], updated);
-    }
+  const float gated = rbf(bf2f(x1[channel]) * bf2f(value[channel]));
+  float term = 0.0F;
+  if (lane < modes) {
+    const std::size_t q = static_cast<std::size_t>(channel) * modes + lane;
+    const float updated = __fadd_rn(__fmul_rn(expf(log_poles[q]), state[q]), gated);
+    state[q] = updated;
+    term = __fmul_rn(residues[q], updated);
   }
 #pragma unroll
-  for (int offset = 16; offset != 0; offset /= 2)
-#pragma unroll
-    for (int lane = 0; lane < 32; ++lane)
-      if (lane < 32 - offset) terms[lane] = __fadd_rn(terms[lane], terms[lane + offset]);
+  for (int offset = 16; offset != 0; offset /= 2) {
+    const float other = __shfl_down_sync(0xffffffffU, term, offset);
+    if (lane < 32 - offset) term = __fadd_rn(term, other);
+  }
+  if (lane != 0) return;
+  if (pregate != nullptr) pregate[channel] = f2bf(gated);
   const float direct_product = rbf(bf2f(direct[channel]) * gated);
-  const float mixed = __fadd_rn(terms[0], direct_product);
-  output[channel] = f2bf(__fmul_rn(bf2f(x2[channel]), mixed));
+  output[channel] = f2bf(__fmul_rn(bf2f(x2[channel]), __fadd_rn(term, direct_product)));
+}
+
+// Diagnostic taps of the long-implicit operator (upstream's kMixerFilter and
+// kMixerConvolution dump points, src/cuda/model.cu:1570-1581): the time-domain
+// filter h[t, c] with upstream's four-accumulator mode sum
+// (src/cuda/hyena.cu:562-592) and the F32 convolution y[t, c] = sum_s h[t-s] u[s]
+// before any rounding, evaluated as the modal recurrence from a zero state.
+// Thread = channel, walking time; neighbouring threads write neighbouring
+// columns of the [length, width] outputs.
+__global__ void modal_taps_kernel(const bf16 *__restrict__ gated, const float *__restrict__ log_poles,
+                                  const float *__restrict__ residues, float *__restrict__ filter,
+                                  float *__restrict__ convolution, const int length, const int width,
+                                  const int modes) {
+  const int channel = blockIdx.x * blockDim.x + threadIdx.x;
+  if (channel >= width) return;
+  const float *const lp = log_poles + static_cast<std::size_t>(channel) * modes;
+  const float *const res = residues + static_cast<std::size_t>(channel) * modes;
+  float state[32];
+#pragma unroll
+  for (int m = 0; m < 32; ++m) state[m] = 0.0F;
+  for (int t = 0; t < length; ++t) {
+    const std::size_t at = static_cast<std::size_t>(t) * width + channel;
+    if (filter != nullptr) {
+      float partial[4] = {0.0F, 0.0F, 0.0F, 0.0F};
+      for (int m = 0; m < modes; ++m)
+        partial[m % 4] = __fadd_rn(partial[m % 4], __fmul_rn(res[m], expf(lp[m] * static_cast<float>(t))));
+      filter[at] = __fadd_rn(__fadd_rn(__fadd_rn(partial[0], partial[1]), partial[2]), partial[3]);
+    }
+    if (convolution != nullptr) {
+      const float u = bf2f(gated[at]);
+      float y = 0.0F;
+#pragma unroll
+      for (int m = 0; m < 32; ++m) {
+        if (m < modes) {
+          state[m] = fmaf(expf(lp[m]), state[m], u);
+          y = fmaf(res[m], state[m], y);
+        }
+      }
+      convolution[at] = y;
+    }
+  }
 }
 
 // -------------------------------------------------------- register streaming
@@ -541,13 +578,28 @@ int modal_decode(const void *x2, const void *x1, const void *value,
       log_poles == nullptr || residues == nullptr || state == nullptr ||
       output == nullptr || width == 0 || modes == 0 || modes > 32)
     return fail(kInvalidArgument, "modal decode arguments are invalid");
-  modal_decode_kernel<<<ceil_div_u(width, 128), 128, 0, stream>>>(
+  if (width > 0x3ffffffU) return fail(kInvalidArgument, "modal decode is too wide");
+  modal_decode_warp_kernel<<<ceil_div_u(width * 32, kDecodeThreads), kDecodeThreads, 0, stream>>>(
       static_cast<const bf16 *>(x2), static_cast<const bf16 *>(x1),
       static_cast<const bf16 *>(value), static_cast<const bf16 *>(direct),
       log_poles, residues, state, static_cast<bf16 *>(pregate),
       static_cast<bf16 *>(output), static_cast<int>(width),
       static_cast<int>(modes));
   return check_launch("modal decode kernel");
+}
+
+int modal_taps(const void *gated, const float *log_poles, const float *residues, const std::size_t length,
+               const std::size_t width, const std::size_t modes, float *filter, float *convolution,
+               cudaStream_t stream) {
+  if (log_poles == nullptr || residues == nullptr || (filter == nullptr && convolution == nullptr) ||
+      (convolution != nullptr && gated == nullptr) || width == 0 || modes == 0 || modes > 32 ||
+      length > 0x7fffffffU || width > 0x7fffffffU)
+    return fail(kInvalidArgument, "modal tap arguments are invalid");
+  if (length == 0) return kOk;
+  modal_taps_kernel<<<ceil_div_u(width, 64), 64, 0, stream>>>(static_cast<const bf16 *>(gated), log_poles, residues,
+                                                              filter, convolution, static_cast<int>(length),
+                                                              static_cast<int>(width), static_cast<int>(modes));
+  return check_launch("modal tap kernel");
 }
 
 }  // namespace evob

@@ -1,7 +1,7 @@
 // Dense-linear offload with upstream's LinearExecutor contract
 // (src/linear_executor.hpp:13-28): F32 host activations [rows, in], a host
-// weight view [out, in] row-major (F32 or BF16), optional bias, F32 host
-// output; the executor may keep device copies of weights keyed by their host
+// weight view [out, in] row-major (F32, BF16 or raw E4M3 codes), optional bias,
+// F32 host output; the executor may keep device copies of weights keyed by their host
 // address (upstream's Metal executor does, src/mps/model.mm:218-238), and
 // serialises calls internally.
 //
@@ -68,6 +68,28 @@ __global__ void pad_bf16_kernel(const bf16 *__restrict__ source, bf16 *__restric
   for (std::size_t i = static_cast<std::size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
     const std::size_t row = i / pitch, column = i % pitch;
     target[i] = column < width ? source[row * width + column] : f2bf(0.0F);
+  }
+}
+
+// E4M3 codes -> padded BF16 [rows, pitch].  Every finite E4M3 value is a BF16
+// value, so one plane holds the weight exactly (upstream's Metal executor
+// decodes the codes the same way, without a scale: src/mps/model.mm:42-58).
+__global__ void decode_e4m3_kernel(const std::uint8_t *__restrict__ source, bf16 *__restrict__ target,
+                                   const std::size_t rows, const std::size_t width, const std::size_t pitch) {
+  const std::size_t total = rows * pitch;
+  const std::size_t stride = static_cast<std::size_t>(blockDim.x) * gridDim.x;
+  for (std::size_t i = static_cast<std::size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
+    const std::size_t row = i / pitch, column = i % pitch;
+    float value = 0.0F;
+    if (column < width) {
+      const unsigned int code = source[row * width + column];
+      const unsigned int magnitude = code & 0x7fU, exponent = magnitude >> 3U, fraction = magnitude & 7U;
+      value = magnitude == 0x7fU ? __int_as_float(0x7fc00000)
+              : exponent == 0    ? static_cast<float>(fraction) * 0.001953125F
+                                 : ldexpf(static_cast<float>(8U + fraction), static_cast<int>(exponent) - 10);
+      if ((code & 0x80U) != 0) value = -value;
+    }
+    target[i] = f2bf(value);
   }
 }
 
@@ -144,7 +166,8 @@ std::size_t linear_executor_cached_bytes(LinearExecutorState *state) {
   return state->cached_bytes;
 }
 
-// dtype: 0 = F32, 1 = BF16 (upstream TensorDType kF32 / kBF16)
+// dtype: 0 = F32, 1 = BF16, 2 = E4M3 codes (upstream TensorDType kF32 / kBF16 /
+// kE4M3Software); biases are F32 or BF16
 int linear_executor_linear(LinearExecutorState *state, const float *input, const std::size_t rows,
                            const std::size_t input_width, const void *weight, const int weight_dtype,
                            const std::size_t weight_elements, const std::size_t output_width,
@@ -155,8 +178,8 @@ int linear_executor_linear(LinearExecutorState *state, const float *input, const
     return fail(kInvalidArgument, "linear executor arguments are invalid");
   if (weight_elements != output_width * input_width)
     return fail(kInternal, "host linear dimensions are inconsistent");
-  if ((weight_dtype != 0 && weight_dtype != 1) || (bias != nullptr && bias_dtype != 0 && bias_dtype != 1))
-    return fail(kUnsupported, "linear executor takes F32 or BF16 weights and biases");
+  if (weight_dtype < 0 || weight_dtype > 2 || (bias != nullptr && bias_dtype != 0 && bias_dtype != 1))
+    return fail(kUnsupported, "linear executor takes F32, BF16 or E4M3 weights and F32 or BF16 biases");
   if (bias != nullptr && bias_elements != output_width)
     return fail(kInternal, "host linear bias width is inconsistent");
   if (rows == 0) return kOk;
@@ -181,7 +204,7 @@ int linear_executor_linear(LinearExecutorState *state, const float *input, const
     entry.plane_count = weight_dtype == 0 ? 3 : 1;
     entry.out = output_width;
     entry.pitch = pitch;
-    const std::size_t element = weight_dtype == 0 ? 4 : 2;
+    const std::size_t element = weight_dtype == 0 ? 4 : weight_dtype == 1 ? 2 : 1;
     const std::size_t plane_bytes = output_width * pitch * 2;
     int status = state->staging.reserve(weight_elements * element);
     if (status != kOk) return status;
@@ -197,9 +220,12 @@ int linear_executor_linear(LinearExecutorState *state, const float *input, const
     if (weight_dtype == 0)
       split_planes_kernel<<<grid_for(output_width * pitch), 256, 0, stream>>>(
           static_cast<const float *>(state->staging.data), entry.planes, output_width, input_width, pitch, 3, false);
-    else
+    else if (weight_dtype == 1)
       pad_bf16_kernel<<<grid_for(output_width * pitch), 256, 0, stream>>>(
           static_cast<const bf16 *>(state->staging.data), entry.planes, output_width, input_width, pitch);
+    else
+      decode_e4m3_kernel<<<grid_for(output_width * pitch), 256, 0, stream>>>(
+          static_cast<const std::uint8_t *>(state->staging.data), entry.planes, output_width, input_width, pitch);
     status = check_launch("linear executor weight conversion");
     if (status != kOk || cudaStreamSynchronize(stream) != cudaSuccess) {
       cudaFree(planes);

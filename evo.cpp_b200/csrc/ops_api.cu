@@ -207,8 +207,8 @@ int evo_b200_bf16_row_to_column_major(const void *input, size_t rows,
 }
 
 int evo_b200_embedding(const uint32_t *tokens, const void *table, size_t rows,
-                       size_t width, void *output, void *stream) {
-  return embedding(tokens, table, rows, width, output, as_stream(stream));
+                       size_t width, size_t vocabulary, void *output, void *stream) {
+  return embedding(tokens, table, rows, width, vocabulary, output, as_stream(stream));
 }
 
 int evo_b200_bf16_split_hyena_projection(const void *projection, size_t rows,
@@ -506,6 +506,20 @@ int evo_b200_linear_executor_linear(evo_b200_linear_executor *executor, const fl
   return linear_executor_linear(reinterpret_cast<LinearExecutorState *>(executor), input, rows, input_width,
                                 weight, weight_dtype, weight_elements, output_width, bias, bias_dtype,
                                 bias_elements, output);
+}
+
+// ---- host E4M3FN codec (include/evo/fp8.hpp)
+uint8_t evo_b200_e4m3_encode(float value) { return fp8::encode_e4m3fn(value); }
+float evo_b200_e4m3_decode(uint8_t code) { return fp8::decode_e4m3fn(code); }
+float evo_b200_e4m3_scaled_roundtrip(float value, float scale) {
+  return fp8::scaled_e4m3fn_roundtrip(value, scale);
+}
+int evo_b200_e4m3_encode_array(const float *values, size_t count, float scale, uint8_t *codes) {
+  if ((values == nullptr || codes == nullptr) && count != 0)
+    return fail(kInvalidArgument, "E4M3 encode arguments are invalid");
+  if (!fp8::valid_scale(scale)) return fail(kInvalidArgument, "E4M3 scale must be positive and finite");
+  for (size_t i = 0; i < count; ++i) codes[i] = fp8::encode_e4m3fn(values[i] * scale);
+  return kOk;
 }
 
 }  // extern "C"

@@ -10,6 +10,14 @@
 
 namespace evob {
 
+// ---- fp8_codec.cpp: host E4M3FN codec (upstream include/evo/fp8.hpp)
+namespace fp8 {
+std::uint8_t encode_e4m3fn(float value) noexcept;
+float decode_e4m3fn(std::uint8_t code) noexcept;
+bool valid_scale(float scale) noexcept;
+float scaled_e4m3fn_roundtrip(float value, float scale) noexcept;
+}  // namespace fp8
+
 // ---- elementwise.cu
 int quantize_bf16(const void *input, std::size_t elements, float scale,
                   void *codes, float *dequantized, cudaStream_t stream);
@@ -26,8 +34,11 @@ int add(const void *first, const void *second, void *output,
         std::size_t elements, cudaStream_t stream);
 int add_bias(void *output, const void *bias, std::size_t rows,
              std::size_t width, cudaStream_t stream);
+// Ids >= vocabulary are not looked up: the row becomes zeros and the per-device
+// error word is raised (reported by gemm_error_state as an invalid argument).
 int embedding(const std::uint32_t *tokens, const void *table, std::size_t rows,
-              std::size_t width, void *output, cudaStream_t stream);
+              std::size_t width, std::size_t vocabulary, void *output,
+              cudaStream_t stream);
 int split_triples(const void *projection, std::size_t rows, std::size_t width,
                   void *x2, void *x1, void *value, cudaStream_t stream);
 int transpose(const void *input, std::size_t rows, std::size_t columns,
@@ -77,8 +88,12 @@ int linear(const LinearArgs &args, cudaStream_t stream);
 // gemv.cu: weight-streaming kernel that linear() uses for 1..8 rows.
 bool small_batch_linear_applicable(const LinearArgs &args);
 int small_batch_linear(const LinearArgs &args, cudaStream_t stream);
-// Synchronises the stream and reports (then clears) a pipeline time-out.
+// Synchronises the stream and reports (then clears) the per-device sticky error
+// word: bit 0 = a pipeline wait of a tcgen05 kernel timed out (cuda), bit 1 = a
+// device-resident token id was outside the vocabulary (invalid_argument).
 int gemm_error_state(cudaStream_t stream);
+// The word itself, for kernels that raise it.
+int *device_error_word(int *status);
 
 // ---- hyena_fir.cu
 struct GatedFirArgs {
@@ -157,6 +172,12 @@ int modal_prefill(const ModalArgs &args, cudaStream_t stream);
 // library image instead of args.scratch (which is ignored); separate x2/x1/v
 // inputs only.  Makes no device allocation.
 int modal_prefill_static_scratch(const ModalArgs &args, cudaStream_t stream);
+// Diagnostic taps: the time-domain modal filter [length, width] F32 and / or
+// the unrounded convolution of `gated` ([length, width] BF16, u = x1 * v) with it
+// from a zero state; either output may be null.
+int modal_taps(const void *gated, const float *log_poles, const float *residues, std::size_t length,
+               std::size_t width, std::size_t modes, float *filter, float *convolution,
+               cudaStream_t stream);
 // One cached-decode step of a whole Hyena mixer (featurizer step, split, gate,
 // inner FIR or modal step with their cache updates, post-gate) in one launch;
 // bit-identical to the unfused sequence.  All histories must be full.  Set

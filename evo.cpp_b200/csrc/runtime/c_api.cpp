@@ -493,6 +493,89 @@ evo_status evo_b200_context_continue_device(evo_context *context, const uint32_t
   });
 }
 
+const char *evo_b200_dump_point_name(int32_t point) { return evob::dump_point_name(point); }
+
+static int make_dump_plan(const evo_b200_dump_request *requests, size_t count, evo_b200_dump_callback callback,
+                          void *user_data, evob::DumpPlan *plan) {
+  if ((requests == nullptr && count != 0) || callback == nullptr)
+    return fail(evob::kInvalidArgument, "dump requests and callback are required");
+  for (size_t i = 0; i < count; ++i) {
+    if (requests[i].point < 0 || requests[i].point >= EVO_B200_DUMP_POINT_COUNT)
+      return fail(evob::kInvalidArgument, "dump point is out of range");
+    plan->requests.push_back({requests[i].layer, static_cast<evob::DumpPoint>(requests[i].point)});
+  }
+  plan->sink = [callback, user_data](const evob::DumpPlan::Request &request, const float *values,
+                                     std::size_t rows, std::size_t columns) -> int {
+    const evo_status status =
+        callback(request.layer, static_cast<int32_t>(request.point), values, rows, columns, user_data);
+    return status == EVO_STATUS_OK ? kOk : (valid_status(status) ? status : EVO_STATUS_INTERNAL);
+  };
+  return kOk;
+}
+
+evo_status evo_b200_context_prefill_with_dumps(evo_context *context, const evo_batch *batch,
+                                               const evo_b200_dump_request *requests, size_t request_count,
+                                               int cached_attention, evo_b200_dump_callback dump_callback,
+                                               evo_logits_callback logits_callback, void *user_data) {
+  return protect([&]() -> int {
+    if (context == nullptr || batch == nullptr || logits_callback == nullptr)
+      return fail(evob::kInvalidArgument, "context, batch and callbacks are required");
+    if (context->failed || context->context->poisoned())
+      return fail(evob::kInvalidArgument, "context was invalidated by an earlier failure");
+    if (context->context->position() != 0)
+      return fail(evob::kInvalidArgument, "prefill requires a fresh context");
+    evob::DumpPlan plan;
+    int status = make_dump_plan(requests, request_count, dump_callback, user_data, &plan);
+    if (status != kOk) return status;
+    std::vector<std::uint32_t> tokens;
+    status = single_sequence_tokens(batch, &tokens);
+    if (status != kOk) return status;
+    if (tokens.size() > context->context->activation_capacity())
+      return fail(evob::kUnsupported, "a prefill with dumps must fit one activation chunk");
+    context->failed = true;
+    std::vector<float> logits;
+    status = context->context->prefill_with_dumps(tokens, plan, cached_attention != 0, &logits);
+    if (status != kOk) return status;
+    const evo_status callback_status =
+        logits_callback(logits.data(), tokens.size(), context->context->config().vocab, 0, user_data);
+    if (callback_status != EVO_STATUS_OK)
+      return fail(valid_status(callback_status) ? callback_status : EVO_STATUS_INTERNAL,
+                  "logits consumer aborted prefill");
+    context->failed = false;
+    return kOk;
+  });
+}
+
+evo_status evo_b200_context_decode_with_dumps(evo_context *context, uint32_t token,
+                                              const evo_b200_dump_request *requests, size_t request_count,
+                                              evo_b200_dump_callback dump_callback,
+                                              evo_logits_callback logits_callback, void *user_data) {
+  return protect([&]() -> int {
+    if (context == nullptr || logits_callback == nullptr)
+      return fail(evob::kInvalidArgument, "context and callbacks are required");
+    if (context->failed || context->context->poisoned())
+      return fail(evob::kInvalidArgument, "context was invalidated by an earlier failure");
+    evob::DumpPlan plan;
+    int status = make_dump_plan(requests, request_count, dump_callback, user_data, &plan);
+    if (status != kOk) return status;
+    std::vector<float> logits;
+    const std::size_t offset = context->context->position();
+    status = context->context->decode_with_dumps(token, plan, &logits);
+    if (status != kOk) {
+      if (context->context->poisoned()) context->failed = true;
+      return status;
+    }
+    const evo_status callback_status =
+        logits_callback(logits.data(), 1, context->context->config().vocab, offset, user_data);
+    if (callback_status != EVO_STATUS_OK) {
+      context->failed = true;
+      return fail(valid_status(callback_status) ? callback_status : EVO_STATUS_INTERNAL,
+                  "logits consumer aborted decode");
+    }
+    return kOk;
+  });
+}
+
 evo_status evo_b200_variant_window_make(const char *sequence, size_t sequence_length, size_t position_1based,
                                         const char *reference, size_t reference_length, const char *alternate,
                                         size_t alternate_length, size_t maximum_tokens,

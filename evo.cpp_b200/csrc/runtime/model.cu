@@ -146,6 +146,183 @@ struct Context::Stage {
   }
 };
 
+// ---- activation taps (upstream dump_matching & friends, src/cuda/model.cu:1583-1742)
+namespace {
+
+struct ScopedDeviceBuffer {
+  void *data = nullptr;
+  int reserve(const std::size_t bytes) {
+    if (cudaMalloc(&data, bytes == 0 ? 16 : bytes) != cudaSuccess) {
+      data = nullptr;
+      return fail(kCuda, "cannot allocate " + std::to_string(bytes >> 20) + " MiB of dump scratch");
+    }
+    return kOk;
+  }
+  ~ScopedDeviceBuffer() {
+    if (data != nullptr) cudaFree(data);
+  }
+};
+
+// Hands `values` to every request of the plan that names (layer, point).
+int deliver(const DumpPlan &plan, const std::size_t layer, const DumpPoint point,
+            const std::vector<float> &values, const std::size_t rows, const std::size_t columns) {
+  for (const DumpPlan::Request &request : plan.requests) {
+    if (request.layer != layer || request.point != point) continue;
+    const int status = plan.sink ? plan.sink(request, values.data(), rows, columns) : kOk;
+    if (status != kOk) return fail(status, "dump consumer aborted the forward pass");
+  }
+  return kOk;
+}
+
+// BF16 [rows, columns] on the device -> F32 on the host -> sink.
+int emit_bf16(cudaStream_t stream, const DumpPlan &plan, const std::size_t layer, const DumpPoint point,
+              const void *device, const std::size_t rows, const std::size_t columns) {
+  if (!plan.wants(layer, point)) return kOk;
+  std::vector<std::uint16_t> raw(rows * columns);
+  if (cudaMemcpyAsync(raw.data(), device, raw.size() * 2, cudaMemcpyDeviceToHost, stream) != cudaSuccess ||
+      cudaStreamSynchronize(stream) != cudaSuccess)
+    return fail(kCuda, std::string("dump read-back failed: ") + cudaGetErrorString(cudaGetLastError()));
+  std::vector<float> values(raw.size());
+  for (std::size_t j = 0; j < raw.size(); ++j) {
+    const std::uint32_t bits = static_cast<std::uint32_t>(raw[j]) << 16U;
+    std::memcpy(&values[j], &bits, 4);
+  }
+  return deliver(plan, layer, point, values, rows, columns);
+}
+
+// F32 [rows, columns] on the device; only the last `active` columns of each row
+// are reported (FIR histories are left-padded with zeros until they fill).
+int emit_f32(cudaStream_t stream, const DumpPlan &plan, const std::size_t layer, const DumpPoint point,
+             const float *device, const std::size_t rows, const std::size_t columns, const std::size_t active) {
+  if (!plan.wants(layer, point)) return kOk;
+  if (active > columns) return fail(kInternal, "active FIR cache columns exceed cache capacity");
+  std::vector<float> padded(rows * columns);
+  if (cudaMemcpyAsync(padded.data(), device, padded.size() * 4, cudaMemcpyDeviceToHost, stream) != cudaSuccess ||
+      cudaStreamSynchronize(stream) != cudaSuccess)
+    return fail(kCuda, std::string("dump read-back failed: ") + cudaGetErrorString(cudaGetLastError()));
+  if (active == columns) return deliver(plan, layer, point, padded, rows, columns);
+  std::vector<float> values(rows * active);
+  for (std::size_t row = 0; row < rows; ++row)
+    std::copy_n(padded.begin() + static_cast<std::ptrdiff_t>(row * columns + columns - active), active,
+                values.begin() + static_cast<std::ptrdiff_t>(row * active));
+  return deliver(plan, layer, point, values, rows, active);
+}
+
+}  // namespace
+
+const char *dump_point_name(const int point) {
+  static const char *const names[static_cast<int>(DumpPoint::kDumpPoints)] = {
+      "block_output", "pre_norm", "mixer_input_projection", "mixer_short_filter", "mixer_short_state",
+      "mixer_inner_state", "mixer_x2", "mixer_x1", "mixer_value", "mixer_pregate", "mixer_state",
+      "mixer_filter", "mixer_convolution", "mixer_output", "mixer_projection", "mixer_residual",
+      "post_norm", "mlp_l1", "mlp_l2", "mlp_activation", "mlp_gated", "mlp_output"};
+  return point >= 0 && point < static_cast<int>(DumpPoint::kDumpPoints) ? names[point] : "";
+}
+
+// Taps inside a Hyena mixer.  After an initial prefill the fused kernels have
+// kept the featurizer output, the split and the pre-gate in registers, so they
+// are recomputed here with the unfused operators (same roundings: the fused
+// short-explicit operator is bit-identical to this sequence); after a
+// continuation or decode step the unfused path has just left them in the arena.
+int Context::dump_mixer_taps(Stage &s, const std::size_t i, const std::size_t rows, const Mode mode,
+                             const DumpPlan &plan) {
+  const ModelConfig &c = weights_->config;
+  const LayerWeights &w = s.weights->layers[i];
+  LayerState &state = s.layers[i];
+  const std::size_t D = c.width, layer = s.weights->layer_begin + i;
+  const bool initial = mode == Mode::kPrefill || mode == Mode::kStateless || mode == Mode::kCachedPrefill;
+  const bool stateless = mode == Mode::kStateless;
+  cudaStream_t stream = s.stream;
+  if (initial) {
+    EVOB_TRY(fir_prefill(s.projection, w.short_filter, false, nullptr, false, rows, 3 * D, 3 * D, c.short_taps,
+                         true, s.short_filtered, nullptr, stream));
+    EVOB_TRY(split_triples(s.short_filtered, rows, D, s.x2, s.x1, s.value, stream));
+    EVOB_TRY(gate(s.x1, s.value, s.pregate, rows * D, false, stream));
+  }
+  const std::size_t seen = (initial ? 0 : position_) + rows;
+  EVOB_TRY(emit_bf16(stream, plan, layer, DumpPoint::kMixerShortFilter, s.short_filtered, rows, 3 * D));
+  if (!stateless)
+    EVOB_TRY(emit_f32(stream, plan, layer, DumpPoint::kMixerShortState, state.short_cache, 3 * D,
+                      c.short_taps - 1, std::min(seen, c.short_taps - 1)));
+  EVOB_TRY(emit_bf16(stream, plan, layer, DumpPoint::kMixerX2, s.x2, rows, D));
+  EVOB_TRY(emit_bf16(stream, plan, layer, DumpPoint::kMixerX1, s.x1, rows, D));
+  EVOB_TRY(emit_bf16(stream, plan, layer, DumpPoint::kMixerValue, s.value, rows, D));
+  if (w.type != MixerType::kHcl && !stateless) {
+    const std::size_t taps = w.type == MixerType::kHcs ? c.hcs_taps : c.hcm_taps;
+    EVOB_TRY(emit_f32(stream, plan, layer, DumpPoint::kMixerInnerState, state.inner_cache, D, taps - 1,
+                      std::min(seen, taps - 1)));
+  }
+  if (w.type == MixerType::kHcl && !stateless)
+    EVOB_TRY(emit_f32(stream, plan, layer, DumpPoint::kMixerState, state.modal_state, D, c.state_size,
+                      c.state_size));
+  EVOB_TRY(emit_bf16(stream, plan, layer, DumpPoint::kMixerPregate, s.pregate, rows, D));
+  if (w.type == MixerType::kHcl && initial) {
+    const bool filter = plan.wants(layer, DumpPoint::kMixerFilter);
+    const bool convolution = plan.wants(layer, DumpPoint::kMixerConvolution);
+    if (filter || convolution) {
+      ScopedDeviceBuffer filter_values, convolution_values;
+      if (filter) EVOB_TRY(filter_values.reserve(rows * D * 4));
+      if (convolution) EVOB_TRY(convolution_values.reserve(rows * D * 4));
+      EVOB_TRY(modal_taps(s.pregate, w.log_poles, w.residues, rows, D, c.state_size,
+                          static_cast<float *>(filter_values.data), static_cast<float *>(convolution_values.data),
+                          stream));
+      if (filter)
+        EVOB_TRY(emit_f32(stream, plan, layer, DumpPoint::kMixerFilter, static_cast<float *>(filter_values.data),
+                          rows, D, D));
+      if (convolution)
+        EVOB_TRY(emit_f32(stream, plan, layer, DumpPoint::kMixerConvolution,
+                          static_cast<float *>(convolution_values.data), rows, D, D));
+    }
+  }
+  return kOk;
+}
+
+// Taps inside the MLP that the gate-fused up-projection never writes: l1(x),
+// l2(x) and, in block 0, gelu(l1(x)).  The interleaved weight is multiplied
+// once more without the gate; its output row is [l1 block 0 | l2 block 0 | l1
+// block 1 | ...] in 128-column blocks, which two strided copies separate.
+int Context::dump_mlp_taps(Stage &s, const std::size_t i, const std::size_t rows, const DumpPlan &plan) {
+  const ModelConfig &c = weights_->config;
+  const LayerWeights &w = s.weights->layers[i];
+  const std::size_t D = c.width, I = c.inner_width, layer = s.weights->layer_begin + i;
+  const bool activation = layer == 0 && plan.wants(layer, DumpPoint::kMlpActivation);
+  if (!plan.wants(layer, DumpPoint::kMlpL1) && !plan.wants(layer, DumpPoint::kMlpL2) && !activation) return kOk;
+  cudaStream_t stream = s.stream;
+  ScopedDeviceBuffer raw, first, second, activated;
+  const void *l1_values = s.mlp_first, *l2_values = s.mlp_second;
+  if (w.l12 != nullptr) {
+    EVOB_TRY(raw.reserve(rows * 2 * I * 2));
+    EVOB_TRY(first.reserve(rows * I * 2));
+    EVOB_TRY(second.reserve(rows * I * 2));
+    LinearArgs a;
+    a.split_workspace = s.split_workspace;
+    a.split_workspace_bytes = kSplitWorkspaceBytes;
+    a.input = s.normalized;
+    a.weight = w.l12;
+    a.output = raw.data;
+    a.rows = rows;
+    a.in_features = D;
+    a.out_features = 2 * I;
+    EVOB_TRY(linear(a, stream));
+    const std::size_t blocks = rows * (I / 128);
+    if (cudaMemcpy2DAsync(first.data, 256, raw.data, 512, 256, blocks, cudaMemcpyDeviceToDevice, stream) !=
+            cudaSuccess ||
+        cudaMemcpy2DAsync(second.data, 256, static_cast<unsigned char *>(raw.data) + 256, 512, 256, blocks,
+                          cudaMemcpyDeviceToDevice, stream) != cudaSuccess)
+      return fail(kCuda, "dump de-interleave failed");
+    l1_values = first.data;
+    l2_values = second.data;
+  }
+  EVOB_TRY(emit_bf16(stream, plan, layer, DumpPoint::kMlpL1, l1_values, rows, I));
+  EVOB_TRY(emit_bf16(stream, plan, layer, DumpPoint::kMlpL2, l2_values, rows, I));
+  if (activation) {
+    EVOB_TRY(activated.reserve(rows * I * 2));
+    EVOB_TRY(gelu(l1_values, activated.data, rows * I, stream));
+    EVOB_TRY(emit_bf16(stream, plan, layer, DumpPoint::kMlpActivation, activated.data, rows, I));
+  }
+  return kOk;
+}
+
 Context::~Context() {
   if (decode_graph_ != nullptr) cudaGraphExecDestroy(static_cast<cudaGraphExec_t>(decode_graph_));
 }
@@ -173,7 +350,7 @@ int Context::decode_step_graph(const std::uint32_t *host_token, bool *launched) 
       return kOk;
     }
     dynamic_position_ = device_position_;
-    int status = embedding(first.tokens, first.weights->embedding, 1, c.width, first.hidden, stream);
+    int status = embedding(first.tokens, first.weights->embedding, 1, c.width, c.vocab, first.hidden, stream);
     if (status == kOk) status = run_stage(first, 1, Mode::kDecode, -1, nullptr);
     if (status == kOk)
       status = rms_norm(first.hidden, first.weights->final_norm, 1, c.width, c.epsilon, first.normalized,
@@ -396,7 +573,8 @@ void Context::read_profile(double (&milliseconds)[kProfileCategories],
 // straight from those earlier rows.
 int Context::run_stage(Stage &s, const std::size_t rows, const Mode mode,
                        const long capture_layer, std::vector<float> *captured,
-                       const std::size_t window_begin, const std::size_t window_position) {
+                       const std::size_t window_begin, const std::size_t window_position,
+                       const DumpPlan *const dumps) {
   const ModelConfig &c = weights_->config;
   const std::size_t D = c.width, I = c.inner_width;
   const bool window = mode == Mode::kWindow;
@@ -412,9 +590,15 @@ int Context::run_stage(Stage &s, const std::size_t rows, const Mode mode,
     LayerState &state = s.layers[i];
     const bool attention = w.type == MixerType::kAttention;
     const bool fp8 = !attention && c.fp8_projection;
+    const std::size_t layer_index = s.weights->layer_begin + i;
+    // taps of this block, if any were asked for (never in window mode)
+    const DumpPlan *const tap = dumps != nullptr && dumps->wants_layer(layer_index) ? dumps : nullptr;
+    const bool tap_pre_norm = tap != nullptr && tap->wants(layer_index, DumpPoint::kPreNorm);
     // pre-norm (+ E4M3 codes of the normalised activations for FP8 projections)
-    EVOB_OP(kCatNorm, rms_norm(s.hidden, w.pre_norm, rows, D, c.epsilon, fp8 ? nullptr : s.normalized,
-                      fp8 ? s.codes : nullptr, w.projection_input_scale, stream));
+    EVOB_OP(kCatNorm, rms_norm(s.hidden, w.pre_norm, rows, D, c.epsilon,
+                      fp8 && !tap_pre_norm ? nullptr : s.normalized, fp8 ? s.codes : nullptr,
+                      w.projection_input_scale, stream));
+    if (tap_pre_norm) EVOB_TRY(emit_bf16(stream, *tap, layer_index, DumpPoint::kPreNorm, s.normalized, rows, D));
     // input projection -> [rows, 3D]
     if (fp8 && profile_ == ExecutionProfile::kExact) {
       EVOB_OP(kCatGemmEmulated, e4m3_emulated_gemm(s.codes, w.projection, rows, D, 3 * D,
@@ -435,12 +619,22 @@ int Context::run_stage(Stage &s, const std::size_t rows, const Mode mode,
       }
       EVOB_OP(fp8 ? kCatGemmFp8 : kCatGemmBf16, linear(a, stream));
     }
+    if (tap != nullptr)
+      EVOB_TRY(emit_bf16(stream, *tap, layer_index, DumpPoint::kMixerInputProjection, s.projection, rows, 3 * D));
     if (attention) {
       const std::size_t prefix = window ? window_position : (initial ? 0 : position_);
       EVOB_OP(kCatAttention, split_rope_append(s.projection, w.inverse_frequency, rows, c.heads, c.head_dim(),
                                  prefix, c.rope_scale, false, s.query, state.key_cache,
                                  state.value_cache, context_size_, stream,
                                  mode == Mode::kDecode ? dynamic_position_ : nullptr));
+      if (tap != nullptr) {
+        // rotated queries, and the rotated keys / values where the append left them in the cache
+        EVOB_TRY(emit_bf16(stream, *tap, layer_index, DumpPoint::kMixerX2, s.query, rows, D));
+        EVOB_TRY(emit_bf16(stream, *tap, layer_index, DumpPoint::kMixerX1,
+                           static_cast<unsigned char *>(state.key_cache) + prefix * D * 2, rows, D));
+        EVOB_TRY(emit_bf16(stream, *tap, layer_index, DumpPoint::kMixerValue,
+                           static_cast<unsigned char *>(state.value_cache) + prefix * D * 2, rows, D));
+      }
       const bool cached = mode == Mode::kCachedPrefill ||
                           ((mode == Mode::kDecode || mode == Mode::kContinue) && cached_attention_);
       if (cached)
@@ -526,7 +720,7 @@ int Context::run_stage(Stage &s, const std::size_t rows, const Mode mode,
                             cudaMemcpyDeviceToDevice, stream) != cudaSuccess)
           return fail(kCuda, "projection history save failed");
       }
-    } else if (mode == Mode::kDecode && rows == 1 && c.short_taps == 3 &&
+    } else if (mode == Mode::kDecode && rows == 1 && c.short_taps == 3 && tap == nullptr &&
                position_ >= std::max({c.short_taps, c.hcs_taps, c.hcm_taps}) &&
                (w.type == MixerType::kHcl ? c.state_size <= 32 : (w.type == MixerType::kHcs ? c.hcs_taps : c.hcm_taps) <= 128)) {
       // one token against full histories: the whole mixer in one launch
@@ -573,6 +767,7 @@ int Context::run_stage(Stage &s, const std::size_t rows, const Mode mode,
           a.log_poles = w.log_poles;
           a.residues = w.residues;
           a.output = s.mixer_out;
+          a.pregate = tap != nullptr ? s.pregate : nullptr;
           a.state = state.modal_state;
           a.scratch = s.modal_scratch;
           a.length = rows;
@@ -592,6 +787,10 @@ int Context::run_stage(Stage &s, const std::size_t rows, const Mode mode,
         EVOB_OP(kCatElementwise, gate(s.query, s.x2, s.mixer_out, rows * D, false, stream));
       }
     }
+    if (tap != nullptr) {
+      if (!attention) EVOB_TRY(dump_mixer_taps(s, i, rows, mode, *tap));
+      EVOB_TRY(emit_bf16(stream, *tap, layer_index, DumpPoint::kMixerOutput, s.mixer_out, rows, D));
+    }
     // output projection + bias + residual -> residual buffer
     {
       LinearArgs a;
@@ -609,10 +808,20 @@ int Context::run_stage(Stage &s, const std::size_t rows, const Mode mode,
       // (upstream src/cuda/model.cu:1768-1799)
       a.bias_mode = (attention || rows == 1) ? 1 : 2;
       EVOB_OP(kCatGemmBf16, linear(a, stream));
+      if (tap != nullptr && tap->wants(layer_index, DumpPoint::kMixerProjection)) {
+        // the projection before the residual joins it: the same product once more
+        a.residual = nullptr;
+        a.output = s.query;
+        EVOB_TRY(linear(a, stream));
+        EVOB_TRY(emit_bf16(stream, *tap, layer_index, DumpPoint::kMixerProjection, s.query, rows, D));
+      }
     }
+    if (tap != nullptr)
+      EVOB_TRY(emit_bf16(stream, *tap, layer_index, DumpPoint::kMixerResidual, s.residual, rows, D));
     EVOB_OP(kCatNorm, rms_norm(s.residual, w.post_norm, rows, D, c.epsilon, s.normalized, nullptr, 1.0F,
                       stream));
-    const std::size_t layer_index = s.weights->layer_begin + i;
+    if (tap != nullptr)
+      EVOB_TRY(emit_bf16(stream, *tap, layer_index, DumpPoint::kPostNorm, s.normalized, rows, D));
     const bool gelu_block = layer_index == 0;
     if (w.l12 != nullptr) {
       LinearArgs a;
@@ -642,6 +851,10 @@ int Context::run_stage(Stage &s, const std::size_t rows, const Mode mode,
       EVOB_OP(kCatGemmBf16, linear(a, stream));
       EVOB_OP(kCatElementwise, gate(s.mlp_first, s.mlp_second, s.gated, rows * I, gelu_block, stream));
     }
+    if (tap != nullptr) {
+      EVOB_TRY(dump_mlp_taps(s, i, rows, *tap));
+      EVOB_TRY(emit_bf16(stream, *tap, layer_index, DumpPoint::kMlpGated, s.gated, rows, I));
+    }
     {
       LinearArgs a;
       a.split_workspace = s.split_workspace;
@@ -654,7 +867,15 @@ int Context::run_stage(Stage &s, const std::size_t rows, const Mode mode,
       a.in_features = I;
       a.out_features = D;
       EVOB_OP(kCatGemmBf16, linear(a, stream));
+      if (tap != nullptr && tap->wants(layer_index, DumpPoint::kMlpOutput)) {
+        a.residual = nullptr;
+        a.output = s.query;
+        EVOB_TRY(linear(a, stream));
+        EVOB_TRY(emit_bf16(stream, *tap, layer_index, DumpPoint::kMlpOutput, s.query, rows, D));
+      }
     }
+    if (tap != nullptr)
+      EVOB_TRY(emit_bf16(stream, *tap, layer_index, DumpPoint::kBlockOutput, s.hidden, rows, D));
     if (capture_layer >= 0 && static_cast<std::size_t>(capture_layer) == layer_index &&
         captured != nullptr) {
       std::vector<std::uint16_t> raw(rows * D);
@@ -711,7 +932,7 @@ int Context::run_wavefront(const std::size_t rows, const Mode /*mode*/, const lo
 
 int Context::forward(const std::uint32_t *host_tokens, const std::uint32_t *device_tokens,
                      const std::size_t rows, const Mode mode, std::vector<float> *logits,
-                     const long capture_layer, std::vector<float> *captured) {
+                     const long capture_layer, std::vector<float> *captured, const DumpPlan *const dumps) {
   const ModelConfig &c = weights_->config;
   if (!healthy_) return fail(kInvalidArgument, "context was invalidated by an earlier failure");
   if (weights_->slice_count > 1)
@@ -738,7 +959,7 @@ int Context::forward(const std::uint32_t *host_tokens, const std::uint32_t *devi
   // in front of them.  (Short chunks and the exact cached-attention profile
   // keep the step kernels.)
   const bool continuation_window = mode == Mode::kContinue && rows >= 16 && !cached_attention_ &&
-                                   capture_layer < 0 && history_current_;
+                                   capture_layer < 0 && history_current_ && dumps == nullptr;
   struct ShiftBack {
     Context *context;
     bool active;
@@ -754,7 +975,7 @@ int Context::forward(const std::uint32_t *host_tokens, const std::uint32_t *devi
   bool graph_step = false;
   if (decode_graph_allowed_ && mode == Mode::kDecode && stages_.size() == 1 && host_tokens != nullptr &&
       !first.profiling && !cached_attention_ && c.head_dim() == 128 && capture_layer < 0 &&
-      position_ >= std::max({c.short_taps, c.hcs_taps, c.hcm_taps}))
+      dumps == nullptr && position_ >= std::max({c.short_taps, c.hcs_taps, c.hcm_taps}))
     status = decode_step_graph(host_tokens, &graph_step);
   if (!graph_step && status == kOk) {
     DeviceGuard guard(first.device);
@@ -765,11 +986,11 @@ int Context::forward(const std::uint32_t *host_tokens, const std::uint32_t *devi
       device_tokens = first.tokens;
     }
     if (status == kOk)
-      status = embedding(device_tokens, first.weights->embedding, rows, c.width, first.hidden,
+      status = embedding(device_tokens, first.weights->embedding, rows, c.width, c.vocab, first.hidden,
                          first.stream);
   }
   const bool wavefront = stages_.size() > 1 && (mode == Mode::kPrefill || mode == Mode::kStateless) &&
-                         rows >= 512 && capture_layer < 0;
+                         rows >= 512 && capture_layer < 0 && dumps == nullptr;
   if (wavefront && status == kOk) status = run_wavefront(rows, mode, capture_layer, captured);
   for (std::size_t index = 0; index < stages_.size() && status == kOk && !wavefront && !graph_step; ++index) {
     Stage &stage = *stages_[index];
@@ -784,7 +1005,7 @@ int Context::forward(const std::uint32_t *host_tokens, const std::uint32_t *devi
     if (status == kOk)
       status = continuation_window
                    ? run_stage(stage, rows, Mode::kWindow, -1, nullptr, kHistoryPad, position_)
-                   : run_stage(stage, rows, mode, capture_layer, captured);
+                   : run_stage(stage, rows, mode, capture_layer, captured, 0, 0, dumps);
     if (status == kOk && cudaEventRecord(stage.done, stage.stream) != cudaSuccess)
       status = fail(kCuda, "stage hand-off failed");
   }
@@ -868,6 +1089,7 @@ int Context::slice_embed(const std::uint32_t *device_tokens, const std::size_t p
     return fail(kInvalidArgument, "slice_embed needs the first slice, a token buffer and a window inside the arena");
   DeviceGuard guard(stage.device);
   return embedding(device_tokens, stage.weights->embedding, rows, weights_->config.width,
+                   weights_->config.vocab,
                    static_cast<unsigned char *>(stage.hidden) + (kHistoryPad + offset) * weights_->config.width * 2,
                    stage.stream);
 }
@@ -953,6 +1175,24 @@ int Context::prefill_embedding(const std::vector<std::uint32_t> &tokens, const s
   std::vector<float> logits;
   return forward(tokens.data(), nullptr, tokens.size(), Mode::kStateless, &logits,
                  static_cast<long>(layer), hidden);
+}
+int Context::prefill_with_dumps(const std::vector<std::uint32_t> &tokens, const DumpPlan &plan,
+                                const bool cached, std::vector<float> *logits) {
+  if (logits == nullptr) return fail(kInvalidArgument, "logits output is null");
+  for (const DumpPlan::Request &request : plan.requests)
+    if (request.layer >= weights_->config.layers || static_cast<int>(request.point) < 0 ||
+        request.point >= DumpPoint::kDumpPoints)
+      return fail(kInvalidArgument, "CUDA dump layer is out of range");
+  return forward(tokens.data(), nullptr, tokens.size(), cached ? Mode::kCachedPrefill : Mode::kPrefill, logits, -1,
+                 nullptr, &plan);
+}
+int Context::decode_with_dumps(const std::uint32_t token, const DumpPlan &plan, std::vector<float> *logits) {
+  if (logits == nullptr) return fail(kInvalidArgument, "logits output is null");
+  for (const DumpPlan::Request &request : plan.requests)
+    if (request.layer >= weights_->config.layers || static_cast<int>(request.point) < 0 ||
+        request.point >= DumpPoint::kDumpPoints)
+      return fail(kInvalidArgument, "CUDA dump layer is out of range");
+  return forward(&token, nullptr, 1, Mode::kDecode, logits, -1, nullptr, &plan);
 }
 int Context::continue_device(const std::uint32_t *device_tokens, const std::size_t rows) {
   if (device_tokens == nullptr) return fail(kInvalidArgument, "token buffer is null");

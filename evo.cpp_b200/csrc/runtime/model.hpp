@@ -9,6 +9,7 @@
 
 #include <cstddef>
 #include <cstdint>
+#include <functional>
 #include <memory>
 #include <string>
 #include <vector>
@@ -34,6 +35,38 @@ enum ProfileCategory : int {
   kProfileCategories
 };
 const char *profile_category_name(int category);
+
+// Named activation taps inside a block, in upstream's order and with
+// upstream's names (LayerDumpPoint, include/evo/cuda/model.hpp:22-45).
+enum class DumpPoint : int {
+  kBlockOutput = 0, kPreNorm, kMixerInputProjection, kMixerShortFilter, kMixerShortState,
+  kMixerInnerState, kMixerX2, kMixerX1, kMixerValue, kMixerPregate, kMixerState, kMixerFilter,
+  kMixerConvolution, kMixerOutput, kMixerProjection, kMixerResidual, kPostNorm, kMlpL1, kMlpL2,
+  kMlpActivation, kMlpGated, kMlpOutput, kDumpPoints
+};
+const char *dump_point_name(int point);  // "block_output", "pre_norm", ... ; "" when out of range
+
+// A set of (layer, point) taps and the consumer of their values.  The sink
+// gets F32 values [rows, columns] (BF16 buffers widened) that are valid during
+// the call; a non-zero return aborts the forward pass with that status.
+struct DumpPlan {
+  struct Request {
+    std::size_t layer = 0;
+    DumpPoint point = DumpPoint::kBlockOutput;
+  };
+  std::vector<Request> requests;
+  std::function<int(const Request &request, const float *values, std::size_t rows, std::size_t columns)> sink;
+  bool wants(std::size_t layer, DumpPoint point) const {
+    for (const Request &r : requests)
+      if (r.layer == layer && r.point == point) return true;
+    return false;
+  }
+  bool wants_layer(std::size_t layer) const {
+    for (const Request &r : requests)
+      if (r.layer == layer) return true;
+    return false;
+  }
+};
 
 // How E4M3 Hyena projections are evaluated.  kExact reproduces upstream's
 // software-QGMMA rounding bit for bit; kTensorCore uses tcgen05 FP8 MMAs with
@@ -122,6 +155,15 @@ class Context {
   // Block output of `layer` ([rows, width] floats) for a fresh stateless prefill.
   int prefill_embedding(const std::vector<std::uint32_t> &tokens, std::size_t layer,
                         std::vector<float> *hidden);
+  // Upstream's prefill_with_dumps / prefill_cached_with_dumps / decode_with_dumps
+  // (include/evo/cuda/model.hpp:121-134, 184-190): the same passes with the
+  // requested taps handed to plan.sink as they are produced.  A layer with taps
+  // inside its mixer or MLP runs the unfused operator sequence for those taps
+  // next to the fused kernels, so that every intermediate exists as a buffer;
+  // the block's own results still come from the ordinary path.
+  int prefill_with_dumps(const std::vector<std::uint32_t> &tokens, const DumpPlan &plan, bool cached,
+                         std::vector<float> *logits);
+  int decode_with_dumps(std::uint32_t token, const DumpPlan &plan, std::vector<float> *logits);
 
   // Device-resident variant used by the benchmark: tokens already on the
   // device of stage 0, logits left on the device (BF16 [rows, vocab]).
@@ -168,10 +210,14 @@ class Context {
   Context() = default;
   int forward(const std::uint32_t *host_tokens, const std::uint32_t *device_tokens,
               std::size_t rows, Mode mode, std::vector<float> *logits, long capture_layer,
-              std::vector<float> *captured);
+              std::vector<float> *captured, const DumpPlan *dumps = nullptr);
   int run_stage(Stage &stage, std::size_t rows, Mode mode, long capture_layer,
                 std::vector<float> *captured, std::size_t window_begin = 0,
-                std::size_t window_position = 0);
+                std::size_t window_position = 0, const DumpPlan *dumps = nullptr);
+  // Taps of block `layer` of `stage` (dumps.cu-style helpers in model.cu).
+  int dump_mixer_taps(Stage &stage, std::size_t local_layer, std::size_t rows, Mode mode,
+                      const DumpPlan &dumps);
+  int dump_mlp_taps(Stage &stage, std::size_t local_layer, std::size_t rows, const DumpPlan &dumps);
   // Chunk wavefront over the pipeline stages: chunk j runs on stage s while
   // chunk j+1 runs on stage s-1 (legal because every mixer carries causal
   // state).  Used for initial prefills on more than one stage.

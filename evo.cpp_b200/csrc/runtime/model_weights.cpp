@@ -255,7 +255,7 @@ int load_weights(const ModelFile &file, const std::vector<int> &devices,
     }
   for (const TensorView &view : file.tensors())
     if (expected_names.count(view.name) == 0)
-      return fail(kModelFormat, "artifact holds an unexpected tensor: " + view.name);
+      return fail(kModelFormat, "unknown tensor for model profile '" + c.model_id + "': " + view.name);
 
   const auto plan = plan_stages(layer_bytes, stage_count, c.test_fixture);
   if (plan.size() != stage_count) return fail(kInternal, "stage planning failed");

@@ -16,8 +16,20 @@ MODEL_FLAG_ALLOW_SYNTHETIC = 1
 CONTEXT_FLAG_TENSORCORE_FP8 = 1 << 8
 CONTEXT_FLAG_FULL_ARENA = 1 << 9
 
+DUMP_POINTS = ("block_output", "pre_norm", "mixer_input_projection", "mixer_short_filter", "mixer_short_state",
+               "mixer_inner_state", "mixer_x2", "mixer_x1", "mixer_value", "mixer_pregate", "mixer_state",
+               "mixer_filter", "mixer_convolution", "mixer_output", "mixer_projection", "mixer_residual",
+               "post_norm", "mlp_l1", "mlp_l2", "mlp_activation", "mlp_gated", "mlp_output")
+
+DUMP_CALLBACK = ctypes.CFUNCTYPE(ctypes.c_int, ctypes.c_size_t, ctypes.c_int32, ctypes.POINTER(ctypes.c_float),
+                                 ctypes.c_size_t, ctypes.c_size_t, ctypes.c_void_p)
+
 LOGITS_CALLBACK = ctypes.CFUNCTYPE(ctypes.c_int, ctypes.POINTER(ctypes.c_float), ctypes.c_size_t,
                                    ctypes.c_size_t, ctypes.c_size_t, ctypes.c_void_p)
+
+
+class DumpRequest(ctypes.Structure):
+    _fields_ = [("layer", ctypes.c_size_t), ("point", ctypes.c_int32)]
 
 
 class ModelParams(ctypes.Structure):
@@ -106,6 +118,12 @@ class EvoLibrary:
                                                           ctypes.POINTER(ctypes.c_uint64), Z]
             lib.evo_b200_profile_category_name.restype = ctypes.c_char_p
             lib.evo_b200_profile_category_name.argtypes = [Z]
+            lib.evo_b200_dump_point_name.restype = ctypes.c_char_p
+            lib.evo_b200_dump_point_name.argtypes = [ctypes.c_int32]
+            lib.evo_b200_context_prefill_with_dumps.argtypes = [V, V, ctypes.POINTER(DumpRequest), Z, I,
+                                                                DUMP_CALLBACK, LOGITS_CALLBACK, V]
+            lib.evo_b200_context_decode_with_dumps.argtypes = [V, ctypes.c_uint32, ctypes.POINTER(DumpRequest), Z,
+                                                               DUMP_CALLBACK, LOGITS_CALLBACK, V]
             lib.evo_b200_model_load_slice.argtypes = [ctypes.c_char_p, ctypes.c_int32, Z, Z,
                                                       ctypes.c_uint32, ctypes.POINTER(V)]
             lib.evo_b200_context_slice_embed.argtypes = [V, V, Z, Z]
@@ -236,6 +254,39 @@ class Context:
             self.library.lib.evo_batch_free(batch)
 
     # ---- extensions of this repository's library
+    def _with_dumps(self, taps, call, consume=None):
+        """taps: iterable of (layer, point name).  Returns (logits, {(layer, name): array}); with
+        `consume` the arrays are handed to consume(layer, name, array) instead of being kept."""
+        taps = list(taps)
+        requests = (DumpRequest * max(1, len(taps)))()
+        for slot, (layer, name) in zip(requests, taps):
+            slot.layer, slot.point = layer, DUMP_POINTS.index(name)
+        collected: dict = {}
+
+        @DUMP_CALLBACK
+        def on_dump(layer, point, data, rows, cols, _user):
+            values = np.ctypeslib.as_array(data, shape=(rows, cols))
+            if consume is not None:
+                return int(consume(layer, DUMP_POINTS[point], values) or 0)
+            collected[(layer, DUMP_POINTS[point])] = values.copy()
+            return 0
+
+        logits = self._collect(lambda cb: call(requests, len(taps), on_dump, cb), self.vocab)
+        return logits, collected
+
+    def prefill_with_dumps(self, sequence: bytes, taps, cached: bool = False, consume=None):
+        batch = self._batch(bytes(sequence))
+        try:
+            return self._with_dumps(taps, lambda r, n, d, cb: self.library.lib.evo_b200_context_prefill_with_dumps(
+                self.handle, batch, r, n, int(cached), d, cb, None), consume)
+        finally:
+            self.library.lib.evo_batch_free(batch)
+
+    def decode_with_dumps(self, token: int, taps, consume=None):
+        logits, dumps = self._with_dumps(taps, lambda r, n, d, cb: self.library.lib.evo_b200_context_decode_with_dumps(
+            self.handle, token, r, n, d, cb, None), consume)
+        return logits[0], dumps
+
     def prefill_device(self, device_tokens: int, rows: int, stateless: bool = True) -> int:
         out = ctypes.c_void_p()
         self.library.check(self.library.lib.evo_b200_context_prefill_device(

@@ -67,6 +67,57 @@ EVO_API evo_status evo_b200_context_stage_info(const evo_context *context, size_
                                                evo_b200_stage_info *info);
 
 
+/* ---- activation taps inside the blocks.
+ * Upstream's C++ runtime can write named intermediate activations of chosen
+ * blocks to NPY files (LayerDumpPoint / LayerDump, include/evo/cuda/model.hpp:22-92;
+ * PipelineModel::prefill_with_dumps, prefill_cached_with_dumps and
+ * decode_with_dumps, :121-134 and :184-190; taken at src/cuda/model.cu:1373-1581
+ * and :1757-1856); its C ABI does not export them.  Here they are a callback:
+ * `point` is one of the 22 taps below, in upstream's order; values are F32
+ * (BF16 activations widened; FIR histories and modal states are F32 already),
+ * row-major [rows, columns], valid during the call.  Shapes: activations are
+ * [tokens, width], [tokens, 3 width] for the projection and its featurizer
+ * output, [tokens, inner] inside the MLP; mixer_short_state [3 width, filled
+ * history], mixer_inner_state [width, filled history], mixer_state [width,
+ * modes]; mixer_filter and mixer_convolution [tokens, width] (initial prefill of
+ * a long-implicit block only).  Taps that a fused kernel keeps in registers are
+ * produced by running the unfused operators for that block as well, so asking
+ * for them costs extra launches; the block's results are unchanged.
+ * The pass itself behaves like evo_context_prefill (fresh context, one
+ * sequence, which must fit one activation chunk: EVO_STATUS_UNSUPPORTED
+ * otherwise) and evo_context_decode.  A non-OK status from either callback
+ * aborts the pass and invalidates the context. */
+enum {
+  EVO_B200_DUMP_BLOCK_OUTPUT = 0, EVO_B200_DUMP_PRE_NORM, EVO_B200_DUMP_MIXER_INPUT_PROJECTION,
+  EVO_B200_DUMP_MIXER_SHORT_FILTER, EVO_B200_DUMP_MIXER_SHORT_STATE, EVO_B200_DUMP_MIXER_INNER_STATE,
+  EVO_B200_DUMP_MIXER_X2, EVO_B200_DUMP_MIXER_X1, EVO_B200_DUMP_MIXER_VALUE, EVO_B200_DUMP_MIXER_PREGATE,
+  EVO_B200_DUMP_MIXER_STATE, EVO_B200_DUMP_MIXER_FILTER, EVO_B200_DUMP_MIXER_CONVOLUTION,
+  EVO_B200_DUMP_MIXER_OUTPUT, EVO_B200_DUMP_MIXER_PROJECTION, EVO_B200_DUMP_MIXER_RESIDUAL,
+  EVO_B200_DUMP_POST_NORM, EVO_B200_DUMP_MLP_L1, EVO_B200_DUMP_MLP_L2, EVO_B200_DUMP_MLP_ACTIVATION,
+  EVO_B200_DUMP_MLP_GATED, EVO_B200_DUMP_MLP_OUTPUT, EVO_B200_DUMP_POINT_COUNT
+};
+typedef struct evo_b200_dump_request {
+  size_t layer;
+  int32_t point;
+} evo_b200_dump_request;
+typedef evo_status (*evo_b200_dump_callback)(size_t layer, int32_t point, const float *values,
+                                             size_t rows, size_t columns, void *user_data);
+/* "block_output", "pre_norm", "mixer_input_projection", ...: the file-name suffixes of
+ * upstream's probe tool (tools/cuda_model_probe.cu:123-151); "" when out of range. */
+EVO_API const char *evo_b200_dump_point_name(int32_t point);
+EVO_API evo_status evo_b200_context_prefill_with_dumps(evo_context *context, const evo_batch *batch,
+                                                       const evo_b200_dump_request *requests,
+                                                       size_t request_count, int cached_attention,
+                                                       evo_b200_dump_callback dump_callback,
+                                                       evo_logits_callback logits_callback,
+                                                       void *user_data);
+EVO_API evo_status evo_b200_context_decode_with_dumps(evo_context *context, uint32_t token,
+                                                      const evo_b200_dump_request *requests,
+                                                      size_t request_count,
+                                                      evo_b200_dump_callback dump_callback,
+                                                      evo_logits_callback logits_callback,
+                                                      void *user_data);
+
 /* ---- variant-effect windows (host-only; need no GPU).
  * The sequence logic of upstream's `evo variant-score` driver
  * (src/variant.cpp:69-174, called from src/cuda/inference_cli.cpp:801-815):

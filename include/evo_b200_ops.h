@@ -119,10 +119,14 @@ EVO_B200_API int evo_b200_bf16_add_bias_inplace(void *output, const void *bias,
 EVO_B200_API int evo_b200_bf16_row_to_column_major(const void *input,
                                                    size_t rows, size_t columns,
                                                    void *output, void *stream);
-/* src/cuda/model.cu:269-284. tokens are uint32 ids on the device. */
+/* src/cuda/model.cu:269-284. tokens are uint32 ids on the device; `vocabulary`
+ * is the number of table rows.  An id >= vocabulary is never used as an index:
+ * its output row is zeros and the next evo_b200_check_async_errors on the
+ * device returns invalid_argument (upstream validates ids on the host,
+ * src/cuda/model.cu:1872-1880, before they reach the device). */
 EVO_B200_API int evo_b200_embedding(const uint32_t *tokens, const void *table,
-                                    size_t rows, size_t width, void *output,
-                                    void *stream);
+                                    size_t rows, size_t width, size_t vocabulary,
+                                    void *output, void *stream);
 
 /* include/evo/cuda/hyena.hpp (bf16_split_hyena_projection),
  * src/cuda/hyena.cu:194-208. */
@@ -272,8 +276,10 @@ EVO_B200_API int evo_b200_bf16_cached_cross_attention(
 /* ---- Dense-linear offload with the contract of upstream's LinearExecutor
  * (src/linear_executor.hpp:13-28; called from cpu::linear,
  * src/cpu/model.cpp:284-302): F32 host activations [rows, input_width], a host
- * weight [output_width, input_width] row-major (dtype 0 = F32, 1 = BF16: upstream
- * TensorDType kF32 / kBF16), optional bias (same dtypes), F32 host output
+ * weight [output_width, input_width] row-major (dtype 0 = F32, 1 = BF16, 2 = raw
+ * E4M3 codes decoded without a scale as upstream's Metal executor does,
+ * src/mps/model.mm:42-58: upstream TensorDType kF32 / kBF16 / kE4M3Software),
+ * optional bias (dtype 0 or 1), F32 host output
  * [rows, output_width].  Operands are split into BF16 planes (exact to 2^-24)
  * and multiplied on the tensor cores; their accumulator truncates, so results
  * agree with F32 arithmetic to a few 1e-6 of sum(|x||w|).  Device copies of weights are cached by
@@ -293,6 +299,19 @@ EVO_B200_API int evo_b200_linear_executor_linear(
     size_t input_width, const void *weight, int weight_dtype,
     size_t weight_elements, size_t output_width, const void *bias,
     int bias_dtype, size_t bias_elements, float *output);
+
+
+/* ---- host E4M3FN codec (no GPU needed): upstream evo::fp8
+ * (include/evo/fp8.hpp:9-18, src/fp8.cpp:26-77).  Round-to-nearest-even,
+ * satfinite (|v| >= 448 and infinities -> +-448), NaN -> 0x7f | sign.
+ * evo_b200_e4m3_scaled_roundtrip = decode(encode(value * scale)) * (1 / scale),
+ * NaN for a scale that is not positive and finite.  The array form encodes
+ * `count` values times `scale`. */
+EVO_B200_API uint8_t evo_b200_e4m3_encode(float value);
+EVO_B200_API float evo_b200_e4m3_decode(uint8_t code);
+EVO_B200_API float evo_b200_e4m3_scaled_roundtrip(float value, float scale);
+EVO_B200_API int evo_b200_e4m3_encode_array(const float *values, size_t count, float scale,
+                                            uint8_t *codes);
 
 #ifdef __cplusplus
 }

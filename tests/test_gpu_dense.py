@@ -168,8 +168,22 @@ def test_embedding_split_transpose_bias(ops, oracle):
     table = rand_bf16(rng, 512, 24)
     tokens = rng.integers(0, 512, 37).astype(np.uint32)
     out = empty_bits(37, 24)
-    ops.call("embedding", p(dev(tokens)), p(dev_bits(table)), 37, 24, p(out), stream())
+    ops.call("embedding", p(dev(tokens)), p(dev_bits(table)), 37, 24, 512, p(out), stream())
     assert np.array_equal(host_bits(out), table[tokens])
+    # an id outside the table is not dereferenced: zero row + a sticky invalid_argument
+    bad = tokens.copy()
+    bad[5] = 512
+    bad[20] = 0xFFFFFFFF
+    out = empty_bits(37, 24)
+    ops.call("embedding", p(dev(bad)), p(dev_bits(table)), 37, 24, 512, p(out), stream())
+    with pytest.raises(RuntimeError, match="token ID exceeds model vocabulary"):
+        ops.call("check_async_errors", stream())
+    got = host_bits(out)
+    assert not got[5].any() and not got[20].any()
+    keep = np.ones(37, bool)
+    keep[[5, 20]] = False
+    assert np.array_equal(got[keep], table[tokens[keep]])
+    ops.call("check_async_errors", stream())  # reported once, then clear
     proj = rand_bf16(rng, 11, 3 * 10)
     x2, x1, v = empty_bits(11, 10), empty_bits(11, 10), empty_bits(11, 10)
     ops.call("bf16_split_hyena_projection", p(dev_bits(proj)), 11, 10, p(x2), p(x1), p(v), stream())

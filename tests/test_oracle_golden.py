@@ -184,3 +184,44 @@ def test_operator_math_against_upstream_cpu_reference(oracle):
         fn(ptr(f32_to_bf16(q.reshape(t, -1))), ptr(f32_to_bf16(k.reshape(t, -1))),
            ptr(f32_to_bf16(v.reshape(t, -1))), t, t, heads, hd, ptr(out))
         _close(out, g["att_y"].reshape(t, -1), atol=5e-2, rtol=3e-2)
+
+
+def test_product_host_codec_matches_upstream_and_oracle(pkg, oracle):
+    """The library's own host E4M3FN codec (csrc/fp8_codec.cpp, upstream
+    src/fp8.cpp:26-77) against upstream's 29 known answers, upstream's encoder
+    over every BF16 bit pattern, and the oracle over a sweep of F32 patterns."""
+    lib = pkg.Ops().lib
+    for value, code in E4M3_KNOWN:
+        assert lib.evo_b200_e4m3_encode(value) == code, value
+    for value, code in [(1000.0, 0x7E), (-1000.0, 0xFE), (float("inf"), 0x7E), (float("-inf"), 0xFE)]:
+        assert lib.evo_b200_e4m3_encode(value) == code
+    assert lib.evo_b200_e4m3_encode(float("nan")) & 0x7F == 0x7F
+    golden = np.load(GOLDEN / "e4m3_exhaustive.npz")
+    values = bf16_to_f32(np.arange(65536, dtype=np.uint32).astype(np.uint16))
+    finite = ~np.isnan(values)
+    for scale in (1.0, 5.75, 0.03125):
+        codes = np.empty(65536, np.uint8)
+        with np.errstate(over="ignore", invalid="ignore"):
+            assert lib.evo_b200_e4m3_encode_array(ptr(np.ascontiguousarray(values)), 65536, scale, ptr(codes)) == 0
+        assert np.array_equal(codes[finite], golden[f"codes_scale_{scale}"][finite])
+    decoded = np.array([lib.evo_b200_e4m3_decode(c) for c in range(256)], np.float32)
+    keep = ~np.isnan(golden["decode"])
+    assert np.array_equal(decoded[keep], golden["decode"][keep]) and np.isnan(decoded[0x7F]) and np.isnan(decoded[0xFF])
+    # F32 patterns between the BF16 ones: every rounding boundary of the 126 finite
+    # codes and its float neighbours, plus a seeded sweep of all exponents
+    rng = np.random.default_rng(5)
+    sweep = rng.integers(0, 1 << 32, 200000, dtype=np.uint64).astype(np.uint32).view(np.float32)
+    grid = np.sort(golden["decode"][:0x7F].astype(np.float64))
+    mid = ((grid[1:] + grid[:-1]) / 2).astype(np.float32)
+    edges = np.concatenate([np.nextafter(mid, np.float32(0)), mid, np.nextafter(mid, np.float32(1e9))])
+    for batch in (sweep, edges, -edges):
+        batch = np.ascontiguousarray(batch[~np.isnan(batch)])
+        codes = np.empty(batch.size, np.uint8)
+        expected = np.empty(batch.size, np.uint8)
+        assert lib.evo_b200_e4m3_encode_array(ptr(batch), batch.size, 1.0, ptr(codes)) == 0
+        oracle.quantize_f32(ptr(batch), batch.size, 1.0, ptr(expected))
+        assert np.array_equal(codes, expected)
+    assert lib.evo_b200_e4m3_scaled_roundtrip(0.3, 4.0) == np.float32(lib.evo_b200_e4m3_decode(
+        lib.evo_b200_e4m3_encode(np.float32(0.3) * np.float32(4.0)))) * np.float32(0.25)
+    assert np.isnan(lib.evo_b200_e4m3_scaled_roundtrip(1.0, 0.0))
+    assert lib.evo_b200_e4m3_encode_array(ptr(batch), batch.size, -1.0, ptr(codes)) == 2

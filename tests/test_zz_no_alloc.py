@@ -32,15 +32,23 @@ def _case(rng, length, width, modes):
     return x2, x1, v, direct, log_poles, residues
 
 
-def _run(ops, entry, case, length, width, modes, scratch):
+def _prepare(case, length, width, modes, scratch, mode=0, initial_state=None):
+    """Every device buffer of one call, allocated up front: (argument list, out, pregate, state)."""
     x2, x1, v, direct, log_poles, residues = case
     out, pregate = empty_bits(length, width), empty_bits(length, width)
-    state = torch.full((width, modes), -3.0, device="cuda")
+    state = (torch.full((width, modes), -3.0, device="cuda") if initial_state is None
+             else torch.from_numpy(initial_state).cuda())
     args = [p(dev_bits(x2)), p(dev_bits(x1)), p(dev_bits(v)), p(dev_bits(direct)), p(dev(log_poles)),
-            p(dev(residues)), length, width, modes, 0, p(state)]
+            p(dev(residues)), length, width, modes, mode, p(state)]
     if scratch is not None:
         args.append(p(scratch))
-    ops.call(entry, *args, p(pregate), p(out), stream())
+    args += [p(pregate), p(out), stream()]
+    return args, out, pregate, state
+
+
+def _run(ops, entry, case, length, width, modes, scratch, mode=0, initial_state=None):
+    args, out, pregate, state = _prepare(case, length, width, modes, scratch, mode, initial_state)
+    ops.call(entry, *args)
     torch.cuda.synchronize()
     return host_bits(out), host_bits(pregate), state.cpu().numpy()
 
@@ -52,9 +60,7 @@ def test_noalloc_entry_matches_the_allocating_one_twice_in_a_row(ops):
         case = _case(rng, length, width, modes)
         scratch = torch.empty(ops.hcl_scratch_floats(length, width, modes), device="cuda")
         expected = _run(ops, "bf16_hcl_prefill", case, length, width, modes, scratch)
-        before = torch.cuda.memory_allocated()
         got = _run(ops, "bf16_hcl_prefill_noalloc", case, length, width, modes, None)
-        assert torch.cuda.memory_allocated() >= before  # only the test's own output tensors
         assert np.array_equal(got[1], expected[1])                       # u = bf16(x1 * v)
         assert_close_bits(got[0], expected[0], atol=0.04, rtol=0.03, min_cosine=0.9999)
         np.testing.assert_allclose(got[2], expected[2], rtol=2e-5, atol=2e-5)
@@ -79,3 +85,38 @@ def test_noalloc_entry_at_model_width_and_rejects_beyond_the_limit(ops):
                         p(dummy), 4, (4 << 20) // 16 + 2, 16, 0, None, None, p(dummy), stream())
     assert status == 2
     assert "fixed scratch of 4194304 floats" in ops.last_error()
+
+
+def test_noalloc_call_leaves_the_free_device_memory_unchanged(ops):
+    """cudaMemGetInfo sees every allocation on the device, whoever makes it.  With all buffers
+    of the call allocated beforehand and one earlier call behind us (the per-device set-up),
+    the free byte count is the same before and after a call."""
+    rng = np.random.default_rng(79)
+    length, width, modes = 1500, 256, 16
+    case = _case(rng, length, width, modes)
+    args, out, _, _ = _prepare(case, length, width, modes, None)
+    ops.call("bf16_hcl_prefill_noalloc", *args)
+    torch.cuda.synchronize()
+    first = host_bits(out).copy()
+    free_before = torch.cuda.mem_get_info()[0]
+    ops.call("bf16_hcl_prefill_noalloc", *args)
+    torch.cuda.synchronize()
+    assert torch.cuda.mem_get_info()[0] == free_before
+    assert np.array_equal(host_bits(out), first)
+
+
+def test_noalloc_continuation_from_a_carried_state_over_several_segments(ops):
+    """mode 1 continues from the state the caller passes in; with more than one row segment the
+    carried-in state travels through its own slot of the shared array.  Output and final state
+    equal the allocating entry point's bit for bit, on two calls in a row."""
+    rng = np.random.default_rng(80)
+    for length, width, modes in [(640, 128, 16), (2048, 512, 16)]:
+        case = _case(rng, length, width, modes)
+        carried = (rng.standard_normal((width, modes)) * 0.5).astype(np.float32)
+        scratch = torch.empty(ops.hcl_scratch_floats(length, width, modes), device="cuda")
+        expected = _run(ops, "bf16_hcl_prefill", case, length, width, modes, scratch, 1, carried)
+        got = _run(ops, "bf16_hcl_prefill_noalloc", case, length, width, modes, None, 1, carried)
+        assert np.array_equal(got[0], expected[0])
+        assert np.array_equal(got[1], expected[1])
+        assert np.array_equal(got[2], expected[2])
+        assert not np.array_equal(got[2], carried)
