@@ -250,6 +250,58 @@ def run_reference(args, rank: int, world: int) -> None:
     print(json.dumps(line))
 
 
+def measure_fp8_library_peak(seconds: float = 1.5) -> dict | None:
+    """Denominator for the E4M3 GEMMs: a library FP8 GEMM (torch._scaled_mm, cuBLASLt) at
+    8192^3, timed like the BF16 figures of MEASURED_PEAKS.json - best single launch (burst)
+    and back to back for `seconds` (sustained, under the power cap)."""
+    import torch
+
+    try:
+        n = 8192
+        a = torch.randn(n, n, device="cuda").to(torch.float8_e4m3fn)
+        b = torch.randn(n, n, device="cuda").to(torch.float8_e4m3fn).t()
+        one = torch.ones((), device="cuda")
+        run = lambda: torch._scaled_mm(a, b, scale_a=one, scale_b=one, out_dtype=torch.bfloat16)
+        for _ in range(3):
+            run()
+        torch.cuda.synchronize()
+        flops = 2.0 * n ** 3
+        best = float("inf")
+        for _ in range(10):
+            start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            start.record()
+            run()
+            stop.record()
+            torch.cuda.synchronize()
+            best = min(best, start.elapsed_time(stop))
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        count = max(10, int(seconds * 1e3 / best))
+        start.record()
+        for _ in range(count):
+            run()
+        stop.record()
+        torch.cuda.synchronize()
+        return {"fp8_tflops": flops / best / 1e9, "fp8_tflops_sustained": flops * count / start.elapsed_time(stop) / 1e9,
+                "how": f"torch._scaled_mm e4m3 8192^3, best of 10 and {count} launches back to back"}
+    except Exception as error:  # the library path is only a denominator
+        return {"fp8_tflops": None, "fp8_tflops_sustained": None, "how": f"unavailable: {error}"}
+
+
+def profile_flags(rt, name: str) -> int:
+    return {"exact": 0, "b200-tc": rt.CONTEXT_FLAG_TENSORCORE_FP8, "b200-fp8": rt.CONTEXT_FLAG_FP8_FFN}[name]
+
+
+def flop_classes(tokens: int, profile: str) -> dict:
+    """Algorithmic GEMM FLOPs of one prefill, by the operator class that runs them."""
+    hyena_layers = LAYERS - ATTENTION_LAYERS
+    projection = 2.0 * tokens * WIDTH * 3 * WIDTH * hyena_layers              # E4M3 Hyena input projections
+    ffn = 2.0 * tokens * (WIDTH * WIDTH + 3 * WIDTH * INNER) * LAYERS         # output + MLP projections
+    total = gemm_flops_per_token(tokens) * tokens
+    if profile == "b200-fp8" and tokens > 128:
+        return {"gemm_e4m3_tcgen05": projection, "gemm_e4m3_ffn_tcgen05": ffn, "gemm_bf16_tcgen05": total - projection - ffn}
+    return {"gemm_e4m3_tcgen05": projection, "gemm_e4m3_ffn_tcgen05": 0.0, "gemm_bf16_tcgen05": total - projection}
+
+
 def compare_logits(actual, expected) -> dict:
     """Agreement of two [rows, vocab] logit matrices: top-1 overall and on the rows whose winner
     in `expected` leads by more than four times the largest per-logit difference."""
@@ -291,7 +343,7 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> None:
     model = library.load(directory, devices=[local_rank])
     load_seconds = time.perf_counter() - load_start
     tokens = args.tokens
-    flags = rt.CONTEXT_FLAG_TENSORCORE_FP8
+    flags = profile_flags(rt, args.profile)
     context = model.context(tokens, flags)
     host_tokens = tokens_for(rank, tokens)
     device_tokens = torch.from_numpy(host_tokens.astype(np.int32)).cuda()
@@ -328,27 +380,45 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> None:
     # operator calls of the runtime; the modal scan is two kernels per call, plus the embedding
     launches_per_step = (sum(n for _, n in profile.values()) + profile.get("hcl_modal_scan", (0, 0))[1]) \
         // args.steps + 1
-    gemm_ms, gemm_launches = profile["gemm_bf16_tcgen05"]
-    fp8_ms, fp8_launches = profile["gemm_e4m3_tcgen05"]
-    hyena_layers = LAYERS - ATTENTION_LAYERS
-    flops_fp8 = 2.0 * tokens * WIDTH * 3 * WIDTH * hyena_layers
-    flops_bf16 = gemm_flops_per_token(tokens) * tokens - flops_fp8
-    achieved = flops_bf16 * args.steps / (gemm_ms * 1e-3) / 1e12
+    classes = flop_classes(tokens, args.profile)
+    class_tflops = {name: (flops * args.steps / (profile[name][0] * 1e-3) / 1e12 if profile.get(name, (0, 0))[0] else None)
+                    for name, flops in classes.items()}
     peaks = {}
     peaks_file = ROOT / "MEASURED_PEAKS.json"
     if peaks_file.exists():
         peaks = json.loads(peaks_file.read_text())
-    peak = peaks.get("bf16_tflops_sustained", 1400.0)
-    roofline = {"bound": "tensor", "kernel": "gemm_tcgen05_kernel<bf16> (all BF16 projections of a step)",
+    bf16_peak = peaks.get("bf16_tflops_sustained", 1400.0)
+    fp8_library = measure_fp8_library_peak() if rank == 0 else None
+    fp8_peak = (fp8_library or {}).get("fp8_tflops_sustained") or 2.0 * bf16_peak
+    # the class that holds most of the step's time is the one the roofline line is about
+    dominant = max(("gemm_bf16_tcgen05", "gemm_e4m3_ffn_tcgen05"), key=lambda name: profile.get(name, (0, 0))[0])
+    fp8_dominant = dominant == "gemm_e4m3_ffn_tcgen05"
+    achieved = class_tflops[dominant]
+    peak = fp8_peak if fp8_dominant else bf16_peak
+    fp8_rates = [class_tflops[n] for n in ("gemm_e4m3_tcgen05", "gemm_e4m3_ffn_tcgen05") if class_tflops[n]]
+    roofline = {"bound": "tensor",
+                "kernel": ("gemm_tcgen05_kernel<e4m3> (output and MLP projections of a step)" if fp8_dominant else
+                           "gemm_tcgen05_kernel<bf16> (all BF16 projections of a step)"),
                 "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
-                "peak_source": "MEASURED_PEAKS.json bf16_tflops_sustained (of measured)" if peaks else
-                               "fallback 1.4 PFLOP/s sustained (of fallback)",
+                "peak_source": ("library E4M3 GEMM 8192^3 measured in this run, sustained (of measured)"
+                                if fp8_dominant and (fp8_library or {}).get("fp8_tflops_sustained") else
+                                "2 x MEASURED_PEAKS.json bf16_tflops_sustained (of measured)" if fp8_dominant else
+                                "MEASURED_PEAKS.json bf16_tflops_sustained (of measured)" if peaks else
+                                "fallback 1.4 PFLOP/s sustained (of fallback)"),
+                "class_tflops": class_tflops,
+                "fp8_library_peak": fp8_library,
+                "fp8_frac_of_measured": {n: class_tflops[n] / fp8_peak for n in
+                                         ("gemm_e4m3_tcgen05", "gemm_e4m3_ffn_tcgen05") if class_tflops[n]},
+                "fp8_frac_of_datasheet_4500": {n: class_tflops[n] / 4500.0 for n in
+                                               ("gemm_e4m3_tcgen05", "gemm_e4m3_ffn_tcgen05") if class_tflops[n]},
+                "bf16_frac_of_measured": class_tflops["gemm_bf16_tcgen05"] / bf16_peak
+                if class_tflops["gemm_bf16_tcgen05"] else None,
                 # DRAM read + write of one launch of this kernel from an ncu capture
                 # (M=8192 K=4096 N=8192: 256 MB algorithmic); the step's launches have other shapes
                 "traffic": 442.7e6,
                 "traffic_case": "ncu capture of gemm_tcgen05_kernel<bf16,256> at M=8192 K=4096 N=8192: "
                                 "332.1 MB read + 110.6 MB written against 256 MB algorithmic",
-                "fp8_projection_tflops": flops_fp8 * args.steps / (fp8_ms * 1e-3) / 1e12 if fp8_ms else None,
+                "fp8_projection_tflops": class_tflops["gemm_e4m3_tcgen05"],
                 "operator_ms_per_step": {k: v[0] / args.steps for k, v in profile.items() if v[1]}}
 
     # ---- end to end through the public C ABI: host bytes in, host F32 logits out
@@ -413,8 +483,8 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> None:
     decode = None
     if rank == 0 and args.decode_tokens > 0:
         decode = {}
-        for name, profile_flags in (("b200-tc", flags), ("exact", 0)):
-            ctx = model.context(min(tokens, 1024) + args.decode_tokens + 16, profile_flags)
+        for name, decode_flags in ((args.profile, flags), ("exact", 0)):
+            ctx = model.context(min(tokens, 1024) + args.decode_tokens + 16, decode_flags)
             prompt_logits = ctx.prefill(sequence[:min(tokens, 1024)])
             token = int(prompt_logits[-1].argmax())
             for _ in range(4):
@@ -482,10 +552,13 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> None:
             "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
             "scaling": "strong" if world == 1 else "weak", "vs_baseline": None,
-            "dtype": "bf16 activations, e4m3 Hyena projections (tcgen05), f32 accumulate",
+            "dtype": ("bf16 activations, e4m3 Hyena / output / MLP projections (tcgen05), f32 accumulate"
+                      if args.profile == "b200-fp8" else
+                      "bf16 activations, e4m3 Hyena projections (tcgen05), f32 accumulate"),
             "data": "synthetic",
             "config": {"workload": f"{SHAPE_TEXT}, "
-                                   f"batch-1 stateless prefill of {tokens} uniform-ACGT tokens, profile b200-tc",
+                                   f"batch-1 stateless prefill of {tokens} uniform-ACGT tokens, profile {args.profile}",
+                       "profile": args.profile,
                        "model_id": MODEL_ID, "seed": SEED, "tokens": tokens,
                        "parallelism": "1 GPU" if world == 1 else f"{world} independent replicas (one sequence per GPU)",
                        "l2_policy": "weights (12 GB) and activations exceed the 126 MB L2 every step; no flush needed",
@@ -538,7 +611,7 @@ def run_pipeline(args, rank: int, world: int, local_rank: int) -> None:
     model = library.load_slice(directory, local_rank, rank, world)
     load_seconds = time.perf_counter() - load_start
     tokens = args.tokens
-    flags = rt.CONTEXT_FLAG_TENSORCORE_FP8
+    flags = profile_flags(rt, args.profile)
     context = model.context(tokens, flags)
     host_tokens = tokens_for(0, tokens)
     pinned_tokens = torch.from_numpy(host_tokens.astype(np.int32)).pin_memory()
@@ -648,7 +721,8 @@ def run_pipeline(args, rank: int, world: int, local_rank: int) -> None:
                        "windows": len(pipe.window_plan(total, world, args.pipeline_chunk))}
 
     totals = torch.tensor([sum(n for _, n in profile.values()) + (1 if rank == 0 else 0) * args.steps,
-                           profile["gemm_bf16_tcgen05"][0], profile["gemm_e4m3_tcgen05"][0]],
+                           profile["gemm_bf16_tcgen05"][0], profile["gemm_e4m3_tcgen05"][0],
+                           profile["gemm_e4m3_ffn_tcgen05"][0]],
                           dtype=torch.float64, device="cuda")
     dist.all_reduce(totals)
     per_operator = torch.tensor([profile[name][0] for name in sorted(profile)], dtype=torch.float64, device="cuda")
@@ -658,21 +732,26 @@ def run_pipeline(args, rank: int, world: int, local_rank: int) -> None:
     dist.all_gather_object(layout, [rank, int(info.layer_begin), int(info.layer_end),
                                     round(info.weight_bytes / 2**30, 2)])
     if rank == 0:
-        launches, gemm_ms, fp8_ms = (float(x) for x in totals.tolist())
-        hyena_layers = LAYERS - ATTENTION_LAYERS
-        flops_fp8 = 2.0 * tokens * WIDTH * 3 * WIDTH * hyena_layers
-        flops_bf16 = gemm_flops_per_token(tokens) * tokens - flops_fp8
-        achieved = flops_bf16 * args.steps / (gemm_ms * 1e-3) / 1e12
+        launches, gemm_ms, fp8_ms, ffn_ms = (float(x) for x in totals.tolist())
+        classes = flop_classes(tokens, args.profile)
+        flops_fp8 = classes["gemm_e4m3_tcgen05"]
         peaks_file = ROOT / "MEASURED_PEAKS.json"
         peaks = json.loads(peaks_file.read_text()) if peaks_file.exists() else {}
-        peak = peaks.get("bf16_tflops_sustained", 1400.0)
+        fp8_dominant = ffn_ms > gemm_ms
+        # window sizes exceed 128 rows, so the FP8 FFN profile applies in every window
+        achieved = (classes["gemm_e4m3_ffn_tcgen05"] * args.steps / (ffn_ms * 1e-3) / 1e12 if fp8_dominant else
+                    classes["gemm_bf16_tcgen05"] * args.steps / (gemm_ms * 1e-3) / 1e12)
+        peak = peaks.get("bf16_tflops_sustained", 1400.0) * (2.0 if fp8_dominant else 1.0)
         line = {
             "metric": METRIC, "value": tokens / (single_ms * 1e-3), "unit": "tokens/s", "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": single_ms, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None,
-            "dtype": "bf16 activations, e4m3 Hyena projections (tcgen05), f32 accumulate", "data": "synthetic",
+            "dtype": ("bf16 activations, e4m3 Hyena / output / MLP projections (tcgen05), f32 accumulate"
+                      if args.profile == "b200-fp8" else
+                      "bf16 activations, e4m3 Hyena projections (tcgen05), f32 accumulate"), "data": "synthetic",
             "config": {"workload": f"{SHAPE_TEXT}, "
-                                   f"batch-1 stateless prefill of {tokens} uniform-ACGT tokens, profile b200-tc",
+                                   f"batch-1 stateless prefill of {tokens} uniform-ACGT tokens, profile {args.profile}",
+                       "profile": args.profile,
                        "model_id": MODEL_ID, "seed": SEED, "tokens": tokens,
                        "parallelism": f"pp{world}: one pipeline stage per rank, chunk wavefront, NCCL send/recv of "
                                       f"hidden rows; one prompt at a time (batch 1), barrier between prompts",
@@ -686,9 +765,12 @@ def run_pipeline(args, rank: int, world: int, local_rank: int) -> None:
             "e2e": {"value": tokens / e2e_seconds, "unit": "tokens/s", "h2d_bytes_per_step": 4 * tokens,
                     "d2h_bytes_per_step": 2 * tokens * VOCAB},
             "gpu_launches": int(launches),
-            "roofline": {"bound": "tensor", "kernel": "gemm_tcgen05_kernel<bf16> (all BF16 projections, all ranks)",
+            "roofline": {"bound": "tensor",
+                         "kernel": ("gemm_tcgen05_kernel<e4m3> (output and MLP projections, all ranks)" if fp8_dominant
+                                    else "gemm_tcgen05_kernel<bf16> (all BF16 projections, all ranks)"),
                          "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
-                         "peak_source": "MEASURED_PEAKS.json bf16_tflops_sustained (of measured)" if peaks else
+                         "peak_source": ("2 x MEASURED_PEAKS.json bf16_tflops_sustained (of measured)" if fp8_dominant
+                                         else "MEASURED_PEAKS.json bf16_tflops_sustained (of measured)") if peaks else
                                         "fallback 1.4 PFLOP/s sustained (of fallback)",
                          "traffic": None,
                          "fp8_projection_tflops": flops_fp8 * args.steps / (fp8_ms * 1e-3) / 1e12 if fp8_ms else None,
@@ -745,6 +827,9 @@ def main() -> None:
                         help="model shape (the headline metric is quoted on evo2_7b)")
     parser.add_argument("--long-tokens", type=int, default=0,
                         help="also time a chunked prefill of this many tokens (> --tokens; 0 disables)")
+    parser.add_argument("--profile", default="b200-tc", choices=["b200-tc", "b200-fp8"],
+                        help="execution profile that is timed (b200-fp8 also runs the output and MLP "
+                             "projections in E4M3)")
     parser.add_argument("--decode-tokens", type=int, default=64,
                         help="cached-decode steps timed after a 1,024-token prompt (0 disables)")
     args = parser.parse_args()

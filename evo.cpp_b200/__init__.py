@@ -28,6 +28,8 @@ OPS_SIGNATURES: dict[str, list] = {
     "evo_b200_software_e4m3_quantize_f32_codes": [_P, _Z, _F, _P, _P],
     "evo_b200_software_e4m3_h100_linear": [_P, _P, _Z, _Z, _Z, _F, _F, _P, _P, _P],
     "evo_b200_e4m3_tensorcore_linear": [_P, _P, _Z, _Z, _Z, _F, _F, _P, _P, _P],
+    "evo_b200_e4m3_quantize_rows": [_P, _Z, _Z, _P, _P, _P],
+    "evo_b200_e4m3_codes_linear": [_P, _P, _P, _P, _P, _Z, _Z, _Z, _F, _I, _I, _P, _P],
     "evo_b200_bf16_linear": [_P, _P, _P, _P, _Z, _Z, _Z, _I, _I, _P, _P],
     "evo_b200_bf16_linear_split_k": [_P, _P, _P, _P, _Z, _Z, _Z, _I, _I, _P, _Z, _P, _P],
     "evo_b200_bf16_gated_up_projection": [_P, _P, _Z, _Z, _Z, _I, _P, _P],

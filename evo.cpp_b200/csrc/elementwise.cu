@@ -89,6 +89,94 @@ __global__ void quantize_bf16_vec_kernel(const uint4 *__restrict__ input,
   }
 }
 
+// ---- per-row dynamic quantisation (FP8 FFN profile)
+// codes[r, :] = E4M3(x[r, :] * q_r) with q_r = 448 / max|x[r, :]|, and
+// row_scale[r] = 1 / q_r for the consuming GEMM's epilogue.  Persistent blocks
+// walk rows; a row is copied into shared memory once (cp.async, the next row in
+// flight while the current one is reduced and converted), so HBM sees 2 bytes
+// in and 1 byte out per element.  The magnitude maximum is taken on the packed
+// bit patterns (for BF16 magnitudes, integer order is value order).
+__global__ void __launch_bounds__(kThreads)
+quantize_rows_kernel(const bf16 *__restrict__ input, std::uint8_t *__restrict__ codes,
+                     float *__restrict__ row_scale, const std::size_t rows, const std::size_t width) {
+  extern __shared__ __align__(16) unsigned short row_cache[];  // 2 x width BF16 values
+  __shared__ unsigned int partial[kThreads / 32];
+  const auto fetch = [&](const std::size_t row, unsigned short *target) {
+    const uint4 *const source = reinterpret_cast<const uint4 *>(input + row * width);
+    for (std::size_t v = threadIdx.x; v < width / 8; v += kThreads) {
+      const std::uint32_t address =
+          static_cast<std::uint32_t>(__cvta_generic_to_shared(reinterpret_cast<uint4 *>(target) + v));
+      asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(address), "l"(source + v) : "memory");
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+  std::size_t row = blockIdx.x;
+  if (row >= rows) return;
+  fetch(row, row_cache);
+  const int vectors = static_cast<int>(width / 8);
+  for (int parity = 0; row < rows; row += gridDim.x, parity ^= 1) {
+    const unsigned short *const current = row_cache + parity * width;
+    const std::size_t next = row + gridDim.x;
+    if (next < rows) {
+      fetch(next, row_cache + (parity ^ 1) * width);
+      asm volatile("cp.async.wait_group 1;" ::: "memory");
+    } else {
+      asm volatile("cp.async.wait_group 0;" ::: "memory");
+    }
+    // a thread reads back exactly the 16-byte chunks it copied, so no barrier is needed before
+    // the reduction; the barriers inside it order this row's reads against the next refill
+    unsigned int high = 0U;
+    for (int v = threadIdx.x; v < vectors; v += kThreads) {
+      const uint4 raw = reinterpret_cast<const uint4 *>(current)[v];
+      high = __vmaxu2(high, __vmaxu2(__vmaxu2(raw.x & 0x7fff7fffU, raw.y & 0x7fff7fffU),
+                                     __vmaxu2(raw.z & 0x7fff7fffU, raw.w & 0x7fff7fffU)));
+    }
+    high = max(high & 0xffffU, high >> 16U);
+#pragma unroll
+    for (int offset = 16; offset > 0; offset /= 2) high = max(high, __shfl_xor_sync(0xffffffffU, high, offset));
+    if (threadIdx.x % 32 == 0) partial[threadIdx.x / 32] = high;
+    __syncthreads();
+    unsigned int magnitude = 0U;
+#pragma unroll
+    for (int w = 0; w < kThreads / 32; ++w) magnitude = max(magnitude, partial[w]);
+    magnitude = min(magnitude, 0x7f7fU);  // infinities and NaNs saturate
+    const float amax = __uint_as_float(magnitude << 16U);
+    const float quant = amax > 0.0F ? __fdiv_rn(448.0F, amax) : 1.0F;
+    if (threadIdx.x == 0) row_scale[row] = __fdiv_rn(1.0F, quant);
+    std::uint8_t *const out = codes + row * width;
+    for (int v = threadIdx.x; v < vectors; v += kThreads) {
+      Bf16x8 values;
+      values.raw = reinterpret_cast<const uint4 *>(current)[v];
+      unsigned int words[2] = {0U, 0U};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 scaled = make_float2(values.get(2 * j) * quant, values.get(2 * j + 1) * quant);
+        const unsigned int two = __nv_cvt_float2_to_fp8x2(scaled, __NV_SATFINITE, __NV_E4M3);
+        words[j / 2] |= two << (16 * (j % 2));
+      }
+      reinterpret_cast<uint2 *>(out)[v] = make_uint2(words[0], words[1]);
+    }
+    __syncthreads();  // partial[] and this half of the row cache are free again
+  }
+}
+
+// Largest magnitude of a BF16 tensor as a bit pattern (atomicMax on the patterns;
+// *result must start at zero).
+__global__ void amax_bf16_kernel(const uint4 *__restrict__ input, const std::size_t vectors,
+                                 unsigned int *__restrict__ result) {
+  unsigned int high = 0U;
+  const std::size_t stride = static_cast<std::size_t>(blockDim.x) * gridDim.x;
+  for (std::size_t i = static_cast<std::size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < vectors; i += stride) {
+    const uint4 raw = input[i];
+    high = __vmaxu2(high, __vmaxu2(__vmaxu2(raw.x & 0x7fff7fffU, raw.y & 0x7fff7fffU),
+                                   __vmaxu2(raw.z & 0x7fff7fffU, raw.w & 0x7fff7fffU)));
+  }
+  high = max(high & 0xffffU, high >> 16U);
+#pragma unroll
+  for (int offset = 16; offset > 0; offset /= 2) high = max(high, __shfl_xor_sync(0xffffffffU, high, offset));
+  if (threadIdx.x % 32 == 0 && high != 0U) atomicMax(result, high);
+}
+
 // ---------------------------------------------------------------- RMSNorm
 // One 256-thread block per row.  The F32 sum of squares is taken in the same
 // order as upstream (thread-strided columns, shuffle-down tree, 8 warp
@@ -460,6 +548,38 @@ int quantize_bf16(const void *input, const std::size_t elements,
         dequantized, elements, scale);
   }
   return check_launch("E4M3 quantise kernel");
+}
+
+int quantize_rows(const void *input, const std::size_t rows, const std::size_t width, void *codes,
+                  float *row_scale, cudaStream_t stream) {
+  if (input == nullptr || codes == nullptr || row_scale == nullptr || width == 0 || width % 8 != 0 ||
+      width > 49152 || !aligned16(input) || (reinterpret_cast<std::uintptr_t>(codes) & 7U) != 0)
+    return fail(kInvalidArgument, "row quantise arguments are invalid (width % 8, 16-byte aligned input)");
+  if (rows == 0) return kOk;
+  const std::size_t smem = 2 * width * sizeof(unsigned short);
+  if (smem + 1024 > 48 * 1024 &&
+      cudaFuncSetAttribute(quantize_rows_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                           static_cast<int>(smem)) != cudaSuccess)
+    return fail(kCuda, "cannot raise the row quantise shared-memory limit");
+  int resident = 0;
+  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&resident, quantize_rows_kernel, kThreads, smem) != cudaSuccess ||
+      resident < 1)
+    resident = 1;
+  const std::size_t grid = std::min<std::size_t>(rows, static_cast<std::size_t>(kSmCount) * resident);
+  quantize_rows_kernel<<<static_cast<unsigned int>(grid), kThreads, smem, stream>>>(
+      static_cast<const bf16 *>(input), static_cast<std::uint8_t *>(codes), row_scale, rows, width);
+  return check_launch("row quantise kernel");
+}
+
+int amax_bf16(const void *input, const std::size_t elements, unsigned int *result_bits, cudaStream_t stream) {
+  if (input == nullptr || result_bits == nullptr || elements % 8 != 0 || !aligned16(input))
+    return fail(kInvalidArgument, "amax arguments are invalid (elements % 8, 16-byte aligned input)");
+  if (cudaMemsetAsync(result_bits, 0, sizeof(unsigned int), stream) != cudaSuccess)
+    return fail(kCuda, "cannot clear the amax word");
+  if (elements == 0) return kOk;
+  amax_bf16_kernel<<<grid_for(elements / 8), kThreads, 0, stream>>>(static_cast<const uint4 *>(input),
+                                                                    elements / 8, result_bits);
+  return check_launch("amax kernel");
 }
 
 int quantize_f32(const float *input, const std::size_t elements,

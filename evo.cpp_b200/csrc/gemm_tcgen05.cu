@@ -42,6 +42,7 @@ struct EpilogueParams {
   const bf16 *residual;
   std::size_t ld_out;
   float alpha;
+  const float *row_scale;  // optional [M]: row r's accumulator is also multiplied by row_scale[r]
   int bias_mode;  // 0 none, 1 fused into the F32 sum, 2 separate BF16 add
   int gate_mode;  // 0 none, 1 first*second halves, 2 gelu(first)*second
   // F32 result mode (split-precision products): out_f32 = [out_f32 +] alpha*acc [+ bias_f32]
@@ -265,6 +266,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
       if (!mbar_wait(tmem_full_bar(acc), acc_phase, abort_flag)) break;
       tc_fence_after();
       const int row = m0 + quarter * 32 + lane;
+      const float scale = ep.row_scale != nullptr && row < M ? ep.alpha * ep.row_scale[row] : ep.alpha;
       const std::uint32_t taddr =
           tmem_base + acc * BN + (static_cast<std::uint32_t>(quarter * 32) << 16U);
       const bool gated = ep.gate_mode != 0;
@@ -284,7 +286,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
 #pragma unroll
             for (int j = 0; j < 32; ++j) {
               if (col + j < n_limit) {
-                float value = __uint_as_float(v[j]) * ep.alpha;
+                float value = __uint_as_float(v[j]) * scale;
                 if (ep.bias_f32 != nullptr) value += ep.bias_f32[col + j];
                 if (ep.accumulate_f32 != 0) value += out_row[col + j];
                 out_row[col + j] = value;
@@ -298,11 +300,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
           float r[32];
 #pragma unroll
           for (int j = 0; j < 32; ++j) {
-            float value = __uint_as_float(v[j]) * ep.alpha;
+            float value = __uint_as_float(v[j]) * scale;
             if (gated) {
               const float first =
                   ep.gate_mode == 2 ? bf2f(gelu_round(value)) : rbf(value);
-              const float second = rbf(__uint_as_float(w[j]) * ep.alpha);
+              const float second = rbf(__uint_as_float(w[j]) * scale);
               r[j] = rbf(first * second);
             } else {
               if (ep.bias_mode == 1 && col + j < n_limit)
@@ -578,7 +580,7 @@ gemm_simt_kernel(const void *__restrict__ a_raw, const void *__restrict__ b_raw,
     for (int j = 0; j < 4; ++j) {
       const int col = n0 + tx * 4 + j;
       if (col >= N) continue;
-      float value = acc[i][j] * ep.alpha;
+      float value = acc[i][j] * (ep.row_scale != nullptr ? ep.alpha * ep.row_scale[row] : ep.alpha);
       if (ep.bias_mode == 1) value += bf2f(ep.bias[col]);
       value = rbf(value);
       if (ep.bias_mode == 2) value = rbf(value + bf2f(ep.bias[col]));
@@ -605,7 +607,7 @@ splitk_finish_kernel(const float *__restrict__ partials, const int splits, const
       float value = 0.0F;
       for (int s = 0; s < splits; ++s)
         value += partials[static_cast<std::size_t>(s) * partial_stride + static_cast<std::size_t>(row) * N + column];
-      return value * ep.alpha;
+      return value * (ep.row_scale != nullptr ? ep.alpha * ep.row_scale[row] : ep.alpha);
     };
     float result;
     if (gated) {
@@ -819,7 +821,7 @@ int linear(const LinearArgs &args, cudaStream_t stream) {
   if (args.output_f32 != nullptr &&
       (fp8 || args.gate_mode != 0 || args.bias_mode != 0 || args.residual != nullptr))
     return fail(kInvalidArgument, "the F32-result mode takes BF16 operands and no BF16 epilogue");
-  if (args.output_f32 == nullptr && small_batch_linear_applicable(args))
+  if (args.output_f32 == nullptr && args.row_scale == nullptr && small_batch_linear_applicable(args))
     return small_batch_linear(args, stream);
   const std::size_t out_columns =
       args.gate_mode != 0 ? args.out_features / 2 : args.out_features;
@@ -829,6 +831,7 @@ int linear(const LinearArgs &args, cudaStream_t stream) {
   ep.residual = static_cast<const bf16 *>(args.residual);
   ep.ld_out = out_columns;
   ep.alpha = args.alpha;
+  ep.row_scale = args.row_scale;
   ep.bias_mode = args.bias_mode;
   ep.gate_mode = args.gate_mode;
   ep.out_f32 = args.output_f32;

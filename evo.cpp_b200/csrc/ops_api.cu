@@ -96,6 +96,35 @@ int evo_b200_e4m3_tensorcore_linear(const void *input, const void *weight,
                     input_scale, output_scale, scratch, output, as_stream(stream));
 }
 
+int evo_b200_e4m3_quantize_rows(const void *input, size_t rows, size_t width, void *codes_u8, float *row_scale,
+                                void *stream) {
+  return quantize_rows(input, rows, width, codes_u8, row_scale, as_stream(stream));
+}
+
+int evo_b200_e4m3_codes_linear(const void *input_codes, const float *row_scale, const void *weight_codes,
+                               const void *bias, const void *residual, size_t rows, size_t in_features,
+                               size_t out_features, float alpha, int bias_mode, int gate_mode, void *output,
+                               void *stream) {
+  LinearArgs args;
+  args.input = input_codes;
+  args.weight = weight_codes;
+  args.operand_type = OperandType::kE4m3;
+  args.row_scale = row_scale;
+  args.alpha = alpha;
+  args.bias = bias;
+  args.residual = residual;
+  args.output = output;
+  args.rows = rows;
+  args.in_features = in_features;
+  args.out_features = out_features;
+  args.bias_mode = bias == nullptr ? 0 : bias_mode;
+  args.gate_mode = gate_mode;
+  if (bias != nullptr && bias_mode != 1 && bias_mode != 2)
+    return fail(kInvalidArgument, "linear bias mode must be 1 or 2");
+  if (gate_mode < 0 || gate_mode > 2) return fail(kInvalidArgument, "gate mode must be 0, 1 or 2");
+  return linear(args, as_stream(stream));
+}
+
 int evo_b200_bf16_linear(const void *input, const void *weight,
                          const void *bias, const void *residual, size_t rows,
                          size_t in_features, size_t out_features,

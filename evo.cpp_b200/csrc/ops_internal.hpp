@@ -23,6 +23,12 @@ int quantize_bf16(const void *input, std::size_t elements, float scale,
                   void *codes, float *dequantized, cudaStream_t stream);
 int quantize_f32(const float *input, std::size_t elements, float scale,
                  void *codes, cudaStream_t stream);
+// Per-row dynamic quantisation of a BF16 matrix: codes[r, :] = E4M3(x[r, :] * q_r)
+// with q_r = 448 / max|x[r, :]| (1 for an all-zero row) and row_scale[r] = 1 / q_r.
+int quantize_rows(const void *input, std::size_t rows, std::size_t width, void *codes,
+                  float *row_scale, cudaStream_t stream);
+// Largest magnitude of a BF16 tensor, left on the device as a BF16 bit pattern.
+int amax_bf16(const void *input, std::size_t elements, unsigned int *result_bits, cudaStream_t stream);
 int rms_norm(const void *input, const float *scale, std::size_t rows,
              std::size_t width, float epsilon, void *output, void *codes,
              float quant_scale, cudaStream_t stream);
@@ -63,6 +69,9 @@ struct LinearArgs {
   std::size_t out_features = 0;
   OperandType operand_type = OperandType::kBf16;
   float alpha = 1.0F;  // applied to the F32 accumulator before rounding
+  // Optional per-row factor [rows] F32 (tile kernel only): the accumulator of row r
+  // is multiplied by alpha * row_scale[r] (dynamic per-row activation quantisation).
+  const float *row_scale = nullptr;
   int bias_mode = 0;   // 0 none, 1 fused F32 add, 2 separate BF16-rounded add
   int gate_mode = 0;   // 0 none, 1 a*b, 2 gelu(a)*b over 128-column halves
   bool force_simt = false;

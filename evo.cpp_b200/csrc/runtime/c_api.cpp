@@ -230,12 +230,15 @@ evo_status evo_context_create(const evo_model *model, const evo_context_params *
     }
     if ((p.flags & EVO_CONTEXT_FLAG_FAST_Q8_KV) != 0)
       return fail(evob::kUnsupported, "the fast-q8-kv profile is not available in this build");
-    const bool tensor_core = (p.flags & EVO_CONTEXT_FLAG_B200_TENSORCORE_FP8) != 0;
+    const bool fp8_ffn = (p.flags & EVO_CONTEXT_FLAG_B200_FP8_FFN) != 0;
+    const bool tensor_core = fp8_ffn || (p.flags & EVO_CONTEXT_FLAG_B200_TENSORCORE_FP8) != 0;
     auto context = std::make_unique<evo_context>();
-    context->profile = tensor_core ? "b200-tc" : "exact";
+    context->profile = fp8_ffn ? "b200-fp8" : tensor_core ? "b200-tc" : "exact";
     const int status = evob::Context::create(
         model->weights, p.context_size,
-        tensor_core ? evob::ExecutionProfile::kTensorCore : evob::ExecutionProfile::kExact,
+        fp8_ffn       ? evob::ExecutionProfile::kTensorCoreFfn
+        : tensor_core ? evob::ExecutionProfile::kTensorCore
+                      : evob::ExecutionProfile::kExact,
         (p.flags & EVO_CONTEXT_FLAG_B200_FULL_ARENA) != 0, &context->context);
     if (status != kOk) return status;
     *context_out = context.release();

@@ -230,7 +230,7 @@ Options parse(int argc, char **argv) {
       for (std::string item; std::getline(list, item, ',');) o.gpus.push_back(std::stoi(item));
     } else if (a == "--version") { std::cout << evo_version_string() << '\n'; std::exit(0); }
     else if (a == "--help" || a == "-h") {
-      std::cout << "usage:\n  evo run -m MODEL -p DNA -n TOKENS [--ctx N --gpu 0,1 --profile exact|b200-tc]\n"
+      std::cout << "usage:\n  evo run -m MODEL -p DNA -n TOKENS [--ctx N --gpu 0,1 --profile exact|b200-tc|b200-fp8]\n"
                    "  evo score -m MODEL --input FASTA_FASTQ_OR_TEXT\n"
                    "  evo bench -m MODEL --input FASTA_FASTQ_OR_TEXT [--warmup N --repetitions N]\n"
                    "  evo embed -m MODEL --input FASTA_FASTQ_OR_TEXT --output DIR --layer N "
@@ -241,8 +241,8 @@ Options parse(int argc, char **argv) {
     } else die(EVO_STATUS_INVALID_ARGUMENT, "unknown option " + a);
   }
   if (o.model.empty()) die(EVO_STATUS_INVALID_ARGUMENT, "a model path is required (-m)");
-  if (o.profile != "exact" && o.profile != "b200-tc")
-    die(EVO_STATUS_UNSUPPORTED, "profile must be exact or b200-tc");
+  if (o.profile != "exact" && o.profile != "b200-tc" && o.profile != "b200-fp8")
+    die(EVO_STATUS_UNSUPPORTED, "profile must be exact, b200-tc or b200-fp8");
   return o;
 }
 
@@ -255,6 +255,7 @@ evo_context *new_context(const evo_model *model, const Options &o) {
   evo_context_params params = evo_context_default_params();
   params.context_size = o.context;
   if (o.profile == "b200-tc") params.flags |= EVO_CONTEXT_FLAG_B200_TENSORCORE_FP8;
+  if (o.profile == "b200-fp8") params.flags |= EVO_CONTEXT_FLAG_B200_FP8_FFN;
   evo_context *context = nullptr;
   check(evo_context_create(model, &params, &context), "context");
   return context;

@@ -72,6 +72,8 @@ struct Context::Stage {
   // activations
   void *hidden = nullptr, *residual = nullptr, *normalized = nullptr, *mixer_out = nullptr;
   void *codes = nullptr, *projection = nullptr, *query = nullptr, *gated = nullptr;
+  void *codes_wide = nullptr;   // [T, I] E4M3 codes of the gated MLP activations (FP8 FFN profile)
+  float *row_scale = nullptr;   // [T] dequantisation factor of the row-quantised operand in flight
   void *mlp_first = nullptr, *mlp_second = nullptr;
   void *short_filtered = nullptr, *x2 = nullptr, *x1 = nullptr, *value = nullptr, *pregate = nullptr;
   float *modal_scratch = nullptr;
@@ -123,6 +125,8 @@ struct Context::Stage {
     for (void **p : {&hidden, &residual, &normalized, &mixer_out, &query, &x2, &x1, &value, &pregate})
       move(*p, D * 2);
     move(codes, D);
+    move(codes_wide, I);
+    if (row_scale != nullptr) row_scale += rows;
     move(projection, D * 6);
     move(short_filtered, D * 6);
     for (void **p : {&gated, &mlp_first, &mlp_second}) move(*p, I * 2);
@@ -281,7 +285,8 @@ int Context::dump_mixer_taps(Stage &s, const std::size_t i, const std::size_t ro
 // l2(x) and, in block 0, gelu(l1(x)).  The interleaved weight is multiplied
 // once more without the gate; its output row is [l1 block 0 | l2 block 0 | l1
 // block 1 | ...] in 128-column blocks, which two strided copies separate.
-int Context::dump_mlp_taps(Stage &s, const std::size_t i, const std::size_t rows, const DumpPlan &plan) {
+int Context::dump_mlp_taps(Stage &s, const std::size_t i, const std::size_t rows, const bool ffn8,
+                           const DumpPlan &plan) {
   const ModelConfig &c = weights_->config;
   const LayerWeights &w = s.weights->layers[i];
   const std::size_t D = c.width, I = c.inner_width, layer = s.weights->layer_begin + i;
@@ -303,6 +308,13 @@ int Context::dump_mlp_taps(Stage &s, const std::size_t i, const std::size_t rows
     a.rows = rows;
     a.in_features = D;
     a.out_features = 2 * I;
+    if (ffn8) {  // the row-quantised operand of the gated product is still in s.codes
+      a.input = s.codes;
+      a.weight = w.l12_codes;
+      a.operand_type = OperandType::kE4m3;
+      a.alpha = w.l12_dequant;
+      a.row_scale = s.row_scale;
+    }
     EVOB_TRY(linear(a, stream));
     const std::size_t blocks = rows * (I / 128);
     if (cudaMemcpy2DAsync(first.data, 256, raw.data, 512, 256, blocks, cudaMemcpyDeviceToDevice, stream) !=
@@ -421,6 +433,13 @@ int Context::create(std::shared_ptr<ModelWeights> weights, const std::size_t con
     EVOB_TRY(stage->allocate(&stage->mixer_out, T * D * 2, arena));
     EVOB_TRY(stage->allocate(&stage->query, T * D * 2, arena));
     EVOB_TRY(stage->allocate(&stage->codes, T * D, arena));
+    if (profile == ExecutionProfile::kTensorCoreFfn) {
+      EVOB_TRY(stage_weights->ensure_fp8_ffn(c));
+      EVOB_TRY(stage->allocate(&stage->codes_wide, T * I, arena));
+      void *scales = nullptr;
+      EVOB_TRY(stage->allocate(&scales, T * 4, arena));
+      stage->row_scale = static_cast<float *>(scales);
+    }
     EVOB_TRY(stage->allocate(&stage->projection, T * D * 6, arena));
     EVOB_TRY(stage->allocate(&stage->gated, T * I * 2, arena));
     if (!fused_gate) {
@@ -538,7 +557,8 @@ int Context::synchronize() {
 const char *profile_category_name(const int category) {
   static const char *const names[kProfileCategories] = {
       "rms_norm", "gemm_bf16_tcgen05", "gemm_e4m3_tcgen05", "gemm_e4m3_emulated", "hcs_fused_fir",
-      "hcm_fused_fir", "hcl_modal_scan", "attention", "state_step", "elementwise"};
+      "hcm_fused_fir", "hcl_modal_scan", "attention", "state_step", "elementwise", "row_quantize",
+      "gemm_e4m3_ffn_tcgen05"};
   return category >= 0 && category < kProfileCategories ? names[category] : "";
 }
 
@@ -600,6 +620,8 @@ int Context::run_stage(Stage &s, const std::size_t rows, const Mode mode,
                       w.projection_input_scale, stream));
     if (tap_pre_norm) EVOB_TRY(emit_bf16(stream, *tap, layer_index, DumpPoint::kPreNorm, s.normalized, rows, D));
     // input projection -> [rows, 3D]
+    // prefill chunks of the FP8 FFN profile: output and MLP projections in E4M3 as well
+    const bool ffn8 = profile_ == ExecutionProfile::kTensorCoreFfn && rows > 128 && w.out_codes != nullptr;
     if (fp8 && profile_ == ExecutionProfile::kExact) {
       EVOB_OP(kCatGemmEmulated, e4m3_emulated_gemm(s.codes, w.projection, rows, D, 3 * D,
                                   w.projection_output_scale, s.projection, stream));
@@ -807,7 +829,15 @@ int Context::run_stage(Stage &s, const std::size_t rows, const Mode mode,
       // fused for attention and single-row Hyena, separately rounded otherwise
       // (upstream src/cuda/model.cu:1768-1799)
       a.bias_mode = (attention || rows == 1) ? 1 : 2;
-      EVOB_OP(kCatGemmBf16, linear(a, stream));
+      if (ffn8) {
+        EVOB_OP(kCatRowQuantize, quantize_rows(s.mixer_out, rows, D, s.codes, s.row_scale, stream));
+        a.input = s.codes;
+        a.weight = w.out_codes;
+        a.operand_type = OperandType::kE4m3;
+        a.alpha = w.out_dequant;
+        a.row_scale = s.row_scale;
+      }
+      EVOB_OP(ffn8 ? kCatGemmFp8Ffn : kCatGemmBf16, linear(a, stream));
       if (tap != nullptr && tap->wants(layer_index, DumpPoint::kMixerProjection)) {
         // the projection before the residual joins it: the same product once more
         a.residual = nullptr;
@@ -834,7 +864,15 @@ int Context::run_stage(Stage &s, const std::size_t rows, const Mode mode,
       a.in_features = D;
       a.out_features = 2 * I;
       a.gate_mode = gelu_block ? 2 : 1;
-      EVOB_OP(kCatGemmBf16, linear(a, stream));
+      if (ffn8) {
+        EVOB_OP(kCatRowQuantize, quantize_rows(s.normalized, rows, D, s.codes, s.row_scale, stream));
+        a.input = s.codes;
+        a.weight = w.l12_codes;
+        a.operand_type = OperandType::kE4m3;
+        a.alpha = w.l12_dequant;
+        a.row_scale = s.row_scale;
+      }
+      EVOB_OP(ffn8 ? kCatGemmFp8Ffn : kCatGemmBf16, linear(a, stream));
     } else {
       LinearArgs a;
       a.split_workspace = s.split_workspace;
@@ -852,7 +890,7 @@ int Context::run_stage(Stage &s, const std::size_t rows, const Mode mode,
       EVOB_OP(kCatElementwise, gate(s.mlp_first, s.mlp_second, s.gated, rows * I, gelu_block, stream));
     }
     if (tap != nullptr) {
-      EVOB_TRY(dump_mlp_taps(s, i, rows, *tap));
+      EVOB_TRY(dump_mlp_taps(s, i, rows, ffn8, *tap));
       EVOB_TRY(emit_bf16(stream, *tap, layer_index, DumpPoint::kMlpGated, s.gated, rows, I));
     }
     {
@@ -866,7 +904,15 @@ int Context::run_stage(Stage &s, const std::size_t rows, const Mode mode,
       a.rows = rows;
       a.in_features = I;
       a.out_features = D;
-      EVOB_OP(kCatGemmBf16, linear(a, stream));
+      if (ffn8) {
+        EVOB_OP(kCatRowQuantize, quantize_rows(s.gated, rows, I, s.codes_wide, s.row_scale, stream));
+        a.input = s.codes_wide;
+        a.weight = w.l3_codes;
+        a.operand_type = OperandType::kE4m3;
+        a.alpha = w.l3_dequant;
+        a.row_scale = s.row_scale;
+      }
+      EVOB_OP(ffn8 ? kCatGemmFp8Ffn : kCatGemmBf16, linear(a, stream));
       if (tap != nullptr && tap->wants(layer_index, DumpPoint::kMlpOutput)) {
         a.residual = nullptr;
         a.output = s.query;

@@ -32,6 +32,8 @@ enum ProfileCategory : int {
   kCatAttention,       // QKV split/RoPE/append + attention
   kCatStateStep,       // continuation / decode FIR and state updates
   kCatElementwise,     // embedding, gates, splits
+  kCatRowQuantize,     // per-row E4M3 quantisation in front of the FP8 FFN / output projections
+  kCatGemmFp8Ffn,      // tcgen05 E4M3 output and MLP projections (profile b200-fp8)
   kProfileCategories
 };
 const char *profile_category_name(int category);
@@ -71,7 +73,9 @@ struct DumpPlan {
 // How E4M3 Hyena projections are evaluated.  kExact reproduces upstream's
 // software-QGMMA rounding bit for bit; kTensorCore uses tcgen05 FP8 MMAs with
 // F32 accumulation (its own execution profile, tolerance parity).
-enum class ExecutionProfile { kExact, kTensorCore };
+// kTensorCoreFfn additionally runs the output and MLP projections of prefill
+// chunks in E4M3 with dynamic per-row activation scales (profile "b200-fp8").
+enum class ExecutionProfile { kExact, kTensorCore, kTensorCoreFfn };
 
 struct ModelConfig {
   std::string architecture, model_id, model_name, artifact_profile;
@@ -101,6 +105,10 @@ struct LayerWeights {
   const void *l1 = nullptr, *l2 = nullptr, *l3 = nullptr;
   const void *l12 = nullptr;  // row-interleaved [2I, D] for the fused gate GEMM
   std::size_t payload_bytes = 0;
+  // E4M3 copies for the FP8 FFN profile (StageWeights::ensure_fp8_ffn): codes in the
+  // layout of the BF16 tensor, and 1 / (448 / max|w|) for the epilogue.
+  const void *out_codes = nullptr, *l12_codes = nullptr, *l3_codes = nullptr;
+  float out_dequant = 1.0F, l12_dequant = 1.0F, l3_dequant = 1.0F;
 };
 
 // Immutable device weights of one pipeline stage (one GPU).
@@ -112,6 +120,11 @@ struct StageWeights {
   const float *final_norm = nullptr;  // same
   void *slab = nullptr;
   std::size_t slab_bytes = 0, weight_bytes = 0;
+  // Quantises the output / MLP projection weights of every block once (first
+  // context of the FP8 FFN profile); later calls return at once.  Thread-safe.
+  int ensure_fp8_ffn(const ModelConfig &config);
+  void *ffn_slab = nullptr;
+  std::size_t ffn_slab_bytes = 0;
   ~StageWeights();
 };
 
@@ -217,7 +230,8 @@ class Context {
   // Taps of block `layer` of `stage` (dumps.cu-style helpers in model.cu).
   int dump_mixer_taps(Stage &stage, std::size_t local_layer, std::size_t rows, Mode mode,
                       const DumpPlan &dumps);
-  int dump_mlp_taps(Stage &stage, std::size_t local_layer, std::size_t rows, const DumpPlan &dumps);
+  int dump_mlp_taps(Stage &stage, std::size_t local_layer, std::size_t rows, bool fp8_ffn,
+                    const DumpPlan &dumps);
   // Chunk wavefront over the pipeline stages: chunk j runs on stage s while
   // chunk j+1 runs on stage s-1 (legal because every mixer carries causal
   // state).  Used for initial prefills on more than one stage.

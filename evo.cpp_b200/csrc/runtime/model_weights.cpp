@@ -10,7 +10,10 @@
 #include <cstring>
 #include <set>
 
+#include <mutex>
+
 #include "../common.cuh"
+#include "../ops_internal.hpp"
 #include "model.hpp"
 
 namespace evob {
@@ -199,13 +202,81 @@ int upload_layer(const ModelFile &file, const ModelConfig &c, const std::size_t 
 }  // namespace
 
 StageWeights::~StageWeights() {
-  if (slab != nullptr) {
+  if (slab != nullptr || ffn_slab != nullptr) {
     int previous = 0;
     cudaGetDevice(&previous);
     cudaSetDevice(device);
-    cudaFree(slab);
+    if (slab != nullptr) cudaFree(slab);
+    if (ffn_slab != nullptr) cudaFree(ffn_slab);
     cudaSetDevice(previous);
   }
+}
+
+// Per-tensor E4M3 copies of the output and MLP projection weights:
+// code = E4M3(w * q), q = 448 / max|w| (the algebra of upstream's checkpoint
+// converter for the Hyena input projections, tools/evo/checkpoint.py:100-112).
+int StageWeights::ensure_fp8_ffn(const ModelConfig &c) {
+  static std::mutex mutex;
+  std::lock_guard<std::mutex> lock(mutex);
+  if (ffn_slab != nullptr) return kOk;
+  const std::size_t D = c.width, I = c.inner_width;
+  for (const LayerWeights &w : layers)
+    if (w.l12 == nullptr)
+      return fail(kUnsupported, "the FP8 FFN profile needs the gate-fused MLP layout (inner width % 128 == 0)");
+  if (D % 16 != 0 || I % 16 != 0) return fail(kUnsupported, "the FP8 FFN profile needs widths divisible by 16");
+  int previous = 0;
+  cudaGetDevice(&previous);
+  struct Restore {
+    int device;
+    ~Restore() { cudaSetDevice(device); }
+  } restore{previous};
+  if (cudaSetDevice(device) != cudaSuccess) return fail(kCuda, "cannot select the stage's device");
+  const std::size_t per_layer = aligned(D * D) + aligned(2 * I * D) + aligned(D * I);
+  void *slab_memory = nullptr;
+  if (cudaMalloc(&slab_memory, per_layer * layers.size() + 256) != cudaSuccess)
+    return fail(kCuda, "cannot allocate " + std::to_string((per_layer * layers.size()) >> 20) +
+                           " MiB for the FP8 FFN weights on device " + std::to_string(device));
+  cudaStream_t stream = nullptr;
+  unsigned int *amax_word = nullptr;
+  int status = kOk;
+  if (cudaStreamCreateWithFlags(&stream, cudaStreamNonBlocking) != cudaSuccess ||
+      cudaMalloc(reinterpret_cast<void **>(&amax_word), sizeof(unsigned int)) != cudaSuccess)
+    status = fail(kCuda, "cannot set up the FP8 FFN weight conversion");
+  unsigned char *cursor = static_cast<unsigned char *>(slab_memory);
+  const auto convert = [&](const void *source, const std::size_t elements, const void **codes, float *dequant) {
+    if (status != kOk) return;
+    status = amax_bf16(source, elements, amax_word, stream);
+    unsigned int bits = 0;
+    if (status == kOk && (cudaMemcpyAsync(&bits, amax_word, sizeof(bits), cudaMemcpyDeviceToHost, stream) != cudaSuccess ||
+                          cudaStreamSynchronize(stream) != cudaSuccess))
+      status = fail(kCuda, "cannot read a weight's magnitude");
+    if (status != kOk) return;
+    bits = std::min(bits, 0x7f7fU) << 16U;
+    float amax = 0.0F;
+    std::memcpy(&amax, &bits, sizeof(amax));
+    const float quant = amax > 0.0F ? 448.0F / amax : 1.0F;
+    status = quantize_bf16(source, elements, quant, cursor, nullptr, stream);
+    *codes = cursor;
+    *dequant = 1.0F / quant;
+    cursor += aligned(elements);
+  };
+  for (LayerWeights &w : layers) {
+    convert(w.out_weight, D * D, &w.out_codes, &w.out_dequant);
+    convert(w.l12, 2 * I * D, &w.l12_codes, &w.l12_dequant);
+    convert(w.l3, D * I, &w.l3_codes, &w.l3_dequant);
+  }
+  if (status == kOk && cudaStreamSynchronize(stream) != cudaSuccess)
+    status = fail(kCuda, "FP8 FFN weight conversion failed");
+  if (amax_word != nullptr) cudaFree(amax_word);
+  if (stream != nullptr) cudaStreamDestroy(stream);
+  if (status != kOk) {
+    cudaFree(slab_memory);
+    for (LayerWeights &w : layers) w.out_codes = w.l12_codes = w.l3_codes = nullptr;
+    return status;
+  }
+  ffn_slab = slab_memory;
+  ffn_slab_bytes = per_layer * layers.size();
+  return kOk;
 }
 
 int load_weights(const ModelFile &file, const std::vector<int> &devices,

@@ -15,6 +15,7 @@ BACKEND_AUTO, BACKEND_CUDA, BACKEND_CPU = 0, 1, 2
 MODEL_FLAG_ALLOW_SYNTHETIC = 1
 CONTEXT_FLAG_TENSORCORE_FP8 = 1 << 8
 CONTEXT_FLAG_FULL_ARENA = 1 << 9
+CONTEXT_FLAG_FP8_FFN = 1 << 10
 
 DUMP_POINTS = ("block_output", "pre_norm", "mixer_input_projection", "mixer_short_filter", "mixer_short_state",
                "mixer_inner_state", "mixer_x2", "mixer_x1", "mixer_value", "mixer_pregate", "mixer_state",

@@ -6,8 +6,8 @@
  * upstream's libevo.so.1 can load this library instead.  Behind it sits the
  * sm_100a runtime of this repository (CUDA backend only; no CPU fallback).
  *
- * Additions that do not change existing layouts: the context flag
- * EVO_CONTEXT_FLAG_B200_TENSORCORE_FP8, and the evo_b200_* extension entry
+ * Additions that do not change existing layouts: the context flags
+ * EVO_CONTEXT_FLAG_B200_*, and the evo_b200_* extension entry
  * points declared separately in evo_b200.h (not part of upstream's ABI).
  */
 #ifndef EVO_EVO_H
@@ -63,7 +63,18 @@ enum {
   /* Test fixtures normally get upstream's 8-row activation arena; this flag
    * gives them the production arena (8192 rows) so that long single-chunk
    * prefills of small synthetic models can be tested. */
-  EVO_CONTEXT_FLAG_B200_FULL_ARENA = 1u << 9u
+  EVO_CONTEXT_FLAG_B200_FULL_ARENA = 1u << 9u,
+  /* Profile "b200-fp8": as "b200-tc", and in prefill chunks of more than 128
+   * rows the output projection and the three MLP projections of every block
+   * also run as E4M3 tcgen05 GEMMs - weights quantised once per model with a
+   * per-tensor scale 448 / max|w|, activations quantised per row with
+   * 448 / max|row| just before each product, F32 accumulation, the BF16
+   * epilogues unchanged.  Upstream keeps these projections in BF16
+   * (src/cuda/ops.cu:1205-1245, src/cuda/model.cu:1787-1791, 1823-1825), so
+   * this is new arithmetic under its own name, with tolerance parity against
+   * "exact" (upstream's rule for approximate profiles:
+   * docs/execution-profiles.md:77-82).  Implies the tensor-core projections. */
+  EVO_CONTEXT_FLAG_B200_FP8_FFN = 1u << 10u
 };
 
 typedef struct evo_model evo_model;

@@ -54,6 +54,25 @@ EVO_B200_API int evo_b200_e4m3_tensorcore_linear(
     size_t in_features, size_t out_features, float input_scale,
     float output_scale, void *codes_scratch, void *output, void *stream);
 
+/* Dynamic per-row quantisation in front of an E4M3 product (profile
+ * "b200-fp8"; no upstream counterpart - upstream quantises with one static
+ * scale per tensor, src/cuda/ops.cu:250-262): codes[r,:] = E4M3(x[r,:] * q_r),
+ * q_r = 448 / max|x[r,:]| (1 for a zero row), row_scale[r] = 1 / q_r (F32
+ * [rows]).  width % 8 == 0, 16-byte aligned input. */
+EVO_B200_API int evo_b200_e4m3_quantize_rows(const void *input, size_t rows, size_t width,
+                                             void *codes_u8, float *row_scale, void *stream);
+/* y = epilogue(alpha * row_scale[r] * (codes_x . codes_w^T)) on the tcgen05 FP8
+ * tensor cores, F32 accumulation; bias / residual / gate as in
+ * evo_b200_bf16_linear and evo_b200_bf16_gated_up_projection (gate_mode 0 none,
+ * 1 product of the interleaved 128-column halves, 2 GELU on the first half;
+ * a gated call takes no bias or residual and writes out_features / 2 columns).
+ * row_scale may be NULL. */
+EVO_B200_API int evo_b200_e4m3_codes_linear(const void *input_codes, const float *row_scale,
+                                            const void *weight_codes, const void *bias,
+                                            const void *residual, size_t rows, size_t in_features,
+                                            size_t out_features, float alpha, int bias_mode,
+                                            int gate_mode, void *output, void *stream);
+
 /* include/evo/cuda/ops.hpp:37-68, src/cuda/ops.cu:535-748: y = x W^T with
  * W [out,in]; bias_mode 0 none, 1 fused into the F32 sum (cuBLASLt BIAS
  * epilogue upstream), 2 separate BF16-rounded add

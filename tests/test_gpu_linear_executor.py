@@ -1,5 +1,5 @@
 """Dense-linear offload with upstream's LinearExecutor contract
-(src/linear_executor.hpp:13-28): F32 host activations, F32 or BF16 host weights,
+(src/linear_executor.hpp:13-28): F32 host activations, F32, BF16 or E4M3 host weights,
 optional bias, F32 host output - about 18 bits of the absolute sum from BF16-plane
 products on the tensor cores, weights cached by host address."""
 from __future__ import annotations
@@ -10,7 +10,7 @@ import numpy as np
 import pytest
 
 pytestmark = pytest.mark.gpu
-F32, BF16 = 0, 1
+F32, BF16, E4M3 = 0, 1, 2
 
 
 def to_bf16_bits(values: np.ndarray) -> np.ndarray:
@@ -72,6 +72,24 @@ def test_matches_float64_reference(ops, executor, rows, k, n, weight_dtype):
     assert np.all(np.abs(first - (want - bias_value)) <= budget + 1e-7)
 
 
+def test_e4m3_weight_views_are_decoded_like_upstreams_executor(ops, executor):
+    """The 1B- and 40B-shaped artifacts carry E4M3 projection weights; upstream's Metal executor
+    decodes the raw codes without a scale (src/mps/model.mm:42-58).  Every finite code is a BF16
+    value, so the product is as exact as with BF16 weights."""
+    rng = np.random.default_rng(8)
+    rows, k, n = 70, 1920, 320
+    x = np.ascontiguousarray(rng.standard_normal((rows, k)).astype(np.float32))
+    codes = rng.integers(0, 256, (n, k)).astype(np.uint8)
+    codes[(codes & 0x7F) == 0x7F] = 0x38                      # no NaN codes in a weight
+    decoded = np.array([ops.lib.evo_b200_e4m3_decode(c) for c in range(256)], np.float32)
+    w_value = decoded[codes] * np.float32(1.0)
+    bias = (rng.standard_normal(n) * 0.5).astype(np.float32)
+    got = run(ops, executor, x, codes, E4M3, bias, F32)
+    want = x.astype(np.float64) @ w_value.astype(np.float64).T + bias
+    budget = (np.abs(x).astype(np.float64) @ np.abs(w_value).astype(np.float64).T + np.abs(bias)) * 4e-6
+    assert np.all(np.abs(got - want) <= budget + 1e-7)
+
+
 def test_contract_errors(ops, executor):
     assert ops.lib.evo_b200_linear_executor_name() == b"b200-tcgen05-bf16x3"
     x = np.zeros((2, 64), np.float32)
@@ -80,8 +98,10 @@ def test_contract_errors(ops, executor):
     # inconsistent dimensions: upstream's "internal" status
     assert ops.status("linear_executor_linear", executor, x.ctypes.data, 2, 64, w.ctypes.data, F32, 100, 64, None,
                       0, 0, out.ctypes.data) == 70
-    assert ops.status("linear_executor_linear", executor, x.ctypes.data, 2, 64, w.ctypes.data, 2, w.size, 64, None,
-                      0, 0, out.ctypes.data) == 5      # E4M3 weights stay on the host
+    assert ops.status("linear_executor_linear", executor, x.ctypes.data, 2, 64, w.ctypes.data, 3, w.size, 64, None,
+                      0, 0, out.ctypes.data) == 5      # no such weight type
+    assert ops.status("linear_executor_linear", executor, x.ctypes.data, 2, 64, w.ctypes.data, F32, w.size, 64,
+                      w.ctypes.data, E4M3, 64, out.ctypes.data) == 5   # biases are F32 or BF16
     narrow = np.zeros((8, 64), np.float32)
     assert ops.status("linear_executor_linear", executor, x.ctypes.data, 2, 64, narrow.ctypes.data, F32, narrow.size,
                       8, None, 0, 0, out.ctypes.data) == 5

@@ -161,3 +161,57 @@ def test_1b_shaped_e4m3_exact_profile_against_tensor_core_profile(rt, evo, tmp_p
     assert decided == 1.0, on_logits
     # the emulation profile is deterministic
     assert np.array_equal(model.context(1024).prefill(sequence), logits_exact)
+
+
+def test_1b_shaped_fp8_ffn_profile_against_exact_and_upstream(rt, evo, tmp_path_factory):
+    """Profile b200-fp8 (output and MLP projections in E4M3 with per-row activation scales, on top of
+    the tensor-core Hyena projections) on the same 1,024 tokens: against `exact` on the E4M3
+    artifact, and - with the BF16 twin, where only the FFN side is quantised - against upstream's
+    CPU backend.  Every product now carries E4M3 operand noise (2^-4 relative per element), so the
+    gates are wider than for b200-tc and are this profile's own: per-block and logit cosine >=
+    0.995, logit MAE <= 0.1, and no top-1 change outside the band the per-logit error explains."""
+    gen = _generator()
+    sequence = gen.prompt()
+    path = gen.write_artifact(tmp_path_factory.mktemp("model_1b_fp8_ffn"), fp8=True)
+    model = evo.load(path)
+    rows_wanted = np.arange(0, 1024, 8)
+    exact = model.context(1024)
+    fast = model.context(1024, flags=rt.CONTEXT_FLAG_FP8_FFN)
+    assert fast.profile == "b200-fp8"
+    logits_exact, blocks_exact, _ = _block_outputs(exact, sequence, rows_wanted)
+    logits_fast, blocks_fast, _ = _block_outputs(fast, sequence, rows_wanted)
+    table = []
+    for layer in range(LAYERS):
+        entry = _errors(blocks_fast[layer], blocks_exact[layer])
+        entry["layer"] = layer
+        table.append(entry)
+    on_logits = _errors(logits_fast, logits_exact)
+    overall, decided, count = _top1(logits_fast, logits_exact, 0.1)
+    on_logits.update(top1=overall, top1_decided_margin_0p1=decided, decided_rows=count)
+    report = {"vs_exact": {"blocks": table, "logits": on_logits}}
+    for entry in table:
+        assert entry["cosine"] >= 0.995, entry
+    assert on_logits["cosine"] >= 0.995 and on_logits["mean_abs"] <= 0.1, on_logits
+    flipped = logits_fast.argmax(-1) != logits_exact.argmax(-1)
+    top = np.take_along_axis(logits_exact, logits_exact.argmax(-1)[:, None], 1)[:, 0]
+    chosen = np.take_along_axis(logits_exact, logits_fast.argmax(-1)[:, None], 1)[:, 0]
+    assert np.all((top - chosen)[flipped] <= 2.0 * on_logits["max_abs"]), on_logits
+    assert overall >= 0.85, on_logits
+    model.close()
+    if GOLDEN.exists():
+        golden = np.load(GOLDEN)
+        twin = evo.load(gen.write_artifact(tmp_path_factory.mktemp("model_1b_bf16_ffn")))
+        logits, sampled, _ = _block_outputs(twin.context(1024, flags=rt.CONTEXT_FLAG_FP8_FFN), sequence,
+                                            golden["block_rows"])
+        expected_logits = golden["logits"].astype(np.float32)
+        blocks = []
+        for layer in range(LAYERS):
+            entry = _errors(sampled[layer], golden[f"block_{layer}"].astype(np.float32))
+            entry["layer"] = layer
+            blocks.append(entry)
+        against_upstream = _errors(logits, expected_logits)
+        overall, decided, count = _top1(logits, expected_logits, 0.1)
+        against_upstream.update(top1=overall, top1_decided_margin_0p1=decided, decided_rows=count)
+        report["bf16_twin_vs_upstream_cpu"] = {"blocks": blocks, "logits": against_upstream}
+        assert against_upstream["cosine"] >= 0.995 and against_upstream["mean_abs"] <= 0.1, against_upstream
+    _report("parity_1b_b200_fp8_profile", report)
