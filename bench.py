@@ -478,6 +478,42 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> None:
             by_length[str(length)] = {"ms": ms, "tokens_per_second": length / (ms * 1e-3)}
             short.close()
 
+    # ---- the opt-in profile with E4M3 output / MLP projections, measured beside the headline one
+    # (same prompt, device-resident tokens; its parity against `exact` is reported, not claimed)
+    other_profile = None
+    if rank == 0 and args.profile == "b200-tc" and tokens > 128 and not args.skip_fp8_profile:
+        fp8_context = model.context(tokens, rt.CONTEXT_FLAG_FP8_FFN)
+        fp8_stream = torch.cuda.ExternalStream(fp8_context.stream())
+        for _ in range(3):
+            fp8_context.prefill_device(device_tokens.data_ptr(), tokens, True)
+        fp8_context.synchronize()
+        begin_event, end_event = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        begin_event.record(fp8_stream)
+        for _ in range(args.steps):
+            fp8_context.prefill_device(device_tokens.data_ptr(), tokens, True)
+        end_event.record(fp8_stream)
+        fp8_context.synchronize()
+        fp8_ms = begin_event.elapsed_time(end_event) / args.steps
+        fp8_context.profile_enable(True)
+        fp8_context.prefill_device(device_tokens.data_ptr(), tokens, True)
+        fp8_context.synchronize()
+        fp8_profile = fp8_context.profile_read()
+        fp8_context.close()
+        head = min(tokens, 1024)
+        short = model.context(head, rt.CONTEXT_FLAG_FP8_FFN)
+        fp8_logits = short.prefill(sequence[:head])
+        short.close()
+        ffn_flops = flop_classes(tokens, "b200-fp8")["gemm_e4m3_ffn_tcgen05"]
+        ffn_tflops = ffn_flops / (fp8_profile["gemm_e4m3_ffn_tcgen05"][0] * 1e-3) / 1e12
+        other_profile = {
+            "profile": "b200-fp8", "ms_per_step": fp8_ms, "tokens_per_second": tokens / (fp8_ms * 1e-3),
+            "ffn_gemm_tflops": ffn_tflops, "ffn_gemm_frac_of_measured_fp8": ffn_tflops / fp8_peak,
+            "ffn_gemm_frac_of_datasheet_4500": ffn_tflops / 4500.0,
+            "operator_ms_per_step": {k: v[0] for k, v in fp8_profile.items() if v[1]},
+            "vs_exact_first_1024_tokens": compare_logits(fp8_logits, exact_logits),
+            "note": "E4M3 rounding of every output / MLP projection operand (~3.8 % per product) is amplified "
+                    "by the gated MLPs of a random-init model; this profile is not parity-green on synthetic weights"}
+
     # ---- cached decode after a 1,024-token prompt (greedy, host sampler, one
     # evo_context_decode call per token: logits come back to the host each step)
     decode = None
@@ -569,7 +605,7 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> None:
             "gflop_per_token": gemm_flops_per_token(tokens) / 1e9,
             "model_tflops": gemm_flops_per_token(tokens) * tokens / (ms_per_step * 1e-3) / 1e12,
             "roofline": roofline, "clocks": clocks.summary(),
-            "parity": parity, "prefill_by_length": by_length,
+            "parity": parity, "prefill_by_length": by_length, "fp8_ffn_profile": other_profile,
             "cached_decode_after_1024_token_prompt": decode,
             "layer_pipeline": pipeline,
             "long_prompt_chunked_prefill": long_prompt,
@@ -830,6 +866,8 @@ def main() -> None:
     parser.add_argument("--profile", default="b200-tc", choices=["b200-tc", "b200-fp8"],
                         help="execution profile that is timed (b200-fp8 also runs the output and MLP "
                              "projections in E4M3)")
+    parser.add_argument("--skip-fp8-profile", action="store_true",
+                        help="do not also time the opt-in b200-fp8 profile")
     parser.add_argument("--decode-tokens", type=int, default=64,
                         help="cached-decode steps timed after a 1,024-token prompt (0 disables)")
     args = parser.parse_args()

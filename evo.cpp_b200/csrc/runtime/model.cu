@@ -412,6 +412,8 @@ int Context::create(std::shared_ptr<ModelWeights> weights, const std::size_t con
   std::unique_ptr<Context> context(new Context());
   context->weights_ = weights;
   context->profile_ = profile;
+  if (const char *const parts = std::getenv("EVO_B200_FP8_FFN_PARTS"))
+    context->fp8_ffn_parts_ = static_cast<unsigned>(std::strtoul(parts, nullptr, 0)) & 7U;
   context->context_size_ = context_size;
   context->arena_rows_ = std::min(
       context_size, c.test_fixture && !full_arena_for_fixtures ? kFixtureArenaRows : kArenaRows);
@@ -829,7 +831,8 @@ int Context::run_stage(Stage &s, const std::size_t rows, const Mode mode,
       // fused for attention and single-row Hyena, separately rounded otherwise
       // (upstream src/cuda/model.cu:1768-1799)
       a.bias_mode = (attention || rows == 1) ? 1 : 2;
-      if (ffn8) {
+      const bool out8 = ffn8 && (fp8_ffn_parts_ & 1U) != 0;
+      if (out8) {
         EVOB_OP(kCatRowQuantize, quantize_rows(s.mixer_out, rows, D, s.codes, s.row_scale, stream));
         a.input = s.codes;
         a.weight = w.out_codes;
@@ -837,7 +840,7 @@ int Context::run_stage(Stage &s, const std::size_t rows, const Mode mode,
         a.alpha = w.out_dequant;
         a.row_scale = s.row_scale;
       }
-      EVOB_OP(ffn8 ? kCatGemmFp8Ffn : kCatGemmBf16, linear(a, stream));
+      EVOB_OP(out8 ? kCatGemmFp8Ffn : kCatGemmBf16, linear(a, stream));
       if (tap != nullptr && tap->wants(layer_index, DumpPoint::kMixerProjection)) {
         // the projection before the residual joins it: the same product once more
         a.residual = nullptr;
@@ -853,6 +856,7 @@ int Context::run_stage(Stage &s, const std::size_t rows, const Mode mode,
     if (tap != nullptr)
       EVOB_TRY(emit_bf16(stream, *tap, layer_index, DumpPoint::kPostNorm, s.normalized, rows, D));
     const bool gelu_block = layer_index == 0;
+    const bool up8 = ffn8 && (fp8_ffn_parts_ & 2U) != 0, down8 = ffn8 && (fp8_ffn_parts_ & 4U) != 0;
     if (w.l12 != nullptr) {
       LinearArgs a;
       a.split_workspace = s.split_workspace;
@@ -864,7 +868,7 @@ int Context::run_stage(Stage &s, const std::size_t rows, const Mode mode,
       a.in_features = D;
       a.out_features = 2 * I;
       a.gate_mode = gelu_block ? 2 : 1;
-      if (ffn8) {
+      if (up8) {
         EVOB_OP(kCatRowQuantize, quantize_rows(s.normalized, rows, D, s.codes, s.row_scale, stream));
         a.input = s.codes;
         a.weight = w.l12_codes;
@@ -872,7 +876,7 @@ int Context::run_stage(Stage &s, const std::size_t rows, const Mode mode,
         a.alpha = w.l12_dequant;
         a.row_scale = s.row_scale;
       }
-      EVOB_OP(ffn8 ? kCatGemmFp8Ffn : kCatGemmBf16, linear(a, stream));
+      EVOB_OP(up8 ? kCatGemmFp8Ffn : kCatGemmBf16, linear(a, stream));
     } else {
       LinearArgs a;
       a.split_workspace = s.split_workspace;
@@ -890,7 +894,7 @@ int Context::run_stage(Stage &s, const std::size_t rows, const Mode mode,
       EVOB_OP(kCatElementwise, gate(s.mlp_first, s.mlp_second, s.gated, rows * I, gelu_block, stream));
     }
     if (tap != nullptr) {
-      EVOB_TRY(dump_mlp_taps(s, i, rows, ffn8, *tap));
+      EVOB_TRY(dump_mlp_taps(s, i, rows, up8, *tap));
       EVOB_TRY(emit_bf16(stream, *tap, layer_index, DumpPoint::kMlpGated, s.gated, rows, I));
     }
     {
@@ -904,7 +908,7 @@ int Context::run_stage(Stage &s, const std::size_t rows, const Mode mode,
       a.rows = rows;
       a.in_features = I;
       a.out_features = D;
-      if (ffn8) {
+      if (down8) {
         EVOB_OP(kCatRowQuantize, quantize_rows(s.gated, rows, I, s.codes_wide, s.row_scale, stream));
         a.input = s.codes_wide;
         a.weight = w.l3_codes;
@@ -912,7 +916,7 @@ int Context::run_stage(Stage &s, const std::size_t rows, const Mode mode,
         a.alpha = w.l3_dequant;
         a.row_scale = s.row_scale;
       }
-      EVOB_OP(ffn8 ? kCatGemmFp8Ffn : kCatGemmBf16, linear(a, stream));
+      EVOB_OP(down8 ? kCatGemmFp8Ffn : kCatGemmBf16, linear(a, stream));
       if (tap != nullptr && tap->wants(layer_index, DumpPoint::kMlpOutput)) {
         a.residual = nullptr;
         a.output = s.query;

@@ -249,6 +249,9 @@ class Context {
   std::shared_ptr<ModelWeights> weights_;
   std::vector<std::unique_ptr<Stage>> stages_;
   ExecutionProfile profile_ = ExecutionProfile::kExact;
+  // Which projections the FP8 FFN profile quantises: bit 0 output projection, bit 1 MLP
+  // up-projections, bit 2 MLP down-projection (EVO_B200_FP8_FFN_PARTS, default all).
+  unsigned fp8_ffn_parts_ = 7U;
   std::size_t context_size_ = 0, arena_rows_ = 0, position_ = 0;
   bool state_valid_ = false, cached_attention_ = false, healthy_ = true;
   bool history_current_ = false;  // per-block projection history covers the rows up to position_

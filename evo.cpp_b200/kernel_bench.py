@@ -6,6 +6,8 @@
     python evo.cpp_b200/kernel_bench.py norm   --rows 8192 --width 4096
     python evo.cpp_b200/kernel_bench.py attention --rows 8192 --heads 32
     python evo.cpp_b200/kernel_bench.py sweep      # the operator shapes of the reference workloads
+    python evo.cpp_b200/kernel_bench.py grid       # E4M3 projection grid: M x {12288, 11264, 4096}, K = 4096, all modes
+    python evo.cpp_b200/kernel_bench.py fp8peak    # library E4M3 GEMM 8192^3 (the FP8 denominator)
 
 Inputs are seeded synthetic tensors with the shapes and value distributions of
 the reference workloads (BF16 N(0,1) activations, N(0,0.02) weights, modal poles
@@ -130,7 +132,60 @@ def bench_gemm(ops, timer, rows, inner, outer, kind):
                                 p(out), stream()))
     ops.call("check_async_errors", stream())
     name = "quantise+gemm_tcgen05_e4m3" if kind == "e4m3" else "quantise+qgmma_emulation"
-    return report(name, ms, flops=flops, rows=rows, inner=inner, outer=outer)
+    return report(name, ms, flops=flops, rows=rows, inner=inner, outer=outer,
+                  weight_gb_per_s=outer * inner / ms / 1e6)
+
+
+def bench_codes_gemm(ops, timer, rows, inner, outer):
+    """The E4M3 GEMM alone (operands already codes, per-row scales in the epilogue)."""
+    gen = torch.Generator(device="cuda").manual_seed(0)
+    x = torch.randn(rows, inner, device="cuda", generator=gen).bfloat16()
+    w = (torch.randn(outer, inner, device="cuda", generator=gen) * 0.02).bfloat16()
+    x_codes = torch.empty(rows, inner, dtype=torch.uint8, device="cuda")
+    scales = torch.empty(rows, device="cuda")
+    ops.call("e4m3_quantize_rows", p(x), rows, inner, p(x_codes), p(scales), stream())
+    w_scale = 448.0 / float(w.float().abs().max())
+    w_codes = (w.float() * w_scale).clamp(-448, 448).to(torch.float8_e4m3fn).view(torch.uint8)
+    out = torch.empty(rows, outer, device="cuda", dtype=torch.bfloat16)
+    ms = timer(lambda: ops.call("e4m3_codes_linear", p(x_codes), p(scales), p(w_codes), None, None, rows, inner,
+                                outer, 1.0 / w_scale, 0, 0, p(out), stream()))
+    ops.call("check_async_errors", stream())
+    line = report("gemm_tcgen05_e4m3_codes", ms, flops=2.0 * rows * inner * outer, rows=rows, inner=inner, outer=outer,
+                  weight_gb_per_s=outer * inner / ms / 1e6)
+    ms = timer(lambda: ops.call("e4m3_quantize_rows", p(x), rows, inner, p(x_codes), p(scales), stream()))
+    report("e4m3_quantize_rows", ms, bytes_moved=3.0 * rows * inner, rows=rows, width=inner)
+    return line
+
+
+def fp8_library_peak(seconds: float = 2.0):
+    n = 8192
+    a = torch.randn(n, n, device="cuda").to(torch.float8_e4m3fn)
+    b = torch.randn(n, n, device="cuda").to(torch.float8_e4m3fn).t()
+    one = torch.ones((), device="cuda")
+    run = lambda: torch._scaled_mm(a, b, scale_a=one, scale_b=one, out_dtype=torch.bfloat16)
+    for _ in range(3):
+        run()
+    torch.cuda.synchronize()
+    best = float("inf")
+    for _ in range(10):
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        run()
+        stop.record()
+        torch.cuda.synchronize()
+        best = min(best, start.elapsed_time(stop))
+    count = max(10, int(seconds * 1e3 / best))
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(count):
+        run()
+    stop.record()
+    torch.cuda.synchronize()
+    flops = 2.0 * n ** 3
+    print(json.dumps({"operator": "library_e4m3_gemm_8192^3 (torch._scaled_mm)", "ms_best": best,
+                      "fp8_tflops": flops / best / 1e9,
+                      "fp8_tflops_sustained": flops * count / start.elapsed_time(stop) / 1e9, "launches": count}),
+          flush=True)
 
 
 def bench_hyena_projection(ops, timer, length, channels, which):
@@ -227,7 +282,7 @@ def bench_attention(ops, timer, rows, heads):
 
 def main() -> None:
     parser = argparse.ArgumentParser()
-    parser.add_argument("what", choices=["gemm", "hyena", "norm", "attention", "sweep"])
+    parser.add_argument("what", choices=["gemm", "hyena", "norm", "attention", "sweep", "grid", "fp8peak"])
     parser.add_argument("--rows", type=int, default=8192)
     parser.add_argument("--inner", type=int, default=4096)
     parser.add_argument("--outer", type=int, default=12288)
@@ -252,6 +307,15 @@ def main() -> None:
         bench_norm(ops, timer, args.rows, args.width)
     elif args.what == "attention":
         bench_attention(ops, timer, args.rows, args.heads)
+    elif args.what == "fp8peak":
+        fp8_library_peak()
+    elif args.what == "grid":
+        for rows in (16, 128, 1024, 8192):
+            for outer in (12288, 11264, 4096):
+                for kind in ("emulated", "e4m3", "bf16"):
+                    line = bench_gemm(ops, timer, rows, 4096, outer, kind)
+                if rows > 128:
+                    bench_codes_gemm(ops, timer, rows, 4096, outer)
     else:
         for rows in (16, 128, 1024, 8192):
             for outer in (12288, 11264, 4096):
