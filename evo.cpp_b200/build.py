@@ -32,7 +32,7 @@ KERNEL_SOURCES = [
 OPS_SOURCES = KERNEL_SOURCES + ["ops_api.cu"]
 RUNTIME_SOURCES = KERNEL_SOURCES + [
     "runtime/safetensors.cpp", "runtime/model_load.cpp", "runtime/model_weights.cpp",
-    "runtime/model.cu", "runtime/sampler.cpp", "runtime/variant.cpp", "runtime/c_api.cpp",
+    "runtime/model.cu", "runtime/sampler.cpp", "runtime/variant.cpp", "runtime/variant_io.cpp", "runtime/c_api.cpp",
 ]
 
 
@@ -87,7 +87,7 @@ def build(force: bool = False) -> dict[str, Path]:
         if force or not lib.exists() or any(
                 o.stat().st_mtime > lib.stat().st_mtime for o in rt_objects):
             _link(rt_objects, lib, [
-                "-Xlinker", f"--version-script={CSRC / 'runtime' / 'evo.map'}",
+                "-lz", "-Xlinker", f"--version-script={CSRC / 'runtime' / 'evo.map'}",
                 "-Xlinker", "-soname=libevo.so.1"])
         outputs["evo"] = lib
         soname = HERE / "libevo.so.1"

@@ -291,10 +291,11 @@ modal_stream_kernel(const ModalParams p) {
 #pragma unroll
     for (int i = 0; i < kUnroll; ++i) rows[i] = next[i];
 #pragma unroll
-    for (int i = 0; i < kUnroll; ++i) next[i] = load_row(checked, base + kUnroll + i);
-#pragma unroll
     for (int i = 0; i < kUnroll; ++i) {
       const int t = base + i;
+      // one row's loads per row of arithmetic instead of a burst of kUnroll rows: the
+      // load / store queue of the SM is not flooded at the start of every group
+      next[i] = load_row(checked, base + kUnroll + i);
       if (kChecked && t >= t_end) break;
       std::uint32_t u_pair;  // u and the x2 gate of the pair, packed BF16
       [[maybe_unused]] std::uint32_t gate_pair = 0U;

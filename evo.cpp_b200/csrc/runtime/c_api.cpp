@@ -20,6 +20,7 @@
 #include "model.hpp"
 #include "sampler.hpp"
 #include "variant.hpp"
+#include "variant_io.hpp"
 
 struct evo_model {
   std::shared_ptr<evob::ModelFile> file;
@@ -33,6 +34,9 @@ struct evo_context {
 struct evo_batch {
   std::size_t capacity = 0;
   std::vector<std::vector<std::uint8_t>> sequences;
+};
+struct evo_b200_reference {
+  std::unique_ptr<evob::ReferenceFasta> fasta;
 };
 struct evo_sampler {
   explicit evo_sampler(const evob::SamplingConfig &config) : sampler(config) {}
@@ -615,6 +619,67 @@ evo_status evo_b200_reverse_complement(const char *sequence, size_t length, char
     const int status = evob::reverse_complement({sequence, length}, &reversed);
     if (status != kOk) return status;
     std::memcpy(output, reversed.data(), reversed.size());
+    return kOk;
+  });
+}
+
+evo_status evo_b200_vcf_stream(const char *path, evo_b200_vcf_callback callback, void *user_data) {
+  return protect([&]() -> int {
+    if (path == nullptr || callback == nullptr)
+      return fail(evob::kInvalidArgument, "VCF path and callback are required");
+    return evob::stream_vcf_file(path, [&](const evob::VcfRecord &record) -> int {
+      evo_b200_vcf_record view{};
+      view.struct_size = sizeof(view);
+      view.contig = record.contig.c_str();
+      view.id = record.id.c_str();
+      view.reference = record.reference.c_str();
+      view.alternate = record.alternate.c_str();
+      view.position_1based = record.position_1based;
+      view.record_index = record.record_index;
+      view.allele_index = record.allele_index;
+      view.line_number = record.line_number;
+      const evo_status status = callback(&view, user_data);
+      if (status == EVO_STATUS_OK) return kOk;
+      return fail(valid_status(status) ? status : EVO_STATUS_INTERNAL, "VCF consumer stopped the stream");
+    });
+  });
+}
+
+evo_status evo_b200_reference_open(const char *path, evo_b200_reference **reference_out) {
+  return protect([&]() -> int {
+    if (reference_out != nullptr) *reference_out = nullptr;
+    if (path == nullptr || reference_out == nullptr)
+      return fail(evob::kInvalidArgument, "reference path and output are required");
+    evob::ReferenceFasta *fasta = nullptr;
+    const int status = evob::ReferenceFasta::open(path, &fasta);
+    if (status != kOk) return status;
+    auto *handle = new evo_b200_reference();
+    handle->fasta.reset(fasta);
+    *reference_out = handle;
+    return kOk;
+  });
+}
+
+void evo_b200_reference_free(evo_b200_reference *reference) { delete reference; }
+
+evo_status evo_b200_reference_window(const evo_b200_reference *reference, const char *contig,
+                                     size_t position_1based, const char *reference_allele,
+                                     size_t reference_length, const char *alternate_allele,
+                                     size_t alternate_length, size_t maximum_tokens, size_t *start, size_t *end,
+                                     size_t *contig_length, char *sequence, size_t capacity) {
+  return protect([&]() -> int {
+    if (reference == nullptr || contig == nullptr || reference_allele == nullptr || alternate_allele == nullptr)
+      return fail(evob::kInvalidArgument, "reference window arguments are invalid");
+    evob::ReferenceSlice slice;
+    const int status = reference->fasta->slice(contig, position_1based, {reference_allele, reference_length},
+                                               {alternate_allele, alternate_length}, maximum_tokens, &slice);
+    if (status != kOk) return status;
+    if (sequence != nullptr && capacity < slice.sequence.size())
+      return fail(evob::kInvalidArgument, "reference window buffer is too small");
+    if (start != nullptr) *start = slice.start;
+    if (end != nullptr) *end = slice.end;
+    if (contig_length != nullptr) *contig_length = slice.contig_length;
+    if (sequence != nullptr) std::memcpy(sequence, slice.sequence.data(), slice.sequence.size());
     return kOk;
   });
 }

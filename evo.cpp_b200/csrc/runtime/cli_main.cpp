@@ -36,8 +36,9 @@ struct Options {
   float temperature = 1.0F, top_p = 1.0F;
   uint64_t seed = 0;
   bool allow_fixture = false;
-  // variant-score (inline form)
+  // variant-score: inline (--sequence --position --ref --alt) or file form (--vcf --reference)
   std::string sequence, reference_allele, alternate_allele, strand = "both", normalization = "sum";
+  std::string vcf_path, reference_path;
   size_t position = 0, window = 0;
 };
 
@@ -218,6 +219,8 @@ Options parse(int argc, char **argv) {
     else if (a == "--pooling") o.pooling = value(i);
     else if (a == "--allow-test-fixture") o.allow_fixture = true;
     else if (a == "--sequence") o.sequence = value(i);
+    else if (a == "--vcf") o.vcf_path = value(i);
+    else if (a == "--reference") o.reference_path = value(i);
     else if (a == "--position") o.position = std::stoull(value(i));
     else if (a == "--ref") o.reference_allele = value(i);
     else if (a == "--alt") o.alternate_allele = value(i);
@@ -236,7 +239,9 @@ Options parse(int argc, char **argv) {
                    "  evo embed -m MODEL --input FASTA_FASTQ_OR_TEXT --output DIR --layer N "
                    "--pooling none|mean|last\n"
                    "  evo variant-score -m MODEL --sequence DNA --position POS --ref REF --alt ALT "
-                   "[--window N --strand forward|reverse|both --normalization sum|mean]\n";
+                   "[--window N --strand forward|reverse|both --normalization sum|mean]\n"
+                   "  evo variant-score -m MODEL --vcf VARIANTS.vcf[.gz] --reference GENOME.fa "
+                   "[--window N --strand ... --normalization ...]\n";
       std::exit(0);
     } else die(EVO_STATUS_INVALID_ARGUMENT, "unknown option " + a);
   }
@@ -431,74 +436,136 @@ int main(int argc, char **argv) {
       ++record_index;
     }
   } else if (o.command == "variant-score") {
-    // Inline form of upstream's variant-effect driver (src/cuda/inference_cli.cpp:801-937):
-    // delta = LL(alternate window) - LL(reference window) per strand, averaged over strands.
-    if (o.sequence.empty() || o.position == 0 || o.reference_allele.empty() || o.alternate_allele.empty())
-      die(EVO_STATUS_INVALID_ARGUMENT, "variant-score needs --sequence, --position (1-based), --ref and --alt");
+    // Upstream's variant-effect driver (src/cuda/inference_cli.cpp:801-975): per allele,
+    // delta = LL(alternate window) - LL(reference window) per strand, averaged over strands; the
+    // alleles come from the command line or from a VCF whose windows are cut out of a reference FASTA.
+    const bool from_files = !o.vcf_path.empty() || !o.reference_path.empty();
+    if (from_files) {
+      if (o.vcf_path.empty() || o.reference_path.empty())
+        die(EVO_STATUS_INVALID_ARGUMENT, "variant-score needs --vcf and --reference together");
+      if (!o.sequence.empty() || o.position != 0 || !o.reference_allele.empty() || !o.alternate_allele.empty())
+        die(EVO_STATUS_INVALID_ARGUMENT, "--vcf/--reference cannot be combined with --sequence/--position/--ref/--alt");
+    } else if (o.sequence.empty() || o.position == 0 || o.reference_allele.empty() || o.alternate_allele.empty()) {
+      die(EVO_STATUS_INVALID_ARGUMENT, "variant-score needs --sequence, --position (1-based), --ref and --alt, "
+                                       "or --vcf and --reference");
+    }
     if (o.strand != "forward" && o.strand != "reverse" && o.strand != "both")
       die(EVO_STATUS_INVALID_ARGUMENT, "--strand must be one of forward, reverse, or both");
     if (o.normalization != "sum" && o.normalization != "mean")
       die(EVO_STATUS_INVALID_ARGUMENT, "--normalization must be one of sum or mean");
     const size_t window_tokens = o.window == 0 ? o.context : o.window;
     if (window_tokens > o.context) die(EVO_STATUS_INVALID_ARGUMENT, "--window must not exceed --ctx");
-    evo_b200_variant_window window{};
-    window.struct_size = sizeof(window);
-    std::string reference(window_tokens, '\0'), alternate(window_tokens, '\0');
-    check(evo_b200_variant_window_make(o.sequence.data(), o.sequence.size(), o.position,
-                                       o.reference_allele.data(), o.reference_allele.size(),
-                                       o.alternate_allele.data(), o.alternate_allele.size(), window_tokens,
-                                       &window, reference.data(), alternate.data(), window_tokens),
-          "variant window");
-    reference.resize(window.reference_length);
-    alternate.resize(window.alternate_length);
-    struct Strand {
-      const char *name;
-      WindowScore reference, alternate;
-      double delta;
-    };
-    std::vector<Strand> strands;
-    const auto score_strand = [&](const char *name, const std::string &ref, const std::string &alt) {
-      Strand strand{name, score_window(model, o, ref, vocab, &metrics, &last_context),
-                    score_window(model, o, alt, vocab, &metrics, &last_context), 0.0};
-      if (o.normalization == "mean") {
-        strand.reference.log_likelihood /= static_cast<double>(strand.reference.scored_tokens);
-        strand.alternate.log_likelihood /= static_cast<double>(strand.alternate.scored_tokens);
+    // `sequence` holds the allele at 1-based `position`; `offset` is where sequence[0] sits on its
+    // contig (0 for the inline form); `vcf` is null for the inline form
+    const auto score_variant = [&](const std::string &sequence, const size_t position, const std::string &ref_allele,
+                                   const std::string &alt_allele, const size_t offset,
+                                   const evo_b200_vcf_record *vcf) -> evo_status {
+      evo_b200_variant_window window{};
+      window.struct_size = sizeof(window);
+      std::string reference(window_tokens, '\0'), alternate(window_tokens, '\0');
+      const evo_status made = evo_b200_variant_window_make(
+          sequence.data(), sequence.size(), position, ref_allele.data(), ref_allele.size(), alt_allele.data(),
+          alt_allele.size(), window_tokens, &window, reference.data(), alternate.data(), window_tokens);
+      if (made != EVO_STATUS_OK) return made;
+      reference.resize(window.reference_length);
+      alternate.resize(window.alternate_length);
+      struct Strand {
+        const char *name;
+        WindowScore reference, alternate;
+        double delta;
+      };
+      std::vector<Strand> strands;
+      const auto score_strand = [&](const char *name, const std::string &ref, const std::string &alt) {
+        Strand strand{name, score_window(model, o, ref, vocab, &metrics, &last_context),
+                      score_window(model, o, alt, vocab, &metrics, &last_context), 0.0};
+        if (o.normalization == "mean") {
+          strand.reference.log_likelihood /= static_cast<double>(strand.reference.scored_tokens);
+          strand.alternate.log_likelihood /= static_cast<double>(strand.alternate.scored_tokens);
+        }
+        strand.delta = strand.alternate.log_likelihood - strand.reference.log_likelihood;
+        strands.push_back(strand);
+      };
+      if (o.strand != "reverse") score_strand("+", reference, alternate);
+      if (o.strand != "forward") score_strand("-", reverse_complement_of(reference), reverse_complement_of(alternate));
+      double aggregate = 0.0;
+      for (const Strand &strand : strands) aggregate += strand.delta;
+      aggregate /= static_cast<double>(strands.size());
+      std::cout << "{\"source\":\"" << (vcf == nullptr ? "inline" : "vcf") << '"';
+      if (vcf != nullptr) {
+        std::cout << ",\"record_index\":" << vcf->record_index << ",\"allele_index\":" << vcf->allele_index
+                  << ",\"vcf_line\":" << vcf->line_number << ",\"id\":";
+        json_string(std::cout, vcf->id);
+        std::cout << ",\"contig\":";
+        json_string(std::cout, vcf->contig);
       }
-      strand.delta = strand.alternate.log_likelihood - strand.reference.log_likelihood;
-      strands.push_back(strand);
+      std::cout << ",\"position\":" << (vcf == nullptr ? position : vcf->position_1based)
+                << ",\"position_coordinate_system\":\"" << (vcf == nullptr ? "1-based" : "VCF-1-based")
+                << "\",\"reference\":";
+      json_string(std::cout, ref_allele);
+      std::cout << ",\"alternate\":";
+      json_string(std::cout, alt_allele);
+      std::cout << ",\"window\":{\"start\":" << offset + window.reference_start << ",\"end\":"
+                << offset + window.reference_end << ",\"coordinate_system\":\"0-based-half-open\"";
+      if (vcf != nullptr) {
+        std::cout << ",\"contig\":";
+        json_string(std::cout, vcf->contig);
+      }
+      std::cout << ",\"reference_sequence\":";
+      json_string(std::cout, reference);
+      std::cout << ",\"alternate_sequence\":";
+      json_string(std::cout, alternate);
+      std::cout << ",\"reference_tokens\":" << reference.size() << ",\"alternate_tokens\":" << alternate.size()
+                << "},\"normalization\":\"" << (o.normalization == "sum" ? "sum_log_likelihood" : "mean_log_likelihood")
+                << "\",\"backend\":\"cuda\",\"profile\":\"" << o.profile << "\",\"test_fixture\":"
+                << (o.allow_fixture ? "true" : "false") << ",\"model_id\":";
+      const std::string id = evo_model_id(model);
+      if (id.empty()) std::cout << "null"; else json_string(std::cout, id);
+      std::cout << ",\"strands\":[" << std::setprecision(17);
+      for (size_t i = 0; i < strands.size(); ++i) {
+        const Strand &strand = strands[i];
+        std::cout << (i ? "," : "") << "{\"strand\":\"" << strand.name << "\",\"reference_log_likelihood\":"
+                  << strand.reference.log_likelihood << ",\"alternate_log_likelihood\":"
+                  << strand.alternate.log_likelihood << ",\"reference_scored_tokens\":"
+                  << strand.reference.scored_tokens << ",\"alternate_scored_tokens\":"
+                  << strand.alternate.scored_tokens << ",\"delta\":" << strand.delta << '}';
+      }
+      std::cout << "],\"aggregation\":\"" << (strands.size() == 1 ? "single_strand" : "mean_across_strands")
+                << "\",\"score\":" << aggregate << "}\n";
+      return EVO_STATUS_OK;
     };
-    if (o.strand != "reverse") score_strand("+", reference, alternate);
-    if (o.strand != "forward") score_strand("-", reverse_complement_of(reference), reverse_complement_of(alternate));
-    double aggregate = 0.0;
-    for (const Strand &strand : strands) aggregate += strand.delta;
-    aggregate /= static_cast<double>(strands.size());
-    std::cout << "{\"source\":\"inline\",\"position\":" << o.position
-              << ",\"position_coordinate_system\":\"1-based\",\"reference\":";
-    json_string(std::cout, o.reference_allele);
-    std::cout << ",\"alternate\":";
-    json_string(std::cout, o.alternate_allele);
-    std::cout << ",\"window\":{\"start\":" << window.reference_start << ",\"end\":" << window.reference_end
-              << ",\"coordinate_system\":\"0-based-half-open\",\"reference_sequence\":";
-    json_string(std::cout, reference);
-    std::cout << ",\"alternate_sequence\":";
-    json_string(std::cout, alternate);
-    std::cout << ",\"reference_tokens\":" << reference.size() << ",\"alternate_tokens\":" << alternate.size()
-              << "},\"normalization\":\"" << (o.normalization == "sum" ? "sum_log_likelihood" : "mean_log_likelihood")
-              << "\",\"backend\":\"cuda\",\"profile\":\"" << o.profile << "\",\"test_fixture\":"
-              << (o.allow_fixture ? "true" : "false") << ",\"model_id\":";
-    const std::string id = evo_model_id(model);
-    if (id.empty()) std::cout << "null"; else json_string(std::cout, id);
-    std::cout << ",\"strands\":[" << std::setprecision(17);
-    for (size_t i = 0; i < strands.size(); ++i) {
-      const Strand &strand = strands[i];
-      std::cout << (i ? "," : "") << "{\"strand\":\"" << strand.name << "\",\"reference_log_likelihood\":"
-                << strand.reference.log_likelihood << ",\"alternate_log_likelihood\":"
-                << strand.alternate.log_likelihood << ",\"reference_scored_tokens\":"
-                << strand.reference.scored_tokens << ",\"alternate_scored_tokens\":"
-                << strand.alternate.scored_tokens << ",\"delta\":" << strand.delta << '}';
+    if (!from_files) {
+      check(score_variant(o.sequence, o.position, o.reference_allele, o.alternate_allele, 0, nullptr),
+            "variant window");
+    } else {
+      evo_b200_reference *genome = nullptr;
+      check(evo_b200_reference_open(o.reference_path.c_str(), &genome), "reference FASTA");
+      struct Walk {
+        evo_b200_reference *genome;
+        size_t window_tokens;
+        const decltype(score_variant) *score;
+      } walk{genome, window_tokens, &score_variant};
+      const evo_status streamed = evo_b200_vcf_stream(
+          o.vcf_path.c_str(),
+          [](const evo_b200_vcf_record *record, void *user) -> evo_status {
+            const Walk &w = *static_cast<const Walk *>(user);
+            std::string slice(w.window_tokens, '\0');
+            size_t start = 0, end = 0;
+            const std::string ref = record->reference, alt = record->alternate;
+            const evo_status cut = evo_b200_reference_window(w.genome, record->contig, record->position_1based,
+                                                             ref.data(), ref.size(), alt.data(), alt.size(),
+                                                             w.window_tokens, &start, &end, nullptr, slice.data(),
+                                                             slice.size());
+            if (cut != EVO_STATUS_OK) {
+              std::cerr << "evo: VCF line " << record->line_number << ": " << evo_last_error() << '\n';
+              return cut;
+            }
+            slice.resize(end - start);
+            return (*w.score)(slice, record->position_1based - start, ref, alt, start, record);
+          },
+          &walk);
+      evo_b200_reference_free(genome);
+      if (streamed != EVO_STATUS_OK) die(static_cast<int>(streamed), std::string("variant-score: ") + evo_last_error());
     }
-    std::cout << "],\"aggregation\":\"" << (strands.size() == 1 ? "single_strand" : "mean_across_strands")
-              << "\",\"score\":" << aggregate << "}\n";
   } else if (o.command == "bench") {
     if (o.input.empty()) die(EVO_STATUS_INVALID_ARGUMENT, "bench needs --input");
     if (o.repetitions == 0) die(EVO_STATUS_INVALID_ARGUMENT, "--repetitions must be positive");

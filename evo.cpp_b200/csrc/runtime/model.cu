@@ -949,9 +949,10 @@ int Context::run_wavefront(const std::size_t rows, const Mode /*mode*/, const lo
   const std::size_t D = c.width, I = c.inner_width;
   std::size_t chunk = wavefront_chunk_;
   if (chunk == 0) {
-    // enough chunks to fill the pipeline (about two per stage), none so small
-    // that the tensor-core tiles run half empty
-    chunk = (rows / (2 * stages_.size()) + 255) / 256 * 256;
+    // enough chunks to fill the pipeline (about two per stage up to four stages, one per
+    // stage beyond), none so small that the tensor-core tiles run half empty
+    const std::size_t per_stage = stages_.size() <= 4 ? 2 : 1;
+    chunk = (rows / (per_stage * stages_.size()) + 255) / 256 * 256;
     chunk = std::max<std::size_t>(512, std::min<std::size_t>(chunk, 2048));
   }
   for (std::size_t begin = 0; begin < rows; begin += chunk) {

@@ -1,7 +1,8 @@
 """Layer pipeline with one stage per process (torchrun: one rank per GPU).
 
-Rank r holds stage r of the byte-balanced split of the blocks
-(``evo_b200_model_load_slice``).  A prompt moves through the stages as a chunk
+Rank r holds stage r of the contiguous split of the blocks
+(``evo_b200_model_load_slice``: upstream's byte-balanced split up to four
+stages, equal block counts beyond).  A prompt moves through the stages as a chunk
 wavefront: rank r receives the hidden rows of window j from rank r-1, runs its
 blocks over them, and sends them on while rank r-1 already works on window
 j+1.  That is legal because every mixer is causal and carries its state from
@@ -12,7 +13,7 @@ never waits for its successor unless it is about to overwrite rows still in
 flight.
 
 Upstream runs the same stage plan inside one process and hands the whole
-sequence from device to device (src/cuda/model.cu:3148-3212); the wavefront is
+sequence from device to device (src/cuda/model.cu:2148-2366); the wavefront is
 this implementation's addition.
 """
 from __future__ import annotations
@@ -21,15 +22,19 @@ from typing import Protocol
 
 
 def window_plan(rows: int, stages: int, chunk: int = 0) -> list[tuple[int, int]]:
-    """[(begin, count)] windows of one prompt: about two windows per stage so the
-    pipeline fills, each a power of two in [512, 2048] rows so the tensor-core
-    tiles stay full and the windows divide the activation capacity (prompts
-    longer than it wrap around)."""
+    """[(begin, count)] windows of one prompt, each a power of two in [512, 2048]
+    rows so that they divide the activation capacity (prompts longer than it
+    wrap around): about two windows per stage up to four stages, one per stage
+    beyond.  More windows fill the pipeline better, but a 512-row window runs
+    the 4096-wide projections at well under half the tensor rate they reach at
+    1,024 rows (128 x 128 tiles re-read their operands from L2 twice as often),
+    which costs an eight-stage pipeline more than the shorter fill gains."""
     if rows <= 0 or stages <= 0:
         raise ValueError("rows and stages must be positive")
     if chunk <= 0:
+        per_stage = 2 if stages <= 4 else 1
         chunk = 512
-        while chunk < 2048 and chunk * 2 * stages < rows:
+        while chunk < 2048 and chunk * per_stage * stages < rows:
             chunk *= 2
     return [(begin, min(chunk, rows - begin)) for begin in range(0, rows, chunk)]
 

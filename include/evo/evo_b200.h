@@ -146,6 +146,41 @@ EVO_API evo_status evo_b200_variant_window_make(const char *sequence, size_t seq
 /* Reverse complement of IUPAC DNA (upstream src/variant.cpp:86-101); `output` holds `length` bytes. */
 EVO_API evo_status evo_b200_reverse_complement(const char *sequence, size_t length, char *output);
 
+/* ---- file inputs of `evo variant-score --vcf ... --reference ...` (host-only).
+ * Upstream: stream_vcf_file and fetch_reference_slice
+ * (include/evo/variant_io.hpp:13-45, src/variant_io.cpp), driven from
+ * src/cuda/inference_cli.cpp:939-975.  evo_b200_vcf_stream calls back once per
+ * ALT allele of every record of a plain or gzip VCF ("-" = standard input);
+ * the record's strings are valid during the call; a non-OK return stops the
+ * stream and is returned.  evo_b200_reference_open scans a plain reference
+ * FASTA once into an index (what a .fai holds; upstream re-reads the file twice
+ * per allele instead), and evo_b200_reference_window checks that the contig
+ * holds `reference` at the 1-based position and cuts the scoring window: as
+ * much flank as `maximum_tokens` allows, half on each side, a side that runs
+ * out of contig ceding its share to the other.  `sequence` (capacity bytes, no
+ * terminator) receives bases [*start, *end) of the contig. */
+typedef struct evo_b200_vcf_record {
+  size_t struct_size;
+  const char *contig;
+  const char *id;
+  const char *reference;
+  const char *alternate;
+  size_t position_1based;
+  size_t record_index;
+  size_t allele_index;
+  size_t line_number;
+} evo_b200_vcf_record;
+typedef evo_status (*evo_b200_vcf_callback)(const evo_b200_vcf_record *record, void *user_data);
+EVO_API evo_status evo_b200_vcf_stream(const char *path, evo_b200_vcf_callback callback, void *user_data);
+typedef struct evo_b200_reference evo_b200_reference;
+EVO_API evo_status evo_b200_reference_open(const char *path, evo_b200_reference **reference_out);
+EVO_API void evo_b200_reference_free(evo_b200_reference *reference);
+EVO_API evo_status evo_b200_reference_window(const evo_b200_reference *reference, const char *contig,
+                                             size_t position_1based, const char *reference_allele,
+                                             size_t reference_length, const char *alternate_allele,
+                                             size_t alternate_length, size_t maximum_tokens,
+                                             size_t *start, size_t *end, size_t *contig_length,
+                                             char *sequence, size_t capacity);
 
 /* ---- one pipeline stage per process (torchrun / MPI style launchers).
  * Upstream runs its layer pipeline inside one process

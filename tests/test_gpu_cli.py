@@ -169,3 +169,33 @@ def test_variant_score_is_the_difference_of_two_window_scores(tmp_path):
     refused = run("variant-score", "--sequence", "AACCGG", "--position", "3", "--ref", "G", "--alt", "T",
                   "--ctx", "64", check=False)
     assert refused.returncode == 2 and b"does not match" in refused.stderr
+
+
+def test_variant_score_from_a_vcf_and_a_reference_fasta(tmp_path):
+    """File form of `evo variant-score` (upstream src/cuda/inference_cli.cpp:939-975): one JSONL
+    row per ALT allele, windows cut out of the reference contig with contig coordinates, and the
+    same scores as the inline form on the same locus."""
+    genome = tmp_path / "genome.fa"
+    genome.write_text(">chr1 test contig\nGGGGAACC\nGGTTGGGG\n>chr2\nACGTACGT\n")
+    vcf = tmp_path / "variants.vcf"
+    vcf.write_text("##fileformat=VCFv4.2\n#CHROM\tPOS\tID\tREF\tALT\tQUAL\tFILTER\tINFO\n"
+                   "chr1\t7\trs7\tC\tT,G\t.\t.\t.\nchr2\t2\t.\tC\tCTT\t.\t.\t.\n")
+    result = run("variant-score", "--vcf", str(vcf), "--reference", str(genome), "--window", "6", "--ctx", "64")
+    rows = [json.loads(line) for line in result.stdout.decode().splitlines()]
+    assert [(r["record_index"], r["allele_index"], r["vcf_line"], r["id"], r["contig"], r["alternate"]) for r in rows] == [
+        (0, 0, 3, "rs7", "chr1", "T"), (0, 1, 3, "rs7", "chr1", "G"), (1, 0, 4, ".", "chr2", "CTT")]
+    first = rows[0]
+    assert first["source"] == "vcf" and first["position"] == 7 and first["position_coordinate_system"] == "VCF-1-based"
+    # chr1 = GGGGAACCGGTTGGGG: the 6-token window around position 7 is AACCGG at contig offset 4
+    assert (first["window"]["start"], first["window"]["end"], first["window"]["contig"]) == (4, 10, "chr1")
+    assert (first["window"]["reference_sequence"], first["window"]["alternate_sequence"]) == ("AACCGG", "AATCGG")
+    inline = json.loads(run("variant-score", "--sequence", "AACCGGTT", "--position", "3", "--ref", "C", "--alt", "T",
+                            "--window", "6", "--ctx", "64").stdout.decode())
+    assert first["score"] == inline["score"] and first["strands"] == inline["strands"]
+    # an insertion: the alternate window holds the longer allele inside the same budget
+    assert rows[2]["window"]["reference_tokens"] + 2 == rows[2]["window"]["alternate_tokens"] <= 6
+    mismatch = tmp_path / "bad.vcf"
+    mismatch.write_text("#CHROM\tPOS\tID\tREF\tALT\tQUAL\tFILTER\tINFO\nchr1\t7\t.\tA\tT\t.\t.\t.\n")
+    refused = run("variant-score", "--vcf", str(mismatch), "--reference", str(genome), "--ctx", "64", check=False)
+    assert refused.returncode == 2 and b"VCF line 2" in refused.stderr and b"does not match" in refused.stderr
+    assert run("variant-score", "--vcf", str(vcf), "--ctx", "64", check=False).returncode == 2

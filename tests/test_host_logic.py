@@ -292,3 +292,144 @@ def test_modal_scratch_size_is_monotonic_and_bounded(pkg):
                 assert floats <= (length // 64 + 3) * width * modes    # never more than a state per 64 rows
         assert fn(1 << 20, width, modes) == fn(131072, width, modes)   # bounded by the grid, not by the length
     assert fn(1 << 20, 4096, 16) * 4 <= 16 << 20                      # 7B shape: below the 16 MiB static array
+
+
+# ---- file inputs of the variant driver (VCF stream, indexed reference FASTA): host-only
+class _VcfRecord(ctypes.Structure):
+    _fields_ = [("struct_size", ctypes.c_size_t), ("contig", ctypes.c_char_p), ("id", ctypes.c_char_p),
+                ("reference", ctypes.c_char_p), ("alternate", ctypes.c_char_p), ("position_1based", ctypes.c_size_t),
+                ("record_index", ctypes.c_size_t), ("allele_index", ctypes.c_size_t), ("line_number", ctypes.c_size_t)]
+
+
+_VCF_CALLBACK = ctypes.CFUNCTYPE(ctypes.c_int, ctypes.POINTER(_VcfRecord), ctypes.c_void_p)
+
+
+def _stream_vcf(evo, path, stop_at=None):
+    records = []
+
+    @_VCF_CALLBACK
+    def on_record(record, _user):
+        r = record.contents
+        records.append((r.contig, r.position_1based, r.id, r.reference, r.alternate, r.record_index, r.allele_index,
+                        r.line_number))
+        return 3 if stop_at is not None and len(records) == stop_at else 0
+
+    fn = evo.lib.evo_b200_vcf_stream
+    fn.argtypes = [ctypes.c_char_p, _VCF_CALLBACK, ctypes.c_void_p]
+    status = fn(str(path).encode(), on_record, None)
+    return status, records, (evo.lib.evo_last_error() or b"").decode()
+
+
+VCF_HEADER = "##fileformat=VCFv4.2\n#CHROM\tPOS\tID\tREF\tALT\tQUAL\tFILTER\tINFO\n"
+
+
+def test_vcf_stream_one_callback_per_alt_allele(evo, tmp_path):
+    import gzip
+
+    text = VCF_HEADER + "chr1\t5\trs1\tA\tG,TT\t.\t.\t.\nchr2\t12\t.\tacg\tA\t50\tPASS\tX=1\tGT\t0/1\r\n"
+    plain = tmp_path / "a.vcf"
+    plain.write_text(text)
+    packed = tmp_path / "a.vcf.gz"
+    packed.write_bytes(gzip.compress(text.encode()))
+    expected = [(b"chr1", 5, b"rs1", b"A", b"G", 0, 0, 3), (b"chr1", 5, b"rs1", b"A", b"TT", 0, 1, 3),
+                (b"chr2", 12, b".", b"acg", b"A", 1, 0, 4)]
+    for path in (plain, packed):
+        status, records, _ = _stream_vcf(evo, path)
+        assert status == 0 and records == expected
+    status, records, message = _stream_vcf(evo, plain, stop_at=2)      # a consumer's error stops the stream
+    assert status == 3 and len(records) == 2
+    cases = {
+        "chr1\t5\t.\tA\tG\t.\t.\t.\n": "before the #CHROM header",
+        VCF_HEADER: "contains no records",
+        VCF_HEADER + "chr1\t0\t.\tA\tG\t.\t.\t.\n": "POS must be a positive integer at line 3",
+        VCF_HEADER + "chr1\t5\t.\tA\t<DEL>\t.\t.\t.\n": "VCF ALT",
+        VCF_HEADER + "chr1\t5\t.\tA\n": "fewer than 8 valid fields at line 3",
+        VCF_HEADER + "\nchr1\t5\t.\tA\tG\t.\t.\t.\n": "empty line at 3",
+        VCF_HEADER + VCF_HEADER.splitlines()[1] + "\n": "repeats the #CHROM header",
+        "##x\n#CHROM\tPOS\n": "unsupported header at line 2",
+    }
+    for index, (body, fragment) in enumerate(cases.items()):
+        path = tmp_path / f"bad{index}.vcf"
+        path.write_text(body)
+        status, _, message = _stream_vcf(evo, path)
+        assert status == 2 and fragment in message, (body, message)
+    assert _stream_vcf(evo, tmp_path / "missing.vcf")[0] == 3
+
+
+def _reference(evo, path):
+    handle = ctypes.c_void_p()
+    fn = evo.lib.evo_b200_reference_open
+    fn.argtypes = [ctypes.c_char_p, ctypes.POINTER(ctypes.c_void_p)]
+    status = fn(str(path).encode(), ctypes.byref(handle))
+    return status, handle, (evo.lib.evo_last_error() or b"").decode()
+
+
+def _window(evo, handle, contig, position, ref, alt, maximum):
+    fn = evo.lib.evo_b200_reference_window
+    Z = ctypes.c_size_t
+    fn.argtypes = [ctypes.c_void_p, ctypes.c_char_p, Z, ctypes.c_char_p, Z, ctypes.c_char_p, Z, Z,
+                   ctypes.POINTER(Z), ctypes.POINTER(Z), ctypes.POINTER(Z), ctypes.c_char_p, Z]
+    start, end, length = Z(), Z(), Z()
+    buffer = ctypes.create_string_buffer(max(maximum, 1))
+    status = fn(handle, contig, position, ref, len(ref), alt, len(alt), maximum, ctypes.byref(start),
+                ctypes.byref(end), ctypes.byref(length), buffer, maximum)
+    if status != 0:
+        return status, (evo.lib.evo_last_error() or b"").decode()
+    return 0, (buffer.raw[:end.value - start.value], start.value, end.value, length.value)
+
+
+def test_reference_fasta_index_and_scoring_windows(evo, tmp_path):
+    rng = np.random.default_rng(21)
+    contigs = {b"chrA": bytes(rng.choice(np.frombuffer(b"ACGTacgtN", np.uint8), 137).tolist()),
+               b"chrB": bytes(rng.choice(np.frombuffer(b"ACGT", np.uint8), 60).tolist()),
+               b"tiny": b"ACG"}
+    evo.lib.evo_b200_reference_free.argtypes = [ctypes.c_void_p]
+    for width, newline in ((10, b"\n"), (60, b"\r\n"), (7, b"\n")):
+        path = tmp_path / f"genome{width}.fa"
+        with open(path, "wb") as out:
+            for name, bases in contigs.items():
+                out.write(b">" + name + b" description text" + newline)
+                for begin in range(0, len(bases), width):
+                    out.write(bases[begin:begin + width] + newline)
+        status, handle, message = _reference(evo, path)
+        assert status == 0, message
+        for _ in range(200):
+            name = [b"chrA", b"chrB", b"tiny"][int(rng.integers(0, 3))]
+            bases = contigs[name]
+            start = int(rng.integers(0, len(bases)))
+            ref = bases[start:start + int(rng.integers(1, min(4, len(bases) - start) + 1))]
+            alt = bytes(rng.choice(np.frombuffer(b"ACGT", np.uint8), int(rng.integers(1, 5))).tolist())
+            maximum = int(rng.integers(2, 50))
+            core = max(len(ref), len(alt))
+            status, result = _window(evo, handle, name, start + 1, ref, alt, maximum)
+            if maximum < core:
+                assert status == 2 and "two tokens" in result
+                continue
+            assert status == 0, result
+            sequence, begin, end, length = result
+            assert length == len(bases) and sequence == bases[begin:end] and begin <= start and start + len(ref) <= end
+            assert (end - begin) - len(ref) == min(maximum - core, len(bases) - len(ref))   # the whole budget
+            left, right = start - begin, end - (start + len(ref))
+            if left < (maximum - core) // 2:
+                assert begin == 0 or right == len(bases) - (start + len(ref))
+        assert _window(evo, handle, b"chrB", 3, b"N" if contigs[b"chrB"][2:3] != b"N" else b"A", b"T", 20)[1].startswith(
+            "invalid_argument: VCF REF does not match reference contig 'chrB' at 1-based position 3")
+        assert "extends beyond" in _window(evo, handle, b"tiny", 3, b"GT", b"T", 20)[1]
+        assert "has no contig 'chrZ'" in _window(evo, handle, b"chrZ", 1, b"A", b"T", 20)[1]
+        evo.lib.evo_b200_reference_free(handle)
+    # refusals at open
+    def refused(name, payload, code, fragment):
+        path = tmp_path / name
+        path.write_bytes(payload)
+        status, _, message = _reference(evo, path)
+        assert status == code and fragment in message, message
+
+    refused("dup.fa", b">a\nAC\n>a\nGT\n", 2, "duplicate contig 'a'")
+    refused("ragged.fa", b">a\nACGT\nAC\nACGT\n", 2, "differ in width")
+    refused("blank.fa", b">a\nACGT\n\nACGT\n", 2, "differ in width")
+    refused("space.fa", b">a\nAC GT\n", 2, "whitespace at line 2")
+    refused("nohdr.fa", b"ACGT\n", 2, "before a header")
+    refused("empty.fa", b"", 2, "not FASTA")
+    import gzip
+    refused("packed.fa.gz", gzip.compress(b">a\nACGT\n"), 5, "gzip-compressed")
+    assert _reference(evo, tmp_path / "absent.fa")[0] == 3

@@ -24,7 +24,8 @@ def test_window_plan_covers_the_prompt(pkg):
         assert all(count % 256 == 0 and 512 <= count <= 2048 for _, count in plan[:-1])
     assert pipeline.window_plan(8192, 2) == [(i * 2048, 2048) for i in range(4)]
     assert pipeline.window_plan(8192, 4) == [(i * 1024, 1024) for i in range(8)]
-    assert pipeline.window_plan(8192, 8) == [(i * 512, 512) for i in range(16)]
+    assert pipeline.window_plan(8192, 8) == [(i * 1024, 1024) for i in range(8)]
+    assert pipeline.window_plan(4096, 8) == [(i * 512, 512) for i in range(8)]
     assert all(8192 % count == 0 for _, count in pipeline.window_plan(131072, 8))
     assert pipeline.window_plan(1000, 2, chunk=300) == [(0, 300), (300, 300), (600, 300), (900, 100)]
     with pytest.raises(ValueError):
