@@ -32,7 +32,7 @@ KERNEL_SOURCES = [
 OPS_SOURCES = KERNEL_SOURCES + ["ops_api.cu"]
 RUNTIME_SOURCES = KERNEL_SOURCES + [
     "runtime/safetensors.cpp", "runtime/model_load.cpp", "runtime/model_weights.cpp",
-    "runtime/model.cu", "runtime/sampler.cpp", "runtime/variant.cpp", "runtime/variant_io.cpp", "runtime/c_api.cpp",
+    "runtime/model.cu", "runtime/sampler.cpp", "runtime/variant.cpp", "runtime/variant_io.cpp", "runtime/scheduler.cpp", "runtime/c_api.cpp",
 ]
 
 

@@ -19,6 +19,7 @@
 #include "../ops_internal.hpp"
 #include "model.hpp"
 #include "sampler.hpp"
+#include "scheduler.hpp"
 #include "variant.hpp"
 #include "variant_io.hpp"
 
@@ -34,6 +35,9 @@ struct evo_context {
 struct evo_batch {
   std::size_t capacity = 0;
   std::vector<std::vector<std::uint8_t>> sequences;
+};
+struct evo_b200_scheduler {
+  std::unique_ptr<evob::Scheduler> scheduler;
 };
 struct evo_b200_reference {
   std::unique_ptr<evob::ReferenceFasta> fasta;
@@ -682,6 +686,100 @@ evo_status evo_b200_reference_window(const evo_b200_reference *reference, const 
     if (sequence != nullptr) std::memcpy(sequence, slice.sequence.data(), slice.sequence.size());
     return kOk;
   });
+}
+
+evo_status evo_b200_scheduler_create(const evo_model *model, const evo_b200_scheduler_params *params,
+                                     evo_b200_scheduler **scheduler_out) {
+  return protect([&]() -> int {
+    if (scheduler_out != nullptr) *scheduler_out = nullptr;
+    if (model == nullptr || params == nullptr || scheduler_out == nullptr ||
+        params->struct_size < sizeof(evo_b200_scheduler_params))
+      return fail(evob::kInvalidArgument, "model, scheduler parameters and output are required");
+    if ((params->context_flags & EVO_CONTEXT_FLAG_FAST_Q8_KV) != 0)
+      return fail(evob::kUnsupported, "the fast-q8-kv profile is not available in this build");
+    const bool fp8_ffn = (params->context_flags & EVO_CONTEXT_FLAG_B200_FP8_FFN) != 0;
+    const bool tensor_core = fp8_ffn || (params->context_flags & EVO_CONTEXT_FLAG_B200_TENSORCORE_FP8) != 0;
+    auto handle = std::make_unique<evo_b200_scheduler>();
+    const int status = evob::Scheduler::create(
+        model->weights, params->workers, params->maximum_queue, params->context_size,
+        fp8_ffn       ? evob::ExecutionProfile::kTensorCoreFfn
+        : tensor_core ? evob::ExecutionProfile::kTensorCore
+                      : evob::ExecutionProfile::kExact,
+        (params->context_flags & EVO_CONTEXT_FLAG_B200_FULL_ARENA) != 0, &handle->scheduler);
+    if (status != kOk) return status;
+    *scheduler_out = handle.release();
+    return kOk;
+  });
+}
+
+void evo_b200_scheduler_free(evo_b200_scheduler *scheduler) { delete scheduler; }
+
+evo_status evo_b200_scheduler_submit(evo_b200_scheduler *scheduler, const evo_b200_request *request,
+                                     evo_b200_request_callback done, void *user_data, uint64_t *ticket) {
+  return protect([&]() -> int {
+    if (ticket != nullptr) *ticket = 0;
+    if (scheduler == nullptr || request == nullptr || ticket == nullptr ||
+        request->struct_size < sizeof(evo_b200_request) || (request->sequence == nullptr && request->length != 0))
+      return fail(evob::kInvalidArgument, "scheduler, request and ticket output are required");
+    if (request->kind != EVO_B200_REQUEST_SCORE && request->kind != EVO_B200_REQUEST_GENERATE)
+      return fail(evob::kInvalidArgument, "request kind must be score or generate");
+    evob::SchedulerRequest copy;
+    copy.kind = request->kind == EVO_B200_REQUEST_SCORE ? evob::SchedulerRequest::Kind::kScore
+                                                        : evob::SchedulerRequest::Kind::kGenerate;
+    copy.sequence.assign(request->sequence, request->sequence + request->length);
+    copy.new_tokens = request->new_tokens;
+    if (copy.kind == evob::SchedulerRequest::Kind::kGenerate) {
+      copy.sampling.temperature = request->sampler.temperature;
+      copy.sampling.top_k = request->sampler.top_k;
+      copy.sampling.top_p = request->sampler.top_p;
+      copy.sampling.seed = request->sampler.seed;
+    }
+    *ticket = scheduler->scheduler->submit(
+        std::move(copy), [done, user_data](const std::uint64_t id, const evob::SchedulerResult &result) {
+          if (done == nullptr) return;
+          evo_b200_request_result view{};
+          view.struct_size = sizeof(view);
+          view.status = static_cast<evo_status>(result.status);
+          view.error = result.error.c_str();
+          view.cancelled = result.cancelled ? 1 : 0;
+          view.log_likelihood = result.log_likelihood;
+          view.scored_tokens = result.scored_tokens;
+          view.token_log_likelihoods = result.token_log_likelihoods.data();
+          view.generated = result.generated.data();
+          view.generated_length = result.generated.size();
+          view.queue_seconds = result.queue_seconds;
+          view.run_seconds = result.run_seconds;
+          done(id, &view, user_data);
+        });
+    return kOk;
+  });
+}
+
+int evo_b200_scheduler_cancel(evo_b200_scheduler *scheduler, uint64_t ticket) {
+  return scheduler != nullptr && scheduler->scheduler->cancel(ticket) ? 1 : 0;
+}
+
+evo_status evo_b200_scheduler_read_metrics(const evo_b200_scheduler *scheduler,
+                                           evo_b200_scheduler_metrics *metrics) {
+  return protect([&]() -> int {
+    if (scheduler == nullptr || metrics == nullptr || metrics->struct_size < sizeof(evo_b200_scheduler_metrics))
+      return fail(evob::kInvalidArgument, "scheduler and metrics output are required");
+    const evob::SchedulerMetrics m = scheduler->scheduler->metrics();
+    metrics->submitted = m.submitted;
+    metrics->rejected = m.rejected;
+    metrics->completed = m.completed;
+    metrics->failed = m.failed;
+    metrics->cancelled = m.cancelled;
+    metrics->queued = m.queued;
+    metrics->queue_peak = m.queue_peak;
+    metrics->active = m.active;
+    metrics->active_peak = m.active_peak;
+    return kOk;
+  });
+}
+
+void evo_b200_scheduler_wait_idle(const evo_b200_scheduler *scheduler) {
+  if (scheduler != nullptr) scheduler->scheduler->wait_idle();
 }
 
 void *evo_b200_context_stream(const evo_context *context) {

@@ -18,6 +18,8 @@
 #include <iomanip>
 #include <iostream>
 #include <limits>
+#include <memory>
+#include <mutex>
 #include <sstream>
 #include <string>
 #include <vector>
@@ -39,6 +41,8 @@ struct Options {
   // variant-score: inline (--sequence --position --ref --alt) or file form (--vcf --reference)
   std::string sequence, reference_allele, alternate_allele, strand = "both", normalization = "sum";
   std::string vcf_path, reference_path;
+  // serve
+  size_t workers = 4, max_queue = 64;
   size_t position = 0, window = 0;
 };
 
@@ -122,6 +126,45 @@ uint64_t fnv1a64(const std::string &bytes) {
     hash *= 1099511628211ULL;
   }
   return hash;
+}
+
+// Value of `key` in a flat JSON object (one request per line): strings are
+// unescaped for \" \\ \n \t \/ and \uXXXX below 0x100, numbers are returned as
+// their text.  Returns false when the key is absent.
+bool json_field(const std::string &line, const std::string &key, std::string *value) {
+  const std::string needle = '"' + key + '"';
+  size_t at = 0;
+  while ((at = line.find(needle, at)) != std::string::npos) {
+    size_t cursor = at + needle.size();
+    while (cursor < line.size() && (line[cursor] == ' ' || line[cursor] == '\t')) ++cursor;
+    if (cursor >= line.size() || line[cursor] != ':') {
+      at += needle.size();
+      continue;
+    }
+    ++cursor;
+    while (cursor < line.size() && (line[cursor] == ' ' || line[cursor] == '\t')) ++cursor;
+    value->clear();
+    if (cursor < line.size() && line[cursor] == '"') {
+      for (++cursor; cursor < line.size() && line[cursor] != '"'; ++cursor) {
+        if (line[cursor] != '\\' || cursor + 1 >= line.size()) {
+          value->push_back(line[cursor]);
+          continue;
+        }
+        const char escaped = line[++cursor];
+        if (escaped == 'n') value->push_back('\n');
+        else if (escaped == 't') value->push_back('\t');
+        else if (escaped == 'u' && cursor + 4 < line.size()) {
+          value->push_back(static_cast<char>(std::stoul(line.substr(cursor + 1, 4), nullptr, 16) & 0xffU));
+          cursor += 4;
+        } else value->push_back(escaped);
+      }
+    } else {
+      while (cursor < line.size() && line[cursor] != ',' && line[cursor] != '}' && line[cursor] != ' ')
+        value->push_back(line[cursor++]);
+    }
+    return true;
+  }
+  return false;
 }
 
 struct Collected {
@@ -220,6 +263,8 @@ Options parse(int argc, char **argv) {
     else if (a == "--allow-test-fixture") o.allow_fixture = true;
     else if (a == "--sequence") o.sequence = value(i);
     else if (a == "--vcf") o.vcf_path = value(i);
+    else if (a == "--workers" || a == "--max-batch") o.workers = std::stoull(value(i));
+    else if (a == "--max-queue") o.max_queue = std::stoull(value(i));
     else if (a == "--reference") o.reference_path = value(i);
     else if (a == "--position") o.position = std::stoull(value(i));
     else if (a == "--ref") o.reference_allele = value(i);
@@ -240,6 +285,7 @@ Options parse(int argc, char **argv) {
                    "--pooling none|mean|last\n"
                    "  evo variant-score -m MODEL --sequence DNA --position POS --ref REF --alt ALT "
                    "[--window N --strand forward|reverse|both --normalization sum|mean]\n"
+                   "  evo serve -m MODEL [--workers N --max-queue M --ctx N --profile ...] < requests.jsonl\n"
                    "  evo variant-score -m MODEL --vcf VARIANTS.vcf[.gz] --reference GENOME.fa "
                    "[--window N --strand ... --normalization ...]\n";
       std::exit(0);
@@ -611,6 +657,110 @@ int main(int argc, char **argv) {
     std::cout << "],\"statistic\":\"median\",\"median_seconds\":" << median
               << ",\"median_tokens_per_second\":" << static_cast<double>(record.bytes.size()) / median
               << "}\n";
+  } else if (o.command == "serve") {
+    // The serving loop of upstream's `evo serve` (src/server.cpp) without its HTTP transport: one
+    // JSON request per input line, one JSON response per request as it completes (not in input
+    // order), on a pool of contexts that share the model's weights.
+    //   {"id":"a","op":"score","sequence":"ACGT..."}
+    //   {"id":"b","op":"generate","prompt":"ACGT","tokens":16,"temperature":1,"top_k":1,"top_p":1,"seed":0}
+    evo_b200_scheduler_params sp{};
+    sp.struct_size = sizeof(sp);
+    sp.workers = o.workers;
+    sp.maximum_queue = std::max(o.max_queue, o.workers);
+    sp.context_size = o.context;
+    if (o.profile == "b200-tc") sp.context_flags |= EVO_CONTEXT_FLAG_B200_TENSORCORE_FP8;
+    if (o.profile == "b200-fp8") sp.context_flags |= EVO_CONTEXT_FLAG_B200_FP8_FFN;
+    evo_b200_scheduler *scheduler = nullptr;
+    check(evo_b200_scheduler_create(model, &sp, &scheduler), "scheduler");
+    struct Pending {
+      std::string id, op;
+      std::mutex *output;
+    };
+    std::mutex output;
+    const auto respond = [](uint64_t, const evo_b200_request_result *r, void *user) {
+      std::unique_ptr<Pending> pending(static_cast<Pending *>(user));
+      std::ostringstream line;
+      line << "{\"id\":";
+      json_string(line, pending->id);
+      line << ",\"op\":";
+      json_string(line, pending->op);
+      if (r->cancelled) {
+        line << ",\"error\":{\"code\":\"cancelled\",\"message\":\"request was cancelled\"}";
+      } else if (r->status != EVO_STATUS_OK) {
+        line << ",\"error\":{\"code\":\"" << evo_status_name(r->status) << "\",\"message\":";
+        json_string(line, r->error);
+        line << '}';
+      } else if (pending->op == "score") {
+        line << std::setprecision(17) << ",\"tokens\":" << r->scored_tokens + 1 << ",\"scored_tokens\":"
+             << r->scored_tokens << ",\"log_likelihood\":" << r->log_likelihood << ",\"mean_log_likelihood\":"
+             << r->log_likelihood / static_cast<double>(r->scored_tokens);
+      } else {
+        line << ",\"generated\":";
+        json_string(line, std::string(reinterpret_cast<const char *>(r->generated), r->generated_length));
+      }
+      line << std::setprecision(6) << ",\"queue_seconds\":" << r->queue_seconds << ",\"run_seconds\":"
+           << r->run_seconds << "}\n";
+      std::lock_guard<std::mutex> lock(*pending->output);
+      std::cout << line.str();
+      std::cout.flush();
+    };
+    size_t line_number = 0;
+    for (std::string line; std::getline(std::cin, line);) {
+      ++line_number;
+      if (line.empty()) continue;
+      auto pending = std::make_unique<Pending>();
+      pending->output = &output;
+      if (!json_field(line, "id", &pending->id)) pending->id = std::to_string(line_number);
+      std::string payload, number;
+      evo_b200_request request{};
+      request.struct_size = sizeof(request);
+      request.sampler = evo_sampler_default_params();
+      const bool has_op = json_field(line, "op", &pending->op);
+      const auto refuse = [&](const char *code, const std::string &message) {
+        std::lock_guard<std::mutex> lock(output);
+        std::cout << "{\"id\":";
+        json_string(std::cout, pending->id);
+        std::cout << ",\"error\":{\"code\":\"" << code << "\",\"message\":";
+        json_string(std::cout, message);
+        std::cout << "}}\n";
+        std::cout.flush();
+      };
+      if (has_op && pending->op == "score" && json_field(line, "sequence", &payload)) {
+        request.kind = EVO_B200_REQUEST_SCORE;
+      } else if (has_op && pending->op == "generate" && json_field(line, "prompt", &payload)) {
+        request.kind = EVO_B200_REQUEST_GENERATE;
+        try {
+          if (json_field(line, "tokens", &number)) request.new_tokens = std::stoull(number);
+          if (json_field(line, "temperature", &number)) request.sampler.temperature = std::stof(number);
+          if (json_field(line, "top_k", &number)) request.sampler.top_k = std::stoull(number);
+          if (json_field(line, "top_p", &number)) request.sampler.top_p = std::stof(number);
+          if (json_field(line, "seed", &number)) request.sampler.seed = std::stoull(number);
+        } catch (const std::exception &) {
+          refuse("invalid_argument", "a numeric request field cannot be parsed");
+          continue;
+        }
+      } else {
+        refuse("invalid_argument", "a request needs \"op\":\"score\" with \"sequence\" or \"op\":\"generate\" with \"prompt\"");
+        continue;
+      }
+      request.sequence = reinterpret_cast<const uint8_t *>(payload.data());
+      request.length = payload.size();
+      uint64_t ticket = 0;
+      Pending *const raw = pending.get();
+      const evo_status submitted = evo_b200_scheduler_submit(scheduler, &request, respond, raw, &ticket);
+      if (submitted != EVO_STATUS_OK) refuse(evo_status_name(submitted), evo_last_error());
+      else if (ticket == 0) refuse("busy", "the request queue is full");
+      else pending.release();  // owned by the completion now
+    }
+    evo_b200_scheduler_wait_idle(scheduler);
+    evo_b200_scheduler_metrics totals{};
+    totals.struct_size = sizeof(totals);
+    check(evo_b200_scheduler_read_metrics(scheduler, &totals), "scheduler metrics");
+    std::cerr << "{\"scheduler\":{\"submitted\":" << totals.submitted << ",\"rejected\":" << totals.rejected
+              << ",\"completed\":" << totals.completed << ",\"failed\":" << totals.failed << ",\"cancelled\":"
+              << totals.cancelled << ",\"queue_peak\":" << totals.queue_peak << ",\"active_peak\":"
+              << totals.active_peak << ",\"workers\":" << o.workers << "}}\n";
+    evo_b200_scheduler_free(scheduler);
   } else if (o.command == "run") {
     if (o.prompt.empty()) die(EVO_STATUS_INVALID_ARGUMENT, "run needs a prompt (-p)");
     if (o.prompt.size() + o.tokens > o.context)
@@ -648,7 +798,7 @@ int main(int argc, char **argv) {
     std::cout.flush();
     evo_sampler_free(sampler);
   } else {
-    die(EVO_STATUS_UNSUPPORTED, "unknown command " + o.command + " (run, score, bench, embed, variant-score)");
+    die(EVO_STATUS_UNSUPPORTED, "unknown command " + o.command + " (run, score, bench, embed, variant-score, serve)");
   }
   print_metrics(metrics, o, last_context);
   if (last_context != nullptr) evo_context_free(last_context);

@@ -56,6 +56,33 @@ class StageInfo(ctypes.Structure):
                 ("arena_bytes", ctypes.c_size_t)]
 
 
+class SchedulerParams(ctypes.Structure):
+    _fields_ = [("struct_size", ctypes.c_size_t), ("workers", ctypes.c_size_t), ("maximum_queue", ctypes.c_size_t),
+                ("context_size", ctypes.c_size_t), ("context_flags", ctypes.c_uint32)]
+
+
+class Request(ctypes.Structure):
+    _fields_ = [("struct_size", ctypes.c_size_t), ("kind", ctypes.c_int32), ("sequence", ctypes.c_char_p),
+                ("length", ctypes.c_size_t), ("new_tokens", ctypes.c_size_t), ("sampler", SamplerParams)]
+
+
+class RequestResult(ctypes.Structure):
+    _fields_ = [("struct_size", ctypes.c_size_t), ("status", ctypes.c_int), ("error", ctypes.c_char_p),
+                ("cancelled", ctypes.c_int32), ("log_likelihood", ctypes.c_double), ("scored_tokens", ctypes.c_size_t),
+                ("token_log_likelihoods", ctypes.POINTER(ctypes.c_double)),
+                ("generated", ctypes.POINTER(ctypes.c_uint8)), ("generated_length", ctypes.c_size_t),
+                ("queue_seconds", ctypes.c_double), ("run_seconds", ctypes.c_double)]
+
+
+class SchedulerMetrics(ctypes.Structure):
+    _fields_ = [("struct_size", ctypes.c_size_t)] + [(n, ctypes.c_uint64) for n in
+                ("submitted", "rejected", "completed", "failed", "cancelled")] + [
+                (n, ctypes.c_size_t) for n in ("queued", "queue_peak", "active", "active_peak")]
+
+
+REQUEST_CALLBACK = ctypes.CFUNCTYPE(None, ctypes.c_uint64, ctypes.POINTER(RequestResult), ctypes.c_void_p)
+
+
 class EvoError(RuntimeError):
     def __init__(self, code: int, message: str):
         super().__init__(f"[{code}] {message}")
@@ -125,6 +152,13 @@ class EvoLibrary:
                                                                 DUMP_CALLBACK, LOGITS_CALLBACK, V]
             lib.evo_b200_context_decode_with_dumps.argtypes = [V, ctypes.c_uint32, ctypes.POINTER(DumpRequest), Z,
                                                                DUMP_CALLBACK, LOGITS_CALLBACK, V]
+            lib.evo_b200_scheduler_create.argtypes = [V, ctypes.POINTER(SchedulerParams), ctypes.POINTER(V)]
+            lib.evo_b200_scheduler_free.argtypes = [V]
+            lib.evo_b200_scheduler_submit.argtypes = [V, ctypes.POINTER(Request), REQUEST_CALLBACK, V,
+                                                      ctypes.POINTER(ctypes.c_uint64)]
+            lib.evo_b200_scheduler_cancel.argtypes = [V, ctypes.c_uint64]
+            lib.evo_b200_scheduler_read_metrics.argtypes = [V, ctypes.POINTER(SchedulerMetrics)]
+            lib.evo_b200_scheduler_wait_idle.argtypes = [V]
             lib.evo_b200_model_load_slice.argtypes = [ctypes.c_char_p, ctypes.c_int32, Z, Z,
                                                       ctypes.c_uint32, ctypes.POINTER(V)]
             lib.evo_b200_context_slice_embed.argtypes = [V, V, Z, Z]
@@ -191,6 +225,71 @@ class Model:
         self.library.check(self.library.lib.evo_context_create(self.handle, ctypes.byref(params),
                                                                ctypes.byref(handle)))
         return Context(self.library, handle, self.vocab, self.width)
+
+
+class Scheduler:
+    """Worker pool over shared-weight contexts of one model (evo_b200_scheduler_*).  Results are
+    collected in `results[ticket]` as plain dicts by the completion callback."""
+
+    def __init__(self, model: "Model", workers: int, maximum_queue: int, context_size: int, flags: int = 0):
+        import threading
+
+        self.library = model.library
+        params = SchedulerParams(ctypes.sizeof(SchedulerParams), workers, maximum_queue, context_size, flags)
+        self.handle = ctypes.c_void_p()
+        self.library.check(self.library.lib.evo_b200_scheduler_create(model.handle, ctypes.byref(params),
+                                                                      ctypes.byref(self.handle)))
+        self.results: dict[int, dict] = {}
+        self._lock = threading.Lock()
+
+        @REQUEST_CALLBACK
+        def on_done(ticket, result, _user):
+            r = result.contents
+            entry = {"status": r.status, "error": (r.error or b"").decode(), "cancelled": bool(r.cancelled),
+                     "log_likelihood": r.log_likelihood, "scored_tokens": r.scored_tokens,
+                     "token_log_likelihoods": [r.token_log_likelihoods[i] for i in range(r.scored_tokens)],
+                     "generated": bytes(r.generated[i] for i in range(r.generated_length)),
+                     "queue_seconds": r.queue_seconds, "run_seconds": r.run_seconds}
+            with self._lock:
+                self.results[ticket] = entry
+
+        self._callback = on_done
+
+    def _submit(self, kind: int, payload: bytes, new_tokens: int = 0, **sampler) -> int:
+        request = Request()
+        request.struct_size = ctypes.sizeof(Request)
+        request.kind, request.sequence, request.length, request.new_tokens = kind, payload, len(payload), new_tokens
+        request.sampler = self.library.lib.evo_sampler_default_params()
+        for name, value in sampler.items():
+            setattr(request.sampler, name, value)
+        ticket = ctypes.c_uint64()
+        self.library.check(self.library.lib.evo_b200_scheduler_submit(self.handle, ctypes.byref(request),
+                                                                      self._callback, None, ctypes.byref(ticket)))
+        return ticket.value
+
+    def score(self, sequence: bytes) -> int:
+        """Ticket of the queued request, 0 when the queue was full."""
+        return self._submit(0, bytes(sequence))
+
+    def generate(self, prompt: bytes, tokens: int, **sampler) -> int:
+        return self._submit(1, bytes(prompt), tokens, **sampler)
+
+    def cancel(self, ticket: int) -> bool:
+        return bool(self.library.lib.evo_b200_scheduler_cancel(self.handle, ticket))
+
+    def wait_idle(self) -> None:
+        self.library.lib.evo_b200_scheduler_wait_idle(self.handle)
+
+    def metrics(self) -> dict:
+        m = SchedulerMetrics()
+        m.struct_size = ctypes.sizeof(SchedulerMetrics)
+        self.library.check(self.library.lib.evo_b200_scheduler_read_metrics(self.handle, ctypes.byref(m)))
+        return {name: int(getattr(m, name)) for name, _ in SchedulerMetrics._fields_[1:]}
+
+    def close(self) -> None:
+        if self.handle:
+            self.library.lib.evo_b200_scheduler_free(self.handle)
+            self.handle = None
 
 
 class Context:

@@ -182,6 +182,74 @@ EVO_API evo_status evo_b200_reference_window(const evo_b200_reference *reference
                                              size_t *start, size_t *end, size_t *contig_length,
                                              char *sequence, size_t capacity);
 
+/* ---- request scheduler over shared-weight contexts.
+ * The serving loop behind upstream's `evo serve` (DynamicScheduler,
+ * include/evo/server.hpp:59-88, src/scheduler.cpp:49-201; contexts that share
+ * one copy of the weights, src/cuda/model.cu:2596-2691), without upstream's
+ * HTTP transport (src/server.cpp), which is not part of this library.
+ * `workers` threads each own one long-lived context of `context_size` tokens
+ * and take requests from a bounded queue as they become free; upstream instead
+ * runs batches of up to --max-batch requests behind a barrier and builds a
+ * context per request.  A request is one sequence to score (sum and per-token
+ * next-token log-likelihoods, the rule of `evo score`) or one prompt to extend
+ * by new_tokens sampled tokens.
+ *  - evo_b200_scheduler_submit copies the request, sets *ticket (0 when the
+ *    queue is full: the request is refused and counted as rejected, status
+ *    stays EVO_STATUS_OK) and returns at once; `done` runs later on a worker
+ *    thread with the result, whose pointers are valid during the call.
+ *  - evo_b200_scheduler_cancel marks a queued or running request: it completes
+ *    with cancelled != 0 at its next check (before it starts, between prefill
+ *    chunks, between decoded tokens).
+ *  - evo_b200_scheduler_free cancels what is still queued, lets running
+ *    requests reach their next check, and joins the workers; the model may be
+ *    freed before or after. */
+typedef struct evo_b200_scheduler evo_b200_scheduler;
+typedef struct evo_b200_scheduler_params {
+  size_t struct_size;
+  size_t workers;        /* concurrent contexts, 1..64 */
+  size_t maximum_queue;  /* >= workers */
+  size_t context_size;   /* tokens per context */
+  uint32_t context_flags; /* EVO_CONTEXT_FLAG_* of every context */
+} evo_b200_scheduler_params;
+enum { EVO_B200_REQUEST_SCORE = 0, EVO_B200_REQUEST_GENERATE = 1 };
+typedef struct evo_b200_request {
+  size_t struct_size;
+  int32_t kind;
+  const uint8_t *sequence;
+  size_t length;
+  size_t new_tokens;          /* generate only */
+  evo_sampler_params sampler; /* generate only */
+} evo_b200_request;
+typedef struct evo_b200_request_result {
+  size_t struct_size;
+  evo_status status;
+  const char *error; /* "" when status is OK */
+  int32_t cancelled;
+  double log_likelihood;
+  size_t scored_tokens;
+  const double *token_log_likelihoods; /* scored_tokens values */
+  const uint8_t *generated;
+  size_t generated_length;
+  double queue_seconds;
+  double run_seconds;
+} evo_b200_request_result;
+typedef void (*evo_b200_request_callback)(uint64_t ticket, const evo_b200_request_result *result,
+                                          void *user_data);
+typedef struct evo_b200_scheduler_metrics {
+  size_t struct_size;
+  uint64_t submitted, rejected, completed, failed, cancelled;
+  size_t queued, queue_peak, active, active_peak;
+} evo_b200_scheduler_metrics;
+EVO_API evo_status evo_b200_scheduler_create(const evo_model *model, const evo_b200_scheduler_params *params,
+                                             evo_b200_scheduler **scheduler_out);
+EVO_API void evo_b200_scheduler_free(evo_b200_scheduler *scheduler);
+EVO_API evo_status evo_b200_scheduler_submit(evo_b200_scheduler *scheduler, const evo_b200_request *request,
+                                             evo_b200_request_callback done, void *user_data, uint64_t *ticket);
+EVO_API int evo_b200_scheduler_cancel(evo_b200_scheduler *scheduler, uint64_t ticket);
+EVO_API evo_status evo_b200_scheduler_read_metrics(const evo_b200_scheduler *scheduler,
+                                                   evo_b200_scheduler_metrics *metrics);
+EVO_API void evo_b200_scheduler_wait_idle(const evo_b200_scheduler *scheduler);
+
 /* ---- one pipeline stage per process (torchrun / MPI style launchers).
  * Upstream runs its layer pipeline inside one process
  * (src/cuda/model.cu:2419-2469 plans the stages, :3148-3212 hands the hidden
