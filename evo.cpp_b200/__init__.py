@@ -60,6 +60,9 @@ OPS_SIGNATURES: dict[str, list] = {
     "evo_b200_linear_executor_create": [_I, ctypes.POINTER(_P)],
     "evo_b200_linear_executor_linear": [_P, _P, _Z, _Z, _P, _I, _Z, _Z, _P, _I, _Z, _P],
     "evo_b200_e4m3_encode_array": [_P, _Z, _F, _P],
+    "evo_b200_q8_kv_append": [_P, _P, _P, _P, _P, _P, _Z, _Z, _Z, _Z, _Z, _P],
+    "evo_b200_q8_kv_expand": [_P, _P, _P, _P, _Z, _Z, _Z, _Z, _P, _P, _P],
+    "evo_b200_q8_attention_decode": [_P, _P, _P, _P, _P, _Z, _Z, _Z, _Z, _Z, _P, _P],
 }
 # entry points that do not return a status
 OPS_OTHER = ("evo_b200_last_error", "evo_b200_hcl_scratch_floats", "evo_b200_linear_executor_free",

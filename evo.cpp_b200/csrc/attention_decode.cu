@@ -43,10 +43,22 @@ __device__ __forceinline__ void merge(float &m, float &l, float &acc, const floa
   m = merged;
 }
 
+// 16 int8 codes of one 128-bit load times their vector's scale.
+__device__ __forceinline__ void unpack16_q8(const uint4 codes, const float scale, float (&out)[16]) {
+  const std::uint32_t words[4] = {codes.x, codes.y, codes.z, codes.w};
+#pragma unroll
+  for (int i = 0; i < 16; ++i)
+    out[i] = static_cast<float>(static_cast<std::int8_t>((words[i / 4] >> (8 * (i % 4))) & 0xffU)) * scale;
+}
+
+// kQ8: K and V come from the paged int8 cache of the fast-q8-kv profile (`pages`) instead of
+// the BF16 caches.
+template <bool kQ8>
 __global__ void __launch_bounds__(kDecodeThreads)
 attention_decode_kernel(const bf16 *__restrict__ query, const bf16 *__restrict__ key_cache,
-                        const bf16 *__restrict__ value_cache, bf16 *__restrict__ output, const int rows,
-                        const int static_total_keys, const int heads, const int *__restrict__ dynamic_prefix) {
+                        const bf16 *__restrict__ value_cache, const Q8PageTable pages, bf16 *__restrict__ output,
+                        const int rows, const int static_total_keys, const int heads,
+                        const int *__restrict__ dynamic_prefix) {
   // replayed launches (CUDA graphs) read the number of keys already cached from device memory
   const int total_keys = dynamic_prefix != nullptr ? *dynamic_prefix + rows : static_total_keys;
   __shared__ float warp_partials[kWarps][kPartial];
@@ -79,11 +91,20 @@ attention_decode_kernel(const bf16 *__restrict__ query, const bf16 *__restrict__
     const bool live = key < key_end;
     float k[16], v[16];
     if (live) {
-      const uint4 *const kp = reinterpret_cast<const uint4 *>(key_cache + static_cast<std::size_t>(key) * width + lane_offset);
-      const uint4 *const vp = reinterpret_cast<const uint4 *>(value_cache + static_cast<std::size_t>(key) * width + lane_offset);
-      const uint4 k0 = __ldg(kp), k1 = __ldg(kp + 1), v0 = __ldg(vp), v1 = __ldg(vp + 1);
-      unpack16(k0, k1, k);
-      unpack16(v0, v1, v);
+      if constexpr (kQ8) {
+        const std::size_t page = static_cast<std::size_t>(key) / pages.page_tokens;
+        const std::size_t slot = (static_cast<std::size_t>(key) % pages.page_tokens) * heads + head;
+        const uint4 kc = __ldg(reinterpret_cast<const uint4 *>(pages.key[page] + slot * kHeadDim + part * 16));
+        const uint4 vc = __ldg(reinterpret_cast<const uint4 *>(pages.value[page] + slot * kHeadDim + part * 16));
+        unpack16_q8(kc, __ldg(pages.key_scale[page] + slot), k);
+        unpack16_q8(vc, __ldg(pages.value_scale[page] + slot), v);
+      } else {
+        const uint4 *const kp = reinterpret_cast<const uint4 *>(key_cache + static_cast<std::size_t>(key) * width + lane_offset);
+        const uint4 *const vp = reinterpret_cast<const uint4 *>(value_cache + static_cast<std::size_t>(key) * width + lane_offset);
+        const uint4 k0 = __ldg(kp), k1 = __ldg(kp + 1), v0 = __ldg(vp), v1 = __ldg(vp + 1);
+        unpack16(k0, k1, k);
+        unpack16(v0, v1, v);
+      }
     } else {
 #pragma unroll
       for (int i = 0; i < 16; ++i) k[i] = v[i] = 0.0F;
@@ -163,9 +184,11 @@ bool attention_decode_applicable(const void *query, const void *key_cache, const
   return true;
 }
 
-int attention_decode(const void *query, const void *key_cache, const void *value_cache, const std::size_t rows,
-                     const std::size_t total_keys, const std::size_t heads, void *output, cudaStream_t stream,
-                     const int *dynamic_prefix) {
+namespace {
+template <bool kQ8>
+int launch_decode(const void *query, const void *key_cache, const void *value_cache, const Q8PageTable &pages,
+                  const std::size_t rows, const std::size_t total_keys, const std::size_t heads, void *output,
+                  cudaStream_t stream, const int *dynamic_prefix) {
   cudaLaunchConfig_t config{};
   config.gridDim = dim3(kSplits, static_cast<unsigned int>(heads), static_cast<unsigned int>(rows));
   config.blockDim = dim3(kDecodeThreads);
@@ -179,12 +202,32 @@ int attention_decode(const void *query, const void *key_cache, const void *value
   config.attrs = &attribute;
   config.numAttrs = 1;
   const cudaError_t error = cudaLaunchKernelEx(
-      &config, attention_decode_kernel, static_cast<const bf16 *>(query), static_cast<const bf16 *>(key_cache),
-      static_cast<const bf16 *>(value_cache), static_cast<bf16 *>(output), static_cast<int>(rows),
-      static_cast<int>(total_keys), static_cast<int>(heads), dynamic_prefix);
+      &config, attention_decode_kernel<kQ8>, static_cast<const bf16 *>(query),
+      static_cast<const bf16 *>(key_cache), static_cast<const bf16 *>(value_cache), pages,
+      static_cast<bf16 *>(output), static_cast<int>(rows), static_cast<int>(total_keys), static_cast<int>(heads),
+      dynamic_prefix);
   if (error != cudaSuccess)
     return fail(kCuda, std::string("attention decode kernel launch failed: ") + cudaGetErrorString(error));
   return check_launch("attention decode kernel");
+}
+}  // namespace
+
+int attention_decode(const void *query, const void *key_cache, const void *value_cache, const std::size_t rows,
+                     const std::size_t total_keys, const std::size_t heads, void *output, cudaStream_t stream,
+                     const int *dynamic_prefix) {
+  return launch_decode<false>(query, key_cache, value_cache, Q8PageTable{}, rows, total_keys, heads, output, stream,
+                              dynamic_prefix);
+}
+
+int q8_attention_decode(const void *query, const Q8PageTable &pages, const std::size_t rows,
+                        const std::size_t total_keys, const std::size_t heads, const std::size_t head_dim,
+                        void *output, cudaStream_t stream) {
+  if (query == nullptr || output == nullptr || pages.key == nullptr || pages.value == nullptr ||
+      pages.key_scale == nullptr || pages.value_scale == nullptr || pages.page_tokens == 0 || head_dim != kHeadDim ||
+      rows == 0 || rows > 8 || heads == 0 || heads > 65535 || total_keys < rows || total_keys > 0x7fffff00U ||
+      (reinterpret_cast<std::uintptr_t>(query) & 15U) != 0)
+    return fail(kInvalidArgument, "quantised decode attention arguments are invalid (1..8 rows, head size 128)");
+  return launch_decode<true>(query, nullptr, nullptr, pages, rows, total_keys, heads, output, stream, nullptr);
 }
 
 }  // namespace evob

@@ -537,6 +537,37 @@ int evo_b200_linear_executor_linear(evo_b200_linear_executor *executor, const fl
                                 bias_elements, output);
 }
 
+// ---- quantised KV cache
+static Q8PageTable q8_table(void *const *key_pages, void *const *value_pages, void *const *key_scale_pages,
+                            void *const *value_scale_pages, size_t page_tokens) {
+  Q8PageTable table;
+  table.key = reinterpret_cast<std::int8_t *const *>(key_pages);
+  table.value = reinterpret_cast<std::int8_t *const *>(value_pages);
+  table.key_scale = reinterpret_cast<float *const *>(key_scale_pages);
+  table.value_scale = reinterpret_cast<float *const *>(value_scale_pages);
+  table.page_tokens = page_tokens;
+  return table;
+}
+int evo_b200_q8_kv_append(const void *key, const void *value, void *const *key_pages, void *const *value_pages,
+                          void *const *key_scale_pages, void *const *value_scale_pages, size_t page_tokens,
+                          size_t first_position, size_t rows, size_t heads, size_t head_dim, void *stream) {
+  return q8_kv_append(key, value, q8_table(key_pages, value_pages, key_scale_pages, value_scale_pages, page_tokens),
+                      first_position, rows, heads, head_dim, as_stream(stream));
+}
+int evo_b200_q8_kv_expand(void *const *key_pages, void *const *value_pages, void *const *key_scale_pages,
+                          void *const *value_scale_pages, size_t page_tokens, size_t count, size_t heads,
+                          size_t head_dim, void *key, void *value, void *stream) {
+  return q8_kv_expand(q8_table(key_pages, value_pages, key_scale_pages, value_scale_pages, page_tokens), count, heads,
+                      head_dim, key, value, as_stream(stream));
+}
+int evo_b200_q8_attention_decode(const void *query, void *const *key_pages, void *const *value_pages,
+                                 void *const *key_scale_pages, void *const *value_scale_pages, size_t page_tokens,
+                                 size_t rows, size_t total_keys, size_t heads, size_t head_dim, void *output,
+                                 void *stream) {
+  return q8_attention_decode(query, q8_table(key_pages, value_pages, key_scale_pages, value_scale_pages, page_tokens),
+                             rows, total_keys, heads, head_dim, output, as_stream(stream));
+}
+
 // ---- host E4M3FN codec (include/evo/fp8.hpp)
 uint8_t evo_b200_e4m3_encode(float value) { return fp8::encode_e4m3fn(value); }
 float evo_b200_e4m3_decode(uint8_t code) { return fp8::decode_e4m3fn(code); }

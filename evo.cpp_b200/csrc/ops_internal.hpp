@@ -214,6 +214,27 @@ int modal_decode(const void *x2, const void *x1, const void *value,
                  float *state, void *pregate, void *output,
                  cudaStream_t stream);
 
+// ---- kv_q8.cu: quantised KV cache (profile fast-q8-kv)
+// Device arrays of page pointers; page p holds positions [p * page_tokens, (p + 1) * page_tokens):
+// codes [page_tokens, heads, 128] int8 and scales [page_tokens, heads] F32.
+struct Q8PageTable {
+  std::int8_t *const *key = nullptr;
+  std::int8_t *const *value = nullptr;
+  float *const *key_scale = nullptr;
+  float *const *value_scale = nullptr;
+  std::size_t page_tokens = 0;
+};
+// K, V: BF16 [rows, heads, head_dim] of positions first_position ..; the pages must exist.
+int q8_kv_append(const void *key, const void *value, const Q8PageTable &pages, std::size_t first_position,
+                 std::size_t rows, std::size_t heads, std::size_t head_dim, cudaStream_t stream);
+// BF16 images [count, heads, head_dim] of positions [0, count).
+int q8_kv_expand(const Q8PageTable &pages, std::size_t count, std::size_t heads, std::size_t head_dim, void *key,
+                 void *value, cudaStream_t stream);
+// Decode attention (1..8 query rows, head size 128) straight from the pages; same contract as
+// causal_attention.
+int q8_attention_decode(const void *query, const Q8PageTable &pages, std::size_t rows, std::size_t total_keys,
+                        std::size_t heads, std::size_t head_dim, void *output, cudaStream_t stream);
+
 // ---- attention.cu
 int split_rope_append(const void *qkv, const float *inverse_frequency,
                       std::size_t rows, std::size_t heads,

@@ -236,18 +236,20 @@ evo_status evo_context_create(const evo_model *model, const evo_context_params *
         return fail(evob::kInvalidArgument, "evo_context_params.struct_size is too small");
       p = *params;
     }
-    if ((p.flags & EVO_CONTEXT_FLAG_FAST_Q8_KV) != 0)
-      return fail(evob::kUnsupported, "the fast-q8-kv profile is not available in this build");
+    const bool q8_kv = (p.flags & EVO_CONTEXT_FLAG_FAST_Q8_KV) != 0;
     const bool fp8_ffn = (p.flags & EVO_CONTEXT_FLAG_B200_FP8_FFN) != 0;
     const bool tensor_core = fp8_ffn || (p.flags & EVO_CONTEXT_FLAG_B200_TENSORCORE_FP8) != 0;
     auto context = std::make_unique<evo_context>();
     context->profile = fp8_ffn ? "b200-fp8" : tensor_core ? "b200-tc" : "exact";
+    // upstream's name for the quantised-cache profile; the projection profile is appended when
+    // it is not the default
+    if (q8_kv) context->profile = context->profile == "exact" ? "fast-q8-kv" : "fast-q8-kv+" + context->profile;
     const int status = evob::Context::create(
         model->weights, p.context_size,
         fp8_ffn       ? evob::ExecutionProfile::kTensorCoreFfn
         : tensor_core ? evob::ExecutionProfile::kTensorCore
                       : evob::ExecutionProfile::kExact,
-        (p.flags & EVO_CONTEXT_FLAG_B200_FULL_ARENA) != 0, &context->context);
+        (p.flags & EVO_CONTEXT_FLAG_B200_FULL_ARENA) != 0, &context->context, q8_kv);
     if (status != kOk) return status;
     *context_out = context.release();
     return kOk;
@@ -695,8 +697,7 @@ evo_status evo_b200_scheduler_create(const evo_model *model, const evo_b200_sche
     if (model == nullptr || params == nullptr || scheduler_out == nullptr ||
         params->struct_size < sizeof(evo_b200_scheduler_params))
       return fail(evob::kInvalidArgument, "model, scheduler parameters and output are required");
-    if ((params->context_flags & EVO_CONTEXT_FLAG_FAST_Q8_KV) != 0)
-      return fail(evob::kUnsupported, "the fast-q8-kv profile is not available in this build");
+    const bool q8_kv = (params->context_flags & EVO_CONTEXT_FLAG_FAST_Q8_KV) != 0;
     const bool fp8_ffn = (params->context_flags & EVO_CONTEXT_FLAG_B200_FP8_FFN) != 0;
     const bool tensor_core = fp8_ffn || (params->context_flags & EVO_CONTEXT_FLAG_B200_TENSORCORE_FP8) != 0;
     auto handle = std::make_unique<evo_b200_scheduler>();
@@ -705,7 +706,7 @@ evo_status evo_b200_scheduler_create(const evo_model *model, const evo_b200_sche
         fp8_ffn       ? evob::ExecutionProfile::kTensorCoreFfn
         : tensor_core ? evob::ExecutionProfile::kTensorCore
                       : evob::ExecutionProfile::kExact,
-        (params->context_flags & EVO_CONTEXT_FLAG_B200_FULL_ARENA) != 0, &handle->scheduler);
+        (params->context_flags & EVO_CONTEXT_FLAG_B200_FULL_ARENA) != 0, q8_kv, &handle->scheduler);
     if (status != kOk) return status;
     *scheduler_out = handle.release();
     return kOk;

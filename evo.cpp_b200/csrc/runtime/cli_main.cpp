@@ -278,7 +278,7 @@ Options parse(int argc, char **argv) {
       for (std::string item; std::getline(list, item, ',');) o.gpus.push_back(std::stoi(item));
     } else if (a == "--version") { std::cout << evo_version_string() << '\n'; std::exit(0); }
     else if (a == "--help" || a == "-h") {
-      std::cout << "usage:\n  evo run -m MODEL -p DNA -n TOKENS [--ctx N --gpu 0,1 --profile exact|b200-tc|b200-fp8]\n"
+      std::cout << "usage:\n  evo run -m MODEL -p DNA -n TOKENS [--ctx N --gpu 0,1 --profile exact|b200-tc|b200-fp8|fast-q8-kv]\n"
                    "  evo score -m MODEL --input FASTA_FASTQ_OR_TEXT\n"
                    "  evo bench -m MODEL --input FASTA_FASTQ_OR_TEXT [--warmup N --repetitions N]\n"
                    "  evo embed -m MODEL --input FASTA_FASTQ_OR_TEXT --output DIR --layer N "
@@ -292,8 +292,8 @@ Options parse(int argc, char **argv) {
     } else die(EVO_STATUS_INVALID_ARGUMENT, "unknown option " + a);
   }
   if (o.model.empty()) die(EVO_STATUS_INVALID_ARGUMENT, "a model path is required (-m)");
-  if (o.profile != "exact" && o.profile != "b200-tc" && o.profile != "b200-fp8")
-    die(EVO_STATUS_UNSUPPORTED, "profile must be exact, b200-tc or b200-fp8");
+  if (o.profile != "exact" && o.profile != "b200-tc" && o.profile != "b200-fp8" && o.profile != "fast-q8-kv")
+    die(EVO_STATUS_UNSUPPORTED, "profile must be exact, b200-tc, b200-fp8 or fast-q8-kv");
   return o;
 }
 
@@ -307,6 +307,7 @@ evo_context *new_context(const evo_model *model, const Options &o) {
   params.context_size = o.context;
   if (o.profile == "b200-tc") params.flags |= EVO_CONTEXT_FLAG_B200_TENSORCORE_FP8;
   if (o.profile == "b200-fp8") params.flags |= EVO_CONTEXT_FLAG_B200_FP8_FFN;
+  if (o.profile == "fast-q8-kv") params.flags |= EVO_CONTEXT_FLAG_FAST_Q8_KV;
   evo_context *context = nullptr;
   check(evo_context_create(model, &params, &context), "context");
   return context;
@@ -332,7 +333,8 @@ void print_metrics(const Metrics &m, const Options &o, const evo_context *contex
             << ",\"teacher_force_tokens\":0,\"teacher_force_seconds\":0,\"teacher_force_tokens_per_second\":0"
             << ",\"decode_tokens\":" << m.decode_tokens << ",\"decode_seconds\":" << m.decode_seconds
             << ",\"decode_tokens_per_second\":" << rate(m.decode_tokens, m.decode_seconds)
-            << ",\"kv_cache\":\"bf16_contiguous\",\"profile\":\"" << o.profile
+            << ",\"kv_cache\":\"" << (o.profile == "fast-q8-kv" ? "q8_paged" : "bf16_contiguous")
+            << "\",\"profile\":\"" << o.profile
             << "\",\"retained_logits_peak_bytes\":0,\"gpus\":[";
   const size_t stages = context == nullptr ? 0 : evo_b200_context_stage_count(context);
   for (size_t i = 0; i < stages; ++i) {
@@ -670,6 +672,7 @@ int main(int argc, char **argv) {
     sp.context_size = o.context;
     if (o.profile == "b200-tc") sp.context_flags |= EVO_CONTEXT_FLAG_B200_TENSORCORE_FP8;
     if (o.profile == "b200-fp8") sp.context_flags |= EVO_CONTEXT_FLAG_B200_FP8_FFN;
+    if (o.profile == "fast-q8-kv") sp.context_flags |= EVO_CONTEXT_FLAG_FAST_Q8_KV;
     evo_b200_scheduler *scheduler = nullptr;
     check(evo_b200_scheduler_create(model, &sp, &scheduler), "scheduler");
     struct Pending {

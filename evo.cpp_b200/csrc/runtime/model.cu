@@ -49,6 +49,7 @@ struct DeviceGuard {
 // multiple of 16 so the tensor-core FIR tiles keep their alignment).
 constexpr std::size_t kHistoryPad = 144;
 constexpr std::size_t kSplitWorkspaceBytes = std::size_t{64} << 20;
+constexpr std::size_t kQ8PageTokens = 16384;  // upstream src/cuda/model.cu:33
 
 struct LayerState {
   float *short_cache = nullptr;  // [3D, short_taps-1]
@@ -60,6 +61,20 @@ struct LayerState {
   // a stage, so a block's own history is parked here between chunks.
   void *history = nullptr;
   std::size_t history_rows = 0;
+  // fast-q8-kv: page p holds positions [p * kQ8PageTokens, ...); pointers are mirrored in four
+  // device arrays (key codes, value codes, key scales, value scales) that the kernels index
+  std::vector<void *> q8_pages[4];
+  void **q8_tables = nullptr;  // [4][page_count] device
+  std::size_t q8_page_count = 0;
+  Q8PageTable q8_table() const {
+    Q8PageTable t;
+    t.key = reinterpret_cast<std::int8_t *const *>(q8_tables);
+    t.value = reinterpret_cast<std::int8_t *const *>(q8_tables + q8_page_count);
+    t.key_scale = reinterpret_cast<float *const *>(q8_tables + 2 * q8_page_count);
+    t.value_scale = reinterpret_cast<float *const *>(q8_tables + 3 * q8_page_count);
+    t.page_tokens = kQ8PageTokens;
+    return t;
+  }
 };
 
 struct Context::Stage {
@@ -78,6 +93,8 @@ struct Context::Stage {
   void *short_filtered = nullptr, *x2 = nullptr, *x1 = nullptr, *value = nullptr, *pregate = nullptr;
   float *modal_scratch = nullptr;
   void *split_workspace = nullptr;  // F32 partial sums of split-K projections (<= 128 rows)
+  // fast-q8-kv: BF16 images [context, D] of the keys and values one attention block at a time
+  void *kv_image_key = nullptr, *kv_image_value = nullptr;
   std::uint32_t *tokens = nullptr;
   void *logits = nullptr;
   std::vector<LayerState> layers;
@@ -130,6 +147,27 @@ struct Context::Stage {
     move(projection, D * 6);
     move(short_filtered, D * 6);
     for (void **p : {&gated, &mlp_first, &mlp_second}) move(*p, I * 2);
+  }
+
+  // Pages of one attention block up to position `tokens_end` (exclusive); new pointers are
+  // written into the device tables in stream order.
+  int ensure_q8_pages(LayerState &state, const std::size_t tokens_end, const std::size_t heads,
+                      const std::size_t head_dim) {
+    const std::size_t needed = (tokens_end + kQ8PageTokens - 1) / kQ8PageTokens;
+    if (needed > state.q8_page_count) return fail(kInvalidArgument, "quantised KV cache capacity exceeded");
+    for (std::size_t page = state.q8_pages[0].size(); page < needed; ++page) {
+      for (int which = 0; which < 4; ++which) {
+        void *memory = nullptr;
+        const std::size_t bytes = which < 2 ? kQ8PageTokens * heads * head_dim : kQ8PageTokens * heads * sizeof(float);
+        const int status = allocate(&memory, bytes, &cache_bytes);
+        if (status != kOk) return status;
+        state.q8_pages[which].push_back(memory);
+        if (cudaMemcpyAsync(state.q8_tables + which * state.q8_page_count + page, &state.q8_pages[which][page],
+                            sizeof(void *), cudaMemcpyHostToDevice, stream) != cudaSuccess)
+          return fail(kCuda, "cannot publish a quantised KV page");
+      }
+    }
+    return kOk;
   }
 
   int allocate(void **out, const std::size_t bytes, std::size_t *counter) {
@@ -402,16 +440,19 @@ int Context::decode_step_graph(const std::uint32_t *host_token, bool *launched) 
 
 int Context::create(std::shared_ptr<ModelWeights> weights, const std::size_t context_size,
                     const ExecutionProfile profile, const bool full_arena_for_fixtures,
-                    std::unique_ptr<Context> *out) {
+                    std::unique_ptr<Context> *out, const bool q8_kv) {
   if (weights == nullptr || out == nullptr || context_size == 0)
     return fail(kInvalidArgument, "context arguments are invalid");
   const ModelConfig &c = weights->config;
   if (!c.test_fixture && context_size > c.max_seqlen)
     return fail(kInvalidArgument, "requested context exceeds model maximum of " +
                                       std::to_string(c.max_seqlen));
+  if (q8_kv && c.head_dim() != 128)
+    return fail(kUnsupported, "the fast-q8-kv profile needs attention heads of 128 dimensions");
   std::unique_ptr<Context> context(new Context());
   context->weights_ = weights;
   context->profile_ = profile;
+  context->q8_kv_ = q8_kv;
   if (const char *const parts = std::getenv("EVO_B200_FP8_FFN_PARTS"))
     context->fp8_ffn_parts_ = static_cast<unsigned>(std::strtoul(parts, nullptr, 0)) & 7U;
   context->context_size_ = context_size;
@@ -465,6 +506,18 @@ int Context::create(std::shared_ptr<ModelWeights> weights, const std::size_t con
     for (std::size_t i = 0; i < stage->layers.size(); ++i) {
       LayerState &state = stage->layers[i];
       const MixerType type = stage_weights->layers[i].type;
+      if (type == MixerType::kAttention && q8_kv) {
+        state.q8_page_count = (context_size + kQ8PageTokens - 1) / kQ8PageTokens;
+        EVOB_TRY(stage->allocate(&p, 4 * state.q8_page_count * sizeof(void *), cache));
+        state.q8_tables = static_cast<void **>(p);
+        if (cudaMemset(state.q8_tables, 0, 4 * state.q8_page_count * sizeof(void *)) != cudaSuccess)
+          return fail(kCuda, "cannot clear the quantised KV page tables");
+        if (stage->kv_image_key == nullptr) {
+          EVOB_TRY(stage->allocate(&stage->kv_image_key, context_size * D * 2, cache));
+          EVOB_TRY(stage->allocate(&stage->kv_image_value, context_size * D * 2, cache));
+        }
+        continue;
+      }
       if (type == MixerType::kAttention) {
         EVOB_TRY(stage->allocate(&state.key_cache, context_size * D * 2, cache));
         EVOB_TRY(stage->allocate(&state.value_cache, context_size * D * 2, cache));
@@ -499,7 +552,7 @@ int Context::create(std::shared_ptr<ModelWeights> weights, const std::size_t con
     EVOB_TRY(first.allocate(&p, 16, &first.arena_bytes));
     context->device_position_ = static_cast<int *>(p);
     const char *const graphs = std::getenv("EVO_B200_DECODE_GRAPH");
-    context->decode_graph_allowed_ = graphs == nullptr || std::string(graphs) != "0";
+    context->decode_graph_allowed_ = (graphs == nullptr || std::string(graphs) != "0") && !q8_kv;
   }
   // Direct peer copies between neighbouring stages (and last -> first for the
   // head); without peer access the copies still work, staged by the driver.
@@ -647,25 +700,44 @@ int Context::run_stage(Stage &s, const std::size_t rows, const Mode mode,
       EVOB_TRY(emit_bf16(stream, *tap, layer_index, DumpPoint::kMixerInputProjection, s.projection, rows, 3 * D));
     if (attention) {
       const std::size_t prefix = window ? window_position : (initial ? 0 : position_);
+      void *const keys = q8_kv_ ? s.kv_image_key : state.key_cache;
+      void *const values = q8_kv_ ? s.kv_image_value : state.value_cache;
+      if (q8_kv_) EVOB_TRY(s.ensure_q8_pages(state, prefix + rows, c.heads, c.head_dim()));
       EVOB_OP(kCatAttention, split_rope_append(s.projection, w.inverse_frequency, rows, c.heads, c.head_dim(),
-                                 prefix, c.rope_scale, false, s.query, state.key_cache,
-                                 state.value_cache, context_size_, stream,
+                                 prefix, c.rope_scale, false, s.query, keys, values, context_size_, stream,
                                  mode == Mode::kDecode ? dynamic_position_ : nullptr));
+      bool attended = false;
+      if (q8_kv_) {
+        // the new rows go into the pages as int8; what attention reads back is their quantised
+        // value, for these rows as for every earlier one
+        const Q8PageTable table = state.q8_table();
+        EVOB_OP(kCatAttention, q8_kv_append(static_cast<unsigned char *>(keys) + prefix * D * 2,
+                                            static_cast<unsigned char *>(values) + prefix * D * 2, table, prefix, rows,
+                                            c.heads, c.head_dim(), stream));
+        if (rows <= 8) {
+          EVOB_OP(kCatAttention, q8_attention_decode(s.query, table, rows, prefix + rows, c.heads, c.head_dim(),
+                                                     s.mixer_out, stream));
+          attended = true;
+        } else {
+          EVOB_OP(kCatAttention, q8_kv_expand(table, prefix + rows, c.heads, c.head_dim(), keys, values, stream));
+        }
+      }
       if (tap != nullptr) {
         // rotated queries, and the rotated keys / values where the append left them in the cache
         EVOB_TRY(emit_bf16(stream, *tap, layer_index, DumpPoint::kMixerX2, s.query, rows, D));
         EVOB_TRY(emit_bf16(stream, *tap, layer_index, DumpPoint::kMixerX1,
-                           static_cast<unsigned char *>(state.key_cache) + prefix * D * 2, rows, D));
+                           static_cast<unsigned char *>(keys) + prefix * D * 2, rows, D));
         EVOB_TRY(emit_bf16(stream, *tap, layer_index, DumpPoint::kMixerValue,
-                           static_cast<unsigned char *>(state.value_cache) + prefix * D * 2, rows, D));
+                           static_cast<unsigned char *>(values) + prefix * D * 2, rows, D));
       }
-      const bool cached = mode == Mode::kCachedPrefill ||
-                          ((mode == Mode::kDecode || mode == Mode::kContinue) && cached_attention_);
-      if (cached)
-        EVOB_OP(kCatAttention, cached_attention(s.query, state.key_cache, state.value_cache, rows, prefix + rows,
+      const bool cached = !q8_kv_ && (mode == Mode::kCachedPrefill ||
+                                      ((mode == Mode::kDecode || mode == Mode::kContinue) && cached_attention_));
+      if (attended) {
+      } else if (cached)
+        EVOB_OP(kCatAttention, cached_attention(s.query, keys, values, rows, prefix + rows,
                                   c.heads, c.head_dim(), s.mixer_out, stream));
       else
-        EVOB_OP(kCatAttention, causal_attention(s.query, state.key_cache, state.value_cache, rows, prefix + rows,
+        EVOB_OP(kCatAttention, causal_attention(s.query, keys, values, rows, prefix + rows,
                                   c.heads, c.head_dim(), s.mixer_out, stream,
                                   mode == Mode::kDecode ? dynamic_position_ : nullptr));
     } else if (initial) {

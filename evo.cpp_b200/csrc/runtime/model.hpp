@@ -155,9 +155,11 @@ int load_weights(const ModelFile &file, const std::vector<int> &devices,
 class Context {
  public:
   ~Context();
+  // q8_kv: keys and values are kept as per-vector int8 in lazily allocated pages of 16,384
+  // tokens (upstream's fast-q8-kv profile, docs/execution-profiles.md:96-127); head size 128 only.
   static int create(std::shared_ptr<ModelWeights> weights, std::size_t context_size,
                     ExecutionProfile profile, bool full_arena_for_fixtures,
-                    std::unique_ptr<Context> *out);
+                    std::unique_ptr<Context> *out, bool q8_kv = false);
 
   // logits: rows * vocab floats (converted from BF16).
   int prefill(const std::vector<std::uint32_t> &tokens, std::vector<float> *logits);
@@ -216,6 +218,7 @@ class Context {
   std::vector<StageAssignment> stages() const;
   bool shares_weights_with(const Context &other) const { return weights_ == other.weights_; }
   bool poisoned() const { return !healthy_; }
+  bool uses_q8_kv_cache() const { return q8_kv_; }
 
  private:
   struct Stage;
@@ -252,6 +255,7 @@ class Context {
   // Which projections the FP8 FFN profile quantises: bit 0 output projection, bit 1 MLP
   // up-projections, bit 2 MLP down-projection (EVO_B200_FP8_FFN_PARTS, default all).
   unsigned fp8_ffn_parts_ = 7U;
+  bool q8_kv_ = false;
   std::size_t context_size_ = 0, arena_rows_ = 0, position_ = 0;
   bool state_valid_ = false, cached_attention_ = false, healthy_ = true;
   bool history_current_ = false;  // per-block projection history covers the rows up to position_

@@ -38,7 +38,7 @@ struct Scheduler::Impl {
   std::vector<std::thread> threads;
   std::size_t maximum_queue = 0, context_size = 0;
   ExecutionProfile profile = ExecutionProfile::kExact;
-  bool full_arena = false;
+  bool full_arena = false, q8_kv = false;
 
   mutable std::mutex mutex;
   mutable std::condition_variable wake, idle;
@@ -148,7 +148,7 @@ struct Scheduler::Impl {
         try {
           if (contexts[index] == nullptr || contexts[index]->poisoned()) {
             contexts[index].reset();
-            const int status = Context::create(weights, context_size, profile, full_arena, &contexts[index]);
+            const int status = Context::create(weights, context_size, profile, full_arena, &contexts[index], q8_kv);
             if (status != kOk) {
               result.status = status;
               result.error = last_error();
@@ -185,7 +185,7 @@ struct Scheduler::Impl {
 
 int Scheduler::create(std::shared_ptr<ModelWeights> weights, const std::size_t workers,
                       const std::size_t maximum_queue, const std::size_t context_size,
-                      const ExecutionProfile profile, const bool full_arena_for_fixtures,
+                      const ExecutionProfile profile, const bool full_arena_for_fixtures, const bool q8_kv,
                       std::unique_ptr<Scheduler> *out) {
   if (out == nullptr || weights == nullptr || workers == 0 || workers > 64 || maximum_queue == 0 ||
       maximum_queue < workers || context_size == 0)
@@ -200,10 +200,11 @@ int Scheduler::create(std::shared_ptr<ModelWeights> weights, const std::size_t w
   impl.context_size = context_size;
   impl.profile = profile;
   impl.full_arena = full_arena_for_fixtures;
+  impl.q8_kv = q8_kv;
   impl.contexts.resize(workers);
   for (std::size_t i = 0; i < workers; ++i) {
     const int status = Context::create(impl.weights, context_size, profile, full_arena_for_fixtures,
-                                       &impl.contexts[i]);
+                                       &impl.contexts[i], q8_kv);
     if (status != kOk) return status;
   }
   for (std::size_t i = 0; i < workers; ++i) impl.threads.emplace_back([&impl, i] { impl.worker(i); });

@@ -59,7 +59,7 @@ class Scheduler {
   // `workers` contexts of `context_size` tokens are created up front.
   static int create(std::shared_ptr<ModelWeights> weights, std::size_t workers, std::size_t maximum_queue,
                     std::size_t context_size, ExecutionProfile profile, bool full_arena_for_fixtures,
-                    std::unique_ptr<Scheduler> *out);
+                    bool q8_kv, std::unique_ptr<Scheduler> *out);
   ~Scheduler();  // cancels what is queued, lets running requests finish their current step, joins
 
   // 0 when the queue is full or the scheduler is stopping (counted as rejected);

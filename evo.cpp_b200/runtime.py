@@ -13,6 +13,7 @@ import numpy as np
 
 BACKEND_AUTO, BACKEND_CUDA, BACKEND_CPU = 0, 1, 2
 MODEL_FLAG_ALLOW_SYNTHETIC = 1
+CONTEXT_FLAG_FAST_Q8_KV = 1 << 0
 CONTEXT_FLAG_TENSORCORE_FP8 = 1 << 8
 CONTEXT_FLAG_FULL_ARENA = 1 << 9
 CONTEXT_FLAG_FP8_FFN = 1 << 10

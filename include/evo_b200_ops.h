@@ -320,6 +320,30 @@ EVO_B200_API int evo_b200_linear_executor_linear(
     int bias_dtype, size_t bias_elements, float *output);
 
 
+/* ---- quantised KV cache (profile fast-q8-kv; upstream src/cuda/attention.cu:798-866 append,
+ * :1072-1141 attention; docs/execution-profiles.md:96-127).  A cache is four device arrays of
+ * page pointers - key codes, value codes (int8 [page_tokens, heads, 128]) and key scales, value
+ * scales (F32 [page_tokens, heads]); page p holds positions [p * page_tokens, (p+1) * page_tokens).
+ * Every (token, head) vector has scale = max|v| / 127 (1 for a zero vector) and codes
+ * clamp(rint(v / scale), -127, 127).  append quantises BF16 K / V [rows, heads, 128] of positions
+ * first_position ..; expand writes BF16 images [count, heads, 128] of positions [0, count);
+ * attention_decode is causal attention of 1..8 query rows (row i sees keys 0 .. total_keys - rows
+ * + i) read straight from the pages. */
+EVO_B200_API int evo_b200_q8_kv_append(const void *key, const void *value, void *const *key_pages,
+                                       void *const *value_pages, void *const *key_scale_pages,
+                                       void *const *value_scale_pages, size_t page_tokens,
+                                       size_t first_position, size_t rows, size_t heads, size_t head_dim,
+                                       void *stream);
+EVO_B200_API int evo_b200_q8_kv_expand(void *const *key_pages, void *const *value_pages,
+                                       void *const *key_scale_pages, void *const *value_scale_pages,
+                                       size_t page_tokens, size_t count, size_t heads, size_t head_dim,
+                                       void *key, void *value, void *stream);
+EVO_B200_API int evo_b200_q8_attention_decode(const void *query, void *const *key_pages,
+                                              void *const *value_pages, void *const *key_scale_pages,
+                                              void *const *value_scale_pages, size_t page_tokens, size_t rows,
+                                              size_t total_keys, size_t heads, size_t head_dim, void *output,
+                                              void *stream);
+
 /* ---- host E4M3FN codec (no GPU needed): upstream evo::fp8
  * (include/evo/fp8.hpp:9-18, src/fp8.cpp:26-77).  Round-to-nearest-even,
  * satfinite (|v| >= 448 and infinities -> +-448), NaN -> 0x7f | sign.
