@@ -329,17 +329,55 @@ evo_status evo_context_decode(evo_context *context, uint32_t token, evo_logits_c
   });
 }
 
-static int embed_rows(evo_context *context, const evo_batch *batch, const size_t layer,
-                      std::vector<float> *hidden, std::size_t *rows) {
+// Shared body of evo_context_embed / evo_context_embed_ex (upstream src/c_api.cpp:1075-1330): a fresh
+// context, one sequence, chunks of the activation capacity, the context advanced as by a prefill.
+// `deliver` gets every chunk's rows (pooling "none") or the pooled row once at the end.
+static int embed_chunks(evo_context *context, const evo_batch *batch, const size_t layer, const std::string &pooling,
+                        const std::function<evo_status(const float *, size_t rows, size_t offset, size_t total)> &deliver) {
   if (context->failed || context->context->poisoned())
     return fail(evob::kInvalidArgument, "context was invalidated by an earlier failure");
+  if (context->context->position() != 0)
+    return fail(evob::kInvalidArgument, "embedding requires a fresh context");
   std::vector<std::uint32_t> tokens;
-  const int status = single_sequence_tokens(batch, &tokens);
+  int status = single_sequence_tokens(batch, &tokens);
   if (status != kOk) return status;
-  if (tokens.size() > context->context->activation_capacity())
-    return fail(evob::kUnsupported, "embedding input exceeds the activation arena");
-  *rows = tokens.size();
-  return context->context->prefill_embedding(tokens, layer, hidden);
+  if (tokens.size() > context->context->context_capacity())
+    return fail(evob::kInvalidArgument, "sequence exceeds the context capacity");
+  if (layer >= context->context->config().layers)
+    return fail(evob::kInvalidArgument, "layer capture index or output is invalid");
+  context->failed = true;  // cleared only if every chunk and callback succeeds
+  const std::size_t capacity = context->context->activation_capacity();
+  const std::size_t width = context->context->config().width;
+  std::vector<float> hidden, pooled(pooling == "mean" ? width : 0, 0.0F);
+  for (std::size_t offset = 0; offset < tokens.size();) {
+    const std::size_t rows = std::min(capacity, tokens.size() - offset);
+    const std::vector<std::uint32_t> chunk(tokens.begin() + offset, tokens.begin() + offset + rows);
+    status = context->context->prefill_chunk_embedding(chunk, layer, offset == 0, &hidden);
+    if (status != kOk) return status;
+    if (hidden.size() != rows * width) return fail(evob::kInternal, "backend returned an incomplete embedding");
+    if (pooling == "none") {
+      const evo_status delivered = deliver(hidden.data(), rows, offset, tokens.size());
+      if (delivered != EVO_STATUS_OK)
+        return fail(valid_status(delivered) ? delivered : EVO_STATUS_INTERNAL, "embedding consumer aborted");
+    } else if (pooling == "mean") {
+      for (std::size_t r = 0; r < rows; ++r)
+        for (std::size_t c = 0; c < width; ++c) pooled[c] += hidden[r * width + c];
+    }
+    offset += rows;
+  }
+  if (pooling != "none") {
+    const float *row = pooled.data();
+    if (pooling == "mean") {
+      for (float &v : pooled) v /= static_cast<float>(tokens.size());
+    } else {
+      row = hidden.data() + (hidden.size() / width - 1) * width;  // "last": final row of the final chunk
+    }
+    const evo_status delivered = deliver(row, 1, 0, tokens.size());
+    if (delivered != EVO_STATUS_OK)
+      return fail(valid_status(delivered) ? delivered : EVO_STATUS_INTERNAL, "embedding consumer aborted");
+  }
+  context->failed = false;
+  return kOk;
 }
 
 evo_status evo_context_embed(evo_context *context, const evo_batch *batch, size_t layer,
@@ -347,16 +385,11 @@ evo_status evo_context_embed(evo_context *context, const evo_batch *batch, size_
   return protect([&]() -> int {
     if (context == nullptr || batch == nullptr || callback == nullptr)
       return fail(evob::kInvalidArgument, "context, batch and callback are required");
-    std::vector<float> hidden;
-    std::size_t rows = 0;
-    const int status = embed_rows(context, batch, layer, &hidden, &rows);
-    if (status != kOk) return status;
-    const evo_status callback_status =
-        callback(hidden.data(), rows, context->context->config().width, 0, user_data);
-    if (callback_status != EVO_STATUS_OK)
-      return fail(valid_status(callback_status) ? callback_status : EVO_STATUS_INTERNAL,
-                  "embedding consumer aborted");
-    return kOk;
+    const std::size_t width = context->context->config().width;
+    return embed_chunks(context, batch, layer, "none",
+                        [&](const float *rows, size_t count, size_t offset, size_t) {
+                          return callback(rows, count, width, offset, user_data);
+                        });
   });
 }
 
@@ -364,47 +397,44 @@ evo_status evo_context_embed_ex(evo_context *context, const evo_batch *batch,
                                 const evo_embedding_options *options,
                                 evo_embedding_ex_callback callback, void *user_data) {
   return protect([&]() -> int {
-    if (context == nullptr || batch == nullptr || callback == nullptr || options == nullptr ||
-        options->struct_size < sizeof(evo_embedding_options))
-      return fail(evob::kInvalidArgument, "context, batch, options and callback are required");
-    if (options->preset != nullptr && options->preset[0] != '\0')
-      return fail(evob::kUnsupported, "embedding presets are not defined for StripedHyena2");
-    const std::string pooling = options->pooling == nullptr ? "none" : options->pooling;
-    if (pooling != "none" && pooling != "mean" && pooling != "last")
-      return fail(evob::kUnsupported, "unsupported pooling: " + pooling);
-    std::vector<float> hidden;
-    std::size_t rows = 0;
-    const int status = embed_rows(context, batch, options->layer, &hidden, &rows);
-    if (status != kOk) return status;
-    const std::size_t width = context->context->config().width;
-    std::vector<float> pooled;
-    std::size_t out_rows = rows;
-    const float *data = hidden.data();
-    if (pooling == "mean") {
-      pooled.assign(width, 0.0F);
-      for (std::size_t r = 0; r < rows; ++r)
-        for (std::size_t c = 0; c < width; ++c) pooled[c] += hidden[r * width + c];
-      for (float &v : pooled) v /= static_cast<float>(rows);
-      data = pooled.data();
-      out_rows = 1;
-    } else if (pooling == "last") {
-      data = hidden.data() + (rows - 1) * width;
-      out_rows = 1;
+    if (context == nullptr || batch == nullptr || callback == nullptr)
+      return fail(evob::kInvalidArgument, "context, batch and callback are required");
+    evo_embedding_options chosen = evo_embedding_default_options();
+    if (options != nullptr) {
+      if (options->struct_size < sizeof(evo_embedding_options))
+        return fail(evob::kInvalidArgument, "evo_embedding_options.struct_size is too small");
+      chosen = *options;
     }
-    evo_embedding_result_info info{};
-    info.struct_size = sizeof(info);
-    info.resolved_preset = "";
-    info.hidden_tap = "block_output";
-    info.pooling = pooling.c_str();
-    info.layer = options->layer;
-    info.original_length = info.effective_length = info.token_count = rows;
-    info.rows = out_rows;
-    info.columns = width;
-    const evo_status callback_status = callback(data, out_rows, width, 0, &info, user_data);
-    if (callback_status != EVO_STATUS_OK)
-      return fail(valid_status(callback_status) ? callback_status : EVO_STATUS_INTERNAL,
-                  "embedding consumer aborted");
-    return kOk;
+    if (chosen.preset != nullptr && chosen.preset[0] != '\0')
+      return fail(evob::kUnsupported, "embedding presets are not defined for StripedHyena2");
+    if (chosen.layer == static_cast<size_t>(-1))
+      return fail(evob::kInvalidArgument, "explicit embedding requires layer");
+    const std::string pooling = chosen.pooling == nullptr || chosen.pooling[0] == '\0' ? "none" : chosen.pooling;
+    if (pooling != "none" && pooling != "mean" && pooling != "last")
+      return fail(evob::kInvalidArgument, "pooling must be none, mean, or last");
+    const std::size_t layer = chosen.layer;
+    const std::size_t width = context->context->config().width;
+    // unpooled rows are handed over once, after the last chunk (upstream collects them the same way)
+    std::vector<float> collected;
+    const auto once = [&](const float *rows, size_t count, size_t offset, size_t total) -> evo_status {
+                          evo_embedding_result_info info{};
+                          info.struct_size = sizeof(info);
+                          info.resolved_preset = "";
+                          info.hidden_tap = "explicit-layer";
+                          info.pooling = pooling.c_str();
+                          info.layer = layer;
+                          info.original_length = info.effective_length = info.token_count = total;
+                          info.rows = count;
+                          info.columns = width;
+                          return callback(rows, count, width, offset, &info, user_data);
+    };
+    return embed_chunks(context, batch, layer, pooling,
+                        [&](const float *rows, size_t count, size_t offset, size_t total) -> evo_status {
+                          if (pooling != "none") return once(rows, count, offset, total);
+                          collected.insert(collected.end(), rows, rows + count * width);
+                          if (offset + count < total) return EVO_STATUS_OK;
+                          return once(collected.data(), total, 0, total);
+                        });
   });
 }
 

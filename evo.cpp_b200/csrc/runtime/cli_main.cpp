@@ -68,7 +68,8 @@ void json_string(std::ostream &out, const std::string &text) {
   out.put('"');
   for (const unsigned char c : text) {
     if (c == '"' || c == '\\') out << '\\' << c;
-    else if (c < 0x20) out << "\\u" << std::hex << std::setw(4) << std::setfill('0') << int(c) << std::dec;
+    else if (c < 0x20 || c >= 0x7f)  // bytes above ASCII as their Latin-1 code points: the line stays valid UTF-8
+      out << "\\u" << std::hex << std::setw(4) << std::setfill('0') << int(c) << std::dec << std::setfill(' ');
     else out.put(static_cast<char>(c));
   }
   out.put('"');

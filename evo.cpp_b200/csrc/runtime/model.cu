@@ -1299,6 +1299,16 @@ int Context::prefill_embedding(const std::vector<std::uint32_t> &tokens, const s
   return forward(tokens.data(), nullptr, tokens.size(), Mode::kStateless, &logits,
                  static_cast<long>(layer), hidden);
 }
+int Context::prefill_chunk_embedding(const std::vector<std::uint32_t> &tokens, const std::size_t layer,
+                                     const bool first, std::vector<float> *hidden) {
+  if (hidden == nullptr || layer >= weights_->config.layers)
+    return fail(kInvalidArgument, "layer capture index or output is invalid");
+  if (!first && state_valid_ && cached_attention_)
+    return fail(kInvalidArgument, "chunk continuation is not available after a cached prefill");
+  std::vector<float> logits;
+  return forward(tokens.data(), nullptr, tokens.size(), first ? Mode::kPrefill : Mode::kContinue, &logits,
+                 static_cast<long>(layer), hidden);
+}
 int Context::prefill_with_dumps(const std::vector<std::uint32_t> &tokens, const DumpPlan &plan,
                                 const bool cached, std::vector<float> *logits) {
   if (logits == nullptr) return fail(kInvalidArgument, "logits output is null");

@@ -170,6 +170,11 @@ class Context {
   // Block output of `layer` ([rows, width] floats) for a fresh stateless prefill.
   int prefill_embedding(const std::vector<std::uint32_t> &tokens, std::size_t layer,
                         std::vector<float> *hidden);
+  // Chunked form (upstream prefill_embedding / prefill_chunk_embedding,
+  // include/evo/cuda/model.hpp:150-170): the first chunk starts the sequence, later ones continue it;
+  // the context advances like a prefill.
+  int prefill_chunk_embedding(const std::vector<std::uint32_t> &tokens, std::size_t layer, bool first,
+                              std::vector<float> *hidden);
   // Upstream's prefill_with_dumps / prefill_cached_with_dumps / decode_with_dumps
   // (include/evo/cuda/model.hpp:121-134, 184-190): the same passes with the
   // requested taps handed to plan.sink as they are produced.  A layer with taps

@@ -74,6 +74,8 @@ def test_concurrent_requests_equal_single_context_results(rt, pkg, fixture_path)
         row, produced = context.prefill(prompt)[-1], []
         for step in range(6):
             token = sampler.sample(row)
+            if token > 255:          # not a byte: generation ends (vocabulary 512, upstream token_to_byte)
+                break
             produced.append(token)
             if step < 5:
                 row = context.decode(token)
@@ -104,7 +106,9 @@ def test_queue_limit_cancellation_and_request_errors(rt, pkg, fixture_path):
     assert metrics["rejected"] == tickets.count(0) and metrics["cancelled"] == 2
     assert metrics["submitted"] == 1 + len(accepted) and metrics["queue_peak"] <= 2
     assert not scheduler.cancel(first)                                        # finished: nothing to cancel
+    scheduler.close()
     # request-level errors come back through the completion, the worker's context stays usable
+    scheduler = rt.Scheduler(model, workers=1, maximum_queue=8, context_size=2048)
     too_long = scheduler.score(b"A" * 3000)
     single = scheduler.score(b"A")
     bad_sampler = scheduler.generate(b"ACGT", 4, temperature=-1.0, top_k=3)
@@ -130,7 +134,7 @@ def test_serve_command_answers_jsonl_requests(pkg, fixture_path, tmp_path):
     rows = {row["id"]: row for row in map(json.loads, result.stdout.decode().splitlines())}
     assert set(rows) == {"s1", "g1", "bad", "4"}
     assert rows["bad"]["error"]["code"] == "invalid_argument"
-    assert rows["s1"]["scored_tokens"] == 9 and rows["4"]["scored_tokens"] == 7 and len(rows["g1"]["generated"]) == 5
+    assert rows["s1"]["scored_tokens"] == 9 and rows["4"]["scored_tokens"] == 7 and len(rows["g1"]["generated"]) <= 5
     raw = tmp_path / "s1.txt"
     raw.write_bytes(b"ACGTACGTAC")
     scored = json.loads(subprocess.run([str(pkg.PACKAGE_DIR / "evo"), "score", "-m", str(fixture_path),
