@@ -24,6 +24,7 @@
 // use tiles at all: gated_fir_stream_kernel keeps the whole sliding window in
 // registers and reads every input once.
 #include <algorithm>
+#include <cstdlib>
 #include <type_traits>
 
 #include "common.cuh"
@@ -788,7 +789,13 @@ int gated_fir_prefill(const GatedFirArgs &a, cudaStream_t stream) {
   int status;
   const bool tensor = !a.cross_correlation && !a.filter_is_f32 && a.taps > 32 &&
                       p.channels_per_group % 16 == 0;
-  if (tensor) {
+  static const bool tcgen05_off = [] {
+    const char *const flag = std::getenv("EVO_B200_HCM_TCGEN05");
+    return flag != nullptr && flag[0] == '0';
+  }();
+  if (tensor && !tcgen05_off && gated_fir_tcgen05_applicable(a)) {
+    status = gated_fir_tcgen05(a, stream);
+  } else if (tensor) {
     constexpr int TT = 256;
     const std::size_t smem = (TT + kMmaHalo) * kRowBytes + TT * kRowBytes + 4 * 128 * 2 +
                              (from_projection ? kRawBytes : 0);

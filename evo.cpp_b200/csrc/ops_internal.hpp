@@ -137,6 +137,10 @@ struct GatedFirArgs {
 // when the layout allows and to the generic kernel of hyena_fir.cu otherwise.
 int gated_fir_prefill(const GatedFirArgs &args, cudaStream_t stream);
 int gated_fir_prefill_generic(const GatedFirArgs &args, cudaStream_t stream);
+// hyena_fir_tcgen05.cu: the k <= 128 causal-convolution form on tcgen05 tensor cores (projection-fed,
+// BF16 filters shared by groups of exactly 16 channels); gated_fir_prefill uses it when applicable.
+bool gated_fir_tcgen05_applicable(const GatedFirArgs &args);
+int gated_fir_tcgen05(const GatedFirArgs &args, cudaStream_t stream);
 
 int fir_prefill(const void *input, const void *filter, bool filter_is_f32,
                 const void *bias, bool multiply_bias, std::size_t length,
