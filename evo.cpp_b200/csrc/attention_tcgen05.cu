@@ -100,8 +100,7 @@ flash_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
                      const __grid_constant__ CUtensorMap map_v, bf16 *const output, const int rows,
                      const int total_keys, const int heads, int *const error_word) {
   extern __shared__ unsigned char smem_raw[];
-  unsigned char *const smem = reinterpret_cast<unsigned char *>(
-      (reinterpret_cast<std::uintptr_t>(smem_raw) + 1023U) & ~static_cast<std::uintptr_t>(1023U));
+  unsigned char *const smem = smem_raw + ((1024U - (smem_u32(smem_raw) & 1023U)) & 1023U)  /* pointer arithmetic keeps the shared address space */;
   const std::uint32_t smem_base = smem_u32(smem);
   auto bar = [&](const int index) { return smem_base + kBarrierOffset + 8U * index; };
   volatile std::uint32_t *const tmem_ptr = reinterpret_cast<volatile std::uint32_t *>(smem + kTmemPtrOffset);

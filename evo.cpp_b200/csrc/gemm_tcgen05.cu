@@ -126,9 +126,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
                     const int K_bytes, int *const error_word) {
   using L = SharedLayout<BN>;
   extern __shared__ unsigned char smem_raw[];
-  unsigned char *const smem = reinterpret_cast<unsigned char *>(
-      (reinterpret_cast<std::uintptr_t>(smem_raw) + 1023U) &
-      ~static_cast<std::uintptr_t>(1023U));
+  unsigned char *const smem = smem_raw + ((1024U - (smem_u32(smem_raw) & 1023U)) & 1023U)  /* pointer arithmetic keeps the shared address space */;
   const std::uint32_t smem_base = smem_u32(smem);
   const std::uint32_t bar_base = smem_base + L::kBarrierOffset;
   auto full_bar = [&](const int s) { return bar_base + 8U * s; };
@@ -408,8 +406,7 @@ gemm_swap_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
                  const int tiles_n, const int k_per_split, int *const error_word) {
   using L = SwapLayout<BT>;
   extern __shared__ unsigned char smem_raw[];
-  unsigned char *const smem = reinterpret_cast<unsigned char *>(
-      (reinterpret_cast<std::uintptr_t>(smem_raw) + 1023U) & ~static_cast<std::uintptr_t>(1023U));
+  unsigned char *const smem = smem_raw + ((1024U - (smem_u32(smem_raw) & 1023U)) & 1023U)  /* pointer arithmetic keeps the shared address space */;
   const std::uint32_t smem_base = smem_u32(smem);
   const std::uint32_t bar_base = smem_base + L::kBarrierOffset;
   auto full_bar = [&](const int s) { return bar_base + 8U * s; };

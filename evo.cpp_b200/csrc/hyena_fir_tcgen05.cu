@@ -9,17 +9,20 @@
 // convolution is a GEMM  Y[128 x 16] = H[128 x 256] . U[256 x 16]  with the
 // banded Toeplitz matrix H[m][k] = h[m + 128 - k] over the 256 rows of u that
 // end with the tile.  One CTA owns a group and walks a range of row tiles:
-//   warps 0-7  a thread owns (row of the tile, half of the 16 channels): it builds u
-//              for the next tile (featurizer from a cp.async-staged copy of the
-//              tile's 96-byte projection rows, staged two tiles ahead; rounding
-//              points of the unfused chain), writes it as the K-major swizzled
-//              B operand [16 channels x time] into a ring of 64-row K blocks,
-//              and later turns the tile's accumulator into outputs: tcgen05.ld
-//              (its row is a TMEM lane), direct term, round, gate, one 16-byte
-//              store.  u and the gate wait for the sums in registers.
+//   warps 0-7  stage the group's 96-byte projection rows two tiles ahead (cp.async
+//              reporting to an mbarrier) and build u: a thread owns a channel pair and four
+//              consecutive rows, keeps its 18 featurizer taps in registers as F32
+//              and unpacks a raw value once for the three rows that use it
+//              (rounding points of the unfused chain); u goes out as the K-major
+//              swizzled B operand [16 channels x time] into a ring of 64-row K
+//              blocks, the x2 gate beside it.  Two iterations later the same
+//              warps turn the tile's accumulator into outputs: tcgen05.ld (a
+//              row is a TMEM lane), direct term, round, gate, one 16-byte store.
 //   warp 8     one lane issues tcgen05.mma M128 N16 K16, sixteen per tile, into
 //              one of two 16-column TMEM accumulators; a tile's MMAs run under
 //              the featurizer of the tile after it.
+// Every hand-over is an mbarrier; there is no CTA-wide barrier in the loop, so
+// the warps of a CTA drift apart and fill each other's latencies.
 // H depends on the group only and is Toeplitz, so its four 64-column K blocks
 // are row windows, 64 rows apart, of one strip T[r][j] = h[r - j] of 320 rows
 // (40 KiB instead of 64): the A descriptors just start at different rows.
@@ -57,10 +60,10 @@ constexpr int kRawBuffers = 3;
 constexpr int kStripOffset = 0;
 constexpr int kRingOffset = kStripOffset + kStripBytes;
 constexpr int kRawOffset = kRingOffset + kRingBlocks * kBlockBytes;
-constexpr int kGateOffset = kRawOffset + kRawBuffers * kRawBytes;     // [channel][time] gate, two steps x two K blocks
-constexpr int kFilterOffset = kGateOffset + 4 * kBlockBytes;          // 128 + 8 BF16 taps
+constexpr int kGateOffset = kRawOffset + kRawBuffers * kRawBytes;     // [channel][time] gate, three steps x two K blocks
+constexpr int kFilterOffset = kGateOffset + 6 * kBlockBytes;          // 128 + 8 BF16 taps
 constexpr int kBarrierOffset = kFilterOffset + 1024;
-constexpr int kBarriers = 6;  // b_full[2], acc_full[2], acc_empty[2]
+constexpr int kBarriers = 14;  // b_full[2], acc_full[2], acc_empty[2], raw_full[3], raw_empty[3], step_done[2]
 constexpr int kTmemPtrOffset = kBarrierOffset + kBarriers * 8;
 constexpr int kAbortOffset = kTmemPtrOffset + 8;
 constexpr int kSmemBytes = kAbortOffset + 8 + 1024;  // + alignment slack
@@ -90,8 +93,6 @@ __device__ __forceinline__ void tmem_load_8(const std::uint32_t taddr, std::uint
                : "memory");
 }
 
-__device__ __forceinline__ void workers_sync() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
-
 __global__ void __launch_bounds__(kThreadsTotal, 2)
 gated_fir_tcgen05_kernel(const TcParams p, int *const error_word) {
   extern __shared__ unsigned char smem_raw[];
@@ -100,7 +101,7 @@ gated_fir_tcgen05_kernel(const TcParams p, int *const error_word) {
   unsigned char *const smem = smem_raw + ((1024U - (smem_u32(smem_raw) & 1023U)) & 1023U);
   const std::uint32_t smem_base = smem_u32(smem);
   auto bar = [&](const int index) { return smem_base + kBarrierOffset + 8U * index; };
-  enum { kBFull = 0, kAccFull = 2, kAccEmpty = 4 };
+  enum { kBFull = 0, kAccFull = 2, kAccEmpty = 4, kRawFull = 6, kRawEmpty = 9, kStepDone = 12 };
   volatile std::uint32_t *const tmem_ptr = reinterpret_cast<volatile std::uint32_t *>(smem + kTmemPtrOffset);
   volatile int *const abort_flag = reinterpret_cast<volatile int *>(smem + kAbortOffset);
   const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
@@ -119,6 +120,12 @@ gated_fir_tcgen05_kernel(const TcParams p, int *const error_word) {
     mbar_init(bar(kAccFull + 1), 1);
     mbar_init(bar(kAccEmpty), kWorkers);
     mbar_init(bar(kAccEmpty + 1), kWorkers);
+    for (int b = 0; b < kRawBuffers; ++b) {
+      mbar_init(bar(kRawFull + b), kWorkers);
+      mbar_init(bar(kRawEmpty + b), kWorkers);
+    }
+    mbar_init(bar(kStepDone), kWorkers);
+    mbar_init(bar(kStepDone + 1), kWorkers);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -193,36 +200,9 @@ gated_fir_tcgen05_kernel(const TcParams p, int *const error_word) {
     // featurizer taps sit in registers as F32, and a raw value that three neighbouring rows use is
     // unpacked once.  Epilogue: thread = (row of the tile, half of the channels), its row being
     // a TMEM lane; u and the gate come back from shared memory, both kept [channel][time].
+    // Warps run free: every hand-over is an mbarrier, none a CTA-wide barrier.
     const int cp = threadIdx.x % 8, quad = threadIdx.x / 8;
     const int row = threadIdx.x % kTile, half = threadIdx.x / kTile;
-    const std::size_t row_elements = static_cast<std::size_t>(p.width) * 3;
-    const bf16 *const group_columns = p.projection + static_cast<std::size_t>(c0) * 3;
-    // raw rows [t0 - 2, t0 + 128) of the group's columns -> buffer; rows outside [0, length) are zeros.
-    // 780 copies of 16 bytes: a thread's (row, chunk) assignments do not change from step to step
-    int stage_row[4], stage_smem[4], stage_global[4];
-#pragma unroll
-    for (int n = 0; n < 4; ++n) {
-      const int item = threadIdx.x + n * kWorkers;
-      stage_row[n] = item / 6 - 2;  // relative to t0
-      stage_smem[n] = (item / 6) * kRawStride + (item % 6) * 16;
-      stage_global[n] = (item / 6 - 2) * p.width * 6 + (item % 6) * 16;  // bytes from row t0 of the group's columns
-    }
-    const auto stage_raw = [&](const int t0, const int buffer) {
-      const std::uint32_t base = smem_base + kRawOffset + buffer * kRawBytes;
-      const unsigned char *const origin =
-          reinterpret_cast<const unsigned char *>(group_columns) + static_cast<std::size_t>(t0) * row_elements * 2;
-#pragma unroll
-      for (int n = 0; n < 4; ++n) {
-        if (n == 3 && threadIdx.x + 3 * kWorkers >= kRawRows * 6) break;
-        const int t = t0 + stage_row[n];
-        const bool valid = t >= 0 && t < p.length;
-        asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(base + stage_smem[n]),
-                     "l"(valid ? origin + stage_global[n] : reinterpret_cast<const unsigned char *>(p.projection)),
-                     "r"(valid ? 16U : 0U)
-                     : "memory");
-      }
-    };
-    const auto commit = [] { asm volatile("cp.async.commit_group;" ::: "memory"); };
     // taps[column][k]: columns (x2, x1, v) of channel 2cp, then of channel 2cp + 1; k oldest first
     float taps[6][3];
     {
@@ -238,23 +218,50 @@ gated_fir_tcgen05_kernel(const TcParams p, int *const error_word) {
     float direct[8];
 #pragma unroll
     for (int c = 0; c < 8; ++c) direct[c] = p.direct != nullptr ? bf2f(p.direct[c0 + half * 8 + c]) : 0.0F;
+    // Raw rows [t0 - 2, t0 + 128) of the group's columns, 780 copies of 16 bytes (zero-filled
+    // outside [0, length)): a thread's (row, chunk) assignments do not change from step to step,
+    // and its copies report to the buffer's mbarrier when they land.
+    const unsigned char *const group_columns =
+        reinterpret_cast<const unsigned char *>(p.projection + static_cast<std::size_t>(c0) * 3);
+    const std::size_t row_bytes = static_cast<std::size_t>(p.width) * 6;
+    int stage_row[4], stage_smem[4], stage_global[4];
+#pragma unroll
+    for (int n = 0; n < 4; ++n) {
+      const int item = threadIdx.x + n * kWorkers;
+      stage_row[n] = item / 6 - 2;  // relative to t0
+      stage_smem[n] = (item / 6) * kRawStride + (item % 6) * 16;
+      stage_global[n] = (item / 6 - 2) * p.width * 6 + (item % 6) * 16;  // bytes from row t0
+    }
+    const auto stage_raw = [&](const int step) {
+      const int t0 = t_first + (step - 1) * kTile;
+      const int buffer = step % kRawBuffers;
+      const std::uint32_t base = smem_base + kRawOffset + buffer * kRawBytes;
+      const unsigned char *const origin = group_columns + static_cast<std::ptrdiff_t>(t0) * static_cast<std::ptrdiff_t>(row_bytes);
+#pragma unroll
+      for (int n = 0; n < 4; ++n) {
+        if (n == 3 && threadIdx.x + 3 * kWorkers >= kRawRows * 6) break;
+        const int t = t0 + stage_row[n];
+        const bool valid = t >= 0 && t < p.length;
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(base + stage_smem[n]),
+                     "l"(valid ? origin + stage_global[n] : reinterpret_cast<const unsigned char *>(p.projection)),
+                     "r"(valid ? 16U : 0U)
+                     : "memory");
+      }
+      asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar(kRawFull + buffer)) : "memory");
+    };
+    if (tiles > 0) {
+      stage_raw(0);
+      stage_raw(1);
+    }
 
     // production step s covers rows [t_first + (s - 1) * 128, + 128): step 0 is the history in
     // front of the range, step s >= 1 the rows of tile s - 1.  Tile i is multiplied once step
-    // i + 1 is published and turned into outputs after step i + 2, so the tensor core works
-    // under the next step's featurizer.  Raw rows are staged two steps ahead.
+    // i + 1 is published and turned into outputs in iteration i + 2, so the tensor core works
+    // under the next step's featurizer.  Iteration s = production of step s, then outputs of tile s - 2.
     const int steps = tiles + 1;
-    if (tiles > 0) {
-      stage_raw(t_first - kTile, 0);
-      commit();
-      stage_raw(t_first, 1);
-      commit();
-    }
-    bool ok = true;
     for (int s = 0; tiles > 0 && s <= steps; ++s) {
       if (s < steps) {
-        asm volatile("cp.async.wait_group 1;" ::: "memory");
-        workers_sync();  // raw rows of step s are visible; step s - 1 is finished everywhere
+        if (!mbar_wait(bar(kRawFull + s % kRawBuffers), (s / kRawBuffers) & 1U, abort_flag)) break;
         // raw rows 4 quad .. 4 quad + 5 (times t - 2 .. t + 3 of the thread's first row), 12 bytes each
         const unsigned char *const raw =
             smem + kRawOffset + (s % kRawBuffers) * kRawBytes + (4 * quad) * kRawStride + cp * 12;
@@ -286,6 +293,7 @@ gated_fir_tcgen05_kernel(const TcParams p, int *const error_word) {
           u[m] = round_pair_bf16(__uint_as_float(x1 << 16U) * __uint_as_float(v << 16U),
                                  __uint_as_float(x1 & 0xffff0000U) * __uint_as_float(v & 0xffff0000U));
         }
+        mbar_arrive(bar(kRawEmpty + s % kRawBuffers));  // the raw rows are in registers
         // decode history: the last taps - 1 values of u per channel, chronological (rows in front
         // of the range count too: a short window ends inside them)
         const int t_quad = t_first + (s - 1) * kTile + 4 * quad;
@@ -300,11 +308,14 @@ gated_fir_tcgen05_kernel(const TcParams p, int *const error_word) {
                 __uint_as_float(u[m] & 0xffff0000U);
           }
         }
+        // The images of step s replace those of step s - 3, which iteration s - 2 read and tiles
+        // s - 4, s - 3 multiplied (this thread saw tile s - 3 finish in its iteration s - 1).
+        if (s >= 2 && !mbar_wait(bar(kStepDone + (s & 1)), ((s - 2) >> 1) & 1U, abort_flag)) break;
         // [channel][time] images: u as the B operand (K block 2s + quad / 16 of the ring), the gate
         // beside it; four consecutive time steps of a channel are eight contiguous bytes
         const int k = (4 * quad) % 64;
         unsigned char *const block = smem + kRingOffset + ((2 * s + quad / 16) % kRingBlocks) * kBlockBytes;
-        unsigned char *const gate_block = smem + kGateOffset + ((s & 1) * 2 + quad / 16) * kBlockBytes;
+        unsigned char *const gate_block = smem + kGateOffset + ((s % 3) * 2 + quad / 16) * kBlockBytes;
 #pragma unroll
         for (int e = 0; e < 2; ++e) {
           const int channel = 2 * cp + e;
@@ -317,51 +328,54 @@ gated_fir_tcgen05_kernel(const TcParams p, int *const error_word) {
         }
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         mbar_arrive(bar(kBFull + (s & 1)));
-        // staged after the arrive: its release must not wait for copies issued in the same step
-        if (s + 2 < steps) stage_raw(t_first + (s + 1) * kTile, (s + 2) % kRawBuffers);
-        commit();
-      } else {
-        workers_sync();  // no production step follows the last one to order its images
+        // stage step s + 2 into the buffer of step s - 1, once every worker has left that one
+        if (s + 2 < steps) {
+          if (s >= 1 && !mbar_wait(bar(kRawEmpty + (s - 1) % kRawBuffers), ((s - 1) / kRawBuffers) & 1U, abort_flag))
+            break;
+          stage_raw(s + 2);
+        }
       }
       // ---- outputs of tile i = s - 2: its rows are those of step s - 1
       const int i = s - 2;
-      if (i < 0) continue;
-      const int acc = i & 1;
-      if (ok) ok = mbar_wait(bar(kAccFull + acc), (i >> 1) & 1U, abort_flag);
-      if (!ok) continue;
-      tc_fence_after();
-      std::uint32_t sums[8];
-      tmem_load_8(tmem_base + acc * kGroup + half * 8 + (static_cast<std::uint32_t>((warp & 3) * 32) << 16U), sums);
-      tmem_load_wait();
-      tc_fence_before();
-      mbar_arrive(bar(kAccEmpty + acc));
-      const int t = t_first + i * kTile + row;
-      if (t >= p.length) continue;
-      const int k = row % 64;
-      const unsigned char *const u_block =
-          smem + kRingOffset + ((2 * (s - 1) + row / 64) % kRingBlocks) * kBlockBytes;
-      const unsigned char *const g_block = smem + kGateOffset + (((s - 1) & 1) * 2 + row / 64) * kBlockBytes;
-      float y[8];
-      std::uint32_t u_bits[8];
+      if (i >= 0) {
+        const int acc = i & 1;
+        if (!mbar_wait(bar(kAccFull + acc), (i >> 1) & 1U, abort_flag)) break;
+        // every worker's images of step s - 1 (the accumulator only proves the tensor core saw them)
+        if (!mbar_wait(bar(kBFull + ((s - 1) & 1)), ((s - 1) >> 1) & 1U, abort_flag)) break;
+        tc_fence_after();
+        std::uint32_t sums[8];
+        tmem_load_8(tmem_base + acc * kGroup + half * 8 + (static_cast<std::uint32_t>((warp & 3) * 32) << 16U), sums);
+        tmem_load_wait();
+        tc_fence_before();
+        mbar_arrive(bar(kAccEmpty + acc));
+        const int t = t_first + i * kTile + row;
+        if (t < p.length) {
+          const int k = row % 64;
+          const unsigned char *const u_block =
+              smem + kRingOffset + ((2 * (s - 1) + row / 64) % kRingBlocks) * kBlockBytes;
+          const unsigned char *const g_block = smem + kGateOffset + (((s - 1) % 3) * 2 + row / 64) * kBlockBytes;
+          float y[8];
+          std::uint32_t u_bits[8];
 #pragma unroll
-      for (int c = 0; c < 8; ++c) {
-        const int channel = half * 8 + c;
-        const int offset = channel * 128 + (((k >> 3) ^ (channel & 7)) << 4) + (k & 7) * 2;
-        u_bits[c] = *reinterpret_cast<const unsigned short *>(u_block + offset);
-        const float gate =
-            __uint_as_float(static_cast<std::uint32_t>(*reinterpret_cast<const unsigned short *>(g_block + offset))
-                            << 16U);
-        y[c] = rbf(fmaf(direct[c], __uint_as_float(u_bits[c] << 16U), __uint_as_float(sums[c]))) * gate;
+          for (int c = 0; c < 8; ++c) {
+            const int channel = half * 8 + c;
+            const int offset = channel * 128 + (((k >> 3) ^ (channel & 7)) << 4) + (k & 7) * 2;
+            u_bits[c] = *reinterpret_cast<const unsigned short *>(u_block + offset);
+            const float gate = __uint_as_float(
+                static_cast<std::uint32_t>(*reinterpret_cast<const unsigned short *>(g_block + offset)) << 16U);
+            y[c] = rbf(fmaf(direct[c], __uint_as_float(u_bits[c] << 16U), __uint_as_float(sums[c]))) * gate;
+          }
+          *reinterpret_cast<uint4 *>(p.output + static_cast<std::size_t>(t) * p.width + c0 + half * 8) = make_uint4(
+              round_pair_bf16(y[0], y[1]), round_pair_bf16(y[2], y[3]), round_pair_bf16(y[4], y[5]),
+              round_pair_bf16(y[6], y[7]));
+          if (p.pregate != nullptr)
+            *reinterpret_cast<uint4 *>(p.pregate + static_cast<std::size_t>(t) * p.width + c0 + half * 8) =
+                make_uint4(u_bits[0] | (u_bits[1] << 16U), u_bits[2] | (u_bits[3] << 16U),
+                           u_bits[4] | (u_bits[5] << 16U), u_bits[6] | (u_bits[7] << 16U));
+        }
       }
-      *reinterpret_cast<uint4 *>(p.output + static_cast<std::size_t>(t) * p.width + c0 + half * 8) = make_uint4(
-          round_pair_bf16(y[0], y[1]), round_pair_bf16(y[2], y[3]), round_pair_bf16(y[4], y[5]),
-          round_pair_bf16(y[6], y[7]));
-      if (p.pregate != nullptr)
-        *reinterpret_cast<uint4 *>(p.pregate + static_cast<std::size_t>(t) * p.width + c0 + half * 8) =
-            make_uint4(u_bits[0] | (u_bits[1] << 16U), u_bits[2] | (u_bits[3] << 16U), u_bits[4] | (u_bits[5] << 16U),
-                       u_bits[6] | (u_bits[7] << 16U));
+      mbar_arrive(bar(kStepDone + (s & 1)));  // this thread is done with iteration s
     }
-    asm volatile("cp.async.wait_group 0;" ::: "memory");
   }
 
   __syncwarp();
