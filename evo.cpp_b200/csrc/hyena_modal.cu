@@ -18,6 +18,7 @@
 // (src/cuda/hyena.cu:534-560).  modal_decode keeps the pinned decode order
 // (separate multiply/add, 32-lane zero-padded tree; src/cuda/hyena.cu:718-761).
 #include <algorithm>
+#include <cstdlib>
 #include <mutex>
 #include <string>
 #include <type_traits>
@@ -149,10 +150,12 @@ __device__ __forceinline__ std::uint32_t add_pairs(const std::uint32_t a, const 
 __device__ __forceinline__ float pair_lo(const std::uint32_t w) { return __uint_as_float(w << 16U); }
 __device__ __forceinline__ float pair_hi(const std::uint32_t w) { return __uint_as_float(w & 0xffff0000U); }
 
-template <int kModes, bool kProj, bool kOutput, int kUnroll>
-__global__ void __launch_bounds__(kStreamThreads, kOutput ? 2 : 3)
+// kC = 2: a channel pair per thread, one 32-bit word per stream and row.  kC = 1: one channel per
+// thread with the same packed arithmetic on the low half of every word (the high half carries
+// zeros), so a channel's bits do not depend on the form; half the registers, twice the warps.
+template <int kModes, bool kProj, bool kOutput, int kUnroll, int kC>
+__global__ void __launch_bounds__(kStreamThreads, kC == 1 ? (kOutput ? 4 : 5) : (kOutput ? 2 : 3))
 modal_stream_kernel(const ModalParams p) {
-  constexpr int kC = 2;             // a channel pair per thread: one 32-bit word per stream and row
   constexpr int kColumns = 3 * kC;  // projection-fed: (x2, x1, v) per channel; else x1 | v | x2
   const int c0 = (blockIdx.x * kStreamThreads + threadIdx.x) * kC;
   if (c0 >= p.width) return;
@@ -221,15 +224,44 @@ modal_stream_kernel(const ModalParams p) {
       if constexpr (kOutput) residue[c][m] = p.residues[mine + c * kModes + m];
     }
   [[maybe_unused]] std::uint32_t direct_pair = 0U;
-  [[maybe_unused]] float direct[kC] = {0.0F, 0.0F};
+  [[maybe_unused]] float direct[kC] = {};
   if constexpr (kOutput) {
-    direct_pair = *reinterpret_cast<const std::uint32_t *>(p.direct + c0);
+    if constexpr (kC == 2) direct_pair = *reinterpret_cast<const std::uint32_t *>(p.direct + c0);
+    else direct_pair = *reinterpret_cast<const unsigned short *>(p.direct + c0);
     direct[0] = pair_lo(direct_pair);
-    direct[1] = pair_hi(direct_pair);
+    if constexpr (kC == 2) direct[1] = pair_hi(direct_pair);
   }
 
   struct Row {
-    std::uint32_t w[3];  // projection-fed: (x2a x1a) (va x2b) (x1b vb); else x1 | v | x2 pairs
+    // kC = 2, projection-fed: (x2a x1a) (va x2b) (x1b vb); separate inputs: x1 | v | x2 pairs.
+    // kC = 1, projection-fed: the two words that hold the channel's three columns - an even channel
+    // owns (x2 x1) (v .), an odd one (. x2) (x1 v); separate inputs: x1 | v | x2 in the low halves.
+    std::uint32_t w[3];
+  };
+  [[maybe_unused]] const int odd = c0 & 1;  // kC = 1: which half of the channel pair's six columns
+  const auto load_words = [&](Row &row, const int t, auto loader) {
+    if constexpr (kProj) {
+      const bf16 *const source = p.projection + static_cast<std::size_t>(t) * 3 * p.width +
+                                 static_cast<std::size_t>(kC == 2 ? c0 : c0 - odd) * 3;
+      if constexpr (kC == 2) {
+#pragma unroll
+        for (int i = 0; i < 3; ++i) row.w[i] = loader(reinterpret_cast<const unsigned int *>(source) + i);
+      } else {
+        row.w[0] = loader(reinterpret_cast<const unsigned int *>(source) + odd);
+        row.w[1] = loader(reinterpret_cast<const unsigned int *>(source) + odd + 1);
+      }
+    } else {
+      const std::size_t index = static_cast<std::size_t>(t) * p.width + c0;
+      if constexpr (kC == 2) {
+        row.w[0] = loader(reinterpret_cast<const unsigned int *>(p.x1 + index));
+        row.w[1] = loader(reinterpret_cast<const unsigned int *>(p.value + index));
+        if constexpr (kOutput) row.w[2] = loader(reinterpret_cast<const unsigned int *>(p.x2 + index));
+      } else {
+        row.w[0] = loader(reinterpret_cast<const unsigned short *>(p.x1 + index));
+        row.w[1] = loader(reinterpret_cast<const unsigned short *>(p.value + index));
+        if constexpr (kOutput) row.w[2] = loader(reinterpret_cast<const unsigned short *>(p.x2 + index));
+      }
+    }
   };
   const auto load_row = [&](auto checked, const int t) {
     constexpr bool kChecked = decltype(checked)::value;
@@ -238,25 +270,23 @@ modal_stream_kernel(const ModalParams p) {
     if constexpr (kChecked) {
       if (t < 0 || t >= t_end) return row;
     }
-    if constexpr (kProj) {
-      const bf16 *const source =
-          p.projection + static_cast<std::size_t>(t) * 3 * p.width + static_cast<std::size_t>(c0) * 3;
-#pragma unroll
-      for (int i = 0; i < 3; ++i) row.w[i] = __ldcs(reinterpret_cast<const unsigned int *>(source) + i);
-    } else {
-      const std::size_t index = static_cast<std::size_t>(t) * p.width + c0;
-      row.w[0] = __ldcs(reinterpret_cast<const unsigned int *>(p.x1 + index));
-      row.w[1] = __ldcs(reinterpret_cast<const unsigned int *>(p.value + index));
-      if constexpr (kOutput) row.w[2] = __ldcs(reinterpret_cast<const unsigned int *>(p.x2 + index));
-    }
+    load_words(row, t, [](const auto *address) { return static_cast<std::uint32_t>(__ldcs(address)); });
     return row;
   };
   // projection-fed rows as one F32 value per column
-  const auto columns_of = [](const Row &row, float (&x)[kColumns]) {
+  const auto columns_of = [&](const Row &row, float (&x)[kColumns]) {
+    if constexpr (kC == 2) {
 #pragma unroll
-    for (int w = 0; w < 3; ++w) {
-      x[2 * w] = pair_lo(row.w[w]);
-      x[2 * w + 1] = pair_hi(row.w[w]);
+      for (int w = 0; w < 3; ++w) {
+        x[2 * w] = pair_lo(row.w[w]);
+        x[2 * w + 1] = pair_hi(row.w[w]);
+      }
+    } else {
+      // even: lo(w0) hi(w0) lo(w1); odd: hi(w0) lo(w1) hi(w1)
+      const std::uint32_t end_selector = odd ? 0x3244U : 0x1044U;  // byte_perm(w, 0, .): hi(w) or lo(w) as F32 bits
+      x[0] = __uint_as_float(__byte_perm(row.w[0], 0U, end_selector));
+      x[1] = __uint_as_float(__byte_perm(row.w[0], row.w[1], odd ? 0x5444U : 0x3244U) & 0xffff0000U);
+      x[2] = __uint_as_float(__byte_perm(row.w[1], 0U, end_selector));
     }
   };
   constexpr std::true_type kCheckedRows{};
@@ -274,12 +304,7 @@ modal_stream_kernel(const ModalParams p) {
       const int t = t_own - 2 + k;
       Row row;
       row.w[0] = row.w[1] = row.w[2] = 0U;
-      if (t >= 0) {
-        const bf16 *const source =
-            p.projection + static_cast<std::size_t>(t) * 3 * p.width + static_cast<std::size_t>(c0) * 3;
-#pragma unroll
-        for (int i = 0; i < 3; ++i) row.w[i] = __ldg(reinterpret_cast<const unsigned int *>(source) + i);
-      }
+      if (t >= 0) load_words(row, t, [](const auto *address) { return static_cast<std::uint32_t>(__ldg(address)); });
       columns_of(row, xh[k]);
     }
   }
@@ -312,13 +337,20 @@ modal_stream_kernel(const ModalParams p) {
           xh[0][column] = xh[1][column];
           xh[1][column] = x[column];
         }
-        if constexpr (kOutput) gate_pair = round_pair_bf16(z[0], z[3]);
-        u_pair = mul_pairs(round_pair_bf16(z[1], z[4]), round_pair_bf16(z[2], z[5]));
+        if constexpr (kC == 2) {
+          if constexpr (kOutput) gate_pair = round_pair_bf16(z[0], z[3]);
+          u_pair = mul_pairs(round_pair_bf16(z[1], z[4]), round_pair_bf16(z[2], z[5]));
+        } else {
+          if constexpr (kOutput) gate_pair = round_pair_bf16(z[0], 0.0F);
+          u_pair = mul_pairs(round_pair_bf16(z[1], 0.0F), round_pair_bf16(z[2], 0.0F));
+        }
       } else {
         u_pair = mul_pairs(rows[i].w[0], rows[i].w[1]);
         gate_pair = rows[i].w[2];
       }
-      const float u[kC] = {pair_lo(u_pair), pair_hi(u_pair)};
+      float u[kC];
+      u[0] = pair_lo(u_pair);
+      if constexpr (kC == 2) u[1] = pair_hi(u_pair);
       if constexpr (!kOutput) {
 #pragma unroll
         for (int m = 0; m < kModes; ++m)
@@ -338,17 +370,24 @@ modal_stream_kernel(const ModalParams p) {
         }
         const std::size_t offset = static_cast<std::size_t>(t) * p.width + c0;
         std::uint32_t result;
+        const float modal_high = kC == 2 ? modal[kC - 1] : 0.0F;
         if (p.continue_from_state) {
           result = pack_bf16x2(pair_lo(gate_pair) * fmaf(direct[0], u[0], modal[0]),
-                               pair_hi(gate_pair) * fmaf(direct[1], u[1], modal[1]));
+                               kC == 2 ? pair_hi(gate_pair) * fmaf(direct[kC - 1], u[kC - 1], modal_high) : 0.0F);
         } else {
           // bf16(bf16(bf16(modal) + bf16(D u)) x2), each step one rounding of an exact result
           const std::uint32_t mixed =
-              add_pairs(round_pair_bf16(modal[0], modal[1]), mul_pairs(direct_pair, u_pair));
+              add_pairs(round_pair_bf16(modal[0], modal_high), mul_pairs(direct_pair, u_pair));
           result = mul_pairs(mixed, gate_pair);
         }
-        *reinterpret_cast<std::uint32_t *>(p.output + offset) = result;
-        if (p.pregate != nullptr) *reinterpret_cast<std::uint32_t *>(p.pregate + offset) = u_pair;
+        if constexpr (kC == 2) {
+          *reinterpret_cast<std::uint32_t *>(p.output + offset) = result;
+          if (p.pregate != nullptr) *reinterpret_cast<std::uint32_t *>(p.pregate + offset) = u_pair;
+        } else {
+          *reinterpret_cast<unsigned short *>(p.output + offset) = static_cast<unsigned short>(result);
+          if (p.pregate != nullptr)
+            *reinterpret_cast<unsigned short *>(p.pregate + offset) = static_cast<unsigned short>(u_pair);
+        }
         if constexpr (kChecked && kProj) {
           // raw rows length-2 and length-1 are the featurizer's decode history
           if (p.short_cache != nullptr && t == p.length - 1) {
@@ -391,17 +430,17 @@ modal_stream_kernel(const ModalParams p) {
 // memory (12 KB in flight per SM), twelve cost the projection-fed form registers.
 constexpr int kStreamUnroll = 8;
 
-template <int kModes, bool kProj>
+template <int kModes, bool kProj, int kC>
 int stream_segments(const int rows, const int width, const std::size_t scratch_floats) {
   static const int resident = [] {
     int blocks = 0;
     if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(
-            &blocks, modal_stream_kernel<kModes, kProj, true, kStreamUnroll>, kStreamThreads, 0) != cudaSuccess ||
+            &blocks, modal_stream_kernel<kModes, kProj, true, kStreamUnroll, kC>, kStreamThreads, 0) != cudaSuccess ||
         blocks < 1)
       blocks = 1;
     return blocks;
   }();
-  const int across = static_cast<int>(ceil_div_u(width / 2, kStreamThreads));
+  const int across = static_cast<int>(ceil_div_u(width / kC, kStreamThreads));
   int segments = std::max(1, kSmCount * resident / across);
   segments = std::min(segments, std::max(1, rows / 64));
   const std::size_t per_segment = static_cast<std::size_t>(width) * kModes;
@@ -410,22 +449,36 @@ int stream_segments(const int rows, const int width, const std::size_t scratch_f
   return static_cast<int>(std::min<std::size_t>(segments, capacity - 1));
 }
 
-template <int kModes, bool kProj>
-int launch_stream(ModalParams p, cudaStream_t stream) {
+template <int kModes, bool kProj, int kC>
+int launch_stream_form(ModalParams p, cudaStream_t stream) {
   const int rows = p.length - p.row_begin;
-  const int segments = stream_segments<kModes, kProj>(rows, p.width, p.scratch_floats);
+  const int segments = stream_segments<kModes, kProj, kC>(rows, p.width, p.scratch_floats);
   p.segment = (rows + segments - 1) / segments;
   p.segments = (rows + p.segment - 1) / p.segment;
-  const unsigned int across = ceil_div_u(p.width / 2, kStreamThreads);
+  const unsigned int across = ceil_div_u(p.width / kC, kStreamThreads);
   if (p.segments > 1) {
-    modal_stream_kernel<kModes, kProj, false, kStreamUnroll>
+    modal_stream_kernel<kModes, kProj, false, kStreamUnroll, kC>
         <<<dim3(across, p.segments - 1), kStreamThreads, 0, stream>>>(p);
     const int status = check_launch("modal segment-state kernel");
     if (status != kOk) return status;
   }
-  modal_stream_kernel<kModes, kProj, true, kStreamUnroll>
+  modal_stream_kernel<kModes, kProj, true, kStreamUnroll, kC>
       <<<dim3(across, p.segments), kStreamThreads, 0, stream>>>(p);
   return check_launch("modal output kernel");
+}
+
+// One channel per thread where the registers of a pair cap the occupancy (16 modes: 96 of them
+// hold poles, residues and states); pairs where they do not.
+template <int kModes, bool kProj>
+int launch_stream(const ModalParams &p, cudaStream_t stream) {
+  static const bool pairs_only = [] {
+    const char *const flag = std::getenv("EVO_B200_MODAL_PAIRS");
+    return flag != nullptr && flag[0] == '1';
+  }();
+  if constexpr (kModes >= 8) {
+    if (!pairs_only) return launch_stream_form<kModes, kProj, 1>(p, stream);
+  }
+  return launch_stream_form<kModes, kProj, 2>(p, stream);
 }
 
 template <int kModes>
