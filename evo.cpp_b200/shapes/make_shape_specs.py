@@ -10,10 +10,13 @@ Needs the upstream tree (its path is the first argument); the JSON files it writ
 committed and are all that is needed afterwards.
 """
 import json
+import os
 import sys
 from pathlib import Path
 
-REF = Path(sys.argv[1]) if len(sys.argv) > 1 else Path("/root/reference")
+if len(sys.argv) < 2 and "EVO_UPSTREAM_ROOT" not in os.environ:
+    sys.exit("usage: pass the upstream source tree as the first argument (or set EVO_UPSTREAM_ROOT)")
+REF = Path(sys.argv[1] if len(sys.argv) > 1 else os.environ["EVO_UPSTREAM_ROOT"])
 sys.path.insert(0, str(REF / "tools"))
 from evo import format as fmt  # noqa: E402
 from evo import model_config as mc  # noqa: E402

@@ -24,6 +24,7 @@ from __future__ import annotations
 import ctypes
 import importlib.util
 import subprocess
+import os
 import sys
 from pathlib import Path
 
@@ -32,7 +33,9 @@ import torch
 
 HERE = Path(__file__).resolve().parent
 ROOT = HERE.parent.parent
-REF = Path(sys.argv[1]) if len(sys.argv) > 1 else Path("/root/reference")
+if len(sys.argv) < 2 and "EVO_UPSTREAM_ROOT" not in os.environ:
+    sys.exit("usage: pass the upstream source tree as the first argument (or set EVO_UPSTREAM_ROOT)")
+REF = Path(sys.argv[1] if len(sys.argv) > 1 else os.environ["EVO_UPSTREAM_ROOT"])
 
 
 def bf16_bits_to_f32(bits: np.ndarray) -> np.ndarray:
