@@ -27,7 +27,7 @@ FLAGS = [
 
 KERNEL_SOURCES = [
     "errors.cu", "elementwise.cu", "qgmma_emulation.cu", "gemm_tcgen05.cu", "gemv.cu",
-    "hyena_fir.cu", "hyena_fir_fused.cu", "hyena_fir_tcgen05.cu", "hyena_modal.cu", "hyena_decode.cu", "attention.cu", "attention_flash.cu", "attention_tcgen05.cu", "attention_decode.cu", "kv_q8.cu", "linear_executor.cu", "fp8_codec.cpp",
+    "hyena_fir.cu", "hyena_fir_fused.cu", "hyena_fir_tcgen05.cu", "hyena_modal.cu", "hyena_decode.cu", "attention.cu", "attention_flash.cu", "attention_tcgen05.cu", "attention_tcgen05_k64.cu", "attention_decode.cu", "kv_q8.cu", "linear_executor.cu", "fp8_codec.cpp",
 ]
 OPS_SOURCES = KERNEL_SOURCES + ["ops_api.cu"]
 RUNTIME_SOURCES = KERNEL_SOURCES + [

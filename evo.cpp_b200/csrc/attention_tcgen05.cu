@@ -25,6 +25,8 @@
 // as the projection kernels.
 #include <cuda.h>
 
+#include <cstdlib>
+
 #include "common.cuh"
 #include "ops_internal.hpp"
 #include "projection_featurizer.cuh"
@@ -377,6 +379,10 @@ flash_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
 
 }  // namespace
 
+// attention_tcgen05_k64.cu: the same contract on 64-key tiles, two CTAs per SM, O kept in TMEM
+int flash_tcgen05_attention_k64(const void *query, const void *key_cache, const void *value_cache, std::size_t rows,
+                                std::size_t total_keys, std::size_t heads, void *output, cudaStream_t stream);
+
 bool flash_tcgen05_applicable(const void *query, const void *key_cache, const void *value_cache,
                               const std::size_t rows, const std::size_t total_keys, const std::size_t heads,
                               const void *output) {
@@ -389,6 +395,12 @@ bool flash_tcgen05_applicable(const void *query, const void *key_cache, const vo
 int flash_tcgen05_attention(const void *query, const void *key_cache, const void *value_cache,
                             const std::size_t rows, const std::size_t total_keys, const std::size_t heads,
                             void *output, cudaStream_t stream) {
+  // EVO_B200_ATTENTION_K64=1: two CTAs per SM on 64-key tiles instead of the one-CTA kernel below
+  static const bool k64 = [] {
+    const char *const flag = std::getenv("EVO_B200_ATTENTION_K64");
+    return flag != nullptr && flag[0] == '1';
+  }();
+  if (k64) return flash_tcgen05_attention_k64(query, key_cache, value_cache, rows, total_keys, heads, output, stream);
   int status = kOk;
   int *const error = error_word(&status, nullptr);
   if (error == nullptr) return status;
