@@ -7,8 +7,8 @@
 // softmax warps walk TMEM load -> row maximum -> exchange -> exp2 -> P store in
 // lock-step and the tensor core waits for them.  Here a CTA still owns 128 query
 // rows of one head but
-//   * walks 64-key tiles, so Q (32 KiB), one K stage, two V stages and the P
-//     tile (16 KiB each) are 96 KiB and two CTAs share an SM: while one CTA's
+//   * walks 64-key tiles, so Q (32 KiB), two K stages, two V stages and the P
+//     tile (16 KiB each) are 112 KiB and two CTAs share an SM: while one CTA's
 //     softmax runs, the other's MMAs do;
 //   * keeps O in TMEM for the whole walk: P_j V_j accumulates in place, and the
 //     accumulator is rescaled (TMEM load, multiply, TMEM store) only when a
@@ -18,11 +18,11 @@
 //   * the row's reference, not its running maximum, is what the probabilities
 //     are taken against: p = 2^((s - ref) / sqrt(128) * log2 e) <= 2^8, the same
 //     value after the final division by the row sum.
-// Warp roles: warp 0 TMA producer, warp 1 MMA issuer (one lane each), warps 2-9
-// softmax (a thread owns half of one query row's 64 keys - its TMEM lane - and
-// half of its 128 output dimensions; the two halves exchange one maximum per
-// tile through shared memory).  Every wait is time-bounded and raises the sticky
-// error word of the projection kernels.
+// Warp roles: warp 0 TMA producer (K and V two stages deep), warp 1 MMA issuer (one
+// lane each), warps 2-5 softmax: a thread owns one query row - its TMEM lane -
+// so the row maximum and the row sum are its own (no exchange between warps),
+// with the scale-and-shift and the sums as packed F32 pairs.  Every wait is
+// time-bounded and raises the sticky error word of the projection kernels.
 #include <cuda.h>
 
 #include "common.cuh"
@@ -36,28 +36,24 @@ using namespace tc;
 
 constexpr int kRows = 128;                      // query rows per CTA = head dimensions
 constexpr int kKeys = 64;                       // keys per tile
-constexpr int kSides = 2;                       // softmax warps per TMEM lane quarter
-constexpr int kKeyColumns = kKeys / kSides;     // keys per softmax thread and tile
-constexpr int kDimColumns = kRows / kSides;     // output dimensions per softmax thread
-constexpr int kThreads = 64 + 128 * kSides;
+constexpr int kThreads = 64 + 128;              // TMA warp, MMA warp, four softmax warps (a thread = a query row)
 constexpr int kQHalfBytes = kRows * 128;        // one 64-column box of Q: 128 rows x 128 bytes
 constexpr int kQBytes = 2 * kQHalfBytes;
 constexpr int kKvHalfBytes = kKeys * 128;       // one 64-column box of K or V: 64 keys x 128 bytes
 constexpr int kKvBytes = 2 * kKvHalfBytes;
 constexpr int kPBytes = kRows * kKeys * 2;      // 128 rows x 64 keys, BF16, K-major
 constexpr int kQOffset = 0;
-constexpr int kKOffset = kQOffset + kQBytes;    // one stage
-constexpr int kVOffset = kKOffset + kKvBytes;   // two stages
+constexpr int kKOffset = kQOffset + kQBytes;    // two stages
+constexpr int kVOffset = kKOffset + 2 * kKvBytes;  // two stages
 constexpr int kPOffset = kVOffset + 2 * kKvBytes;
 constexpr int kBarrierOffset = kPOffset + kPBytes;
 enum Barrier : int {
-  kQFull = 0, kKFull = 1, kKEmpty = 2, kVFull = 3, kVEmpty = 5, kSFull = 7, kSEmpty = 9, kPFull = 11, kOFull = 12,
-  kMaxReady = 13 /* one per lane quarter */, kSumReady = 17, kBarriers = 18
+  kQFull = 0, kKFull = 1, kKEmpty = 3, kVFull = 5, kVEmpty = 7, kSFull = 9, kSEmpty = 11, kPFull = 13, kOFull = 14,
+  kBarriers = 15
 };
 constexpr int kTmemPtrOffset = kBarrierOffset + kBarriers * 8;
 constexpr int kAbortOffset = kTmemPtrOffset + 8;
-constexpr int kExchangeOffset = kAbortOffset + 16;  // [2 tiles][kSides][128 rows] floats
-constexpr int kSmemBytes = kExchangeOffset + 2 * kSides * kRows * 4 + 1024;  // + alignment slack
+constexpr int kSmemBytes = kAbortOffset + 16;  // no slack: the kernel checks the 1024-byte alignment it asked for
 static_assert(2 * (kSmemBytes + 1024) <= 228 * 1024, "two CTAs per SM");
 constexpr std::uint32_t kTmemColumns = 256;  // S0 | S1 (64 each) | O (128)
 constexpr std::uint32_t kScoreColumns = kKeys;
@@ -141,9 +137,7 @@ __global__ void __launch_bounds__(kThreads, 2)
 flash_tcgen05_k64_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                          const __grid_constant__ CUtensorMap map_v, bf16 *const output, const int rows,
                          const int total_keys, const int heads, int *const error_word) {
-  extern __shared__ unsigned char smem_raw[];
-  // aligned by pointer arithmetic: the shared address space stays visible to the compiler
-  unsigned char *const smem = smem_raw + ((1024U - (smem_u32(smem_raw) & 1023U)) & 1023U);
+  extern __shared__ __align__(1024) unsigned char smem[];
   const std::uint32_t smem_base = smem_u32(smem);
   auto bar = [&](const int index) { return smem_base + kBarrierOffset + 8U * index; };
   volatile std::uint32_t *const tmem_ptr = reinterpret_cast<volatile std::uint32_t *>(smem + kTmemPtrOffset);
@@ -161,19 +155,17 @@ flash_tcgen05_k64_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
 
   if (threadIdx.x == 0) {
     mbar_init(bar(kQFull), 1);
-    mbar_init(bar(kKFull), 1);
-    mbar_init(bar(kKEmpty), 1);
     for (int s = 0; s < 2; ++s) {
+      mbar_init(bar(kKFull + s), 1);
+      mbar_init(bar(kKEmpty + s), 1);
       mbar_init(bar(kVFull + s), 1);
       mbar_init(bar(kVEmpty + s), 1);
       mbar_init(bar(kSFull + s), 1);
-      mbar_init(bar(kSEmpty + s), 4 * kSides);
+      mbar_init(bar(kSEmpty + s), 4);
     }
-    mbar_init(bar(kPFull), 4 * kSides);
+    mbar_init(bar(kPFull), 4);
     mbar_init(bar(kOFull), 1);
-    for (int q = 0; q < 4; ++q) mbar_init(bar(kMaxReady + q), kSides);
-    mbar_init(bar(kSumReady), 4 * kSides);
-    *abort_flag = 0;
+    *abort_flag = (smem_base & 1023U) != 0U ? 1 : 0;  // the tiles need the alignment the declaration asks for
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
@@ -189,21 +181,25 @@ flash_tcgen05_k64_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
   tc_fence_after();
   const std::uint32_t tmem_base = *tmem_ptr;
   const std::uint32_t tmem_o = tmem_base + 2 * kScoreColumns;
+  const bool aligned = *abort_flag == 0;
 
-  if (warp == 0) {
+  if (!aligned) {
+    // nothing is issued; the error word is raised below
+  } else if (warp == 0) {
     if (lane == 0) {
       const int column = head * kRows;
       mbar_expect_tx(bar(kQFull), kQBytes);
       tma_load_2d(smem_base + kQOffset, &map_q, bar(kQFull), column, q0);
       tma_load_2d(smem_base + kQOffset + kQHalfBytes, &map_q, bar(kQFull), column + 64, q0);
       for (int j = 0; j < tiles; ++j) {
-        // K has one stage: tile j lands once the scores of tile j - 1 are done
-        if (!mbar_wait(bar(kKEmpty), (j & 1U) ^ 1U, abort_flag)) break;
-        mbar_expect_tx(bar(kKFull), kKvBytes);
-        tma_load_2d(smem_base + kKOffset, &map_k, bar(kKFull), column, j * kKeys);
-        tma_load_2d(smem_base + kKOffset + kKvHalfBytes, &map_k, bar(kKFull), column + 64, j * kKeys);
         const int s = j & 1;
-        if (!mbar_wait(bar(kVEmpty + s), ((j >> 1) & 1U) ^ 1U, abort_flag)) break;
+        const std::uint32_t phase = (j >> 1) & 1U;
+        if (!mbar_wait(bar(kKEmpty + s), phase ^ 1U, abort_flag)) break;
+        const std::uint32_t k_dst = smem_base + kKOffset + s * kKvBytes;
+        mbar_expect_tx(bar(kKFull + s), kKvBytes);
+        tma_load_2d(k_dst, &map_k, bar(kKFull + s), column, j * kKeys);
+        tma_load_2d(k_dst + kKvHalfBytes, &map_k, bar(kKFull + s), column + 64, j * kKeys);
+        if (!mbar_wait(bar(kVEmpty + s), phase ^ 1U, abort_flag)) break;
         const std::uint32_t v_dst = smem_base + kVOffset + s * kKvBytes;
         mbar_expect_tx(bar(kVFull + s), kKvBytes);
         tma_load_2d(v_dst, &map_v, bar(kVFull + s), column, j * kKeys);
@@ -218,16 +214,18 @@ flash_tcgen05_k64_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
       // S_j = Q K_j^T (M128 N64, K = 128 dimensions in eight k16 steps) into score buffer j & 1
       auto issue_scores = [&](const int j) -> bool {
         const int s = j & 1;
-        if (!mbar_wait(bar(kKFull), j & 1U, abort_flag)) return false;
-        if (!mbar_wait(bar(kSEmpty + s), ((j >> 1) & 1U) ^ 1U, abort_flag)) return false;
+        const std::uint32_t phase = (j >> 1) & 1U;
+        if (!mbar_wait(bar(kKFull + s), phase, abort_flag)) return false;
+        if (!mbar_wait(bar(kSEmpty + s), phase ^ 1U, abort_flag)) return false;
         tc_fence_after();
+        const std::uint32_t k_base = smem_base + kKOffset + s * kKvBytes;
 #pragma unroll
         for (int k = 0; k < 8; ++k)
           tc_mma<false>(tmem_base + s * kScoreColumns,
                         smem_descriptor(smem_base + kQOffset + (k / 4) * kQHalfBytes + (k % 4) * 32),
-                        smem_descriptor(smem_base + kKOffset + (k / 4) * kKvHalfBytes + (k % 4) * 32), idesc_scores,
+                        smem_descriptor(k_base + (k / 4) * kKvHalfBytes + (k % 4) * 32), idesc_scores,
                         k != 0 ? 1U : 0U);
-        tc_commit(bar(kKEmpty));
+        tc_commit(bar(kKEmpty + s));
         tc_commit(bar(kSFull + s));
         return true;
       };
@@ -251,16 +249,14 @@ flash_tcgen05_k64_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     }
   } else {
     const int quarter = warp % 4;
-    const int side = (warp - 2) / 4;
     const int row = quarter * 32 + lane;  // query row inside the block = TMEM lane
     const std::uint32_t lane_base = static_cast<std::uint32_t>(quarter * 32) << 16U;
     const int position = prefix + q0 + row;  // last key this row may see
     const float scale_log2 = 1.4426950408889634F * rsqrtf(static_cast<float>(kRows));
     const float slack = kLazyDoublings / scale_log2;  // in score units
+    const unsigned long long scale_pair = pack_f32x2(scale_log2, scale_log2);
     float reference = -INFINITY, running_sum = 0.0F;
     unsigned char *const p_row = smem + kPOffset + row * 128;
-    const int first_chunk = side * kKeyColumns / 8;
-    float *const exchange = reinterpret_cast<float *>(smem + kExchangeOffset);
     bool ok = true;
 
     for (int j = 0; j < tiles; ++j) {
@@ -270,67 +266,38 @@ flash_tcgen05_k64_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
         break;
       }
       tc_fence_after();
-      std::uint32_t v[kKeyColumns];
-      tmem_load_32(tmem_base + s * kScoreColumns + lane_base + side * kKeyColumns, v);
-      tmem_load_wait();
+      std::uint32_t v[kKeys];
+      {
+        std::uint32_t chunk[2][32];
+        tmem_load_32(tmem_base + s * kScoreColumns + lane_base, chunk[0]);
+        tmem_load_32(tmem_base + s * kScoreColumns + lane_base + 32, chunk[1]);
+        tmem_load_wait();
+#pragma unroll
+        for (int i = 0; i < kKeys; ++i) v[i] = chunk[i / 32][i % 32];
+      }
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar(kSEmpty + s));  // the score buffer may be overwritten
-      const int key0 = j * kKeys + side * kKeyColumns;
-      if (j * kKeys + kKeys - 1 > prefix + q0) {  // some key hidden from some row
+      if (j * kKeys + kKeys - 1 > prefix + q0) {     // some key hidden from some row
 #pragma unroll
-        for (int i = 0; i < kKeyColumns; ++i)
-          if (key0 + i > position) v[i] = 0xff800000U;  // -inf
+        for (int i = 0; i < kKeys; ++i)
+          if (j * kKeys + i > position) v[i] = 0xff800000U;  // -inf
       }
       float partial_max[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-      for (int i = 0; i < kKeyColumns; i += 2)
+      for (int i = 0; i < kKeys; i += 2)
         partial_max[(i / 2) % 4] = max3(partial_max[(i / 2) % 4], __uint_as_float(v[i]), __uint_as_float(v[i + 1]));
-      const float side_max = fmaxf(fmaxf(partial_max[0], partial_max[1]), fmaxf(partial_max[2], partial_max[3]));
-      exchange[(s * kSides + side) * kRows + row] = side_max;
-      __syncwarp();
-      if (lane == 0) mbar_arrive(bar(kMaxReady + quarter));
-      if (!mbar_wait(bar(kMaxReady + quarter), j & 1U, abort_flag)) {
-        ok = false;
-        break;
-      }
-      float tile_max = side_max;
-#pragma unroll
-      for (int other = 1; other < kSides; ++other)
-        tile_max = fmaxf(tile_max, exchange[(s * kSides + ((side + other) % kSides)) * kRows + row]);
-      // both halves of a row see the same tile_max and reference, so they take the same decision
+      const float tile_max = fmaxf(fmaxf(partial_max[0], partial_max[1]), fmaxf(partial_max[2], partial_max[3]));
       const bool moved = tile_max > reference + slack;  // true on the first tile: reference = -inf
       const float alpha = moved ? fast_exp2((reference - tile_max) * scale_log2) : 1.0F;
       if (moved) reference = tile_max;
       const float bias = -reference * scale_log2;
-      if (j > 0) {
-        // P V of the previous tile has read the P tile and updated O
-        if (!mbar_wait(bar(kOFull), (j - 1) & 1U, abort_flag)) {
-          ok = false;
-          break;
-        }
-        tc_fence_after();
-        if (__any_sync(0xffffffffU, moved)) {
-#pragma unroll
-          for (int c = 0; c < kDimColumns / 16; ++c) {
-            std::uint32_t o[16];
-            const std::uint32_t address = tmem_o + lane_base + side * kDimColumns + c * 16;
-            tmem_load_16(address, o);
-            tmem_load_wait();
-#pragma unroll
-            for (int i = 0; i < 16; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-            tmem_store_16(address, o);
-          }
-          tmem_store_wait();
-        }
-      }
-      // probabilities, partial row sum, BF16 pack into the swizzled P tile; scale-and-shift and the
-      // sums two values per instruction (packed F32 pairs)
+      const unsigned long long bias_pair = pack_f32x2(bias, bias);
+      // probabilities and the row sum first: they need nothing from the previous tile's P V
       unsigned long long partial_sum[2] = {0ULL, 0ULL};  // two (even key, odd key) pairs of F32 sums
-      std::uint32_t packed[kKeyColumns / 2];
-      const unsigned long long scale_pair = pack_f32x2(scale_log2, scale_log2), bias_pair = pack_f32x2(bias, bias);
+      std::uint32_t packed[kKeys / 2];
 #pragma unroll
-      for (int i = 0; i < kKeyColumns; i += 2) {
+      for (int i = 0; i < kKeys; i += 2) {
         float tx, ty;
         unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(v[i]), __uint_as_float(v[i + 1])), scale_pair, bias_pair), tx,
                      ty);
@@ -341,46 +308,58 @@ flash_tcgen05_k64_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
       float sum_even, sum_odd, sum_even_b, sum_odd_b;
       unpack_f32x2(partial_sum[0], sum_even, sum_odd);
       unpack_f32x2(partial_sum[1], sum_even_b, sum_odd_b);
-      const float tile_sum = (sum_even + sum_odd) + (sum_even_b + sum_odd_b);
+      running_sum = fmaf(running_sum, alpha, (sum_even + sum_odd) + (sum_even_b + sum_odd_b));
+      if (j > 0) {
+        // P V of the previous tile has read the P tile and updated O
+        if (!mbar_wait(bar(kOFull), (j - 1) & 1U, abort_flag)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        if (__any_sync(0xffffffffU, moved)) {
 #pragma unroll
-      for (int q = 0; q < kKeyColumns / 8; ++q)
-        *reinterpret_cast<uint4 *>(p_row + (((first_chunk + q) ^ (row & 7)) << 4)) =
+          for (int c = 0; c < kRows / 16; ++c) {
+            std::uint32_t o[16];
+            const std::uint32_t address = tmem_o + lane_base + c * 16;
+            tmem_load_16(address, o);
+            tmem_load_wait();
+#pragma unroll
+            for (int i = 0; i < 16; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+            tmem_store_16(address, o);
+          }
+          tmem_store_wait();
+        }
+      }
+      // BF16 P into the swizzled K-major tile
+#pragma unroll
+      for (int q = 0; q < kKeys / 8; ++q)
+        *reinterpret_cast<uint4 *>(p_row + ((q ^ (row & 7)) << 4)) =
             make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
       // P visible to the tensor core (async proxy); the O rescale is ordered by the tcgen05 fence
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar(kPFull));
-      running_sum = fmaf(running_sum, alpha, tile_sum);
     }
     if (ok && tiles > 0 && mbar_wait(bar(kOFull), (tiles - 1) & 1U, abort_flag)) {
       tc_fence_after();
-      // the row sum is the sum of the halves' partial sums
-      exchange[side * kRows + row] = running_sum;
-      __syncwarp();
-      if (lane == 0) mbar_arrive(bar(kSumReady));
-      if (mbar_wait(bar(kSumReady), 0U, abort_flag)) {
-        float total = 0.0F;
+      const float inverse = 1.0F / running_sum;
+      bf16 *const out = output + static_cast<std::size_t>(q0 + row) * (static_cast<std::size_t>(heads) * kRows) +
+                        static_cast<std::size_t>(head) * kRows;
 #pragma unroll
-        for (int other = 0; other < kSides; ++other) total += exchange[other * kRows + row];
-        const float inverse = 1.0F / total;
-        bf16 *const out = output + static_cast<std::size_t>(q0 + row) * (static_cast<std::size_t>(heads) * kRows) +
-                          static_cast<std::size_t>(head) * kRows + side * kDimColumns;
+      for (int c = 0; c < kRows / 32; ++c) {
+        std::uint32_t o[32];
+        tmem_load_32(tmem_o + lane_base + c * 32, o);  // warp-wide: before the row test
+        tmem_load_wait();
+        if (q0 + row < rows) {
 #pragma unroll
-        for (int c = 0; c < kDimColumns / 32; ++c) {
-          std::uint32_t o[32];
-          tmem_load_32(tmem_o + lane_base + side * kDimColumns + c * 32, o);  // warp-wide: before the row test
-          tmem_load_wait();
-          if (q0 + row < rows) {
-#pragma unroll
-            for (int q = 0; q < 4; ++q) {
-              uint4 word;
-              word.x = round_pair_bf16(__uint_as_float(o[8 * q]) * inverse, __uint_as_float(o[8 * q + 1]) * inverse);
-              word.y = round_pair_bf16(__uint_as_float(o[8 * q + 2]) * inverse, __uint_as_float(o[8 * q + 3]) * inverse);
-              word.z = round_pair_bf16(__uint_as_float(o[8 * q + 4]) * inverse, __uint_as_float(o[8 * q + 5]) * inverse);
-              word.w = round_pair_bf16(__uint_as_float(o[8 * q + 6]) * inverse, __uint_as_float(o[8 * q + 7]) * inverse);
-              *reinterpret_cast<uint4 *>(out + c * 32 + 8 * q) = word;
-            }
+          for (int q = 0; q < 4; ++q) {
+            uint4 word;
+            word.x = round_pair_bf16(__uint_as_float(o[8 * q]) * inverse, __uint_as_float(o[8 * q + 1]) * inverse);
+            word.y = round_pair_bf16(__uint_as_float(o[8 * q + 2]) * inverse, __uint_as_float(o[8 * q + 3]) * inverse);
+            word.z = round_pair_bf16(__uint_as_float(o[8 * q + 4]) * inverse, __uint_as_float(o[8 * q + 5]) * inverse);
+            word.w = round_pair_bf16(__uint_as_float(o[8 * q + 6]) * inverse, __uint_as_float(o[8 * q + 7]) * inverse);
+            *reinterpret_cast<uint4 *>(out + c * 32 + 8 * q) = word;
           }
         }
       }
@@ -392,6 +371,7 @@ flash_tcgen05_k64_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
   __syncthreads();
   if (*abort_flag != 0) {
     // let copies that may still be in flight land before the shared memory is recycled
+    // (also reached when the dynamic shared memory did not start on a 1024-byte boundary)
     const unsigned long long start = global_timer_ns();
     while (global_timer_ns() - start < 200000ULL) __nanosleep(1000);
     if (threadIdx.x == 0) atomicOr(error_word, 1);
@@ -418,7 +398,9 @@ int flash_tcgen05_attention_k64(const void *query, const void *key_cache, const 
       (status = tc::make_bf16_tile_map(&map_v, value_cache, total_keys, width, kKeys)) != kOk)
     return status;
   if (cudaFuncSetAttribute(flash_tcgen05_k64_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) !=
-      cudaSuccess)
+          cudaSuccess ||
+      cudaFuncSetAttribute(flash_tcgen05_k64_kernel, cudaFuncAttributePreferredSharedMemoryCarveout,
+                           cudaSharedmemCarveoutMaxShared) != cudaSuccess)
     return fail(kCuda, "cannot raise the attention shared-memory limit");
   const dim3 grid(ceil_div_u(rows, kRows), static_cast<unsigned int>(heads));
   flash_tcgen05_k64_kernel<<<grid, kThreads, kSmemBytes, stream>>>(map_q, map_k, map_v, static_cast<bf16 *>(output),
