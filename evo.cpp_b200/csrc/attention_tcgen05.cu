@@ -395,10 +395,11 @@ bool flash_tcgen05_applicable(const void *query, const void *key_cache, const vo
 int flash_tcgen05_attention(const void *query, const void *key_cache, const void *value_cache,
                             const std::size_t rows, const std::size_t total_keys, const std::size_t heads,
                             void *output, cudaStream_t stream) {
-  // EVO_B200_ATTENTION_K64=1: two CTAs per SM on 64-key tiles instead of the one-CTA kernel below
+  // two CTAs per SM on 64-key tiles (attention_tcgen05_k64.cu) unless EVO_B200_ATTENTION_K64=0 asks for the
+  // one-CTA kernel below
   static const bool k64 = [] {
     const char *const flag = std::getenv("EVO_B200_ATTENTION_K64");
-    return flag != nullptr && flag[0] == '1';
+    return flag == nullptr || flag[0] != '0';
   }();
   if (k64) return flash_tcgen05_attention_k64(query, key_cache, value_cache, rows, total_keys, heads, output, stream);
   int status = kOk;

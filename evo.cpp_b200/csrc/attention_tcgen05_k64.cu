@@ -7,9 +7,13 @@
 // softmax warps walk TMEM load -> row maximum -> exchange -> exp2 -> P store in
 // lock-step and the tensor core waits for them.  Here a CTA still owns 128 query
 // rows of one head but
-//   * walks 64-key tiles, so Q (32 KiB), two K stages, two V stages and the P
-//     tile (16 KiB each) are 112 KiB and two CTAs share an SM: while one CTA's
+//   * walks 64-key tiles, so Q (32 KiB), two K stages and two V stages
+//     (16 KiB each) are 96 KiB and two CTAs share an SM: while one CTA's
 //     softmax runs, the other's MMAs do;
+//   * keeps P in TMEM: the BF16 probabilities overwrite the first half of the
+//     row's scores (tcgen05.st) and are the A operand of P_j V_j from there, so P
+//     costs no shared-memory write, read or proxy fence - shared-memory bandwidth
+//     (Q and K_j for the scores, V_j, the TMA writes) is what bounds the kernel;
 //   * keeps O in TMEM for the whole walk: P_j V_j accumulates in place, and the
 //     accumulator is rescaled (TMEM load, multiply, TMEM store) only when a
 //     row's reference maximum moves up by more than 2^8 - rows whose reference
@@ -41,21 +45,18 @@ constexpr int kQHalfBytes = kRows * 128;        // one 64-column box of Q: 128 r
 constexpr int kQBytes = 2 * kQHalfBytes;
 constexpr int kKvHalfBytes = kKeys * 128;       // one 64-column box of K or V: 64 keys x 128 bytes
 constexpr int kKvBytes = 2 * kKvHalfBytes;
-constexpr int kPBytes = kRows * kKeys * 2;      // 128 rows x 64 keys, BF16, K-major
 constexpr int kQOffset = 0;
 constexpr int kKOffset = kQOffset + kQBytes;    // two stages
 constexpr int kVOffset = kKOffset + 2 * kKvBytes;  // two stages
-constexpr int kPOffset = kVOffset + 2 * kKvBytes;
-constexpr int kBarrierOffset = kPOffset + kPBytes;
+constexpr int kBarrierOffset = kVOffset + 2 * kKvBytes;
 enum Barrier : int {
-  kQFull = 0, kKFull = 1, kKEmpty = 3, kVFull = 5, kVEmpty = 7, kSFull = 9, kSEmpty = 11, kPFull = 13, kOFull = 14,
-  kBarriers = 15
+  kQFull = 0, kKFull = 1, kKEmpty = 3, kVFull = 5, kVEmpty = 7, kSFull = 9, kPFull = 11, kOFull = 12, kBarriers = 13
 };
 constexpr int kTmemPtrOffset = kBarrierOffset + kBarriers * 8;
 constexpr int kAbortOffset = kTmemPtrOffset + 8;
 constexpr int kSmemBytes = kAbortOffset + 16;  // no slack: the kernel checks the 1024-byte alignment it asked for
 static_assert(2 * (kSmemBytes + 1024) <= 228 * 1024, "two CTAs per SM");
-constexpr std::uint32_t kTmemColumns = 256;  // S0 | S1 (64 each) | O (128)
+constexpr std::uint32_t kTmemColumns = 256;  // S0 | S1 (64 each; P_j replaces the first 32 columns of S_j) | O (128)
 constexpr std::uint32_t kScoreColumns = kKeys;
 // A reference maximum is replaced only when the tile's maximum exceeds it by this many doublings.
 constexpr float kLazyDoublings = 8.0F;
@@ -93,6 +94,28 @@ __device__ __forceinline__ float fast_exp2(const float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
+}
+// D[tmem] (+)= A[tmem] * B[smem]: the A operand (M x 16 BF16, two per 32-bit column) is read from
+// tensor memory.
+__device__ __forceinline__ void tc_mma_a_tmem(const std::uint32_t tmem_d, const std::uint32_t tmem_a,
+                                              const std::uint64_t desc_b, const std::uint32_t idesc,
+                                              const std::uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}" ::"r"(tmem_d),
+      "r"(tmem_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_store_32(const std::uint32_t taddr, const std::uint32_t (&v)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+      "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};" ::"r"(taddr),
+      "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]), "r"(v[8]), "r"(v[9]),
+      "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15]), "r"(v[16]), "r"(v[17]), "r"(v[18]),
+      "r"(v[19]), "r"(v[20]), "r"(v[21]), "r"(v[22]), "r"(v[23]), "r"(v[24]), "r"(v[25]), "r"(v[26]), "r"(v[27]),
+      "r"(v[28]), "r"(v[29]), "r"(v[30]), "r"(v[31])
+      : "memory");
 }
 // Packed F32 pairs: one instruction for two lanes of F32 arithmetic.
 __device__ __forceinline__ unsigned long long pack_f32x2(const float low, const float high) {
@@ -161,7 +184,6 @@ flash_tcgen05_k64_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
       mbar_init(bar(kVFull + s), 1);
       mbar_init(bar(kVEmpty + s), 1);
       mbar_init(bar(kSFull + s), 1);
-      mbar_init(bar(kSEmpty + s), 4);
     }
     mbar_init(bar(kPFull), 4);
     mbar_init(bar(kOFull), 1);
@@ -211,12 +233,13 @@ flash_tcgen05_k64_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
       constexpr std::uint32_t idesc_scores = instruction_descriptor(kKeys, false);
       constexpr std::uint32_t idesc_output = instruction_descriptor(kRows, true);
       bool ok = mbar_wait(bar(kQFull), 0U, abort_flag);
-      // S_j = Q K_j^T (M128 N64, K = 128 dimensions in eight k16 steps) into score buffer j & 1
+      // S_j = Q K_j^T (M128 N64, K = 128 dimensions in eight k16 steps) into score buffer j & 1.
+      // P_{j-2} sat in that buffer: its P V must have finished (which also means the scores of
+      // tile j - 2 were read long ago).
       auto issue_scores = [&](const int j) -> bool {
         const int s = j & 1;
-        const std::uint32_t phase = (j >> 1) & 1U;
-        if (!mbar_wait(bar(kKFull + s), phase, abort_flag)) return false;
-        if (!mbar_wait(bar(kSEmpty + s), phase ^ 1U, abort_flag)) return false;
+        if (!mbar_wait(bar(kKFull + s), (j >> 1) & 1U, abort_flag)) return false;
+        if (j >= 2 && !mbar_wait(bar(kOFull), (j - 2) & 1U, abort_flag)) return false;
         tc_fence_after();
         const std::uint32_t k_base = smem_base + kKOffset + s * kKvBytes;
 #pragma unroll
@@ -234,14 +257,14 @@ flash_tcgen05_k64_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
         if (j + 1 < tiles && !issue_scores(j + 1)) break;
         const int s = j & 1;
         if (!mbar_wait(bar(kVFull + s), (j >> 1) & 1U, abort_flag)) break;
-        // P_j is stored, and O is rescaled where a row needed it
+        // P_j is in tensor memory, and O is rescaled where a row needed it
         if (!mbar_wait(bar(kPFull), j & 1U, abort_flag)) break;
         tc_fence_after();
         const std::uint32_t v_base = smem_base + kVOffset + s * kKvBytes;
 #pragma unroll
         for (int k = 0; k < kKeys / 16; ++k)
-          // A: 16 keys of P (K-major, 32 bytes inside the swizzle row); B: 16 key rows of V
-          tc_mma<false>(tmem_o, smem_descriptor(smem_base + kPOffset + k * 32), v_descriptor(v_base + k * 16 * 128),
+          // A: 16 keys of P (eight 32-bit columns of tensor memory); B: 16 key rows of V
+          tc_mma_a_tmem(tmem_o, tmem_base + s * kScoreColumns + k * 8, v_descriptor(v_base + k * 16 * 128),
                         idesc_output, (j | k) != 0 ? 1U : 0U);
         tc_commit(bar(kVEmpty + s));
         tc_commit(bar(kOFull));
@@ -256,7 +279,6 @@ flash_tcgen05_k64_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     const float slack = kLazyDoublings / scale_log2;  // in score units
     const unsigned long long scale_pair = pack_f32x2(scale_log2, scale_log2);
     float reference = -INFINITY, running_sum = 0.0F;
-    unsigned char *const p_row = smem + kPOffset + row * 128;
     bool ok = true;
 
     for (int j = 0; j < tiles; ++j) {
@@ -275,9 +297,6 @@ flash_tcgen05_k64_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
 #pragma unroll
         for (int i = 0; i < kKeys; ++i) v[i] = chunk[i / 32][i % 32];
       }
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(bar(kSEmpty + s));  // the score buffer may be overwritten
       if (j * kKeys + kKeys - 1 > prefix + q0) {     // some key hidden from some row
 #pragma unroll
         for (int i = 0; i < kKeys; ++i)
@@ -294,49 +313,48 @@ flash_tcgen05_k64_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
       const float bias = -reference * scale_log2;
       const unsigned long long bias_pair = pack_f32x2(bias, bias);
       // probabilities and the row sum first: they need nothing from the previous tile's P V
-      unsigned long long partial_sum[2] = {0ULL, 0ULL};  // two (even key, odd key) pairs of F32 sums
+      unsigned long long partial_sum[4] = {0ULL, 0ULL, 0ULL, 0ULL};  // (even key, odd key) pairs of F32 sums
       std::uint32_t packed[kKeys / 2];
+      // in three sweeps, so that no instruction waits for the one before it
+      float t[kKeys];
+#pragma unroll
+      for (int i = 0; i < kKeys; i += 2)
+        unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(v[i]), __uint_as_float(v[i + 1])), scale_pair, bias_pair),
+                     t[i], t[i + 1]);
+#pragma unroll
+      for (int i = 0; i < kKeys; ++i) t[i] = fast_exp2(t[i]);
 #pragma unroll
       for (int i = 0; i < kKeys; i += 2) {
-        float tx, ty;
-        unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(v[i]), __uint_as_float(v[i + 1])), scale_pair, bias_pair), tx,
-                     ty);
-        const float px = fast_exp2(tx), py = fast_exp2(ty);
-        partial_sum[(i / 2) % 2] = add_f32x2(partial_sum[(i / 2) % 2], pack_f32x2(px, py));
-        packed[i / 2] = round_pair_bf16(px, py);
+        partial_sum[(i / 2) % 4] = add_f32x2(partial_sum[(i / 2) % 4], pack_f32x2(t[i], t[i + 1]));
+        packed[i / 2] = round_pair_bf16(t[i], t[i + 1]);
       }
+      partial_sum[0] = add_f32x2(partial_sum[0], partial_sum[2]);
+      partial_sum[1] = add_f32x2(partial_sum[1], partial_sum[3]);
       float sum_even, sum_odd, sum_even_b, sum_odd_b;
       unpack_f32x2(partial_sum[0], sum_even, sum_odd);
       unpack_f32x2(partial_sum[1], sum_even_b, sum_odd_b);
       running_sum = fmaf(running_sum, alpha, (sum_even + sum_odd) + (sum_even_b + sum_odd_b));
-      if (j > 0) {
-        // P V of the previous tile has read the P tile and updated O
+      if (j > 0 && __any_sync(0xffffffffU, moved)) {
+        // O may be touched once the previous tile's P V has finished
         if (!mbar_wait(bar(kOFull), (j - 1) & 1U, abort_flag)) {
           ok = false;
           break;
         }
         tc_fence_after();
-        if (__any_sync(0xffffffffU, moved)) {
 #pragma unroll
-          for (int c = 0; c < kRows / 16; ++c) {
-            std::uint32_t o[16];
-            const std::uint32_t address = tmem_o + lane_base + c * 16;
-            tmem_load_16(address, o);
-            tmem_load_wait();
+        for (int c = 0; c < kRows / 16; ++c) {
+          std::uint32_t o[16];
+          const std::uint32_t address = tmem_o + lane_base + c * 16;
+          tmem_load_16(address, o);
+          tmem_load_wait();
 #pragma unroll
-            for (int i = 0; i < 16; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-            tmem_store_16(address, o);
-          }
-          tmem_store_wait();
+          for (int i = 0; i < 16; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+          tmem_store_16(address, o);
         }
       }
-      // BF16 P into the swizzled K-major tile
-#pragma unroll
-      for (int q = 0; q < kKeys / 8; ++q)
-        *reinterpret_cast<uint4 *>(p_row + ((q ^ (row & 7)) << 4)) =
-            make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
-      // P visible to the tensor core (async proxy); the O rescale is ordered by the tcgen05 fence
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      // BF16 P over the first 32 columns of this row's scores (all 64 are in registers by now)
+      tmem_store_32(tmem_base + s * kScoreColumns + lane_base, packed);
+      tmem_store_wait();
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar(kPFull));
