@@ -159,6 +159,40 @@ def test_projection_fed_fused_prefill_matches_unfused_chain(ops, oracle, kind):
     assert np.array_equal(short_cache.cpu().numpy(), expected_short_cache)
 
 
+@pytest.mark.parametrize("length,width,groups,taps", [(19, 32, 2, 128), (127, 32, 2, 64), (129, 48, 3, 100),
+                                                       (257, 16, 1, 33), (1000, 64, 4, 128)])
+def test_projection_fed_hcm_on_tensor_cores_ragged_shapes(ops, oracle, length, width, groups, taps):
+    """The tcgen05 Toeplitz kernel (groups of 16 channels, 32 < taps <= 128) at lengths below, at and
+    across its 128-row tile, filters shorter than the strip, with and without the direct term; outputs
+    against the unfused oracle chain, both decode caches bit for bit."""
+    rng = np.random.default_rng(length * 7 + taps)
+    projection = rand_bf16(rng, length, 3 * width)
+    short = rand_bf16(rng, 3 * width, 3, scale=0.5)
+    h = rand_bf16(rng, groups, taps, scale=0.2)
+    direct = rand_bf16(rng, width) if taps != 64 else None
+    out = empty_bits(length, width)
+    inner_cache = torch.full((width, taps - 1), 3.0, device="cuda")
+    short_cache = torch.zeros((3 * width, 2), device="cuda")
+    ops.call("bf16_projection_gated_fir_prefill", p(dev_bits(projection)), p(dev_bits(short)), p(dev_bits(h)),
+             0, p(dev_bits(direct)) if direct is not None else None, length, width, groups, taps,
+             1, None, p(inner_cache), p(short_cache), p(out), stream())
+    filtered = np.empty((length, 3 * width), np.uint16)
+    expected_short_cache = np.empty((3 * width, 2), np.float32)
+    oracle.fir_prefill(ptr(projection), ptr(short), 0, None, 0, length, 3 * width, 3 * width, 3, 1,
+                       ptr(filtered), ptr(expected_short_cache))
+    x2, x1, v = (np.empty((length, width), np.uint16) for _ in range(3))
+    oracle.split(ptr(filtered), length * width, ptr(x2), ptr(x1), ptr(v))
+    expected = np.empty((length, width), np.uint16)
+    expected_cache = np.empty((width, taps - 1), np.float32)
+    oracle.gated_fir(ptr(x2), ptr(x1), ptr(v), ptr(h), 0, ptr(direct) if direct is not None else None,
+                     length, width, groups, taps, 0, None, ptr(expected_cache), ptr(expected))
+    fraction, _ = ulp_mismatch_report(host_bits(out), expected)
+    assert fraction < 0.02, fraction
+    assert_close_bits(host_bits(out), expected, atol=0.03, rtol=0.02, min_cosine=0.9999)
+    assert np.array_equal(inner_cache.cpu().numpy(), expected_cache)
+    assert np.array_equal(short_cache.cpu().numpy(), expected_short_cache)
+
+
 def _modal_params(rng, width, modes):
     radius = rng.uniform(0.9, 0.999, (width, modes))
     log_poles = np.log(radius).astype(np.float32)
