@@ -102,6 +102,34 @@ def test_tcgen05_attention_matches_warp_mma_kernel(ops, rows, prefix, heads):
     assert (a[:, :128] - reference).abs().max().item() < 0.03
 
 
+@pytest.mark.parametrize("rows,prefix,growth", [(1024, 0, 2.0), (1024, 0, 0.05), (640, 384, 0.02)])
+def test_tcgen05_attention_with_growing_scores(ops, rows, prefix, growth):
+    """Scores that climb with the key position, at a different rate per query row: the row maximum
+    keeps moving, so the accumulated output has to be rescaled again and again (the two-CTA kernel
+    keeps it in tensor memory and rescales only rows whose reference moved by more than 2^8, other
+    rows of the same warp multiply by one).  Against F32 softmax attention."""
+    gen = torch.Generator(device="cuda").manual_seed(int(rows + prefix + growth * 100))
+    total = prefix + rows
+    direction = torch.sign(torch.randn(128, device="cuda", generator=gen)) / 128 ** 0.5
+    # row i looks along `direction` with strength i % 5 (0: flat scores), key j lies growth * j along it
+    strength = (torch.arange(rows, device="cuda") % 5).float()[:, None]
+    q = (strength * direction[None, :] * 128 ** 0.5 + 0.3 * torch.randn(rows, 128, device="cuda", generator=gen))
+    k = (growth * torch.arange(total, device="cuda").float()[:, None] * direction[None, :]
+         + 0.3 * torch.randn(total, 128, device="cuda", generator=gen))
+    v = torch.randn(total, 128, device="cuda", generator=gen)
+    q, k, v = q.bfloat16(), k.bfloat16(), v.bfloat16()
+    out = torch.full_like(q, 7.0)
+    ops.call("bf16_causal_attention", p(q), p(k), p(v), rows, total, 1, 128, p(out), stream())
+    ops.call("check_async_errors", stream())
+    scores = (q.float() @ k.float().T) / 128 ** 0.5
+    visible = torch.arange(total, device="cuda")[None, :] <= (prefix + torch.arange(rows, device="cuda"))[:, None]
+    reference = torch.softmax(scores.masked_fill(~visible, float("-inf")), dim=-1) @ v.float()
+    got = out.float()
+    assert torch.isfinite(got).all()
+    assert (got - reference).abs().max().item() < 0.04, (got - reference).abs().max().item()
+    assert torch.nn.functional.cosine_similarity(got.flatten(), reference.flatten(), dim=0).item() > 0.9995
+
+
 @pytest.mark.parametrize("rows,prefix,heads,head_dim", [(1, 0, 2, 128), (1, 2048, 2, 128), (9, 0, 3, 8),
                                                        (40, 100, 2, 128), (1, 10240, 1, 128)])
 def test_cached_cross_attention(ops, oracle, rows, prefix, heads, head_dim):
