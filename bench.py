@@ -696,20 +696,22 @@ def run_pipeline(args, rank: int, world: int, local_rank: int) -> None:
         profile = context.profile_read()
         context.profile_enable(False)
         # ---- end to end: pinned host tokens in on rank 0, logits out to pinned
-        # host memory on the last rank, every step
-        barrier()
-        begin = time.perf_counter()
+        # host memory on the last rank, one prompt at a time like `value`
+        e2e_total = 0.0
         for _ in range(args.steps):
+            barrier()
+            begin = time.perf_counter()
             if rank == 0:
                 device_tokens.copy_(pinned_tokens, non_blocking=True)
             driver.step(tokens)
             if last:
                 raw = torch.as_tensor(pipe.DeviceRows(stage.logits_address, tokens, VOCAB), device="cuda")
                 pinned_logits.copy_(raw, non_blocking=True)
-        driver.drain()
-        context.synchronize()
+            driver.drain()
+            context.synchronize()
+            e2e_total += max_over_ranks(time.perf_counter() - begin, "cuda", True)
         barrier()
-        e2e_seconds = max_over_ranks(time.perf_counter() - begin, "cuda", True) / args.steps
+        e2e_seconds = e2e_total / args.steps
     parity = None
     if last:
         bits = pinned_logits.numpy().astype(np.uint16).astype(np.uint32) << 16
