@@ -273,6 +273,32 @@ modal_stream_kernel(const ModalParams p) {
     load_words(row, t, [](const auto *address) { return static_cast<std::uint32_t>(__ldcs(address)); });
     return row;
   };
+  // The streaming loads walk the rows in order: the projection-fed form keeps a word pointer that moves
+  // one row per call instead of rebuilding the 64-bit address from the row number.
+  [[maybe_unused]] const unsigned int *cursor = nullptr;
+  [[maybe_unused]] const std::size_t cursor_stride = static_cast<std::size_t>(p.width) * 3 / 2;  // words per row
+  if constexpr (kProj)
+    cursor = reinterpret_cast<const unsigned int *>(p.projection + static_cast<std::size_t>(t_own) * 3 * p.width +
+                                                    static_cast<std::size_t>(kC == 2 ? c0 : c0 - odd) * 3) +
+             (kC == 2 ? 0 : odd);
+  const auto load_next_row = [&](auto checked, const int t) {
+    if constexpr (!kProj) {
+      return load_row(checked, t);
+    } else {
+      constexpr bool kChecked = decltype(checked)::value;
+      Row row;
+      row.w[0] = row.w[1] = row.w[2] = 0U;
+      const unsigned int *const at = cursor;
+      cursor += cursor_stride;
+      if constexpr (kChecked) {
+        if (t < 0 || t >= t_end) return row;
+      }
+      row.w[0] = __ldcs(at);
+      row.w[1] = __ldcs(at + 1);
+      if constexpr (kC == 2) row.w[2] = __ldcs(at + 2);
+      return row;
+    }
+  };
   // projection-fed rows as one F32 value per column
   const auto columns_of = [&](const Row &row, float (&x)[kColumns]) {
     if constexpr (kC == 2) {
@@ -310,6 +336,7 @@ modal_stream_kernel(const ModalParams p) {
   }
 
   Row next[kUnroll];
+  [[maybe_unused]] std::size_t out_offset = static_cast<std::size_t>(t_own) * p.width + c0;
   const auto run_group = [&](auto checked, const int base) {
     constexpr bool kChecked = decltype(checked)::value;
     Row rows[kUnroll];
@@ -320,7 +347,7 @@ modal_stream_kernel(const ModalParams p) {
       const int t = base + i;
       // one row's loads per row of arithmetic instead of a burst of kUnroll rows: the
       // load / store queue of the SM is not flooded at the start of every group
-      next[i] = load_row(checked, base + kUnroll + i);
+      next[i] = load_next_row(checked, base + kUnroll + i);
       if (kChecked && t >= t_end) break;
       std::uint32_t u_pair;  // u and the x2 gate of the pair, packed BF16
       [[maybe_unused]] std::uint32_t gate_pair = 0U;
@@ -368,7 +395,8 @@ modal_stream_kernel(const ModalParams p) {
           }
           modal[c] = ((partial[0] + partial[1]) + partial[2]) + partial[3];
         }
-        const std::size_t offset = static_cast<std::size_t>(t) * p.width + c0;
+        const std::size_t offset = out_offset;  // = t * width + c0, carried from row to row
+        out_offset += static_cast<std::size_t>(p.width);
         std::uint32_t result;
         const float modal_high = kC == 2 ? modal[kC - 1] : 0.0F;
         if (p.continue_from_state) {
@@ -402,7 +430,7 @@ modal_stream_kernel(const ModalParams p) {
   };
 
 #pragma unroll
-  for (int i = 0; i < kUnroll; ++i) next[i] = load_row(kCheckedRows, t_own + i);
+  for (int i = 0; i < kUnroll; ++i) next[i] = load_next_row(kCheckedRows, t_own + i);
   int base = t_own;
   for (; base + 2 * kUnroll <= t_end; base += kUnroll) run_group(kPlainRows, base);
   for (; base < t_end; base += kUnroll) run_group(kCheckedRows, base);
