@@ -549,6 +549,31 @@ gated_fir_stream_kernel(const Params p, const int segment_rows) {
     }
     return row;
   };
+  // The rows are loaded in order, one call per row from the first warm-up row on: the
+  // projection-fed form carries the row's address along instead of rebuilding it from t.
+  [[maybe_unused]] std::intptr_t cursor =
+      reinterpret_cast<std::intptr_t>(p.projection) +
+      (static_cast<std::intptr_t>(t_own - kWarm) * 3 * p.width + static_cast<std::intptr_t>(c0) * 3) *
+          static_cast<std::intptr_t>(sizeof(bf16));
+  [[maybe_unused]] const std::intptr_t cursor_stride = static_cast<std::intptr_t>(p.width) * 3 * sizeof(bf16);
+  const auto load_next_row = [&](auto checked, const int t) {
+    if constexpr (!kProj) {
+      return load_row(checked, t);
+    } else {
+      constexpr bool kChecked = decltype(checked)::value;
+      Row row;
+      const bf16 *const source = reinterpret_cast<const bf16 *>(cursor);
+      cursor += cursor_stride;
+      if constexpr (kChecked) {
+#pragma unroll
+        for (int i = 0; i < kWords; ++i) row.w[i] = 0U;
+        if (t < 0 || t >= t_end) return row;
+      }
+#pragma unroll
+      for (int i = 0; i < 3; ++i) load_pairs<kC>(source + i * kC, row.w + i * kPairs);
+      return row;
+    }
+  };
 
   float xh[2][kProj ? 3 * kC : 1];   // raw rows t-2, t-1
 #pragma unroll
@@ -564,13 +589,14 @@ gated_fir_stream_kernel(const Params p, const int segment_rows) {
   const int t_first = t_own - kWarm;
 
   Row next[kUnroll];
+  std::size_t out_offset = static_cast<std::size_t>(t_own) * p.width + c0;
   const auto run_group = [&](auto checked, const int base) {
     constexpr bool kChecked = decltype(checked)::value;
     Row rows[kUnroll];
 #pragma unroll
     for (int i = 0; i < kUnroll; ++i) rows[i] = next[i];
 #pragma unroll
-    for (int i = 0; i < kUnroll; ++i) next[i] = load_row(checked, base + kUnroll + i);
+    for (int i = 0; i < kUnroll; ++i) next[i] = load_next_row(checked, base + kUnroll + i);
 #pragma unroll
     for (int i = 0; i < kUnroll; ++i) {
       const int t = base + i;
@@ -625,8 +651,10 @@ gated_fir_stream_kernel(const Params p, const int segment_rows) {
 #pragma unroll
         for (int j = 0; j < kPairs; ++j)
           packed[j] = mul_pairs(round_pair_bf16(y[2 * j], y[2 * j + 1]), gate_pair[j]);
-        store_pairs<kC>(p.output + static_cast<std::size_t>(t) * p.width + c0, packed);
-        if (p.pregate != nullptr) store_pairs<kC>(p.pregate + static_cast<std::size_t>(t) * p.width + c0, u_pair);
+        // rows t_own .. t_end - 1 come by in order: the offset t * width + c0 is carried along
+        store_pairs<kC>(p.output + out_offset, packed);
+        if (p.pregate != nullptr) store_pairs<kC>(p.pregate + out_offset, u_pair);
+        out_offset += static_cast<std::size_t>(p.width);
       }
       if constexpr (kChecked && kProj) {
         // raw rows length-2 and length-1 are the featurizer's decode history
@@ -662,7 +690,7 @@ gated_fir_stream_kernel(const Params p, const int segment_rows) {
   constexpr std::true_type kCheckedRows{};
   constexpr std::false_type kPlainRows{};
 #pragma unroll
-  for (int i = 0; i < kUnroll; ++i) next[i] = load_row(kCheckedRows, t_first + i);
+  for (int i = 0; i < kUnroll; ++i) next[i] = load_next_row(kCheckedRows, t_first + i);
   int base = t_first;
   for (; base < t_own; base += kUnroll) run_group(kCheckedRows, base);  // warm-up: kWarm is a multiple of kUnroll
   // steady state: this group and the one being fetched lie inside the segment,
