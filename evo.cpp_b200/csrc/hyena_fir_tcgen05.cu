@@ -241,7 +241,9 @@ gated_fir_tcgen05_kernel(const TcParams p, int *const error_word) {
       for (int n = 0; n < 4; ++n) {
         if (n == 3 && threadIdx.x + 3 * kWorkers >= kRawRows * 6) break;
         const int t = t0 + stage_row[n];
-        const bool valid = t >= 0 && t < p.length;
+        // The oldest raw row of step 0 only feeds u[t_first - 128], which meets a zero tap: it is not
+        // read, so a window needs taps + 1 = 129 rows of history in front of it, as the other kernels do.
+        const bool valid = t >= 0 && t < p.length && (step != 0 || stage_row[n] != -2);
         asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(base + stage_smem[n]),
                      "l"(valid ? origin + stage_global[n] : reinterpret_cast<const unsigned char *>(p.projection)),
                      "r"(valid ? 16U : 0U)
