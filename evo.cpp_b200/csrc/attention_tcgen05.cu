@@ -368,7 +368,7 @@ flash_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
     // let copies that may still be in flight land before the shared memory is recycled
     const unsigned long long start = global_timer_ns();
     while (global_timer_ns() - start < 200000ULL) __nanosleep(1000);
-    if (threadIdx.x == 0) atomicOr(error_word, 1);
+    if (threadIdx.x == 0) atomicOr(error_word, 1 | 16);  // bit 4: this kernel
   }
   if (warp == 1) {
     tc_fence_after();

@@ -352,6 +352,13 @@ flash_tcgen05_k64_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
           tmem_store_16(address, o);
         }
       }
+      // An mbarrier does not know which tile an arrival belongs to: a warp that runs a whole tile ahead
+      // of a slower one must not arrive for tile j while the phase of tile j - 1 is still open, or that
+      // phase would complete without the slower warp's probabilities.
+      if (j > 0 && !mbar_wait(bar(kPFull), (j - 1) & 1U, abort_flag)) {
+        ok = false;
+        break;
+      }
       // BF16 P over the first 32 columns of this row's scores (all 64 are in registers by now)
       tmem_store_32(tmem_base + s * kScoreColumns + lane_base, packed);
       tmem_store_wait();
@@ -359,6 +366,10 @@ flash_tcgen05_k64_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
       __syncwarp();
       if (lane == 0) mbar_arrive(bar(kPFull));
     }
+    // A parity wait cannot tell a phase from the one two before it.  A warp that never had to rescale has
+    // not looked at this barrier since the start, and all it knows from the scores of its last tile is
+    // that P V of tile `tiles - 3` is done: it first waits for tile `tiles - 2`, then for the last one.
+    if (ok && tiles > 1) ok = mbar_wait(bar(kOFull), (tiles - 2) & 1U, abort_flag);
     if (ok && tiles > 0 && mbar_wait(bar(kOFull), (tiles - 1) & 1U, abort_flag)) {
       tc_fence_after();
       const float inverse = 1.0F / running_sum;
@@ -392,7 +403,7 @@ flash_tcgen05_k64_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     // (also reached when the dynamic shared memory did not start on a 1024-byte boundary)
     const unsigned long long start = global_timer_ns();
     while (global_timer_ns() - start < 200000ULL) __nanosleep(1000);
-    if (threadIdx.x == 0) atomicOr(error_word, 1);
+    if (threadIdx.x == 0) atomicOr(error_word, 1 | 8);  // bit 3: this kernel
   }
   if (warp == 1) {
     tc_fence_after();

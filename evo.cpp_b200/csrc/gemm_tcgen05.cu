@@ -364,7 +364,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
     // memory of this CTA is recycled, then report.
     const unsigned long long start = global_timer_ns();
     while (global_timer_ns() - start < 200000ULL) __nanosleep(1000);
-    if (threadIdx.x == 0) atomicOr(error_word, 1);
+    if (threadIdx.x == 0) atomicOr(error_word, 1 | 32);  // bit 5: a projection kernel
   }
   if (warp == 1) {
     tc_fence_after();
@@ -518,7 +518,7 @@ gemm_swap_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
   if (*abort_flag != 0) {
     const unsigned long long start = global_timer_ns();
     while (global_timer_ns() - start < 200000ULL) __nanosleep(1000);
-    if (threadIdx.x == 0) atomicOr(error_word, 1);
+    if (threadIdx.x == 0) atomicOr(error_word, 1 | 32);  // bit 5: a projection kernel
   }
   if (warp == 1) {
     tc_fence_after();
@@ -791,7 +791,15 @@ int gemm_error_state(cudaStream_t stream) {
     return fail(kCuda, "cannot read the GEMM error word");
   if (value != 0) {
     cudaMemsetAsync(state->error_word, 0, sizeof(int), stream);
-    if ((value & 1) != 0) return fail(kCuda, "a tcgen05 GEMM pipeline wait timed out");
+    if ((value & 1) != 0) {
+      // bits 2..5 name the kernel family whose bounded wait ran out
+      std::string where;
+      if ((value & 4) != 0) where += " [medium FIR]";
+      if ((value & 8) != 0) where += " [attention, 64-key tiles]";
+      if ((value & 16) != 0) where += " [attention, 128-key tiles]";
+      if ((value & 32) != 0) where += " [projection]";
+      return fail(kCuda, "a tcgen05 GEMM pipeline wait timed out" + where);
+    }
     return fail(kInvalidArgument, "token ID exceeds model vocabulary");
   }
   return kOk;

@@ -386,7 +386,7 @@ gated_fir_tcgen05_kernel(const TcParams p, int *const error_word) {
   if (*abort_flag != 0) {
     const unsigned long long start = global_timer_ns();
     while (global_timer_ns() - start < 200000ULL) __nanosleep(1000);
-    if (threadIdx.x == 0) atomicOr(error_word, 1);
+    if (threadIdx.x == 0) atomicOr(error_word, 1 | 4);  // bit 2: this kernel
   }
   if (warp == kMmaWarp) {
     tc_fence_after();

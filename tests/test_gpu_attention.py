@@ -130,6 +130,46 @@ def test_tcgen05_attention_with_growing_scores(ops, rows, prefix, growth):
     assert torch.nn.functional.cosine_similarity(got.flatten(), reference.flatten(), dim=0).item() > 0.9995
 
 
+def test_tcgen05_attention_gives_the_same_bits_on_concurrent_streams(ops):
+    """Six host threads, each with its own stream, run the attention operator over and over on
+    prompts of 151..361 rows.  With several kernels sharing the SMs the warps of a CTA drift far
+    apart, which is when a hand-over that is only safe at similar speeds shows (one did: a warp
+    that never rescaled read the accumulator two phases early).  Every result must equal the one
+    computed alone, bit for bit."""
+    import threading
+
+    gen = torch.Generator(device="cuda").manual_seed(11)
+    jobs = []
+    for rows in (243, 233, 361, 151, 348, 205):
+        q, k, v = (torch.randn(rows, 256, device="cuda", generator=gen).bfloat16() for _ in range(3))
+        alone = torch.empty_like(q)
+        ops.call("bf16_causal_attention", p(q), p(k), p(v), rows, rows, 2, 128, p(alone), stream())
+        jobs.append((rows, q, k, v, alone))
+    torch.cuda.synchronize()
+    failures = []
+
+    def worker(job):
+        rows, q, k, v, alone = job
+        own = torch.cuda.Stream()
+        with torch.cuda.stream(own):
+            out = torch.empty_like(q)
+            for iteration in range(400):
+                out.zero_()
+                ops.call("bf16_causal_attention", p(q), p(k), p(v), rows, rows, 2, 128, p(out), own.cuda_stream)
+                own.synchronize()
+                if not torch.equal(out, alone):
+                    failures.append((rows, iteration, int((out != alone).any(dim=1).nonzero()[0])))
+                    return
+
+    threads = [threading.Thread(target=worker, args=(job,)) for job in jobs]
+    for thread in threads:
+        thread.start()
+    for thread in threads:
+        thread.join()
+    ops.call("check_async_errors", stream())
+    assert not failures, failures
+
+
 @pytest.mark.parametrize("rows,prefix,heads,head_dim", [(1, 0, 2, 128), (1, 2048, 2, 128), (9, 0, 3, 8),
                                                        (40, 100, 2, 128), (1, 10240, 1, 128)])
 def test_cached_cross_attention(ops, oracle, rows, prefix, heads, head_dim):

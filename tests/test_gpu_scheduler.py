@@ -58,7 +58,10 @@ def test_concurrent_requests_equal_single_context_results(rt, pkg, fixture_path)
     assert all(tickets) and greedy and sampled
     scheduler.wait_idle()
     metrics = scheduler.metrics()
-    assert metrics["submitted"] == metrics["completed"] == 26 and metrics["failed"] == metrics["rejected"] == 0
+    unfinished = {t: (r["status"], r["error"], r["cancelled"]) for t, r in scheduler.results.items()
+                  if r["status"] != 0 or r["cancelled"]}
+    assert metrics["submitted"] == metrics["completed"] == 26 and metrics["failed"] == metrics["rejected"] == 0, \
+        (metrics, unfinished)
     assert metrics["queued"] == metrics["active"] == 0 and 1 <= metrics["active_peak"] <= 4
     for ticket, sequence in zip(tickets, sequences):
         result = scheduler.results[ticket]
