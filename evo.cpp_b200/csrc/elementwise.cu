@@ -357,6 +357,56 @@ rms_norm_kernel(const bf16 *__restrict__ input, const float *__restrict__ scale,
   }
 }
 
+// A few rows (cached decode, very short prompts): one block per row, every load of the row and of the
+// gains issued before anything is waited for - one trip to memory where the streaming kernel makes three
+// in a row (gains, row, next row) and the generic one two.  A thread owns columns t, t + 256, ... in
+// registers: exactly the terms of its partial sum in row_denominator's order, and the columns it
+// normalises and stores (neighbouring threads write neighbouring columns).
+template <int kPerThread>
+__global__ void __launch_bounds__(kThreads)
+rms_norm_few_rows_kernel(const bf16 *__restrict__ input, const float *__restrict__ scale,
+                         bf16 *__restrict__ output, std::uint8_t *__restrict__ codes, const int width,
+                         const float epsilon, const float quant_scale) {
+  __shared__ float partial[32];
+  const std::size_t row = blockIdx.x;
+  const unsigned short *const in = reinterpret_cast<const unsigned short *>(input) + row * width;
+  unsigned short raw[kPerThread];
+  float gain[kPerThread];
+#pragma unroll
+  for (int k = 0; k < kPerThread; ++k) raw[k] = __ldg(in + threadIdx.x + k * kThreads);
+#pragma unroll
+  for (int k = 0; k < kPerThread; ++k) gain[k] = __ldg(scale + threadIdx.x + k * kThreads);
+  float sum = 0.0F;
+#pragma unroll
+  for (int k = 0; k < kPerThread; ++k) {
+    const float value = bits2f_bf16(raw[k]);
+    sum = fmaf(value, value, sum);
+  }
+  // the rest of row_denominator: shuffle-down tree, the warps' sums, the three roundings
+  sum = warp_sum_down(sum);
+  const int lane = threadIdx.x % 32, warp = threadIdx.x / 32;
+  if (lane == 0) partial[warp] = sum;
+  __syncthreads();
+  if (warp == 0) {
+    float block_sum = lane < kThreads / 32 ? partial[lane] : 0.0F;
+    block_sum = warp_sum_down(block_sum);
+    if (lane == 0) {
+      const float norm = rbf(sqrtf(block_sum));
+      const float scaled = rbf(norm * rsqrtf(static_cast<float>(width)));
+      partial[0] = rbf(scaled + epsilon);
+    }
+  }
+  __syncthreads();
+  const float denominator = partial[0];
+#pragma unroll
+  for (int k = 0; k < kPerThread; ++k) {
+    const std::size_t column = threadIdx.x + k * kThreads;
+    const bf16 result = f2bf(rbf(__fdiv_rn(bits2f_bf16(raw[k]), denominator)) * rbf(gain[k]));
+    if (output != nullptr) output[row * width + column] = result;
+    if (codes != nullptr) codes[row * width + column] = e4m3_code(bf2f(result) * quant_scale);
+  }
+}
+
 // Vector form (width % 8 == 0, 16-byte aligned pointers): persistent blocks, each
 // walking rows blockIdx.x, blockIdx.x + gridDim.x, ...  The next row of a block
 // is copied into the other half of the shared row cache with cp.async while
@@ -635,6 +685,23 @@ int rms_norm(const void *input, const float *scale, const std::size_t rows,
   };
   const bool vectors = width % 8 == 0 && aligned(input, 15) && aligned(scale, 15) &&
                        (output == nullptr || aligned(output, 15)) && (codes == nullptr || aligned(codes, 7));
+  if (rows <= 8 && width % kThreads == 0) {
+    const auto launch_few = [&](auto kernel) {
+      kernel<<<static_cast<unsigned int>(rows), kThreads, 0, stream>>>(
+          static_cast<const bf16 *>(input), scale, static_cast<bf16 *>(output), static_cast<std::uint8_t *>(codes),
+          static_cast<int>(width), epsilon, quant_scale);
+      return check_launch("RMSNorm kernel");
+    };
+    switch (width / kThreads) {
+      case 1: return launch_few(rms_norm_few_rows_kernel<1>);
+      case 2: return launch_few(rms_norm_few_rows_kernel<2>);
+      case 4: return launch_few(rms_norm_few_rows_kernel<4>);
+      case 8: return launch_few(rms_norm_few_rows_kernel<8>);     // 2048
+      case 16: return launch_few(rms_norm_few_rows_kernel<16>);   // 4096
+      case 32: return launch_few(rms_norm_few_rows_kernel<32>);   // 8192
+      default: break;
+    }
+  }
   if (vectors) {
     const std::size_t smem = 3 * width * sizeof(unsigned short);
     const auto launch = [&](auto kernel) {

@@ -110,7 +110,8 @@ def test_emulated_qgmma_random_shapes_bit_exact(ops, oracle, rows, inner, column
 
 def test_rms_norm_and_fused_codes(ops, oracle):
     rng = np.random.default_rng(3)
-    for rows, width in [(5, 1920), (33, 4096), (3, 8), (2, 513)]:
+    # (3, 4096), (1, 8192), (8, 256): the few-row kernel of decode steps (width a multiple of 256)
+    for rows, width in [(5, 1920), (33, 4096), (3, 8), (2, 513), (3, 4096), (1, 8192), (8, 256)]:
         x_bits = rand_bf16(rng, rows, width, scale=2.0)
         scale = (1 + 0.1 * rng.standard_normal(width)).astype(np.float32)
         out = empty_bits(rows, width)
