@@ -103,7 +103,7 @@ gemv_kernel(const GemvParams p) {
   const std::size_t row_bytes = static_cast<std::size_t>(p.K) * (kFp8 ? 1 : 2);
   const unsigned char *const wb = static_cast<const unsigned char *>(p.w);
   const unsigned char *const xb = static_cast<const unsigned char *>(p.x);
-#pragma unroll(kRows <= 2 ? 2 : 1)
+#pragma unroll(kRows == 1 ? 4 : (kRows == 2 ? 2 : 1))
   for (int chunk = threadIdx.x; chunk < chunks; chunk += kThreads) {
     uint4 wraw[kColumns];
 #pragma unroll
