@@ -59,6 +59,9 @@ attention_decode_kernel(const bf16 *__restrict__ query, const bf16 *__restrict__
                         const bf16 *__restrict__ value_cache, const Q8PageTable pages, bf16 *__restrict__ output,
                         const int rows, const int static_total_keys, const int heads,
                         const int *__restrict__ dynamic_prefix) {
+  // lets a one-row projection launched with programmatic stream serialisation start (and fetch its
+  // weights) under this kernel; it still waits for this grid to finish before it reads the result
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   // replayed launches (CUDA graphs) read the number of keys already cached from device memory
   const int total_keys = dynamic_prefix != nullptr ? *dynamic_prefix + rows : static_total_keys;
   __shared__ float warp_partials[kWarps][kPartial];

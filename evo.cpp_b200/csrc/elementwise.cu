@@ -367,15 +367,21 @@ __global__ void __launch_bounds__(kThreads)
 rms_norm_few_rows_kernel(const bf16 *__restrict__ input, const float *__restrict__ scale,
                          bf16 *__restrict__ output, std::uint8_t *__restrict__ codes, const int width,
                          const float epsilon, const float quant_scale) {
+  // lets a one-row projection launched with programmatic stream serialisation start (and fetch its
+  // weights) under this kernel; it still waits for this grid to finish before it reads the result
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   __shared__ float partial[32];
   const std::size_t row = blockIdx.x;
   const unsigned short *const in = reinterpret_cast<const unsigned short *>(input) + row * width;
   unsigned short raw[kPerThread];
   float gain[kPerThread];
 #pragma unroll
-  for (int k = 0; k < kPerThread; ++k) raw[k] = __ldg(in + threadIdx.x + k * kThreads);
-#pragma unroll
   for (int k = 0; k < kPerThread; ++k) gain[k] = __ldg(scale + threadIdx.x + k * kThreads);
+  // launched with programmatic stream serialisation, the gains above were requested while the kernel
+  // that writes the row may still be running; otherwise this returns at once
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+#pragma unroll
+  for (int k = 0; k < kPerThread; ++k) raw[k] = in[threadIdx.x + k * kThreads];
   float sum = 0.0F;
 #pragma unroll
   for (int k = 0; k < kPerThread; ++k) {
@@ -672,7 +678,7 @@ int quantize_f32(const float *input, const std::size_t elements,
 
 int rms_norm(const void *input, const float *scale, const std::size_t rows,
              const std::size_t width, const float epsilon, void *output,
-             void *codes, const float quant_scale, cudaStream_t stream) {
+             void *codes, const float quant_scale, cudaStream_t stream, const bool dependent_launch) {
   if (input == nullptr || scale == nullptr ||
       (output == nullptr && codes == nullptr) || width == 0 ||
       width > 24576 || rows > 0x7fffffffU)
@@ -687,9 +693,19 @@ int rms_norm(const void *input, const float *scale, const std::size_t rows,
                        (output == nullptr || aligned(output, 15)) && (codes == nullptr || aligned(codes, 7));
   if (rows <= 8 && width % kThreads == 0) {
     const auto launch_few = [&](auto kernel) {
-      kernel<<<static_cast<unsigned int>(rows), kThreads, 0, stream>>>(
-          static_cast<const bf16 *>(input), scale, static_cast<bf16 *>(output), static_cast<std::uint8_t *>(codes),
-          static_cast<int>(width), epsilon, quant_scale);
+      cudaLaunchAttribute attribute{};
+      attribute.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+      attribute.val.programmaticStreamSerializationAllowed = dependent_launch ? 1 : 0;
+      cudaLaunchConfig_t config{};
+      config.gridDim = dim3(static_cast<unsigned int>(rows));
+      config.blockDim = dim3(kThreads);
+      config.stream = stream;
+      config.attrs = &attribute;
+      config.numAttrs = 1;
+      if (cudaLaunchKernelEx(&config, kernel, static_cast<const bf16 *>(input), scale, static_cast<bf16 *>(output),
+                             static_cast<std::uint8_t *>(codes), static_cast<int>(width), epsilon,
+                             quant_scale) != cudaSuccess)
+        return fail(kCuda, "cannot launch the RMSNorm kernel");
       return check_launch("RMSNorm kernel");
     };
     switch (width / kThreads) {

@@ -25,6 +25,7 @@ struct GemvParams {
   int rows, K, N;      // N = weight rows
   float alpha;
   int bias_mode, gate_mode;
+  int dependent_launch;  // launched with programmatic stream serialisation: see the kernel
 };
 
 template <bool kFp8>
@@ -103,6 +104,20 @@ gemv_kernel(const GemvParams p) {
   const std::size_t row_bytes = static_cast<std::size_t>(p.K) * (kFp8 ? 1 : 2);
   const unsigned char *const wb = static_cast<const unsigned char *>(p.w);
   const unsigned char *const xb = static_cast<const unsigned char *>(p.x);
+  // Programmatic dependent launch (one-row steps inside the captured decode graph): this grid may be
+  // started while the kernel that produces x is still running.  The weights do not depend on that
+  // kernel, so the CTA first asks L2 for its weight rows, lets the grid after it start as well, and only
+  // then waits for the producer to finish and its writes to be visible.  Without such a launch the two
+  // instructions do nothing.
+  if (p.dependent_launch != 0) {
+    for (int chunk = threadIdx.x * 8; chunk < chunks; chunk += kThreads * 8) {  // one request per 128-byte line
+#pragma unroll
+      for (int c = 0; c < kColumns; ++c)
+        asm volatile("prefetch.global.L2 [%0];" ::"l"(wb + weight_row[c] * row_bytes + static_cast<std::size_t>(chunk) * 16));
+    }
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+  }
 #pragma unroll(kRows == 1 ? 4 : (kRows == 2 ? 2 : 1))
   for (int chunk = threadIdx.x; chunk < chunks; chunk += kThreads) {
     uint4 wraw[kColumns];
@@ -173,7 +188,20 @@ int launch_gemv(const GemvParams &p, cudaStream_t stream) {
   const int out_columns = p.gate_mode != 0 ? p.N / 2 : p.N;
   const int per_cta = p.gate_mode != 0 ? kColumnsPerCta / 2 : kColumnsPerCta;
   const unsigned int grid = static_cast<unsigned int>((out_columns + per_cta - 1) / per_cta);
-  if (p.rows == 1)
+  if (p.rows == 1 && p.dependent_launch != 0) {
+    cudaLaunchAttribute attribute{};
+    attribute.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attribute.val.programmaticStreamSerializationAllowed = 1;
+    cudaLaunchConfig_t config{};
+    config.gridDim = dim3(grid);
+    config.blockDim = dim3(kThreads);
+    config.dynamicSmemBytes = 0;
+    config.stream = stream;
+    config.attrs = &attribute;
+    config.numAttrs = 1;
+    if (cudaLaunchKernelEx(&config, gemv_kernel<kFp8, 1, kColumnsPerCta>, p) != cudaSuccess)
+      return fail(kCuda, "cannot launch the small-batch projection kernel");
+  } else if (p.rows == 1)
     gemv_kernel<kFp8, 1, kColumnsPerCta><<<grid, kThreads, 0, stream>>>(p);
   else if (p.rows <= 2)
     gemv_kernel<kFp8, 2, kColumnsPerCta><<<grid, kThreads, 0, stream>>>(p);
@@ -210,6 +238,7 @@ int small_batch_linear(const LinearArgs &a, cudaStream_t stream) {
   p.alpha = a.alpha;
   p.bias_mode = a.bias_mode;
   p.gate_mode = a.gate_mode;
+  p.dependent_launch = a.dependent_launch && a.rows == 1 ? 1 : 0;
   return a.operand_type == OperandType::kE4m3 ? launch_gemv<true>(p, stream)
                                               : launch_gemv<false>(p, stream);
 }

@@ -40,6 +40,9 @@ __device__ __forceinline__ float filter_tap(const void *filter, const bool is_f3
 template <bool kModal>
 __global__ void __launch_bounds__(kThreads)
 mixer_decode_kernel(const Params p) {
+  // lets a one-row projection launched with programmatic stream serialisation start (and fetch its
+  // weights) under this kernel; it still waits for this grid to finish before it reads the result
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const int channel = (blockIdx.x * kThreads + threadIdx.x) / 32;
   const int lane = threadIdx.x % 32;
   if (channel >= p.width) return;

@@ -409,6 +409,7 @@ int Context::decode_step_graph(const std::uint32_t *host_token, bool *launched) 
       LinearArgs a;
       a.split_workspace = first.split_workspace;
       a.split_workspace_bytes = kSplitWorkspaceBytes;
+      a.dependent_launch = decode_dependent_launch_ && true;
       a.input = first.normalized;
       a.weight = first.weights->embedding;  // tied head
       a.output = first.logits;
@@ -553,6 +554,8 @@ int Context::create(std::shared_ptr<ModelWeights> weights, const std::size_t con
     context->device_position_ = static_cast<int *>(p);
     const char *const graphs = std::getenv("EVO_B200_DECODE_GRAPH");
     context->decode_graph_allowed_ = (graphs == nullptr || std::string(graphs) != "0") && !q8_kv;
+    const char *const dependent = std::getenv("EVO_B200_DECODE_PDL");
+    context->decode_dependent_launch_ = dependent == nullptr || std::string(dependent) != "0";
   }
   // Direct peer copies between neighbouring stages (and last -> first for the
   // head); without peer access the copies still work, staged by the driver.
@@ -684,6 +687,7 @@ int Context::run_stage(Stage &s, const std::size_t rows, const Mode mode,
       LinearArgs a;
       a.split_workspace = s.split_workspace;
       a.split_workspace_bytes = kSplitWorkspaceBytes;
+      a.dependent_launch = decode_dependent_launch_ && rows == 1;
       a.input = fp8 ? s.codes : s.normalized;
       a.weight = w.projection;
       a.output = s.projection;
@@ -892,6 +896,7 @@ int Context::run_stage(Stage &s, const std::size_t rows, const Mode mode,
       LinearArgs a;
       a.split_workspace = s.split_workspace;
       a.split_workspace_bytes = kSplitWorkspaceBytes;
+      a.dependent_launch = decode_dependent_launch_ && rows == 1;
       a.input = s.mixer_out;
       a.weight = w.out_weight;
       a.bias = w.out_bias;
@@ -933,6 +938,7 @@ int Context::run_stage(Stage &s, const std::size_t rows, const Mode mode,
       LinearArgs a;
       a.split_workspace = s.split_workspace;
       a.split_workspace_bytes = kSplitWorkspaceBytes;
+      a.dependent_launch = decode_dependent_launch_ && rows == 1;
       a.input = s.normalized;
       a.weight = w.l12;
       a.output = s.gated;
@@ -973,6 +979,7 @@ int Context::run_stage(Stage &s, const std::size_t rows, const Mode mode,
       LinearArgs a;
       a.split_workspace = s.split_workspace;
       a.split_workspace_bytes = kSplitWorkspaceBytes;
+      a.dependent_launch = decode_dependent_launch_ && rows == 1;
       a.input = s.gated;
       a.weight = w.l3;
       a.residual = s.residual;
@@ -1148,6 +1155,7 @@ int Context::forward(const std::uint32_t *host_tokens, const std::uint32_t *devi
       LinearArgs a;
       a.split_workspace = first.split_workspace;
       a.split_workspace_bytes = kSplitWorkspaceBytes;
+      a.dependent_launch = decode_dependent_launch_ && rows == 1;
       a.input = first.normalized;
       a.weight = first.weights->embedding;  // tied head
       a.output = first.logits;

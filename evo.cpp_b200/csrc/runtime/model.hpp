@@ -253,6 +253,8 @@ class Context {
   const int *dynamic_position_ = nullptr; // == device_position_ while the graph is being recorded
   int decode_position_host_ = 0;
   bool decode_graph_allowed_ = true;
+  // one-row projections are launched with programmatic stream serialisation (EVO_B200_DECODE_PDL=0: plain launches)
+  bool decode_dependent_launch_ = true;
 
   std::shared_ptr<ModelWeights> weights_;
   std::vector<std::unique_ptr<Stage>> stages_;

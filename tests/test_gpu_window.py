@@ -165,6 +165,33 @@ def test_decode_graph_replay_is_bit_identical(pkg, tmp_path_factory, monkeypatch
         assert plain.position == replayed.position == 312
 
 
+def test_decode_with_dependent_launches_is_bit_identical(pkg, tmp_path_factory, monkeypatch):
+    """One-row projections start under the kernel in front of them (programmatic stream
+    serialisation: they pull their weights into L2, then wait for that kernel before reading its
+    output).  Same logits, bit for bit, as plain launches - in the captured graph and without it."""
+    rt = importlib.import_module("evo_cpp_b200.runtime")
+    art = importlib.import_module("evo_cpp_b200.artifact")
+    evo = rt.EvoLibrary(pkg.EVO_LIBRARY)
+    directory = tmp_path_factory.mktemp("pdl")
+    spec = art.fixture_spec(width=256, layers=8, heads=2, inner=512, hcs_groups=16, hcm_groups=16, fp8=True)
+    art.write_synthetic(directory / "model.safetensors", spec, seed=31, weight_std=0.05, filter_std=0.3)
+    model = evo.load(directory / "model.safetensors", devices=[0], flags=rt.MODEL_FLAG_ALLOW_SYNTHETIC)
+    prompt = bytes(np.random.default_rng(8).choice(np.frombuffer(b"ACGT", np.uint8), 150).tolist())
+    flags = rt.CONTEXT_FLAG_FULL_ARENA | rt.CONTEXT_FLAG_TENSORCORE_FP8
+    for graph in ("1", "0"):
+        monkeypatch.setenv("EVO_B200_DECODE_GRAPH", graph)
+        monkeypatch.setenv("EVO_B200_DECODE_PDL", "0")
+        plain = model.context(1024, flags)
+        monkeypatch.delenv("EVO_B200_DECODE_PDL")
+        dependent = model.context(1024, flags)
+        token = int(plain.prefill(prompt)[-1].argmax())
+        assert int(dependent.prefill(prompt)[-1].argmax()) == token
+        for _ in range(16):
+            a, b = plain.decode(token), dependent.decode(token)
+            assert np.array_equal(a, b)
+            token = int(a.argmax())
+
+
 def test_continuation_after_decode_steps_uses_current_state(pkg, tmp_path_factory):
     """prefill -> a few decode steps -> a 100-row continuation chunk: the decode steps do not
     update the fused kernels' carried projection history, so the chunk must fall back to the step
