@@ -193,6 +193,48 @@ def test_projection_fed_hcm_on_tensor_cores_ragged_shapes(ops, oracle, length, w
     assert np.array_equal(short_cache.cpu().numpy(), expected_short_cache)
 
 
+def test_projection_fed_hcm_gives_the_same_bits_on_concurrent_streams(ops):
+    """The tcgen05 Toeplitz kernel hands tiles between its warps with mbarriers only; with several
+    launches sharing the SMs its warps drift apart.  Six threads on six streams, every result equal to
+    the one computed alone."""
+    import threading
+
+    rng = np.random.default_rng(41)
+    width, groups, taps = 256, 16, 128
+    jobs = []
+    for length in (243, 130, 361, 517, 64, 205):
+        tensors = [dev_bits(rand_bf16(rng, length, 3 * width)), dev_bits(rand_bf16(rng, 3 * width, 3, scale=0.5)),
+                   dev_bits(rand_bf16(rng, groups, taps, scale=0.2)), dev_bits(rand_bf16(rng, width))]
+        alone = empty_bits(length, width)
+        ops.call("bf16_projection_gated_fir_prefill", p(tensors[0]), p(tensors[1]), p(tensors[2]), 0, p(tensors[3]),
+                 length, width, groups, taps, 1, None, None, None, p(alone), stream())
+        jobs.append((length, tensors, alone))
+    torch.cuda.synchronize()
+    failures = []
+
+    def worker(job):
+        length, tensors, alone = job
+        own = torch.cuda.Stream()
+        with torch.cuda.stream(own):
+            out = empty_bits(length, width)
+            for iteration in range(300):
+                out.zero_()
+                ops.call("bf16_projection_gated_fir_prefill", p(tensors[0]), p(tensors[1]), p(tensors[2]), 0,
+                         p(tensors[3]), length, width, groups, taps, 1, None, None, None, p(out), own.cuda_stream)
+                own.synchronize()
+                if not torch.equal(out, alone):
+                    failures.append((length, iteration))
+                    return
+
+    threads = [threading.Thread(target=worker, args=(job,)) for job in jobs]
+    for thread in threads:
+        thread.start()
+    for thread in threads:
+        thread.join()
+    ops.call("check_async_errors", stream())
+    assert not failures, failures
+
+
 def _modal_params(rng, width, modes):
     radius = rng.uniform(0.9, 0.999, (width, modes))
     log_poles = np.log(radius).astype(np.float32)
