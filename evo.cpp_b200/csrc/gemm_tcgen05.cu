@@ -1,6 +1,9 @@
 // Dense projections y = x . W^T on the 5th-generation tensor cores.
 //
-// One persistent CTA per SM walks 128 x BN output tiles.  Warp roles:
+// Large projections (at least 74 tiles of 256 x 256) run on CTA pairs: gemm_tcgen05_pair_kernel, two
+// CTAs of a cluster on one 256 x 256 tile with tcgen05.mma.cta_group::2 (see there).  Everything else,
+// and every shape when EVO_B200_GEMM_PAIR=0, runs on gemm_tcgen05_kernel:
+// one persistent CTA per SM walks 128 x BN output tiles.  Warp roles:
 //   warp 0   TMA producer: streams 128B-swizzled K-major tiles of x [M,K] and
 //            W [N,K] into a 4-deep shared-memory ring (mbarrier full/empty).
 //   warp 1   MMA issuer: one lane issues tcgen05.mma (M=128, N=BN, K=32 bytes
@@ -21,6 +24,8 @@
 // (src/cuda/ops.cu:916-1006).
 #include <cuda.h>
 
+#include <algorithm>
+#include <cstdlib>
 #include <mutex>
 #include <type_traits>
 
@@ -103,6 +108,101 @@ __device__ __forceinline__ void tile_coordinates(const int tile, const int tiles
   const int local = tile - band * per_band;
   *tile_m = first + local % rows;
   *tile_n = local / rows;
+}
+
+// One warp's share of a finished 128 x BN accumulator (TMEM lane quarter `quarter` of the tile that
+// starts at column address tmem_tile): scale, bias, gate, residual and the BF16 rounding points of the
+// upstream graph, or the F32 / split-K forms.  Rows m0 .., columns n0 .. of the output.
+template <int BN>
+__device__ __forceinline__ void epilogue_tile(const EpilogueParams &ep, const int M, const int N, const int m0,
+                                              const int n0, const int split, const std::uint32_t tmem_tile,
+                                              const int quarter, const int lane) {
+  const int row = m0 + quarter * 32 + lane;
+  const float scale = ep.row_scale != nullptr && row < M ? ep.alpha * ep.row_scale[row] : ep.alpha;
+  const std::uint32_t taddr = tmem_tile + (static_cast<std::uint32_t>(quarter * 32) << 16U);
+  const bool gated = ep.gate_mode != 0;
+  const int chunks = gated ? BN / 64 : BN / 32;
+  for (int c = 0; c < chunks; ++c) {
+    std::uint32_t v[32];
+    std::uint32_t w[32];
+    tmem_load_32(taddr + c * 32, v);
+    if (gated) tmem_load_32(taddr + BN / 2 + c * 32, w);
+    tmem_load_wait();
+    const int col = gated ? n0 / 2 + c * 32 : n0 + c * 32;
+    const int n_limit = gated ? N / 2 : N;
+    if (ep.out_f32 != nullptr) {
+      if (row < M && col < n_limit) {
+        float *const out_row = ep.out_f32 + static_cast<std::size_t>(split) * ep.partial_stride +
+                               static_cast<std::size_t>(row) * ep.ld_out;
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          if (col + j < n_limit) {
+            float value = __uint_as_float(v[j]) * scale;
+            if (ep.bias_f32 != nullptr) value += ep.bias_f32[col + j];
+            if (ep.accumulate_f32 != 0) value += out_row[col + j];
+            out_row[col + j] = value;
+          }
+        }
+      }
+      continue;
+    }
+    if (row < M && col < n_limit) {
+      bf16 *const out_row = ep.out + static_cast<std::size_t>(row) * ep.ld_out;
+      float r[32];
+#pragma unroll
+      for (int j = 0; j < 32; ++j) {
+        float value = __uint_as_float(v[j]) * scale;
+        if (gated) {
+          const float first =
+              ep.gate_mode == 2 ? bf2f(gelu_round(value)) : rbf(value);
+          const float second = rbf(__uint_as_float(w[j]) * scale);
+          r[j] = rbf(first * second);
+        } else {
+          if (ep.bias_mode == 1 && col + j < n_limit)
+            value += bf2f(ep.bias[col + j]);
+          value = rbf(value);
+          if (ep.bias_mode == 2 && col + j < n_limit)
+            value = rbf(value + bf2f(ep.bias[col + j]));
+          r[j] = value;
+        }
+      }
+      const bool vector_ok =
+          col + 32 <= n_limit && (ep.ld_out % 8) == 0 &&
+          (reinterpret_cast<std::uintptr_t>(ep.out) & 15U) == 0;
+      if (ep.residual != nullptr) {
+        const bf16 *const res_row =
+            ep.residual + static_cast<std::size_t>(row) * ep.ld_out;
+        if (vector_ok &&
+            (reinterpret_cast<std::uintptr_t>(ep.residual) & 15U) == 0) {
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            Bf16x8 packed;
+            packed.raw = *reinterpret_cast<const uint4 *>(res_row + col + q * 8);
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+              r[q * 8 + j] = rbf(r[q * 8 + j] + packed.get(j));
+          }
+        } else {
+          for (int j = 0; j < 32; ++j)
+            if (col + j < n_limit) r[j] = rbf(r[j] + bf2f(res_row[col + j]));
+        }
+      }
+      if (vector_ok) {
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const uint4 packed = make_uint4(
+              pack_bf16x2(r[q * 8 + 0], r[q * 8 + 1]),
+              pack_bf16x2(r[q * 8 + 2], r[q * 8 + 3]),
+              pack_bf16x2(r[q * 8 + 4], r[q * 8 + 5]),
+              pack_bf16x2(r[q * 8 + 6], r[q * 8 + 7]));
+          *reinterpret_cast<uint4 *>(out_row + col + q * 8) = packed;
+        }
+      } else {
+        for (int j = 0; j < 32; ++j)
+          if (col + j < n_limit) out_row[col + j] = f2bf(r[j]);
+      }
+    }
+  }
 }
 
 template <int BN>
@@ -263,93 +363,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
       const std::uint32_t acc_phase = (local >> 1) & 1U;
       if (!mbar_wait(tmem_full_bar(acc), acc_phase, abort_flag)) break;
       tc_fence_after();
-      const int row = m0 + quarter * 32 + lane;
-      const float scale = ep.row_scale != nullptr && row < M ? ep.alpha * ep.row_scale[row] : ep.alpha;
-      const std::uint32_t taddr =
-          tmem_base + acc * BN + (static_cast<std::uint32_t>(quarter * 32) << 16U);
-      const bool gated = ep.gate_mode != 0;
-      const int chunks = gated ? BN / 64 : BN / 32;
-      for (int c = 0; c < chunks; ++c) {
-        std::uint32_t v[32];
-        std::uint32_t w[32];
-        tmem_load_32(taddr + c * 32, v);
-        if (gated) tmem_load_32(taddr + BN / 2 + c * 32, w);
-        tmem_load_wait();
-        const int col = gated ? n0 / 2 + c * 32 : n0 + c * 32;
-        const int n_limit = gated ? N / 2 : N;
-        if (ep.out_f32 != nullptr) {
-          if (row < M && col < n_limit) {
-            float *const out_row = ep.out_f32 + static_cast<std::size_t>(split) * ep.partial_stride +
-                                   static_cast<std::size_t>(row) * ep.ld_out;
-#pragma unroll
-            for (int j = 0; j < 32; ++j) {
-              if (col + j < n_limit) {
-                float value = __uint_as_float(v[j]) * scale;
-                if (ep.bias_f32 != nullptr) value += ep.bias_f32[col + j];
-                if (ep.accumulate_f32 != 0) value += out_row[col + j];
-                out_row[col + j] = value;
-              }
-            }
-          }
-          continue;
-        }
-        if (row < M && col < n_limit) {
-          bf16 *const out_row = ep.out + static_cast<std::size_t>(row) * ep.ld_out;
-          float r[32];
-#pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            float value = __uint_as_float(v[j]) * scale;
-            if (gated) {
-              const float first =
-                  ep.gate_mode == 2 ? bf2f(gelu_round(value)) : rbf(value);
-              const float second = rbf(__uint_as_float(w[j]) * scale);
-              r[j] = rbf(first * second);
-            } else {
-              if (ep.bias_mode == 1 && col + j < n_limit)
-                value += bf2f(ep.bias[col + j]);
-              value = rbf(value);
-              if (ep.bias_mode == 2 && col + j < n_limit)
-                value = rbf(value + bf2f(ep.bias[col + j]));
-              r[j] = value;
-            }
-          }
-          const bool vector_ok =
-              col + 32 <= n_limit && (ep.ld_out % 8) == 0 &&
-              (reinterpret_cast<std::uintptr_t>(ep.out) & 15U) == 0;
-          if (ep.residual != nullptr) {
-            const bf16 *const res_row =
-                ep.residual + static_cast<std::size_t>(row) * ep.ld_out;
-            if (vector_ok &&
-                (reinterpret_cast<std::uintptr_t>(ep.residual) & 15U) == 0) {
-#pragma unroll
-              for (int q = 0; q < 4; ++q) {
-                Bf16x8 packed;
-                packed.raw = *reinterpret_cast<const uint4 *>(res_row + col + q * 8);
-#pragma unroll
-                for (int j = 0; j < 8; ++j)
-                  r[q * 8 + j] = rbf(r[q * 8 + j] + packed.get(j));
-              }
-            } else {
-              for (int j = 0; j < 32; ++j)
-                if (col + j < n_limit) r[j] = rbf(r[j] + bf2f(res_row[col + j]));
-            }
-          }
-          if (vector_ok) {
-#pragma unroll
-            for (int q = 0; q < 4; ++q) {
-              const uint4 packed = make_uint4(
-                  pack_bf16x2(r[q * 8 + 0], r[q * 8 + 1]),
-                  pack_bf16x2(r[q * 8 + 2], r[q * 8 + 3]),
-                  pack_bf16x2(r[q * 8 + 4], r[q * 8 + 5]),
-                  pack_bf16x2(r[q * 8 + 6], r[q * 8 + 7]));
-              *reinterpret_cast<uint4 *>(out_row + col + q * 8) = packed;
-            }
-          } else {
-            for (int j = 0; j < 32; ++j)
-              if (col + j < n_limit) out_row[col + j] = f2bf(r[j]);
-          }
-        }
-      }
+      epilogue_tile<BN>(ep, M, N, m0, n0, split, tmem_base + acc * BN, quarter, lane);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(tmem_empty_bar(acc));
@@ -371,6 +385,252 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(
                      tmem_base),
                  "r"(kTmemColumns)
+                 : "memory");
+  }
+}
+
+// ------------------------------------------------------- CTA pairs (cta_group::2)
+// The same projection with two CTAs of a cluster on one 256 x 256 output tile.  Each CTA loads its own
+// 128 rows of A and its own 128 of the tile's 256 weight rows (TMA without multicast; the copies report
+// to the leader's mbarrier), the leader issues tcgen05.mma.cta_group::2 (M = 256, N = 256), and each CTA
+// ends up with its 128 rows x 256 columns of the accumulator in its own tensor memory and stores them as
+// the one-CTA kernel does.  Per SM a stage is 32 KiB instead of 48 for the same arithmetic: a third
+// less traffic from L2, and six stages in flight instead of four.
+constexpr int kPairStages = 6;
+constexpr int kPairN = 256;
+
+struct PairLayout {
+  static constexpr int kABytes = kBlockM * kBlockKBytes;  // 128 rows of A
+  static constexpr int kBBytes = 128 * kBlockKBytes;       // this CTA's 128 weight rows of the tile
+  static constexpr int kStageBytes = kABytes + kBBytes;
+  static constexpr int kBarrierOffset = kPairStages * kStageBytes;
+  // full[kPairStages], empty[kPairStages], tmem_full[2], tmem_empty[2]
+  static constexpr int kBarrierCount = 2 * kPairStages + 4;
+  static constexpr int kTmemPtrOffset = kBarrierOffset + kBarrierCount * 8;
+  static constexpr int kAbortOffset = kTmemPtrOffset + 8;
+  static constexpr int kTotal = kAbortOffset + 8 + 1024;  // + alignment slack
+};
+
+__device__ __forceinline__ std::uint32_t cluster_rank() {
+  std::uint32_t rank;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
+  return rank;
+}
+// shared::cluster address of `address` (a shared::cta address of this CTA) in CTA `rank` of the cluster
+__device__ __forceinline__ std::uint32_t map_to_cta(const std::uint32_t address, const std::uint32_t rank) {
+  std::uint32_t mapped;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(mapped) : "r"(address), "r"(rank));
+  return mapped;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// 2-D tile load of a CTA pair: lands in this CTA's shared memory, reports its bytes to `bar`, a
+// shared::cluster address that may belong to the other CTA of the pair.  No multicast.
+__device__ __forceinline__ void tma_load_2d_pair(const std::uint32_t dst, const CUtensorMap *const map,
+                                                 const std::uint32_t bar, const int x, const int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes "
+      "[%0], [%1, {%3, %4}], [%2];" ::"r"(dst),
+      "l"(reinterpret_cast<std::uint64_t>(map)), "r"(bar), "r"(x), "r"(y)
+      : "memory");
+}
+template <bool kFp8>
+__device__ __forceinline__ void tc_mma_pair(const std::uint32_t tmem_d, const std::uint64_t desc_a,
+                                            const std::uint64_t desc_b, const std::uint32_t idesc,
+                                            const std::uint32_t accumulate) {
+  if constexpr (kFp8) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
+        "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+        : "memory");
+  } else {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
+        "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+        : "memory");
+  }
+}
+// arrives on the mbarrier at this shared::cta offset in both CTAs of the pair once the MMAs issued so far
+// have finished (the multicast is of the arrival, not of a load)
+__device__ __forceinline__ void tc_commit_pair(const std::uint32_t bar) {
+  asm volatile(
+      "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(bar),
+      "h"(static_cast<unsigned short>(3))
+      : "memory");
+}
+
+template <bool kFp8>
+__host__ __device__ constexpr std::uint32_t pair_instruction_descriptor() {
+  std::uint32_t d = 0;
+  d |= 1U << 4U;                          // accumulator F32
+  d |= (kFp8 ? 0U : 1U) << 7U;            // A: E4M3 / BF16
+  d |= (kFp8 ? 0U : 1U) << 10U;           // B: E4M3 / BF16
+  d |= static_cast<std::uint32_t>(kPairN >> 3) << 17U;
+  d |= static_cast<std::uint32_t>(256 >> 4) << 24U;  // M = 256 over the pair
+  return d;
+}
+
+template <bool kFp8>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
+gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                         const EpilogueParams ep, const int M, const int N, const int K_bytes,
+                         int *const error_word) {
+  using L = PairLayout;
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char *const smem = smem_raw + ((1024U - (smem_u32(smem_raw) & 1023U)) & 1023U);
+  const std::uint32_t smem_base = smem_u32(smem);
+  const std::uint32_t bar_base = smem_base + L::kBarrierOffset;
+  auto full_bar = [&](const int s) { return bar_base + 8U * s; };
+  auto empty_bar = [&](const int s) { return bar_base + 8U * (kPairStages + s); };
+  auto tmem_full_bar = [&](const int s) { return bar_base + 8U * (2 * kPairStages + s); };
+  auto tmem_empty_bar = [&](const int s) { return bar_base + 8U * (2 * kPairStages + 2 + s); };
+  volatile std::uint32_t *const tmem_ptr = reinterpret_cast<volatile std::uint32_t *>(smem + L::kTmemPtrOffset);
+  volatile int *const abort_flag = reinterpret_cast<volatile int *>(smem + L::kAbortOffset);
+  const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+  const std::uint32_t rank = cluster_rank();  // 0: the leader (issues the MMAs, owns the full barriers)
+  constexpr std::uint32_t kTmemColumns = 2 * kPairN;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kPairStages; ++s) {
+      mbar_init(full_bar(s), 1);   // the leader's: its expect_tx arrival + both CTAs' bytes
+      mbar_init(empty_bar(s), 1);  // each CTA's own, signalled by the pair commit
+    }
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(tmem_full_bar(s), 1);
+      mbar_init(tmem_empty_bar(s), 8);  // the leader's: four epilogue warps of each CTA
+    }
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                     smem_u32(const_cast<std::uint32_t *>(tmem_ptr))),
+                 "r"(kTmemColumns)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();  // both CTAs' barriers exist before anything is signalled across the pair
+  tc_fence_after();
+  const std::uint32_t tmem_base = *tmem_ptr;
+
+  const int tiles_m = (M + 255) / 256;
+  const int tiles_n = (N + kPairN - 1) / kPairN;
+  const int splits = ep.split_k > 1 ? ep.split_k : 1;
+  const int tiles_mn = tiles_m * tiles_n;
+  const int tiles = tiles_mn * splits;
+  const int k_blocks = (K_bytes + kBlockKBytes - 1) / kBlockKBytes;
+  const int k_per_split = k_blocks / splits;
+  const int pair = static_cast<int>(blockIdx.x / 2), pairs = static_cast<int>(gridDim.x / 2);
+
+  if (warp == 0) {
+    if (lane == 0) {
+      int stage = 0;
+      std::uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = pair; tile < tiles && ok; tile += pairs) {
+        int tile_m, tile_n;
+        tile_coordinates(tile % tiles_mn, tiles_m, tiles_n, &tile_m, &tile_n);
+        const int m0 = tile_m * 256 + static_cast<int>(rank) * 128;
+        const int n0 = tile_n * kPairN + static_cast<int>(rank) * 128;
+        const int kb_begin = (tile / tiles_mn) * k_per_split;
+        for (int kb = kb_begin; kb < kb_begin + k_per_split; ++kb) {
+          if (!mbar_wait(empty_bar(stage), phase ^ 1U, abort_flag)) {
+            ok = false;
+            break;
+          }
+          const std::uint32_t a_dst = smem_base + stage * L::kStageBytes;
+          const std::uint32_t b_dst = a_dst + L::kABytes;
+          if (rank == 0) mbar_expect_tx(full_bar(stage), 2 * L::kStageBytes);
+          const std::uint32_t leader_full = map_to_cta(full_bar(stage), 0);
+          const int k_elem = kFp8 ? kb * kBlockKBytes : kb * (kBlockKBytes / 2);
+          const int kb_b = ep.weight_wrap_blocks > 0 ? kb % ep.weight_wrap_blocks : kb;
+          const int k_elem_b = kFp8 ? kb_b * kBlockKBytes : kb_b * (kBlockKBytes / 2);
+          tma_load_2d_pair(a_dst, &map_a, leader_full, k_elem, m0);
+          tma_load_2d_pair(b_dst, &map_b, leader_full, k_elem_b, n0);
+          if (++stage == kPairStages) {
+            stage = 0;
+            phase ^= 1U;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0 && rank == 0) {
+      constexpr std::uint32_t idesc = pair_instruction_descriptor<kFp8>();
+      int stage = 0;
+      std::uint32_t phase = 0;
+      int local = 0;
+      bool ok = true;
+      for (int tile = pair; tile < tiles && ok; tile += pairs, ++local) {
+        const int acc = local & 1;
+        const std::uint32_t acc_phase = (local >> 1) & 1U;
+        if (!mbar_wait(tmem_empty_bar(acc), acc_phase ^ 1U, abort_flag)) break;
+        tc_fence_after();
+        const std::uint32_t tmem_d = tmem_base + acc * kPairN;
+        for (int kb = 0; kb < k_per_split; ++kb) {
+          if (!mbar_wait(full_bar(stage), phase, abort_flag)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const std::uint32_t a_addr = smem_base + stage * L::kStageBytes;
+          const std::uint64_t a_desc = smem_descriptor(a_addr);
+          const std::uint64_t b_desc = smem_descriptor(a_addr + L::kABytes);
+#pragma unroll
+          for (int k = 0; k < kBlockKBytes / 32; ++k)
+            tc_mma_pair<kFp8>(tmem_d, a_desc + 2U * k, b_desc + 2U * k, idesc, (kb | k) != 0 ? 1U : 0U);
+          tc_commit_pair(empty_bar(stage));  // the slot is free in both CTAs
+          if (++stage == kPairStages) {
+            stage = 0;
+            phase ^= 1U;
+          }
+        }
+        if (ok) tc_commit_pair(tmem_full_bar(acc));
+      }
+    }
+  } else {
+    const int quarter = warp % 4;
+    int local = 0;
+    for (int tile = pair; tile < tiles; tile += pairs, ++local) {
+      int tile_m, tile_n;
+      tile_coordinates(tile % tiles_mn, tiles_m, tiles_n, &tile_m, &tile_n);
+      const int m0 = tile_m * 256 + static_cast<int>(rank) * 128;
+      const int n0 = tile_n * kPairN;
+      const int split = tile / tiles_mn;
+      const int acc = local & 1;
+      const std::uint32_t acc_phase = (local >> 1) & 1U;
+      if (!mbar_wait(tmem_full_bar(acc), acc_phase, abort_flag)) break;
+      tc_fence_after();
+      epilogue_tile<kPairN>(ep, M, N, m0, n0, split, tmem_base + acc * kPairN, quarter, lane);
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) {
+        const std::uint32_t leader_empty = map_to_cta(tmem_empty_bar(acc), 0);
+        asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(leader_empty) : "memory");
+      }
+    }
+  }
+
+  __syncwarp();
+  tc_fence_before();
+  __syncthreads();
+  if (*abort_flag != 0) {
+    const unsigned long long start = global_timer_ns();
+    while (global_timer_ns() - start < 200000ULL) __nanosleep(1000);
+    if (threadIdx.x == 0) atomicOr(error_word, 1 | 32);  // bit 5: a projection kernel
+  }
+  // neither CTA leaves while the other may still read its shared memory or signal its barriers
+  cluster_sync_all();
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemColumns)
                  : "memory");
   }
 }
@@ -736,6 +996,36 @@ int launch_tc(const void *a, const void *b, const EpilogueParams &ep,
   return check_launch("tcgen05 GEMM kernel");
 }
 
+template <bool kFp8>
+int launch_tc_pair(const void *a, const void *b, const EpilogueParams &ep, const std::size_t M, const std::size_t N,
+                   const std::size_t K, cudaStream_t stream) {
+  const std::size_t weight_k = ep.weight_wrap_blocks > 0 ? static_cast<std::size_t>(ep.weight_wrap_blocks) * 64 : K;
+  int status = kOk;
+  DeviceState *const state = device_state(&status);
+  if (state == nullptr) return status;
+  CUtensorMap map_a, map_b;
+  status = make_map(&map_a, a, kFp8, M, K, kBlockM);
+  if (status != kOk) return status;
+  status = make_map(&map_b, b, kFp8, N, weight_k, 128);  // a CTA loads its 128 of the tile's 256 weight rows
+  if (status != kOk) return status;
+  static bool configured[64] = {};
+  int device = 0;
+  cudaGetDevice(&device);
+  if (!configured[device]) {
+    if (cudaFuncSetAttribute(gemm_tcgen05_pair_kernel<kFp8>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             PairLayout::kTotal) != cudaSuccess)
+      return fail(kCuda, "cannot raise the GEMM shared-memory limit");
+    configured[device] = true;
+  }
+  const std::size_t tiles =
+      ((M + 255) / 256) * ((N + kPairN - 1) / kPairN) * static_cast<std::size_t>(ep.split_k > 1 ? ep.split_k : 1);
+  const std::size_t pairs = std::min<std::size_t>(tiles, static_cast<std::size_t>(state->sm_count) / 2);
+  gemm_tcgen05_pair_kernel<kFp8><<<static_cast<unsigned int>(2 * pairs), kGemmThreads, PairLayout::kTotal, stream>>>(
+      map_a, map_b, ep, static_cast<int>(M), static_cast<int>(N), static_cast<int>(K * (kFp8 ? 1 : 2)),
+      state->error_word);
+  return check_launch("tcgen05 GEMM kernel (CTA pairs)");
+}
+
 template <bool kFp8, int BT>
 int launch_swap(const void *x, const void *w, float *partials, const std::size_t M, const std::size_t N,
                 const std::size_t K, const int split, cudaStream_t stream) {
@@ -940,11 +1230,21 @@ int linear(const LinearArgs &args, cudaStream_t stream) {
     }
   }
   if (tma_ok) {
+    if (args.gate_mode != 0 && args.out_features % 256 != 0)
+      return fail(kInvalidArgument, "gated linear needs the interleaved width to be a multiple of 256");
+    // CTA pairs on 256 x 256 tiles where there are enough of them to fill the pairs of the GPU
+    // (EVO_B200_GEMM_PAIR=0: one CTA per 128 x 256 tile everywhere)
+    static const bool pairs_enabled = [] {
+      const char *const flag = std::getenv("EVO_B200_GEMM_PAIR");
+      return flag == nullptr || flag[0] != '0';
+    }();
+    if (pairs_enabled && ep.weight_wrap_blocks == 0 &&
+        ((args.rows + 255) / 256) * ((args.out_features + 255) / 256) >= 74)
+      return fp8 ? launch_tc_pair<true>(args.input, args.weight, ep, args.rows, args.out_features, args.in_features,
+                                        stream)
+                 : launch_tc_pair<false>(args.input, args.weight, ep, args.rows, args.out_features,
+                                         args.in_features, stream);
     if (args.gate_mode != 0) {
-      if (args.out_features % 256 != 0)
-        return fail(kInvalidArgument,
-                    "gated linear needs the interleaved width to be a "
-                    "multiple of 256");
       return fp8 ? launch_tc<true, 256>(args.input, args.weight, ep, args.rows,
                                         args.out_features, args.in_features,
                                         stream)
