@@ -1238,7 +1238,8 @@ int linear(const LinearArgs &args, cudaStream_t stream) {
       const char *const flag = std::getenv("EVO_B200_GEMM_PAIR");
       return flag == nullptr || flag[0] != '0';
     }();
-    if (pairs_enabled && ep.weight_wrap_blocks == 0 &&
+    // (not below 512 rows: a pair's tile is 256 rows, and at 128 rows half of every pair would idle)
+    if (pairs_enabled && ep.weight_wrap_blocks == 0 && args.rows >= 512 &&
         ((args.rows + 255) / 256) * ((args.out_features + 255) / 256) >= 74)
       return fp8 ? launch_tc_pair<true>(args.input, args.weight, ep, args.rows, args.out_features, args.in_features,
                                         stream)
