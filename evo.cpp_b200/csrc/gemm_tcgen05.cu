@@ -1,6 +1,6 @@
 // Dense projections y = x . W^T on the 5th-generation tensor cores.
 //
-// Large projections (at least 74 tiles of 256 x 256) run on CTA pairs: gemm_tcgen05_pair_kernel, two
+// Large projections (512 rows and 48 tiles of 256 x 256 or more) run on CTA pairs: gemm_tcgen05_pair_kernel, two
 // CTAs of a cluster on one 256 x 256 tile with tcgen05.mma.cta_group::2 (see there).  Everything else,
 // and every shape when EVO_B200_GEMM_PAIR=0, runs on gemm_tcgen05_kernel:
 // one persistent CTA per SM walks 128 x BN output tiles.  Warp roles:
@@ -1239,8 +1239,15 @@ int linear(const LinearArgs &args, cudaStream_t stream) {
       return flag == nullptr || flag[0] != '0';
     }();
     // (not below 512 rows: a pair's tile is 256 rows, and at 128 rows half of every pair would idle)
+    static const std::size_t pair_tiles = [] {
+      const char *const text = std::getenv("EVO_B200_GEMM_PAIR_MIN_TILES");
+      const long value = text != nullptr ? std::strtol(text, nullptr, 10) : 0;
+      // 1,024 x 4096 outputs are 64 pair tiles on 74 pairs: 883 against 840 TFLOP/s at K = 4096, 1,214 against
+      // 1,126 at K = 11264
+      return value > 0 ? static_cast<std::size_t>(value) : std::size_t{48};
+    }();
     if (pairs_enabled && ep.weight_wrap_blocks == 0 && args.rows >= 512 &&
-        ((args.rows + 255) / 256) * ((args.out_features + 255) / 256) >= 74)
+        ((args.rows + 255) / 256) * ((args.out_features + 255) / 256) >= pair_tiles)
       return fp8 ? launch_tc_pair<true>(args.input, args.weight, ep, args.rows, args.out_features, args.in_features,
                                         stream)
                  : launch_tc_pair<false>(args.input, args.weight, ep, args.rows, args.out_features,
