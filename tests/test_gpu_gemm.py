@@ -72,6 +72,36 @@ def test_bf16_linear_large_against_f32_matmul(ops, rows, inner, columns):
     assert float(cosine) > 0.99995
 
 
+def test_pair_kernel_epilogues_at_ragged_sizes(ops):
+    """600 rows (two full pair tiles and a ragged third) x 6400 / 12800 columns run on CTA pairs.
+    Gated: the fused up-projection equals two linears and the gate bit for bit (same accumulators,
+    same rounding points).  Bias + residual: against an F32 matmul with the BF16 rounding chain."""
+    torch.manual_seed(600)
+    rows, inner, hidden = 600, 512, 6400
+    x = torch.randn(rows, inner, device="cuda").bfloat16()
+    w1 = (torch.randn(hidden, inner, device="cuda") * 0.08).bfloat16()
+    w2 = (torch.randn(hidden, inner, device="cuda") * 0.08).bfloat16()
+    packed = torch.empty(2 * hidden, inner, device="cuda", dtype=torch.bfloat16)
+    ops.call("interleave_gate_weights", p(w1), p(w2), hidden, inner, p(packed), stream())
+    fused = torch.empty(rows, hidden, device="cuda", dtype=torch.bfloat16)
+    ops.call("bf16_gated_up_projection", p(x), p(packed), rows, inner, hidden, 0, p(fused), stream())
+    first, second = (torch.empty(rows, hidden, device="cuda", dtype=torch.bfloat16) for _ in range(2))
+    ops.call("bf16_linear", p(x), p(w1), None, None, rows, inner, hidden, 0, 0, p(first), stream())
+    ops.call("bf16_linear", p(x), p(w2), None, None, rows, inner, hidden, 0, 0, p(second), stream())
+    unfused = torch.empty_like(fused)
+    ops.call("bf16_gated_elementwise", p(first), p(second), rows * hidden, 0, p(unfused), stream())
+    ops.call("check_async_errors", stream())
+    assert torch.equal(fused.view(torch.int16), unfused.view(torch.int16))
+    bias = torch.randn(hidden, device="cuda").bfloat16()
+    residual = torch.randn(rows, hidden, device="cuda").bfloat16()
+    out = torch.empty(rows, hidden, device="cuda", dtype=torch.bfloat16)
+    ops.call("bf16_linear", p(x), p(w1), p(bias), p(residual), rows, inner, hidden, 1, 0, p(out), stream())
+    ops.call("check_async_errors", stream())
+    reference = ((x.float() @ w1.float().T + bias.float()).bfloat16().float() + residual.float())
+    error = (out.float() - reference).abs()
+    assert bool((error <= 0.03 + 0.02 * reference.abs()).all()), float(error.max())
+
+
 def test_gated_up_projection_matches_two_linears_and_gate(ops, oracle):
     rng = np.random.default_rng(11)
     rows, inner, hidden = 150, 256, 384
