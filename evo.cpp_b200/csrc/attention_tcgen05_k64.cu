@@ -334,30 +334,30 @@ flash_tcgen05_k64_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
       unpack_f32x2(partial_sum[0], sum_even, sum_odd);
       unpack_f32x2(partial_sum[1], sum_even_b, sum_odd_b);
       running_sum = fmaf(running_sum, alpha, (sum_even + sum_odd) + (sum_even_b + sum_odd_b));
-      if (j > 0 && __any_sync(0xffffffffU, moved)) {
-        // O may be touched once the previous tile's P V has finished
+      if (j > 0) {
+        // Every warp follows the O-ready barrier tile by tile, whether it has to rescale or not: a parity
+        // wait cannot tell a phase from the one two before or two after it, so a waiter that skipped
+        // phases would either run ahead of a P V that has not finished or wait for one that finished
+        // long ago.  Having seen P V of tile j - 1 finish also means every warp has stored its
+        // probabilities of tile j - 1 (an mbarrier does not know which tile an arrival belongs to: no
+        // warp may arrive for tile j while the phase of tile j - 1 is still open).
         if (!mbar_wait(bar(kOFull), (j - 1) & 1U, abort_flag)) {
           ok = false;
           break;
         }
         tc_fence_after();
+        if (__any_sync(0xffffffffU, moved)) {
 #pragma unroll
-        for (int c = 0; c < kRows / 16; ++c) {
-          std::uint32_t o[16];
-          const std::uint32_t address = tmem_o + lane_base + c * 16;
-          tmem_load_16(address, o);
-          tmem_load_wait();
+          for (int c = 0; c < kRows / 16; ++c) {
+            std::uint32_t o[16];
+            const std::uint32_t address = tmem_o + lane_base + c * 16;
+            tmem_load_16(address, o);
+            tmem_load_wait();
 #pragma unroll
-          for (int i = 0; i < 16; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-          tmem_store_16(address, o);
+            for (int i = 0; i < 16; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+            tmem_store_16(address, o);
+          }
         }
-      }
-      // An mbarrier does not know which tile an arrival belongs to: a warp that runs a whole tile ahead
-      // of a slower one must not arrive for tile j while the phase of tile j - 1 is still open, or that
-      // phase would complete without the slower warp's probabilities.
-      if (j > 0 && !mbar_wait(bar(kPFull), (j - 1) & 1U, abort_flag)) {
-        ok = false;
-        break;
       }
       // BF16 P over the first 32 columns of this row's scores (all 64 are in registers by now)
       tmem_store_32(tmem_base + s * kScoreColumns + lane_base, packed);
@@ -366,10 +366,6 @@ flash_tcgen05_k64_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
       __syncwarp();
       if (lane == 0) mbar_arrive(bar(kPFull));
     }
-    // A parity wait cannot tell a phase from the one two before it.  A warp that never had to rescale has
-    // not looked at this barrier since the start, and all it knows from the scores of its last tile is
-    // that P V of tile `tiles - 3` is done: it first waits for tile `tiles - 2`, then for the last one.
-    if (ok && tiles > 1) ok = mbar_wait(bar(kOFull), (tiles - 2) & 1U, abort_flag);
     if (ok && tiles > 0 && mbar_wait(bar(kOFull), (tiles - 1) & 1U, abort_flag)) {
       tc_fence_after();
       const float inverse = 1.0F / running_sum;

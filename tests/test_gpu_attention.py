@@ -133,9 +133,9 @@ def test_tcgen05_attention_with_growing_scores(ops, rows, prefix, growth):
 def test_tcgen05_attention_gives_the_same_bits_on_concurrent_streams(ops):
     """Six host threads, each with its own stream, run the attention operator over and over on
     prompts of 151..361 rows.  With several kernels sharing the SMs the warps of a CTA drift far
-    apart, which is when a hand-over that is only safe at similar speeds shows (one did: a warp
-    that never rescaled read the accumulator two phases early).  Every result must equal the one
-    computed alone, bit for bit."""
+    apart, which is when a hand-over that is only safe at similar speeds shows (two did: a warp that
+    skipped phases of a barrier read the accumulator two phases early, or waited for a phase that had
+    long passed).  Every result must equal the one computed alone, bit for bit."""
     import threading
 
     gen = torch.Generator(device="cuda").manual_seed(11)
@@ -161,7 +161,27 @@ def test_tcgen05_attention_gives_the_same_bits_on_concurrent_streams(ops):
                     failures.append((rows, iteration, int((out != alone).any(dim=1).nonzero()[0])))
                     return
 
+    # two more threads keep every SM busy with large projections (persistent CTA pairs): attention CTAs
+    # then start late and their warps see very different delays
+    x = torch.randn(1024, 4096, device="cuda", generator=gen).bfloat16()
+    w = (torch.randn(12288, 4096, device="cuda", generator=gen) * 0.05).bfloat16()
+    product = torch.empty(1024, 12288, device="cuda", dtype=torch.bfloat16)
+    ops.call("bf16_linear", p(x), p(w), None, None, 1024, 4096, 12288, 0, 0, p(product), stream())
+    torch.cuda.synchronize()
+
+    def load():
+        own = torch.cuda.Stream()
+        with torch.cuda.stream(own):
+            out = torch.empty_like(product)
+            for iteration in range(150):
+                ops.call("bf16_linear", p(x), p(w), None, None, 1024, 4096, 12288, 0, 0, p(out), own.cuda_stream)
+                own.synchronize()
+                if not torch.equal(out, product):
+                    failures.append(("projection", iteration))
+                    return
+
     threads = [threading.Thread(target=worker, args=(job,)) for job in jobs]
+    threads += [threading.Thread(target=load) for _ in range(2)]
     for thread in threads:
         thread.start()
     for thread in threads:
