@@ -427,8 +427,31 @@ fir_decode_warp_kernel(const bf16 *__restrict__ input, const void *__restrict__ 
 
 }  // namespace
 
+// Odd widths (no model shape has one; upstream's operator tests do): the fused kernels work on channel
+// pairs, so the operator runs as its three steps - inner gate into `pregate`, the plain FIR with the
+// direct term as a multiply-input bias, outer gate in place - with the same BF16 rounding points.
+static int gated_fir_prefill_unfused(const GatedFirArgs &a, cudaStream_t stream) {
+  if (a.projection != nullptr || a.row_begin != 0)
+    return fail(kUnsupported, "gated FIR at an odd width takes separate x2 / x1 / value inputs and whole sequences");
+  if (a.pregate == nullptr)
+    return fail(kInvalidArgument, "gated FIR at an odd width needs the pregate buffer for the inner gate");
+  if (a.x2 == nullptr || a.x1 == nullptr || a.value == nullptr)
+    return fail(kInvalidArgument, "gated FIR inputs are incomplete");
+  if (a.length == 0) return kOk;
+  const std::size_t elements = a.length * a.width;
+  int status = gate(a.x1, a.value, a.pregate, elements, false, stream);
+  if (status != kOk) return status;
+  status = fir_prefill(a.pregate, a.filter, a.filter_is_f32, a.direct, a.direct != nullptr, a.length, a.width,
+                       a.groups, a.taps, a.cross_correlation, a.output, a.inner_cache, stream);
+  if (status != kOk) return status;
+  return gate(a.output, a.x2, a.output, elements, false, stream);
+}
+
 int gated_fir_prefill_generic(const GatedFirArgs &a, cudaStream_t stream) {
   const bool from_projection = a.projection != nullptr;
+  if (a.filter != nullptr && a.output != nullptr && a.width % 2 != 0 && a.groups != 0 && a.taps != 0 &&
+      a.taps <= kMaxTaps && a.width % a.groups == 0)
+    return gated_fir_prefill_unfused(a, stream);
   if (a.filter == nullptr || a.output == nullptr || a.width == 0 ||
       a.groups == 0 || a.taps == 0 || a.taps > kMaxTaps ||
       a.width % a.groups != 0 || a.width % 2 != 0)

@@ -528,7 +528,77 @@ std::size_t modal_scratch_floats(const std::size_t length,
   return (segments + 2) * width * modes;
 }
 
+// Any width and any state size up to 32 (the model shapes use even widths and 16 modes; upstream's
+// operator tests use 7 x 3): a thread owns a channel and walks the rows in order, the modal state in
+// registers.  Same rounding points as the chunked kernels: the first prefill rounds the convolution,
+// the direct product and their sum to BF16 before the outer gate; a continuation rounds once.
+namespace {
+constexpr int kAnyModes = 32;
+
+__global__ void __launch_bounds__(128)
+modal_prefill_any_kernel(const bf16 *__restrict__ x2, const bf16 *__restrict__ x1, const bf16 *__restrict__ value,
+                         const bf16 *__restrict__ direct, const float *__restrict__ log_poles,
+                         const float *__restrict__ residues, float *__restrict__ state, bf16 *__restrict__ pregate,
+                         bf16 *__restrict__ output, const int row_begin, const int length, const int width,
+                         const int modes, const bool continue_from_state) {
+  const int channel = blockIdx.x * blockDim.x + threadIdx.x;
+  if (channel >= width) return;
+  float pole[kAnyModes], residue[kAnyModes], held[kAnyModes];
+  for (int m = 0; m < modes; ++m) {
+    const std::size_t q = static_cast<std::size_t>(channel) * modes + m;
+    pole[m] = expf(log_poles[q]);
+    residue[m] = residues[q];
+    held[m] = continue_from_state ? state[q] : 0.0F;
+  }
+  const float d = bf2f(direct[channel]);
+  for (int t = row_begin; t < length; ++t) {
+    const std::size_t at = static_cast<std::size_t>(t) * width + channel;
+    const bf16 gated = f2bf(__fmul_rn(bf2f(x1[at]), bf2f(value[at])));
+    if (pregate != nullptr) pregate[at] = gated;
+    const float u = bf2f(gated);
+    float modal = 0.0F;
+    for (int m = 0; m < modes; ++m) {
+      held[m] = fmaf(pole[m], held[m], u);
+      modal = fmaf(residue[m], held[m], modal);
+    }
+    const float gate_value = bf2f(x2[at]);
+    if (continue_from_state) {
+      output[at] = f2bf(__fmul_rn(gate_value, fmaf(d, u, modal)));
+    } else {
+      const float mixed = rbf(__fadd_rn(rbf(modal), rbf(__fmul_rn(u, d))));
+      output[at] = f2bf(__fmul_rn(mixed, gate_value));
+    }
+  }
+  if (state != nullptr)
+    for (int m = 0; m < modes; ++m) state[static_cast<std::size_t>(channel) * modes + m] = held[m];
+}
+
+bool takes_chunked_kernels(const ModalArgs &a) {
+  return a.width % 2 == 0 && (a.modes == 1 || a.modes == 2 || a.modes == 4 || a.modes == 8 || a.modes == 16);
+}
+
+int modal_prefill_any(const ModalArgs &a, cudaStream_t stream) {
+  if (a.projection != nullptr)
+    return fail(kUnsupported, "modal prefill from the raw projection needs an even width and 1, 2, 4, 8 or 16 modes");
+  if (a.x2 == nullptr || a.x1 == nullptr || a.value == nullptr || a.direct == nullptr || a.log_poles == nullptr ||
+      a.residues == nullptr || a.output == nullptr || a.width == 0 || a.modes == 0)
+    return fail(kInvalidArgument, "modal prefill arguments are invalid");
+  if (a.modes > kAnyModes) return fail(kUnsupported, "modal state size must be at most 32");
+  if (a.continue_from_state && a.state == nullptr) return fail(kInvalidArgument, "modal continuation needs a state");
+  if (a.length > 0x7fffff00U || a.width > 0x3fffffffU || a.row_begin > a.length)
+    return fail(kInvalidArgument, "modal prefill dimensions are too large");
+  if (a.length == a.row_begin) return kOk;
+  modal_prefill_any_kernel<<<ceil_div_u(a.width, 128), 128, 0, stream>>>(
+      static_cast<const bf16 *>(a.x2), static_cast<const bf16 *>(a.x1), static_cast<const bf16 *>(a.value),
+      static_cast<const bf16 *>(a.direct), a.log_poles, a.residues, a.state, static_cast<bf16 *>(a.pregate),
+      static_cast<bf16 *>(a.output), static_cast<int>(a.row_begin), static_cast<int>(a.length),
+      static_cast<int>(a.width), static_cast<int>(a.modes), a.continue_from_state);
+  return check_launch("modal prefill kernel (any shape)");
+}
+}  // namespace
+
 int modal_prefill(const ModalArgs &a, cudaStream_t stream) {
+  if (a.width != 0 && a.modes != 0 && !takes_chunked_kernels(a)) return modal_prefill_any(a, stream);
   const bool from_projection = a.projection != nullptr;
   if (a.direct == nullptr || a.log_poles == nullptr || a.residues == nullptr ||
       a.output == nullptr || a.scratch == nullptr || a.width == 0 ||
@@ -607,6 +677,7 @@ int static_scratch_address(float **out) {
 }  // namespace
 
 int modal_prefill_static_scratch(const ModalArgs &a, cudaStream_t stream) {
+  if (a.width != 0 && a.modes != 0 && !takes_chunked_kernels(a)) return modal_prefill_any(a, stream);  // needs no scratch
   if (a.projection != nullptr || a.x2 == nullptr || a.x1 == nullptr || a.value == nullptr ||
       a.direct == nullptr || a.log_poles == nullptr || a.residues == nullptr ||
       a.output == nullptr || a.width == 0 || a.width % 2 != 0 || a.modes == 0)

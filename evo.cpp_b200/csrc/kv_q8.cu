@@ -88,10 +88,53 @@ q8_expand_kernel(const Q8PageTable pages, bf16 *__restrict__ key, bf16 *__restri
   }
 }
 
+// The same two operators for any head size (the model shapes all use 128): a warp still owns a
+// (token, head) vector, its lanes stride over the dimensions one element at a time.
+__global__ void __launch_bounds__(kThreads)
+q8_append_any_kernel(const bf16 *__restrict__ key, const bf16 *__restrict__ value, const Q8PageTable pages,
+                     const std::size_t first_position, const std::size_t rows, const int heads, const int head_dim) {
+  const std::size_t vector = (static_cast<std::size_t>(blockIdx.x) * kThreads + threadIdx.x) / 32;
+  const int lane = threadIdx.x % 32;
+  if (vector >= rows * heads) return;
+  const std::size_t position = first_position + vector / heads;
+  const int head = static_cast<int>(vector % heads);
+  const std::size_t page = position / pages.page_tokens, within = position % pages.page_tokens;
+  const std::size_t slot = within * heads + head;
+  for (int which = 0; which < 2; ++which) {
+    const bf16 *const source = (which == 0 ? key : value) + vector * head_dim;
+    float largest = 0.0F;
+    for (int d = lane; d < head_dim; d += 32) largest = fmaxf(largest, fabsf(bf2f(source[d])));
+    largest = warp_max_all(largest);
+    const float scale = largest == 0.0F ? 1.0F : __fdiv_rn(largest, 127.0F);
+    std::int8_t *const codes = (which == 0 ? pages.key : pages.value)[page] + slot * head_dim;
+    for (int d = lane; d < head_dim; d += 32)
+      codes[d] = static_cast<std::int8_t>(max(-127, min(127, __float2int_rn(__fdiv_rn(bf2f(source[d]), scale)))));
+    if (lane == 0) (which == 0 ? pages.key_scale : pages.value_scale)[page][slot] = scale;
+  }
+}
+
+__global__ void __launch_bounds__(kThreads)
+q8_expand_any_kernel(const Q8PageTable pages, bf16 *__restrict__ key, bf16 *__restrict__ value, const std::size_t count,
+                     const int heads, const int head_dim) {
+  const std::size_t vector = (static_cast<std::size_t>(blockIdx.x) * kThreads + threadIdx.x) / 32;
+  const int lane = threadIdx.x % 32;
+  if (vector >= count * heads) return;
+  const std::size_t position = vector / heads;
+  const int head = static_cast<int>(vector % heads);
+  const std::size_t page = position / pages.page_tokens, within = position % pages.page_tokens;
+  const std::size_t slot = within * heads + head;
+  for (int which = 0; which < 2; ++which) {
+    const std::int8_t *const codes = (which == 0 ? pages.key : pages.value)[page] + slot * head_dim;
+    const float scale = (which == 0 ? pages.key_scale : pages.value_scale)[page][slot];
+    bf16 *const target = (which == 0 ? key : value) + vector * head_dim;
+    for (int d = lane; d < head_dim; d += 32) target[d] = f2bf(static_cast<float>(codes[d]) * scale);
+  }
+}
+
 int check_table(const Q8PageTable &pages, const std::size_t heads, const std::size_t head_dim) {
   if (pages.key == nullptr || pages.value == nullptr || pages.key_scale == nullptr || pages.value_scale == nullptr ||
-      pages.page_tokens == 0 || heads == 0 || heads > 0x7fffU || head_dim != kHeadDim)
-    return fail(kInvalidArgument, "quantised KV cache arguments are invalid (head size 128 only)");
+      pages.page_tokens == 0 || heads == 0 || heads > 0x7fffU || head_dim == 0 || head_dim > 0x7fffU)
+    return fail(kInvalidArgument, "quantised KV cache arguments are invalid");
   return kOk;
 }
 
@@ -101,12 +144,18 @@ int q8_kv_append(const void *key, const void *value, const Q8PageTable &pages, c
                  const std::size_t rows, const std::size_t heads, const std::size_t head_dim, cudaStream_t stream) {
   const int status = check_table(pages, heads, head_dim);
   if (status != kOk) return status;
-  if (key == nullptr || value == nullptr || (reinterpret_cast<std::uintptr_t>(key) & 7U) != 0 ||
-      (reinterpret_cast<std::uintptr_t>(value) & 7U) != 0)
-    return fail(kInvalidArgument, "quantised KV append needs 8-byte aligned K and V");
+  if (key == nullptr || value == nullptr) return fail(kInvalidArgument, "quantised KV append needs K and V");
   if (rows == 0) return kOk;
   const std::size_t warps = rows * heads;
   if (warps > 0x3ffffffU) return fail(kInvalidArgument, "quantised KV append is too large");
+  if (head_dim != kHeadDim) {
+    q8_append_any_kernel<<<ceil_div_u(warps * 32, kThreads), kThreads, 0, stream>>>(
+        static_cast<const bf16 *>(key), static_cast<const bf16 *>(value), pages, first_position, rows,
+        static_cast<int>(heads), static_cast<int>(head_dim));
+    return check_launch("quantised KV append kernel");
+  }
+  if ((reinterpret_cast<std::uintptr_t>(key) & 7U) != 0 || (reinterpret_cast<std::uintptr_t>(value) & 7U) != 0)
+    return fail(kInvalidArgument, "quantised KV append needs 8-byte aligned K and V");
   q8_append_kernel<<<ceil_div_u(warps * 32, kThreads), kThreads, 0, stream>>>(
       static_cast<const bf16 *>(key), static_cast<const bf16 *>(value), pages, first_position, rows,
       static_cast<int>(heads));
@@ -117,8 +166,9 @@ int q8_kv_expand(const Q8PageTable &pages, const std::size_t count, const std::s
                  const std::size_t head_dim, void *key, void *value, cudaStream_t stream) {
   const int status = check_table(pages, heads, head_dim);
   if (status != kOk) return status;
-  if (key == nullptr || value == nullptr || (reinterpret_cast<std::uintptr_t>(key) & 7U) != 0 ||
-      (reinterpret_cast<std::uintptr_t>(value) & 7U) != 0)
+  if (key == nullptr || value == nullptr) return fail(kInvalidArgument, "quantised KV expansion needs outputs");
+  if (head_dim == kHeadDim &&
+      ((reinterpret_cast<std::uintptr_t>(key) & 7U) != 0 || (reinterpret_cast<std::uintptr_t>(value) & 7U) != 0))
     return fail(kInvalidArgument, "quantised KV expansion needs 8-byte aligned outputs");
   if (count == 0) return kOk;
   const std::size_t warps = count * heads;
@@ -134,11 +184,17 @@ int q8_kv_expand(const Q8PageTable &pages, const std::size_t count, const std::s
       shifted.value_scale += begin / pages.page_tokens;
       const std::size_t part = std::min(step, count - begin);
       const int inner = q8_kv_expand(shifted, part, heads, head_dim,
-                                     static_cast<bf16 *>(key) + begin * heads * kHeadDim,
-                                     static_cast<bf16 *>(value) + begin * heads * kHeadDim, stream);
+                                     static_cast<bf16 *>(key) + begin * heads * head_dim,
+                                     static_cast<bf16 *>(value) + begin * heads * head_dim, stream);
       if (inner != kOk) return inner;
     }
     return kOk;
+  }
+  if (head_dim != kHeadDim) {
+    q8_expand_any_kernel<<<ceil_div_u(warps * 32, kThreads), kThreads, 0, stream>>>(
+        pages, static_cast<bf16 *>(key), static_cast<bf16 *>(value), count, static_cast<int>(heads),
+        static_cast<int>(head_dim));
+    return check_launch("quantised KV expansion kernel");
   }
   q8_expand_kernel<<<ceil_div_u(warps * 32, kThreads), kThreads, 0, stream>>>(
       pages, static_cast<bf16 *>(key), static_cast<bf16 *>(value), count, static_cast<int>(heads));

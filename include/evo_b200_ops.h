@@ -172,7 +172,8 @@ EVO_B200_API int evo_b200_bf16_fir_continue_direct(
 /* include/evo/cuda/hyena.hpp:203-250 (bf16_hcs_prefill, bf16_hcm_prefill,
  * bf16_hcm_prefill_direct): out = bf16(bf16(fir(bf16(x1*v)) [+ direct*u]) *
  * x2) in one fused pass.  direct may be NULL (HCS).  pregate (optional)
- * receives u; inner_cache (optional) the F32 tail of u. */
+ * receives u; inner_cache (optional) the F32 tail of u.  An odd width runs
+ * as three passes (gate, FIR, gate) and needs pregate. */
 EVO_B200_API int evo_b200_bf16_gated_fir_prefill(
     const void *x2, const void *x1, const void *value, const void *filter,
     int filter_is_f32, const void *direct, size_t length, size_t width,
@@ -322,13 +323,13 @@ EVO_B200_API int evo_b200_linear_executor_linear(
 
 /* ---- quantised KV cache (profile fast-q8-kv; upstream src/cuda/attention.cu:798-866 append,
  * :1072-1141 attention; docs/execution-profiles.md:96-127).  A cache is four device arrays of
- * page pointers - key codes, value codes (int8 [page_tokens, heads, 128]) and key scales, value
+ * page pointers - key codes, value codes (int8 [page_tokens, heads, head_dim]) and key scales, value
  * scales (F32 [page_tokens, heads]); page p holds positions [p * page_tokens, (p+1) * page_tokens).
  * Every (token, head) vector has scale = max|v| / 127 (1 for a zero vector) and codes
- * clamp(rint(v / scale), -127, 127).  append quantises BF16 K / V [rows, heads, 128] of positions
- * first_position ..; expand writes BF16 images [count, heads, 128] of positions [0, count);
+ * clamp(rint(v / scale), -127, 127).  append quantises BF16 K / V [rows, heads, head_dim] of positions
+ * first_position ..; expand writes BF16 images [count, heads, head_dim] of positions [0, count);
  * attention_decode is causal attention of 1..8 query rows (row i sees keys 0 .. total_keys - rows
- * + i) read straight from the pages. */
+ * + i) read straight from the pages, head size 128 only (append and expand take any head size). */
 EVO_B200_API int evo_b200_q8_kv_append(const void *key, const void *value, void *const *key_pages,
                                        void *const *value_pages, void *const *key_scale_pages,
                                        void *const *value_scale_pages, size_t page_tokens,

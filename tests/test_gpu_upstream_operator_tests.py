@@ -1,0 +1,54 @@
+"""Upstream evo.cpp's own CUDA operator tests as acceptance tests of the drop-in boundary.
+
+`oracle/Makefile` (target `operator_tests`) compiles upstream's tests/test_cuda_ops.cu,
+tests/test_cuda_hyena.cu and tests/test_cuda_attention.cu unmodified, from the upstream source tree,
+against upstream's headers, and links them with the `evo::cuda` source-compatibility layer
+(`evo.cpp_b200/compat/`) over this build's operator library.  Each binary prints one `FAIL: <what>`
+line per failed check and exits non-zero if there was any.
+
+Every check must pass except the ones listed in KNOWN: known answers that hash the bits of upstream's
+own reduction order (PyTorch's softmax kernels and cuBLAS GEMMs on the reference stack) for an operator
+this build computes on chip in another order, within the tolerance its own parity tests state.
+"""
+import pathlib
+import subprocess
+
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+BINARIES = pathlib.Path(__file__).resolve().parent.parent / "oracle" / "_ref"
+
+KNOWN = {
+    "ops": set(),
+    "hyena": set(),
+    "attention": {
+        # upstream tests/test_cuda_attention.cu:341-393: FNV-1a hashes of raw BF16 bytes produced by
+        # PyTorch's cached softmax and cuBLAS on the reference stack; the probabilities are not even
+        # written to memory here
+        "cached softmax probabilities are bit exact to PyTorch",
+        "cached cross-attention output is bit exact to PyTorch",
+    },
+}
+
+
+def run(name):
+    binary = BINARIES / f"upstream_test_cuda_{name}"
+    if not binary.exists():
+        pytest.skip(f"{binary.name} was not built (the upstream source tree was absent at build time)")
+    done = subprocess.run([str(binary)], capture_output=True, text=True, timeout=600)
+    failed = [line[len("FAIL: "):].strip() for line in done.stderr.splitlines() if line.startswith("FAIL: ")]
+    return done, failed
+
+
+@pytest.mark.parametrize("name", ["ops", "hyena", "attention"])
+def test_upstream_operator_tests_pass_against_the_compatibility_layer(name):
+    done, failed = run(name)
+    unexpected = sorted(set(failed) - KNOWN[name])
+    assert not unexpected, f"unexpected failures: {unexpected}\nstdout: {done.stdout[-2000:]}\nstderr: {done.stderr[-4000:]}"
+    if not failed:
+        assert done.returncode == 0, done.stderr[-2000:]
+        assert "tests passed" in done.stdout
+    else:
+        # only the documented known-answer checks failed; the binary still ran to its end
+        assert "test(s) failed" in done.stderr, done.stderr[-2000:]
