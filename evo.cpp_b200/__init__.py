@@ -57,6 +57,7 @@ OPS_SIGNATURES: dict[str, list] = {
     "evo_b200_bf16_causal_attention": [_P, _P, _P, _Z, _Z, _Z, _Z, _P, _P],
     "evo_b200_bf16_causal_attention_mma_sync": [_P, _P, _P, _Z, _Z, _Z, _Z, _P, _P],
     "evo_b200_bf16_cached_cross_attention": [_P, _P, _P, _Z, _Z, _Z, _Z, _P, _P],
+    "evo_b200_bf16_cached_cross_attention_probabilities": [_P, _P, _P, _Z, _Z, _Z, _Z, _P, _P, _P],
     "evo_b200_linear_executor_create": [_I, ctypes.POINTER(_P)],
     "evo_b200_linear_executor_linear": [_P, _P, _Z, _Z, _P, _I, _Z, _Z, _P, _I, _Z, _P],
     "evo_b200_e4m3_encode_array": [_P, _Z, _F, _P],

@@ -11,9 +11,9 @@
 //  * The quantised (Q8, paged) cache keeps upstream's layout: pages allocated when first touched,
 //    device tables of page pointers, host mirrors.  Chunks attend to a BF16 image rebuilt from the
 //    pages; 1..8-row steps at head size 128 read the pages directly.
-//  * bf16_cached_cross_attention does not write its intermediate tensors: scores and probabilities
-//    stay on chip.  The three scratch buffers are grown to upstream's sizes and zero-filled so that
-//    callers' size assumptions hold; their contents carry no information.
+//  * bf16_cached_cross_attention keeps the scaled keys and the scores on chip; of upstream's three
+//    intermediate tensors only the BF16 probabilities are written.  All three scratch buffers are grown
+//    to upstream's sizes (and zero-filled when new) so that callers' size assumptions hold.
 #include "compat_common.hpp"
 
 #include <algorithm>
@@ -401,8 +401,9 @@ Status bf16_cached_cross_attention(const Blas &blas, const DeviceBuffer &query, 
     if (status.ok() && fresh) status = buffer->zero(stream);
     if (!status.ok()) return status;
   }
-  return from_code(evo_b200_bf16_cached_cross_attention(query.data(), key.data(), value.data(), query_tokens, key_tokens,
-                                                        heads, head_dim, output->data(), raw(stream)),
+  return from_code(evo_b200_bf16_cached_cross_attention_probabilities(
+                       query.data(), key.data(), value.data(), query_tokens, key_tokens, heads, head_dim,
+                       probabilities == nullptr ? nullptr : probabilities->data(), output->data(), raw(stream)),
                    "cached attention");
 }
 

@@ -164,7 +164,7 @@ attention_row_kernel(const bf16 *__restrict__ query,
                      const bf16 *__restrict__ value_cache,
                      bf16 *__restrict__ output, const int rows,
                      const int total_keys, const int heads,
-                     const int head_dim) {
+                     const int head_dim, bf16 *__restrict__ probabilities) {
   extern __shared__ float shared[];
   __shared__ float reduce_scratch[kRowThreads / 32];
   float *const q = shared;
@@ -197,6 +197,13 @@ attention_row_kernel(const bf16 *__restrict__ query,
   }
   const float row_sum = block_reduce(local_sum, reduce_scratch, false);
   __syncthreads();
+  if (kCachedRounding && probabilities != nullptr) {
+    // [heads, rows, total_keys] BF16, zeros behind the causal boundary: the tensor upstream's cached
+    // path materialises between its two GEMMs
+    bf16 *const target = probabilities + (static_cast<std::size_t>(head) * rows + row) * total_keys;
+    for (int j = threadIdx.x; j < total_keys; j += kRowThreads)
+      target[j] = f2bf(j < visible ? scores[j] / row_sum : 0.0F);
+  }
   for (int d = threadIdx.x; d < head_dim; d += kRowThreads) {
     float acc = 0.0F;
     const bf16 *const v = value_cache + head * head_dim + d;
@@ -213,7 +220,7 @@ template <bool kCachedRounding>
 int launch_rows(const void *query, const void *key_cache,
                 const void *value_cache, const std::size_t rows,
                 const std::size_t total_keys, const std::size_t heads,
-                const std::size_t head_dim, void *output, cudaStream_t stream) {
+                const std::size_t head_dim, void *output, cudaStream_t stream, void *probabilities = nullptr) {
   if (query == nullptr || key_cache == nullptr || value_cache == nullptr ||
       output == nullptr || heads == 0 || head_dim == 0 || total_keys < rows ||
       heads > 65535 || total_keys > 0x7fffffffU)
@@ -233,7 +240,7 @@ int launch_rows(const void *query, const void *key_cache,
       static_cast<const bf16 *>(query), static_cast<const bf16 *>(key_cache),
       static_cast<const bf16 *>(value_cache), static_cast<bf16 *>(output),
       static_cast<int>(rows), static_cast<int>(total_keys),
-      static_cast<int>(heads), static_cast<int>(head_dim));
+      static_cast<int>(heads), static_cast<int>(head_dim), static_cast<bf16 *>(probabilities));
   return check_launch("row-wise attention kernel");
 }
 
@@ -338,9 +345,9 @@ int cached_attention(const void *query, const void *key_cache,
                      const void *value_cache, const std::size_t rows,
                      const std::size_t total_keys, const std::size_t heads,
                      const std::size_t head_dim, void *output,
-                     cudaStream_t stream) {
+                     cudaStream_t stream, void *probabilities) {
   return launch_rows<true>(query, key_cache, value_cache, rows, total_keys,
-                           heads, head_dim, output, stream);
+                           heads, head_dim, output, stream, probabilities);
 }
 
 }  // namespace evob

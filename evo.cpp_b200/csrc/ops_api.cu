@@ -517,6 +517,14 @@ int evo_b200_bf16_cached_cross_attention(const void *query,
                           heads, head_dim, output, as_stream(stream));
 }
 
+int evo_b200_bf16_cached_cross_attention_probabilities(const void *query, const void *key_cache,
+                                                       const void *value_cache, size_t rows, size_t total_keys,
+                                                       size_t heads, size_t head_dim, void *probabilities,
+                                                       void *output, void *stream) {
+  return cached_attention(query, key_cache, value_cache, rows, total_keys, heads, head_dim, output,
+                          as_stream(stream), probabilities);
+}
+
 // ---- LinearExecutor offload (src/linear_executor.hpp:13-28)
 int evo_b200_linear_executor_create(int device, evo_b200_linear_executor **executor_out) {
   return linear_executor_create(device, reinterpret_cast<LinearExecutorState **>(executor_out));

@@ -275,7 +275,8 @@ int causal_attention_mma_sync(const void *query, const void *key_cache,
 int cached_attention(const void *query, const void *key_cache,
                      const void *value_cache, std::size_t rows,
                      std::size_t total_keys, std::size_t heads,
-                     std::size_t head_dim, void *output, cudaStream_t stream);
+                     std::size_t head_dim, void *output, cudaStream_t stream,
+                     void *probabilities = nullptr);  // optional BF16 [heads, rows, total_keys]
 
 // ---- linear_executor.cu: dense-linear offload with upstream's LinearExecutor contract
 struct LinearExecutorState;

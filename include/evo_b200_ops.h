@@ -292,6 +292,15 @@ EVO_B200_API int evo_b200_bf16_cached_cross_attention(
     const void *query, const void *key_cache, const void *value_cache,
     size_t rows, size_t total_keys, size_t heads, size_t head_dim,
     void *output, void *stream);
+/* The same operator, also writing the BF16 probabilities [heads, rows,
+ * total_keys] (zeros behind the causal boundary) that upstream materialises
+ * between its two GEMMs (the `probabilities` scratch of
+ * bf16_cached_cross_attention, include/evo/cuda/attention.hpp:131-140).
+ * probabilities may be NULL. */
+EVO_B200_API int evo_b200_bf16_cached_cross_attention_probabilities(
+    const void *query, const void *key_cache, const void *value_cache,
+    size_t rows, size_t total_keys, size_t heads, size_t head_dim,
+    void *probabilities, void *output, void *stream);
 
 /* ---- Dense-linear offload with the contract of upstream's LinearExecutor
  * (src/linear_executor.hpp:13-28; called from cpu::linear,

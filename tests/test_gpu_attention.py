@@ -9,7 +9,7 @@ import torch
 
 from gpu_util import (assert_close_bits, dev, dev_bits, empty_bits, host_bits, p, rand_bf16, stream,
                       ulp_mismatch_report)
-from oracle_lib import ptr
+from oracle_lib import bf16_to_f32, f32_to_bf16, ptr
 
 pytestmark = pytest.mark.gpu
 
@@ -205,6 +205,42 @@ def test_cached_cross_attention(ops, oracle, rows, prefix, heads, head_dim):
     oracle.cached_attention(ptr(q), ptr(k), ptr(v), rows, total, heads, head_dim, ptr(expected))
     # same BF16 materialisation points; only F32 summation order differs
     assert_close_bits(host_bits(out), expected, atol=0.01, rtol=0.02, min_cosine=0.9999)
+
+
+@pytest.mark.parametrize("rows,prefix,heads,head_dim", [(1, 2048, 2, 8), (5, 300, 3, 16), (1, 10240, 2, 8)])
+def test_cached_cross_attention_writes_its_probabilities(ops, rows, prefix, heads, head_dim):
+    """The BF16 probabilities [heads, rows, keys] upstream materialises between its two GEMMs
+    (include/evo/cuda/attention.hpp:131-140), zeros behind the causal boundary, and the same output bits as
+    the entry that does not write them.  Reference: the same materialisation points in numpy (BF16 scaled
+    keys, BF16 scores, F32 softmax); its sums run in another order, so a probability may differ by one
+    BF16 step where the quotient sits on a rounding boundary."""
+    rng = np.random.default_rng(prefix + head_dim)
+    width, total = heads * head_dim, prefix + rows
+    q = rand_bf16(rng, rows, width)
+    k, v = rand_bf16(rng, total, width), rand_bf16(rng, total, width)
+    out, plain = empty_bits(rows, width), empty_bits(rows, width)
+    probabilities = torch.full((heads, rows, total), 0x7fc0, dtype=torch.int16, device="cuda")
+    ops.call("bf16_cached_cross_attention_probabilities", p(dev_bits(q)), p(dev_bits(k)), p(dev_bits(v)), rows, total,
+             heads, head_dim, p(probabilities), p(out), stream())
+    ops.call("bf16_cached_cross_attention", p(dev_bits(q)), p(dev_bits(k)), p(dev_bits(v)), rows, total, heads,
+             head_dim, p(plain), stream())
+    assert np.array_equal(host_bits(out), host_bits(plain))
+    got = bf16_to_f32(probabilities.cpu().numpy().view(np.uint16))
+    rbf = lambda x: bf16_to_f32(f32_to_bf16(np.asarray(x, np.float32)))
+    scale = np.float32(1.0 / np.sqrt(head_dim))
+    qf = bf16_to_f32(q).reshape(rows, heads, head_dim)
+    kf = rbf(bf16_to_f32(k).reshape(total, heads, head_dim) * scale)
+    for r in range(rows):
+        visible = prefix + r + 1
+        assert not got[:, r, visible:].any()
+        scores = rbf(np.einsum("hd,thd->ht", qf[r].astype(np.float64), kf[:visible].astype(np.float64)))
+        e = np.exp(scores - scores.max(axis=1, keepdims=True), dtype=np.float32)
+        expected = rbf(e / e.sum(axis=1, keepdims=True, dtype=np.float32))
+        # a score on a BF16 rounding boundary (F32 against F64 dot product) moves a probability by ~1 %
+        np.testing.assert_allclose(got[:, r, :visible], expected, rtol=0.03, atol=1e-30)
+        off = np.abs(got[:, r, :visible] - expected) > 2.0 ** -7 * np.abs(expected)
+        assert off.mean() < 1e-3, off.mean()
+        np.testing.assert_allclose(got[:, r, :visible].astype(np.float64).sum(axis=1), 1.0, atol=0.01)
 
 
 def test_attention_rejects_bad_arguments(ops):

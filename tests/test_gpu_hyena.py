@@ -75,7 +75,8 @@ def _gated_inputs(rng, length, width):
     return rand_bf16(rng, length, width), rand_bf16(rng, length, width), rand_bf16(rng, length, width)
 
 
-@pytest.mark.parametrize("length,width,groups", [(19, 16, 4), (128, 64, 8), (129, 130, 13), (1000, 256, 16)])
+@pytest.mark.parametrize("length,width,groups", [(19, 16, 4), (128, 64, 8), (129, 130, 13), (1000, 256, 16),
+                                                 (13, 9, 3)])  # odd width: the three-pass route
 def test_hcs_fused_prefill_bit_exact(ops, oracle, length, width, groups):
     """k=7 cross-correlation: same tap order and rounding points as upstream's
     gate -> direct FIR -> gate chain, so the fused kernel is bit-identical."""
@@ -96,7 +97,7 @@ def test_hcs_fused_prefill_bit_exact(ops, oracle, length, width, groups):
 
 
 @pytest.mark.parametrize("length,width,groups,f32_filter", [(19, 8, 2, 1), (128, 64, 4, 0), (129, 64, 64, 0),
-                                                           (700, 192, 12, 1)])
+                                                           (700, 192, 12, 1), (19, 15, 5, 1), (129, 15, 5, 0)])
 def test_hcm_fused_prefill(ops, oracle, length, width, groups, f32_filter):
     """k=128 causal convolution with the direct term.  Upstream evaluates it by
     FFT (tolerance 0.03 abs + 0.02 rel, cosine >= 0.999 in its own test); the
@@ -108,9 +109,10 @@ def test_hcm_fused_prefill(ops, oracle, length, width, groups, f32_filter):
     direct = rand_bf16(rng, width)
     out = empty_bits(length, width)
     cache = torch.zeros((width, 127), device="cuda")
+    pregate = empty_bits(length, width) if width % 2 else None  # an odd width runs as three passes and needs it
     ops.call("bf16_gated_fir_prefill", p(dev_bits(x2)), p(dev_bits(x1)), p(dev_bits(v)),
              p(dev(h32) if f32_filter else dev_bits(h)), f32_filter, p(dev_bits(direct)), length, width,
-             groups, 128, 1, None, p(cache), p(out), stream())
+             groups, 128, 1, p(pregate) if pregate is not None else None, p(cache), p(out), stream())
     expected = np.empty((length, width), np.uint16)
     expected_cache = np.empty((width, 127), np.float32)
     oracle.gated_fir(ptr(x2), ptr(x1), ptr(v), ptr(h32) if f32_filter else ptr(h), f32_filter, ptr(direct),
@@ -242,7 +244,8 @@ def _modal_params(rng, width, modes):
     return log_poles, residues
 
 
-@pytest.mark.parametrize("length,width,modes", [(19, 8, 2), (128, 64, 16), (129, 64, 16), (1000, 96, 16)])
+@pytest.mark.parametrize("length,width,modes", [(19, 8, 2), (128, 64, 16), (129, 64, 16), (1000, 96, 16),
+                                                (9, 7, 3), (300, 6, 5), (65, 33, 16)])  # any-shape kernel
 def test_hcl_prefill_output_and_state(ops, oracle, length, width, modes):
     """Chunked-scan prefill vs the FFT-path contract (exact convolution with the
     materialised filter, four BF16 roundings).  Upstream's own gate for this
@@ -314,6 +317,31 @@ def test_hcl_continuation_matches_single_pass_and_decode(ops, oracle):
     oracle.hcl_decode(ptr(row[0]), ptr(row[1]), ptr(row[2]), ptr(direct), ptr(log_poles), ptr(residues),
                       width, modes, ptr(host_state), None, ptr(expected))
     assert_close_bits(host_bits(out), expected, atol=0.02, rtol=0.02)
+
+
+def test_hcl_continuation_at_an_odd_width_and_state_size(ops, oracle):
+    """Width 7 with 3 modes (the shape of upstream's own operator test) takes the one-thread-per-channel
+    kernel; the allocation-free entry needs no scratch for it.  A continuation rounds once."""
+    rng = np.random.default_rng(31)
+    length, width, modes, first = 40, 7, 3, 9
+    x2, x1, v = _gated_inputs(rng, length, width)
+    direct = rand_bf16(rng, width)
+    log_poles, residues = _modal_params(rng, width, modes)
+    state = torch.zeros((width, modes), device="cuda")
+    host_state = np.zeros((width, modes), np.float32)
+    lp, res, d = dev(log_poles), dev(residues), dev_bits(direct)
+    for begin, end, mode in ((0, first, 0), (first, length, 1)):
+        rows = end - begin
+        part = [np.ascontiguousarray(a[begin:end]) for a in (x2, x1, v)]
+        out, pregate = empty_bits(rows, width), empty_bits(rows, width)
+        ops.call("bf16_hcl_prefill_noalloc", p(dev_bits(part[0])), p(dev_bits(part[1])), p(dev_bits(part[2])), p(d),
+                 p(lp), p(res), rows, width, modes, mode, p(state), p(pregate), p(out), stream())
+        expected, expected_u = np.empty((rows, width), np.uint16), np.empty((rows, width), np.uint16)
+        oracle.hcl_prefill(ptr(part[0]), ptr(part[1]), ptr(part[2]), ptr(direct), ptr(log_poles), ptr(residues),
+                           rows, width, modes, mode, ptr(host_state), ptr(expected_u), ptr(expected))
+        assert np.array_equal(host_bits(pregate), expected_u)
+        assert_close_bits(host_bits(out), expected, atol=0.04, rtol=0.03, min_cosine=0.9999)
+        np.testing.assert_allclose(state.cpu().numpy(), host_state, rtol=3e-5, atol=3e-5)
 
 
 def test_hcl_decode_reduction_tree_known_answer(ops):

@@ -25,9 +25,9 @@ HEAD_DIM = 128
 
 
 class Pages:
-    def __init__(self, page_tokens, page_count, heads):
-        self.page_tokens, self.heads = page_tokens, heads
-        self.codes = [[torch.zeros(page_tokens * heads * HEAD_DIM, dtype=torch.int8, device="cuda")
+    def __init__(self, page_tokens, page_count, heads, head_dim=HEAD_DIM):
+        self.page_tokens, self.heads, self.head_dim = page_tokens, heads, head_dim
+        self.codes = [[torch.zeros(page_tokens * heads * head_dim, dtype=torch.int8, device="cuda")
                        for _ in range(page_count)] for _ in range(2)]
         self.scales = [[torch.zeros(page_tokens * heads, device="cuda") for _ in range(page_count)] for _ in range(2)]
         self.tables = [torch.tensor([t.data_ptr() for t in group], dtype=torch.int64, device="cuda")
@@ -37,7 +37,7 @@ class Pages:
         return [p(t) for t in self.tables] + [self.page_tokens]
 
     def host(self, which, count):
-        codes = torch.cat(self.codes[which]).cpu().numpy().reshape(-1, self.heads, HEAD_DIM)[:count]
+        codes = torch.cat(self.codes[which]).cpu().numpy().reshape(-1, self.heads, self.head_dim)[:count]
         scales = torch.cat(self.scales[which]).cpu().numpy().reshape(-1, self.heads)[:count]
         return codes, scales
 
@@ -93,6 +93,30 @@ def test_append_expand_and_decode_from_pages(ops, heads, page_tokens):
             expected[r] = np.einsum("ht,thd->hd", weights, v[:visible].astype(np.float64))
         got = bf16_to_f32(host_bits(out)).astype(np.float64)
         assert np.all(np.abs(got - expected) <= 0.02 + 0.02 * np.abs(expected)), np.abs(got - expected).max()
+
+
+@pytest.mark.parametrize("heads,head_dim,page_tokens", [(2, 32, 3), (3, 6, 5), (1, 200, 4)])
+def test_append_and_expand_at_other_head_sizes(ops, heads, head_dim, page_tokens):
+    """Append and expand take any head size (upstream's own paged-cache test uses 32); same codes and scales."""
+    rng = np.random.default_rng(head_dim)
+    total = 11
+    pages = Pages(page_tokens, (total + page_tokens - 1) // page_tokens, heads, head_dim)
+    key, value = rand_bf16(rng, total, heads, head_dim), rand_bf16(rng, total, heads, head_dim, scale=3.0)
+    key[2, 0] = 0
+    for begin, end in ((0, 4), (4, total)):
+        ops.call("q8_kv_append", p(dev_bits(key[begin:end])), p(dev_bits(value[begin:end])), *pages.args(), begin,
+                 end - begin, heads, head_dim, stream())
+    image_k, image_v = empty_bits(total, heads, head_dim), empty_bits(total, heads, head_dim)
+    ops.call("q8_kv_expand", *pages.args(), total, heads, head_dim, p(image_k), p(image_v), stream())
+    for which, source, image in ((0, key, image_k), (1, value, image_v)):
+        codes, scales = pages.host(which, total)
+        expected_codes, expected_scales = reference_quantise(source)
+        assert np.array_equal(scales, expected_scales)
+        assert np.array_equal(codes, expected_codes)
+        assert np.array_equal(host_bits(image), f32_to_bf16(codes.astype(np.float32) * scales[..., None]))
+    query, out = rand_bf16(rng, 1, heads, head_dim), empty_bits(1, heads, head_dim)
+    assert ops.status("q8_attention_decode", p(dev_bits(query)), *pages.args(), 1, total, heads, head_dim, p(out),
+                      stream()) == 2  # reading the pages directly stays a head-size-128 kernel
 
 
 def test_profile_against_exact_with_upstreams_gates(pkg, tmp_path_factory):

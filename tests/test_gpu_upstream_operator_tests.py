@@ -6,9 +6,9 @@ against upstream's headers, and links them with the `evo::cuda` source-compatibi
 (`evo.cpp_b200/compat/`) over this build's operator library.  Each binary prints one `FAIL: <what>`
 line per failed check and exits non-zero if there was any.
 
-Every check must pass except the ones listed in KNOWN: known answers that hash the bits of upstream's
-own reduction order (PyTorch's softmax kernels and cuBLAS GEMMs on the reference stack) for an operator
-this build computes on chip in another order, within the tolerance its own parity tests state.
+Every check must pass except the one listed in KNOWN: a known answer that hashes the bits of a cuBLAS
+GEMM's summation order on the reference stack, for a product this build sums in another order (within
+the tolerance its own parity tests state).
 """
 import pathlib
 import subprocess
@@ -23,10 +23,10 @@ KNOWN = {
     "ops": set(),
     "hyena": set(),
     "attention": {
-        # upstream tests/test_cuda_attention.cu:341-393: FNV-1a hashes of raw BF16 bytes produced by
-        # PyTorch's cached softmax and cuBLAS on the reference stack; the probabilities are not even
-        # written to memory here
-        "cached softmax probabilities are bit exact to PyTorch",
+        # upstream tests/test_cuda_attention.cu:341-393: FNV-1a hashes of raw BF16 bytes from PyTorch on the
+        # reference stack, five context lengths.  The five probability tensors match bit for bit and so do
+        # four of the five outputs; at 10,240 keys the F32 sum of probabilities x values rounds differently
+        # in one of its 16 BF16 results than the library GEMM behind the reference bytes.
         "cached cross-attention output is bit exact to PyTorch",
     },
 }
@@ -50,5 +50,6 @@ def test_upstream_operator_tests_pass_against_the_compatibility_layer(name):
         assert done.returncode == 0, done.stderr[-2000:]
         assert "tests passed" in done.stdout
     else:
-        # only the documented known-answer checks failed; the binary still ran to its end
+        # only the documented known-answer check failed, once; the binary still ran to its end
         assert "test(s) failed" in done.stderr, done.stderr[-2000:]
+        assert len(failed) == 1, failed
