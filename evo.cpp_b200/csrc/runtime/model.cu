@@ -448,8 +448,6 @@ int Context::create(std::shared_ptr<ModelWeights> weights, const std::size_t con
   if (!c.test_fixture && context_size > c.max_seqlen)
     return fail(kInvalidArgument, "requested context exceeds model maximum of " +
                                       std::to_string(c.max_seqlen));
-  if (q8_kv && c.head_dim() != 128)
-    return fail(kUnsupported, "the fast-q8-kv profile needs attention heads of 128 dimensions");
   std::unique_ptr<Context> context(new Context());
   context->weights_ = weights;
   context->profile_ = profile;
@@ -718,7 +716,7 @@ int Context::run_stage(Stage &s, const std::size_t rows, const Mode mode,
         EVOB_OP(kCatAttention, q8_kv_append(static_cast<unsigned char *>(keys) + prefix * D * 2,
                                             static_cast<unsigned char *>(values) + prefix * D * 2, table, prefix, rows,
                                             c.heads, c.head_dim(), stream));
-        if (rows <= 8) {
+        if (rows <= 8 && c.head_dim() == 128) {  // other head sizes attend to the BF16 image of the pages
           EVOB_OP(kCatAttention, q8_attention_decode(s.query, table, rows, prefix + rows, c.heads, c.head_dim(),
                                                      s.mixer_out, stream));
           attended = true;

@@ -32,11 +32,11 @@ KNOWN = {
 }
 
 
-def run(name):
+def run(name, *arguments):
     binary = BINARIES / f"upstream_test_cuda_{name}"
     if not binary.exists():
         pytest.skip(f"{binary.name} was not built (the upstream source tree was absent at build time)")
-    done = subprocess.run([str(binary)], capture_output=True, text=True, timeout=600)
+    done = subprocess.run([str(binary), *arguments], capture_output=True, text=True, timeout=600)
     failed = [line[len("FAIL: "):].strip() for line in done.stderr.splitlines() if line.startswith("FAIL: ")]
     return done, failed
 
@@ -53,3 +53,14 @@ def test_upstream_operator_tests_pass_against_the_compatibility_layer(name):
         # only the documented known-answer check failed, once; the binary still ran to its end
         assert "test(s) failed" in done.stderr, done.stderr[-2000:]
         assert len(failed) == 1, failed
+
+
+def test_upstream_c_api_test_passes_against_libevo():
+    """Upstream's tests/test_cuda_c_api.c, compiled as C against upstream's include/evo/evo.h and linked with
+    this build's libevo.so, on the strict tiny fixture its own driver generates (tools/generate_tiny_model.py;
+    the committed copy under tests/golden/tiny): shared-weight contexts, the exact and fast-q8-kv profiles,
+    embeddings of an inner layer, byte-deterministic prefill and decode, callback abort poisoning."""
+    model = pathlib.Path(__file__).resolve().parent / "golden" / "tiny" / "tiny.safetensors"
+    done, failed = run("c_api", str(model))
+    assert not failed, f"{failed}\n{done.stderr[-2000:]}"
+    assert done.returncode == 0 and "CUDA C API tests passed" in done.stdout, done.stderr[-2000:]
