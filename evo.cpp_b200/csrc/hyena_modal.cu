@@ -150,6 +150,23 @@ __device__ __forceinline__ std::uint32_t add_pairs(const std::uint32_t a, const 
 __device__ __forceinline__ float pair_lo(const std::uint32_t w) { return __uint_as_float(w << 16U); }
 __device__ __forceinline__ float pair_hi(const std::uint32_t w) { return __uint_as_float(w & 0xffff0000U); }
 
+// Two F32 values in one 64-bit register and the packed FMA of sm_100 on them: each half is an
+// ordinary round-to-nearest FMA, so a pair of modes advanced this way has the bits of two scalar FMAs.
+__device__ __forceinline__ unsigned long long pack_f32_pair(const float low, const float high) {
+  unsigned long long pair;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(pair) : "f"(low), "f"(high));
+  return pair;
+}
+__device__ __forceinline__ void unpack_f32_pair(const unsigned long long pair, float &low, float &high) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(low), "=f"(high) : "l"(pair));
+}
+__device__ __forceinline__ unsigned long long fma_f32_pair(const unsigned long long a, const unsigned long long b,
+                                                           const unsigned long long c) {
+  unsigned long long d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+
 // kC = 2: a channel pair per thread, one 32-bit word per stream and row.  kC = 1: one channel per
 // thread with the same packed arithmetic on the low half of every word (the high half carries
 // zeros), so a channel's bits do not depend on the form; half the registers, twice the warps.
@@ -335,6 +352,21 @@ modal_stream_kernel(const ModalParams p) {
     }
   }
 
+  // One channel per thread, an even number of modes: the modes advance two at a time in packed
+  // registers (pole, state and residue pairs); the scalar arrays are only the prologue's and the
+  // epilogue's view of the same values.
+  constexpr bool kPacked = kC == 1 && kModes % 2 == 0;
+  constexpr int kPairs = kPacked ? kModes / 2 : 1;
+  [[maybe_unused]] unsigned long long pole2[kPairs], state2[kPairs], residue2[kPairs];
+  if constexpr (kPacked) {
+#pragma unroll
+    for (int q = 0; q < kPairs; ++q) {
+      pole2[q] = pack_f32_pair(pole[0][2 * q], pole[0][2 * q + 1]);
+      state2[q] = pack_f32_pair(state[0][2 * q], state[0][2 * q + 1]);
+      if constexpr (kOutput) residue2[q] = pack_f32_pair(residue[0][2 * q], residue[0][2 * q + 1]);
+    }
+  }
+
   Row next[kUnroll];
   [[maybe_unused]] std::size_t out_offset = static_cast<std::size_t>(t_own) * p.width + c0;
   const auto run_group = [&](auto checked, const int base) {
@@ -379,21 +411,43 @@ modal_stream_kernel(const ModalParams p) {
       u[0] = pair_lo(u_pair);
       if constexpr (kC == 2) u[1] = pair_hi(u_pair);
       if constexpr (!kOutput) {
+        if constexpr (kPacked) {
+          const unsigned long long u2 = pack_f32_pair(u[0], u[0]);
 #pragma unroll
-        for (int m = 0; m < kModes; ++m)
+          for (int q = 0; q < kPairs; ++q) state2[q] = fma_f32_pair(pole2[q], state2[q], u2);
+        } else {
 #pragma unroll
-          for (int c = 0; c < kC; ++c) state[c][m] = fmaf(pole[c][m], state[c][m], u[c]);
+          for (int m = 0; m < kModes; ++m)
+#pragma unroll
+            for (int c = 0; c < kC; ++c) state[c][m] = fmaf(pole[c][m], state[c][m], u[c]);
+        }
       } else {
         float modal[kC];
+        if constexpr (kPacked) {
+          // partial sums by mode % 4 as in the scalar form: pair q feeds (partial[0], partial[1]) when
+          // q is even and (partial[2], partial[3]) when it is odd
+          const unsigned long long u2 = pack_f32_pair(u[0], u[0]);
+          unsigned long long partial2[2] = {0ULL, 0ULL};
 #pragma unroll
-        for (int c = 0; c < kC; ++c) {
-          float partial[4] = {0.0F, 0.0F, 0.0F, 0.0F};
-#pragma unroll
-          for (int m = 0; m < kModes; ++m) {
-            state[c][m] = fmaf(pole[c][m], state[c][m], u[c]);
-            partial[m % 4] = fmaf(residue[c][m], state[c][m], partial[m % 4]);
+          for (int q = 0; q < kPairs; ++q) {
+            state2[q] = fma_f32_pair(pole2[q], state2[q], u2);
+            partial2[q % 2] = fma_f32_pair(residue2[q], state2[q], partial2[q % 2]);
           }
-          modal[c] = ((partial[0] + partial[1]) + partial[2]) + partial[3];
+          float partial[4];
+          unpack_f32_pair(partial2[0], partial[0], partial[1]);
+          unpack_f32_pair(partial2[1], partial[2], partial[3]);
+          modal[0] = ((partial[0] + partial[1]) + partial[2]) + partial[3];
+        } else {
+#pragma unroll
+          for (int c = 0; c < kC; ++c) {
+            float partial[4] = {0.0F, 0.0F, 0.0F, 0.0F};
+#pragma unroll
+            for (int m = 0; m < kModes; ++m) {
+              state[c][m] = fmaf(pole[c][m], state[c][m], u[c]);
+              partial[m % 4] = fmaf(residue[c][m], state[c][m], partial[m % 4]);
+            }
+            modal[c] = ((partial[0] + partial[1]) + partial[2]) + partial[3];
+          }
         }
         const std::size_t offset = out_offset;  // = t * width + c0, carried from row to row
         out_offset += static_cast<std::size_t>(p.width);
@@ -434,6 +488,10 @@ modal_stream_kernel(const ModalParams p) {
   int base = t_own;
   for (; base + 2 * kUnroll <= t_end; base += kUnroll) run_group(kPlainRows, base);
   for (; base < t_end; base += kUnroll) run_group(kCheckedRows, base);
+  if constexpr (kPacked) {
+#pragma unroll
+    for (int q = 0; q < kPairs; ++q) unpack_f32_pair(state2[q], state[0][2 * q], state[0][2 * q + 1]);
+  }
 
   if constexpr (kOutput) {
     if (t_end == p.length && p.state != nullptr) {
