@@ -397,8 +397,8 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> None:
     peak = fp8_peak if fp8_dominant else bf16_peak
     fp8_rates = [class_tflops[n] for n in ("gemm_e4m3_tcgen05", "gemm_e4m3_ffn_tcgen05") if class_tflops[n]]
     roofline = {"bound": "tensor",
-                "kernel": ("gemm_tcgen05_kernel<e4m3> (output and MLP projections of a step)" if fp8_dominant else
-                           "gemm_tcgen05_kernel<bf16> (all BF16 projections of a step)"),
+                "kernel": ("gemm_tcgen05_pair_kernel<e4m3> (output and MLP projections of a step)" if fp8_dominant else
+                           "gemm_tcgen05_pair_kernel<bf16> (all BF16 projections of a step; CTA pairs on 256 x 256 tiles)"),
                 "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
                 "peak_source": ("library E4M3 GEMM 8192^3 measured in this run, sustained (of measured)"
                                 if fp8_dominant and (fp8_library or {}).get("fp8_tflops_sustained") else
@@ -415,9 +415,9 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> None:
                 if class_tflops["gemm_bf16_tcgen05"] else None,
                 # DRAM read + write of one launch of this kernel from an ncu capture
                 # (M=8192 K=4096 N=8192: 256 MB algorithmic); the step's launches have other shapes
-                "traffic": 442.7e6,
-                "traffic_case": "ncu capture of gemm_tcgen05_kernel<bf16,256> at M=8192 K=4096 N=8192: "
-                                "332.1 MB read + 110.6 MB written against 256 MB algorithmic",
+                "traffic": 337.1e6,
+                "traffic_case": "ncu capture of gemm_tcgen05_pair_kernel<bf16> at M=8192 K=4096 N=8192: "
+                                "223.2 MB read + 113.9 MB written against 256 MB algorithmic",
                 "fp8_projection_tflops": class_tflops["gemm_e4m3_tcgen05"],
                 "operator_ms_per_step": {k: v[0] / args.steps for k, v in profile.items() if v[1]}}
 
@@ -804,8 +804,10 @@ def run_pipeline(args, rank: int, world: int, local_rank: int) -> None:
                     "d2h_bytes_per_step": 2 * tokens * VOCAB},
             "gpu_launches": int(launches),
             "roofline": {"bound": "tensor",
-                         "kernel": ("gemm_tcgen05_kernel<e4m3> (output and MLP projections, all ranks)" if fp8_dominant
-                                    else "gemm_tcgen05_kernel<bf16> (all BF16 projections, all ranks)"),
+                         "kernel": ("gemm_tcgen05_kernel / gemm_tcgen05_pair_kernel <e4m3> (output and MLP projections, "
+                                    "all ranks)" if fp8_dominant
+                                    else "gemm_tcgen05_kernel / gemm_tcgen05_pair_kernel <bf16> (all BF16 projections, "
+                                         "all ranks; pairs from 48 tiles per window on)"),
                          "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
                          "peak_source": ("2 x MEASURED_PEAKS.json bf16_tflops_sustained (of measured)" if fp8_dominant
                                          else "MEASURED_PEAKS.json bf16_tflops_sustained (of measured)") if peaks else
