@@ -565,8 +565,6 @@ evo_status evo_b200_context_prefill_with_dumps(evo_context *context, const evo_b
       return fail(evob::kInvalidArgument, "context, batch and callbacks are required");
     if (context->failed || context->context->poisoned())
       return fail(evob::kInvalidArgument, "context was invalidated by an earlier failure");
-    if (context->context->position() != 0)
-      return fail(evob::kInvalidArgument, "prefill requires a fresh context");
     evob::DumpPlan plan;
     int status = make_dump_plan(requests, request_count, dump_callback, user_data, &plan);
     if (status != kOk) return status;
@@ -870,6 +868,104 @@ evo_status evo_b200_plan_stages(const size_t *layer_bytes, size_t layers, size_t
 
 size_t evo_b200_context_stage_count(const evo_context *context) {
   return context == nullptr ? 0 : context->context->stages().size();
+}
+
+evo_status evo_b200_context_prefill_tokens(evo_context *context, const uint32_t *tokens, size_t token_count,
+                                           int32_t mode, evo_logits_callback callback, void *user_data) {
+  return protect([&]() -> int {
+    if (context == nullptr || tokens == nullptr || token_count == 0 || callback == nullptr)
+      return fail(evob::kInvalidArgument, "context, tokens and callback are required");
+    if (mode < EVO_B200_PREFILL_FRESH || mode > EVO_B200_PREFILL_CHUNK)
+      return fail(evob::kInvalidArgument, "unknown prefill mode");
+    if (context->failed || context->context->poisoned())
+      return fail(evob::kInvalidArgument, "context was invalidated by an earlier failure");
+    evob::Context &model = *context->context;
+    const std::size_t capacity = model.activation_capacity();
+    const std::size_t columns = model.config().vocab;
+    const std::size_t begin = mode == EVO_B200_PREFILL_CHUNK ? model.position() : 0;
+    if (token_count > model.context_capacity() - std::min(begin, model.context_capacity()))
+      return fail(evob::kInvalidArgument, "sequence exceeds the context capacity");
+    if (mode != EVO_B200_PREFILL_FRESH && token_count > capacity)
+      return fail(evob::kInvalidArgument, "this prefill form takes at most one activation chunk of tokens");
+    std::vector<float> logits;
+    for (std::size_t offset = 0; offset < token_count;) {
+      const std::size_t rows = std::min(capacity, token_count - offset);
+      const std::vector<std::uint32_t> chunk(tokens + offset, tokens + offset + rows);
+      int status;
+      switch (mode) {
+        case EVO_B200_PREFILL_STATELESS: status = model.prefill_stateless(chunk, &logits); break;
+        case EVO_B200_PREFILL_CACHED: status = model.prefill_cached(chunk, &logits); break;
+        case EVO_B200_PREFILL_CHUNK: status = model.prefill_chunk(chunk, &logits); break;
+        default: status = offset == 0 ? model.prefill(chunk, &logits) : model.prefill_chunk(chunk, &logits); break;
+      }
+      if (status != kOk) {
+        if (model.poisoned()) context->failed = true;
+        return status;
+      }
+      if (logits.size() != rows * columns) return fail(evob::kInternal, "backend returned incomplete logits");
+      const evo_status callback_status = callback(logits.data(), rows, columns, begin + offset, user_data);
+      if (callback_status != EVO_STATUS_OK) {
+        context->failed = true;
+        return fail(valid_status(callback_status) ? callback_status : EVO_STATUS_INTERNAL,
+                    "logits consumer aborted prefill");
+      }
+      offset += rows;
+    }
+    return kOk;
+  });
+}
+
+size_t evo_b200_context_activation_capacity(const evo_context *context) {
+  return context == nullptr ? 0 : context->context->activation_capacity();
+}
+
+evo_status evo_b200_read_model_config(const char *path, int32_t allow_test_fixture, evo_b200_model_config *config,
+                                      uint8_t *mixer_types, size_t mixer_capacity) {
+  return protect([&]() -> int {
+    if (path == nullptr || config == nullptr || config->struct_size < sizeof(evo_b200_model_config))
+      return fail(evob::kInvalidArgument, "model path and a sized configuration struct are required");
+    std::shared_ptr<evob::ModelFile> file;
+    int status = evob::ModelFile::open(path, &file);
+    if (status != kOk) return status;
+    evob::ModelConfig c;
+    status = evob::read_model_config(*file, allow_test_fixture != 0, &c);
+    if (status != kOk) return status;
+    status = evob::check_tensor_set(*file, c);
+    if (status != kOk) return status;
+    const auto copy_text = [](char (&target)[64], const std::string &source) {
+      std::memset(target, 0, sizeof(target));
+      std::memcpy(target, source.data(), std::min(source.size(), sizeof(target) - 1));
+    };
+    const std::size_t struct_size = config->struct_size;
+    std::memset(config, 0, sizeof(*config));
+    config->struct_size = struct_size;
+    copy_text(config->model_id, c.model_id);
+    copy_text(config->architecture, c.architecture);
+    copy_text(config->artifact_profile, c.artifact_profile);
+    config->vocab_size = c.vocab;
+    config->width = c.width;
+    config->layers = c.layers;
+    config->heads = c.heads;
+    config->state_size = c.state_size;
+    config->inner_width = c.inner_width;
+    config->short_filter_length = c.short_taps;
+    config->hcs_filter_length = c.hcs_taps;
+    config->hcm_filter_length = c.hcm_taps;
+    config->hcs_filter_groups = c.hcs_groups;
+    config->hcm_filter_groups = c.hcm_groups;
+    config->max_seqlen = c.max_seqlen;
+    config->epsilon = c.epsilon;
+    config->rope_scale = c.rope_scale;
+    config->rope_base = c.rope_base;
+    config->qkv_source_head_major = c.qkv_source_head_major ? 1 : 0;
+    config->hyena_projection_e4m3 = c.fp8_projection ? 1 : 0;
+    config->hcm_filter_f32 = c.hcm_filter_f32 ? 1 : 0;
+    config->test_fixture = c.test_fixture ? 1 : 0;
+    if (mixer_types != nullptr)
+      for (std::size_t i = 0; i < c.mixers.size() && i < mixer_capacity; ++i)
+        mixer_types[i] = static_cast<uint8_t>(c.mixers[i]);
+    return kOk;
+  });
 }
 
 evo_status evo_b200_context_stage_info(const evo_context *context, size_t index,

@@ -1290,7 +1290,7 @@ int Context::prefill_cached(const std::vector<std::uint32_t> &tokens, std::vecto
 int Context::prefill_chunk(const std::vector<std::uint32_t> &tokens, std::vector<float> *logits) {
   if (logits == nullptr) return fail(kInvalidArgument, "logits output is null");
   if (state_valid_ && cached_attention_)
-    return fail(kInvalidArgument, "chunk continuation is not available after a cached prefill");
+    return fail(kInvalidArgument, "a cached prefill continues through exact token decode only, not through another chunk");
   return forward(tokens.data(), nullptr, tokens.size(), Mode::kContinue, logits, -1, nullptr);
 }
 int Context::decode(const std::uint32_t token, std::vector<float> *logits) {
@@ -1310,7 +1310,7 @@ int Context::prefill_chunk_embedding(const std::vector<std::uint32_t> &tokens, c
   if (hidden == nullptr || layer >= weights_->config.layers)
     return fail(kInvalidArgument, "layer capture index or output is invalid");
   if (!first && state_valid_ && cached_attention_)
-    return fail(kInvalidArgument, "chunk continuation is not available after a cached prefill");
+    return fail(kInvalidArgument, "a cached prefill continues through exact token decode only, not through another chunk");
   std::vector<float> logits;
   return forward(tokens.data(), nullptr, tokens.size(), first ? Mode::kPrefill : Mode::kContinue, &logits,
                  static_cast<long>(layer), hidden);
@@ -1336,7 +1336,7 @@ int Context::decode_with_dumps(const std::uint32_t token, const DumpPlan &plan, 
 int Context::continue_device(const std::uint32_t *device_tokens, const std::size_t rows) {
   if (device_tokens == nullptr) return fail(kInvalidArgument, "token buffer is null");
   if (state_valid_ && cached_attention_)
-    return fail(kInvalidArgument, "chunk continuation is not available after a cached prefill");
+    return fail(kInvalidArgument, "a cached prefill continues through exact token decode only, not through another chunk");
   return forward(nullptr, device_tokens, rows, Mode::kContinue, nullptr, -1, nullptr);
 }
 int Context::prefill_device(const std::uint32_t *device_tokens, const std::size_t rows,

@@ -90,6 +90,9 @@ struct ModelConfig {
 };
 
 int read_model_config(const ModelFile &file, bool allow_test_fixture, ModelConfig *config);
+// Every tensor the configuration calls for is there with its type and shape, and nothing else is
+// (host only; load_weights makes the same checks while it gathers the views).
+int check_tensor_set(const ModelFile &file, const ModelConfig &config);
 
 struct LayerWeights {
   MixerType type = MixerType::kHcs;

@@ -279,6 +279,25 @@ int StageWeights::ensure_fp8_ffn(const ModelConfig &c) {
   return kOk;
 }
 
+int check_tensor_set(const ModelFile &file, const ModelConfig &c) {
+  std::set<std::string> expected_names = {"embedding_layer.weight", "unembed.weight", "norm.scale"};
+  const TensorView *view = nullptr;
+  int status;
+  if ((status = lookup(file, {"embedding_layer.weight", TensorType::kBF16, {c.vocab, c.width}}, &view)) != kOk ||
+      (status = lookup(file, {"unembed.weight", TensorType::kBF16, {c.vocab, c.width}}, &view)) != kOk ||
+      (status = lookup(file, {"norm.scale", TensorType::kF32, {c.width}}, &view)) != kOk)
+    return status;
+  for (std::size_t layer = 0; layer < c.layers; ++layer)
+    for (const Expected &e : expected_block_tensors(c, layer)) {
+      if ((status = lookup(file, e, &view)) != kOk) return status;
+      expected_names.insert(e.name);
+    }
+  for (const TensorView &tensor : file.tensors())
+    if (expected_names.count(tensor.name) == 0)
+      return fail(kModelFormat, "unknown tensor for model profile '" + c.model_id + "': " + tensor.name);
+  return kOk;
+}
+
 int load_weights(const ModelFile &file, const std::vector<int> &devices,
                  const bool allow_test_fixture, const std::size_t layer_limit,
                  std::shared_ptr<ModelWeights> *out, const std::size_t slice_index,

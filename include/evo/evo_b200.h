@@ -41,6 +41,48 @@ EVO_API evo_status evo_b200_context_prefill_device(evo_context *context,
 EVO_API evo_status evo_b200_context_continue_device(evo_context *context,
                                                     const uint32_t *device_tokens, size_t rows,
                                                     const void **device_logits_out);
+/* The prefill forms of upstream's model classes that the portable ABI folds into evo_context_prefill
+ * (SingleGpuModel / PipelineModel, include/evo/cuda/model.hpp:121-170), on token ids instead of bytes:
+ *   FRESH      prefill(): starts a new sequence on any context (earlier state is dropped); prompts
+ *              longer than the activation capacity run as chunks;
+ *   STATELESS  prefill_stateless(): the same logits, no caches kept, position stays 0;
+ *   CACHED     prefill_cached(): the exact cached-generation arithmetic (BF16 score and probability
+ *              tensors); continues through evo_context_decode only;
+ *   CHUNK      prefill_chunk(): the next tokens of the sequence a FRESH prefill started.
+ * STATELESS, CACHED and CHUNK take at most evo_b200_context_activation_capacity tokens.  The
+ * callback receives the rows of each chunk as evo_context_prefill delivers them. */
+enum {
+  EVO_B200_PREFILL_FRESH = 0, EVO_B200_PREFILL_STATELESS = 1, EVO_B200_PREFILL_CACHED = 2,
+  EVO_B200_PREFILL_CHUNK = 3
+};
+EVO_API evo_status evo_b200_context_prefill_tokens(evo_context *context, const uint32_t *tokens,
+                                                   size_t token_count, int32_t mode,
+                                                   evo_logits_callback callback, void *user_data);
+/* Rows of one activation chunk (upstream activation_capacity(), include/evo/cuda/model.hpp:141, 222). */
+EVO_API size_t evo_b200_context_activation_capacity(const evo_context *context);
+/* The runtime configuration of a model file without loading its weights (upstream
+ * read_runtime_model_config + RuntimeModelConfig, include/evo/cuda/model.hpp:47-104): the same keys,
+ * the same refusals (a synthetic fixture needs allow_test_fixture; precision metadata that disagrees
+ * with the configuration, an unsupported projection dtype and tensors outside the profile's exact set
+ * are rejected here, before any device work).  mixer_types (optional) receives one code per block -
+ * 0 HCS, 1 HCM, 2 HCL, 3 attention - up to mixer_capacity. */
+typedef struct evo_b200_model_config {
+  size_t struct_size;
+  char model_id[64];
+  char architecture[64];
+  char artifact_profile[64];
+  size_t vocab_size, width, layers, heads, state_size, inner_width;
+  size_t short_filter_length, hcs_filter_length, hcm_filter_length;
+  size_t hcs_filter_groups, hcm_filter_groups, max_seqlen;
+  float epsilon, rope_scale, rope_base;
+  int32_t qkv_source_head_major;
+  int32_t hyena_projection_e4m3; /* 0: BF16 projections, 1: E4M3 codes + software QGMMA contract */
+  int32_t hcm_filter_f32;
+  int32_t test_fixture;
+} evo_b200_model_config;
+EVO_API evo_status evo_b200_read_model_config(const char *path, int32_t allow_test_fixture,
+                                              evo_b200_model_config *config, uint8_t *mixer_types,
+                                              size_t mixer_capacity);
 /* cudaStream_t of pipeline stage 0 (where a forward pass starts and ends). */
 EVO_API void *evo_b200_context_stream(const evo_context *context);
 /* Waits for all stages and reports asynchronous kernel errors. */
@@ -83,9 +125,9 @@ EVO_API evo_status evo_b200_context_stage_info(const evo_context *context, size_
  * a long-implicit block only).  Taps that a fused kernel keeps in registers are
  * produced by running the unfused operators for that block as well, so asking
  * for them costs extra launches; the block's results are unchanged.
- * The pass itself behaves like evo_context_prefill (fresh context, one
- * sequence, which must fit one activation chunk: EVO_STATUS_UNSUPPORTED
- * otherwise) and evo_context_decode.  A non-OK status from either callback
+ * The pass itself behaves like upstream's prefill_with_dumps (it starts a new
+ * sequence on any context; one sequence, which must fit one activation chunk:
+ * EVO_STATUS_UNSUPPORTED otherwise) and like evo_context_decode.  A non-OK status from either callback
  * aborts the pass and invalidates the context. */
 enum {
   EVO_B200_DUMP_BLOCK_OUTPUT = 0, EVO_B200_DUMP_PRE_NORM, EVO_B200_DUMP_MIXER_INPUT_PROJECTION,
