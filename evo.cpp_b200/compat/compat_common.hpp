@@ -1,12 +1,14 @@
 // Shared helpers of the evo::cuda source-compatibility layer.
 //
-// The layer defines the classes and operator functions that upstream evo.cpp declares in
-// include/evo/cuda/{runtime,ops,hyena,attention}.hpp on top of this library's C operator entry points
-// (include/evo_b200_ops.h).  It is compiled against upstream's own headers, found through an include
-// path given at build time, so that code written against `evo::cuda` (upstream's operator tests
-// tests/test_cuda_{ops,hyena,attention}.cu among it) links against this build unchanged.  Nothing here
-// computes on the device: every kernel that runs belongs to libevo_b200_ops; the layer checks sizes,
-// keeps host-side bookkeeping (cache lengths, plan counters, page tables) and issues copies.
+// The layer defines what upstream evo.cpp declares in include/evo/cuda/{runtime,ops,hyena,attention}.hpp
+// (classes and operator functions, on this library's C operator entry points, include/evo_b200_ops.h) and
+// in include/evo/cuda/model.hpp (the model classes, on the model-level C ABI, include/evo/evo.h and
+// include/evo/evo_b200.h).  It is compiled against upstream's own headers, found through an include path
+// given at build time, so that code written against `evo::cuda` (upstream's test programs
+// tests/test_cuda_{ops,hyena,attention,model,pipeline}.cu among it) links against this build unchanged.
+// Nothing here computes on the device: every kernel that runs belongs to libevo_b200_ops or libevo; the
+// layer checks sizes, keeps host-side bookkeeping (cache lengths, plan counters, page tables), issues
+// copies and writes dump files.
 #pragma once
 
 #include <cstddef>
