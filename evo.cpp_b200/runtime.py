@@ -40,6 +40,18 @@ class ModelParams(ctypes.Structure):
                 ("flags", ctypes.c_uint32)]
 
 
+class ModelConfig(ctypes.Structure):
+    """evo_b200_model_config (include/evo/evo_b200.h)."""
+    _fields_ = ([("struct_size", ctypes.c_size_t), ("model_id", ctypes.c_char * 64), ("architecture", ctypes.c_char * 64),
+                 ("artifact_profile", ctypes.c_char * 64)] +
+                [(name, ctypes.c_size_t) for name in
+                 ("vocab_size", "width", "layers", "heads", "state_size", "inner_width", "short_filter_length",
+                  "hcs_filter_length", "hcm_filter_length", "hcs_filter_groups", "hcm_filter_groups", "max_seqlen")] +
+                [(name, ctypes.c_float) for name in ("epsilon", "rope_scale", "rope_base")] +
+                [(name, ctypes.c_int32) for name in
+                 ("qkv_source_head_major", "hyena_projection_e4m3", "hcm_filter_f32", "test_fixture")])
+
+
 class ContextParams(ctypes.Structure):
     _fields_ = [("struct_size", ctypes.c_size_t), ("context_size", ctypes.c_size_t),
                 ("flags", ctypes.c_uint32)]
@@ -135,6 +147,12 @@ class EvoLibrary:
         if self.has_extensions:
             lib.evo_b200_context_prefill_device.argtypes = [V, V, Z, I, ctypes.POINTER(V)]
             lib.evo_b200_context_continue_device.argtypes = [V, V, Z, ctypes.POINTER(V)]
+            lib.evo_b200_context_prefill_tokens.argtypes = [V, ctypes.POINTER(ctypes.c_uint32), Z, ctypes.c_int32,
+                                                            LOGITS_CALLBACK, V]
+            lib.evo_b200_context_activation_capacity.restype = Z
+            lib.evo_b200_context_activation_capacity.argtypes = [V]
+            lib.evo_b200_read_model_config.argtypes = [ctypes.c_char_p, ctypes.c_int32, ctypes.POINTER(ModelConfig),
+                                                       ctypes.POINTER(ctypes.c_uint8), Z]
             lib.evo_b200_context_stream.restype = V
             lib.evo_b200_context_stream.argtypes = [V]
             lib.evo_b200_context_synchronize.argtypes = [V]
@@ -167,6 +185,15 @@ class EvoLibrary:
             lib.evo_b200_context_slice_head.argtypes = [V, Z, Z, ctypes.POINTER(V)]
             lib.evo_b200_context_slice_hidden.restype = V
             lib.evo_b200_context_slice_hidden.argtypes = [V]
+
+    def read_model_config(self, path, allow_test_fixture: bool = False):
+        """(ModelConfig, mixer codes per block: 0 HCS, 1 HCM, 2 HCL, 3 attention) without loading weights."""
+        config = ModelConfig()
+        config.struct_size = ctypes.sizeof(ModelConfig)
+        mixers = (ctypes.c_uint8 * 4096)()
+        self.check(self.lib.evo_b200_read_model_config(str(path).encode(), int(allow_test_fixture), ctypes.byref(config),
+                                                       mixers, 4096))
+        return config, list(mixers[:config.layers])
 
     def check(self, status: int) -> None:
         if status != 0:
@@ -341,6 +368,18 @@ class Context:
                                  self.vocab)
         finally:
             self.library.lib.evo_batch_free(batch)
+
+    PREFILL_FRESH, PREFILL_STATELESS, PREFILL_CACHED, PREFILL_CHUNK = 0, 1, 2, 3
+
+    def prefill_tokens(self, tokens, mode: int = 0) -> np.ndarray:
+        """evo_b200_context_prefill_tokens: token ids, one of the PREFILL_* forms; F32 logits [tokens, vocab]."""
+        ids = (ctypes.c_uint32 * len(tokens))(*tokens)
+        return self._collect(lambda cb: self.library.lib.evo_b200_context_prefill_tokens(
+            self.handle, ids, len(tokens), mode, cb, None), self.vocab)
+
+    @property
+    def activation_capacity(self) -> int:
+        return self.library.lib.evo_b200_context_activation_capacity(self.handle)
 
     def decode(self, token: int) -> np.ndarray:
         return self._collect(lambda cb: self.library.lib.evo_context_decode(self.handle, token, cb, None),

@@ -139,6 +139,20 @@ def mt19937_64_first_output(seed: int) -> int:
     return y & mask
 
 
+def test_model_configuration_is_read_without_a_device(evo, rt):
+    """evo_b200_read_model_config on upstream's 50-block tiny fixture: the fields upstream's own model test checks
+    (tests/test_cuda_model.cu:175-191) and the refusal of a synthetic fixture without permission."""
+    path = ROOT / "tests" / "golden" / "tiny" / "tiny.safetensors"
+    with pytest.raises(rt.EvoError):
+        evo.read_model_config(path, allow_test_fixture=False)
+    config, mixers = evo.read_model_config(path, allow_test_fixture=True)
+    assert (config.layers, config.vocab_size, config.width) == (50, 512, 8)
+    assert config.architecture == b"StripedHyena2Test" and config.test_fixture == 1
+    assert len(mixers) == 50 and mixers.count(3) == 8 and set(mixers) == {0, 1, 2, 3}
+    assert config.hyena_projection_e4m3 == 0 and config.hcm_filter_f32 == 1
+    assert (config.heads, config.hcm_filter_length, config.short_filter_length) == (2, 4, 3)
+
+
 def test_sampler_matches_upstream_rule(evo, rt):
     assert mt19937_64_first_output(5489) == 14514284786278117030  # the standard's check value seed
     logits = np.array([0.5, 2.0, 2.0, -1.0, 1.5], np.float32)
