@@ -58,16 +58,18 @@ Status enable_peer_access(const int device, const int peer_device) {
 
 Stream::~Stream() { reset(); }
 
-Stream::Stream(Stream &&other) noexcept
-    : stream_(std::exchange(other.stream_, nullptr)), device_(std::exchange(other.device_, -1)) {}
+// Moves are swaps: every member has an "empty" default, so a moved-into object starts empty, trades
+// places with its source, and whatever it held before leaves with the temporary.
+Stream::Stream(Stream &&other) noexcept {
+  std::swap(stream_, other.stream_);
+  std::swap(device_, other.device_);
+}
 
 Stream &Stream::operator=(Stream &&other) noexcept {
-  if (this != &other) {
-    reset();
-    stream_ = std::exchange(other.stream_, nullptr);
-    device_ = std::exchange(other.device_, -1);
-  }
-  return *this;
+  Stream incoming(std::move(other));
+  std::swap(stream_, incoming.stream_);
+  std::swap(device_, incoming.device_);
+  return *this;  // `incoming` now owns the old stream and destroys it
 }
 
 Status Stream::create(const unsigned int flags) {
@@ -126,20 +128,19 @@ Status check_transfer(const bool allocated, const void *host, const std::size_t 
 
 DeviceBuffer::~DeviceBuffer() { reset(); }
 
-DeviceBuffer::DeviceBuffer(DeviceBuffer &&other) noexcept
-    : allocation_(std::move(other.allocation_)),
-      data_(std::exchange(other.data_, nullptr)),
-      bytes_(std::exchange(other.bytes_, 0)),
-      device_(std::exchange(other.device_, -1)) {}
+DeviceBuffer::DeviceBuffer(DeviceBuffer &&other) noexcept {
+  allocation_.swap(other.allocation_);
+  std::swap(data_, other.data_);
+  std::swap(bytes_, other.bytes_);
+  std::swap(device_, other.device_);
+}
 
 DeviceBuffer &DeviceBuffer::operator=(DeviceBuffer &&other) noexcept {
-  if (this != &other) {
-    reset();
-    allocation_ = std::move(other.allocation_);
-    data_ = std::exchange(other.data_, nullptr);
-    bytes_ = std::exchange(other.bytes_, 0);
-    device_ = std::exchange(other.device_, -1);
-  }
+  DeviceBuffer incoming(std::move(other));
+  allocation_.swap(incoming.allocation_);
+  std::swap(data_, incoming.data_);
+  std::swap(bytes_, incoming.bytes_);
+  std::swap(device_, incoming.device_);
   return *this;
 }
 
@@ -221,14 +222,15 @@ Status DeviceBuffer::zero(const Stream &stream) {
 
 Blas::~Blas() { reset(); }
 
-Blas::Blas(Blas &&other) noexcept
-    : handle_(std::exchange(other.handle_, nullptr)), device_(std::exchange(other.device_, -1)) {}
+Blas::Blas(Blas &&other) noexcept {
+  std::swap(handle_, other.handle_);
+  std::swap(device_, other.device_);
+}
 
 Blas &Blas::operator=(Blas &&other) noexcept {
-  if (this != &other) {
-    handle_ = std::exchange(other.handle_, nullptr);
-    device_ = std::exchange(other.device_, -1);
-  }
+  Blas incoming(std::move(other));
+  std::swap(handle_, incoming.handle_);
+  std::swap(device_, incoming.device_);
   return *this;
 }
 
@@ -248,10 +250,11 @@ void Blas::reset() noexcept {
 
 BlasLt::~BlasLt() { reset(); }
 
-BlasLt::BlasLt(BlasLt &&other) noexcept : handle_(std::exchange(other.handle_, nullptr)) {}
+BlasLt::BlasLt(BlasLt &&other) noexcept { std::swap(handle_, other.handle_); }
 
 BlasLt &BlasLt::operator=(BlasLt &&other) noexcept {
-  if (this != &other) handle_ = std::exchange(other.handle_, nullptr);
+  BlasLt incoming(std::move(other));
+  std::swap(handle_, incoming.handle_);
   return *this;
 }
 
