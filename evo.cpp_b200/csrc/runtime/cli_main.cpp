@@ -43,6 +43,12 @@ struct Options {
   std::string vcf_path, reference_path;
   // serve
   size_t workers = 4, max_queue = 64;
+  // generation / scoring diagnostics (upstream src/cli.cpp:166-172): how many prompt tokens the cached
+  // prefill takes before the rest is teacher-forced through decode; token, logit and block-output dumps
+  size_t force_prompt_threshold = 0;  // 0: not given
+  bool dump_tokens = false;
+  std::string dump_logits_path, dump_layer_path;
+  size_t dump_layer = static_cast<size_t>(-1);
   size_t position = 0, window = 0;
 };
 
@@ -262,6 +268,27 @@ Options parse(int argc, char **argv) {
     else if (a == "--layer") o.layer = std::stoull(value(i));
     else if (a == "--pooling") o.pooling = value(i);
     else if (a == "--allow-test-fixture") o.allow_fixture = true;
+    else if (a == "--force-prompt-threshold") {
+      const std::string text = value(i);
+      char *end = nullptr;
+      const unsigned long long parsed = std::strtoull(text.c_str(), &end, 10);
+      if (text.empty() || text[0] == '-' || *end != '\0' || parsed < 1 || parsed > 1048576ULL)
+        die(EVO_STATUS_INVALID_ARGUMENT, "--force-prompt-threshold must be an integer in [1, 1048576]");
+      o.force_prompt_threshold = static_cast<size_t>(parsed);
+    } else if (a == "--dump-tokens") o.dump_tokens = true;
+    else if (a == "--dump-logits") {
+      o.dump_logits_path = value(i);
+      if (o.dump_logits_path.empty()) die(EVO_STATUS_INVALID_ARGUMENT, "--dump-logits path must not be empty");
+    } else if (a == "--dump-layer") {
+      const std::string spec = value(i);
+      const size_t colon = spec.find(':');
+      char *end = nullptr;
+      const unsigned long long layer = std::strtoull(spec.c_str(), &end, 10);
+      if (colon == std::string::npos || colon == 0 || colon + 1 >= spec.size() || end != spec.c_str() + colon)
+        die(EVO_STATUS_INVALID_ARGUMENT, "--dump-layer must be a nonnegative INDEX:PATH");
+      o.dump_layer = static_cast<size_t>(layer);
+      o.dump_layer_path = spec.substr(colon + 1);
+    }
     else if (a == "--sequence") o.sequence = value(i);
     else if (a == "--vcf") o.vcf_path = value(i);
     else if (a == "--workers" || a == "--max-batch") o.workers = std::stoull(value(i));
@@ -280,7 +307,8 @@ Options parse(int argc, char **argv) {
     } else if (a == "--version") { std::cout << evo_version_string() << '\n'; std::exit(0); }
     else if (a == "--help" || a == "-h") {
       std::cout << "usage:\n  evo run -m MODEL -p DNA -n TOKENS [--ctx N --gpu 0,1 --profile exact|b200-tc|b200-fp8|fast-q8-kv]\n"
-                   "  evo score -m MODEL --input FASTA_FASTQ_OR_TEXT\n"
+                   "          [--force-prompt-threshold N --dump-tokens --dump-logits PATH --dump-layer INDEX:PATH]\n"
+                   "  evo score -m MODEL --input FASTA_FASTQ_OR_TEXT [--dump-tokens --dump-logits PATH --dump-layer INDEX:PATH]\n"
                    "  evo bench -m MODEL --input FASTA_FASTQ_OR_TEXT [--warmup N --repetitions N]\n"
                    "  evo embed -m MODEL --input FASTA_FASTQ_OR_TEXT --output DIR --layer N "
                    "--pooling none|mean|last\n"
@@ -293,15 +321,60 @@ Options parse(int argc, char **argv) {
     } else die(EVO_STATUS_INVALID_ARGUMENT, "unknown option " + a);
   }
   if (o.model.empty()) die(EVO_STATUS_INVALID_ARGUMENT, "a model path is required (-m)");
+  const bool generation = o.command == "run";
+  if (o.force_prompt_threshold != 0 && !generation)
+    die(EVO_STATUS_INVALID_ARGUMENT, "--force-prompt-threshold is only valid for generation");
+  if ((!o.dump_logits_path.empty() || !o.dump_layer_path.empty()) && !generation && o.command != "score")
+    die(EVO_STATUS_INVALID_ARGUMENT, "--dump-logits and --dump-layer are valid for generation and scoring only");
   if (o.profile != "exact" && o.profile != "b200-tc" && o.profile != "b200-fp8" && o.profile != "fast-q8-kv")
     die(EVO_STATUS_UNSUPPORTED, "profile must be exact, b200-tc, b200-fp8 or fast-q8-kv");
   return o;
 }
 
 struct Metrics {
-  double load_seconds = 0, prefill_seconds = 0, decode_seconds = 0;
-  size_t prefill_tokens = 0, decode_tokens = 0;
+  double load_seconds = 0, prefill_seconds = 0, decode_seconds = 0, teacher_force_seconds = 0;
+  size_t prefill_tokens = 0, decode_tokens = 0, teacher_force_tokens = 0, retained_logits_peak_bytes = 0;
 };
+
+void print_tokens(const std::string &label, const std::string &bytes) {
+  std::cerr << "tokens " << label << "=[";
+  for (size_t i = 0; i < bytes.size(); ++i) std::cerr << (i ? "," : "") << int(static_cast<unsigned char>(bytes[i]));
+  std::cerr << "]\n";
+}
+
+// One prefill whose block output `layer` goes to an NPY file (upstream --dump-layer INDEX:PATH, the
+// block-output tap): the sequence has to fit one activation chunk.  cached selects the exact
+// cached-generation arithmetic (generation) or the ordinary prefill (scoring).
+struct LayerDumpSink {
+  std::filesystem::path path;
+  Collected logits;
+};
+evo_status write_layer_dump(size_t, int32_t, const float *values, size_t rows, size_t columns, void *user) {
+  Matrix matrix;
+  matrix.values.assign(values, values + rows * columns);
+  matrix.rows = rows;
+  matrix.columns = columns;
+  write_npy(static_cast<LayerDumpSink *>(user)->path, matrix);
+  return EVO_STATUS_OK;
+}
+evo_status collect_beside_dump(const float *logits, size_t rows, size_t columns, size_t offset, void *user) {
+  return collect(logits, rows, columns, offset, &static_cast<LayerDumpSink *>(user)->logits);
+}
+Collected prefill_with_layer_dump(evo_context *context, const std::string &bytes, const Options &o, const bool cached) {
+  if (bytes.size() > evo_b200_context_activation_capacity(context))
+    die(EVO_STATUS_INVALID_ARGUMENT, "--dump-layer is unavailable when prefill spans multiple activation chunks");
+  evo_batch *batch = nullptr;
+  check(evo_batch_create(1, &batch), "batch");
+  check(evo_batch_add_sequence(batch, reinterpret_cast<const uint8_t *>(bytes.data()), bytes.size()), "batch");
+  LayerDumpSink sink;
+  sink.path = o.dump_layer_path;
+  const evo_b200_dump_request request{o.dump_layer, EVO_B200_DUMP_BLOCK_OUTPUT};
+  const evo_status status = evo_b200_context_prefill_with_dumps(context, batch, &request, 1, cached ? 1 : 0,
+                                                                write_layer_dump, collect_beside_dump, &sink);
+  evo_batch_free(batch);
+  check(status, "prefill with --dump-layer");
+  return sink.logits;
+}
 
 evo_context *new_context(const evo_model *model, const Options &o) {
   evo_context_params params = evo_context_default_params();
@@ -331,12 +404,14 @@ void print_metrics(const Metrics &m, const Options &o, const evo_context *contex
   std::cerr << "evo_metrics {\"model_load_seconds\":" << std::setprecision(9) << m.load_seconds
             << ",\"prefill_tokens\":" << m.prefill_tokens << ",\"prefill_seconds\":" << m.prefill_seconds
             << ",\"prefill_tokens_per_second\":" << rate(m.prefill_tokens, m.prefill_seconds)
-            << ",\"teacher_force_tokens\":0,\"teacher_force_seconds\":0,\"teacher_force_tokens_per_second\":0"
+            << ",\"teacher_force_tokens\":" << m.teacher_force_tokens << ",\"teacher_force_seconds\":"
+            << m.teacher_force_seconds << ",\"teacher_force_tokens_per_second\":"
+            << rate(m.teacher_force_tokens, m.teacher_force_seconds)
             << ",\"decode_tokens\":" << m.decode_tokens << ",\"decode_seconds\":" << m.decode_seconds
             << ",\"decode_tokens_per_second\":" << rate(m.decode_tokens, m.decode_seconds)
             << ",\"kv_cache\":\"" << (o.profile == "fast-q8-kv" ? "q8_paged" : "bf16_contiguous")
             << "\",\"profile\":\"" << o.profile
-            << "\",\"retained_logits_peak_bytes\":0,\"gpus\":[";
+            << "\",\"retained_logits_peak_bytes\":" << m.retained_logits_peak_bytes << ",\"gpus\":[";
   const size_t stages = context == nullptr ? 0 : evo_b200_context_stage_count(context);
   for (size_t i = 0; i < stages; ++i) {
     evo_b200_stage_info info{};
@@ -399,14 +474,28 @@ int main(int argc, char **argv) {
 
   if (o.command == "score") {
     if (o.input.empty()) die(EVO_STATUS_INVALID_ARGUMENT, "score needs --input");
+    const bool dumping = !o.dump_logits_path.empty() || !o.dump_layer_path.empty();
+    size_t processed = 0;
     for (const Record &record : read_records(o.input, o.context)) {
+      if (processed++ != 0 && dumping)
+        die(EVO_STATUS_INVALID_ARGUMENT, "--dump-logits and --dump-layer require a score input with exactly one record");
+      if (o.dump_tokens) print_tokens(record.name, record.bytes);
       if (record.bytes.size() < 2) die(EVO_STATUS_INVALID_ARGUMENT, "scoring needs at least two tokens");
       if (last_context != nullptr) evo_context_free(last_context);
       last_context = new_context(model, o);
       const auto start = std::chrono::steady_clock::now();
-      const Collected out = prefill(last_context, record.bytes);
+      const Collected out = o.dump_layer_path.empty() ? prefill(last_context, record.bytes)
+                                                      : prefill_with_layer_dump(last_context, record.bytes, o, false);
       metrics.prefill_seconds += seconds_since(start);
       metrics.prefill_tokens += record.bytes.size();
+      if (!o.dump_logits_path.empty()) {
+        Matrix all;
+        all.values = out.logits;
+        all.rows = record.bytes.size();
+        all.columns = vocab;
+        write_npy(o.dump_logits_path, all);
+        metrics.retained_logits_peak_bytes = std::max(metrics.retained_logits_peak_bytes, out.logits.size() * sizeof(float));
+      }
       std::vector<double> scores;
       for (size_t t = 0; t + 1 < record.bytes.size(); ++t)
         scores.push_back(log_probability(out.logits.data() + t * vocab, vocab,
@@ -777,14 +866,47 @@ int main(int argc, char **argv) {
     evo_sampler *sampler = nullptr;
     check(evo_sampler_create(&sp, &sampler), "sampler");
     last_context = new_context(model, o);
+    if (o.dump_tokens) print_tokens("prompt", o.prompt);
+    // Upstream's generation pass (src/cuda/inference_cli.cpp:436-470): the first tokens of the prompt - all of
+    // it up to min(3000, activation capacity) unless --force-prompt-threshold says otherwise - run as one
+    // exact cached prefill, the rest of the prompt is teacher-forced through decode.
+    const size_t capacity = evo_b200_context_activation_capacity(last_context);
+    const size_t threshold = o.force_prompt_threshold != 0 ? o.force_prompt_threshold : std::min<size_t>(3000, capacity);
+    const size_t prefilled = std::min(o.prompt.size(), threshold);
+    if (prefilled > capacity)
+      die(EVO_STATUS_INVALID_ARGUMENT, "prompt prefill: exact cached prefill must fit one activation chunk; lower "
+                                       "--force-prompt-threshold to at most " + std::to_string(capacity));
     auto start = std::chrono::steady_clock::now();
-    Collected out = prefill(last_context, o.prompt);
+    Collected out;
+    if (!o.dump_layer_path.empty()) {
+      out = prefill_with_layer_dump(last_context, o.prompt.substr(0, prefilled), o, true);
+    } else {
+      std::vector<uint32_t> ids(prefilled);
+      for (size_t i = 0; i < prefilled; ++i) ids[i] = static_cast<unsigned char>(o.prompt[i]);
+      check(evo_b200_context_prefill_tokens(last_context, ids.data(), ids.size(), EVO_B200_PREFILL_CACHED, collect, &out),
+            "prompt prefill");
+    }
     metrics.prefill_seconds = seconds_since(start);
-    metrics.prefill_tokens = o.prompt.size();
+    metrics.prefill_tokens = prefilled;
     std::vector<float> logits(out.logits.end() - static_cast<std::ptrdiff_t>(vocab), out.logits.end());
+    start = std::chrono::steady_clock::now();
+    for (size_t i = prefilled; i < o.prompt.size(); ++i) {
+      Collected step;
+      check(evo_context_decode(last_context, static_cast<unsigned char>(o.prompt[i]), collect, &step),
+            "teacher-forced prompt token");
+      logits = step.logits;
+      ++metrics.teacher_force_tokens;
+    }
+    metrics.teacher_force_seconds = seconds_since(start);
+    Matrix dumped;  // --dump-logits: the logits every sampling step saw, [generated tokens, vocabulary]
+    dumped.columns = vocab;
     std::string generated;
     start = std::chrono::steady_clock::now();
     for (size_t i = 0; i < o.tokens; ++i) {
+      if (!o.dump_logits_path.empty()) {
+        dumped.values.insert(dumped.values.end(), logits.begin(), logits.end());
+        ++dumped.rows;
+      }
       uint32_t token = 0;
       check(evo_sampler_sample(sampler, logits.data(), vocab, &token), "sample");
       uint8_t byte = 0;
@@ -797,6 +919,10 @@ int main(int argc, char **argv) {
       ++metrics.decode_tokens;
     }
     metrics.decode_seconds = seconds_since(start);
+    if (!o.dump_logits_path.empty()) {
+      write_npy(o.dump_logits_path, dumped);
+      metrics.retained_logits_peak_bytes = dumped.values.size() * sizeof(float);
+    }
     if (o.output_format == "fasta") std::cout << '>' << o.name << '\n' << generated << '\n';
     else std::cout << generated;
     std::cout.flush();

@@ -90,6 +90,65 @@ def test_greedy_generation_is_deterministic_and_legacy_form_agrees():
     assert run("run", "-p", "ACGT", "-n", "80", "--ctx", "64", check=False).returncode == 2
 
 
+def test_generation_prefills_up_to_a_threshold_and_teacher_forces_the_rest(tmp_path):
+    """Upstream's generation pass (src/cuda/inference_cli.cpp:436-470; tests/test_cuda_cli.py:243-390): the cached
+    prefill takes min(prompt, threshold) tokens - threshold = min(3000, activation capacity) unless
+    --force-prompt-threshold is given - and the rest of the prompt is teacher-forced through decode.  Both
+    routes are the exact cached-generation arithmetic, so the logits of the first generated token agree; a
+    threshold beyond the activation arena (8 rows for the fixture) is refused."""
+    prompt = bytes([2, 5, 7, 3, 9, 11]).decode("latin-1")
+    whole, split = tmp_path / "whole.npy", tmp_path / "split.npy"
+    first = run("run", "-p", prompt, "-n", "1", "--ctx", "64", "--top-k", "1", "--dump-logits", str(whole), "--dump-tokens")
+    second = run("run", "-p", prompt, "-n", "1", "--ctx", "64", "--top-k", "1", "--dump-logits", str(split),
+                 "--force-prompt-threshold", "2")
+    assert b"tokens prompt=[2,5,7,3,9,11]" in first.stderr
+    a, b = np.load(whole), np.load(split)
+    assert a.shape == b.shape == (1, 512) and a.dtype == np.float32
+    np.testing.assert_allclose(a, b, atol=0.08, rtol=0.06)
+    assert first.stdout == second.stdout == bytes([16])          # greedy: the lower index of the fixture's tied pair
+    m1, m2 = metrics_line(first.stderr), metrics_line(second.stderr)
+    assert (m1["prefill_tokens"], m1["teacher_force_tokens"]) == (6, 0)
+    assert (m2["prefill_tokens"], m2["teacher_force_tokens"]) == (2, 4)
+    assert m1["retained_logits_peak_bytes"] == 512 * 4
+    long_prompt = bytes(range(2, 12)).decode("latin-1")            # ten tokens, arena of eight
+    refused = run("run", "-p", long_prompt, "-n", "1", "--ctx", "64", "--top-k", "1", "--force-prompt-threshold", "9",
+                  check=False)
+    assert refused.returncode == 2 and b"--force-prompt-threshold to at most 8" in refused.stderr
+    ok = run("run", "-p", long_prompt, "-n", "1", "--ctx", "64", "--top-k", "1")   # default threshold = the arena
+    m3 = metrics_line(ok.stderr)
+    assert (m3["prefill_tokens"], m3["teacher_force_tokens"]) == (8, 2)
+    assert run("score", "--input", str(whole), "--force-prompt-threshold", "2", check=False).returncode == 2
+
+
+def test_logit_and_layer_dumps(tmp_path):
+    """--dump-logits / --dump-layer INDEX:PATH (upstream tests/test_cuda_cli.py:120-160, 399-543): NPY v1 F32
+    matrices; generation dumps one row per sampled token and the block output of the prefilled prompt, scoring
+    dumps every position's logits and needs exactly one record."""
+    prompt = bytes([2, 5, 7, 3])
+    logits, layer = tmp_path / "logits.npy", tmp_path / "layer.npy"
+    run("run", "-p", prompt.decode("latin-1"), "-n", "3", "--ctx", "64", "--top-k", "1", "--dump-logits", str(logits),
+        "--dump-layer", f"17:{layer}")
+    assert np.load(logits).shape == (3, 512) and np.load(layer).shape == (4, 8)
+    expected_layer = np.fromfile(ROOT / "tests" / "golden" / "tiny" / "layer17.f32", "<f4").reshape(4, 8)
+    np.testing.assert_allclose(np.load(layer), expected_layer, atol=0.06, rtol=0.05)
+    raw = tmp_path / "prompt.txt"
+    raw.write_bytes(prompt)
+    scored, scored_layer = tmp_path / "scored.npy", tmp_path / "scored_layer.npy"
+    result = run("score", "--input", str(raw), "--ctx", "64", "--dump-logits", str(scored), "--dump-layer",
+                 f"17:{scored_layer}", "--dump-tokens")
+    assert b"=[2,5,7,3]" in result.stderr
+    golden = np.fromfile(ROOT / "tests" / "golden" / "tiny" / "logits.f32", "<f4").reshape(4, 512)
+    np.testing.assert_allclose(np.load(scored), golden, atol=0.08, rtol=0.06)
+    np.testing.assert_allclose(np.load(scored_layer), expected_layer, atol=0.06, rtol=0.05)
+    assert metrics_line(result.stderr)["retained_logits_peak_bytes"] == 4 * 512 * 4
+    two = tmp_path / "two.fa"
+    two.write_bytes(b">a\nACGT\n>b\nGGCC\n")
+    refused = run("score", "--input", str(two), "--ctx", "64", "--dump-logits", str(scored), check=False)
+    assert refused.returncode == 2 and b"exactly one record" in refused.stderr
+    assert run("run", "-p", "ACGT", "-n", "1", "--ctx", "64", "--top-k", "1", "--dump-layer", f"50:{layer}",
+               check=False).returncode == 2
+
+
 def test_bench_report_schema(tmp_path):
     raw = tmp_path / "dna.txt"
     raw.write_bytes(b"ACGTACGTAC")
