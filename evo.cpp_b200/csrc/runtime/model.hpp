@@ -159,7 +159,8 @@ class Context {
  public:
   ~Context();
   // q8_kv: keys and values are kept as per-vector int8 in lazily allocated pages of 16,384
-  // tokens (upstream's fast-q8-kv profile, docs/execution-profiles.md:96-127); head size 128 only.
+  // tokens (upstream's fast-q8-kv profile, docs/execution-profiles.md:96-127).  Any head size: steps of
+  // 1..8 rows read the pages directly at head size 128, everything else attends to their BF16 image.
   static int create(std::shared_ptr<ModelWeights> weights, std::size_t context_size,
                     ExecutionProfile profile, bool full_arena_for_fixtures,
                     std::unique_ptr<Context> *out, bool q8_kv = false);
