@@ -380,6 +380,16 @@ struct Core final {
     return status;
   }
 
+  Status chunk_embedding(const std::vector<TokenId> &tokens, const std::size_t layer, std::vector<float> *hidden) {
+    auto status = ready(hidden);
+    if (!status.ok()) return status;
+    if (tokens.empty()) return invalid("an embedding needs at least one token");
+    hidden->clear();
+    Rows rows{hidden};
+    return from_abi(evo_b200_context_embed_tokens(context, tokens.data(), tokens.size(), layer, 0, &Core::gather, &rows),
+                    "embedding of a continuation chunk");
+  }
+
   std::size_t position() const { return context == nullptr ? 0 : evo_context_position(context); }
   std::size_t activation_capacity() const { return context == nullptr ? 0 : evo_b200_context_activation_capacity(context); }
 };
@@ -461,8 +471,9 @@ Status SingleGpuModel::prefill_embedding(const std::vector<TokenId> &tokens, con
                                          std::vector<float> *embedding) {
   return impl_->core.embedding(tokens, layer, embedding);
 }
-Status SingleGpuModel::prefill_chunk_embedding(const std::vector<TokenId> &, std::size_t, std::vector<float> *) {
-  return not_offered("a chunked embedding on token ids");
+Status SingleGpuModel::prefill_chunk_embedding(const std::vector<TokenId> &tokens, const std::size_t layer,
+                                               std::vector<float> *embedding) {
+  return impl_->core.chunk_embedding(tokens, layer, embedding);
 }
 Status SingleGpuModel::decode(const TokenId token, std::vector<float> *logits) { return impl_->core.decode(token, logits); }
 Status SingleGpuModel::decode_with_dumps(const TokenId token, std::vector<float> *logits,
@@ -537,8 +548,9 @@ Status PipelineModel::prefill_embedding(const std::vector<TokenId> &tokens, cons
                                         std::vector<float> *embedding) {
   return impl_->core.embedding(tokens, layer, embedding);
 }
-Status PipelineModel::prefill_chunk_embedding(const std::vector<TokenId> &, std::size_t, std::vector<float> *) {
-  return not_offered("a chunked embedding on token ids");
+Status PipelineModel::prefill_chunk_embedding(const std::vector<TokenId> &tokens, const std::size_t layer,
+                                              std::vector<float> *embedding) {
+  return impl_->core.chunk_embedding(tokens, layer, embedding);
 }
 Status PipelineModel::decode(const TokenId token, std::vector<float> *logits) { return impl_->core.decode(token, logits); }
 Status PipelineModel::decode_with_dumps(const TokenId token, std::vector<float> *logits,

@@ -915,6 +915,37 @@ evo_status evo_b200_context_prefill_tokens(evo_context *context, const uint32_t 
   });
 }
 
+evo_status evo_b200_context_embed_tokens(evo_context *context, const uint32_t *tokens, size_t token_count, size_t layer,
+                                         int32_t first_chunk, evo_embedding_callback callback, void *user_data) {
+  return protect([&]() -> int {
+    if (context == nullptr || tokens == nullptr || token_count == 0 || callback == nullptr)
+      return fail(evob::kInvalidArgument, "context, tokens and callback are required");
+    if (context->failed || context->context->poisoned())
+      return fail(evob::kInvalidArgument, "context was invalidated by an earlier failure");
+    evob::Context &model = *context->context;
+    if (token_count > model.activation_capacity())
+      return fail(evob::kInvalidArgument, "an embedding chunk takes at most one activation chunk of tokens");
+    const std::size_t begin = first_chunk != 0 ? 0 : model.position();
+    if (token_count > model.context_capacity() - std::min(begin, model.context_capacity()))
+      return fail(evob::kInvalidArgument, "sequence exceeds the context capacity");
+    const std::vector<std::uint32_t> chunk(tokens, tokens + token_count);
+    std::vector<float> hidden;
+    const int status = model.prefill_chunk_embedding(chunk, layer, first_chunk != 0, &hidden);
+    if (status != kOk) {
+      if (model.poisoned()) context->failed = true;
+      return status;
+    }
+    const std::size_t width = model.config().width;
+    if (hidden.size() != token_count * width) return fail(evob::kInternal, "backend returned an incomplete embedding");
+    const evo_status delivered = callback(hidden.data(), token_count, width, begin, user_data);
+    if (delivered != EVO_STATUS_OK) {
+      context->failed = true;
+      return fail(valid_status(delivered) ? delivered : EVO_STATUS_INTERNAL, "embedding consumer aborted");
+    }
+    return kOk;
+  });
+}
+
 size_t evo_b200_context_activation_capacity(const evo_context *context) {
   return context == nullptr ? 0 : context->context->activation_capacity();
 }

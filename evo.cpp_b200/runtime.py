@@ -149,6 +149,8 @@ class EvoLibrary:
             lib.evo_b200_context_continue_device.argtypes = [V, V, Z, ctypes.POINTER(V)]
             lib.evo_b200_context_prefill_tokens.argtypes = [V, ctypes.POINTER(ctypes.c_uint32), Z, ctypes.c_int32,
                                                             LOGITS_CALLBACK, V]
+            lib.evo_b200_context_embed_tokens.argtypes = [V, ctypes.POINTER(ctypes.c_uint32), Z, Z, ctypes.c_int32,
+                                                          LOGITS_CALLBACK, V]
             lib.evo_b200_context_activation_capacity.restype = Z
             lib.evo_b200_context_activation_capacity.argtypes = [V]
             lib.evo_b200_read_model_config.argtypes = [ctypes.c_char_p, ctypes.c_int32, ctypes.POINTER(ModelConfig),
@@ -376,6 +378,12 @@ class Context:
         ids = (ctypes.c_uint32 * len(tokens))(*tokens)
         return self._collect(lambda cb: self.library.lib.evo_b200_context_prefill_tokens(
             self.handle, ids, len(tokens), mode, cb, None), self.vocab)
+
+    def embed_tokens(self, tokens, layer: int, first_chunk: bool = True) -> np.ndarray:
+        """evo_b200_context_embed_tokens: block output of `layer` for one chunk of token ids, F32 [tokens, width]."""
+        ids = (ctypes.c_uint32 * len(tokens))(*tokens)
+        return self._collect(lambda cb: self.library.lib.evo_b200_context_embed_tokens(
+            self.handle, ids, len(tokens), layer, int(first_chunk), cb, None), self.width)
 
     @property
     def activation_capacity(self) -> int:

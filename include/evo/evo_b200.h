@@ -58,6 +58,13 @@ enum {
 EVO_API evo_status evo_b200_context_prefill_tokens(evo_context *context, const uint32_t *tokens,
                                                    size_t token_count, int32_t mode,
                                                    evo_logits_callback callback, void *user_data);
+/* Block output of `layer` for one activation chunk of token ids (upstream prefill_embedding /
+ * prefill_chunk_embedding, include/evo/cuda/model.hpp:150-170): first_chunk != 0 starts a new sequence
+ * on any context, 0 continues the one a first chunk or a FRESH prefill started.  The context advances
+ * as by a prefill; the callback receives [token_count, width] and the position of the first row. */
+EVO_API evo_status evo_b200_context_embed_tokens(evo_context *context, const uint32_t *tokens,
+                                                 size_t token_count, size_t layer, int32_t first_chunk,
+                                                 evo_embedding_callback callback, void *user_data);
 /* Rows of one activation chunk (upstream activation_capacity(), include/evo/cuda/model.hpp:141, 222). */
 EVO_API size_t evo_b200_context_activation_capacity(const evo_context *context);
 /* The runtime configuration of a model file without loading its weights (upstream
