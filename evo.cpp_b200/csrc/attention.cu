@@ -204,15 +204,36 @@ attention_row_kernel(const bf16 *__restrict__ query,
     for (int j = threadIdx.x; j < total_keys; j += kRowThreads)
       target[j] = f2bf(j < visible ? scores[j] / row_sum : 0.0F);
   }
-  for (int d = threadIdx.x; d < head_dim; d += kRowThreads) {
-    float acc = 0.0F;
-    const bf16 *const v = value_cache + head * head_dim + d;
-    for (int j = 0; j < visible; ++j) {
-      const float p = kCachedRounding ? rbf(scores[j] / row_sum) : scores[j];
-      acc = fmaf(p, bf2f(v[static_cast<std::size_t>(j) * width]), acc);
+  // probabilities x values.  The block's threads form `lanes` key lanes x `dims` output dimensions;
+  // a thread walks every lanes-th key with four running sums (keys 0, 4, 8, ... of its own sequence in
+  // the first, and so on), the lanes' partial sums are then added in lane order.  One running sum over
+  // ten thousand keys loses enough low bits to move a BF16 result (it did at 10,240 keys against the
+  // reference bytes of upstream's known-answer test); blocked sums do not, and they overlap the loads.
+  __shared__ float lane_sums[kRowThreads];
+  const int dims = min(head_dim, kRowThreads);
+  const int lanes = kRowThreads / dims;
+  const int lane = threadIdx.x / dims;
+  for (int d0 = 0; d0 < head_dim; d0 += dims) {
+    const int d = d0 + threadIdx.x % dims;
+    const bool active = lane < lanes && d < head_dim;
+    float sums[4] = {0.0F, 0.0F, 0.0F, 0.0F};
+    if (active) {
+      const bf16 *const v = value_cache + head * head_dim + d;
+      int turn = 0;
+      for (int j = lane; j < visible; j += lanes, turn = (turn + 1) & 3) {
+        const float p = kCachedRounding ? rbf(scores[j] / row_sum) : scores[j];
+        sums[turn] = fmaf(p, bf2f(v[static_cast<std::size_t>(j) * width]), sums[turn]);
+      }
     }
-    if (!kCachedRounding) acc /= row_sum;
-    output[static_cast<std::size_t>(row) * width + head * head_dim + d] = f2bf(acc);
+    __syncthreads();  // the previous pass has read lane_sums
+    lane_sums[threadIdx.x] = (sums[0] + sums[1]) + (sums[2] + sums[3]);
+    __syncthreads();
+    if (active && lane == 0) {
+      float acc = lane_sums[threadIdx.x];
+      for (int other = 1; other < lanes; ++other) acc += lane_sums[other * dims + threadIdx.x];
+      if (!kCachedRounding) acc /= row_sum;
+      output[static_cast<std::size_t>(row) * width + head * head_dim + d] = f2bf(acc);
+    }
   }
 }
 
