@@ -272,7 +272,7 @@ Options parse(int argc, char **argv) {
       const std::string text = value(i);
       char *end = nullptr;
       const unsigned long long parsed = std::strtoull(text.c_str(), &end, 10);
-      if (text.empty() || text[0] == '-' || *end != '\0' || parsed < 1 || parsed > 1048576ULL)
+      if (text.empty() || text[0] < '0' || text[0] > '9' || *end != '\0' || parsed < 1 || parsed > 1048576ULL)
         die(EVO_STATUS_INVALID_ARGUMENT, "--force-prompt-threshold must be an integer in [1, 1048576]");
       o.force_prompt_threshold = static_cast<size_t>(parsed);
     } else if (a == "--dump-tokens") o.dump_tokens = true;
@@ -284,7 +284,8 @@ Options parse(int argc, char **argv) {
       const size_t colon = spec.find(':');
       char *end = nullptr;
       const unsigned long long layer = std::strtoull(spec.c_str(), &end, 10);
-      if (colon == std::string::npos || colon == 0 || colon + 1 >= spec.size() || end != spec.c_str() + colon)
+      if (colon == std::string::npos || colon == 0 || colon + 1 >= spec.size() || end != spec.c_str() + colon ||
+          spec[0] < '0' || spec[0] > '9')
         die(EVO_STATUS_INVALID_ARGUMENT, "--dump-layer must be a nonnegative INDEX:PATH");
       o.dump_layer = static_cast<size_t>(layer);
       o.dump_layer_path = spec.substr(colon + 1);

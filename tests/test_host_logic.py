@@ -153,6 +153,28 @@ def test_model_configuration_is_read_without_a_device(evo, rt):
     assert (config.heads, config.hcm_filter_length, config.short_filter_length) == (2, 4, 3)
 
 
+def test_cli_refuses_bad_diagnostic_flags_before_any_device_work():
+    """Option errors of the generation / scoring diagnostics (upstream src/cli.cpp:654-667, 737-762, 1049-1051):
+    exit code 2 and upstream's wording, decided while parsing."""
+    import subprocess
+
+    binary = ROOT / "evo.cpp_b200" / "evo"
+
+    def refused(*arguments):
+        done = subprocess.run([str(binary), *arguments], capture_output=True, timeout=60)
+        assert done.returncode == 2, (arguments, done.returncode, done.stderr)
+        return done.stderr.decode()
+
+    for bad in ("0", "-3", "1048577", "ten", ""):
+        assert "--force-prompt-threshold must be an integer in [1, 1048576]" in refused(
+            "run", "-m", "x", "-p", "AC", "--force-prompt-threshold", bad)
+    assert "only valid for generation" in refused("score", "-m", "x", "--input", "y", "--force-prompt-threshold", "3")
+    for bad in ("17", ":path", "17:", "x:path", "-1:path"):
+        assert "--dump-layer must be a nonnegative INDEX:PATH" in refused("run", "-m", "x", "-p", "AC", "--dump-layer", bad)
+    assert "--dump-logits path must not be empty" in refused("run", "-m", "x", "-p", "AC", "--dump-logits", "")
+    assert "generation and scoring only" in refused("bench", "-m", "x", "--input", "y", "--dump-logits", "z.npy")
+
+
 def test_sampler_matches_upstream_rule(evo, rt):
     assert mt19937_64_first_output(5489) == 14514284786278117030  # the standard's check value seed
     logits = np.array([0.5, 2.0, 2.0, -1.0, 1.5], np.float32)
