@@ -153,6 +153,39 @@ def test_model_configuration_is_read_without_a_device(evo, rt):
     assert (config.heads, config.hcm_filter_length, config.short_filter_length) == (2, 4, 3)
 
 
+def test_model_configuration_reader_refuses_what_the_loader_refuses(evo, rt, pkg, tmp_path):
+    """The three refusals of upstream's configuration reader that its model test pins
+    (tests/test_cuda_model.cu:195-208), from evo_b200_read_model_config: no device is involved."""
+    import importlib
+
+    art = importlib.import_module("evo_cpp_b200.artifact")
+    base = dict(width=64, layers=4, heads=1, inner=128, hcs_groups=8, hcm_groups=8)
+
+    def write(name, mutate, extra=None):
+        spec = art.fixture_spec(**base)
+        mutate(spec)
+        tensors = list(art.synthetic_tensors(spec, seed=1))
+        if extra is not None:
+            tensors.append(extra)
+        path = tmp_path / f"{name}.safetensors"
+        art.write_model(path, spec["metadata"], tensors)
+        return path
+
+    good = write("good", lambda s: None)
+    config, mixers = evo.read_model_config(good, allow_test_fixture=True)
+    assert (config.layers, config.width, config.inner_width) == (4, 64, 128) and len(mixers) == 4
+    for path, code, fragment in (
+            (write("disagrees", lambda s: s["metadata"].update({"hyena_projection_dtype": art.typed("E4M3_SW")})), 4,
+             "disagrees"),
+            (write("dtype", lambda s: s["metadata"].update({"hyena_projection_dtype": art.typed("INT8")})), 5,
+             "unsupported Hyena projection dtype: INT8"),
+            (write("extra", lambda s: None, ("blocks.0.surplus", "F32", [4], bytes(16))), 4,
+             "unknown tensor for model profile")):
+        with pytest.raises(rt.EvoError) as refused:
+            evo.read_model_config(path, allow_test_fixture=True)
+        assert refused.value.code == code and fragment in str(refused.value), str(refused.value)
+
+
 def test_cli_refuses_bad_diagnostic_flags_before_any_device_work():
     """Option errors of the generation / scoring diagnostics (upstream src/cli.cpp:654-667, 737-762, 1049-1051):
     exit code 2 and upstream's wording, decided while parsing."""
