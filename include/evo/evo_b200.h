@@ -72,7 +72,8 @@ EVO_API size_t evo_b200_context_activation_capacity(const evo_context *context);
  * the same refusals (a synthetic fixture needs allow_test_fixture; precision metadata that disagrees
  * with the configuration, an unsupported projection dtype and tensors outside the profile's exact set
  * are rejected here, before any device work).  mixer_types (optional) receives one code per block -
- * 0 HCS, 1 HCM, 2 HCL, 3 attention - up to mixer_capacity. */
+ * 0 HCS, 1 HCM, 2 HCL, 3 attention - up to mixer_capacity.  The three names are NUL-terminated and cut
+ * at 63 bytes. */
 typedef struct evo_b200_model_config {
   size_t struct_size;
   char model_id[64];
